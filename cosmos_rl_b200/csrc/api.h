@@ -1,0 +1,106 @@
+// C ABI of the sm_100a kernel library (libb200rl). Every launcher takes raw device pointers and a
+// stream, allocates nothing unless stated, and returns 0 or a negative B200_ERR_* code. Kernels
+// that can wait (tensor-core pipelines, peer flags) also take a device `status` word that stays 0
+// on success and receives a b200::ST_* code when a bounded wait ran out.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define B200_ERR_ARG (-1)
+#define B200_ERR_TENSORMAP (-2)
+#define B200_ERR_LAUNCH (-3)
+#define B200_ERR_TOO_LARGE (-4)
+#define B200_ERR_RUNTIME (-5)
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- tensor-core GEMMs ---------------------------------------------------------------------------
+int b200_gemm_bf16_nt(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                      long long ldc, int out_fp32, int accumulate, uint32_t* status, int num_sms,
+                      cudaStream_t stream);
+
+// Fused lm_head GEMM + per-token log-prob statistics, never materialising [T, V] logits.
+//   hidden [T, H] bf16, weight [V, H] bf16, labels [T] int64 (label < 0: row ignored)
+//   partial [T, nsplit, 4] fp32 scratch: (max, sumexp, label_logit, sum p_unnorm*logit)
+// followed by b200_logprob_combine -> logprob [T], lse [T], entropy [T] (fp32).
+int b200_lmhead_logprob_partial(const void* hidden, const void* weight, const long long* labels, float* partial,
+                                int T, int V, int H, long long ldh, long long ldw, float inv_temperature,
+                                int nsplit, uint32_t* status, int num_sms, cudaStream_t stream);
+int b200_logprob_combine(const float* partial, const long long* labels, float* logprob, float* lse, float* entropy,
+                         int T, int nsplit, cudaStream_t stream);
+// Backward helper: dlogits[T, Vc] (bf16) = (softmax(logits/temp) * (g_lp_total) - onehot * g_lp) * inv_temp for a vocab
+// chunk [v0, v0+Vc), recomputing the logits tile on the tensor cores.
+int b200_lmhead_dlogits(const void* hidden, const void* weight, const long long* labels, const float* lse,
+                        const float* g_logprob, const float* g_entropy, const float* entropy, void* dlogits, int T,
+                        int V, int H, long long ldh, long long ldw, int v0, int Vc, long long ldd,
+                        float inv_temperature, uint32_t* status, int num_sms, cudaStream_t stream);
+
+// ---- normalisation / activation / rotary ------------------------------------------------------------
+int b200_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* residual_out, float* rstd,
+                     int T, int H, float eps, cudaStream_t stream);
+int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                     float* dw_partial, int n_partial, int T, int H, cudaStream_t stream);
+int b200_colsum_f32(const float* partial, float* out, int rows, int cols, int accumulate, cudaStream_t stream);
+int b200_rope_inplace(void* q, void* k, const long long* positions, int T, int hq, int hkv, int d, long long q_stride,
+                      long long k_stride, float theta, int backward, cudaStream_t stream);
+int b200_swiglu_fwd(const void* gate_up, void* out, long long T, int I, cudaStream_t stream);
+int b200_swiglu_bwd(const void* dout, const void* gate_up, void* dgate_up, long long T, int I, cudaStream_t stream);
+
+// ---- optimizer -----------------------------------------------------------------------------------------
+// Flat fused AdamW on fp32 master weights with bf16 (or fp32) grads; writes the bf16 compute copy.
+// grad_scale_dev: device scalar multiplied into every gradient (clip coefficient), may be null.
+int b200_adamw(float* master, float* m, float* v, const void* grad, int grad_fp32, void* param_bf16, long long n,
+               float lr, float beta1, float beta2, float eps, float weight_decay, float bias1, float bias2,
+               const float* grad_scale_dev, cudaStream_t stream);
+int b200_sumsq(const void* x, int is_fp32, long long n, float* out_accum, cudaStream_t stream);
+int b200_clip_coef(const float* sumsq, float max_norm, float* coef_out, float* norm_out, cudaStream_t stream);
+
+// ---- sampling --------------------------------------------------------------------------------------------
+// logits [B, V] (fp32 or bf16), per-row temperature/top_p/top_k; writes token [B] (int64) and its log-prob
+// under softmax(logits / temperature).
+int b200_sample(const void* logits, int logits_bf16, long long ld, int B, int V, const float* temperature,
+                const float* top_p, const int* top_k, unsigned long long seed, unsigned long long offset,
+                long long* tokens, float* logprobs, cudaStream_t stream);
+
+// ---- attention ----------------------------------------------------------------------------------------------
+// Paged KV cache layout: [num_pages, 2 (k,v), page_size, hkv, d] bf16.
+int b200_kv_append(const void* k, const void* v, void* cache, const int* slot_mapping, int T, int hkv, int d,
+                   long long k_stride, long long v_stride, int page_size, cudaStream_t stream);
+int b200_paged_decode(const void* q, const void* cache, const int* block_table, const int* seq_lens, void* out,
+                      float* scratch, int B, int hq, int hkv, int d, int page_size, int max_pages, int nsplit,
+                      float scale, cudaStream_t stream);
+// Varlen causal flash attention (packed sequences, GQA). q [T,hq,d], k/v [T,hkv,d] with row strides.
+int b200_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_seqlens,
+                   int n_seqs, int T, int hq, int hkv, int d, long long q_stride, long long kv_stride,
+                   long long o_stride, float scale, int max_seqlen, cudaStream_t stream);
+int b200_flash_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+                   void* dq, void* dk, void* dv, float* dq_accum, float* delta, const int* cu_seqlens, int n_seqs,
+                   int T, int hq, int hkv, int d, long long q_stride, long long kv_stride, long long o_stride,
+                   float scale, int max_seqlen, cudaStream_t stream);
+
+// ---- quantisation ----------------------------------------------------------------------------------------------
+// bf16 [R, C] -> e4m3 [R, C] with one fp32 scale per 128 x 128 block (weights) or per 1 x 128 (activations).
+int b200_quant_fp8_block(const void* src, long long ld_src, void* dst, long long ld_dst, float* scales, int R, int C,
+                         int block_rows, cudaStream_t stream);
+
+// ---- peer-memory weight sync -------------------------------------------------------------------------------------
+// One descriptor = copy a [rows, cols] bf16 rectangle from (possibly another GPU's) memory into a local
+// destination, optionally quantising to block-scaled fp8 on the way.
+struct B200CopyDesc {
+  const void* src;      // peer or local pointer
+  void* dst;            // local pointer (bf16 or e4m3)
+  float* dst_scale;     // fp8 only: scale for this rectangle's 128x128 blocks, row-major [ceil(rows/128), ld_scale]
+  long long src_ld;     // elements
+  long long dst_ld;     // elements
+  int rows, cols;
+  int ld_scale;
+  int quant;            // 0: bf16 copy, 1: fp8 e4m3 128x128 block-scaled (rows/cols of dst start on block boundaries)
+};
+int b200_reshard_pull(const B200CopyDesc* descs_dev, const int* tile_prefix_dev, int n_desc, int total_tiles,
+                      uint32_t* status, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,258 @@
+// Persistent, warp-specialised tcgen05 GEMM main loop for sm_100a.
+//
+//   D[M, N] = A[M, K] * B[N, K]^T      (both operands K-major, bf16, fp32 accumulate)
+//
+// One CTA per SM walks a list of 128 x BN output tiles. Warp 0 streams A/B tiles
+// into a STAGES-deep shared-memory ring with TMA (128-byte swizzle), warp 1 issues
+// tcgen05.mma (M=128, N=BN, K=16) from a single elected thread into one of two
+// TMEM accumulators, and warps 2..5 drain the other accumulator with tcgen05.ld
+// and hand 32-column row fragments to an Epilogue functor. The epilogue of tile i
+// overlaps the main loop of tile i+1.
+//
+// The Epilogue and the tile Schedule are template parameters so that fused
+// kernels (online-softmax log-prob, gather-from-peer prologues, ...) reuse the
+// same pipeline. All mbarrier waits are bounded; on a timeout the kernel records
+// a status code, frees its TMEM and returns.
+#pragma once
+#include "sm100.cuh"
+
+namespace b200 {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int GEMM_THREADS = 192;
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_BYTES = 256;
+  // +1024 so the ring can be aligned to 1024 bytes inside dynamic shared memory
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+};
+
+// Default schedule: grouped raster over (m, n) tiles, strided over the grid.
+struct RasterSchedule {
+  int num_m, num_n, total;
+  template <class P>
+  __device__ __forceinline__ void init(int M, int N, int BN, const P&) {
+    num_m = (M + GEMM_BM - 1) / GEMM_BM;
+    num_n = (N + BN - 1) / BN;
+    total = num_m * num_n;
+  }
+  __device__ __forceinline__ bool get(int it, int& m_blk, int& n_blk) const {
+    int t = blockIdx.x + it * gridDim.x;
+    if (t >= total) return false;
+    constexpr int G = 8;
+    int group_size = G * num_n;
+    int group = t / group_size;
+    int first_m = group * G;
+    int gsz = min(num_m - first_m, G);
+    int r = t - group * group_size;
+    m_blk = first_m + r % gsz;
+    n_blk = r / gsz;
+    return true;
+  }
+};
+
+// Epilogue concept:
+//   struct Epi { struct Params {...};
+//     __device__ void tile_begin(const Params&, int m_blk, int n_blk, int row /*0..127*/);
+//     __device__ void chunk(const Params&, int m_blk, int n_blk, int row, int col0 /*within tile*/, const float (&v)[32]);
+//     __device__ void tile_end(const Params&, int m_blk, int n_blk, int row);
+//     __device__ void finish(const Params&);   // after the last tile
+//   };
+
+template <int BN, int STAGES, class Epi, class Sched>
+__device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUtensorMap* tmB, int M, int N, int K,
+                                              const typename Epi::Params& ep, uint32_t* status) {
+  using SM = GemmSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * SM::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;   // [2]
+  uint64_t* tempty_bar = tfull_bar + 2;       // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);  // one arrive per epilogue warp
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(tmA);
+    tma_prefetch_desc(tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  Sched sched;
+  sched.init(M, N, BN, ep);
+  const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      int m_blk, n_blk;
+      for (int it = 0; sched.get(it, m_blk, n_blk) && !*abort_flag; ++it) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            atomicCAS(status, ST_OK, ST_TIMEOUT_EMPTY);
+            *abort_flag = 1;
+            break;
+          }
+          uint8_t* sa = smem + stage * SM::STAGE_BYTES;
+          uint8_t* sb = sa + SM::A_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], SM::STAGE_BYTES);
+          tma_load_2d(sa, tmA, &full_bar[stage], kb * GEMM_BK, m_blk * GEMM_BM);
+          tma_load_2d(sb, tmB, &full_bar[stage], kb * GEMM_BK, n_blk * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(GEMM_BM, BN);
+      uint32_t stage = 0, phase = 0;
+      uint32_t acc = 0, acc_phase = 0;
+      int m_blk, n_blk;
+      for (int it = 0; sched.get(it, m_blk, n_blk) && !*abort_flag; ++it) {
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1)) {
+          atomicCAS(status, ST_OK, ST_TIMEOUT_TMEM_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) {
+            atomicCAS(status, ST_OK, ST_TIMEOUT_FULL);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * SM::STAGE_BYTES);
+          const uint32_t sb = sa + SM::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            uint64_t ad = umma_desc_kmajor_sw128(sa + k * 32);
+            uint64_t bd = umma_desc_kmajor_sw128(sb + k * 32);
+            umma_bf16_ss(tmem_d, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);  // frees this smem stage once the MMAs retire
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(&tfull_bar[acc]);  // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (warps 2..5) ---------------------
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may access
+    const int row = quad * 32 + lane;
+    Epi epi;
+    uint32_t acc = 0, acc_phase = 0;
+    int m_blk, n_blk;
+    for (int it = 0; sched.get(it, m_blk, n_blk) && !*abort_flag; ++it) {
+      if (!mbar_wait(&tfull_bar[acc], acc_phase)) {
+        atomicCAS(status, ST_OK, ST_TIMEOUT_TMEM_FULL);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after_sync();
+      epi.tile_begin(ep, m_blk, n_blk, row);
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c, r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        epi.chunk(ep, m_blk, n_blk, row, c, v);
+      }
+      epi.tile_end(ep, m_blk, n_blk, row);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    epi.finish(ep);
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    // let copies that were already issued land before the CTA's shared memory is released
+    for (int i = 0; i < 100; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side: tensor-map encoding through the driver entry point (no -lcuda).
+// ---------------------------------------------------------------------------
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline PFN_encodeTiled get_encode_tiled() {
+  static PFN_encodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<PFN_encodeTiled>(p);
+  }
+  return fn;
+}
+
+// Row-major [rows, cols] matrix of 2-byte (or 1-byte) elements with leading dimension ld (elements);
+// box = box_rows x box_cols, 128-byte swizzle (box_cols * elem_bytes must be 128).
+inline int make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                        uint32_t box_rows, uint32_t box_cols, int elem_bytes) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  if (!enc) return -1;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * elem_bytes) & 15)) return -2;
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstr[1] = {ld * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = enc(out, dt, 2, const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+}  // namespace b200

@@ -1,0 +1,386 @@
+"""Differentiable front-ends of the sm_100a kernels.
+
+CUDA tensors always run the hand-written kernels from ``libb200rl.so`` (a missing library raises);
+CPU tensors run the fp32 PyTorch statements in :mod:`cosmos_rl_b200.ops.reference`, which are also the
+test oracles. Tensor layouts follow the packed ("varlen") convention used across the framework:
+activations are ``[T, ...]`` with ``T`` the total number of tokens of the micro-batch.
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Optional, Tuple
+
+import torch
+
+from . import native, reference
+
+_N_PARTIAL_NORM = 296  # CTAs (2 per SM) that accumulate RMSNorm weight-gradient partials
+
+
+def _c(t: torch.Tensor) -> torch.Tensor:
+    return t if t.is_contiguous() else t.contiguous()
+
+
+# --------------------------------------------------------------------------------------------------
+# RMSNorm
+# --------------------------------------------------------------------------------------------------
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps, residual):
+        shape = x.shape
+        H = shape[-1]
+        x2 = _c(x).view(-1, H)
+        T = x2.shape[0]
+        res2 = _c(residual).view(-1, H) if residual is not None else None
+        y = torch.empty_like(x2)
+        res_out = torch.empty_like(x2) if residual is not None else None
+        rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+        L = native.lib()
+        native.check(L.b200_rmsnorm_fwd(native.ptr(x2), native.ptr(res2), native.ptr(weight), native.ptr(y),
+                                        native.ptr(res_out), native.ptr(rstd), T, H, eps, native.stream()),
+                     "rmsnorm_fwd")
+        h = res_out if residual is not None else x2
+        ctx.save_for_backward(h, weight, rstd)
+        ctx.has_res = residual is not None
+        ctx.shape = shape
+        if residual is not None:
+            return y.view(shape), res_out.view(shape)
+        return y.view(shape), None
+
+    @staticmethod
+    def backward(ctx, dy, dres_out):
+        h, weight, rstd = ctx.saved_tensors
+        H = h.shape[-1]
+        T = h.shape[0]
+        dy2 = _c(dy).view(-1, H)
+        dres2 = _c(dres_out).view(-1, H) if dres_out is not None else None
+        dx = torch.empty_like(h)
+        n_partial = min(_N_PARTIAL_NORM, max(T, 1))
+        dwp = torch.empty(n_partial, H, dtype=torch.float32, device=h.device)
+        L = native.lib()
+        native.check(L.b200_rmsnorm_bwd(native.ptr(dy2), native.ptr(h), native.ptr(weight), native.ptr(rstd),
+                                        native.ptr(dres2), native.ptr(dx), native.ptr(dwp), n_partial, T, H,
+                                        native.stream()), "rmsnorm_bwd")
+        dw = torch.empty(H, dtype=torch.float32, device=h.device)
+        native.check(L.b200_colsum_f32(native.ptr(dwp), native.ptr(dw), n_partial, H, 0, native.stream()), "colsum")
+        dxv = dx.view(ctx.shape)
+        return dxv, dw.to(weight.dtype), None, (dxv if ctx.has_res else None)
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, residual: Optional[torch.Tensor] = None):
+    """Returns ``(y, new_residual)``; ``new_residual`` is ``x + residual`` (or ``None`` without residual)."""
+    if x.is_cuda:
+        if x.dtype != torch.bfloat16:
+            raise TypeError("rms_norm on CUDA expects bf16 activations")
+        return _RMSNorm.apply(x, weight, eps, residual)
+    return reference.rms_norm(x, weight, eps, residual)
+
+
+# --------------------------------------------------------------------------------------------------
+# RoPE (in place on views of the fused qkv projection)
+# --------------------------------------------------------------------------------------------------
+def _rope_native(q, k, positions, theta, backward):
+    T, hq, d = q.shape
+    hkv = k.shape[1] if k is not None else 0
+    assert q.stride(-1) == 1 and q.stride(1) == d
+    if k is not None:
+        assert k.stride(-1) == 1 and k.stride(1) == d
+    L = native.lib()
+    native.check(L.b200_rope_inplace(native.ptr(q), native.ptr(k), native.ptr(positions), T, hq, hkv, d, q.stride(0),
+                                     k.stride(0) if k is not None else 0, float(theta), 1 if backward else 0,
+                                     native.stream()), "rope")
+
+
+class _RoPE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, positions, theta):
+        _rope_native(q, k, positions, theta, False)
+        ctx.mark_dirty(q, k)
+        ctx.save_for_backward(positions)
+        ctx.theta = theta
+        return q, k
+
+    @staticmethod
+    def backward(ctx, dq, dk):
+        (positions,) = ctx.saved_tensors
+        dq = dq.contiguous() if not (dq.stride(-1) == 1 and dq.stride(1) == dq.shape[-1]) else dq.clone()
+        dk = dk.contiguous() if not (dk.stride(-1) == 1 and dk.stride(1) == dk.shape[-1]) else dk.clone()
+        _rope_native(dq, dk, positions, ctx.theta, True)
+        return dq, dk, None, None
+
+
+def apply_rope(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, theta: float):
+    """Rotary embedding of ``q [T, hq, d]`` and ``k [T, hkv, d]``. On CUDA the rotation is done in place
+    (the inputs must not be needed un-rotated afterwards) and positions must be int64."""
+    if q.is_cuda:
+        positions = positions.to(torch.int64)
+        if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad):
+            return _RoPE.apply(q, k, positions, theta)
+        _rope_native(q, k, positions, theta, False)
+        return q, k
+    return reference.apply_rope(q, k, positions, theta)
+
+
+class _RoPEQKV(torch.autograd.Function):
+    """In-place rotation of the q and k column blocks of a fused ``[T, (hq + 2 hkv) d]`` projection."""
+
+    @staticmethod
+    def forward(ctx, qkv, positions, hq, hkv, d, theta):
+        T = qkv.shape[0]
+        q = qkv[:, : hq * d].unflatten(-1, (hq, d))
+        k = qkv[:, hq * d: (hq + hkv) * d].unflatten(-1, (hkv, d))
+        _rope_native(q, k, positions, theta, False)
+        ctx.mark_dirty(qkv)
+        ctx.save_for_backward(positions)
+        ctx.cfg = (hq, hkv, d, theta)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, dqkv):
+        (positions,) = ctx.saved_tensors
+        hq, hkv, d, theta = ctx.cfg
+        dqkv = dqkv.clone(memory_format=torch.contiguous_format)
+        q = dqkv[:, : hq * d].unflatten(-1, (hq, d))
+        k = dqkv[:, hq * d: (hq + hkv) * d].unflatten(-1, (hkv, d))
+        _rope_native(q, k, positions, theta, True)
+        return dqkv, None, None, None, None, None
+
+
+def rope_qkv_(qkv: torch.Tensor, positions: torch.Tensor, hq: int, hkv: int, d: int, theta: float) -> torch.Tensor:
+    """Rotary embedding applied to the q and k blocks of a fused qkv projection ``[T, (hq + 2 hkv) d]``.
+    In place on CUDA (returns the same tensor); a new tensor on CPU."""
+    if qkv.is_cuda:
+        positions = positions.to(torch.int64)
+        if torch.is_grad_enabled() and qkv.requires_grad:
+            return _RoPEQKV.apply(qkv, positions, hq, hkv, d, theta)
+        q = qkv[:, : hq * d].unflatten(-1, (hq, d))
+        k = qkv[:, hq * d: (hq + hkv) * d].unflatten(-1, (hkv, d))
+        _rope_native(q, k, positions, theta, False)
+        return qkv
+    T = qkv.shape[0]
+    q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
+    q, k = reference.apply_rope(q.reshape(T, hq, d), k.reshape(T, hkv, d), positions, theta)
+    return torch.cat([q.reshape(T, -1), k.reshape(T, -1), v], dim=-1)
+
+
+# --------------------------------------------------------------------------------------------------
+# SwiGLU
+# --------------------------------------------------------------------------------------------------
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate_up):
+        I2 = gate_up.shape[-1]
+        gu = _c(gate_up).view(-1, I2)
+        out = torch.empty(gu.shape[0], I2 // 2, dtype=gu.dtype, device=gu.device)
+        native.check(native.lib().b200_swiglu_fwd(native.ptr(gu), native.ptr(out), gu.shape[0], I2 // 2,
+                                                  native.stream()), "swiglu_fwd")
+        ctx.save_for_backward(gu)
+        ctx.shape = gate_up.shape
+        return out.view(*gate_up.shape[:-1], I2 // 2)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gu,) = ctx.saved_tensors
+        d2 = _c(dout).view(-1, gu.shape[1] // 2)
+        dgu = torch.empty_like(gu)
+        native.check(native.lib().b200_swiglu_bwd(native.ptr(d2), native.ptr(gu), native.ptr(dgu), gu.shape[0],
+                                                  gu.shape[1] // 2, native.stream()), "swiglu_bwd")
+        return dgu.view(ctx.shape)
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    if gate_up.is_cuda:
+        return _SwiGLU.apply(gate_up)
+    return reference.swiglu(gate_up)
+
+
+# --------------------------------------------------------------------------------------------------
+# dense GEMM (tcgen05)
+# --------------------------------------------------------------------------------------------------
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16,
+            accumulate: bool = False) -> torch.Tensor:
+    """``a [M, K] @ b [N, K]^T`` on the tcgen05 kernel (bf16 in, bf16 or fp32 out)."""
+    assert a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.stride(-1) == 1 and b.stride(-1) == 1 and a.dim() == 2 and b.dim() == 2
+    M, K = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    st = native.status_word(a.device)
+    dev = a.device.index if a.device.index is not None else torch.cuda.current_device()
+    native.check(native.lib().b200_gemm_bf16_nt(native.ptr(a), native.ptr(b), native.ptr(out), M, N, K, a.stride(0),
+                                                b.stride(0), out.stride(0), 1 if out.dtype == torch.float32 else 0,
+                                                1 if accumulate else 0, native.ptr(st), native.num_sms(dev),
+                                                native.stream()), "gemm_bf16_nt")
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
+# fused lm_head + log-prob + entropy
+# --------------------------------------------------------------------------------------------------
+def _pick_nsplit(T: int, V: int, sms: int) -> int:
+    num_m = (T + 127) // 128
+    num_n = (V + 255) // 256
+    best, best_score = 1, -1.0
+    for ns in range(1, min(num_n, 64) + 1):
+        units = num_m * ns
+        waves = math.ceil(units / sms)
+        eff = units / (waves * sms)
+        # prefer full waves, then fewer splits (less scratch, fewer partial merges)
+        score = eff - 0.002 * ns
+        if score > best_score:
+            best, best_score = ns, score
+    return best
+
+
+_DLOGITS_CHUNK = int(os.environ.get("B200RL_DLOGITS_CHUNK", "16384"))
+
+
+class _FusedLogprob(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, temperature, want_entropy):
+        T, H = hidden.shape
+        V = weight.shape[0]
+        hidden = _c(hidden)
+        dev = hidden.device.index if hidden.device.index is not None else torch.cuda.current_device()
+        sms = native.num_sms(dev)
+        nsplit = _pick_nsplit(T, V, sms)
+        partial = torch.empty(T, nsplit, 4, dtype=torch.float32, device=hidden.device)
+        lp = torch.empty(T, dtype=torch.float32, device=hidden.device)
+        lse = torch.empty_like(lp)
+        ent = torch.empty_like(lp)
+        st = native.status_word(hidden.device)
+        L = native.lib()
+        native.check(L.b200_lmhead_logprob_partial(native.ptr(hidden), native.ptr(weight), native.ptr(labels),
+                                                   native.ptr(partial), T, V, H, hidden.stride(0), weight.stride(0),
+                                                   1.0 / temperature, nsplit, native.ptr(st), sms, native.stream()),
+                     "lmhead_logprob_partial")
+        native.check(L.b200_logprob_combine(native.ptr(partial), native.ptr(labels), native.ptr(lp), native.ptr(lse),
+                                            native.ptr(ent), T, nsplit, native.stream()), "logprob_combine")
+        ctx.save_for_backward(hidden, weight, labels, lse, ent)
+        ctx.temperature = temperature
+        ctx.want_entropy = want_entropy
+        ctx.sms = sms
+        return lp, ent
+
+    @staticmethod
+    def backward(ctx, g_lp, g_ent):
+        hidden, weight, labels, lse, ent = ctx.saved_tensors
+        T, H = hidden.shape
+        V = weight.shape[0]
+        g_lp = _c(g_lp.float())
+        use_ent = ctx.want_entropy and g_ent is not None
+        g_ent_t = _c(g_ent.float()) if use_ent else None
+        st = native.status_word(hidden.device)
+        L = native.lib()
+        need_dh = ctx.needs_input_grad[0]
+        need_dw = ctx.needs_input_grad[1]
+        dh = torch.zeros(T, H, dtype=torch.float32, device=hidden.device) if need_dh else None
+        dw = torch.empty_like(weight) if need_dw else None
+        chunk = min(_DLOGITS_CHUNK, V)
+        buf = torch.empty(T, chunk, dtype=torch.bfloat16, device=hidden.device)
+        for v0 in range(0, V, chunk):
+            vc = min(chunk, V - v0)
+            dl = buf[:, :vc]
+            native.check(L.b200_lmhead_dlogits(native.ptr(hidden), native.ptr(weight), native.ptr(labels),
+                                               native.ptr(lse), native.ptr(g_lp), native.ptr(g_ent_t),
+                                               native.ptr(ent) if use_ent else None, native.ptr(buf), T, V, H,
+                                               hidden.stride(0), weight.stride(0), v0, vc, buf.stride(0),
+                                               1.0 / ctx.temperature, native.ptr(st), ctx.sms, native.stream()),
+                         "lmhead_dlogits")
+            if need_dh:
+                dh.add_(torch.mm(dl, weight[v0:v0 + vc]))
+            if need_dw:
+                torch.mm(dl.t(), hidden, out=dw[v0:v0 + vc])
+        return (dh.to(hidden.dtype) if need_dh else None), dw, None, None, None
+
+
+def fused_logprob(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0,
+                  want_entropy: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Log-prob of ``labels [T]`` and entropy under ``softmax(hidden @ weight.T / temperature)`` without
+    materialising the logits. ``hidden [T, H]`` bf16, ``weight [V, H]`` bf16. Returns fp32 ``(logprob, entropy)``."""
+    if hidden.is_cuda:
+        labels = labels.to(torch.int64)
+        return _FusedLogprob.apply(hidden, weight, labels, float(temperature), want_entropy)
+    return reference.logprob_entropy(hidden, weight, labels, temperature)
+
+
+# --------------------------------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------------------------------
+def varlen_attention(q, k, v, cu_seqlens, max_seqlen: int, scale: Optional[float] = None):
+    """Causal GQA attention over packed sequences."""
+    if q.is_cuda:
+        from . import attention
+        return attention.varlen_attention_cuda(q, k, v, cu_seqlens, max_seqlen, scale)
+    return reference.varlen_attention(q, k, v, cu_seqlens, scale)
+
+
+def kv_append(k, v, cache, slot_mapping):
+    if k.is_cuda:
+        T, hkv, d = k.shape
+        assert k.stride(-1) == 1 and k.stride(1) == d and v.stride(-1) == 1 and v.stride(1) == d
+        native.check(native.lib().b200_kv_append(native.ptr(k), native.ptr(v), native.ptr(cache),
+                                                 native.ptr(slot_mapping), T, hkv, d, k.stride(0), v.stride(0),
+                                                 cache.shape[3], native.stream()), "kv_append")
+    else:
+        reference.kv_append(k, v, cache, slot_mapping)
+
+
+def paged_decode(q, cache, block_table, seq_lens, scale: Optional[float] = None, nsplit: Optional[int] = None,
+                 scratch: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):
+    """Decode attention of ``q [B, hq, d]`` against the paged cache ``[pages, 2, hkv, page_size, d]``."""
+    if not q.is_cuda:
+        return reference.paged_decode(q, cache, block_table, seq_lens, scale)
+    B, hq, d = q.shape
+    hkv, page_size = cache.shape[2], cache.shape[3]
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    if nsplit is None:
+        # fill the machine: B*hkv CTAs per split
+        nsplit = max(1, min(16, (2 * 148) // max(1, B * hkv)))
+    if out is None:
+        out = torch.empty_like(q)
+    if nsplit > 1 and scratch is None:
+        scratch = torch.empty(B * hq * nsplit * (d + 2), dtype=torch.float32, device=q.device)
+    native.check(native.lib().b200_paged_decode(native.ptr(_c(q)), native.ptr(cache), native.ptr(block_table),
+                                                native.ptr(seq_lens), native.ptr(out), native.ptr(scratch), B, hq,
+                                                hkv, d, page_size, block_table.shape[1], nsplit, scale,
+                                                native.stream()), "paged_decode")
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
+# sampling
+# --------------------------------------------------------------------------------------------------
+def sample(logits: torch.Tensor, temperature=None, top_p=None, top_k=None, seed: int = 0, offset: int = 0,
+           generator: Optional[torch.Generator] = None):
+    """Returns ``(tokens [B] int64, logprobs [B] fp32)``; per-row ``temperature/top_p`` fp32 and ``top_k`` int32."""
+    if not logits.is_cuda:
+        return reference.sample(logits, temperature, top_p, top_k, generator)
+    B, V = logits.shape
+    assert logits.stride(-1) == 1 and logits.dtype in (torch.float32, torch.bfloat16)
+    toks = torch.empty(B, dtype=torch.int64, device=logits.device)
+    lps = torch.empty(B, dtype=torch.float32, device=logits.device)
+    native.check(native.lib().b200_sample(native.ptr(logits), 1 if logits.dtype == torch.bfloat16 else 0,
+                                          logits.stride(0), B, V, native.ptr(temperature), native.ptr(top_p),
+                                          native.ptr(top_k), seed & (2 ** 64 - 1), offset & (2 ** 64 - 1),
+                                          native.ptr(toks), native.ptr(lps), native.stream()), "sample")
+    return toks, lps
+
+
+# --------------------------------------------------------------------------------------------------
+# fp8 block quantisation
+# --------------------------------------------------------------------------------------------------
+def quant_fp8_block(w: torch.Tensor, block_rows: int = 128):
+    """bf16 ``[R, C]`` -> (e4m3 ``[R, C]``, fp32 scales ``[ceil(R/block_rows), ceil(C/128)]``)."""
+    if not w.is_cuda:
+        return reference.quant_fp8_block(w, block_rows, 128)
+    R, C = w.shape
+    assert w.stride(-1) == 1 and w.dtype == torch.bfloat16
+    q = torch.empty(R, C, dtype=torch.float8_e4m3fn, device=w.device)
+    scales = torch.empty((R + block_rows - 1) // block_rows, (C + 127) // 128, dtype=torch.float32, device=w.device)
+    native.check(native.lib().b200_quant_fp8_block(native.ptr(w), w.stride(0), native.ptr(q), q.stride(0),
+                                                   native.ptr(scales), R, C, block_rows, native.stream()),
+                 "quant_fp8_block")
+    return q, scales
