@@ -1,0 +1,221 @@
+"""Numerics of every sm_100a kernel against the fp32 PyTorch statements in ops/reference.py."""
+import math
+
+import pytest
+import torch
+
+from cosmos_rl_b200.ops import functional as F
+from cosmos_rl_b200.ops import native, reference as R
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _bf16(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (300, 1000, 520), (1024, 3584, 3584),
+                                   (77, 128, 64), (4096, 152, 1024)])
+def test_gemm_bf16_nt(M, N, K):
+    torch.manual_seed(0)
+    a, b = _bf16(M, K), _bf16(N, K)
+    c = F.gemm_nt(a, b)
+    native.read_status(a.device)
+    ref = a.float() @ b.float().t()
+    err = (c.float() - ref).abs().max().item()
+    tol = 2e-2 * math.sqrt(K) + 1e-2 * ref.abs().max().item()
+    assert err < tol, (err, tol)
+    # tight check against a bf16-rounded fp32 result
+    assert torch.allclose(c.float(), ref.to(torch.bfloat16).float(), rtol=2e-2, atol=1e-2 * math.sqrt(K))
+
+
+def test_gemm_fp32_accumulate():
+    torch.manual_seed(1)
+    a, b = _bf16(256, 512), _bf16(384, 512)
+    out = torch.ones(256, 384, dtype=torch.float32, device=DEV)
+    F.gemm_nt(a, b, out=out, accumulate=True)
+    native.read_status(a.device)
+    ref = a.float() @ b.float().t() + 1.0
+    assert torch.allclose(out, ref, rtol=1e-3, atol=1e-2)
+
+
+@pytest.mark.parametrize("T,V,H,temp", [(100, 1000, 128, 1.0), (257, 5000, 256, 0.7), (1024, 32000, 512, 1.0)])
+def test_fused_logprob_fwd_bwd(T, V, H, temp):
+    torch.manual_seed(2)
+    h = _bf16(T, H).requires_grad_(True)
+    w = _bf16(V, H, scale=0.05).requires_grad_(True)
+    labels = torch.randint(0, V, (T,), device=DEV)
+    labels[::7] = -100
+    lp, ent = F.fused_logprob(h, w, labels, temp)
+    native.read_status(h.device)
+    hr = h.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    lpr, entr = R.logprob_entropy(hr, wr, labels, temp)
+    assert torch.allclose(lp, lpr, rtol=1e-3, atol=2e-3), (lp - lpr).abs().max()
+    assert torch.allclose(ent, entr, rtol=1e-3, atol=2e-3), (ent - entr).abs().max()
+    g1 = torch.randn(T, device=DEV)
+    g2 = torch.randn(T, device=DEV) * 0.1
+    (lp * g1 + ent * g2).sum().backward()
+    native.read_status(h.device)
+    (lpr * g1 + entr * g2).sum().backward()
+    assert torch.allclose(h.grad.float(), hr.grad, rtol=5e-2, atol=5e-2 * hr.grad.abs().max().item())
+    assert torch.allclose(w.grad.float(), wr.grad, rtol=5e-2, atol=5e-2 * wr.grad.abs().max().item())
+
+
+@pytest.mark.parametrize("T,H", [(33, 256), (1000, 3584), (64, 8192)])
+@pytest.mark.parametrize("with_res", [False, True])
+def test_rmsnorm(T, H, with_res):
+    torch.manual_seed(3)
+    x = _bf16(T, H).requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16).requires_grad_(True)
+    res = _bf16(T, H).requires_grad_(True) if with_res else None
+    y, ro = F.rms_norm(x, w, 1e-6, res)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    rr = res.detach().float().requires_grad_(True) if with_res else None
+    h = (xr + rr).to(torch.bfloat16).float() if with_res else xr
+    if with_res:
+        # straight-through for the bf16 rounding of the residual stream
+        h = (xr + rr) + (h - (xr + rr)).detach()
+    yr = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
+    assert torch.allclose(y.float(), yr, rtol=2e-2, atol=2e-2)
+    gy = torch.randn_like(yr)
+    loss = (y.float() * gy).sum()
+    lossr = (yr * gy).sum()
+    if with_res:
+        gr = torch.randn_like(yr)
+        loss = loss + (ro.float() * gr).sum()
+        lossr = lossr + (h * gr).sum()
+    loss.backward()
+    lossr.backward()
+    assert torch.allclose(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2)
+    assert torch.allclose(w.grad.float(), wr.grad, rtol=3e-2, atol=3e-2 * wr.grad.abs().max().item())
+    if with_res:
+        assert torch.allclose(res.grad.float(), rr.grad, rtol=3e-2, atol=3e-2)
+
+
+def test_rope_qkv_fwd_bwd():
+    torch.manual_seed(4)
+    T, hq, hkv, d = 50, 4, 2, 128
+    base = _bf16(T, (hq + 2 * hkv) * d)
+    pos = torch.randint(0, 4000, (T,), device=DEV)
+    a = base.clone().requires_grad_(True)
+    out = F.rope_qkv_(a * 1.0, pos, hq, hkv, d, 1e6)
+    b = base.detach().cpu().float().requires_grad_(True)
+    outr = F.rope_qkv_(b, pos.cpu(), hq, hkv, d, 1e6)
+    assert torch.allclose(out.float().cpu(), outr, rtol=2e-2, atol=2e-2)
+    g = torch.randn_like(outr)
+    (out.float() * g.to(DEV)).sum().backward()
+    (outr * g).sum().backward()
+    assert torch.allclose(a.grad.float().cpu(), b.grad, rtol=2e-2, atol=2e-2)
+
+
+def test_swiglu():
+    torch.manual_seed(5)
+    gu = _bf16(300, 2 * 1024).requires_grad_(True)
+    y = F.swiglu(gu)
+    gr = gu.detach().float().requires_grad_(True)
+    yr = R.swiglu(gr)
+    assert torch.allclose(y.float(), yr, rtol=2e-2, atol=2e-2)
+    g = torch.randn_like(yr)
+    (y.float() * g).sum().backward()
+    (yr * g).sum().backward()
+    assert torch.allclose(gu.grad.float(), gr.grad, rtol=3e-2, atol=3e-2)
+
+
+def test_adamw_and_clip():
+    from cosmos_rl_b200.ops import optim
+    torch.manual_seed(6)
+    n = 100003
+    master = torch.randn(n, device=DEV)
+    m = torch.zeros(n, device=DEV)
+    v = torch.zeros(n, device=DEV)
+    shadow = master.to(torch.bfloat16)
+    mr, mm, vv = master.clone(), m.clone(), v.clone()
+    for step in range(1, 4):
+        grad = (torch.randn(n, device=DEV) * 0.1).to(torch.bfloat16)
+        norm, coef = optim.grad_norm_and_clip([grad], 1.0)
+        ref_norm = grad.float().norm()
+        assert abs(norm.item() - ref_norm.item()) < 1e-2 * ref_norm.item()
+        optim.adamw_flat(master, m, v, grad, shadow, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01,
+                         step=step, grad_scale=coef)
+        R.adamw_step(mr, mm, vv, grad, 1e-3, 0.9, 0.999, 1e-8, 0.01, step, grad_scale=min(1.0, 1.0 / (ref_norm.item() + 1e-6)))
+    assert torch.allclose(master, mr, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(shadow.float(), mr.to(torch.bfloat16).float(), rtol=1e-2, atol=1e-2)
+
+
+def test_sampling_distribution_and_logprob():
+    torch.manual_seed(7)
+    B, V = 64, 1000
+    logits = torch.randn(1, V, device=DEV).repeat(B, 1) * 2
+    temp = torch.full((B,), 0.8, device=DEV)
+    counts = torch.zeros(V, device=DEV)
+    n_rounds = 200
+    for i in range(n_rounds):
+        toks, lps = F.sample(logits, temp, None, None, seed=123, offset=i)
+        counts.index_add_(0, toks, torch.ones(B, device=DEV))
+    p = torch.softmax(logits[0] / 0.8, -1)
+    emp = counts / counts.sum()
+    assert (emp - p).abs().sum().item() < 0.15  # total variation small with 12800 draws
+    lsm = torch.log_softmax(logits[0] / 0.8, -1)
+    assert torch.allclose(lps, lsm[toks], rtol=1e-4, atol=1e-4)
+    # greedy
+    toks, _ = F.sample(logits, torch.zeros(B, device=DEV), None, None, seed=1, offset=0)
+    assert (toks == logits[0].argmax()).all()
+    # top-k / top-p restrict the support
+    topk = torch.full((B,), 5, dtype=torch.int32, device=DEV)
+    allowed = set(torch.topk(logits[0], 5).indices.tolist())
+    for i in range(20):
+        toks, _ = F.sample(logits, temp, None, topk, seed=5, offset=i)
+        assert set(toks.tolist()) <= allowed
+    topp = torch.full((B,), 0.5, device=DEV)
+    sp, si = torch.sort(p, descending=True)
+    ncut = int((sp.cumsum(0) < 0.5).sum()) + 1
+    allowed = set(si[:ncut + 1].tolist())
+    for i in range(20):
+        toks, _ = F.sample(logits, temp, topp, None, seed=9, offset=i)
+        assert set(toks.tolist()) <= allowed
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(28, 4, 128), (8, 8, 128), (16, 2, 64)])
+def test_paged_decode_and_append(hq, hkv, d):
+    torch.manual_seed(8)
+    B, page_size, n_pages = 5, 16, 64
+    cache = torch.zeros(n_pages, 2, hkv, page_size, d, dtype=torch.bfloat16, device=DEV)
+    seq_lens = torch.tensor([1, 17, 100, 160, 33], dtype=torch.int32, device=DEV)
+    max_pages = 12
+    perm = torch.randperm(n_pages, device=DEV)[: B * max_pages].view(B, max_pages).to(torch.int32)
+    # append all tokens through the kernel
+    ks, vs, slots = [], [], []
+    for b in range(B):
+        L = int(seq_lens[b])
+        ks.append(_bf16(L, hkv, d))
+        vs.append(_bf16(L, hkv, d))
+        t = torch.arange(L, device=DEV)
+        slots.append(perm[b, t // page_size].long() * page_size + t % page_size)
+    k, v, slot = torch.cat(ks), torch.cat(vs), torch.cat(slots).to(torch.int32)
+    F.kv_append(k, v, cache, slot)
+    cache_ref = torch.zeros_like(cache).cpu()
+    R.kv_append(k.cpu(), v.cpu(), cache_ref, slot.cpu())
+    assert torch.equal(cache.cpu(), cache_ref)
+    q = _bf16(B, hq, d)
+    ref = R.paged_decode(q.cpu(), cache_ref, perm.cpu(), seq_lens.cpu())
+    for nsplit in (1, 4):
+        out = F.paged_decode(q, cache, perm, seq_lens, nsplit=nsplit)
+        assert torch.allclose(out.float().cpu(), ref.float(), rtol=2e-2, atol=2e-2), nsplit
+
+
+@pytest.mark.parametrize("R_,C", [(256, 384), (300, 200), (128, 128)])
+def test_quant_fp8(R_, C):
+    torch.manual_seed(9)
+    w = _bf16(R_, C)
+    q, s = F.quant_fp8_block(w, 128)
+    qr, sr = R.quant_fp8_block(w.cpu(), 128, 128)
+    assert torch.allclose(s.cpu(), sr, rtol=1e-5)
+    deq = R.dequant_fp8_block(q.cpu(), s.cpu())
+    assert (deq - w.cpu().float()).abs().max() <= 0.07 * w.abs().max().item()
+    assert (q.cpu().float() - qr.float()).abs().max() <= 32  # at most one e4m3 ulp at the top binade
+    qa, sa = F.quant_fp8_block(w, 1)
+    deqa = R.dequant_fp8_block(qa.cpu(), sa.cpu(), 1, 128)
+    assert (deqa - w.cpu().float()).abs().max() <= 0.07 * w.abs().max().item()
