@@ -59,13 +59,13 @@ int b200_clip_coef(const float* sumsq, float max_norm, float* coef_out, float* n
 
 // ---- sampling --------------------------------------------------------------------------------------------
 // logits [B, V] (fp32 or bf16), per-row temperature/top_p/top_k; writes token [B] (int64) and its log-prob
-// under softmax(logits / temperature).
+// under softmax(logits / temperature). offset_dev (nullable) is a device counter added to `offset`.
 int b200_sample(const void* logits, int logits_bf16, long long ld, int B, int V, const float* temperature,
                 const float* top_p, const int* top_k, unsigned long long seed, unsigned long long offset,
-                long long* tokens, float* logprobs, cudaStream_t stream);
+                const unsigned long long* offset_dev, long long* tokens, float* logprobs, cudaStream_t stream);
 
 // ---- attention ----------------------------------------------------------------------------------------------
-// Paged KV cache layout: [num_pages, 2 (k,v), page_size, hkv, d] bf16.
+// Paged KV cache layout: [num_pages, 2 (k,v), hkv, page_size, d] bf16.
 int b200_kv_append(const void* k, const void* v, void* cache, const int* slot_mapping, int T, int hkv, int d,
                    long long k_stride, long long v_stride, int page_size, cudaStream_t stream);
 int b200_paged_decode(const void* q, const void* cache, const int* block_table, const int* seq_lens, void* out,

@@ -57,7 +57,9 @@ struct SumOp { __device__ float operator()(float a, float b) const { return a + 
 __global__ void __launch_bounds__(S_THREADS)
 sample_kernel(const void* __restrict__ logits, int bf16, long long ld, int V, const float* __restrict__ temperature,
               const float* __restrict__ top_p, const int* __restrict__ top_k, uint64_t seed, uint64_t offset,
-              long long* __restrict__ tokens, float* __restrict__ logprobs) {
+              const unsigned long long* __restrict__ offset_dev, long long* __restrict__ tokens,
+              float* __restrict__ logprobs) {
+  if (offset_dev) offset += *offset_dev;  // step counter living on the device (CUDA-graph replays)
   __shared__ float shf[32];
   __shared__ float sh_key[32];
   __shared__ int sh_idx[32];
@@ -167,10 +169,11 @@ sample_kernel(const void* __restrict__ logits, int bf16, long long ld, int V, co
 
 extern "C" int b200_sample(const void* logits, int logits_bf16, long long ld, int B, int V, const float* temperature,
                            const float* top_p, const int* top_k, unsigned long long seed, unsigned long long offset,
-                           long long* tokens, float* logprobs, cudaStream_t stream) {
+                           const unsigned long long* offset_dev, long long* tokens, float* logprobs,
+                           cudaStream_t stream) {
   if (B <= 0) return 0;
   if (V <= 0) return B200_ERR_ARG;
-  sample_kernel<<<B, S_THREADS, 0, stream>>>(logits, logits_bf16, ld, V, temperature, top_p, top_k, seed, offset, tokens,
-                                             logprobs);
+  sample_kernel<<<B, S_THREADS, 0, stream>>>(logits, logits_bf16, ld, V, temperature, top_p, top_k, seed, offset,
+                                             offset_dev, tokens, logprobs);
   return cudaGetLastError() == cudaSuccess ? 0 : B200_ERR_LAUNCH;
 }

@@ -1,0 +1,159 @@
+"""Data packers: model-specific conversion of dataset samples into rollout-engine inputs and of
+(prompt, completion) pairs into policy training tensors
+(contract of cosmos_rl/dispatcher/data/packer/base.py:54-266, decoder-only implementation
+decoder_only_llm_data_packer.py:13-319).
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional, Sequence, Type, Union
+
+import torch
+
+
+class BaseDataPacker:
+    _registry: Dict[str, Type["BaseDataPacker"]] = {}
+
+    @classmethod
+    def register(cls, model_types: Union[str, Sequence[str]], packer_cls: Optional[type] = None):
+        if isinstance(model_types, str):
+            model_types = [model_types]
+
+        def deco(c):
+            for mt in model_types:
+                cls._registry[mt] = c
+            return c
+        return deco(packer_cls) if packer_cls is not None else deco
+
+    @classmethod
+    def get_default(cls, model_type: str) -> Type["BaseDataPacker"]:
+        return cls._registry.get(model_type, DecoderOnlyLLMDataPacker)
+
+    def setup(self, config, tokenizer=None, *a, **kw):
+        self.config = config
+        self.tokenizer = tokenizer
+
+    # rollout side
+    def get_rollout_input(self, item: Any) -> Any:
+        raise NotImplementedError
+
+    def rollout_collate_fn(self, items: List[Any]) -> Any:
+        return items
+
+    def get_rollout_output(self, items: List[Any], completed_conversations=None, logprobs=None, token_ids=None, **kw):
+        return items
+
+    # policy side
+    def get_policy_input(self, sample: Any, rollout_output: Any, n_ignore_prefix_tokens: int = 0, **kw) -> Any:
+        raise NotImplementedError
+
+    def policy_compute_max_len(self, processed: List[Any]) -> int:
+        raise NotImplementedError
+
+    def policy_collate_fn(self, processed: List[Any], computed_max_len: int) -> Dict[str, Any]:
+        raise NotImplementedError
+
+    # sft
+    def sft_process_sample(self, sample: Any) -> Any:
+        raise NotImplementedError
+
+    def sft_compute_max_len(self, processed: List[Any]) -> int:
+        raise NotImplementedError
+
+    def sft_collate_fn(self, processed: List[Any], computed_max_len: int, ignore_label_id: int = -100):
+        raise NotImplementedError
+
+    def batch_size(self, batch: Dict[str, Any]) -> int:
+        return int(batch["input_ids"].shape[0])
+
+    def slice_batch(self, batch: Dict[str, Any], start: int, end: int) -> Dict[str, Any]:
+        return {k: (v[start:end] if torch.is_tensor(v) else v) for k, v in batch.items()}
+
+    def save_state(self, path: str) -> None:
+        pass
+
+
+class DecoderOnlyLLMDataPacker(BaseDataPacker):
+    """Text-only decoder LLMs. Prompts may be strings, chat conversations or already-tokenised id lists."""
+
+    class PolicyInput:
+        __slots__ = ("input_ids", "logprob_masks")
+
+        def __init__(self, input_ids: List[int], logprob_masks: List[int]):
+            self.input_ids = input_ids
+            self.logprob_masks = logprob_masks
+
+    def _encode_prompt(self, prompt) -> List[int]:
+        if isinstance(prompt, (list, tuple)) and (len(prompt) == 0 or isinstance(prompt[0], int)):
+            return list(prompt)
+        if self.tokenizer is None:
+            raise RuntimeError("a tokenizer is required for text prompts")
+        if isinstance(prompt, str):
+            return self.tokenizer.encode(prompt, add_special_tokens=False)
+        return self.tokenizer.apply_chat_template(prompt, tokenize=True, add_generation_prompt=True)
+
+    def _encode_completion(self, completion) -> List[int]:
+        if isinstance(completion, (list, tuple)) and (len(completion) == 0 or isinstance(completion[0], int)):
+            return list(completion)
+        if self.tokenizer is None:
+            raise RuntimeError("a tokenizer is required for text completions")
+        ids = self.tokenizer.encode(completion, add_special_tokens=False)
+        eos = getattr(self.tokenizer, "eos_token_id", None)
+        return ids + ([eos] if eos is not None else [])
+
+    def get_rollout_input(self, item):
+        return self._encode_prompt(item)
+
+    def get_policy_input(self, sample, rollout_output, n_ignore_prefix_tokens: int = 0, **kw):
+        p = self._encode_prompt(sample)
+        c = self._encode_completion(rollout_output)
+        n_ign = min(n_ignore_prefix_tokens, len(c))
+        # mask[i] == 1  <=>  token i+1 is a completion token whose log-prob is scored
+        mask = [0] * (len(p) - 1 + n_ign) + [1] * (len(c) - n_ign) + [0]
+        return self.PolicyInput(p + c, mask)
+
+    def policy_compute_max_len(self, processed):
+        return max(len(x.input_ids) for x in processed)
+
+    def policy_collate_fn(self, processed, computed_max_len: int):
+        pad = getattr(self.tokenizer, "pad_token_id", None) or 0
+        ids = torch.full((len(processed), computed_max_len), pad, dtype=torch.long)
+        masks = torch.zeros((len(processed), computed_max_len), dtype=torch.bool)
+        for i, x in enumerate(processed):
+            n = min(len(x.input_ids), computed_max_len)
+            ids[i, :n] = torch.tensor(x.input_ids[:n], dtype=torch.long)
+            masks[i, :n] = torch.tensor(x.logprob_masks[:n], dtype=torch.bool)
+        return {"input_ids": ids, "logprob_masks": masks}
+
+    # ---- SFT
+    def sft_process_sample(self, sample):
+        if isinstance(sample, dict) and "input_ids" in sample:
+            return {"input_ids": list(sample["input_ids"]), "label_ids": list(sample.get("label_ids", sample["input_ids"]))}
+        if isinstance(sample, (list, tuple)) and sample and isinstance(sample[0], int):
+            return {"input_ids": list(sample), "label_ids": list(sample)}
+        if self.tokenizer is None:
+            raise RuntimeError("a tokenizer is required for conversation samples")
+        conv = sample
+        ids = self.tokenizer.apply_chat_template(conv, tokenize=True, add_generation_prompt=False)
+        labels = list(ids)
+        # score only assistant turns: mask the prefix up to the last assistant message
+        prefix = self.tokenizer.apply_chat_template(conv[:-1], tokenize=True, add_generation_prompt=True)
+        labels[: len(prefix)] = [-100] * min(len(prefix), len(labels))
+        return {"input_ids": ids, "label_ids": labels}
+
+    def sft_compute_max_len(self, processed):
+        return max(len(x["input_ids"]) for x in processed)
+
+    def sft_collate_fn(self, processed, computed_max_len: int, ignore_label_id: int = -100):
+        pad = getattr(self.tokenizer, "pad_token_id", None) or 0
+        ids = torch.full((len(processed), computed_max_len), pad, dtype=torch.long)
+        labels = torch.full((len(processed), computed_max_len), ignore_label_id, dtype=torch.long)
+        lens = torch.zeros(len(processed), dtype=torch.long)
+        for i, x in enumerate(processed):
+            n = min(len(x["input_ids"]), computed_max_len)
+            ids[i, :n] = torch.tensor(x["input_ids"][:n])
+            labels[i, :n] = torch.tensor(x["label_ids"][:n])
+            lens[i] = n
+        return {"input_ids": ids, "label_ids": labels, "seq_lens": lens}
+
+
+BaseDataPacker.register(["llama", "qwen2", "qwen3", "qwen3_moe", "hfmodel"], DecoderOnlyLLMDataPacker)

@@ -1,0 +1,14 @@
+"""Model zoo. Importing this package registers every model family with :class:`ModelRegistry`."""
+from .base import BaseModel, ModelRegistry, WeightMapper  # noqa: F401
+from . import gpt  # noqa: F401
+
+
+def named_architectures():
+    """Built-in architectures that can be instantiated with random weights (no download needed)."""
+    out = dict(gpt.ARCHS)
+    try:
+        from . import qwen3_moe
+        out.update(qwen3_moe.ARCHS)
+    except ImportError:
+        pass
+    return out

@@ -1,0 +1,299 @@
+"""Dense decoder-only transformer (Llama / Qwen2 / Qwen2.5 / Qwen3 families).
+
+Same model family as cosmos_rl/policy/model/gpt/__init__.py:119-813, laid out for this framework:
+* q/k/v and gate/up are stored fused (``qkv_proj``, ``gate_up_proj``): one GEMM each, and the parameter
+  layout is exactly what the rollout engine consumes, so colocated rollouts share the policy's tensors and
+  separated rollouts receive rectangular slices.
+* activations are packed ``[T, H]`` (no padding); attention takes ``cu_seqlens``.
+* the model returns the final hidden states; log-probabilities come from the fused lm_head kernel
+  (``logprobs``), logits are only materialised by ``logits`` for generation.
+Tensor parallelism: column-parallel qkv / gate_up, row-parallel o / down, vocabulary-parallel embedding and
+lm_head; the collectives are issued through :mod:`cosmos_rl_b200.parallel.tp`.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as tF
+from torch.utils.checkpoint import checkpoint
+
+from ..ops import functional as F
+from .base import BaseModel, ModelRegistry, WeightMapper
+
+
+@dataclass
+class GPTArgs:
+    vocab_size: int = 32000
+    dim: int = 256
+    n_layers: int = 2
+    n_heads: int = 4
+    n_kv_heads: int = 2
+    head_dim: Optional[int] = None
+    ffn_dim: int = 688
+    norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    qkv_bias: bool = True
+    qk_norm: bool = False
+    tie_word_embeddings: bool = False
+    max_seq_len: int = 4096
+    model_type: str = "qwen2"
+    tp_size: int = 1
+    tp_rank: int = 0
+
+    def __post_init__(self):
+        if self.head_dim is None:
+            self.head_dim = self.dim // self.n_heads
+
+    @classmethod
+    def from_hf_config(cls, c, **over) -> "GPTArgs":
+        g = (lambda k, d=None: c.get(k, d)) if isinstance(c, dict) else (lambda k, d=None: getattr(c, k, d))
+        mt = g("model_type", "qwen2")
+        a = cls(
+            vocab_size=g("vocab_size"), dim=g("hidden_size"), n_layers=g("num_hidden_layers"),
+            n_heads=g("num_attention_heads"), n_kv_heads=g("num_key_value_heads") or g("num_attention_heads"),
+            head_dim=g("head_dim"), ffn_dim=g("intermediate_size"), norm_eps=g("rms_norm_eps", 1e-6),
+            rope_theta=float(g("rope_theta", 1e4) or 1e4),
+            qkv_bias=bool(g("attention_bias", mt == "qwen2")), qk_norm=(mt == "qwen3"),
+            tie_word_embeddings=bool(g("tie_word_embeddings", False)),
+            max_seq_len=g("max_position_embeddings", 4096), model_type=mt)
+        for k, v in over.items():
+            setattr(a, k, v)
+        a.__post_init__()
+        return a
+
+    def to_hf_config(self) -> Dict[str, Any]:
+        arch = {"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM", "llama": "LlamaForCausalLM"}
+        return {
+            "architectures": [arch.get(self.model_type, "Qwen2ForCausalLM")], "model_type": self.model_type,
+            "vocab_size": self.vocab_size, "hidden_size": self.dim, "num_hidden_layers": self.n_layers,
+            "num_attention_heads": self.n_heads, "num_key_value_heads": self.n_kv_heads, "head_dim": self.head_dim,
+            "intermediate_size": self.ffn_dim, "rms_norm_eps": self.norm_eps, "rope_theta": self.rope_theta,
+            "attention_bias": self.qkv_bias, "tie_word_embeddings": self.tie_word_embeddings,
+            "max_position_embeddings": self.max_seq_len, "hidden_act": "silu", "torch_dtype": "bfloat16",
+        }
+
+
+# named benchmark architectures (random-init; shapes of the public checkpoints)
+ARCHS: Dict[str, GPTArgs] = {
+    "tiny-qwen2": GPTArgs(vocab_size=32000, dim=256, n_layers=2, n_heads=4, n_kv_heads=2, ffn_dim=688,
+                          rope_theta=1e6, qkv_bias=True, model_type="qwen2"),
+    "qwen2.5-7b": GPTArgs(vocab_size=152064, dim=3584, n_layers=28, n_heads=28, n_kv_heads=4, ffn_dim=18944,
+                          rope_theta=1e6, qkv_bias=True, model_type="qwen2", max_seq_len=32768),
+    "qwen3-32b": GPTArgs(vocab_size=151936, dim=5120, n_layers=64, n_heads=64, n_kv_heads=8, head_dim=128,
+                         ffn_dim=25600, rope_theta=1e6, qkv_bias=False, qk_norm=True, model_type="qwen3",
+                         max_seq_len=40960),
+    "llama3-8b": GPTArgs(vocab_size=128256, dim=4096, n_layers=32, n_heads=32, n_kv_heads=8, ffn_dim=14336,
+                         rope_theta=5e5, qkv_bias=False, model_type="llama", max_seq_len=8192),
+}
+
+
+def _linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -> torch.Tensor:
+    return tF.linear(x, w, b)
+
+
+class Attention(nn.Module):
+    def __init__(self, a: GPTArgs):
+        super().__init__()
+        assert a.n_heads % a.tp_size == 0, "attention heads must divide by tp"
+        self.hq = a.n_heads // a.tp_size
+        self.hkv = max(1, a.n_kv_heads // a.tp_size)
+        self.d = a.head_dim
+        self.theta = a.rope_theta
+        self.qk_norm = a.qk_norm
+        self.eps = a.norm_eps
+        self.qkv_proj = nn.Linear(a.dim, (self.hq + 2 * self.hkv) * self.d, bias=a.qkv_bias)
+        self.o_proj = nn.Linear(self.hq * self.d, a.dim, bias=False)
+        if a.qk_norm:
+            self.q_norm = nn.Parameter(torch.ones(self.d))
+            self.k_norm = nn.Parameter(torch.ones(self.d))
+
+    def project_qkv(self, x: torch.Tensor, positions: torch.Tensor):
+        """x [T, H] -> q [T, hq, d], k, v [T, hkv, d] with RoPE (and per-head q/k norm) applied."""
+        T = x.shape[0]
+        qkv = _linear(x, self.qkv_proj.weight, self.qkv_proj.bias)
+        hq, hkv, d = self.hq, self.hkv, self.d
+        if self.qk_norm:
+            q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
+            q = F.rms_norm(q.reshape(T * hq, d), self.q_norm, self.eps)[0].view(T, hq, d)
+            k = F.rms_norm(k.reshape(T * hkv, d), self.k_norm, self.eps)[0].view(T, hkv, d)
+            q, k = F.apply_rope(q, k, positions, self.theta)
+            return q, k, v.reshape(T, hkv, d)
+        qkv = F.rope_qkv_(qkv, positions, hq, hkv, d, self.theta)
+        q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
+        return q.unflatten(-1, (hq, d)), k.unflatten(-1, (hkv, d)), v.unflatten(-1, (hkv, d))
+
+    def forward(self, x, positions, cu_seqlens, max_seqlen, tp=None):
+        q, k, v = self.project_qkv(x, positions)
+        o = F.varlen_attention(q, k, v, cu_seqlens, max_seqlen)
+        out = _linear(o.reshape(x.shape[0], -1), self.o_proj.weight)
+        return tp.reduce_output(out) if tp is not None else out
+
+
+class FeedForward(nn.Module):
+    def __init__(self, a: GPTArgs):
+        super().__init__()
+        assert a.ffn_dim % a.tp_size == 0
+        self.I = a.ffn_dim // a.tp_size
+        self.gate_up_proj = nn.Linear(a.dim, 2 * self.I, bias=False)
+        self.down_proj = nn.Linear(self.I, a.dim, bias=False)
+
+    def forward(self, x, tp=None):
+        out = _linear(F.swiglu(_linear(x, self.gate_up_proj.weight)), self.down_proj.weight)
+        return tp.reduce_output(out) if tp is not None else out
+
+
+class GPTBlock(nn.Module):
+    def __init__(self, a: GPTArgs):
+        super().__init__()
+        self.eps = a.norm_eps
+        self.input_layernorm = nn.Parameter(torch.ones(a.dim))
+        self.self_attn = Attention(a)
+        self.post_attention_layernorm = nn.Parameter(torch.ones(a.dim))
+        self.mlp = FeedForward(a)
+
+    def forward(self, h, res, positions, cu_seqlens, max_seqlen, tp=None):
+        """(h, res) is the un-added residual pair: the stream value is h + res (res None on the first block)."""
+        if res is None:
+            x, _ = F.rms_norm(h, self.input_layernorm, self.eps)
+            res = h
+        else:
+            x, res = F.rms_norm(h, self.input_layernorm, self.eps, residual=res)
+        h = self.self_attn(x, positions, cu_seqlens, max_seqlen, tp)
+        x, res = F.rms_norm(h, self.post_attention_layernorm, self.eps, residual=res)
+        h = self.mlp(x, tp)
+        return h, res
+
+
+class GPTWeightMapper(WeightMapper):
+    """HF stores q_proj/k_proj/v_proj and gate_proj/up_proj separately; this framework fuses them."""
+
+    FUSED = {"qkv_proj": ("q_proj", "k_proj", "v_proj"), "gate_up_proj": ("gate_proj", "up_proj")}
+    RENAME = {"input_layernorm": "input_layernorm.weight", "post_attention_layernorm": "post_attention_layernorm.weight",
+              "self_attn.q_norm": "self_attn.q_norm.weight", "self_attn.k_norm": "self_attn.k_norm.weight",
+              "norm": "norm.weight"}
+
+    def hf_names(self, local: str) -> List[str]:
+        """HF parameter names a local parameter is assembled from (in row order)."""
+        name = local
+        for k, v in self.RENAME.items():
+            if name == k or name.endswith("." + k):
+                name = name[: len(name) - len(k)] + v
+                break
+        if not name.startswith("lm_head"):
+            name = "model." + name
+        for fused, parts in self.FUSED.items():
+            if f".{fused}." in name:
+                return [name.replace(fused, p) for p in parts]
+        return [name]
+
+
+@ModelRegistry.register(GPTWeightMapper, default=True)
+class GPT(BaseModel):
+    def __init__(self, args: GPTArgs):
+        super().__init__()
+        self.args = args
+        a = args
+        assert a.vocab_size % a.tp_size == 0 or a.tp_size == 1
+        self.v_local = a.vocab_size // a.tp_size if a.tp_size > 1 else a.vocab_size
+        self.embed_tokens = nn.Embedding(self.v_local, a.dim)
+        self.layers = nn.ModuleList([GPTBlock(a) for _ in range(a.n_layers)])
+        self.norm = nn.Parameter(torch.ones(a.dim))
+        if a.tie_word_embeddings:
+            self.lm_head = None
+        else:
+            self.lm_head = nn.Linear(a.dim, self.v_local, bias=False)
+        self.gradient_checkpointing = False
+        self.tp = None  # set by parallel.tp.TensorParallel when tp_size > 1
+
+    # ------------------------------------------------------------------ registry hooks
+    @staticmethod
+    def supported_model_types():
+        return ["llama", "qwen2", "qwen3"]
+
+    @classmethod
+    def from_hf_config(cls, hf_config, **kw):
+        return cls(GPTArgs.from_hf_config(hf_config, **kw))
+
+    @property
+    def lm_head_weight(self) -> torch.Tensor:
+        return self.embed_tokens.weight if self.lm_head is None else self.lm_head.weight
+
+    def init_weights(self, seed: int = 0, std: float = 0.02) -> None:
+        """Random init from a seed; identical on every rank given the same seed."""
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        for name, p in self.named_parameters():
+            with torch.no_grad():
+                if p.dim() == 1 and ("norm" in name):
+                    p.fill_(1.0)
+                elif p.dim() == 1:
+                    p.zero_()
+                else:
+                    p.copy_(torch.randn(p.shape, generator=g, dtype=torch.float32).mul_(std).to(p.dtype))
+
+    def init_weights_on_device(self, seed: int = 0, std: float = 0.02) -> None:
+        """Fast random init directly on the parameter's device (benchmark-sized models)."""
+        g = torch.Generator(device=self.norm.device).manual_seed(seed)
+        for name, p in self.named_parameters():
+            with torch.no_grad():
+                if p.dim() == 1 and ("norm" in name):
+                    p.fill_(1.0)
+                elif p.dim() == 1:
+                    p.zero_()
+                else:
+                    p.normal_(0.0, std, generator=g)
+
+    # ------------------------------------------------------------------ forward
+    def embed(self, input_ids: torch.Tensor) -> torch.Tensor:
+        if self.tp is not None:
+            return self.tp.vocab_parallel_embed(input_ids, self.embed_tokens.weight)
+        return self.embed_tokens(input_ids)
+
+    def forward(self, input_ids: torch.Tensor, position_ids: torch.Tensor, cu_seqlens: torch.Tensor,
+                max_seqlen: int) -> torch.Tensor:
+        """Packed forward: ``input_ids [T]`` -> final hidden states ``[T, H]`` (after the last norm)."""
+        h = self.embed(input_ids)
+        res = None
+        for layer in self.layers:
+            if self.gradient_checkpointing and torch.is_grad_enabled():
+                h, res = checkpoint(layer, h, res, position_ids, cu_seqlens, max_seqlen, self.tp, use_reentrant=False)
+            else:
+                h, res = layer(h, res, position_ids, cu_seqlens, max_seqlen, self.tp)
+        out, _ = F.rms_norm(h, self.norm, self.args.norm_eps, residual=res)
+        return out
+
+    def logprobs(self, hidden: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0):
+        """Per-token log-prob of ``labels`` and entropy from hidden states, through the fused lm_head kernel."""
+        if self.tp is not None:
+            return self.tp.vocab_parallel_logprob(hidden, self.lm_head_weight, labels, temperature)
+        return F.fused_logprob(hidden, self.lm_head_weight, labels, temperature)
+
+    def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        out = _linear(hidden, self.lm_head_weight)
+        return self.tp.gather_vocab(out) if self.tp is not None else out
+
+    # ------------------------------------------------------------------ accounting
+    def get_nparams_and_flops(self, seq_len: int) -> Tuple[int, int]:
+        """(parameter count, training FLOPs per token = 6N + attention term), cosmos_rl/policy/model/gpt/__init__.py:689-713."""
+        a = self.args
+        n = sum(p.numel() for p in self.parameters()) * a.tp_size
+        n_embed = a.vocab_size * a.dim
+        flops = 6 * (n - n_embed) + 12 * a.n_layers * a.n_heads * a.head_dim * seq_len
+        return n, flops
+
+    def check_tp_compatible(self, tp_size: int) -> None:
+        a = self.args
+        if a.n_heads % tp_size or a.ffn_dim % tp_size or (a.n_kv_heads % tp_size and tp_size % a.n_kv_heads):
+            raise ValueError(f"tp_size={tp_size} incompatible with heads={a.n_heads}/{a.n_kv_heads}, ffn={a.ffn_dim}")
+
+    def check_cp_compatible(self, cp_size: int, tp_size: int) -> None:
+        if self.args.n_heads % (cp_size * tp_size):
+            raise ValueError("n_heads must be divisible by cp_size * tp_size")
+
+    def get_position_ids(self, cu_seqlens: torch.Tensor, total: int) -> torch.Tensor:
+        pos = torch.arange(total, device=cu_seqlens.device)
+        starts = torch.repeat_interleave(cu_seqlens[:-1], (cu_seqlens[1:] - cu_seqlens[:-1]))
+        return pos - starts

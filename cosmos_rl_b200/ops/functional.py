@@ -354,18 +354,19 @@ def paged_decode(q, cache, block_table, seq_lens, scale: Optional[float] = None,
 # sampling
 # --------------------------------------------------------------------------------------------------
 def sample(logits: torch.Tensor, temperature=None, top_p=None, top_k=None, seed: int = 0, offset: int = 0,
-           generator: Optional[torch.Generator] = None):
+           generator: Optional[torch.Generator] = None, offset_dev: Optional[torch.Tensor] = None,
+           out_tokens: Optional[torch.Tensor] = None, out_logprobs: Optional[torch.Tensor] = None):
     """Returns ``(tokens [B] int64, logprobs [B] fp32)``; per-row ``temperature/top_p`` fp32 and ``top_k`` int32."""
     if not logits.is_cuda:
         return reference.sample(logits, temperature, top_p, top_k, generator)
     B, V = logits.shape
     assert logits.stride(-1) == 1 and logits.dtype in (torch.float32, torch.bfloat16)
-    toks = torch.empty(B, dtype=torch.int64, device=logits.device)
-    lps = torch.empty(B, dtype=torch.float32, device=logits.device)
+    toks = out_tokens if out_tokens is not None else torch.empty(B, dtype=torch.int64, device=logits.device)
+    lps = out_logprobs if out_logprobs is not None else torch.empty(B, dtype=torch.float32, device=logits.device)
     native.check(native.lib().b200_sample(native.ptr(logits), 1 if logits.dtype == torch.bfloat16 else 0,
                                           logits.stride(0), B, V, native.ptr(temperature), native.ptr(top_p),
                                           native.ptr(top_k), seed & (2 ** 64 - 1), offset & (2 ** 64 - 1),
-                                          native.ptr(toks), native.ptr(lps), native.stream()), "sample")
+                                          native.ptr(offset_dev), native.ptr(toks), native.ptr(lps), native.stream()), "sample")
     return toks, lps
 
 

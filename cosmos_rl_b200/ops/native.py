@@ -69,7 +69,7 @@ _SIGS = {
     "b200_sumsq": [c_void_p, c_int, c_longlong, c_void_p, c_void_p],
     "b200_clip_coef": [c_void_p, c_float, c_void_p, c_void_p, c_void_p],
     "b200_sample": [c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_ulonglong,
-                    c_ulonglong, c_void_p, c_void_p, c_void_p],
+                    c_ulonglong, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200_kv_append": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
                        c_void_p],
     "b200_paged_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -107,7 +107,15 @@ def stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+LAUNCHES = [0]  # launcher calls into libb200rl since import (CUDA-graph replays add their captured count)
+
+
+def add_launches(n: int) -> None:
+    LAUNCHES[0] += n
+
+
 def check(rc: int, what: str) -> None:
+    LAUNCHES[0] += 1
     if rc != 0:
         names = {-1: "bad argument", -2: "tensor map encode failed", -3: "kernel launch failed",
                  -4: "size beyond the supported maximum", -5: "CUDA runtime error"}

@@ -1,0 +1,133 @@
+"""Optimizer and LR schedule of the policy trainers.
+
+``FlatAdamW`` keeps fp32 master weights and Adam moments for this rank's shard of the flat parameter buffer
+and updates them with one fused kernel that also rewrites the bf16 compute copy; the clip coefficient stays
+on the device. Data parallel (``dp_shard``): gradients are reduce-scattered into the shard and the updated
+bf16 weights all-gathered back, each once per optimizer step (optimizer-state + gradient sharding; with
+180 GB of HBM per GPU the bf16 weights of the supported models stay resident, so no parameter all-gather
+sits inside forward/backward). The schedule is warmup-stable-decay as in
+cosmos_rl/policy/trainer/optm/__init__.py:500-620.
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import optim as K
+from ..parallel.flat import FlatParams
+
+
+def lr_factor(step: int, total_steps: int, warmup_steps, warmup_start_factor: float = 0.0,
+              decay_ratio: Optional[float] = None, decay_type: Optional[str] = None,
+              min_lr_factor: float = 0.0) -> float:
+    """Multiplier applied to the base LR at optimizer step ``step`` (0-based)."""
+    if isinstance(warmup_steps, float) and warmup_steps < 1.0:
+        warmup = int(round(warmup_steps * total_steps))
+    else:
+        warmup = int(warmup_steps)
+    if warmup > 0 and step < warmup:
+        return warmup_start_factor + (1.0 - warmup_start_factor) * (step + 1) / (warmup + 1)
+    if not decay_type or total_steps <= 0:
+        return 1.0
+    decay_steps = int(total_steps * decay_ratio) if decay_ratio is not None else max(total_steps - warmup, 1)
+    stable_end = total_steps - decay_steps
+    if step < stable_end:
+        return 1.0
+    prog = min(1.0, max(0.0, (step - stable_end + 1) / max(decay_steps, 1)))
+    if decay_type == "linear":
+        f = 1.0 - prog
+    elif decay_type == "cosine":
+        f = 0.5 * (1.0 + math.cos(math.pi * prog))
+    elif decay_type == "sqrt":
+        f = 1.0 - math.sqrt(prog)
+    else:
+        raise ValueError(f"unknown decay type {decay_type!r}")
+    return min_lr_factor + (1.0 - min_lr_factor) * f
+
+
+class FlatAdamW:
+    def __init__(self, flat: FlatParams, lr: float, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
+                 max_grad_norm: float = 1.0, dp_group: Optional[dist.ProcessGroup] = None,
+                 master_dtype: torch.dtype = torch.float32, collective=None):
+        self.flat = flat
+        self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
+        self.max_grad_norm = max_grad_norm
+        self.group = dp_group
+        self.world = dist.get_world_size(dp_group) if dp_group is not None else 1
+        self.rank = dist.get_rank(dp_group) if dp_group is not None else 0
+        self.collective = collective  # optional fused peer-memory reduce-scatter / all-gather provider
+        self.lo, self.hi = flat.shard_range(self.rank, self.world)
+        n = self.hi - self.lo
+        dev = flat.device
+        self.master = flat.data[self.lo:self.hi].to(torch.float32, copy=True)
+        self.m = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.grad_shard = torch.zeros(n, dtype=torch.float32, device=dev) if self.world > 1 else None
+        self.step_count = 0
+        self.last_grad_norm: Optional[torch.Tensor] = None
+        self.trainable = flat.trainable_mask()
+
+    # ------------------------------------------------------------------
+    def refresh_master_from_params(self) -> None:
+        """After loading weights into the bf16 buffer (HF load, weight resume)."""
+        self.master.copy_(self.flat.data[self.lo:self.hi].to(torch.float32))
+
+    def _reduce_grads(self) -> torch.Tensor:
+        """Returns this rank's averaged gradient shard (fp32 when dp > 1, a bf16 view otherwise)."""
+        g = self.flat.grad
+        if self.trainable is not None:
+            g.mul_(self.trainable.to(g.dtype))
+        if self.world == 1:
+            return g[self.lo:self.hi]
+        if self.collective is not None:
+            self.collective.reduce_scatter_avg(g, self.grad_shard)
+        else:
+            # library path (the baseline): fp32 reduce as in FSDP2's reduce_dtype=float32
+            full = g.to(torch.float32)
+            dist.reduce_scatter_tensor(self.grad_shard, full, op=dist.ReduceOp.AVG, group=self.group)
+        return self.grad_shard
+
+    def step(self, lr_scale: float = 1.0, extra_norm_groups=()) -> torch.Tensor:
+        """Reduce, clip, update, republish weights. Returns the global gradient norm (1-element tensor)."""
+        self.step_count += 1
+        g = self._reduce_grads()
+        sumsq = K.grad_sumsq([g])
+        if self.world > 1:
+            dist.all_reduce(sumsq, group=self.group)
+        for grp in extra_norm_groups:  # e.g. tensor-/pipeline-parallel groups that hold disjoint parameters
+            dist.all_reduce(sumsq, group=grp)
+        norm, coef = K.clip_coef_from_sumsq(sumsq, self.max_grad_norm)
+        shadow = self.flat.data[self.lo:self.hi]
+        K.adamw_flat(self.master, self.m, self.v, g, shadow, lr=self.lr * lr_scale, beta1=self.betas[0],
+                     beta2=self.betas[1], eps=self.eps, weight_decay=self.wd, step=self.step_count, grad_scale=coef)
+        if self.world > 1:
+            if self.collective is not None:
+                self.collective.all_gather_params(self.flat.data, self.lo, self.hi)
+            else:
+                dist.all_gather_into_tensor(self.flat.data, shadow.clone(), group=self.group)
+        self.last_grad_norm = norm
+        return norm
+
+    def zero_grad(self) -> None:
+        self.flat.zero_grad()
+
+    # ------------------------------------------------------------------ state (per-rank shard)
+    def state_dict(self) -> Dict[str, Any]:
+        return {"master": self.master, "m": self.m, "v": self.v, "step": self.step_count, "lo": self.lo,
+                "hi": self.hi, "world": self.world}
+
+    def load_state_dict(self, sd: Dict[str, Any]) -> None:
+        if sd["hi"] - sd["lo"] != self.hi - self.lo:
+            raise ValueError("optimizer shard size changed; re-shard the checkpoint first")
+        self.master.copy_(sd["master"])
+        self.m.copy_(sd["m"])
+        self.v.copy_(sd["v"])
+        self.step_count = int(sd["step"])
+        self.flat.data[self.lo:self.hi].copy_(self.master.to(self.flat.dtype))
+
+    def state_tensors(self):
+        """Named tensors shipped to a new replica on elastic scale-up (policy-to-policy unicast)."""
+        return [("optim.master", self.master), ("optim.m", self.m), ("optim.v", self.v)]

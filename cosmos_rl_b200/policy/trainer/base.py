@@ -1,0 +1,50 @@
+"""Trainer registry and interface (cosmos_rl/policy/trainer/base.py:105-255)."""
+from __future__ import annotations
+
+from abc import ABC, abstractmethod
+from typing import Any, Dict, List, Optional, Type
+
+
+class TrainerRegistry:
+    _trainers: Dict[str, Type["Trainer"]] = {}
+
+    @classmethod
+    def register(cls, trainer_type: str):
+        def deco(c):
+            cls._trainers[trainer_type] = c
+            return c
+        return deco
+
+    @classmethod
+    def get_trainer_cls(cls, trainer_type: str) -> Type["Trainer"]:
+        if trainer_type not in cls._trainers:
+            raise KeyError(f"unknown trainer type {trainer_type!r}; known: {sorted(cls._trainers)}")
+        return cls._trainers[trainer_type]
+
+    @classmethod
+    def known(cls) -> List[str]:
+        return sorted(cls._trainers)
+
+
+class Trainer(ABC):
+    """Keys every trainer reports after a step (aggregated and logged by the controller)."""
+    REPORT_KEYS = ("train/loss_avg", "train/loss_max", "train/learning_rate", "train/iteration_time",
+                   "train/grad_norm")
+
+    @abstractmethod
+    def step_training(self, *a, **kw) -> Dict[str, Any]: ...
+
+    def step_validation(self, *a, **kw) -> Dict[str, Any]:
+        return {}
+
+    @abstractmethod
+    def export_safetensors(self, output_dir: str, **kw) -> None: ...
+
+    @abstractmethod
+    def model_load_from_hf(self) -> None: ...
+
+    @abstractmethod
+    def model_resume_from_checkpoint(self) -> bool: ...
+
+    @abstractmethod
+    def save_checkpoint(self, step: int, total_steps: int, **kw) -> None: ...

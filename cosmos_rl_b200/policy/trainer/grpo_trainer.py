@@ -1,0 +1,214 @@
+"""GRPO trainer: turns a batch of rollouts into packed micro-batches, runs forward/backward through the
+fused log-prob kernel and the GRPO loss, and applies one (or several) optimizer steps
+(cosmos_rl/policy/trainer/llm_trainer/grpo_trainer.py:977-1931).
+
+Phases of a step: [reference log-probs when kl_beta != 0] -> [old log-probs when the batch is optimised in
+several chunks or mu_iterations > 1] -> training. Mini-batches are built by count (``mini_batch``) or by
+token budget (``max_token_len_per_mini_batch``) and always packed (no padding reaches the GPU).
+"""
+from __future__ import annotations
+
+import time
+from typing import Any, Dict, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ...dispatcher.data.schema import Rollout
+from ...utils.logging import logger
+from ...utils.sequence_packing import pack_sequences, token_budget_batches
+from ..loss import GrpoLossConfig, grpo_loss
+from .base import TrainerRegistry
+from .llm_trainer import LLMTrainer
+
+
+class _Sample:
+    __slots__ = ("ids", "mask", "advantage", "reward", "rollout_lp", "n_scored")
+
+    def __init__(self, ids, mask, advantage, reward, rollout_lp):
+        self.ids, self.mask, self.advantage, self.reward, self.rollout_lp = ids, mask, advantage, reward, rollout_lp
+        self.n_scored = int(sum(mask))
+
+
+@TrainerRegistry.register("grpo")
+class GRPOTrainer(LLMTrainer):
+    def __init__(self, config, parallel_dims, **kw):
+        super().__init__(config, parallel_dims, **kw)
+        self.tp_cfg = config.train.train_policy
+        self.loss_cfg = GrpoLossConfig.from_config(self.tp_cfg)
+        self.temperature = float(self.tp_cfg.temperature)
+        self.reference_state: Optional[torch.Tensor] = None   # host copy of the reference weights (kl_beta != 0)
+        if self.tp_cfg.kl_beta != 0.0:
+            self._reference_pending = True
+        self.inter_replica = kw.get("inter_replica")  # elastic data parallelism across policy replicas
+
+    # ------------------------------------------------------------------ data
+    def _prepare(self, rollouts: Sequence[Rollout]) -> List[_Sample]:
+        out = []
+        for r in rollouts:
+            comp = r.completion
+            if r.completion_token_ids:
+                comp = [pos[0] for pos in r.completion_token_ids]
+            pi = self.data_packer.get_policy_input(r.prompt, comp, r.n_ignore_prefix_tokens)
+            lp = None
+            if r.completion_logprobs:
+                lp = [pos[0] for pos in r.completion_logprobs][r.n_ignore_prefix_tokens:]
+            max_len = self.config.policy.model_max_length
+            ids, mask = pi.input_ids[:max_len], pi.logprob_masks[:max_len]
+            if len(ids) < len(pi.input_ids):
+                mask[-1] = 0
+            out.append(_Sample(ids, mask, float(r.advantage), float(r.reward), lp))
+        return out
+
+    def _mini_batches(self, samples: List[_Sample]) -> List[List[int]]:
+        budget = self.tp_cfg.max_token_len_per_mini_batch
+        if budget:
+            return token_budget_batches([len(s.ids) for s in samples], budget * self.parallel_dims.cp)
+        mb = max(1, self.tp_cfg.mini_batch)
+        return [list(range(i, min(i + mb, len(samples)))) for i in range(0, len(samples), mb)]
+
+    def _pack(self, samples: List[_Sample]) -> Dict[str, Any]:
+        pad_mult = self.parallel_dims.cp * self.parallel_dims.tp
+        b = pack_sequences([s.ids for s in samples], [s.mask for s in samples], device=self.device,
+                           pad_multiple=1 if pad_mult == 1 else pad_mult)
+        sel = (b["label_ids"] >= 0).nonzero(as_tuple=True)[0]
+        b["sel"] = sel
+        b["labels_sel"] = b["label_ids"][sel]
+        b["seq_ids_sel"] = b["seq_ids"][sel]
+        adv = torch.tensor([s.advantage for s in samples], dtype=torch.float32, device=self.device)
+        b["adv_tok"] = adv[b["seq_ids_sel"]]
+        b["seq_rewards"] = torch.tensor([s.reward for s in samples], dtype=torch.float32, device=self.device)
+        if all(s.rollout_lp is not None and len(s.rollout_lp) == s.n_scored for s in samples):
+            flat = [x for s in samples for x in s.rollout_lp]
+            b["rollout_lp"] = torch.tensor(flat, dtype=torch.float32, device=self.device)
+        return b
+
+    def _forward_logprobs(self, b: Dict[str, Any]):
+        hidden = self.model(b["input_ids"], b["position_ids"], b["cu_seqlens"], b["max_seqlen"])
+        return self.model.logprobs(hidden[b["sel"]], b["labels_sel"], self.temperature)
+
+    @torch.no_grad()
+    def _compute_logprobs_nograd(self, batches: List[Dict[str, Any]]) -> List[torch.Tensor]:
+        return [self._forward_logprobs(b)[0].detach() for b in batches]
+
+    # ------------------------------------------------------------------ reference policy (KL)
+    def _swap_flat(self, other: torch.Tensor) -> torch.Tensor:
+        cur = self.flat.data.to("cpu", copy=True)
+        self.flat.data.copy_(other.to(self.device))
+        return cur
+
+    def _reference_logprobs(self, batches):
+        if self.reference_state is None:
+            self.reference_state = self.flat.data.to("cpu", copy=True)
+        cur = self._swap_flat(self.reference_state)
+        try:
+            return self._compute_logprobs_nograd(batches)
+        finally:
+            self.flat.data.copy_(cur.to(self.device))
+
+    def reference_reset(self) -> None:
+        """Make the current weights the new reference (every ``reference_reset_interval`` steps)."""
+        self.reference_state = self.flat.data.to("cpu", copy=True)
+        if self.tp_cfg.reset_optimizer_with_reference:
+            self.optimizer.m.zero_()
+            self.optimizer.v.zero_()
+
+    # ------------------------------------------------------------------ the step
+    def step_training(self, rollouts: Sequence[Rollout], current_step: int, total_steps: int,
+                      remain_samples_num: int = 0, do_save: bool = False, **kw) -> Dict[str, Any]:
+        t0 = time.perf_counter()
+        if self.device.type == "cuda":
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+        self.total_steps = total_steps
+        samples = self._prepare(rollouts)
+        n = len(samples)
+        per_opt = self.tp_cfg.batch_size_per_optimize or n
+        mu = max(1, self.tp_cfg.mu_iterations)
+        chunks = [list(range(i, min(i + per_opt, n))) for i in range(0, n, per_opt)]
+        need_old = len(chunks) > 1 or mu > 1
+        use_rollout_lp = self.tp_cfg.use_rollout_logprobs_for_loss
+        losses: List[torch.Tensor] = []
+        metrics_acc: Dict[str, List[torch.Tensor]] = {}
+        grad_norms: List[torch.Tensor] = []
+        dp_world = self.parallel_dims.dp_shard
+        self.model.train()
+
+        # pack once; the same packed mini-batches serve every phase
+        chunk_batches = []
+        for ch in chunks:
+            sub = [samples[i] for i in ch]
+            chunk_batches.append([self._pack([sub[i] for i in idxs]) for idxs in self._mini_batches(sub)])
+
+        ref_lps = old_lps = None
+        if self.tp_cfg.kl_beta != 0.0:
+            ref_lps = [self._reference_logprobs(bs) for bs in chunk_batches]
+        if need_old and not use_rollout_lp:
+            old_lps = [self._compute_logprobs_nograd(bs) for bs in chunk_batches]
+
+        for it in range(mu):
+            for ci, batches in enumerate(chunk_batches):
+                tok = torch.tensor(float(sum(int(b["sel"].numel()) for b in batches)), device=self.device)
+                if self.tp_cfg.balance_dp_token and dp_world > 1:
+                    dist.all_reduce(tok, group=self.parallel_dims.group("dp_shard"))
+                    tok = tok / dp_world
+                if self.inter_replica is not None and self.tp_cfg.balance_dp_token:
+                    tok = self.inter_replica.balance_token_count(tok)
+                self.optimizer.zero_grad()
+                for bi, b in enumerate(batches):
+                    lp, ent = self._forward_logprobs(b)
+                    if use_rollout_lp and "rollout_lp" in b:
+                        old = b["rollout_lp"]
+                    elif old_lps is not None:
+                        old = old_lps[ci][bi]
+                    else:
+                        old = lp.detach()
+                    loss, m = grpo_loss(
+                        lp, old, b["adv_tok"], b["seq_ids_sel"], int(b["cu_seqlens"].numel() - 1), self.loss_cfg,
+                        ref_logprob=ref_lps[ci][bi] if ref_lps is not None else None,
+                        rollout_logprob=b.get("rollout_lp"), entropy=ent, seq_rewards=b["seq_rewards"],
+                        total_tokens=tok if self.loss_cfg.loss_type == "token-mean" else None)
+                    if self.loss_cfg.loss_type != "token-mean":
+                        loss = loss * (len(b["seq_rewards"]) / max(1, sum(len(x["seq_rewards"]) for x in batches)))
+                    loss.backward()
+                    losses.append(loss.detach())
+                    for k, v in m.items():
+                        metrics_acc.setdefault(k, []).append(v.detach())
+                if self.inter_replica is not None:
+                    self.inter_replica.all_reduce_grads(self.flat.grad)
+                grad_norms.append(self.optimizer.step(self.lr_scale(self.train_step)))
+            # mu-iterations re-use the same old log-probs
+        self.train_step = current_step
+
+        if self.tp_cfg.reference_reset_interval and current_step % self.tp_cfg.reference_reset_interval == 0 \
+                and self.tp_cfg.kl_beta != 0.0:
+            self.reference_reset()
+        if do_save:
+            self.save_checkpoint(current_step, total_steps, remain_samples_num,
+                                 is_final=current_step >= total_steps)
+
+        if self.device.type == "cuda":
+            ev1.record()
+            ev1.synchronize()
+            iter_time = ev0.elapsed_time(ev1) / 1e3
+        else:
+            iter_time = time.perf_counter() - t0
+        loss_t = torch.stack(losses) if losses else torch.zeros(1, device=self.device)
+        n_mb = max(1, len(losses) // max(1, len(chunks) * mu))
+        report = {
+            "train/loss_avg": float(loss_t.sum() / max(1, len(chunks) * mu)),
+            "train/loss_max": float(loss_t.max() * n_mb),
+            "train/learning_rate": self.optimizer.lr * self.lr_scale(max(self.train_step - 1, 0)),
+            "train/iteration_time": iter_time,
+            "train/grad_norm": float(torch.stack(grad_norms).mean()) if grad_norms else 0.0,
+            "train/n_tokens": float(sum(len(s.ids) for s in samples)),
+        }
+        for k, v in metrics_acc.items():
+            report[f"train/{k}"] = float(torch.stack(v).mean())
+        if self.config.logging.report_mfu and self.device.type == "cuda":
+            from ...utils.misc import peak_flops
+            ntok = sum(len(s.ids) for s in samples)
+            avg_len = ntok / max(1, len(samples))
+            _, flops_per_tok = self.model.get_nparams_and_flops(int(avg_len))
+            report["train/mfu"] = flops_per_tok * ntok * mu / iter_time / peak_flops("bf16")
+        return report

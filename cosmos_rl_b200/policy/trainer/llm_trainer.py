@@ -1,0 +1,157 @@
+"""Shared machinery of the LLM trainers: model construction, flat parameter storage, optimizer, LR schedule,
+checkpointing and HF export (cosmos_rl/policy/trainer/llm_trainer/llm_trainer.py:51-790)."""
+from __future__ import annotations
+
+import json
+import os
+import time
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ...config import Config
+from ...data.packer import BaseDataPacker
+from ...models.base import ModelRegistry
+from ...parallel.dims import ParallelDims
+from ...parallel.flat import FlatParams
+from ...utils import checkpoint as ckpt_util
+from ...utils.logging import logger
+from ...utils.misc import seed_everything, str2dtype
+from ..optim import FlatAdamW, lr_factor
+from .base import Trainer
+
+
+def resolve_hf_config(config: Config):
+    """Model architecture: a named built-in architecture, a local HF folder, or a dict under [custom]."""
+    from ...models import hf_io
+    return hf_io.load_hf_config(config.policy.model_name_or_path, config.custom.get("model_config"))
+
+
+class LLMTrainer(Trainer):
+    def __init__(self, config: Config, parallel_dims: ParallelDims, device: Optional[torch.device] = None,
+                 data_packer: Optional[BaseDataPacker] = None, val_data_packer=None, hook_fns=None, **kw):
+        self.config = config
+        self.parallel_dims = parallel_dims
+        self.device = device or parallel_dims.device
+        self.hook_fns = hook_fns or {}
+        seed_everything(config.train.seed)
+        if config.train.deterministic and self.device.type == "cuda":
+            torch.use_deterministic_algorithms(True, warn_only=True)
+        self.param_dtype = str2dtype(config.train.param_dtype) if self.device.type == "cuda" else torch.float32
+        self.hf_config = resolve_hf_config(config)
+        mt = self.hf_config.get("model_type") if isinstance(self.hf_config, dict) else self.hf_config.model_type
+        self.model_type = mt
+        tp = parallel_dims.tp
+        with torch.device("meta"):
+            model = ModelRegistry.build_model(self.hf_config, tp_size=tp, tp_rank=parallel_dims.tp_coord)
+        # the model stays on the meta device here: FlatParams materialises every parameter as a view of
+        # one flat buffer, so no second copy of the weights is ever allocated
+        self.model = model
+        self._apply_trainable_patterns()
+        dp = parallel_dims.dp_shard
+        self.flat = FlatParams(model, self.param_dtype, self.device, shard_multiple=dp,
+                               allocator=kw.get("allocator"))
+        model.gradient_checkpointing = bool(config.policy.model_gradient_checkpointing)
+        if tp > 1:
+            from ...parallel.tp import TensorParallel
+            model.tp = TensorParallel(parallel_dims.group("tp"), tp, parallel_dims.tp_coord)
+        lr = config.train.optm_lr if isinstance(config.train.optm_lr, float) else float(
+            list(config.train.optm_lr.values())[0] if isinstance(config.train.optm_lr, dict) else config.train.optm_lr[0])
+        self.optimizer = FlatAdamW(
+            self.flat, lr=lr, betas=tuple(config.train.optm_betas), eps=config.train.epsilon,
+            weight_decay=config.train.optm_weight_decay, max_grad_norm=config.train.optm_grad_norm_clip,
+            dp_group=parallel_dims.group("dp_shard") if dp > 1 else None, collective=kw.get("collective"))
+        self.data_packer = data_packer or BaseDataPacker.get_default(mt)()
+        self.tokenizer = kw.get("tokenizer")
+        self.data_packer.setup(config, self.tokenizer)
+        self.ckpt_manager = ckpt_util.CheckpointManager(config, parallel_dims.global_rank)
+        self.train_step = 0
+        self.total_steps = 0
+        self.weights_ready = False
+
+    # ------------------------------------------------------------------
+    def _apply_trainable_patterns(self) -> None:
+        import re
+        pc = self.config.policy
+        for name, p in self.model.named_parameters():
+            if pc.freeze_pattern and any(re.search(pat, name) for pat in pc.freeze_pattern):
+                p.requires_grad_(False)
+            if pc.trainable_pattern:
+                p.requires_grad_(any(re.search(pat, name) for pat in pc.trainable_pattern))
+            if pc.trainable_map and name in pc.trainable_map:
+                p.requires_grad_(bool(pc.trainable_map[name]))
+
+    def lr_scale(self, step: int) -> float:
+        t = self.config.train
+        return lr_factor(step, self.total_steps, t.optm_warmup_steps, t.optm_warmup_start_factor, t.optm_decay_ratio,
+                         t.optm_decay_type, t.optm_min_lr_factor)
+
+    # ------------------------------------------------------------------ weights in
+    def model_load_from_hf(self) -> None:
+        from ...models import hf_io
+        path = self.config.policy.model_safetensor_path or self.config.policy.model_name_or_path
+        if path and os.path.isdir(path) and hf_io.has_safetensors(path):
+            hf_io.load_hf_weights(self.model, path, self.parallel_dims)
+        else:
+            seed = self.config.train.seed if self.config.train.seed is not None else 0
+            if self.device.type == "cuda":
+                self.model.init_weights_on_device(seed)
+            else:
+                self.model.init_weights(seed)
+            logger.info("[Policy] no checkpoint at %r: random-init weights from seed %d", path, seed)
+        self.optimizer.refresh_master_from_params()
+        self.weights_ready = True
+
+    def model_resume_from_checkpoint(self) -> bool:
+        state = self.ckpt_manager.load_latest(self.device)
+        if state is None:
+            return False
+        self.flat.data.copy_(state["model"]["flat"].to(self.flat.dtype))
+        self.optimizer.load_state_dict(state["optimizer"])
+        extra = state["extra_info"]
+        self.train_step = int(extra.get("step", 0))
+        self.total_steps = int(extra.get("total_steps", 0))
+        ckpt_util.restore_rng(extra)
+        self.resume_extra_info = extra
+        self.weights_ready = True
+        logger.info("[Policy] resumed from checkpoint at step %d", self.train_step)
+        return True
+
+    def weight_resume(self) -> bool:
+        """Load the latest valid checkpoint when resuming, else the HF weights. Returns True if resumed."""
+        if self.config.train.resume and self.model_resume_from_checkpoint():
+            return True
+        self.model_load_from_hf()
+        return False
+
+    # ------------------------------------------------------------------ weights out
+    def save_checkpoint(self, step: int, total_steps: int, remain_samples_num: int = 0, is_final: bool = False,
+                        **kw) -> None:
+        extra = {"step": step, "total_steps": total_steps, "remain_samples_num": remain_samples_num,
+                 "is_final": is_final}
+        self.ckpt_manager.save(step, model_state={"flat": self.flat.data, "slots": [s.__dict__ for s in self.flat.slots]},
+                               optimizer_state=self.optimizer.state_dict(), scheduler_state={"step": step},
+                               extra_info=extra, is_final=is_final)
+        if self.config.train.ckpt.export_safetensors:
+            out = os.path.join(self.config.train.output_dir, "safetensors", f"step_{step}")
+            self.export_safetensors(out)
+        hook = self.hook_fns.get("save_checkpoint_hook")
+        if hook:
+            hook(step=step, trainer=self)
+
+    def export_safetensors(self, output_dir: str, **kw) -> None:
+        from ...models import hf_io
+        hf_io.export_safetensors(self.model, self.hf_config, output_dir, self.parallel_dims,
+                                 source_dir=self.config.policy.model_name_or_path)
+
+    # ------------------------------------------------------------------ state shipping (elastic scale-up)
+    def state_tensors(self) -> List[Tuple[str, torch.Tensor]]:
+        """Every tensor a new policy replica needs to continue identically: weights, optimizer state, step."""
+        meta = torch.tensor([self.train_step, self.total_steps, self.optimizer.step_count], dtype=torch.int64,
+                            device=self.device)
+        return [("flat.data", self.flat.data), *self.optimizer.state_tensors(), ("meta", meta)]
+
+    def after_state_received(self, meta: torch.Tensor) -> None:
+        self.train_step, self.total_steps, self.optimizer.step_count = (int(x) for x in meta.tolist())
+        self.weights_ready = True

@@ -1,0 +1,415 @@
+"""The built-in generation engine (replaces vLLM / TensorRT-LLM of the reference:
+cosmos_rl/rollout/vllm_rollout/vllm_rollout.py:145-1128).
+
+* Paged KV cache ``[layers, pages, 2, hkv, page_size, d]``; page 0 is a scratch page for padded slots.
+* Each prompt is prefilled once; its ``n`` samples share the prompt's full pages and own the rest
+  (pages for the whole response are reserved at admission, so a running sequence is never preempted).
+* The decode step (embedding -> layers with paged attention -> lm_head -> fused sampler -> bookkeeping)
+  runs entirely on the device and is replayed from a CUDA graph per batch-size bucket; the host looks at
+  the produced tokens only every ``check_interval`` steps to retire finished sequences and admit new ones.
+* The engine runs on the policy model's own parameter tensors when colocated, or on its own copy that the
+  weight-sync kernel writes into.
+On CPU the same code runs with the PyTorch statements of the ops (no graphs).
+"""
+from __future__ import annotations
+
+import math
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Any, Deque, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..ops import functional as F
+from ..utils.logging import logger
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = -1
+    repetition_penalty: float = 1.0
+    n: int = 1
+    max_tokens: int = 128
+    stop_token_ids: Tuple[int, ...] = ()
+    logprobs: bool = True
+    seed: Optional[int] = None
+
+    @classmethod
+    def from_config(cls, config, validation: bool = False) -> "SamplingParams":
+        r, s = config.rollout, config.rollout.sampling_config
+        if validation:
+            v = config.validation
+            return cls(temperature=v.temperature, top_p=v.top_p if v.top_p is not None else s.top_p,
+                       top_k=v.top_k if v.top_k is not None else s.top_k, repetition_penalty=v.repetition_penalty,
+                       n=v.n_generation, max_tokens=v.max_response_length or r.max_response_length, seed=r.seed)
+        return cls(temperature=s.temperature, top_p=s.top_p, top_k=s.top_k, repetition_penalty=s.repetition_penalty,
+                   n=r.n_generation, max_tokens=r.max_response_length, seed=r.seed)
+
+
+@dataclass
+class Completion:
+    token_ids: List[int]
+    logprobs: List[float]
+    finish_reason: str = "length"
+
+    @property
+    def cumulative_logprob(self) -> float:
+        return float(sum(self.logprobs))
+
+
+@dataclass
+class _Seq:
+    prompt_idx: int
+    sample_idx: int
+    slot: int
+    pages: List[int]
+    shared_pages: int
+    start_step: int = 0
+    n_generated: int = 0
+    tokens: List[int] = field(default_factory=list)
+    lps: List[float] = field(default_factory=list)
+    done: bool = False
+    finish_reason: str = "length"
+
+
+class RolloutEngine:
+    def __init__(self, model, *, max_num_seqs: int = 128, max_model_len: int = 2048, page_size: int = 128,
+                 num_pages: Optional[int] = None, max_prefill_tokens: int = 16384, use_cuda_graph: bool = True,
+                 check_interval: int = 16, seed: int = 0, tp=None):
+        self.model = model
+        self.args = model.args
+        self.device = model.norm.device
+        self.dtype = model.norm.dtype
+        self.cuda = self.device.type == "cuda"
+        self.S = max_num_seqs
+        self.max_model_len = max_model_len
+        self.P = page_size if self.cuda else min(page_size, 16)
+        self.max_pages_per_seq = (max_model_len + check_interval + self.P - 1) // self.P + 1
+        a = self.args
+        self.hq = a.n_heads // a.tp_size
+        self.hkv = max(1, a.n_kv_heads // a.tp_size)
+        self.d = a.head_dim
+        self.L = a.n_layers
+        if num_pages is None:
+            num_pages = 1 + self.S * self.max_pages_per_seq
+        self.num_pages = num_pages
+        self.kv = torch.zeros(self.L, num_pages, 2, self.hkv, self.P, self.d, dtype=self.dtype, device=self.device)
+        self.free_pages: List[int] = list(range(num_pages - 1, 0, -1))
+        self.page_refs: Dict[int, int] = {}
+        self.max_prefill_tokens = max_prefill_tokens
+        self.use_graph = use_cuda_graph and self.cuda
+        self.check_interval = check_interval if self.cuda else 1
+        self.seed = seed
+        self.tp = tp if tp is not None else getattr(model, "tp", None)
+        self.weight_version = 0
+        # ---- static decode state (device)
+        S = self.S
+        i32 = dict(dtype=torch.int32, device=self.device)
+        self.block_table = torch.zeros(S, self.max_pages_per_seq, **i32)
+        self.cur_len = torch.zeros(S, **i32)
+        self.active = torch.zeros(S, **i32)
+        self.last_tok = torch.zeros(S, dtype=torch.int64, device=self.device)
+        self.temp = torch.ones(S, dtype=torch.float32, device=self.device)
+        self.top_p = torch.ones(S, dtype=torch.float32, device=self.device)
+        self.top_k = torch.full((S,), -1, **i32)
+        self.step_counter = torch.zeros(1, dtype=torch.int64, device=self.device)
+        self.ring = max(self.check_interval, 1)
+        self.out_tok = torch.zeros(self.ring, S, dtype=torch.int64, device=self.device)
+        self.out_lp = torch.zeros(self.ring, S, dtype=torch.float32, device=self.device)
+        self.graphs: Dict[int, Any] = {}
+        self.graph_launches: Dict[int, int] = {}
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "decode_steps": 0}
+
+    # ------------------------------------------------------------------ pages
+    def _alloc(self, n: int) -> List[int]:
+        if len(self.free_pages) < n:
+            raise RuntimeError("KV cache exhausted")
+        out = [self.free_pages.pop() for _ in range(n)]
+        for p in out:
+            self.page_refs[p] = 1
+        return out
+
+    def _release(self, pages: Sequence[int]) -> None:
+        for p in pages:
+            self.page_refs[p] -= 1
+            if self.page_refs[p] == 0:
+                del self.page_refs[p]
+                self.free_pages.append(p)
+
+    def pages_needed(self, prompt_len: int, max_tokens: int, n: int) -> int:
+        total = prompt_len + max_tokens + self.check_interval
+        per_seq = (total + self.P - 1) // self.P
+        shared = prompt_len // self.P
+        return shared + n * (per_seq - shared)
+
+    # ------------------------------------------------------------------ model pieces
+    def _layers(self, h, positions, slot_mapping, attn):
+        res = None
+        m = self.model
+        eps = self.args.norm_eps
+        for li, layer in enumerate(m.layers):
+            if res is None:
+                x, _ = F.rms_norm(h, layer.input_layernorm, eps)
+                res = h
+            else:
+                x, res = F.rms_norm(h, layer.input_layernorm, eps, residual=res)
+            q, k, v = layer.self_attn.project_qkv(x, positions)
+            F.kv_append(k, v, self.kv[li], slot_mapping)
+            o = attn(li, q, k, v)
+            h = torch.nn.functional.linear(o.reshape(o.shape[0], -1), layer.self_attn.o_proj.weight)
+            if self.tp is not None:
+                h = self.tp.reduce_output(h)
+            x, res = F.rms_norm(h, layer.post_attention_layernorm, eps, residual=res)
+            h = layer.mlp(x, self.tp)
+        out, _ = F.rms_norm(h, m.norm, eps, residual=res)
+        return out
+
+    # ------------------------------------------------------------------ prefill
+    @torch.no_grad()
+    def _prefill(self, prompts: List[List[int]], page_lists: List[List[int]]) -> torch.Tensor:
+        """Run the prompts (packed), fill their pages, return last-position logits [n_prompts, V] fp32."""
+        if torch.is_tensor(prompts[0]):
+            ids = torch.cat([p.to(self.device, dtype=torch.long) for p in prompts])
+        else:
+            ids = torch.tensor([t for p in prompts for t in p], dtype=torch.long, device=self.device)
+        lens = [len(p) for p in prompts]
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0).tolist()), dtype=torch.int32, device=self.device)
+        pos = torch.cat([torch.arange(n, device=self.device) for n in lens])
+        slots = []
+        for n, pages in zip(lens, page_lists):
+            t = torch.arange(n)
+            slots.append(torch.tensor(pages, dtype=torch.long)[t // self.P] * self.P + t % self.P)
+        slot_mapping = torch.cat(slots).to(torch.int32).to(self.device)
+        max_len = max(lens)
+        h = self.model.embed(ids)
+        out = self._layers(h, pos, slot_mapping,
+                           lambda li, q, k, v: F.varlen_attention(q, k, v, cu, max_len))
+        last = (cu[1:] - 1).long()
+        self.stats["prefill_tokens"] += int(ids.numel())
+        return self.model.logits(out[last]).float()
+
+    # ------------------------------------------------------------------ decode
+    def _decode_body(self, B: int) -> None:
+        """One decode step for slots [0, B): everything on the device, no host reads."""
+        cur = self.cur_len[:B]
+        act = self.active[:B]
+        page_idx = (cur // self.P).long()
+        page = self.block_table[:B].gather(1, page_idx[:, None]).squeeze(1)
+        slot = torch.where(act > 0, page * self.P + cur % self.P, torch.full_like(cur, -1))
+        seq_lens = torch.where(act > 0, cur + 1, torch.ones_like(cur))
+        h = self.model.embed(self.last_tok[:B])
+        bt = self.block_table[:B]
+        out = self._layers(h, cur.long(), slot,
+                           lambda li, q, k, v: F.paged_decode(q, self.kv[li], bt, seq_lens))
+        logits = self.model.logits(out)
+        r = (self.step_counter % self.ring).long()
+        if self.cuda:
+            toks = torch.empty(B, dtype=torch.int64, device=self.device)
+            lps = torch.empty(B, dtype=torch.float32, device=self.device)
+            F.sample(logits, self.temp[:B], self.top_p[:B], self.top_k[:B], seed=self.seed, offset=1 << 20,
+                     offset_dev=self.step_counter, out_tokens=toks, out_logprobs=lps)
+        else:
+            toks, lps = F.sample(logits.float(), self.temp[:B], self.top_p[:B], self.top_k[:B])
+        self.out_tok.index_copy_(0, r, toks.unsqueeze(0) if B == self.S else
+                                 torch.cat([toks, self.out_tok[0, B:]]).unsqueeze(0))
+        self.out_lp.index_copy_(0, r, lps.unsqueeze(0) if B == self.S else
+                                torch.cat([lps, self.out_lp[0, B:]]).unsqueeze(0))
+        self.last_tok[:B] = torch.where(act > 0, toks, self.last_tok[:B])
+        self.cur_len[:B] += act
+        self.step_counter += 1
+
+    def _bucket(self, n: int) -> int:
+        b = 8
+        while b < n:
+            b *= 2
+        return min(b, self.S)
+
+    @torch.no_grad()
+    def _decode_step(self, n_slots: int) -> None:
+        B = self._bucket(n_slots)
+        if not self.use_graph:
+            self._decode_body(B)
+            return
+        g = self.graphs.get(B)
+        if g is None:
+            # warm up outside capture (lazy initialisations, autotuned library GEMMs), then restore state
+            saved = (self.cur_len.clone(), self.last_tok.clone(), self.step_counter.clone(),
+                     self.out_tok.clone(), self.out_lp.clone())
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                for _ in range(2):
+                    self._decode_body(B)
+            torch.cuda.current_stream().wait_stream(s)
+            g = torch.cuda.CUDAGraph()
+            from ..ops import native
+            before = native.LAUNCHES[0]
+            with torch.cuda.graph(g):
+                self._decode_body(B)
+            self.graph_launches[B] = native.LAUNCHES[0] - before
+            self.cur_len.copy_(saved[0]); self.last_tok.copy_(saved[1]); self.step_counter.copy_(saved[2])
+            self.out_tok.copy_(saved[3]); self.out_lp.copy_(saved[4])
+            self.graphs[B] = g
+        g.replay()
+        from ..ops import native
+        native.add_launches(self.graph_launches.get(B, 0))
+
+    # ------------------------------------------------------------------ public API
+    @torch.no_grad()
+    def generate(self, prompts: Sequence[Sequence[int]], sp: SamplingParams) -> List[List[Completion]]:
+        """Generate ``sp.n`` completions for every prompt (token id lists)."""
+        n = max(1, sp.n)
+        results: List[List[Optional[Completion]]] = [[None] * n for _ in prompts]
+        waiting: Deque[int] = deque(range(len(prompts)))
+        running: Dict[int, _Seq] = {}
+        free_slots = list(range(self.S - 1, -1, -1))
+        stop = set(sp.stop_token_ids)
+        if sp.seed is not None:
+            self.seed = sp.seed
+        steps_since_check = 0
+        host_step = 0
+
+        def admit() -> None:
+            nonlocal host_step
+            batch, page_lists, tok_budget = [], [], self.max_prefill_tokens
+            while waiting and len(free_slots) >= n:
+                pi = waiting[0]
+                p = prompts[pi] if torch.is_tensor(prompts[pi]) else list(prompts[pi])
+                if len(p) + sp.max_tokens > self.max_model_len:
+                    p = p[-(self.max_model_len - sp.max_tokens):]
+                need = self.pages_needed(len(p), sp.max_tokens, n)
+                if need > len(self.free_pages) or (batch and len(p) > tok_budget):
+                    break
+                waiting.popleft()
+                n_prompt_pages = (len(p) + self.P - 1) // self.P
+                pp = self._alloc(n_prompt_pages)
+                batch.append((pi, p, pp))
+                page_lists.append(pp)
+                tok_budget -= len(p)
+                for _ in range(n):
+                    free_slots.pop()  # reserve; the real slot ids are assigned below
+            if not batch:
+                return
+            logits = self._prefill([b[1] for b in batch], page_lists)
+            # first token of each of the n samples comes from the prompt's last-position logits
+            rep = logits.repeat_interleave(n, dim=0)
+            B0 = rep.shape[0]
+            t = torch.full((B0,), sp.temperature, dtype=torch.float32, device=self.device)
+            tp_ = torch.full((B0,), sp.top_p, dtype=torch.float32, device=self.device)
+            tk = torch.full((B0,), sp.top_k, dtype=torch.int32, device=self.device)
+            first_tok, first_lp = F.sample(rep, t, tp_, tk, seed=self.seed, offset=host_step)
+            first_tok_h, first_lp_h = first_tok.tolist(), first_lp.tolist()
+            total_per_seq = lambda L: (L + sp.max_tokens + self.check_interval + self.P - 1) // self.P
+            slots_taken = []
+            for bi, (pi, p, pp) in enumerate(batch):
+                shared = len(p) // self.P
+                for si in range(n):
+                    slot = self._take_slot(running)
+                    own_n = total_per_seq(len(p)) - shared
+                    own = self._alloc(own_n)
+                    for q in pp[:shared]:
+                        self.page_refs[q] += 1
+                    pages = pp[:shared] + own
+                    if shared < len(pp):
+                        # the prompt's partial last page is private: copy it
+                        self.kv[:, own[0]].copy_(self.kv[:, pp[shared]])
+                    seq = _Seq(pi, si, slot, pages, shared, start_step=host_step)
+                    k = bi * n + si
+                    seq.tokens.append(first_tok_h[k])
+                    seq.lps.append(first_lp_h[k])
+                    seq.n_generated = 1
+                    running[slot] = seq
+                    slots_taken.append((slot, pages, len(p), first_tok_h[k]))
+                self._release(pp)  # drop the prefill's own reference; children hold theirs
+            # publish the new sequences' state to the device in one shot
+            idx = torch.tensor([s[0] for s in slots_taken], dtype=torch.long, device=self.device)
+            bt = torch.zeros(len(slots_taken), self.max_pages_per_seq, dtype=torch.int32)
+            for i, (_, pages, _, _) in enumerate(slots_taken):
+                bt[i, : len(pages)] = torch.tensor(pages, dtype=torch.int32)
+            self.block_table.index_copy_(0, idx, bt.to(self.device))
+            self.cur_len.index_copy_(0, idx, torch.tensor([s[2] for s in slots_taken], dtype=torch.int32, device=self.device))
+            self.last_tok.index_copy_(0, idx, torch.tensor([s[3] for s in slots_taken], dtype=torch.int64, device=self.device))
+            self.active.index_fill_(0, idx, 1)
+            self.temp.index_fill_(0, idx, sp.temperature)
+            self.top_p.index_fill_(0, idx, sp.top_p)
+            self.top_k.index_fill_(0, idx, sp.top_k)
+
+        self._free_slots = free_slots
+
+        def retire(seq: _Seq, reason: str) -> None:
+            seq.done, seq.finish_reason = True, reason
+            results[seq.prompt_idx][seq.sample_idx] = Completion(seq.tokens, seq.lps, reason)
+            self._release(seq.pages)
+            del running[seq.slot]
+            free_slots.append(seq.slot)
+            self.active[seq.slot] = 0
+
+        def harvest(n_steps: int) -> None:
+            """Read the last ``n_steps`` rows of the token ring and retire finished sequences."""
+            if n_steps == 0:
+                return
+            sc = int(self.step_counter.item())
+            rows = [(sc - n_steps + i) % self.ring for i in range(n_steps)]
+            toks = self.out_tok[rows].tolist()
+            lps = self.out_lp[rows].tolist()
+            for slot, seq in list(running.items()):
+                first = max(0, seq.start_step - (host_step - n_steps))
+                for i in range(first, n_steps):
+                    if seq.done:
+                        break
+                    tok = toks[i][slot]
+                    seq.tokens.append(tok)
+                    seq.lps.append(lps[i][slot])
+                    seq.n_generated += 1
+                    if tok in stop:
+                        retire(seq, "stop")
+                    elif seq.n_generated >= sp.max_tokens:
+                        retire(seq, "length")
+            # sequences that finished on their very first token
+            for slot, seq in list(running.items()):
+                if not seq.done and (seq.tokens[-1] in stop or seq.n_generated >= sp.max_tokens):
+                    retire(seq, "stop" if seq.tokens[-1] in stop else "length")
+
+        admit()
+        harvest(0)
+        for slot, seq in list(running.items()):
+            if seq.tokens[-1] in stop or seq.n_generated >= sp.max_tokens:
+                retire(seq, "stop" if seq.tokens[-1] in stop else "length")
+        while running or waiting:
+            if not running:
+                admit()
+                if not running:
+                    raise RuntimeError("a prompt does not fit in the KV cache")
+                continue
+            hi = max(running) + 1
+            self._decode_step(hi)
+            host_step += 1
+            steps_since_check += 1
+            self.stats["decode_steps"] += 1
+            self.stats["decode_tokens"] += len(running)
+            remaining = min(sp.max_tokens - s.n_generated - steps_since_check for s in running.values())
+            if steps_since_check >= self.check_interval or remaining <= 0:
+                harvest(steps_since_check)
+                steps_since_check = 0
+                if waiting:
+                    admit()
+        return [[c for c in row] for row in results]
+
+    def _take_slot(self, running: Dict[int, _Seq]) -> int:
+        # lowest free slot keeps the active range dense (smaller decode buckets)
+        s = 0
+        while s in running:
+            s += 1
+        return s
+
+    def release_cache(self) -> None:
+        """Free the KV cache memory (colocated mode hands the memory to training)."""
+        self.kv = None
+        self.graphs.clear()
+        if self.cuda:
+            torch.cuda.empty_cache()
+
+    def invalidate_graphs(self) -> None:
+        self.graphs.clear()
