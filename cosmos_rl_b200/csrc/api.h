@@ -71,6 +71,16 @@ int b200_kv_append(const void* k, const void* v, void* cache, const int* slot_ma
 int b200_paged_decode(const void* q, const void* cache, const int* block_table, const int* seq_lens, void* out,
                       float* scratch, int B, int hq, int hkv, int d, int page_size, int max_pages, int nsplit,
                       float scale, cudaStream_t stream);
+// Decode attention for callers that cannot allocate device memory (a host that gave the whole device to
+// weights and KV cache at start-up, or plain-C callers without a device allocator). Same computation and
+// arguments as b200_paged_decode, minus `scratch`: the split-merge scratch is a 16 MiB array inside the
+// library, held by every GPU that loads it until exit. Limit: B * hq * nsplit * (d + 2) <= 4 Mi floats,
+// otherwise B200_ERR_TOO_LARGE. The first call on a device resolves the array's device address and should
+// come before any stream capture; calls that overlap on the GPU race on the shared array. Allocates
+// nothing. This entry point has no counterpart in the reference.
+int b200_paged_decode_static(const void* q, const void* cache, const int* block_table, const int* seq_lens,
+                             void* out, int B, int hq, int hkv, int d, int page_size, int max_pages, int nsplit,
+                             float scale, cudaStream_t stream);
 // Varlen causal flash attention (packed sequences, GQA). q [T,hq,d], k/v [T,hkv,d] with row strides.
 int b200_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_seqlens,
                    int n_seqs, int T, int hq, int hkv, int d, long long q_stride, long long kv_stride,

@@ -255,3 +255,68 @@ int b200_paged_decode(const void* q, const void* cache, const int* block_table, 
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------
+// Split-KV decode attention for callers that cannot allocate device memory.
+//
+// Who needs this: a host program that embeds the rollout engine after it has already given the whole
+// device to weights and KV cache (its memory budget is fixed at start-up, so a later cudaMalloc can
+// fail or fragment the budget), or a caller written against the plain C ABI that has no device
+// allocator of its own to obtain the split-merge scratch buffer from. For them the scratch lives in the
+// library image: a file-scope __device__ array of PD_STATIC_SCRATCH_FLOATS floats (16 MiB). Every GPU
+// on which this library is loaded holds that array from load until the process exits.
+//
+// Rules of use:
+//  * The first call on a device looks up the array's device address (cudaGetSymbolAddress with that
+//    device current) and remembers it; make that first call before any stream capture begins.
+//  * B * hq * nsplit * (d + 2) must not exceed PD_STATIC_SCRATCH_FLOATS, else B200_ERR_TOO_LARGE is
+//    returned and nothing is launched.
+//  * All calls on a device share the one array. The first kernel writes every element the merge kernel
+//    reads (empty splits included), so nothing has to be cleared and contents left by the previous call
+//    are harmless; but two calls whose kernels overlap on the GPU (different streams) would race on it.
+//  * No cudaMalloc, cudaFree or other allocating routine is called, here or in the kernels.
+// ---------------------------------------------------------------------------------------------------
+#include <mutex>
+
+#define PD_STATIC_SCRATCH_FLOATS (4u * 1024u * 1024u)
+#define PD_MAX_DEVICES 64
+
+static __device__ __align__(256) float g_pd_static_scratch[PD_STATIC_SCRATCH_FLOATS];
+static float* g_pd_scratch_addr[PD_MAX_DEVICES];  // device address of the array, per device
+static std::mutex g_pd_scratch_mu;
+
+extern "C" int b200_paged_decode_static(const void* q, const void* cache, const int* block_table,
+                                        const int* seq_lens, void* out, int B, int hq, int hkv, int d,
+                                        int page_size, int max_pages, int nsplit, float scale,
+                                        cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (hkv <= 0 || hq % hkv || hq / hkv > PD_MAXG || nsplit <= 0 || (d != 128 && d != 64)) return B200_ERR_ARG;
+  const unsigned long long need = (unsigned long long)B * hq * nsplit * (d + 2);
+  if (need > PD_STATIC_SCRATCH_FLOATS) return B200_ERR_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= PD_MAX_DEVICES) return B200_ERR_RUNTIME;
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_pd_scratch_mu);
+    if (g_pd_scratch_addr[dev] == nullptr) {
+      // In host code the array's name is only a stand-in; the address the kernel may use comes from here.
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_pd_static_scratch) != cudaSuccess || p == nullptr) return B200_ERR_RUNTIME;
+      g_pd_scratch_addr[dev] = static_cast<float*>(p);
+    }
+    scratch = g_pd_scratch_addr[dev];
+  }
+  dim3 grid(hkv, B, nsplit);
+  if (d == 128) {
+    paged_decode_kernel<128><<<grid, PD_WARPS * 32, 0, stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_table, seq_lens, (__nv_bfloat16*)out, scratch, hq,
+        hkv, page_size, max_pages, nsplit, scale * LOG2E);
+    if (nsplit > 1) paged_decode_merge_kernel<128><<<B * hq, 128, 0, stream>>>(scratch, (__nv_bfloat16*)out, nsplit);
+  } else {
+    paged_decode_kernel<64><<<grid, PD_WARPS * 32, 0, stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_table, seq_lens, (__nv_bfloat16*)out, scratch, hq,
+        hkv, page_size, max_pages, nsplit, scale * LOG2E);
+    if (nsplit > 1) paged_decode_merge_kernel<64><<<B * hq, 64, 0, stream>>>(scratch, (__nv_bfloat16*)out, nsplit);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : B200_ERR_LAUNCH;
+}
