@@ -71,6 +71,14 @@ int b200_kv_append(const void* k, const void* v, void* cache, const int* slot_ma
 int b200_paged_decode(const void* q, const void* cache, const int* block_table, const int* seq_lens, void* out,
                       float* scratch, int B, int hq, int hkv, int d, int page_size, int max_pages, int nsplit,
                       float scale, cudaStream_t stream);
+// Tensor-core (tcgen05 + TMA) decode attention. Requires d == 128, page_size == 128 and the cache layout
+// [pages, 2, hkv, 128 x 128] with K slabs as [token, d] and V slabs transposed as [d, token]
+// (written by b200_kv_append_vt). hq / hkv <= 8.
+int b200_kv_append_vt(const void* k, const void* v, void* cache, const int* slot_mapping, int T, int hkv, int d,
+                      long long k_stride, long long v_stride, int page_size, cudaStream_t stream);
+int b200_paged_decode_tc(const void* q, const void* cache, long long num_pages, const int* block_table,
+                         const int* seq_lens, void* out, float* scratch, int B, int hq, int hkv, int d, int page_size,
+                         int max_pages, int nsplit, float scale, uint32_t* status, int num_sms, cudaStream_t stream);
 // Decode attention for callers that cannot allocate device memory (a host that gave the whole device to
 // weights and KV cache at start-up, or plain-C callers without a device allocator). Same computation and
 // arguments as b200_paged_decode, minus `scratch`: the split-merge scratch is a 16 MiB array inside the

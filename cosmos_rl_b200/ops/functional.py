@@ -317,33 +317,55 @@ def varlen_attention(q, k, v, cu_seqlens, max_seqlen: int, scale: Optional[float
     return reference.varlen_attention(q, k, v, cu_seqlens, scale)
 
 
-def kv_append(k, v, cache, slot_mapping):
+def tc_decode_supported(d: int, page_size: int, hq: int, hkv: int) -> bool:
+    """The tcgen05 decode kernel needs head_dim 128, 128-token pages and a GQA group of at most 8."""
+    return d == 128 and page_size == 128 and hq % hkv == 0 and hq // hkv <= 8
+
+
+def kv_append(k, v, cache, slot_mapping, v_transposed: bool = False):
+    """Write new K/V rows into the paged cache ``[pages, 2, hkv, page_size, d]``. With ``v_transposed`` the V
+    slabs are stored as ``[d, page_size]`` (the layout the tensor-core decode kernel consumes)."""
     if k.is_cuda:
         T, hkv, d = k.shape
         assert k.stride(-1) == 1 and k.stride(1) == d and v.stride(-1) == 1 and v.stride(1) == d
-        native.check(native.lib().b200_kv_append(native.ptr(k), native.ptr(v), native.ptr(cache),
-                                                 native.ptr(slot_mapping), T, hkv, d, k.stride(0), v.stride(0),
-                                                 cache.shape[3], native.stream()), "kv_append")
+        fn = native.lib().b200_kv_append_vt if v_transposed else native.lib().b200_kv_append
+        native.check(fn(native.ptr(k), native.ptr(v), native.ptr(cache), native.ptr(slot_mapping), T, hkv, d,
+                        k.stride(0), v.stride(0), cache.shape[3], native.stream()), "kv_append")
     else:
-        reference.kv_append(k, v, cache, slot_mapping)
+        reference.kv_append(k, v, cache, slot_mapping, v_transposed)
 
 
 def paged_decode(q, cache, block_table, seq_lens, scale: Optional[float] = None, nsplit: Optional[int] = None,
-                 scratch: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):
-    """Decode attention of ``q [B, hq, d]`` against the paged cache ``[pages, 2, hkv, page_size, d]``."""
+                 scratch: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                 v_transposed: bool = False):
+    """Decode attention of ``q [B, hq, d]`` against the paged cache ``[pages, 2, hkv, page_size, d]``.
+    ``v_transposed`` selects the tcgen05 kernel (V slabs stored ``[d, page_size]``)."""
     if not q.is_cuda:
-        return reference.paged_decode(q, cache, block_table, seq_lens, scale)
+        return reference.paged_decode(q, cache, block_table, seq_lens, scale, v_transposed)
     B, hq, d = q.shape
     hkv, page_size = cache.shape[2], cache.shape[3]
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    dev = q.device.index if q.device.index is not None else torch.cuda.current_device()
+    sms = native.num_sms(dev)
     if nsplit is None:
-        # fill the machine: B*hkv CTAs per split
-        nsplit = max(1, min(16, (2 * 148) // max(1, B * hkv)))
+        if v_transposed:
+            # persistent kernel: at least ~2 work items per SM, splits only when B * hkv under-fills the machine
+            nsplit = max(1, min(8, (2 * sms) // max(1, B * hkv)))
+        else:
+            nsplit = max(1, min(16, (2 * sms) // max(1, B * hkv)))
     if out is None:
         out = torch.empty_like(q)
     if nsplit > 1 and scratch is None:
         scratch = torch.empty(B * hq * nsplit * (d + 2), dtype=torch.float32, device=q.device)
-    native.check(native.lib().b200_paged_decode(native.ptr(_c(q)), native.ptr(cache), native.ptr(block_table),
+    qc = _c(q)
+    if v_transposed:
+        st = native.status_word(q.device)
+        native.check(native.lib().b200_paged_decode_tc(
+            native.ptr(qc), native.ptr(cache), cache.shape[0], native.ptr(block_table), native.ptr(seq_lens),
+            native.ptr(out), native.ptr(scratch), B, hq, hkv, d, page_size, block_table.shape[1], nsplit, scale,
+            native.ptr(st), sms, native.stream()), "paged_decode_tc")
+        return out
+    native.check(native.lib().b200_paged_decode(native.ptr(qc), native.ptr(cache), native.ptr(block_table),
                                                 native.ptr(seq_lens), native.ptr(out), native.ptr(scratch), B, hq,
                                                 hkv, d, page_size, block_table.shape[1], nsplit, scale,
                                                 native.stream()), "paged_decode")

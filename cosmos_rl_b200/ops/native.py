@@ -74,6 +74,10 @@ _SIGS = {
                        c_void_p],
     "b200_paged_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_int, c_float, c_void_p],
+    "b200_kv_append_vt": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
+                          c_void_p],
+    "b200_paged_decode_tc": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
     "b200_quant_fp8_block": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
     "b200_reshard_pull": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
 }

@@ -92,8 +92,9 @@ def varlen_attention(q, k, v, cu_seqlens, scale: Optional[float] = None, causal:
     return out
 
 
-def paged_decode(q, cache, block_table, seq_lens, scale: Optional[float] = None):
-    """One-query-per-sequence attention over a paged cache ``[pages, 2, hkv, page_size, d]``."""
+def paged_decode(q, cache, block_table, seq_lens, scale: Optional[float] = None, v_transposed: bool = False):
+    """One-query-per-sequence attention over a paged cache ``[pages, 2, hkv, page_size, d]`` (V slabs stored
+    as ``[d, page_size]`` when ``v_transposed``)."""
     B, hq, d = q.shape
     hkv, page_size = cache.shape[2], cache.shape[3]
     g = hq // hkv
@@ -106,7 +107,10 @@ def paged_decode(q, cache, block_table, seq_lens, scale: Optional[float] = None)
         n_pages = (L + page_size - 1) // page_size
         pages = block_table[b, :n_pages].long()
         kk = cache[pages, 0].permute(1, 0, 2, 3).reshape(hkv, -1, d)[:, :L].float()
-        vv = cache[pages, 1].permute(1, 0, 2, 3).reshape(hkv, -1, d)[:, :L].float()
+        if v_transposed:
+            vv = cache[pages, 1].reshape(-1, hkv, d, page_size).permute(1, 0, 3, 2).reshape(hkv, -1, d)[:, :L].float()
+        else:
+            vv = cache[pages, 1].permute(1, 0, 2, 3).reshape(hkv, -1, d)[:, :L].float()
         kk = kk.repeat_interleave(g, dim=0)
         vv = vv.repeat_interleave(g, dim=0)
         sc = torch.einsum("hd,hld->hl", q[b].float(), kk) * scale
@@ -114,15 +118,19 @@ def paged_decode(q, cache, block_table, seq_lens, scale: Optional[float] = None)
     return out
 
 
-def kv_append(k, v, cache, slot_mapping):
+def kv_append(k, v, cache, slot_mapping, v_transposed: bool = False):
     page_size = cache.shape[3]
+    hkv, d = k.shape[1], k.shape[2]
     for t in range(k.shape[0]):
         slot = int(slot_mapping[t])
         if slot < 0:
             continue
         page, off = divmod(slot, page_size)
         cache[page, 0, :, off] = k[t]
-        cache[page, 1, :, off] = v[t]
+        if v_transposed:
+            cache[page, 1].view(hkv, d, page_size)[:, :, off] = v[t]
+        else:
+            cache[page, 1, :, off] = v[t]
 
 
 def sample(logits, temperature, top_p, top_k, generator: Optional[torch.Generator] = None):

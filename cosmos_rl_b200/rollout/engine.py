@@ -96,6 +96,8 @@ class RolloutEngine:
             num_pages = 1 + self.S * self.max_pages_per_seq
         self.num_pages = num_pages
         self.kv = torch.zeros(self.L, num_pages, 2, self.hkv, self.P, self.d, dtype=self.dtype, device=self.device)
+        # tensor-core decode kernel: V slabs are stored transposed
+        self.kv_vt = self.cuda and F.tc_decode_supported(self.d, self.P, self.hq, self.hkv)
         self.free_pages: List[int] = list(range(num_pages - 1, 0, -1))
         self.page_refs: Dict[int, int] = {}
         self.max_prefill_tokens = max_prefill_tokens
@@ -156,7 +158,7 @@ class RolloutEngine:
             else:
                 x, res = F.rms_norm(h, layer.input_layernorm, eps, residual=res)
             q, k, v = layer.self_attn.project_qkv(x, positions)
-            F.kv_append(k, v, self.kv[li], slot_mapping)
+            F.kv_append(k, v, self.kv[li], slot_mapping, self.kv_vt)
             o = attn(li, q, k, v)
             h = torch.nn.functional.linear(o.reshape(o.shape[0], -1), layer.self_attn.o_proj.weight)
             if self.tp is not None:
@@ -202,7 +204,7 @@ class RolloutEngine:
         h = self.model.embed(self.last_tok[:B])
         bt = self.block_table[:B]
         out = self._layers(h, cur.long(), slot,
-                           lambda li, q, k, v: F.paged_decode(q, self.kv[li], bt, seq_lens))
+                           lambda li, q, k, v: F.paged_decode(q, self.kv[li], bt, seq_lens, v_transposed=self.kv_vt))
         logits = self.model.logits(out)
         r = (self.step_counter % self.ring).long()
         if self.cuda:

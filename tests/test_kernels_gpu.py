@@ -219,3 +219,32 @@ def test_quant_fp8(R_, C):
     qa, sa = F.quant_fp8_block(w, 1)
     deqa = R.dequant_fp8_block(qa.cpu(), sa.cpu(), 1, 128)
     assert (deqa - w.cpu().float()).abs().max() <= 0.07 * w.abs().max().item()
+
+
+@pytest.mark.parametrize("hq,hkv", [(28, 4), (8, 8), (64, 8), (4, 4)])
+def test_paged_decode_tensor_core(hq, hkv):
+    """tcgen05 decode kernel (V stored transposed, 128-token pages) against the fp32 statement."""
+    torch.manual_seed(10)
+    d, P, B, n_pages, max_pages = 128, 128, 7, 64, 6
+    cache = torch.zeros(n_pages, 2, hkv, P, d, dtype=torch.bfloat16, device=DEV)
+    seq_lens = torch.tensor([1, 127, 128, 129, 500, 768, 300], dtype=torch.int32, device=DEV)
+    perm = torch.stack([torch.randperm(n_pages - 1, device=DEV)[:max_pages] + 1 for _ in range(B)]).to(torch.int32)
+    ks, vs, slots = [], [], []
+    for b in range(B):
+        L = int(seq_lens[b])
+        ks.append(_bf16(L, hkv, d))
+        vs.append(_bf16(L, hkv, d))
+        t = torch.arange(L, device=DEV)
+        slots.append(perm[b, t // P].long() * P + t % P)
+    k, v, slot = torch.cat(ks), torch.cat(vs), torch.cat(slots).to(torch.int32)
+    F.kv_append(k, v, cache, slot, v_transposed=True)
+    cache_ref = torch.zeros_like(cache).cpu()
+    R.kv_append(k.cpu(), v.cpu(), cache_ref, slot.cpu(), v_transposed=True)
+    assert torch.equal(cache.cpu(), cache_ref)
+    q = _bf16(B, hq, d)
+    ref = R.paged_decode(q.cpu(), cache_ref, perm.cpu(), seq_lens.cpu(), v_transposed=True)
+    for nsplit in (1, 3):
+        out = F.paged_decode(q, cache, perm, seq_lens, nsplit=nsplit, v_transposed=True)
+        native.read_status(q.device)
+        err = (out.float().cpu() - ref.float()).abs().max().item()
+        assert err < 3e-2, (nsplit, err)
