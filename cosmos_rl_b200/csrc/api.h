@@ -57,6 +57,15 @@ int b200_adamw(float* master, float* m, float* v, const void* grad, int grad_fp3
 int b200_sumsq(const void* x, int is_fp32, long long n, float* out_accum, cudaStream_t stream);
 int b200_clip_coef(const float* sumsq, float max_norm, float* coef_out, float* norm_out, cudaStream_t stream);
 
+// Data-parallel step over peer memory (n_ranks <= 8): gradient reduce-scatter + sum of squares, and AdamW whose
+// bf16 store goes to every rank's parameter buffer. Pointers are device addresses valid in this process
+// (own buffer or IPC-mapped peers); lo and n are multiples of 8 elements.
+int b200_reduce_scatter_sumsq(void* const* grads, int n_ranks, long long lo, long long n, float* out_shard,
+                              float* sumsq_accum, float scale, cudaStream_t stream);
+int b200_adamw_publish(float* master, float* m, float* v, const float* grad_shard, void* const* params, int n_ranks,
+                       long long lo, long long n, float lr, float beta1, float beta2, float eps, float weight_decay,
+                       float bias1, float bias2, const float* grad_scale_dev, cudaStream_t stream);
+
 // ---- sampling --------------------------------------------------------------------------------------------
 // logits [B, V] (fp32 or bf16), per-row temperature/top_p/top_k; writes token [B] (int64) and its log-prob
 // under softmax(logits / temperature). offset_dev (nullable) is a device counter added to `offset`.

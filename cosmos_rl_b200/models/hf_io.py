@@ -75,12 +75,35 @@ def _tp_slice(name: str, t: torch.Tensor, tp: int, r: int, cfg) -> torch.Tensor:
     return t
 
 
+def load_hf_state(model, read, available, cfg: Dict[str, Any], tp: int = 1, r: int = 0) -> None:
+    """Fill ``model`` (fused layout, TP rank ``r`` of ``tp``) from HF-named tensors served by ``read(name)``."""
+    from .base import ModelRegistry
+    mapper = ModelRegistry.mapper(cfg.get("model_type"))(cfg)
+    missing = []
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if hasattr(mapper, "load_param") and mapper.load_param(name, p, read, available, tp, r):
+                continue
+            hf_names = mapper.hf_names(name)
+            if not all(h in available for h in hf_names):
+                if name.startswith("lm_head") and "model.embed_tokens.weight" in available:
+                    hf_names = ["model.embed_tokens.weight"]
+                else:
+                    missing.append(name)
+                    continue
+            parts = [_tp_slice(h, read(h), tp, r, cfg) for h in hf_names]
+            t = parts[0] if len(parts) == 1 else torch.cat(parts, dim=0)
+            if tuple(t.shape) != tuple(p.shape):
+                raise ValueError(f"{name}: checkpoint shape {tuple(t.shape)} != model shape {tuple(p.shape)}")
+            p.copy_(t.to(p.dtype))
+    if missing:
+        raise KeyError(f"parameters missing from checkpoint: {missing[:5]}{'...' if len(missing) > 5 else ''}")
+
+
 def load_hf_weights(model, path: str, parallel_dims=None) -> None:
     """Fill ``model`` (already on its device, fused layout) from an HF safetensors folder."""
     from safetensors import safe_open
-    from .base import ModelRegistry
     cfg = load_hf_config(path)
-    mapper = ModelRegistry.mapper(cfg.get("model_type"))(cfg)
     tp = parallel_dims.tp if parallel_dims is not None else 1
     r = parallel_dims.tp_coord if parallel_dims is not None else 0
     index = _index(path)
@@ -92,26 +115,21 @@ def load_hf_weights(model, path: str, parallel_dims=None) -> None:
             handles[fn] = safe_open(os.path.join(path, fn), framework="pt")
         return handles[fn].get_tensor(hf_name)
 
-    missing = []
-    with torch.no_grad():
-        for name, p in model.named_parameters():
-            hf_names = mapper.hf_names(name)
-            if hasattr(mapper, "load_param"):
-                if mapper.load_param(name, p, read, tp, r):
-                    continue
-            if not all(h in index for h in hf_names):
-                if name.startswith("lm_head") and "model.embed_tokens.weight" in index:
-                    hf_names = ["model.embed_tokens.weight"]
-                else:
-                    missing.append(name)
-                    continue
-            parts = [_tp_slice(h, read(h), tp, r, cfg) for h in hf_names]
-            t = parts[0] if len(parts) == 1 else torch.cat(parts, dim=0)
-            if tuple(t.shape) != tuple(p.shape):
-                raise ValueError(f"{name}: checkpoint shape {tuple(t.shape)} != model shape {tuple(p.shape)}")
-            p.copy_(t.to(p.dtype))
-    if missing:
-        raise KeyError(f"parameters missing from checkpoint {path}: {missing[:5]}{'...' if len(missing) > 5 else ''}")
+    load_hf_state(model, read, index, cfg, tp, r)
+
+
+def hf_state_dict(model, hf_config: Dict[str, Any]) -> Dict[str, torch.Tensor]:
+    """HF-named tensors of an unsharded (tp = 1) model: fused parameters are split back."""
+    from .base import ModelRegistry
+    mapper = ModelRegistry.mapper(hf_config.get("model_type"))(hf_config)
+    a = model.args
+    out: Dict[str, torch.Tensor] = {}
+    if hasattr(model, "export_items"):
+        return {k: v.detach() for k, v in model.export_items()}
+    for name, p in model.named_parameters():
+        for hf_name, piece in _split_fused(name, p.detach(), mapper, hf_config, a.n_heads, a.n_kv_heads, a.head_dim):
+            out[hf_name] = piece
+    return out
 
 
 def _split_fused(name: str, t: torch.Tensor, mapper, cfg, hq: int, hkv: int, d: int) -> List[Tuple[str, torch.Tensor]]:

@@ -82,31 +82,42 @@ class FlatAdamW:
             g.mul_(self.trainable.to(g.dtype))
         if self.world == 1:
             return g[self.lo:self.hi]
-        if self.collective is not None:
-            self.collective.reduce_scatter_avg(g, self.grad_shard)
-        else:
-            # library path (the baseline): fp32 reduce as in FSDP2's reduce_dtype=float32
-            full = g.to(torch.float32)
-            dist.reduce_scatter_tensor(self.grad_shard, full, op=dist.ReduceOp.AVG, group=self.group)
+        # library path (the baseline): fp32 reduce as in FSDP2's reduce_dtype=float32, in chunks so the fp32
+        # staging copy stays small
+        per = self.hi - self.lo
+        chunk = min(per, 1 << 26)
+        for c0 in range(0, per, chunk):
+            c1 = min(per, c0 + chunk)
+            stage = torch.stack([g[r * per + c0: r * per + c1].to(torch.float32) for r in range(self.world)])
+            dist.reduce_scatter_tensor(self.grad_shard[c0:c1], stage.view(-1), op=dist.ReduceOp.AVG, group=self.group)
         return self.grad_shard
 
     def step(self, lr_scale: float = 1.0, extra_norm_groups=()) -> torch.Tensor:
         """Reduce, clip, update, republish weights. Returns the global gradient norm (1-element tensor)."""
         self.step_count += 1
-        g = self._reduce_grads()
-        sumsq = K.grad_sumsq([g])
+        fused = self.world > 1 and self.collective is not None
+        if fused:
+            if self.trainable is not None:
+                self.flat.grad.mul_(self.trainable.to(self.flat.grad.dtype))
+            sumsq = torch.zeros(1, dtype=torch.float32, device=self.flat.device)
+            self.collective.reduce_scatter_sumsq(self.lo, self.hi, self.grad_shard, sumsq)
+            g = self.grad_shard
+        else:
+            g = self._reduce_grads()
+            sumsq = K.grad_sumsq([g])
         if self.world > 1:
             dist.all_reduce(sumsq, group=self.group)
         for grp in extra_norm_groups:  # e.g. tensor-/pipeline-parallel groups that hold disjoint parameters
             dist.all_reduce(sumsq, group=grp)
         norm, coef = K.clip_coef_from_sumsq(sumsq, self.max_grad_norm)
-        shadow = self.flat.data[self.lo:self.hi]
-        K.adamw_flat(self.master, self.m, self.v, g, shadow, lr=self.lr * lr_scale, beta1=self.betas[0],
-                     beta2=self.betas[1], eps=self.eps, weight_decay=self.wd, step=self.step_count, grad_scale=coef)
-        if self.world > 1:
-            if self.collective is not None:
-                self.collective.all_gather_params(self.flat.data, self.lo, self.hi)
-            else:
+        hp = dict(lr=self.lr * lr_scale, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps,
+                  weight_decay=self.wd, step=self.step_count, grad_scale=coef)
+        if fused:
+            self.collective.adamw_publish(self.master, self.m, self.v, g, self.lo, self.hi, **hp)
+        else:
+            shadow = self.flat.data[self.lo:self.hi]
+            K.adamw_flat(self.master, self.m, self.v, g, shadow, **hp)
+            if self.world > 1:
                 dist.all_gather_into_tensor(self.flat.data, shadow.clone(), group=self.group)
         self.last_grad_norm = norm
         return norm
