@@ -155,8 +155,9 @@ def main():
     if rank == 0:
         print(json.dumps(result))
     if world > 1:
+        from cosmos_rl_b200.utils.dist_util import safe_destroy
         dist.barrier()
-        dist.destroy_process_group()
+        safe_destroy(20.0)
     return 0
 
 

@@ -246,6 +246,8 @@ def run_disaggregated(bench) -> Dict[str, Any]:
                       "h2d_bytes_per_step": n_prompts_global * a.prompt_len * 8 + tokens_per_step * 8 * 3,
                       "d2h_bytes_per_step": n_prompts_global * a.group * a.max_response * 12 + 64 * P,
                       "api": "GRPOTrainer.step_training + RolloutEngine.generate + PeerWeightSync.pull"}
+    if engine is not None:
+        engine.invalidate_graphs()   # CUDA graphs hold the TP communicator
     for m in maps:
         m.close()
     if coll is not None:

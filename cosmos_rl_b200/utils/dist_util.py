@@ -1,0 +1,51 @@
+"""Process-group helpers: initialisation for CPU (gloo) or GPU (nccl + gloo) worlds and a shutdown that
+cannot hang (cosmos_rl/utils/distributed.py:57-84 initialises ``cuda:nccl,cpu:gloo``; the reference's
+shutdown aborts every communicator before destroying the group, cosmos_rl/utils/pynccl.py:609-676)."""
+from __future__ import annotations
+
+import gc
+import os
+import sys
+import threading
+from datetime import timedelta
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .logging import logger
+
+
+def init_distributed(backend: Optional[str] = None, timeout_s: float = 600.0) -> None:
+    if dist.is_initialized():
+        return
+    if "RANK" not in os.environ:
+        return
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    cuda = torch.cuda.is_available()
+    backend = backend or ("cuda:nccl,cpu:gloo" if cuda else "gloo")
+    kw = {}
+    if cuda:
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        kw["device_id"] = torch.device("cuda", local)
+    dist.init_process_group(backend, timeout=timedelta(seconds=timeout_s), **kw)
+
+
+def safe_destroy(timeout_s: float = 20.0, exit_code: int = 0) -> None:
+    """Destroy the default process group, but never wait longer than ``timeout_s``: communicators that were
+    captured into CUDA graphs (or that lost a peer) can block in their destructor; in that case the process
+    ends with ``os._exit`` once everything it had to print is flushed."""
+    if not dist.is_initialized():
+        return
+    gc.collect()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    t = threading.Thread(target=dist.destroy_process_group, daemon=True)
+    t.start()
+    t.join(timeout_s)
+    if t.is_alive():
+        logger.warning("process-group teardown did not finish in %.0f s; exiting without it", timeout_s)
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(exit_code)

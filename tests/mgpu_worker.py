@@ -28,6 +28,9 @@ def args(tp=1, r=0):
 
 
 def main():
+    import faulthandler
+    # a rank that is still running after this long dumps its stacks and exits: a test must never sit on a GPU
+    faulthandler.dump_traceback_later(float(os.environ.get("MGPU_TEST_LIMIT_S", "150")), exit=True)
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     torch.cuda.set_device(dev)
@@ -112,13 +115,24 @@ def main():
     out_tp = eng.generate(prompts, sp)
     native.read_status(dev)
     if rank == 0:
-        eng1 = RolloutEngine(m, max_num_seqs=8, max_model_len=512, page_size=128)
-        out_1 = eng1.generate(prompts, sp)
-        agree = sum(a.token_ids == b.token_ids for ra, rb in zip(out_tp, out_1) for a, b in zip(ra, rb))
-        total = sum(len(r) for r in out_1)
-        # bf16 reductions in a different order may flip a near-tie; most sequences must agree exactly
-        assert agree >= total - 1, f"TP generation differs from single-GPU generation ({agree}/{total})"
-        print(f"tp{world} engine vs tp1 engine: {agree}/{total} sequences identical", flush=True)
+        # Teacher-forced check against the unsharded model: random-init weights give nearly uniform next-token
+        # distributions, so the greedy argmax itself is not stable under a different bf16 summation order, but
+        # the log-prob the TP engine reports for each token it chose must match the full model's, and the
+        # chosen token must be (within noise) the full model's argmax.
+        n_tok = 0
+        for p_ids, comps in zip(prompts, out_tp):
+            for c in comps:
+                ids = torch.tensor(p_ids + c.token_ids, device=dev)
+                cu = torch.tensor([0, ids.numel()], dtype=torch.int32, device=dev)
+                with torch.no_grad():
+                    h = m(ids, torch.arange(ids.numel(), device=dev), cu, int(ids.numel()))
+                    lsm = torch.log_softmax(m.logits(h).float(), -1)
+                for i, (tok, lp) in enumerate(zip(c.token_ids, c.logprobs)):
+                    row = lsm[len(p_ids) - 1 + i]
+                    assert abs(row[tok].item() - lp) < 0.08, (i, row[tok].item(), lp)
+                    assert row[tok].item() > row.max().item() - 0.15, (i, row[tok].item(), row.max().item())
+                    n_tok += 1
+        print(f"tp{world} engine: {n_tok} generated tokens match the unsharded model's log-probs", flush=True)
     toks = torch.tensor([c.token_ids for r in out_tp for c in r], device=dev)
     peers = [torch.empty_like(toks) for _ in range(world)]
     dist.all_gather(peers, toks, group=grp)
@@ -127,10 +141,12 @@ def main():
     if mp is not None:
         mp.close()
     coll.close()
+    eng.invalidate_graphs()   # graphs hold the TP communicator: release them before tearing it down
     dist.barrier(group=gloo)
-    dist.destroy_process_group()
     if rank == 0:
         print("ALL OK", flush=True)
+    from cosmos_rl_b200.utils.dist_util import safe_destroy
+    safe_destroy(10.0)
 
 
 if __name__ == "__main__":
