@@ -140,6 +140,11 @@ class APIClient:
         r = self.post(suffix, {"rank": rank})
         return msgpack.unpackb(base64.b64decode(r["insts_b64"]), raw=False, strict_map_key=False)
 
+    def get_shard_infos(self, role: str):
+        r = self.get(S.COSMOS_API_SHARD_INFOS_SUFFIX, {"role": role})
+        raw = r.get("infos_b64")
+        return msgpack.unpackb(base64.b64decode(raw), raw=False, strict_map_key=False) if raw else None
+
     def post_resume_info(self, extra_info: Dict[str, Any]):
         return self.post(S.COSMOS_API_RESUME_INFO_SUFFIX, {"ckpt_extra_info": extra_info})
 
@@ -221,6 +226,9 @@ class LocalAPIClient:
     def get_shard_insts(self, role, rank):
         from ...parallel.reshard import plan_for_rank
         return plan_for_rank(self.c.get_shard_infos("policy"), self.c.get_shard_infos("rollout"), role, rank)
+
+    def get_shard_infos(self, role):
+        return self.c.get_shard_infos(role)
 
     def post_resume_info(self, extra_info):
         self.c.set_resume_info(extra_info)

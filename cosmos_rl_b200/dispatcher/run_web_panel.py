@@ -166,6 +166,13 @@ def create_app(controller: Controller) -> FastAPI:
                                        "rollout", req.rank)
         return JSONResponse({"insts_b64": base64.b64encode(msgpack.packb(plan)).decode()})
 
+    @app.get(S.COSMOS_API_SHARD_INFOS_SUFFIX)
+    async def shard_infos(role: str):
+        infos = c.get_shard_infos(role)
+        if infos is None:
+            return {"infos_b64": None}
+        return {"infos_b64": base64.b64encode(msgpack.packb(infos, use_bin_type=True)).decode()}
+
     @app.get(S.COSMOS_API_GET_TRAINABLE_PARAMS_SUFFIX)
     async def trainable_params():
         infos = c.get_shard_infos("policy") or {}

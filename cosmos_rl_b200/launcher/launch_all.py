@@ -1,0 +1,251 @@
+"""``cosmos-rl`` launcher: read the job file, size and place the replicas, reserve the controller port, start
+the controller and one ``torchrun`` group per replica, forward pre-emption signals to the policy processes
+and supervise everything (cosmos_rl/launcher/launch_all.py:104-1017, launcher/utility.py:454-850).
+
+    cosmos-rl --config job.toml [--policy N] [--rollout M] [--port P] [--log-dir DIR] [user_script.py ...]
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import signal
+import socket
+import subprocess
+import sys
+import tempfile
+import time
+from typing import Dict, List, Optional, Tuple
+
+from ..config import Config, dump_toml, load_toml
+from ..utils.logging import logger
+
+
+def parse_args(argv=None):
+    ap = argparse.ArgumentParser(prog="cosmos-rl", description="launch a cosmos-rl job on this node")
+    ap.add_argument("--config", required=True)
+    ap.add_argument("--url", default=None, help="address of an already running controller (host:port)")
+    ap.add_argument("--port", type=int, default=None)
+    ap.add_argument("--policy", type=int, default=None, help="number of policy replicas")
+    ap.add_argument("--rollout", type=int, default=None, help="number of rollout replicas")
+    ap.add_argument("--reference", type=int, default=None, help="number of reference (teacher) replicas")
+    ap.add_argument("--p2r-ratio", type=str, default=None, help="policy:rollout replica ratio, e.g. 1:2; the node's "
+                                                                "GPUs are divided accordingly")
+    ap.add_argument("--log-dir", default=None)
+    ap.add_argument("--num-workers", type=int, default=1, help="number of nodes of the job")
+    ap.add_argument("--worker-idx", type=int, default=0, help="index of this node")
+    ap.add_argument("--node-ip-list", default=None, help="semicolon separated node addresses (multi-node)")
+    ap.add_argument("--rdzv-port", type=int, default=29345)
+    ap.add_argument("--cpu", action="store_true", help="run every replica on CPU (gloo); for plumbing tests")
+    ap.add_argument("--no-controller", action="store_true")
+    ap.add_argument("script", nargs="?", default=None)
+    ap.add_argument("script_args", nargs=argparse.REMAINDER)
+    return ap.parse_args(argv)
+
+
+def gpus_per_replica(par) -> int:
+    """tp * dp_replicate * pp * cp * dp_shard (dp_shard -1/0 counts as 1 until the world size is known)."""
+    return par.tp_size * max(par.dp_replicate_size, 1) * par.pp_size * par.cp_size * max(par.dp_shard_size, 1)
+
+
+def replica_counts(config: Config, args, n_gpus: int) -> Tuple[int, int, int]:
+    is_sft = config.train.train_policy.type == "sft"
+    n_policy = args.policy if args.policy is not None else config.policy.parallelism.n_init_replicas
+    n_rollout = 0 if is_sft else (args.rollout if args.rollout is not None else
+                                  config.rollout.parallelism.n_init_replicas)
+    n_ref = args.reference if args.reference is not None else (
+        config.distillation.parallelism.n_init_replicas if config.distillation.enable else 0)
+    if args.p2r_ratio and not is_sft and n_gpus > 0:
+        p, r = (int(x) for x in args.p2r_ratio.split(":"))
+        gp, gr = gpus_per_replica(config.policy.parallelism), gpus_per_replica(config.rollout.parallelism)
+        unit = p * gp + r * gr
+        k = max(1, n_gpus // unit)
+        n_policy, n_rollout = p * k, r * k
+    if config.mode == "colocated":
+        if n_policy != n_rollout and n_rollout != 0:
+            raise ValueError("colocated mode needs as many rollout replicas as policy replicas")
+    return n_policy, n_rollout, n_ref
+
+
+def place_replicas(n_policy: int, n_rollout: int, n_ref: int, config: Config, n_gpus: int, colocated: bool
+                   ) -> List[Dict]:
+    """Assign GPU ids of this node to replicas, policies first. Colocated replicas share the policy's GPUs."""
+    out, next_gpu = [], 0
+    sizes = {"policy": gpus_per_replica(config.policy.parallelism),
+             "rollout": gpus_per_replica(config.rollout.parallelism),
+             "reference": gpus_per_replica(config.distillation.parallelism)}
+    policy_gpus: List[List[int]] = []
+    for role, n in (("policy", n_policy), ("rollout", n_rollout), ("reference", n_ref)):
+        for i in range(n):
+            k = sizes[role]
+            if colocated and role == "rollout" and i < len(policy_gpus):
+                gpus = policy_gpus[i][:k]
+            else:
+                gpus = list(range(next_gpu, next_gpu + k))
+                next_gpu += k
+                if n_gpus and next_gpu > n_gpus:
+                    raise ValueError(f"job needs more than the {n_gpus} GPUs of this node "
+                                     f"({role} replica {i} wants GPUs {gpus})")
+            if role == "policy":
+                policy_gpus.append(gpus)
+            out.append({"role": role, "index": i, "gpus": gpus, "nproc": k})
+    return out
+
+
+def reserve_port(port: Optional[int]) -> Tuple[socket.socket, int]:
+    """Bind the controller's listening socket here and hand the descriptor to the controller process, so the
+    port cannot be taken by someone else between choosing it and serving on it."""
+    s = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+    s.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+    s.bind(("0.0.0.0", port or 0))
+    s.listen(128)
+    s.set_inheritable(True)
+    return s, s.getsockname()[1]
+
+
+def wait_for_url(url: str, timeout_s: float = 120.0) -> None:
+    import requests
+    t0 = time.time()
+    while time.time() - t0 < timeout_s:
+        try:
+            if requests.get(url + "/api/meta", timeout=2).status_code == 200:
+                return
+        except Exception:
+            pass
+        time.sleep(0.2)
+    raise TimeoutError(f"controller at {url} did not come up within {timeout_s:.0f} s")
+
+
+def is_coordinated_controller_exit(returncode: Optional[int]) -> bool:
+    """The controller terminates itself with SIGTERM after every replica has checked out: that is success."""
+    return returncode in (0, -signal.SIGTERM, 128 + signal.SIGTERM)
+
+
+def main(argv=None) -> int:
+    args = parse_args(argv)
+    raw = load_toml(args.config)
+    config = Config.from_dict(raw)
+    try:
+        import torch
+        n_gpus = 0 if args.cpu else torch.cuda.device_count()
+    except Exception:
+        n_gpus = 0
+    n_policy, n_rollout, n_ref = replica_counts(config, args, n_gpus)
+    placement = place_replicas(n_policy, n_rollout, n_ref, config, n_gpus, config.mode == "colocated")
+    log_dir = None
+    if args.log_dir:
+        log_dir = os.path.join(args.log_dir, time.strftime("logs_%Y%m%d-%H%M%S"))
+        os.makedirs(log_dir, exist_ok=True)
+        latest = os.path.join(args.log_dir, "logs_latest")
+        tmp = latest + f".tmp{os.getpid()}"
+        os.symlink(os.path.basename(log_dir), tmp)
+        os.replace(tmp, latest)
+
+    # the job file the controller serves carries the replica counts actually launched
+    raw.setdefault("policy", {}).setdefault("parallelism", {})["n_init_replicas"] = max(n_policy, 1)
+    raw.setdefault("rollout", {}).setdefault("parallelism", {})["n_init_replicas"] = max(n_rollout, 1)
+    tmp_cfg = tempfile.NamedTemporaryFile("w", suffix=".toml", delete=False)
+    tmp_cfg.write(dump_toml(raw))
+    tmp_cfg.close()
+
+    procs: List[Tuple[str, subprocess.Popen]] = []
+    env_base = dict(os.environ)
+    env_base.setdefault("NCCL_CUMEM_ENABLE", "0")
+    script = [args.script] + list(args.script_args) if args.script else None
+
+    def spawn(name: str, cmd: List[str], env: Dict[str, str], pass_fds=()):
+        out = open(os.path.join(log_dir, f"{name}.log"), "w") if log_dir else None
+        p = subprocess.Popen(cmd, env=env, stdout=out or None, stderr=subprocess.STDOUT if out else None,
+                             pass_fds=pass_fds)
+        procs.append((name, p))
+        return p
+
+    controller = None
+    if args.url:
+        host = args.url
+    else:
+        sock, port = reserve_port(args.port)
+        host = f"127.0.0.1:{port}"
+        if not args.no_controller and args.worker_idx == 0:
+            env = dict(env_base, COSMOS_ROLE="Controller", COSMOS_CONTROLLER_LISTEN_FD=str(sock.fileno()),
+                       COSMOS_CONTROLLER_SELF_TERMINATE="1")
+            cmd = [sys.executable] + (script if script else ["-m", "cosmos_rl_b200.dispatcher.run_web_panel"]) + \
+                  ["--config", tmp_cfg.name, "--port", str(port)]
+            controller = spawn("controller", cmd, env, pass_fds=(sock.fileno(),))
+            wait_for_url(f"http://{host}")
+        sock.close()
+    ips = args.node_ip_list.split(";") if args.node_ip_list else []
+    ctrl_hosts = host if not ips else ";".join(f"{ip}:{host.split(':')[1]}" for ip in ips[:1])
+
+    rdzv = args.rdzv_port
+    for rep in placement:
+        env = dict(env_base, COSMOS_ROLE=rep["role"].capitalize(), COSMOS_CONTROLLER_HOST=ctrl_hosts)
+        if rep["gpus"] and n_gpus:
+            env["CUDA_VISIBLE_DEVICES"] = ",".join(str(g) for g in rep["gpus"])
+        elif args.cpu or not n_gpus:
+            env["CUDA_VISIBLE_DEVICES"] = ""
+        if config.mode != "colocated_separated":
+            env.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+        module = {"policy": "cosmos_rl_b200.policy.train", "rollout": "cosmos_rl_b200.rollout.rollout_entry",
+                  "reference": "cosmos_rl_b200.reference.reference_entry"}[rep["role"]]
+        target = script if script else ["-m", module]
+        rdzv += 1
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={max(1, rep['nproc'])}",
+               "--master-addr", "127.0.0.1", "--master-port", str(rdzv)] + \
+              (target if script else ["--module", module])
+        spawn(f"{rep['role']}_{rep['index']}", cmd, env)
+
+    policy_procs = [p for n, p in procs if n.startswith("policy")]
+
+    def forward(signum, _frame):
+        for p in policy_procs:
+            try:
+                p.send_signal(signum)
+            except Exception:
+                pass
+
+    for name in config.train.signal_to_handle:
+        sig = getattr(signal, name, None)
+        if sig is not None:
+            signal.signal(sig, forward)
+
+    # supervise: a failing replica or controller takes the job down; the controller's own SIGTERM is success
+    rc = 0
+    try:
+        while True:
+            alive = False
+            for name, p in procs:
+                code = p.poll()
+                if code is None:
+                    alive = True
+                    continue
+                if name == "controller":
+                    if not is_coordinated_controller_exit(code):
+                        logger.error("controller exited with %s", code)
+                        rc = code or 1
+                        raise KeyboardInterrupt
+                elif code != 0:
+                    logger.error("%s exited with %s", name, code)
+                    rc = code
+                    raise KeyboardInterrupt
+            workers_alive = any(p.poll() is None for n, p in procs if n != "controller")
+            if not workers_alive:
+                break
+            time.sleep(0.5)
+    except KeyboardInterrupt:
+        pass
+    finally:
+        deadline = time.time() + 10
+        for name, p in procs:
+            if p.poll() is None and (name != "controller" or rc != 0 or time.time() > deadline):
+                p.terminate()
+        for name, p in procs:
+            try:
+                p.wait(timeout=15)
+            except subprocess.TimeoutExpired:
+                p.kill()
+        os.unlink(tmp_cfg.name)
+    return rc
+
+
+if __name__ == "__main__":
+    sys.exit(main())

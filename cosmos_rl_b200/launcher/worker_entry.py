@@ -1,0 +1,131 @@
+"""User-facing entry point of every process of a job
+(cosmos_rl/launcher/worker_entry.py:10-105).
+
+A user script calls ``main(dataset=..., reward_fns=[...], data_packer=...)``; the launcher starts that same
+script once per role with ``COSMOS_ROLE`` set to ``Controller``, ``Policy``, ``Rollout`` or ``Reference``
+and this function dispatches accordingly.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+from typing import Any, Callable, Dict, List, Optional
+
+from ..utils.logging import logger
+
+
+def _worker_setup(role: str):
+    import torch
+    from ..config import Config
+    from ..dispatcher.api.client import APIClient
+    from ..parallel.dims import ParallelDims
+    from ..utils.dist_util import init_distributed
+    api = APIClient(role)
+    meta = api.get_controller_metadata()
+    config = Config.from_dict(meta["config"])
+    init_distributed()
+    import torch.distributed as dist
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    if torch.cuda.is_available():
+        device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")) % torch.cuda.device_count())
+    else:
+        device = torch.device("cpu")
+    par = {"POLICY": config.policy.parallelism, "ROLLOUT": config.rollout.parallelism,
+           "REFERENCE": config.distillation.parallelism}[role.upper()]
+    dims = ParallelDims.from_config_parallelism(par, world, rank, device)
+    dims.build_groups()
+    return config, dims, device, api
+
+
+def _tokenizer(config):
+    path = config.policy.model_name_or_path
+    if os.path.isdir(path):
+        try:
+            from transformers import AutoTokenizer
+            return AutoTokenizer.from_pretrained(path)
+        except Exception as e:
+            logger.warning("no tokenizer loaded from %s: %s", path, e)
+    return None
+
+
+def policy_entry(dataset=None, val_dataset=None, data_packer=None, val_data_packer=None, hook_fns=None, **kw):
+    config, dims, device, api = _worker_setup("POLICY")
+    from ..policy.trainer import dpo_trainer, grpo_trainer, sft_trainer  # noqa: F401 (registry)
+    tp = config.train.train_policy
+    if tp.type == "sft":
+        from ..policy.worker.sft_worker import SFTPolicyWorker
+        worker = SFTPolicyWorker(config, dims, dataset=dataset, val_dataset=val_dataset, data_packer=data_packer,
+                                 val_data_packer=val_data_packer, hook_fns=hook_fns, api=api, device=device,
+                                 tokenizer=_tokenizer(config))
+    else:
+        from ..policy.worker.rl_worker import RLPolicyWorker
+        worker = RLPolicyWorker(config, dims, dataset=dataset, val_dataset=val_dataset, data_packer=data_packer,
+                                val_data_packer=val_data_packer, hook_fns=hook_fns, api=api, device=device,
+                                tokenizer=_tokenizer(config))
+    try:
+        worker.execute()
+    finally:
+        worker.handle_shutdown()
+        from ..parallel.dyncomm import abort_all
+        from ..utils.dist_util import safe_destroy
+        abort_all()
+        safe_destroy()
+
+
+def rollout_entry(dataset=None, val_dataset=None, data_packer=None, val_data_packer=None, reward_fns=None,
+                  filter_reward_fns=None, val_reward_fns=None, **kw):
+    config, dims, device, api = _worker_setup("ROLLOUT")
+    from ..rollout.worker import DisaggregatedRolloutControlWorker
+    worker = DisaggregatedRolloutControlWorker(
+        config, dims, dataset=dataset, val_dataset=val_dataset, data_packer=data_packer,
+        val_data_packer=val_data_packer, reward_fns=reward_fns, filter_reward_fns=filter_reward_fns,
+        val_reward_fns=val_reward_fns, api=api, device=device, tokenizer=_tokenizer(config))
+    try:
+        worker.work()
+    finally:
+        worker.handle_shutdown()
+        from ..parallel.dyncomm import abort_all
+        from ..utils.dist_util import safe_destroy
+        abort_all()
+        safe_destroy()
+
+
+def reference_entry(**kw):
+    config, dims, device, api = _worker_setup("REFERENCE")
+    from ..reference.teacher_worker import TeacherWorker
+    worker = TeacherWorker(config, dims, api=api, device=device)
+    try:
+        worker.execute()
+    finally:
+        worker.handle_shutdown()
+
+
+def controller_entry(dataset=None, val_dataset=None, custom_logger_fns=None, sampler=None, args=None, **kw):
+    from ..dispatcher.run_web_panel import main as controller_main
+    controller_main(args, dataset=dataset, val_dataset=val_dataset, custom_logger_fns=custom_logger_fns,
+                    sampler=sampler)
+
+
+def main(dataset=None, val_dataset=None, data_packer=None, val_data_packer=None, reward_fns=None,
+         filter_reward_fns=None, val_reward_fns=None, custom_logger_fns=None, hook_fns=None, sampler=None,
+         batch_sampler=None, args=None, **kw):
+    role = os.environ.get("COSMOS_ROLE", "Controller").lower()
+    if role == "controller":
+        return controller_entry(dataset=dataset, val_dataset=val_dataset, custom_logger_fns=custom_logger_fns,
+                                sampler=sampler, args=args)
+    if role == "policy":
+        return policy_entry(dataset=dataset, val_dataset=val_dataset, data_packer=data_packer,
+                            val_data_packer=val_data_packer, hook_fns=hook_fns)
+    if role == "rollout":
+        return rollout_entry(dataset=dataset, val_dataset=val_dataset, data_packer=data_packer,
+                             val_data_packer=val_data_packer, reward_fns=reward_fns,
+                             filter_reward_fns=filter_reward_fns, val_reward_fns=val_reward_fns)
+    if role == "reference":
+        return reference_entry()
+    raise ValueError(f"unknown COSMOS_ROLE {role!r}")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,90 @@
+"""Supervised fine-tuning trainer: token cross-entropy on packed sequences through the fused lm_head kernel,
+token-balanced across data-parallel ranks (cosmos_rl/policy/trainer/llm_trainer/sft_trainer.py:49-553)."""
+from __future__ import annotations
+
+import time
+from typing import Any, Dict, List, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ...utils.sequence_packing import pack_sequences, token_budget_batches
+from ..loss import sft_ce_loss
+from .base import TrainerRegistry
+from .llm_trainer import LLMTrainer
+
+
+@TrainerRegistry.register("sft")
+class SFTTrainer(LLMTrainer):
+    def _pack(self, samples: List[Dict[str, Any]]) -> Dict[str, Any]:
+        seqs = [s["input_ids"] for s in samples]
+        # mask[i] = 1 where token i+1 is a label to learn
+        masks = [[1 if (i + 1 < len(s["label_ids"]) and s["label_ids"][i + 1] != -100) else 0
+                  for i in range(len(s["input_ids"]))] for s in samples]
+        b = pack_sequences(seqs, masks, device=self.device,
+                           pad_multiple=max(1, self.parallel_dims.cp * self.parallel_dims.tp))
+        sel = (b["label_ids"] >= 0).nonzero(as_tuple=True)[0]
+        b["sel"], b["labels_sel"] = sel, b["label_ids"][sel]
+        return b
+
+    def _batches(self, processed: List[Dict[str, Any]]) -> List[List[int]]:
+        tp = self.config.train.train_policy
+        budget = getattr(tp, "load_balanced_max_tokens_for_batch", None)
+        if budget:
+            return token_budget_batches([len(s["input_ids"]) for s in processed], budget)
+        mb = max(1, tp.mini_batch)
+        return [list(range(i, min(i + mb, len(processed)))) for i in range(0, len(processed), mb)]
+
+    def _loss_on(self, b, total_tokens):
+        hidden = self.model(b["input_ids"], b["position_ids"], b["cu_seqlens"], b["max_seqlen"])
+        lp, _ = self.model.logprobs(hidden[b["sel"]], b["labels_sel"], 1.0)
+        return sft_ce_loss(lp, total_tokens)
+
+    def step_training(self, global_batch: Sequence[Any], total_steps: int, train_step: int, save_freq: int = 0,
+                      do_save: bool = False, **kw) -> Dict[str, Any]:
+        t0 = time.perf_counter()
+        self.total_steps = total_steps
+        max_len = self.config.policy.model_max_length
+        processed = [self.data_packer.sft_process_sample(s) for s in global_batch]
+        for p in processed:
+            p["input_ids"], p["label_ids"] = p["input_ids"][:max_len], p["label_ids"][:max_len]
+        packed = [self._pack([processed[i] for i in idxs]) for idxs in self._batches(processed)]
+        tok = torch.tensor(float(sum(int(b["sel"].numel()) for b in packed)), device=self.device)
+        dp = self.parallel_dims.dp_shard
+        if dp > 1 and getattr(self.config.train.train_policy, "balance_dp_token", True):
+            dist.all_reduce(tok, group=self.parallel_dims.group("dp_shard"))
+            tok = tok / dp
+        inter = getattr(self, "inter_replica", None)
+        if inter is not None:
+            tok = inter.balance_token_count(tok)
+        self.model.train()
+        self.optimizer.zero_grad()
+        losses = []
+        for b in packed:
+            loss = self._loss_on(b, tok.clamp_min(1.0))
+            loss.backward()
+            losses.append(loss.detach())
+        if inter is not None:
+            inter.all_reduce_grads(self.flat.grad)
+        norm = self.optimizer.step(self.lr_scale(self.train_step))
+        self.train_step = train_step
+        if do_save:
+            self.save_checkpoint(train_step, total_steps, is_final=train_step >= total_steps)
+        loss_sum = torch.stack(losses).sum()
+        return {"train/loss_avg": float(loss_sum), "train/loss_max": float(loss_sum),
+                "train/learning_rate": self.optimizer.lr * self.lr_scale(max(train_step - 1, 0)),
+                "train/iteration_time": time.perf_counter() - t0, "train/grad_norm": float(norm),
+                "train/n_tokens": float(sum(len(p["input_ids"]) for p in processed))}
+
+    @torch.no_grad()
+    def step_validation(self, batch: Sequence[Any], **kw) -> Dict[str, Any]:
+        self.model.eval()
+        processed = [self.data_packer.sft_process_sample(s) for s in batch]
+        packed = [self._pack([processed[i] for i in idxs]) for idxs in self._batches(processed)]
+        tok = torch.tensor(float(sum(int(b["sel"].numel()) for b in packed)), device=self.device).clamp_min(1.0)
+        loss = sum(float(self._loss_on(b, tok)) for b in packed)
+        return {"val/loss": loss}
+
+    def __init__(self, config, parallel_dims, **kw):
+        self.inter_replica = kw.pop("inter_replica", None)
+        super().__init__(config, parallel_dims, **kw)

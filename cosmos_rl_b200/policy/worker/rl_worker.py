@@ -1,0 +1,304 @@
+"""RL policy worker: the consumer side of the asynchronous loop
+(cosmos_rl/policy/worker/rl_worker.py:80-1067).
+
+Rank 0 runs two fetch threads (commands, rollouts); the main loop takes the next command, shares it with the
+other ranks of the replica and executes its handler: load weights, (re)build the inter-replica mesh, ship the
+full training state to other policy replicas, synchronise weights to a rollout replica, train a step on
+``items_count`` rollouts, or finish.
+"""
+from __future__ import annotations
+
+import queue
+import signal
+import threading
+import time
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ...comm.base import CommMixin
+from ...comm.broker import rollout_stream
+from ...dispatcher import command as cmd
+from ...dispatcher.data import CosmosDataset, WorkerDataFetcher
+from ...dispatcher.data.schema import Rollout
+from ...dispatcher.protocol import Role
+from ...parallel.dims import ParallelDims
+from ...parallel.inter_replica import InterReplicaComm
+from ...parallel.reshard import model_parts, shard_info
+from ...utils.logging import logger
+from ..trainer.base import TrainerRegistry
+
+
+class RLPolicyWorker(CommMixin):
+    role = Role.POLICY
+
+    def __init__(self, config, parallel_dims: ParallelDims, dataset=None, val_dataset=None, data_packer=None,
+                 val_data_packer=None, hook_fns=None, api=None, device=None, **kw):
+        self.config = config
+        self.parallel_dims = parallel_dims
+        self.device = device or parallel_dims.device
+        self.init_comm(api)
+        ds = CosmosDataset(dataset, config) if dataset is not None else None
+        self.data_fetcher = WorkerDataFetcher(config, ds)
+        tp = config.train.train_policy
+        self.inter_replica = InterReplicaComm(self.api, self.replica_name, self.global_rank, self.device)
+        trainer_kw = dict(device=self.device, data_packer=data_packer, val_data_packer=val_data_packer,
+                          hook_fns=hook_fns, inter_replica=self.inter_replica)
+        if self.device.type == "cuda" and config.b200.peer_weight_sync:
+            from ...parallel.peer import peer_allocator
+            trainer_kw["allocator"] = peer_allocator(self.device)
+        trainer_kw.update(kw)
+        self.trainer = TrainerRegistry.get_trainer_cls(tp.trainer_type)(config, parallel_dims, **trainer_kw)
+        if parallel_dims.dp_shard > 1 and self.device.type == "cuda" and config.b200.peer_weight_sync:
+            from ...parallel.fsdp import PeerCollective
+            self.trainer.optimizer.collective = PeerCollective(self.trainer.flat, parallel_dims.group("dp_shard"))
+        self.data_queue: "queue.Queue[Rollout]" = queue.Queue()
+        self._last_rollout_id = 0
+        self.handlers = cmd.PolicyCommandRegistry()
+        for c, h in ((cmd.WeightResumeCommand, self.execute_weight_resume),
+                     (cmd.BuildMeshCommand, self.execute_build_mesh),
+                     (cmd.PolicyToPolicyBroadcastCommand, self.execute_policy_to_policy_broadcast),
+                     (cmd.PolicyToPolicyUnicastCommand, self.execute_policy_to_policy_unicast),
+                     (cmd.PolicyToRolloutUnicastCommand, self.execute_policy_to_rollout_unicast),
+                     (cmd.DataFetchCommand, self.execute_data_fetch),
+                     (cmd.TrainingCompleteCommand, self.execute_training_complete)):
+            self.handlers.register(c, h)
+        self.p2r_comms: Dict[str, Any] = {}
+        self.p2r_send_plan = None
+        self.shard_infos_posted = False
+        self.force_save = threading.Event()
+        self.profiler = None
+        if config.profiler.enable_profiler:
+            from ...utils.profiler import CosmosProfiler
+            self.profiler = CosmosProfiler(config, self.replica_name, self.global_rank, self.api)
+        self._install_signal_handlers()
+
+    # ------------------------------------------------------------------ signals
+    def _install_signal_handlers(self) -> None:
+        if threading.current_thread() is not threading.main_thread():
+            return
+        for name in self.config.train.signal_to_handle:
+            sig = getattr(signal, name, None)
+            if sig is None:
+                continue
+            try:
+                signal.signal(sig, lambda *_: self.force_save.set())
+            except (ValueError, OSError):
+                pass
+
+    # ------------------------------------------------------------------ shard infos for weight sync
+    def post_shard_infos(self) -> None:
+        if self.shard_infos_posted:
+            return
+        info = shard_info(self.global_rank, model_parts(self.trainer.model, self.trainer.flat), self.trainer.flat.total)
+        buf = getattr(self.trainer.flat.data, "_peer_buffer", None)
+        if buf is not None:
+            info["ipc_handle"] = buf.export()
+            info["nbytes"] = buf.nbytes
+            info["host"] = __import__("socket").gethostname()
+        infos = [None] * self.world_size
+        if self.world_size > 1:
+            dist.all_gather_object(infos, info)
+        else:
+            infos = [info]
+        if self.global_rank == 0:
+            trainable = [n for n, p in self.trainer.model.named_parameters() if p.requires_grad]
+            self.api.post_shard_infos("policy", {"ranks": infos, "trainable_params": trainable,
+                                                 "replica": self.replica_name})
+        self.shard_infos_posted = True
+
+    # ------------------------------------------------------------------ handlers
+    def execute_weight_resume(self, c: cmd.WeightResumeCommand) -> bool:
+        resumed = self.trainer.weight_resume()
+        if resumed and self.global_rank == 0:
+            self.api.post_resume_info(getattr(self.trainer, "resume_extra_info", {}))
+        self.post_shard_infos()
+        return False
+
+    def execute_build_mesh(self, c: cmd.BuildMeshCommand) -> bool:
+        self.inter_replica.rebuild(c.replica_name_to_rank, c.uuid_value)
+        return False
+
+    def execute_policy_to_policy_broadcast(self, c: cmd.PolicyToPolicyBroadcastCommand) -> bool:
+        src = self.inter_replica.mapping.get(c.src_replica_name, 0)
+        tensors = self.trainer.state_tensors()
+        self.inter_replica.broadcast_state(tensors, src)
+        if self.replica_name != c.src_replica_name:
+            self.trainer.after_state_received(dict(tensors)["meta"])
+        self.post_shard_infos()
+        return False
+
+    def execute_policy_to_policy_unicast(self, c: cmd.PolicyToPolicyUnicastCommand) -> bool:
+        tensors = self.trainer.state_tensors()
+        if self.replica_name == c.src_replica_name:
+            self.inter_replica.send_state(tensors, self.inter_replica.mapping[c.dst_replica_name])
+        else:
+            self.inter_replica.recv_state(tensors, self.inter_replica.mapping[c.src_replica_name])
+            self.trainer.after_state_received(dict(tensors)["meta"])
+            self.post_shard_infos()
+        return False
+
+    def execute_policy_to_rollout_unicast(self, c: cmd.PolicyToRolloutUnicastCommand) -> bool:
+        """Make this replica's weights available to one rollout replica.
+
+        Peer mode (GPUs of one node): the weights already sit in IPC-exported memory; the policy only has to
+        guarantee they are final (device synchronise), announce it, and wait for the puller's completion mark
+        so that the next optimizer step cannot overwrite them mid-pull. Collective mode: send the rectangles
+        of the plan over a dynamic communicator that spans both replicas (policy ranks first)."""
+        if self.replica_name != c.src_replica_name:
+            return False
+        self.post_shard_infos()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        key = f"p2r:{c.uuid_value}"
+        if self._peer_mode():
+            if self.world_size > 1:
+                dist.barrier()
+            if self.global_rank == 0:
+                self.broker.kv_set(key + ":ready", b"1", ttl_s=3600)
+                deadline = time.time() + 600
+                done = 0
+                while done < c.dst_replica_size and time.time() < deadline:
+                    done = sum(1 for r in range(c.dst_replica_size) if self.broker.kv_get(f"{key}:done:{r}"))
+                    if done < c.dst_replica_size:
+                        time.sleep(0.01)
+                if done < c.dst_replica_size:
+                    logger.warning("[Policy] weight sync %s: only %d/%d rollout ranks confirmed", key, done,
+                                   c.dst_replica_size)
+            if self.world_size > 1:
+                dist.barrier()
+            return False
+        from ...parallel.dyncomm import create_comm
+        from ...rollout.weight_sync import CollectiveWeightSync
+        pair = f"p2r-{c.src_replica_name}-{c.dst_replica_name}"
+        comm = self.p2r_comms.get(pair)
+        if comm is None or comm.aborted:
+            comm = create_comm(self.api, f"{pair}-{c.uuid_value}" if comm is not None else pair, self.global_rank,
+                               c.src_replica_size + c.dst_replica_size, self.device,
+                               is_initiator=self.global_rank == 0)
+            self.p2r_comms[pair] = comm
+        if self.p2r_send_plan is None:
+            self.p2r_send_plan = self.api.get_shard_insts("policy", self.global_rank)
+        flat = self.trainer.flat.data
+        from ...utils.misc import str2dtype
+        tdt = str2dtype(self.config.train.transfer_dtype) if self.device.type == "cuda" else None
+        P = c.src_replica_size
+        for dst_rank, d in self.p2r_send_plan:
+            t = torch.as_strided(flat, (d[5], d[6]), (d[2], 1), flat.storage_offset() + d[1]).contiguous()
+            comm.send(t.to(tdt) if tdt is not None else t, P + dst_rank)
+        return False
+
+    def _peer_mode(self) -> bool:
+        return bool(self.config.b200.peer_weight_sync and self.device.type == "cuda"
+                    and getattr(self.trainer.flat.data, "_peer_buffer", None) is not None)
+
+    # ------------------------------------------------------------------ data path
+    def start_rollout_thread(self) -> None:
+        if self.global_rank != 0:
+            return
+
+        def loop():
+            stream = rollout_stream(self.replica_name)
+            while not self.shutdown_signal.is_set():
+                try:
+                    msgs = self.broker.read(stream, self._last_rollout_id, count=64, block_ms=500)
+                except Exception as e:
+                    logger.warning("[Policy] rollout read failed: %s", e)
+                    time.sleep(0.5)
+                    continue
+                for mid, data in msgs:
+                    self._last_rollout_id = mid
+                    self.data_queue.put(Rollout.model_validate_json(data))
+
+        t = threading.Thread(target=loop, name="fetch_rollouts", daemon=True)
+        t.start()
+        self._threads.append(t)
+
+    def dispatch_rollouts(self, items_count: int) -> List[Rollout]:
+        """Rank 0 pops ``items_count`` rollouts and deals them round-robin to the data-parallel ranks."""
+        dp = self.parallel_dims.dp_shard * self.parallel_dims.dp_replicate
+        per_rank: List[List[Rollout]] = [[] for _ in range(self.world_size)]
+        if self.global_rank == 0:
+            got: List[Rollout] = []
+            deadline = time.time() + 600
+            while len(got) < items_count and time.time() < deadline:
+                try:
+                    got.append(self.data_queue.get(timeout=1.0))
+                except queue.Empty:
+                    continue
+            for r in got:
+                if r.prompt is None:
+                    self.data_fetcher.fill(r)
+            for rank in range(self.world_size):
+                coords = self.parallel_dims.coords_of(rank)
+                dp_idx = coords["dp_replicate"] * self.parallel_dims.dp_shard + coords["dp_shard"]
+                per_rank[rank] = got[dp_idx::dp]
+        if self.world_size > 1:
+            out = [None]
+            dist.scatter_object_list(out, per_rank if self.global_rank == 0 else None, src=0)
+            return out[0]
+        return per_rank[0]
+
+    def execute_data_fetch(self, c: cmd.DataFetchCommand) -> bool:
+        if c.replica_name != self.replica_name:
+            return False
+        rollouts = self.dispatch_rollouts(c.items_count)
+        do_save = bool(c.do_save)
+        if self.config.train.save_ckpt_at_exit or self.force_save.is_set():
+            flag = torch.tensor([1 if self.force_save.is_set() else 0])
+            if self.world_size > 1:
+                dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+            if int(flag) > 0:
+                do_save = True
+                self.force_save.clear()
+        if self.profiler is not None and c.do_profile:
+            self.profiler.start_dynamic(c)
+        is_master = self.inter_replica.rank == 0
+        report = self.trainer.step_training(rollouts, c.global_step, c.total_steps, c.remain_samples_num,
+                                            do_save=do_save and is_master)
+        profile_finished = False
+        if self.profiler is not None:
+            profile_finished = self.profiler.step()
+        if self.global_rank == 0:
+            self.api.post_train_ack(self.replica_name, c.global_step, c.total_steps, profile_finished, report)
+        return c.replica_should_stop()
+
+    def execute_training_complete(self, c: cmd.TrainingCompleteCommand) -> bool:
+        if c.do_save and self.inter_replica.rank == 0:
+            self.trainer.save_checkpoint(c.final_step, c.checkpoint_total_steps, c.remain_samples_num, is_final=True)
+        return True
+
+    # ------------------------------------------------------------------ main loop
+    def main_loop(self) -> None:
+        self.start_command_thread()
+        self.start_rollout_thread()
+        stop = False
+        while not stop and not self.shutdown_signal.is_set():
+            c = self.next_command(timeout=0.2)
+            if c is None:
+                continue
+            handler = self.handlers.get_command_handler(c)
+            if handler is None:
+                logger.warning("[Policy] no handler for %r", c)
+                continue
+            logger.debug("[Policy] executing %r", c)
+            stop = bool(handler(c))
+        self.handle_shutdown()
+
+    execute = main_loop
+
+    def handle_shutdown(self) -> None:
+        """Order matters: stop producing work, finish checkpoints, abort dynamic communicators, unregister."""
+        if getattr(self, "_shut", False):
+            return
+        self._shut = True
+        self.shutdown_signal.set()
+        try:
+            self.trainer.ckpt_manager.finalize()
+        except Exception as e:
+            logger.warning("checkpoint finalize failed: %s", e)
+        self.inter_replica.shutdown()
+        for c in self.p2r_comms.values():
+            c.abort()
+        self.unregister_from_controller()

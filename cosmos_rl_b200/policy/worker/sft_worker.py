@@ -1,0 +1,117 @@
+"""SFT / DPO policy worker: owns its dataloader (data-parallel sampler, epochs, resume position), runs
+``trainer.step_training`` per global batch, validates every ``validation.freq`` steps and checkpoints
+(cosmos_rl/policy/worker/sft_worker.py:308-1097). With several policy replicas the gradients are averaged over
+the elastic inter-replica communicator, as in cosmos_rl/policy/worker/multi_replica_sft_worker.py:44-565."""
+from __future__ import annotations
+
+import random
+from typing import Any, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ...comm.base import CommMixin
+from ...dispatcher import command as cmd
+from ...dispatcher.data import CosmosDataset
+from ...dispatcher.protocol import Role
+from ...parallel.inter_replica import InterReplicaComm
+from ...utils.logging import logger
+from ..trainer.base import TrainerRegistry
+
+
+class SFTPolicyWorker(CommMixin):
+    role = Role.POLICY
+
+    def __init__(self, config, parallel_dims, dataset=None, val_dataset=None, data_packer=None, val_data_packer=None,
+                 hook_fns=None, api=None, device=None, tokenizer=None, standalone: bool = False, **kw):
+        self.config, self.parallel_dims = config, parallel_dims
+        self.device = device or parallel_dims.device
+        self.standalone = standalone or api is None and False
+        if not standalone:
+            self.init_comm(api)
+            self.inter_replica = InterReplicaComm(self.api, self.replica_name, self.global_rank, self.device)
+        else:
+            self.global_rank = dist.get_rank() if dist.is_initialized() else 0
+            self.world_size = dist.get_world_size() if dist.is_initialized() else 1
+            self.inter_replica = None
+        self.dataset = CosmosDataset(dataset, config, tokenizer) if dataset is not None else None
+        self.val_dataset = CosmosDataset(val_dataset, config, tokenizer) if val_dataset is not None else None
+        tp = config.train.train_policy
+        self.trainer = TrainerRegistry.get_trainer_cls(tp.trainer_type)(
+            config, parallel_dims, device=self.device, data_packer=data_packer, val_data_packer=val_data_packer,
+            hook_fns=hook_fns, tokenizer=tokenizer, inter_replica=self.inter_replica, **kw)
+        resumed = self.trainer.weight_resume()
+        self.start_step = self.trainer.train_step if resumed else 0
+        self.dp = parallel_dims.dp_shard * parallel_dims.dp_replicate
+        c = parallel_dims.coords
+        self.dp_rank = c["dp_replicate"] * parallel_dims.dp_shard + c["dp_shard"]
+        self.batch_per_rank = max(1, config.train.train_batch_per_replica // self.dp)
+        n = len(self.dataset) if self.dataset is not None else 0
+        per_step = self.batch_per_rank * self.dp
+        self.steps_per_epoch = n // per_step if tp.dataloader_drop_last else -(-n // per_step)
+        self.total_steps = self.steps_per_epoch * config.train.epoch
+        if config.train.max_num_steps:
+            self.total_steps = min(self.total_steps, config.train.max_num_steps)
+        self.history: List[dict] = []
+
+    def _epoch_order(self, epoch: int) -> List[int]:
+        tp = self.config.train.train_policy
+        order = list(range(len(self.dataset)))
+        if tp.dataloader_shuffle:
+            random.Random(tp.dataloader_seed + epoch).shuffle(order)
+        return order
+
+    def _batch(self, step: int) -> List[Any]:
+        """Samples of this data-parallel rank for global step ``step`` (0-based)."""
+        epoch, k = divmod(step, max(1, self.steps_per_epoch))
+        order = self._epoch_order(epoch)
+        per_step = self.batch_per_rank * self.dp
+        idxs = order[k * per_step:(k + 1) * per_step][self.dp_rank::self.dp]
+        return [self.dataset[i] for i in idxs]
+
+    def validate(self, step: int) -> Optional[float]:
+        if self.val_dataset is None:
+            return None
+        bs = self.config.validation.batch_size or self.batch_per_rank
+        total, n = 0.0, 0
+        for i in range(self.dp_rank * bs, len(self.val_dataset), bs * self.dp):
+            batch = [self.val_dataset[j] for j in range(i, min(i + bs, len(self.val_dataset)))]
+            total += self.trainer.step_validation(batch).get("val/loss", 0.0)
+            n += 1
+        score = -total / max(n, 1)
+        self.trainer.ckpt_manager.report_validation_score(step, score)
+        logger.info("[SFT] validation at step %d: loss=%.4f", step, -score)
+        return -score
+
+    def main_loop(self) -> None:
+        ck, val = self.config.train.ckpt, self.config.validation
+        if val.enable and val.val_before_train:
+            self.validate(self.start_step)
+        for step in range(self.start_step, self.total_steps):
+            do_save = ck.enable_checkpoint and ((step + 1) % max(1, ck.save_freq) == 0 or step + 1 == self.total_steps)
+            report = self.trainer.step_training(self._batch(step), self.total_steps, step + 1, do_save=do_save)
+            self.history.append({"step": step + 1, **report})
+            if (step + 1) % max(1, self.config.logging.log_interval) == 0 and self.global_rank == 0:
+                logger.info("[SFT] step %d/%d loss=%.4f grad_norm=%.3f", step + 1, self.total_steps,
+                            report["train/loss_avg"], report["train/grad_norm"])
+            if val.enable and val.freq and (step + 1) % val.freq == 0:
+                self.validate(step + 1)
+            if not self.standalone and self.global_rank == 0:
+                try:
+                    self.api.post_train_ack(self.replica_name, step + 1, self.total_steps, False, report)
+                except Exception as e:
+                    logger.warning("train_ack failed: %s", e)
+        self.handle_shutdown()
+
+    execute = main_loop
+
+    def handle_shutdown(self) -> None:
+        if getattr(self, "_shut", False):
+            return
+        self._shut = True
+        self.trainer.ckpt_manager.finalize()
+        if not self.standalone:
+            self.shutdown_signal.set()
+            if self.inter_replica is not None:
+                self.inter_replica.shutdown()
+            self.unregister_from_controller()

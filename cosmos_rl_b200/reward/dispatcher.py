@@ -1,0 +1,154 @@
+"""Reward computation for finished generations (cosmos_rl/reward/dispatcher.py:27-264,
+reward/local_calculator.py:27-360, reward/base.py:22-169).
+
+The rollout worker enqueues one task per prompt (its n completions); a worker pool computes rewards,
+group-relative advantages, DAPO validity (a group whose filter rewards are all equal carries no signal and
+is dropped) and the shared-prefix mask (completions of one group that start with the same long prefix but
+got different rewards: the prefix tokens are excluded from the loss). Finished payloads are collected with
+``dequeue``.
+"""
+from __future__ import annotations
+
+import concurrent.futures
+import queue
+import threading
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+from ..dispatcher.algo.grpo import GRPO
+from ..dispatcher.algo.reward import Reward, get_reward_fn
+from ..dispatcher.data.schema import RLPayload
+
+
+def shared_prefix_ignore(token_lists: Sequence[Sequence[int]], rewards: Sequence[float], min_tokens: int) -> List[int]:
+    """For each completion: length of the longest prefix (>= ``min_tokens``) it shares with a completion of the
+    same group that received a different reward."""
+    n = len(token_lists)
+    out = [0] * n
+    for i in range(n):
+        for j in range(n):
+            if i == j or rewards[i] == rewards[j]:
+                continue
+            a, b = token_lists[i], token_lists[j]
+            k = 0
+            m = min(len(a), len(b))
+            while k < m and a[k] == b[k]:
+                k += 1
+            if k >= min_tokens:
+                out[i] = max(out[i], k)
+    return out
+
+
+class LocalRewardCalculator:
+    def __init__(self, config, reward_fns: Optional[List[Callable]] = None,
+                 filter_reward_fns: Optional[List[Callable]] = None, validation: bool = False):
+        self.config = config
+        tp = config.train.train_policy
+        spec = config.validation.reward_function if validation and config.validation.reward_function else \
+            getattr(tp, "reward_function", None)
+        self.reward = Reward(spec, explicit_fns=reward_fns)
+        self.filter_reward = Reward(getattr(tp, "filter_reward_metric", None), explicit_fns=filter_reward_fns) \
+            if (filter_reward_fns or getattr(tp, "filter_reward_metric", None)) else None
+        self.algo = GRPO(self.reward, unbiased=getattr(tp, "unbiased_advantage", False),
+                         filter_reward_fn=self.filter_reward)
+        self.variant = getattr(tp, "variant", "grpo")
+        self.min_prefix = getattr(tp, "min_filter_prefix_tokens", None)
+        self.bypass = bool(getattr(tp, "bypass_reward", False))
+        self.overlong = getattr(tp, "overlong_reward", None)
+        self.max_response = config.rollout.max_response_length
+        self.adv_low = getattr(tp, "advantage_low", -1e9)
+        self.adv_high = getattr(tp, "advantage_high", 1e9)
+
+    def compute(self, payload: RLPayload) -> RLPayload:
+        comps = payload.completions or []
+        toks = [[p[0] for p in c] for c in payload.completion_token_ids] if payload.completion_token_ids else None
+        if self.bypass:
+            payload.rewards = [0.0] * len(comps)
+            payload.advantages = [0.0] * len(comps)
+            payload.filter_rewards = [0.0] * len(comps)
+            payload.valid = True
+            return payload
+        rewards, filt = [], []
+        for i, c in enumerate(comps):
+            kw = {"token_ids": toks[i]} if toks else {}
+            r = float(self.algo.compute_reward(c, payload.reference_answer, prompt=payload.prompt, **kw))
+            if self.overlong is not None and self.overlong.enable_overlong_penalty and toks:
+                from ..dispatcher.algo.reward import overlong_reward
+                r += overlong_reward(c, length=len(toks[i]), max_length=self.max_response,
+                                     buffer_length=self.overlong.buffer_length,
+                                     penalty_factor=self.overlong.penalty_factor)
+            rewards.append(r)
+            f = self.algo.compute_filter_reward(c, payload.reference_answer, prompt=payload.prompt, **kw)
+            filt.append(float(f) if f is not None else r)
+        advs = [min(max(a, self.adv_low), self.adv_high) for a in self.algo.compute_advantage(rewards)]
+        payload.rewards, payload.advantages, payload.filter_rewards = rewards, advs, filt
+        payload.valid = True
+        if self.variant == "dapo" and len(set(filt)) <= 1:
+            payload.valid = False   # dynamic sampling: no learning signal in this group
+        if self.min_prefix and toks:
+            payload.n_ignore_prefix_tokens = shared_prefix_ignore(toks, rewards, self.min_prefix)
+        return payload
+
+
+class RemoteRewardCalculator:
+    """Scores completions through an HTTP reward service (cosmos_rl/reward/remote_calculator.py:41-436)."""
+
+    def __init__(self, config, url: str, timeout_s: float = 60.0):
+        self.config, self.url, self.timeout_s = config, url, timeout_s
+        self.rr = config.train.train_policy.remote_reward
+        self.local = LocalRewardCalculator(config, reward_fns=[lambda *a, **k: 0.0])
+
+    def compute(self, payload: RLPayload) -> RLPayload:
+        import requests
+        body = {"prompt": payload.prompt, "completions": payload.completions, "reference": payload.reference_answer}
+        r = requests.post(self.url, json=body, timeout=self.timeout_s)
+        r.raise_for_status()
+        scores = r.json()["scores"]
+        rr = self.rr
+        rewards = [min(max(float(s) * rr.scale, rr.reward_clip_min), rr.reward_clip_max) for s in scores]
+        payload.rewards = rewards
+        payload.advantages = self.local.algo.compute_advantage(rewards)
+        payload.filter_rewards = list(rewards)
+        payload.valid = True
+        return payload
+
+
+class RewardDispatcher:
+    def __init__(self, calculator, num_workers: int = 2):
+        self.calc = calculator
+        self.pool = concurrent.futures.ThreadPoolExecutor(max_workers=max(1, num_workers),
+                                                          thread_name_prefix="reward")
+        self.pending: "queue.Queue[concurrent.futures.Future]" = queue.Queue()
+        self.n_inflight = 0
+        self.lock = threading.Lock()
+
+    def enqueue_rewards_cal(self, payloads: List[RLPayload], is_validation: bool = False, step: int = 0) -> None:
+        for p in payloads:
+            with self.lock:
+                self.n_inflight += 1
+            self.pending.put(self.pool.submit(self.calc.compute, p))
+
+    def dequeue(self, block: bool = False, timeout: Optional[float] = None) -> List[RLPayload]:
+        """Payloads whose rewards are done, in submission order (stops at the first unfinished one unless
+        ``block``)."""
+        out: List[RLPayload] = []
+        while True:
+            try:
+                fut = self.pending.queue[0] if not block else self.pending.get(timeout=timeout)
+            except (IndexError, queue.Empty):
+                break
+            if not block:
+                if not fut.done():
+                    break
+                self.pending.get_nowait()
+            out.append(fut.result())
+            with self.lock:
+                self.n_inflight -= 1
+            if block and self.pending.empty():
+                break
+        return out
+
+    def is_empty(self) -> bool:
+        return self.n_inflight == 0
+
+    def shutdown(self) -> None:
+        self.pool.shutdown(wait=False, cancel_futures=True)

@@ -1,0 +1,78 @@
+"""The built-in rollout backend: this framework's own sm_100a generation engine behind the
+``RolloutBase`` interface. The names ``vllm``, ``vllm_async`` and ``trtllm`` are accepted as aliases so job
+files written for the reference run unchanged (cosmos_rl/rollout/vllm_rollout/vllm_rollout.py:145-1128)."""
+from __future__ import annotations
+
+import copy
+from typing import Any, List, Optional
+
+import torch
+
+from ..models import hf_io
+from ..models.base import ModelRegistry
+from ..parallel.flat import FlatParams
+from .base import RolloutBase, RolloutRegistry, RolloutResult
+from .engine import RolloutEngine, SamplingParams
+
+
+@RolloutRegistry.register("b200")
+class B200Rollout(RolloutBase):
+    def __init__(self, config, parallel_dims, device, tokenizer=None, **kw):
+        super().__init__(config, parallel_dims, device)
+        self.tokenizer = tokenizer
+        self.engine: Optional[RolloutEngine] = None
+        self.model = None
+        self.flat: Optional[FlatParams] = None
+
+    def init_engine(self, load_format: str = "dummy", shared_model=None, seed: Optional[int] = None, **kw) -> None:
+        cfg = self.config
+        if shared_model is not None:
+            self.model = shared_model          # colocated: generate on the policy's own tensors
+        else:
+            hf_config = hf_io.load_hf_config(cfg.policy.model_name_or_path, cfg.custom.get("model_config"))
+            tp = self.parallel_dims.tp
+            with torch.device("meta"):
+                self.model = ModelRegistry.build_model(hf_config, tp_size=tp, tp_rank=self.parallel_dims.tp_coord)
+            dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+            self.flat = FlatParams(self.model, dtype, self.device, with_grad=False)
+            if tp > 1:
+                from ..parallel.tp import TensorParallel
+                self.model.tp = TensorParallel(self.parallel_dims.group("tp"), tp, self.parallel_dims.tp_coord)
+            path = cfg.policy.model_name_or_path
+            import os
+            if load_format != "dummy" and os.path.isdir(path) and hf_io.has_safetensors(path):
+                hf_io.load_hf_weights(self.model, path, self.parallel_dims)
+        r = cfg.rollout
+        self.engine = RolloutEngine(
+            self.model, max_num_seqs=max(8, r.batch_size * r.n_generation),
+            max_model_len=cfg.policy.model_max_length, page_size=cfg.b200.rollout_page_size,
+            use_cuda_graph=cfg.b200.cuda_graph_decode and not r.enforce_eager or cfg.b200.cuda_graph_decode,
+            seed=seed if seed is not None else (r.seed or 0))
+
+    def get_underlying_model(self):
+        return self.model
+
+    def rollout_generation(self, payloads, data_packer, data_fetcher=None, is_validation: bool = False, **kw
+                           ) -> List[RolloutResult]:
+        sp = SamplingParams.from_config(self.config, validation=is_validation)
+        eos = getattr(self.tokenizer, "eos_token_id", None)
+        if eos is not None:
+            sp.stop_token_ids = (eos,)
+        prompts = [data_packer.get_rollout_input(p.prompt) for p in payloads]
+        outs = self.engine.generate(prompts, sp)
+        results = []
+        for p, comps in zip(payloads, outs):
+            if self.tokenizer is not None and not self.config.train.train_policy.rollout_as_token_ids:
+                texts = [self.tokenizer.decode(c.token_ids, skip_special_tokens=True) for c in comps]
+            else:
+                texts = [c.token_ids for c in comps]
+            results.append(RolloutResult(
+                prompt=p.prompt, completions=texts,
+                completion_token_ids=[c.token_ids for c in comps],
+                completion_logprobs=[c.logprobs for c in comps],
+                cumulative_logprob=[c.cumulative_logprob for c in comps]))
+        return results
+
+
+for _alias in ("vllm", "vllm_async", "trtllm"):
+    RolloutRegistry._backends[_alias] = B200Rollout

@@ -1,0 +1,292 @@
+"""Rollout control worker: the producer side of the asynchronous loop
+(cosmos_rl/rollout/worker/rollout_control.py:129-2936).
+
+Main loop: consume commands (weight sync, mesh, stop) -> fetch prompts from the controller (rank 0, then
+broadcast / scatter) -> hold back while the head prompt asks for weights newer than
+``current_weight_version + allowed_outdated_steps`` -> generate -> hand completions to the reward pool ->
+report finished payloads. The end of the prompt stream (``is_end``) and the STOP command both lead to an
+orderly exit.
+"""
+from __future__ import annotations
+
+import queue
+import threading
+import time
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..comm.base import CommMixin
+from ..data.packer import BaseDataPacker
+from ..dispatcher import command as cmd
+from ..dispatcher.data import CosmosDataset, WorkerDataFetcher
+from ..dispatcher.data.schema import RLPayload
+from ..dispatcher.protocol import Role
+from ..parallel.dims import ParallelDims
+from ..parallel.reshard import build_plan, model_parts, shard_info
+from ..reward.dispatcher import LocalRewardCalculator, RewardDispatcher
+from ..utils import constant
+from ..utils.logging import logger
+from .base import RolloutRegistry
+from . import b200_rollout  # noqa: F401  (registers the built-in backend)
+
+
+class DisaggregatedRolloutControlWorker(CommMixin):
+    role = Role.ROLLOUT
+
+    def __init__(self, config, parallel_dims: ParallelDims, dataset=None, val_dataset=None, data_packer=None,
+                 val_data_packer=None, reward_fns=None, filter_reward_fns=None, val_reward_fns=None, api=None,
+                 device=None, tokenizer=None, **kw):
+        self.config = config
+        self.parallel_dims = parallel_dims
+        self.device = device or parallel_dims.device
+        self.init_comm(api)
+        ds = CosmosDataset(dataset, config) if dataset is not None else None
+        vds = CosmosDataset(val_dataset, config) if val_dataset is not None else None
+        self.data_fetcher = WorkerDataFetcher(config, ds, vds)
+        self.tokenizer = tokenizer
+        backend = config.rollout.backend
+        self.rollout = RolloutRegistry.get(backend)(config, parallel_dims, self.device, tokenizer=tokenizer)
+        self.rollout.init_engine(load_format="dummy", seed=(config.rollout.seed or 0) + hash(self.replica_name) % 9973)
+        mt = getattr(self.rollout.model.args, "model_type", "hfmodel")
+        self.data_packer = data_packer or BaseDataPacker.get_default(mt)()
+        self.data_packer.setup(config, tokenizer)
+        self.reward_dispatcher = RewardDispatcher(LocalRewardCalculator(config, reward_fns, filter_reward_fns))
+        self.val_reward_dispatcher = RewardDispatcher(
+            LocalRewardCalculator(config, val_reward_fns or reward_fns, validation=True))
+        self.current_weight_version = -1
+        self.weights_ready = False
+        self.prompt_queue: List[Tuple[int, RLPayload]] = []
+        self.prompt_end = False
+        self.stopped = False
+        self.total_steps: Optional[int] = None
+        self.batch_size = config.rollout.batch_size
+        self.handlers = cmd.RolloutCommandRegistry()
+        for c, h in ((cmd.BuildMeshCommand, self.execute_build_mesh),
+                     (cmd.PolicyToRolloutUnicastCommand, self.policy_to_rollout_unicast),
+                     (cmd.RolloutToRolloutBroadcastCommand, self.rollout_to_rollout_broadcast),
+                     (cmd.StopCommand, self.execute_stop)):
+            self.handlers.register(c, h)
+        self.mesh: Dict[str, int] = {}
+        self.p2r_comms: Dict[str, Any] = {}
+        self.peer_sync = None
+        self.recv_plan = None
+        self.r2r_comm = None
+        self.stats = {"generated_tokens": 0, "batches": 0, "sync_ms": []}
+        self.post_shard_infos()
+
+    # ------------------------------------------------------------------ shard infos
+    def post_shard_infos(self) -> None:
+        if self.rollout.flat is None:
+            return
+        info = shard_info(self.global_rank, model_parts(self.rollout.model, self.rollout.flat), self.rollout.flat.total)
+        infos = [None] * self.world_size
+        if self.world_size > 1:
+            dist.all_gather_object(infos, info)
+        else:
+            infos = [info]
+        self.my_shard_info = info
+        if self.global_rank == 0:
+            self.api.post_shard_infos("rollout", {"ranks": infos, "replica": self.replica_name})
+
+    # ------------------------------------------------------------------ command handlers
+    def execute_build_mesh(self, c: cmd.BuildMeshCommand) -> bool:
+        self.mesh = dict(c.replica_name_to_rank)
+        return False
+
+    def execute_stop(self, c: cmd.StopCommand) -> bool:
+        self.stopped = True
+        return True
+
+    def _policy_infos(self):
+        return self.api.get_shard_infos("policy")
+
+    def policy_to_rollout_unicast(self, c: cmd.PolicyToRolloutUnicastCommand) -> bool:
+        if c.dst_replica_name != self.replica_name:
+            return False
+        t0 = time.perf_counter()
+        key = f"p2r:{c.uuid_value}"
+        peer = bool(self.config.b200.peer_weight_sync and self.device.type == "cuda")
+        if peer:
+            self._peer_pull(c, key)
+        else:
+            self._collective_recv(c)
+        self.weights_ready = True
+        self._pending_version = c.weight_step if c.weight_step is not None else 0
+        self.total_steps = c.total_steps
+        self.stats["sync_ms"].append((time.perf_counter() - t0) * 1e3)
+        return False
+
+    def _peer_pull(self, c, key: str) -> None:
+        from ..parallel.peer import PeerMapping
+        from .weight_sync import PeerWeightSync
+        deadline = time.time() + 600
+        while not self.broker.kv_get(key + ":ready"):
+            if time.time() > deadline:
+                raise TimeoutError(f"policy never announced weights for {key}")
+            time.sleep(0.005)
+        if self.peer_sync is None:
+            infos = self.api.get_shard_insts("rollout", self.global_rank)  # plan rows
+            pol = self._policy_infos()
+            ptrs, self._peer_maps = {}, []
+            for info in pol["ranks"]:
+                m = PeerMapping(info["ipc_handle"], info["nbytes"], self.device)
+                self._peer_maps.append(m)
+                ptrs[info["rank"]] = m.ptr
+            self.peer_sync = PeerWeightSync(self.rollout.flat.data, infos, ptrs)
+        self.peer_sync.pull()
+        torch.cuda.synchronize()
+        from ..ops import native
+        native.read_status(self.device)
+        self.broker.kv_set(f"{key}:done:{self.global_rank}", b"1", ttl_s=3600)
+
+    def _collective_recv(self, c) -> None:
+        from ..parallel.dyncomm import create_comm
+        from ..utils.misc import str2dtype
+        pair = f"p2r-{c.src_replica_name}-{c.dst_replica_name}"
+        comm = self.p2r_comms.get(pair)
+        P = c.src_replica_size
+        if comm is None or comm.aborted:
+            comm = create_comm(self.api, f"{pair}-{c.uuid_value}" if comm is not None else pair,
+                               P + self.global_rank, P + c.dst_replica_size, self.device, is_initiator=False)
+            self.p2r_comms[pair] = comm
+        if self.recv_plan is None:
+            self.recv_plan = self.api.get_shard_insts("rollout", self.global_rank)
+        flat = self.rollout.flat.data
+        tdt = str2dtype(self.config.train.transfer_dtype) if self.device.type == "cuda" else flat.dtype
+        for d in self.recv_plan:
+            buf = torch.empty(d[5], d[6], dtype=tdt, device=self.device)
+            comm.recv(buf, d[0])
+            torch.as_strided(flat, (d[5], d[6]), (d[4], 1), flat.storage_offset() + d[3]).copy_(buf)
+
+    def rollout_to_rollout_broadcast(self, c: cmd.RolloutToRolloutBroadcastCommand) -> bool:
+        """Commit a weight version. With peer sync every replica has already pulled its own copy, so this
+        carries no data; otherwise the source replica broadcasts its parameters to the others."""
+        if self.replica_name not in c.dst_replica_names:
+            return False
+        peer = bool(self.config.b200.peer_weight_sync and self.device.type == "cuda")
+        if not peer and len(c.dst_replica_names) > 1:
+            self._r2r_data(c)
+        if c.weight_step is not None:
+            self.current_weight_version = c.weight_step
+        else:
+            self.current_weight_version = getattr(self, "_pending_version", 0)
+        self.weights_ready = True
+        self.rollout.engine.weight_version = self.current_weight_version
+        if c.total_steps is not None:
+            self.total_steps = c.total_steps
+        return bool(c.replica_should_stop())
+
+    def _r2r_data(self, c) -> None:
+        from ..parallel.dyncomm import create_comm
+        names = sorted(c.dst_replica_names, key=lambda n: self.mesh.get(n, 0))
+        rank = names.index(self.replica_name)
+        key = f"r2r-{'-'.join(n[:8] for n in names)}-r{self.global_rank}"
+        if self.r2r_comm is None or self.r2r_comm.aborted or self.r2r_comm.size != len(names):
+            self.r2r_comm = create_comm(self.api, key + f"-{c.uuid_value}", rank, len(names), self.device,
+                                        is_initiator=rank == 0)
+        src = names.index(c.src_replica_name)
+        self.r2r_comm.broadcast(self.rollout.flat.data, src)
+
+    # ------------------------------------------------------------------ prompts
+    def request_new_prompts(self, n: int, validation_step: Optional[int] = None) -> None:
+        batch, is_end = [], False
+        if self.global_rank == 0:
+            batch, is_end = self.api.get_next_prompt(n, validation_step=validation_step)
+            for _, p in batch:
+                self.data_fetcher.fill(p, validation=validation_step is not None)
+        if self.world_size > 1:
+            box = [([(i, p.model_dump()) for i, p in batch], is_end)]
+            dist.broadcast_object_list(box, src=0)
+            raw, is_end = box[0]
+            batch = [(i, RLPayload.model_validate(p)) for i, p in raw]
+        self.prompt_queue.extend(batch)
+        if is_end:
+            self.prompt_end = True
+
+    def consume_commands(self, block: float = 0.0) -> bool:
+        """Run every queued command; True when one of them asks the loop to stop."""
+        stop = False
+        while True:
+            c = self.next_command(timeout=block)
+            block = 0.0
+            if c is None:
+                return stop
+            h = self.handlers.get_command_handler(c)
+            if h is not None:
+                stop = bool(h(c)) or stop
+
+    def report_rollouts(self, block: bool = False, is_end: bool = False) -> None:
+        done = self.reward_dispatcher.dequeue(block=block and not self.reward_dispatcher.is_empty())
+        if self.global_rank != 0:
+            return
+        if done or is_end:
+            self.api.post_rollout_completion(self.replica_name, done, is_end=is_end,
+                                             metrics={"generated_tokens": self.stats["generated_tokens"]})
+
+    # ------------------------------------------------------------------ generation
+    def one_step_generation(self) -> None:
+        n = min(self.batch_size, len(self.prompt_queue))
+        batch = self.prompt_queue[:n]
+        del self.prompt_queue[:n]
+        payloads = [p for _, p in batch]
+        results = self.rollout.rollout_generation(payloads, self.data_packer, self.data_fetcher)
+        reporter = self.parallel_dims.tp_coord == 0 and self.parallel_dims.pp_coord == self.parallel_dims.pp - 1
+        for p, r in zip(payloads, results):
+            p.completions = r.completions
+            p.completion_token_ids = [[[t] for t in toks] for toks in r.completion_token_ids]
+            if self.config.train.train_policy.collect_rollout_logprobs or \
+                    self.config.train.train_policy.use_rollout_logprobs_for_loss:
+                p.completion_logprobs = [[[l] for l in lps] for lps in r.completion_logprobs]
+            p.cumulative_logprob = r.cumulative_logprob
+            p.weight_version = self.current_weight_version
+            self.stats["generated_tokens"] += sum(len(t) for t in r.completion_token_ids)
+        self.stats["batches"] += 1
+        if reporter:
+            self.reward_dispatcher.enqueue_rewards_cal(payloads)
+
+    def main_loop(self) -> None:
+        self.start_command_thread()
+        allowed = getattr(self.config.train.train_policy, "allowed_outdated_steps", 0)
+        while not self.shutdown_signal.is_set():
+            if self.consume_commands(block=0.05 if not self.weights_ready else 0.0) or self.stopped:
+                break
+            if not self.weights_ready:
+                continue
+            if not self.prompt_queue and not self.prompt_end:
+                self.request_new_prompts(self.batch_size)
+            if not self.prompt_queue:
+                self.report_rollouts()
+                if self.prompt_end and self.reward_dispatcher.is_empty():
+                    break
+                time.sleep(constant.COSMOS_WEIGHT_GATE_SLEEP)
+                continue
+            # weight-version gate: never run further ahead of training than the allowed staleness
+            head_version = self.prompt_queue[0][1].weight_version
+            if head_version > self.current_weight_version + allowed:
+                self.report_rollouts()
+                time.sleep(constant.COSMOS_WEIGHT_GATE_SLEEP)
+                continue
+            self.one_step_generation()
+            self.report_rollouts()
+        # drain: finish rewards, report the end of this replica's stream
+        self.report_rollouts(block=True, is_end=True)
+        self.handle_shutdown()
+
+    work = main_loop
+
+    def handle_shutdown(self) -> None:
+        if getattr(self, "_shut", False):
+            return
+        self._shut = True
+        self.shutdown_signal.set()
+        self.reward_dispatcher.shutdown()
+        self.val_reward_dispatcher.shutdown()
+        for c in self.p2r_comms.values():
+            c.abort()
+        if self.r2r_comm is not None:
+            self.r2r_comm.abort()
+        for m in getattr(self, "_peer_maps", []):
+            m.close()
+        self.unregister_from_controller()
