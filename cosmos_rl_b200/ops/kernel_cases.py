@@ -1,0 +1,186 @@
+"""Small, self-contained launches of each sm_100a kernel for timing and profiling.
+
+    python -m cosmos_rl_b200.ops.kernel_cases <case> [--iters N]
+
+Every case uses inputs larger than the 126 MB L2 (so DRAM figures mean something) but at most a few GB,
+launches the kernel ``--iters`` times after 3 warm-up launches, times the launches with CUDA events and
+prints achieved bandwidth / FLOP rate next to the measured machine peaks (``MEASURED_PEAKS.json`` at the
+repository root when present, else 6.65 TB/s and 1.59 PFLOP/s).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+from . import functional as F
+from . import native, optim
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "measured"
+    return 6.65e12, 1.59e15, "fallback"
+
+
+def timed(fn, iters: int) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters / 1e3
+
+
+def report(name: str, seconds: float, nbytes: float = 0.0, flops: float = 0.0) -> None:
+    bw, fl, kind = peaks()
+    line = f"{name}: {seconds * 1e6:.1f} us"
+    if nbytes:
+        line += f" | {nbytes / seconds / 1e9:.0f} GB/s = {nbytes / seconds / bw:.2f} of {kind} HBM copy bandwidth"
+    if flops:
+        line += f" | {flops / seconds / 1e12:.0f} TFLOP/s = {flops / seconds / fl:.2f} of {kind} cuBLAS bf16"
+    print(line, flush=True)
+
+
+def bf(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def case_gemm(iters):
+    M, N, K = 8192, 8192, 4096
+    a, b = bf(M, K), bf(N, K)
+    c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    t = timed(lambda: F.gemm_nt(a, b, out=c), iters)
+    report(f"gemm_bf16_nt {M}x{N}x{K}", t, flops=2.0 * M * N * K)
+
+
+def case_logprob(iters):
+    T, V, H = 4096, 152064, 3584
+    h, w = bf(T, H), bf(V, H, scale=0.02)
+    lab = torch.randint(0, V, (T,), device="cuda")
+    t = timed(lambda: F.fused_logprob(h, w, lab, 1.0), iters)
+    report(f"lmhead_logprob fwd T={T} V={V} H={H}", t, flops=2.0 * T * V * H)
+
+
+def case_dlogits(iters):
+    T, V, H = 4096, 32768, 3584
+    h = bf(T, H).requires_grad_(True)
+    w = bf(V, H, scale=0.02).requires_grad_(True)
+    lab = torch.randint(0, V, (T,), device="cuda")
+
+    def run():
+        lp, ent = F.fused_logprob(h, w, lab, 1.0)
+        lp.sum().backward()
+        h.grad = None
+        w.grad = None
+    t = timed(run, iters)
+    report(f"lmhead_logprob fwd+bwd T={T} V={V} H={H}", t, flops=8.0 * T * V * H)
+
+
+def case_decode(iters):
+    B, hq, hkv, d, P, L = 128, 28, 4, 128, 128, 1000
+    pages = B * 8 + 1
+    cache = bf(pages, 2, hkv, P, d)
+    bt = (torch.arange(B * 8, device="cuda", dtype=torch.int32) + 1).view(B, 8)
+    lens = torch.full((B,), L, dtype=torch.int32, device="cuda")
+    q = bf(B, hq, d)
+    t = timed(lambda: F.paged_decode(q, cache, bt, lens, v_transposed=True), iters)
+    report(f"paged_decode_tc B={B} hq={hq} hkv={hkv} len={L}", t, nbytes=B * 8 * P * hkv * d * 2 * 2)
+
+
+def case_reshard(iters):
+    from ..rollout.weight_sync import PeerWeightSync
+    rows, cols = 16384, 16384
+    src = bf(rows * cols)
+    dst = torch.empty_like(src)
+    plan = [[0, 0, cols, 0, cols, rows, cols]]
+    ws = PeerWeightSync(dst, plan, {0: src.data_ptr()})
+    t = timed(ws.pull, iters)
+    report(f"reshard_pull (local source) {rows}x{cols} bf16", t, nbytes=2.0 * rows * cols * 2)
+
+
+def case_quant(iters):
+    R, C = 16384, 16384
+    w = bf(R, C)
+    t = timed(lambda: F.quant_fp8_block(w, 128), iters)
+    report(f"quant_fp8_block 128x128 {R}x{C}", t, nbytes=R * C * 3.0)
+
+
+def case_rmsnorm(iters):
+    T, H = 65536, 3584
+    x, r, w = bf(T, H), bf(T, H), bf(H)
+    t = timed(lambda: F.rms_norm(x, w, 1e-6, r), iters)
+    report(f"rmsnorm_fwd(+residual) T={T} H={H}", t, nbytes=T * H * 2.0 * 4)
+    xg = x.clone().requires_grad_(True)
+    wg = w.clone().requires_grad_(True)
+    y, _ = F.rms_norm(xg, wg, 1e-6)
+    g = torch.randn_like(y)
+    t = timed(lambda: torch.autograd.grad(y, (xg, wg), g, retain_graph=True), iters)
+    report(f"rmsnorm_bwd T={T} H={H}", t, nbytes=T * H * 2.0 * 3)
+
+
+def case_swiglu(iters):
+    T, I = 32768, 18944
+    gu = bf(T, 2 * I)
+    t = timed(lambda: F.swiglu(gu), iters)
+    report(f"swiglu_fwd T={T} I={I}", t, nbytes=T * I * 2.0 * 3)
+
+
+def case_rope(iters):
+    T, hq, hkv, d = 65536, 28, 4, 128
+    qkv = bf(T, (hq + 2 * hkv) * d)
+    pos = torch.arange(T, device="cuda") % 4096
+    t = timed(lambda: F.rope_qkv_(qkv, pos, hq, hkv, d, 1e6), iters)
+    report(f"rope_qkv T={T}", t, nbytes=T * (hq + hkv) * d * 2.0 * 2)
+
+
+def case_adamw(iters):
+    n = 1 << 26
+    master = torch.randn(n, device="cuda")
+    m, v = torch.zeros_like(master), torch.zeros_like(master)
+    g = bf(n, scale=0.01)
+    shadow = master.to(torch.bfloat16)
+    coef = torch.ones(1, device="cuda")
+    t = timed(lambda: optim.adamw_flat(master, m, v, g, shadow, lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8,
+                                       weight_decay=0.01, step=3, grad_scale=coef), iters)
+    report(f"adamw_flat n={n}", t, nbytes=n * (12 + 2 + 12 + 2.0))
+
+
+def case_sample(iters):
+    B, V = 512, 152064
+    logits = torch.randn(B, V, device="cuda")
+    temp = torch.ones(B, device="cuda")
+    t = timed(lambda: F.sample(logits, temp, None, None, seed=1, offset=2), iters)
+    report(f"sample B={B} V={V} (no truncation: 3 passes over the row, 2 served by L2)", t, nbytes=B * V * 4.0)
+
+
+CASES = {"gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
+         "reshard": case_reshard, "quant": case_quant, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu,
+         "rope": case_rope, "adamw": case_adamw, "sample": case_sample}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=sorted(CASES) + ["all"])
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args(argv)
+    torch.manual_seed(0)
+    for name in (sorted(CASES) if a.case == "all" else [a.case]):
+        CASES[name](a.iters)
+        native.read_status(torch.device("cuda", torch.cuda.current_device()))
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()
