@@ -37,7 +37,7 @@ def parse_args():
     ap.add_argument("--group", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--max-response", type=int, default=1024)
-    ap.add_argument("--mb-tokens", type=int, default=16384, help="token budget of one training micro-batch")
+    ap.add_argument("--mb-tokens", type=int, default=8192, help="token budget of one training micro-batch")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
 

@@ -429,6 +429,8 @@ class B200Config(_Section):
     fused_logprob: bool = True           # tcgen05 fused lm_head + log-prob kernel
     nvls: bool = True                    # allow multimem (NVSwitch) reductions where available
     dlogits_chunk: int = 16384
+    recompute: str = "selective"         # with policy.model_gradient_checkpointing: "selective" (attention half +
+                                         # SwiGLU only) or "full" (whole block, least memory)
 
 
 class Config(_Section):

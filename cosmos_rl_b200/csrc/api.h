@@ -20,6 +20,11 @@ extern "C" {
 int b200_gemm_bf16_nt(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                       long long ldc, int out_fp32, int accumulate, uint32_t* status, int num_sms,
                       cudaStream_t stream);
+// General form: a_mn / b_mn = 1 when the operand is stored with the contraction index as the ROW index
+// ([K, M] / [K, N] row-major). Covers forward (0,0), dgrad (0,1) and wgrad (1,1) without transposed copies.
+int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                   long long ldc, int a_mn, int b_mn, int out_fp32, int accumulate, uint32_t* status, int num_sms,
+                   cudaStream_t stream);
 
 // Fused lm_head GEMM + per-token log-prob statistics, never materialising [T, V] logits.
 //   hidden [T, H] bf16, weight [V, H] bf16, labels [T] int64 (label < 0: row ignored)

@@ -32,39 +32,66 @@ struct GemmSmem {
   static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
 };
 
+// One output tile as seen by every role of the pipeline.
+struct TileInfo {
+  int m_blk, n_blk;  // tile indices handed to the epilogue
+  int a_mn0;         // first row of the A operand (coordinate along A's M dimension)
+  int b_mn0;         // first row of the B operand (coordinate along B's N dimension)
+  int k0;            // first contraction index
+  int num_kb;        // number of 64-wide contraction blocks
+  int batch;         // third tensor-map coordinate (expert / batch index) when a map is 3-D
+};
+
+// Operand layouts. K-major: the contraction index is contiguous in memory (x[M,K] row-major, W[N,K]
+// row-major). MN-major: the M (or N) index is contiguous, i.e. the operand is stored transposed
+// ([K, M] row-major); this is what dgrad (B = W[N,K] contracted over N) and wgrad (both operands contracted
+// over the token dimension) need, so no transposed copies are ever made.
+template <bool A_MN_ = false, bool B_MN_ = false, bool A_3D_ = false, bool B_3D_ = false>
+struct GemmTraits {
+  static constexpr bool A_MN = A_MN_, B_MN = B_MN_, A_3D = A_3D_, B_3D = B_3D_;
+};
+
 // Default schedule: grouped raster over (m, n) tiles, strided over the grid.
 struct RasterSchedule {
-  int num_m, num_n, total;
+  int num_m, num_n, total, num_kb;
   template <class P>
-  __device__ __forceinline__ void init(int M, int N, int BN, const P&) {
+  __device__ __forceinline__ void init(int M, int N, int K, int BN, const P&) {
     num_m = (M + GEMM_BM - 1) / GEMM_BM;
     num_n = (N + BN - 1) / BN;
     total = num_m * num_n;
+    num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+    bn = BN;
   }
-  __device__ __forceinline__ bool get(int it, int& m_blk, int& n_blk) const {
-    int t = blockIdx.x + it * gridDim.x;
-    if (t >= total) return false;
+  int bn;
+  __device__ __forceinline__ bool get(int it, TileInfo& t) const {
+    int i = blockIdx.x + it * gridDim.x;
+    if (i >= total) return false;
     constexpr int G = 8;
     int group_size = G * num_n;
-    int group = t / group_size;
+    int group = i / group_size;
     int first_m = group * G;
     int gsz = min(num_m - first_m, G);
-    int r = t - group * group_size;
-    m_blk = first_m + r % gsz;
-    n_blk = r / gsz;
+    int r = i - group * group_size;
+    t.m_blk = first_m + r % gsz;
+    t.n_blk = r / gsz;
+    t.a_mn0 = t.m_blk * GEMM_BM;
+    t.b_mn0 = t.n_blk * bn;
+    t.k0 = 0;
+    t.num_kb = num_kb;
+    t.batch = 0;
     return true;
   }
 };
 
 // Epilogue concept:
 //   struct Epi { struct Params {...};
-//     __device__ void tile_begin(const Params&, int m_blk, int n_blk, int row /*0..127*/);
-//     __device__ void chunk(const Params&, int m_blk, int n_blk, int row, int col0 /*within tile*/, const float (&v)[32]);
-//     __device__ void tile_end(const Params&, int m_blk, int n_blk, int row);
+//     __device__ void tile_begin(const Params&, const TileInfo&, int row /*0..127*/);
+//     __device__ void chunk(const Params&, const TileInfo&, int row, int col0 /*within tile*/, const float (&v)[32]);
+//     __device__ void tile_end(const Params&, const TileInfo&, int row);
 //     __device__ void finish(const Params&);   // after the last tile
 //   };
 
-template <int BN, int STAGES, class Epi, class Sched>
+template <int BN, int STAGES, class Epi, class Sched, class Traits = GemmTraits<>>
 __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUtensorMap* tmB, int M, int N, int K,
                                               const typename Epi::Params& ep, uint32_t* status) {
   using SM = GemmSmem<BN, STAGES>;
@@ -105,16 +132,15 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
   const uint32_t tmem_base = *tmem_slot;
 
   Sched sched;
-  sched.init(M, N, BN, ep);
-  const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+  sched.init(M, N, K, BN, ep);
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
-      int m_blk, n_blk;
-      for (int it = 0; sched.get(it, m_blk, n_blk) && !*abort_flag; ++it) {
-        for (int kb = 0; kb < num_kb; ++kb) {
+      TileInfo t;
+      for (int it = 0; sched.get(it, t) && !*abort_flag; ++it) {
+        for (int kb = 0; kb < t.num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
             atomicCAS(status, ST_OK, ST_TIMEOUT_EMPTY);
             *abort_flag = 1;
@@ -122,9 +148,28 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
           }
           uint8_t* sa = smem + stage * SM::STAGE_BYTES;
           uint8_t* sb = sa + SM::A_BYTES;
+          const int k = t.k0 + kb * GEMM_BK;
           mbar_arrive_expect_tx(&full_bar[stage], SM::STAGE_BYTES);
-          tma_load_2d(sa, tmA, &full_bar[stage], kb * GEMM_BK, m_blk * GEMM_BM);
-          tma_load_2d(sb, tmB, &full_bar[stage], kb * GEMM_BK, n_blk * BN);
+          if constexpr (!Traits::A_MN) {
+            if constexpr (Traits::A_3D) tma_load_3d(sa, tmA, &full_bar[stage], k, t.a_mn0, t.batch);
+            else tma_load_2d(sa, tmA, &full_bar[stage], k, t.a_mn0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < GEMM_BM / 64; ++i) {
+              if constexpr (Traits::A_3D) tma_load_3d(sa + i * 8192, tmA, &full_bar[stage], t.a_mn0 + i * 64, k, t.batch);
+              else tma_load_2d(sa + i * 8192, tmA, &full_bar[stage], t.a_mn0 + i * 64, k);
+            }
+          }
+          if constexpr (!Traits::B_MN) {
+            if constexpr (Traits::B_3D) tma_load_3d(sb, tmB, &full_bar[stage], k, t.b_mn0, t.batch);
+            else tma_load_2d(sb, tmB, &full_bar[stage], k, t.b_mn0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i) {
+              if constexpr (Traits::B_3D) tma_load_3d(sb + i * 8192, tmB, &full_bar[stage], t.b_mn0 + i * 64, k, t.batch);
+              else tma_load_2d(sb + i * 8192, tmB, &full_bar[stage], t.b_mn0 + i * 64, k);
+            }
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -132,11 +177,12 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16_f32(GEMM_BM, BN);
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(GEMM_BM, BN) | (Traits::A_MN ? (1u << 15) : 0u) |
+                                 (Traits::B_MN ? (1u << 16) : 0u);
       uint32_t stage = 0, phase = 0;
       uint32_t acc = 0, acc_phase = 0;
-      int m_blk, n_blk;
-      for (int it = 0; sched.get(it, m_blk, n_blk) && !*abort_flag; ++it) {
+      TileInfo t;
+      for (int it = 0; sched.get(it, t) && !*abort_flag; ++it) {
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1)) {
           atomicCAS(status, ST_OK, ST_TIMEOUT_TMEM_EMPTY);
           *abort_flag = 1;
@@ -145,7 +191,7 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
         bool ok = true;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = 0; kb < t.num_kb; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase)) {
             atomicCAS(status, ST_OK, ST_TIMEOUT_FULL);
             *abort_flag = 1;
@@ -157,14 +203,19 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
           const uint32_t sb = sa + SM::A_BYTES;
 #pragma unroll
           for (int k = 0; k < GEMM_BK / 16; ++k) {
-            uint64_t ad = umma_desc_kmajor_sw128(sa + k * 32);
-            uint64_t bd = umma_desc_kmajor_sw128(sb + k * 32);
+            // K-major: 16 contraction elements = 32 bytes inside the 128-byte swizzle row.
+            // MN-major: 16 contraction rows of 128 bytes = 2048 bytes.
+            uint64_t ad = Traits::A_MN ? umma_desc_mnmajor_sw128(sa + k * 2048, 8192) : umma_desc_kmajor_sw128(sa + k * 32);
+            uint64_t bd = Traits::B_MN ? umma_desc_mnmajor_sw128(sb + k * 2048, 8192) : umma_desc_kmajor_sw128(sb + k * 32);
             umma_bf16_ss(tmem_d, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           tc_commit(&empty_bar[stage]);  // frees this smem stage once the MMAs retire
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
+        if (t.num_kb == 0) {
+          // nothing to contract: the epilogue of this tile reads zeros it must not rely on; signal anyway
+        }
         tc_commit(&tfull_bar[acc]);  // accumulator complete
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
@@ -175,15 +226,15 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
     const int row = quad * 32 + lane;
     Epi epi;
     uint32_t acc = 0, acc_phase = 0;
-    int m_blk, n_blk;
-    for (int it = 0; sched.get(it, m_blk, n_blk) && !*abort_flag; ++it) {
+    TileInfo t;
+    for (int it = 0; sched.get(it, t) && !*abort_flag; ++it) {
       if (!mbar_wait(&tfull_bar[acc], acc_phase)) {
         atomicCAS(status, ST_OK, ST_TIMEOUT_TMEM_FULL);
         *abort_flag = 1;
         break;
       }
       tc_fence_after_sync();
-      epi.tile_begin(ep, m_blk, n_blk, row);
+      epi.tile_begin(ep, t, row);
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
@@ -192,10 +243,10 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
         tmem_ld_wait();
         float v[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-        epi.chunk(ep, m_blk, n_blk, row, c, v);
+        for (int i = 0; i < 32; ++i) v[i] = (t.num_kb > 0) ? __uint_as_float(r[i]) : 0.f;
+        epi.chunk(ep, t, row, c, v);
       }
-      epi.tile_end(ep, m_blk, n_blk, row);
+      epi.tile_end(ep, t, row);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
@@ -236,6 +287,23 @@ inline PFN_encodeTiled get_encode_tiled() {
     fn = reinterpret_cast<PFN_encodeTiled>(p);
   }
   return fn;
+}
+
+// Generic tiled map over a row-major tensor [d2][rows][cols] (d2 = 1 for 2-D): box = box_rows x box_cols with the
+// 128-byte swizzle (box_cols * elem_bytes == 128). ld = elements between rows, ld2 = elements between slices.
+inline int make_tmap_3d(CUtensorMap* out, const void* ptr, uint64_t d2, uint64_t rows, uint64_t cols, uint64_t ld,
+                        uint64_t ld2, uint32_t box_rows, uint32_t box_cols, int elem_bytes) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  if (!enc) return -1;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * elem_bytes) & 15) || ((ld2 * elem_bytes) & 15)) return -2;
+  cuuint64_t gdim[3] = {cols, rows, d2};
+  cuuint64_t gstr[2] = {ld * (uint64_t)elem_bytes, ld2 * (uint64_t)elem_bytes};
+  cuuint32_t box[3] = {box_cols, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = enc(out, dt, 3, const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
 }
 
 // Row-major [rows, cols] matrix of 2-byte (or 1-byte) elements with leading dimension ld (elements);

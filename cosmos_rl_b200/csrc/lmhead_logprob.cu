@@ -38,7 +38,8 @@ struct LogprobEpilogue {
       *reinterpret_cast<float4*>(p.partial + (r * p.nsplit + cur_split) * 4) = o;
     }
   }
-  __device__ __forceinline__ void tile_begin(const Params& p, int m_blk, int n_blk, int row) {
+  __device__ __forceinline__ void tile_begin(const Params& p, const TileInfo& t, int row) {
+    const int m_blk = t.m_blk, n_blk = t.n_blk;
     int split = n_blk / p.tps;
     if (m_blk != cur_unit_m || split != cur_split) {
       flush(p, row);
@@ -49,9 +50,9 @@ struct LogprobEpilogue {
       label = r < p.T ? p.labels[r] : -1;
     }
   }
-  __device__ __forceinline__ void chunk(const Params& p, int m_blk, int n_blk, int row, int col0,
+  __device__ __forceinline__ void chunk(const Params& p, const TileInfo& t, int row, int col0,
                                         const float (&v)[32]) {
-    const int c = n_blk * LP_BN + col0;
+    const int c = t.n_blk * LP_BN + col0;
     if (c >= p.V) return;
     float x[32];
     float cmax = -INFINITY;
@@ -79,7 +80,7 @@ struct LogprobEpilogue {
         if (i == (int)off) z = x[i];
     }
   }
-  __device__ __forceinline__ void tile_end(const Params&, int, int, int) {}
+  __device__ __forceinline__ void tile_end(const Params&, const TileInfo&, int) {}
   __device__ __forceinline__ void finish(const Params& p) {
     const int quad = (threadIdx.x >> 5) & 3;
     flush(p, quad * 32 + (threadIdx.x & 31));
@@ -90,18 +91,24 @@ struct LogprobEpilogue {
 // vocabulary tiles of each. n_blk may run past the last real tile in the final split: those tiles read
 // zero-filled weights and the epilogue masks every column >= V.
 struct LogprobSched {
-  int num_m, tps, units;
-  __device__ __forceinline__ void init(int M, int, int, const LogprobEpilogue::Params& p) {
+  int num_m, tps, units, num_kb;
+  __device__ __forceinline__ void init(int M, int, int K, int, const LogprobEpilogue::Params& p) {
     num_m = (M + GEMM_BM - 1) / GEMM_BM;
     tps = p.tps;
     units = num_m * p.nsplit;
+    num_kb = (K + GEMM_BK - 1) / GEMM_BK;
   }
-  __device__ __forceinline__ bool get(int it, int& m_blk, int& n_blk) const {
+  __device__ __forceinline__ bool get(int it, TileInfo& t) const {
     int j = it / tps, i = it - j * tps;
     int u = blockIdx.x + j * gridDim.x;
     if (u >= units) return false;
-    m_blk = u % num_m;
-    n_blk = (u / num_m) * tps + i;
+    t.m_blk = u % num_m;
+    t.n_blk = (u / num_m) * tps + i;
+    t.a_mn0 = t.m_blk * GEMM_BM;
+    t.b_mn0 = t.n_blk * LP_BN;
+    t.k0 = 0;
+    t.num_kb = num_kb;
+    t.batch = 0;
     return true;
   }
 };
@@ -152,8 +159,8 @@ struct DlogitsEpilogue {
   };
   float lse_r, glp, gent, ent_r;
   long long label;
-  __device__ __forceinline__ void tile_begin(const Params& p, int m_blk, int, int row) {
-    long long r = (long long)m_blk * GEMM_BM + row;
+  __device__ __forceinline__ void tile_begin(const Params& p, const TileInfo& t, int row) {
+    long long r = (long long)t.m_blk * GEMM_BM + row;
     if (r < p.T) {
       lse_r = p.lse[r];
       glp = p.g_lp[r];
@@ -163,10 +170,10 @@ struct DlogitsEpilogue {
       if (label < 0) { glp = 0.f; }
     }
   }
-  __device__ __forceinline__ void chunk(const Params& p, int m_blk, int n_blk, int row, int col0,
+  __device__ __forceinline__ void chunk(const Params& p, const TileInfo& t, int row, int col0,
                                         const float (&v)[32]) {
-    const long long r = (long long)m_blk * GEMM_BM + row;
-    const int c = n_blk * LP_BN + col0;
+    const long long r = (long long)t.m_blk * GEMM_BM + row;
+    const int c = t.n_blk * LP_BN + col0;
     if (r >= p.T || c >= p.Vc) return;
     float o[32];
     const long long off = label - (long long)(p.v0 + c);
@@ -193,7 +200,7 @@ struct DlogitsEpilogue {
       for (int i = 0; i < 32 && c + i < p.Vc; ++i) dst[i] = __float2bfloat16(o[i]);
     }
   }
-  __device__ __forceinline__ void tile_end(const Params&, int, int, int) {}
+  __device__ __forceinline__ void tile_end(const Params&, const TileInfo&, int) {}
   __device__ __forceinline__ void finish(const Params&) {}
 };
 

@@ -179,7 +179,23 @@ __device__ __forceinline__ uint64_t umma_desc_kmajor_sw128(uint32_t smem_addr_by
   return d;
 }
 
-// Instruction descriptor for kind::f16 with bf16 A/B, fp32 accumulate, both operands K-major.
+// Descriptor for an MN-major operand tile (the M or N index is contiguous in memory): the tile is a set of
+// TMA boxes of 64 MN-elements (128 bytes, 128-byte swizzle) x R contraction rows. A swizzle atom is 8
+// contraction rows x 128 bytes; atoms follow each other along the contraction every 1024 bytes (SBO) and
+// along MN every `mn_block_bytes` (LBO = the size of one box). Stepping UMMA_K = 16 contraction rows is
+// done by adding 16 * 128 bytes to the start address.
+__device__ __forceinline__ uint64_t umma_desc_mnmajor_sw128(uint32_t smem_addr_bytes, uint32_t mn_block_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr_bytes & 0x3FFFF) >> 4);
+  d |= (uint64_t)((mn_block_bytes >> 4) & 0x3FFF) << 16;  // LBO
+  d |= (uint64_t)(1024 >> 4) << 32;                       // SBO
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::f16 with bf16 A/B, fp32 accumulate, both operands K-major
+// (bit 15 / bit 16 select MN-major A / B).
 __host__ __device__ constexpr uint32_t umma_idesc_bf16_f32(int M, int N) {
   return (1u << 4)                      // D format = F32
          | (1u << 7)                    // A format = BF16

@@ -216,6 +216,64 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
     return out
 
 
+def gemm(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = False,
+         out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, accumulate: bool = False) -> torch.Tensor:
+    """General tcgen05 GEMM ``C[M, N] (+)= A . B^T`` on row-major bf16 tensors.
+    ``a_mn``: ``a`` is stored ``[K, M]`` instead of ``[M, K]``; ``b_mn``: ``b`` is stored ``[K, N]`` instead of ``[N, K]``."""
+    assert a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.stride(-1) == 1 and b.stride(-1) == 1 and a.dim() == 2 and b.dim() == 2
+    K, M = (a.shape[0], a.shape[1]) if a_mn else (a.shape[1], a.shape[0])
+    Kb, N = (b.shape[0], b.shape[1]) if b_mn else (b.shape[1], b.shape[0])
+    assert K == Kb, (a.shape, b.shape, a_mn, b_mn)
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    st = native.status_word(a.device)
+    dev = a.device.index if a.device.index is not None else torch.cuda.current_device()
+    native.check(native.lib().b200_gemm_bf16(native.ptr(a), native.ptr(b), native.ptr(out), M, N, K, a.stride(0),
+                                             b.stride(0), out.stride(0), int(a_mn), int(b_mn),
+                                             1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0,
+                                             native.ptr(st), native.num_sms(dev), native.stream()), "gemm_bf16")
+    return out
+
+
+class _LinearTC(torch.autograd.Function):
+    """``y = x W^T (+ b)`` with forward, dgrad and wgrad on the tcgen05 GEMM. When ``W.grad`` already exists
+    the weight gradient is accumulated into it by the GEMM epilogue itself (no separate add pass)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        x2 = _c(x).view(-1, x.shape[-1])
+        y = gemm(x2, weight)
+        if bias is not None:
+            y += bias
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias = bias is not None
+        ctx.shape = x.shape
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = _c(dy).view(-1, weight.shape[0])
+        dx = gemm(dy2, weight, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            if weight.grad is not None and weight.grad.dtype in (torch.bfloat16, torch.float32):
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=weight.grad, accumulate=True)
+                dw = None  # accumulated in place
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+        db = dy2.sum(0) if ctx.has_bias else None
+        return (dx.view(ctx.shape) if dx is not None else None), dw, db
+
+
+def linear_tc(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Linear layer on this library's GEMM (CUDA bf16); CPU tensors use ``torch.nn.functional.linear``."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _LinearTC.apply(x, weight, bias)
+    return torch.nn.functional.linear(x, weight, bias)
+
+
 # --------------------------------------------------------------------------------------------------
 # fused lm_head + log-prob + entropy
 # --------------------------------------------------------------------------------------------------

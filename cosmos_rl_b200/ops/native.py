@@ -50,6 +50,8 @@ class CopyDesc(ctypes.Structure):
 _SIGS = {
     "b200_gemm_bf16_nt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
                           c_int, c_int, c_void_p, c_int, c_void_p],
+    "b200_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
+                       c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "b200_lmhead_logprob_partial": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong,
                                     c_longlong, c_float, c_int, c_void_p, c_int, c_void_p],
     "b200_logprob_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],

@@ -52,7 +52,8 @@ class LLMTrainer(Trainer):
         dp = parallel_dims.dp_shard
         self.flat = FlatParams(model, self.param_dtype, self.device, shard_multiple=dp,
                                allocator=kw.get("allocator"))
-        model.gradient_checkpointing = bool(config.policy.model_gradient_checkpointing)
+        model.gradient_checkpointing = (config.b200.recompute if config.policy.model_gradient_checkpointing
+                                        else False)
         if tp > 1:
             from ...parallel.tp import TensorParallel
             model.tp = TensorParallel(parallel_dims.group("tp"), tp, parallel_dims.tp_coord)

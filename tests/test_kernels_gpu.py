@@ -248,3 +248,40 @@ def test_paged_decode_tensor_core(hq, hkv):
         native.read_status(q.device)
         err = (out.float().cpu() - ref.float()).abs().max().item()
         assert err < 3e-2, (nsplit, err)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(256, 512, 384), (300, 200, 520), (1024, 3584, 2048)])
+def test_gemm_operand_layouts(a_mn, b_mn, M, N, K):
+    """dgrad (B stored [K, N]) and wgrad (both stored [K, *]) forms against fp32 matmul."""
+    torch.manual_seed(11)
+    K8 = K
+    a = _bf16(K8, (M + 7) // 8 * 8)[:, :M] if a_mn else _bf16(M, K8)
+    b = _bf16(K8, (N + 7) // 8 * 8)[:, :N] if b_mn else _bf16(N, K8)
+    out = F.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    native.read_status(a.device)
+    af = a.float().t() if a_mn else a.float()
+    bf_ = b.float().t() if b_mn else b.float()
+    ref = af @ bf_.t()
+    assert torch.allclose(out.float(), ref, rtol=2e-2, atol=1e-2 * math.sqrt(K)), (out.float() - ref).abs().max()
+
+
+def test_linear_tc_matches_torch_linear():
+    torch.manual_seed(12)
+    x = _bf16(512, 1024).requires_grad_(True)
+    w = _bf16(768, 1024, scale=0.05).requires_grad_(True)
+    b = _bf16(768).requires_grad_(True)
+    y = F.linear_tc(x, w, b)
+    g = _bf16(512, 768)
+    y.backward(g)
+    native.read_status(x.device)
+    xr, wr, br = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(g.float())
+    assert torch.allclose(y.float(), yr, rtol=2e-2, atol=0.3)
+    assert torch.allclose(x.grad.float(), xr.grad, rtol=2e-2, atol=0.3)
+    assert torch.allclose(w.grad.float(), wr.grad, rtol=2e-2, atol=0.5)
+    # second backward accumulates into the existing .grad inside the GEMM epilogue
+    y2 = F.linear_tc(x.detach(), w, None)
+    y2.backward(g)
+    assert torch.allclose(w.grad.float(), 2 * wr.grad, rtol=3e-2, atol=1.0)
