@@ -42,6 +42,31 @@ int b200_lmhead_dlogits(const void* hidden, const void* weight, const long long*
                         int V, int H, long long ldh, long long ldw, int v0, int Vc, long long ldd,
                         float inv_temperature, uint32_t* status, int num_sms, cudaStream_t stream);
 
+// ---- mixture of experts ----------------------------------------------------------------------------------
+// Router: logits [T, E] fp32 -> softmax -> top-k (k <= 8, E <= 256) -> probs [T, k] (renormalised when renorm),
+// idx [T, k], and the per-expert histogram counts [E] (must be zeroed by the caller; may be null).
+int b200_moe_route_topk(const float* logits, int T, int E, int k, int renorm, float* probs, int* idx, int* counts,
+                        cudaStream_t stream);
+// counts [E] -> offsets [E+1] (every expert block padded to 128 rows), tile_expert [max_tiles], n_tiles [1];
+// cursor [E] is cleared for the permute kernel.
+int b200_moe_offsets(const int* counts, int E, int* offsets, int* tile_expert, int* n_tiles, int* cursor,
+                     int max_tiles, cudaStream_t stream);
+int b200_moe_permute(const void* x, const int* idx, const int* offsets, int* cursor, int* row_map, void* xp, int T,
+                     int k, int H, cudaStream_t stream);
+int b200_moe_scatter_scaled(const void* src, const float* probs, const int* row_map, void* dst, int T, int k, int H,
+                            cudaStream_t stream);
+int b200_moe_combine(const void* y, const float* probs, const int* row_map, void* out, int T, int k, int H,
+                     cudaStream_t stream);
+int b200_moe_combine_dprob(const void* dout, const void* y, const int* row_map, float* dprob, int T, int k, int H,
+                           cudaStream_t stream);
+// Grouped GEMMs over the padded, expert-sorted token buffer (see grouped_gemm.cu for the three forms).
+int b200_grouped_gemm(const void* X, const void* W, void* Y, int max_rows, int N, int K, int num_experts,
+                      long long ldx, long long ldy, const int* tile_expert, const int* n_tiles, int mode,
+                      int accumulate, uint32_t* status, int num_sms, cudaStream_t stream);
+int b200_grouped_wgrad(const void* dY, const void* X, void* dW, int max_rows, int N, int K, int num_experts,
+                       long long lddy, long long ldx, const int* expert_offsets, int out_fp32, int accumulate,
+                       uint32_t* status, int num_sms, cudaStream_t stream);
+
 // ---- normalisation / activation / rotary ------------------------------------------------------------
 int b200_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* residual_out, float* rstd,
                      int T, int H, float eps, cudaStream_t stream);

@@ -1,6 +1,7 @@
 """Model zoo. Importing this package registers every model family with :class:`ModelRegistry`."""
 from .base import BaseModel, ModelRegistry, WeightMapper  # noqa: F401
 from . import gpt  # noqa: F401
+from . import qwen3_moe  # noqa: F401
 
 
 def named_architectures():

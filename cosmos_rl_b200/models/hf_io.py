@@ -79,6 +79,7 @@ def load_hf_state(model, read, available, cfg: Dict[str, Any], tp: int = 1, r: i
     """Fill ``model`` (fused layout, TP rank ``r`` of ``tp``) from HF-named tensors served by ``read(name)``."""
     from .base import ModelRegistry
     mapper = ModelRegistry.mapper(cfg.get("model_type"))(cfg)
+    mapper.ep_rank = getattr(getattr(model, "args", None), "ep_rank", 0)
     missing = []
     with torch.no_grad():
         for name, p in model.named_parameters():

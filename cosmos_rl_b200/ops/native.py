@@ -80,6 +80,16 @@ _SIGS = {
                           c_void_p],
     "b200_paged_decode_tc": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                              c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
+    "b200_moe_route_topk": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "b200_moe_offsets": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "b200_moe_permute": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "b200_moe_scatter_scaled": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "b200_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "b200_moe_combine_dprob": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "b200_grouped_gemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p,
+                          c_void_p, c_int, c_int, c_void_p, c_int, c_void_p],
+    "b200_grouped_wgrad": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong,
+                           c_void_p, c_int, c_int, c_void_p, c_int, c_void_p],
     "b200_quant_fp8_block": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
     "b200_reshard_pull": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
 }

@@ -285,3 +285,42 @@ def test_linear_tc_matches_torch_linear():
     y2 = F.linear_tc(x.detach(), w, None)
     y2.backward(g)
     assert torch.allclose(w.grad.float(), 2 * wr.grad, rtol=3e-2, atol=1.0)
+
+
+def test_moe_router_topk():
+    from cosmos_rl_b200.ops import moe
+    torch.manual_seed(13)
+    T, E, k = 777, 128, 8
+    logits = torch.randn(T, E, device=DEV) * 2
+    counts = torch.zeros(E, dtype=torch.int32, device=DEV)
+    p, i = moe.route_topk(logits, k, True, counts)
+    pr, ir = moe.route_topk_reference(logits, k, True)
+    assert torch.equal(i.long().sort(-1).values, ir.long().sort(-1).values)
+    assert torch.allclose(p.sort(-1).values, pr.sort(-1).values, rtol=1e-4, atol=1e-6)
+    assert torch.equal(counts.long(), torch.bincount(ir.flatten().long(), minlength=E))
+
+
+@pytest.mark.parametrize("T,H,I,E,k", [(300, 256, 128, 8, 2), (1024, 2048, 768, 16, 8), (64, 512, 256, 32, 4)])
+def test_moe_experts_fwd_bwd(T, H, I, E, k):
+    from cosmos_rl_b200.ops import moe
+    torch.manual_seed(14)
+    x = _bf16(T, H).requires_grad_(True)
+    wgu = _bf16(E, 2 * I, H, scale=0.05).requires_grad_(True)
+    wd = _bf16(E, H, I, scale=0.05).requires_grad_(True)
+    logits = torch.randn(T, E, device=DEV)
+    probs, idx = moe.route_topk(logits, k, True)
+    probs = probs.clone().requires_grad_(True)
+    out = moe.moe_experts(x, probs, idx, wgu, wd)
+    native.read_status(x.device)
+    xr, pr, wgur, wdr = (t.detach().float().requires_grad_(True) for t in (x, probs, wgu, wd))
+    ref = moe.moe_experts_reference(xr, pr, idx, wgur, wdr)
+    scale = ref.abs().max().item()
+    assert torch.allclose(out.float(), ref, rtol=3e-2, atol=3e-2 * scale), (out.float() - ref).abs().max()
+    g = _bf16(T, H)
+    out.backward(g)
+    native.read_status(x.device)
+    ref.backward(g.float())
+    for name, a, b in (("dx", x.grad, xr.grad), ("dprob", probs.grad, pr.grad), ("dwgu", wgu.grad, wgur.grad),
+                       ("dwd", wd.grad, wdr.grad)):
+        s = b.abs().max().item()
+        assert torch.allclose(a.float(), b, rtol=5e-2, atol=5e-2 * s), (name, (a.float() - b).abs().max().item(), s)

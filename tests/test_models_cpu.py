@@ -1,0 +1,159 @@
+"""Model-level checks on CPU: packed forward vs per-sequence forward, recompute modes, generation engine vs
+teacher forcing, HF safetensors export / reload (dense and MoE), training checkpoint save / resume, MoE
+weight-sync parts."""
+import json
+import os
+
+import pytest
+import torch
+
+from cosmos_rl_b200.config import Config
+from cosmos_rl_b200.dispatcher.data.schema import Rollout
+from cosmos_rl_b200.models import hf_io, named_architectures
+from cosmos_rl_b200.models.gpt import ARCHS, GPT
+from cosmos_rl_b200.models.qwen3_moe import ARCHS as MOE_ARCHS
+from cosmos_rl_b200.models.qwen3_moe import Qwen3MoE
+from cosmos_rl_b200.parallel.dims import ParallelDims
+from cosmos_rl_b200.parallel.flat import FlatParams
+from cosmos_rl_b200.parallel.reshard import build_plan, model_parts, shard_info
+from cosmos_rl_b200.policy.trainer.grpo_trainer import GRPOTrainer
+from cosmos_rl_b200.rollout.engine import RolloutEngine, SamplingParams
+
+
+def _tiny(kind="dense"):
+    torch.manual_seed(0)
+    m = GPT(ARCHS["tiny-qwen2"]) if kind == "dense" else Qwen3MoE(MOE_ARCHS["tiny-qwen3-moe"])
+    m.init_weights(0)
+    return m
+
+
+@pytest.mark.parametrize("kind", ["dense", "moe"])
+def test_packed_forward_equals_per_sequence(kind):
+    m = _tiny(kind)
+    a, b = torch.randint(0, 32000, (9,)), torch.randint(0, 32000, (14,))
+    ids = torch.cat([a, b])
+    cu = torch.tensor([0, 9, 23])
+    with torch.no_grad():
+        packed = m(ids, m.get_position_ids(cu, 23), cu, 14)
+        ha = m(a, torch.arange(9), torch.tensor([0, 9]), 9)
+        hb = m(b, torch.arange(14), torch.tensor([0, 14]), 14)
+    assert torch.allclose(packed, torch.cat([ha, hb]), atol=1e-5)
+
+
+def test_recompute_modes_give_identical_gradients():
+    m = _tiny()
+    ids, cu = torch.randint(0, 32000, (20,)), torch.tensor([0, 8, 20])
+    lab = torch.randint(0, 32000, (20,))
+    grads = {}
+    for mode in (False, "full", "selective"):
+        m.gradient_checkpointing = mode
+        m.zero_grad()
+        lp, _ = m.logprobs(m(ids, m.get_position_ids(cu, 20), cu, 12), lab)
+        lp.sum().backward()
+        grads[mode] = torch.cat([p.grad.flatten() for p in m.parameters()])
+    assert torch.equal(grads[False], grads["full"]) and torch.equal(grads[False], grads["selective"])
+
+
+@pytest.mark.parametrize("kind", ["dense", "moe"])
+def test_engine_greedy_matches_teacher_forcing_and_frees_pages(kind):
+    m = _tiny(kind)
+    e = RolloutEngine(m, max_num_seqs=8, max_model_len=64, page_size=16)
+    prompts = [torch.randint(0, 32000, (10 + 3 * i,)).tolist() for i in range(4)]
+    out = e.generate(prompts, SamplingParams(n=2, max_tokens=10, temperature=0.0))
+    assert len(e.free_pages) == e.num_pages - 1
+    for p, comps in zip(prompts, out):
+        assert comps[0].token_ids == comps[1].token_ids            # greedy samples of one prompt agree
+        ids = torch.tensor(p + comps[0].token_ids)
+        with torch.no_grad():
+            h = m(ids, torch.arange(len(ids)), torch.tensor([0, len(ids)]), len(ids))
+            lsm = torch.log_softmax(m.logits(h).float(), -1)
+        for i, (tok, lp) in enumerate(zip(comps[0].token_ids, comps[0].logprobs)):
+            row = lsm[len(p) - 1 + i]
+            assert int(row.argmax()) == tok and abs(row[tok].item() - lp) < 1e-3
+
+
+def test_engine_stop_tokens_and_more_prompts_than_slots():
+    m = _tiny()
+    e = RolloutEngine(m, max_num_seqs=4, max_model_len=64, page_size=16)
+    prompts = [torch.randint(0, 32000, (8,)).tolist() for _ in range(6)]     # 6 prompts x 2 samples > 4 slots
+    ref = e.generate(prompts, SamplingParams(n=2, max_tokens=8, temperature=0.0))
+    stop = ref[0][0].token_ids[3]
+    out = e.generate(prompts, SamplingParams(n=2, max_tokens=8, temperature=0.0, stop_token_ids=(stop,)))
+    first = out[0][0]
+    assert first.finish_reason == "stop" and first.token_ids[-1] == stop and len(first.token_ids) <= 4
+    assert all(len(c.token_ids) <= 8 for r in out for c in r)
+    assert len(e.free_pages) == e.num_pages - 1
+
+
+@pytest.mark.parametrize("kind", ["dense", "moe"])
+def test_safetensors_export_and_reload(kind, tmp_path):
+    m = _tiny(kind)
+    cfg = m.args.to_hf_config()
+    out = str(tmp_path / "export")
+    hf_io.export_safetensors(m, cfg, out)
+    index = json.load(open(os.path.join(out, "model.safetensors.index.json")))
+    assert "model.layers.0.self_attn.q_proj.weight" in index["weight_map"]
+    if kind == "moe":
+        assert "model.layers.1.mlp.experts.7.down_proj.weight" in index["weight_map"]
+    else:
+        assert "model.layers.0.mlp.gate_proj.weight" in index["weight_map"]
+    assert hf_io.load_hf_config(out)["hidden_size"] == m.args.dim
+    m2 = type(m)(m.args)
+    hf_io.load_hf_weights(m2, out)
+    for (n1, p1), (n2, p2) in zip(m.named_parameters(), m2.named_parameters()):
+        assert torch.equal(p1, p2), n1
+
+
+def test_checkpoint_save_resume_and_prune(tmp_path):
+    d = {"policy": {"model_name_or_path": "tiny-qwen2", "parallelism": {"tp_size": 1}, "model_max_length": 64},
+         "train": {"optm_lr": 1e-3, "seed": 0, "output_dir": str(tmp_path), "resume": True,
+                   "ckpt": {"enable_checkpoint": True, "save_mode": "sync", "max_keep": 2, "export_safetensors": False},
+                   "train_policy": {"type": "grpo", "mini_batch": 4}}}
+    cfg = Config.from_dict(d)
+    t = GRPOTrainer(cfg, ParallelDims(world_size=1))
+    assert t.weight_resume() is False
+    rs = [Rollout(prompt=[1, 2, 3, 4], completion=[5, 6, 7], advantage=float(i) - 1.5, reward=0.0) for i in range(4)]
+    for step in (1, 2, 3):
+        t.step_training(rs, step, 10, do_save=True)
+    assert t.ckpt_manager.steps_on_disk() == [2, 3]                 # max_keep pruned step 1
+    w = t.flat.data.clone()
+    m_state = t.optimizer.m.clone()
+    t2 = GRPOTrainer(cfg, ParallelDims(world_size=1))
+    assert t2.weight_resume() is True
+    assert t2.train_step == 3 and torch.equal(t2.flat.data, w) and torch.equal(t2.optimizer.m, m_state)
+    assert t2.optimizer.step_count == t.optimizer.step_count
+    # an incomplete step directory (no completion marker) is ignored by resume
+    os.makedirs(os.path.join(str(tmp_path), "checkpoints", "step_9", "policy"))
+    assert t2.ckpt_manager.latest_valid_step() == 3
+    # both trainers continue identically
+    r1 = t.step_training(rs, 4, 10)
+    r2 = t2.step_training(rs, 4, 10)
+    assert abs(r1["train/grad_norm"] - r2["train/grad_norm"]) < 1e-5 and torch.allclose(t.flat.data, t2.flat.data)
+
+
+def test_moe_weight_sync_parts_cover_every_parameter():
+    m = _tiny("moe")
+    with torch.device("meta"):
+        dst = Qwen3MoE(MOE_ARCHS["tiny-qwen3-moe"])
+    src_flat = FlatParams(m, torch.float32, torch.device("cpu"), with_grad=False)
+    dst_flat = FlatParams(dst, torch.float32, torch.device("cpu"), with_grad=False)
+    plan = build_plan([shard_info(0, model_parts(m, src_flat), src_flat.total)],
+                      shard_info(0, model_parts(dst, dst_flat), dst_flat.total))
+    for _, so, sld, do, dld, rows, cols in plan:
+        torch.as_strided(dst_flat.data, (rows, cols), (dld, 1), do).copy_(
+            torch.as_strided(src_flat.data, (rows, cols), (sld, 1), so))
+    for (n1, p1), (n2, p2) in zip(m.named_parameters(), dst.named_parameters()):
+        assert torch.equal(p1, p2), n1
+
+
+def test_named_architectures_shapes():
+    archs = named_architectures()
+    a = archs["qwen2.5-7b"]
+    assert (a.dim, a.n_layers, a.n_heads, a.n_kv_heads, a.ffn_dim, a.vocab_size) == (3584, 28, 28, 4, 18944, 152064)
+    b = archs["qwen3-30b-a3b"]
+    assert (b.dim, b.n_layers, b.n_experts, b.top_k, b.moe_ffn_dim) == (2048, 48, 128, 8, 768)
+    c = archs["qwen3-32b"]
+    assert (c.dim, c.n_layers, c.n_heads, c.n_kv_heads, c.ffn_dim) == (5120, 64, 64, 8, 25600)
+    with torch.device("meta"):
+        n = sum(p.numel() for p in GPT(a).parameters())
+    assert 7.5e9 < n < 7.7e9
