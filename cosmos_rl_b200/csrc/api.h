@@ -72,6 +72,8 @@ int b200_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y
                      int T, int H, float eps, cudaStream_t stream);
 int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
                      float* dw_partial, int n_partial, int T, int H, cudaStream_t stream);
+int b200_rmsnorm_bwd2(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                      float* dw_accum, long long T, int H, cudaStream_t stream);
 int b200_colsum_f32(const float* partial, float* out, int rows, int cols, int accumulate, cudaStream_t stream);
 int b200_rope_inplace(void* q, void* k, const long long* positions, int T, int hq, int hkv, int d, long long q_stride,
                       long long k_stride, float theta, int backward, cudaStream_t stream);

@@ -178,6 +178,143 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
+// ---- RMSNorm backward, split in two bandwidth-shaped kernels ---------------------------------------------
+// dx: fully parallel over rows (one CTA per row for wide rows, one warp per row for narrow rows such as the
+// per-head q/k norms), no weight-gradient state in registers. dw: column strips, each warp streams a strip of
+// rows for 256 columns and the strips meet in one fp32 atomicAdd per column.
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_dx_row_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                      const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                      const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx, int H) {
+  __shared__ float sh[32];
+  const long long row = blockIdx.x;
+  const int nvec = H >> 3;
+  const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * H);
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  const float rs = rstd[row];
+  float xh[NORM_MAXV][8], dxh[NORM_MAXV][8];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    int v = threadIdx.x + i * NORM_THREADS;
+    if (v < nvec) {
+      float a[8], b[8], g[8];
+      unpack8(dyr[v], a);
+      unpack8(xr[v], b);
+      unpack8(wr[v], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        xh[i][j] = b[j] * rs;
+        dxh[i][j] = a[j] * g[j];
+        dot += dxh[i][j] * xh[i][j];
+      }
+    }
+  }
+  dot = block_sum<NORM_THREADS>(dot, sh) / (float)H;
+  uint4* dxr = reinterpret_cast<uint4*>(dx + row * H);
+  const uint4* drr = dres ? reinterpret_cast<const uint4*>(dres + row * H) : nullptr;
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    int v = threadIdx.x + i * NORM_THREADS;
+    if (v < nvec) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rs * (dxh[i][j] - xh[i][j] * dot);
+      if (drr) {
+        float r[8];
+        unpack8(drr[v], r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += r[j];
+      }
+      dxr[v] = pack8(o);
+    }
+  }
+}
+
+// narrow rows (H <= 1024, H % 8 == 0): one warp per row, up to 4 vectors per lane
+__global__ void __launch_bounds__(256)
+rmsnorm_dx_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                       const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                       const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx, long long T, int H) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= T) return;
+  const int lane = threadIdx.x & 31, nvec = H >> 3;
+  const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * H);
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  const float rs = rstd[row];
+  float xh[4][8], dxh[4][8];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int v = lane + 32 * i;
+    if (v < nvec) {
+      float a[8], b[8], g[8];
+      unpack8(dyr[v], a);
+      unpack8(xr[v], b);
+      unpack8(wr[v], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        xh[i][j] = b[j] * rs;
+        dxh[i][j] = a[j] * g[j];
+        dot += dxh[i][j] * xh[i][j];
+      }
+    }
+  }
+  dot = warp_sum(dot) / (float)H;
+  uint4* dxr = reinterpret_cast<uint4*>(dx + row * H);
+  const uint4* drr = dres ? reinterpret_cast<const uint4*>(dres + row * H) : nullptr;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int v = lane + 32 * i;
+    if (v < nvec) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rs * (dxh[i][j] - xh[i][j] * dot);
+      if (drr) {
+        float r[8];
+        unpack8(drr[v], r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += r[j];
+      }
+      dxr[v] = pack8(o);
+    }
+  }
+}
+
+// dw[c] += sum_t dy[t,c] * x[t,c] * rstd[t]; grid (ceil(H/256), row strips), 8 warps per CTA split the strip
+__global__ void __launch_bounds__(256)
+rmsnorm_dw_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                  const float* __restrict__ rstd, float* __restrict__ dw, long long T, int H) {
+  __shared__ float sh[8][256];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c0 = blockIdx.x * 256 + lane * 8;
+  const long long rows_per_cta = (T + gridDim.y - 1) / gridDim.y;
+  const long long r0 = blockIdx.y * rows_per_cta, r1 = min(T, r0 + rows_per_cta);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (c0 < H) {
+    for (long long r = r0 + warp; r < r1; r += 8) {
+      float a[8], b[8];
+      unpack8(*reinterpret_cast<const uint4*>(dy + r * H + c0), a);
+      unpack8(*reinterpret_cast<const uint4*>(x + r * H + c0), b);
+      const float rs = rstd[r];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += a[j] * b[j] * rs;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sh[warp][lane * 8 + j] = acc[j];
+  __syncthreads();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < H) {
+    float s = 0.f;
+#pragma unroll
+    for (int wv = 0; wv < 8; ++wv) s += sh[wv][threadIdx.x];
+    atomicAdd(&dw[c], s);
+  }
+}
+
 __global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ out, int rows, int cols,
                               int accumulate) {
   int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -376,6 +513,31 @@ int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* 
   rmsnorm_bwd_kernel<<<n_partial, NORM_THREADS, 0, stream>>>(
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
       (__nv_bfloat16*)dx, dw_partial, T, H);
+  return ok();
+}
+
+// dx (+ dres) and dw (fp32, ACCUMULATED into dw_accum, which the caller zeroes or reuses across micro-batches)
+int b200_rmsnorm_bwd2(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                      float* dw_accum, long long T, int H, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((H & 7) || H > NORM_THREADS * 8 * NORM_MAXV) return B200_ERR_ARG;
+  if (H <= 1024)
+    rmsnorm_dx_warp_kernel<<<(unsigned)((T + 7) / 8), 256, 0, stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
+        (__nv_bfloat16*)dx, T, H);
+  else
+    rmsnorm_dx_row_kernel<<<(unsigned)T, NORM_THREADS, 0, stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
+        (__nv_bfloat16*)dx, H);
+  if (dw_accum) {
+    const int col_blocks = (H + 255) / 256;
+    long long strips = (148 * 8 + col_blocks - 1) / col_blocks;
+    if (strips > (T + 63) / 64) strips = (T + 63) / 64;
+    if (strips < 1) strips = 1;
+    dim3 grid(col_blocks, (unsigned)strips);
+    rmsnorm_dw_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, rstd, dw_accum, T,
+                                                H);
+  }
   return ok();
 }
 

@@ -56,14 +56,10 @@ class _RMSNorm(torch.autograd.Function):
         dy2 = _c(dy).view(-1, H)
         dres2 = _c(dres_out).view(-1, H) if dres_out is not None else None
         dx = torch.empty_like(h)
-        n_partial = min(_N_PARTIAL_NORM, max(T, 1))
-        dwp = torch.empty(n_partial, H, dtype=torch.float32, device=h.device)
-        L = native.lib()
-        native.check(L.b200_rmsnorm_bwd(native.ptr(dy2), native.ptr(h), native.ptr(weight), native.ptr(rstd),
-                                        native.ptr(dres2), native.ptr(dx), native.ptr(dwp), n_partial, T, H,
-                                        native.stream()), "rmsnorm_bwd")
-        dw = torch.empty(H, dtype=torch.float32, device=h.device)
-        native.check(L.b200_colsum_f32(native.ptr(dwp), native.ptr(dw), n_partial, H, 0, native.stream()), "colsum")
+        dw = torch.zeros(H, dtype=torch.float32, device=h.device)
+        native.check(native.lib().b200_rmsnorm_bwd2(native.ptr(dy2), native.ptr(h), native.ptr(weight),
+                                                    native.ptr(rstd), native.ptr(dres2), native.ptr(dx),
+                                                    native.ptr(dw), T, H, native.stream()), "rmsnorm_bwd")
         dxv = dx.view(ctx.shape)
         return dxv, dw.to(weight.dtype), None, (dxv if ctx.has_res else None)
 
@@ -93,10 +89,12 @@ def _rope_native(q, k, positions, theta, backward):
 
 
 class _RoPE(torch.autograd.Function):
+    """Out-of-place on separate q / k tensors (the fused-qkv form below rotates in place)."""
+
     @staticmethod
     def forward(ctx, q, k, positions, theta):
+        q, k = q.clone(memory_format=torch.contiguous_format), k.clone(memory_format=torch.contiguous_format)
         _rope_native(q, k, positions, theta, False)
-        ctx.mark_dirty(q, k)
         ctx.save_for_backward(positions)
         ctx.theta = theta
         return q, k
@@ -104,15 +102,14 @@ class _RoPE(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dq, dk):
         (positions,) = ctx.saved_tensors
-        dq = dq.contiguous() if not (dq.stride(-1) == 1 and dq.stride(1) == dq.shape[-1]) else dq.clone()
-        dk = dk.contiguous() if not (dk.stride(-1) == 1 and dk.stride(1) == dk.shape[-1]) else dk.clone()
+        dq, dk = dq.clone(memory_format=torch.contiguous_format), dk.clone(memory_format=torch.contiguous_format)
         _rope_native(dq, dk, positions, ctx.theta, True)
         return dq, dk, None, None
 
 
 def apply_rope(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, theta: float):
-    """Rotary embedding of ``q [T, hq, d]`` and ``k [T, hkv, d]``. On CUDA the rotation is done in place
-    (the inputs must not be needed un-rotated afterwards) and positions must be int64."""
+    """Rotary embedding of ``q [T, hq, d]`` and ``k [T, hkv, d]`` (int64 positions on CUDA). With autograd the
+    result is a new pair of tensors; without, the rotation is done in place."""
     if q.is_cuda:
         positions = positions.to(torch.int64)
         if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad):

@@ -61,6 +61,8 @@ _SIGS = {
     "b200_rmsnorm_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
     "b200_rmsnorm_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                          c_void_p],
+    "b200_rmsnorm_bwd2": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int,
+                          c_void_p],
     "b200_colsum_f32": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "b200_rope_inplace": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_float,
                           c_int, c_void_p],

@@ -324,3 +324,21 @@ def test_moe_experts_fwd_bwd(T, H, I, E, k):
                        ("dwd", wd.grad, wdr.grad)):
         s = b.abs().max().item()
         assert torch.allclose(a.float(), b, rtol=5e-2, atol=5e-2 * s), (name, (a.float() - b).abs().max().item(), s)
+
+
+def test_rope_separate_qk_autograd_on_views():
+    """q / k that are views of another tensor (the per-head-norm path of Qwen3) must work under autograd."""
+    torch.manual_seed(15)
+    T, hq, hkv, d = 40, 4, 2, 128
+    qb = _bf16(T * hq, d).requires_grad_(True)
+    kb = _bf16(T * hkv, d).requires_grad_(True)
+    pos = torch.randint(0, 3000, (T,), device=DEV)
+    q, k = F.apply_rope((qb * 1.0).view(T, hq, d), (kb * 1.0).view(T, hkv, d), pos, 1e6)
+    qr = qb.detach().float().cpu().requires_grad_(True)
+    kr = kb.detach().float().cpu().requires_grad_(True)
+    qe, ke = R.apply_rope(qr.view(T, hq, d), kr.view(T, hkv, d), pos.cpu(), 1e6)
+    assert torch.allclose(q.float().cpu(), qe, rtol=2e-2, atol=2e-2)
+    (q.float().sum() + 2 * k.float().sum()).backward()
+    (qe.sum() + 2 * ke.sum()).backward()
+    assert torch.allclose(qb.grad.float().cpu(), qr.grad, rtol=2e-2, atol=2e-2)
+    assert torch.allclose(kb.grad.float().cpu(), kr.grad, rtol=2e-2, atol=2e-2)
