@@ -1,0 +1,179 @@
+"""CPU tests of the auxiliary components: colocated worker, teacher worker, asynchronous weight sync,
+LoRA, EMA, trace lines, activation offloading."""
+import os
+import time
+
+import pytest
+import torch
+import torch.nn as nn
+
+from cosmos_rl_b200.comm.broker import InProcessBroker
+from cosmos_rl_b200.config import Config, load_toml
+from cosmos_rl_b200.dispatcher.data import SyntheticTokenDataset
+
+CFG = os.path.join(os.path.dirname(__file__), "configs", "tiny_grpo_cpu.toml")
+
+
+def _config(tmp_path, **over):
+    c = Config.from_dict(load_toml(CFG))
+    c.train.output_dir = str(tmp_path)
+    c.train.train_batch_per_replica = 16
+    c.rollout.batch_size = 4
+    c.rollout.max_response_length = 12
+    for k, v in over.items():
+        setattr(c, k, v)
+    return c
+
+
+def test_colocated_worker_trains_to_completion(tmp_path):
+    from cosmos_rl_b200.colocated.worker import ColocatedRLControlWorker
+    from cosmos_rl_b200.dispatcher.algo.reward import even_token_fraction
+    c = _config(tmp_path)
+    c.mode = "colocated"
+    w = ColocatedRLControlWorker(c, SyntheticTokenDataset(8, 12, 32000), reward_fns=[even_token_fraction],
+                                 device=torch.device("cpu"))
+    reports = w.run(max_iterations=200)
+    assert len(reports) == 2                      # 8 prompts x 4 samples / 16 per step
+    assert all("train/loss_avg" in r or any(k.startswith("train/") for k in r) for r in reports)
+    assert w.controller.finalized.is_set()
+
+
+def test_teacher_worker_scores_requests(tmp_path):
+    from cosmos_rl_b200.reference.teacher_worker import (TeacherEngine, fetch_teacher_result,
+                                                         submit_teacher_request, teacher_key)
+    c = _config(tmp_path)
+    c.distillation.top_k = 3
+    eng = TeacherEngine(c, torch.device("cpu"))
+    seqs = [torch.randint(0, 32000, (n,)).tolist() for n in (9, 14)]
+    out = eng.score(seqs, [4, 6])
+    for s, n, o in zip(seqs, (4, 6), out):
+        assert len(o["logprobs"]) == len(s) - n
+        ids = torch.tensor(s)
+        with torch.no_grad():
+            h = eng.model(ids, torch.arange(len(s)), torch.tensor([0, len(s)]), len(s))
+            lsm = torch.log_softmax(eng.model.logits(h).float(), -1)
+        want = [lsm[i - 1, s[i]].item() for i in range(n, len(s))]
+        assert torch.allclose(torch.tensor(o["logprobs"]), torch.tensor(want), atol=1e-4)
+        assert len(o["topk_ids"]) == len(s) - n and len(o["topk_ids"][0]) == 3
+        assert o["topk_logprobs"][0][0] >= o["topk_logprobs"][0][1]
+    # request / result path through the broker, two teachers in one consumer group never share a request
+    import msgpack
+    from cosmos_rl_b200.comm.broker import TEACHER_REQUEST_STREAM
+    b = InProcessBroker()
+    uids = [submit_teacher_request(b, s, 4) for s in seqs]
+    first = b.read_group(TEACHER_REQUEST_STREAM, "teachers", 1, 0)
+    second = b.read_group(TEACHER_REQUEST_STREAM, "teachers", 4, 0)
+    assert len(first) == 1 and len(second) == 1 and first[0][0] != second[0][0]
+    for _, d in first + second:
+        r = msgpack.unpackb(d, raw=False)
+        b.kv_set(teacher_key(r["uuid"]), msgpack.packb(eng.score([r["ids"]], [r["n_prompt"]])[0]))
+    assert len(fetch_teacher_result(b, uids[1], 1.0)["logprobs"]) == 10
+    assert fetch_teacher_result(b, "missing", 0.05) is None
+
+
+def test_weight_sync_thread_adopts_newest_version_only():
+    from cosmos_rl_b200.rollout.weight_sync_thread import WeightSyncThread
+    live = torch.zeros(1000)
+    seen = []
+
+    def receive(buf, req):
+        time.sleep(0.02)
+        seen.append(req)
+        buf.fill_(float(req))
+
+    t = WeightSyncThread(live, receive)
+    try:
+        assert t.sync_buffer_to_live() == -1 and live.sum() == 0
+        for v in (1, 2, 3):
+            t.submit(v, v)
+        assert t.fence(5.0)
+        time.sleep(0.05)
+        assert t.sync_buffer_to_live() == 3 and torch.all(live == 3.0)
+        assert seen[-1] == 3 and len(seen) <= 3
+        assert t.sync_buffer_to_live() == 3       # idempotent
+
+        def bad(buf, req):
+            raise RuntimeError("receive failed")
+        t.receive_fn = bad
+        t.submit(4, 4)
+        t.ready.clear()
+        assert t.ready.wait(2.0)
+        with pytest.raises(RuntimeError):
+            t.sync_buffer_to_live()
+        assert torch.all(live == 3.0)
+    finally:
+        t.stop()
+
+
+def test_lora_inject_merge_unmerge_and_adapter_state():
+    from cosmos_rl_b200.config import LoraConfig
+    from cosmos_rl_b200.policy import lora
+
+    class M(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj, self.up_proj, self.other = nn.Linear(16, 16, bias=False), nn.Linear(16, 32), nn.Linear(16, 4)
+
+        def forward(self, x):
+            return self.up_proj(self.q_proj(x)).sum(-1, keepdim=True) + self.other(x)
+
+    torch.manual_seed(0)
+    m = M()
+    x = torch.randn(5, 16)
+    y0 = m(x)
+    cfg = LoraConfig(r=4, lora_alpha=8, target_modules=["q_proj", "up_proj"])
+    wrapped = lora.inject_lora(m, cfg)
+    assert sorted(wrapped) == ["q_proj", "up_proj"]
+    assert torch.allclose(m(x), y0, atol=1e-6)                       # B starts at zero
+    trainable = [n for n, p in m.named_parameters() if p.requires_grad]
+    assert trainable and all("lora_" in n for n in trainable)
+    for mod in lora.lora_modules(m):
+        nn.init.normal_(mod.lora_B, std=0.1)
+    y1 = m(x)
+    assert not torch.allclose(y1, y0)
+    lora.merge_lora(m)
+    assert torch.allclose(m(x), y1, atol=1e-5)
+    lora.unmerge_lora(m)
+    assert torch.allclose(m(x), y1, atol=1e-5)
+    sd = lora.adapter_state_dict(m)
+    assert len(sd) == 4 and all(k.endswith(".weight") for k in sd)
+    assert lora.adapter_config(cfg, wrapped)["r"] == 4
+
+
+def test_flat_ema_update_and_swap():
+    from cosmos_rl_b200.utils.ema import FlatEMA
+    w = torch.ones(10)
+    ema = FlatEMA(w, decay=0.5)
+    w.fill_(3.0)
+    ema.update()
+    assert torch.allclose(ema.shadow, torch.full((10,), 2.0))
+    with ema.swapped_in():
+        assert torch.all(w == 2.0)
+    assert torch.all(w == 3.0)
+    e2 = FlatEMA(torch.zeros(10), decay=0.5)
+    e2.load_state_dict(ema.state_dict())
+    assert torch.equal(e2.shadow, ema.shadow)
+
+
+def test_trace_lines_round_trip():
+    from cosmos_rl_b200.utils import trace
+    line = trace.format_line("policy-0", "main", "train_step", 10.0, 10.5, step=3)
+    recs = list(trace.parse_lines(["noise", line, line]))
+    assert len(recs) == 2 and recs[0]["op"] == "train_step" and recs[0]["step"] == "3"
+    s = trace.summarize(recs)
+    assert s["policy-0:train_step"]["count"] == 2 and abs(s["policy-0:train_step"]["total"] - 1.0) < 1e-9
+
+
+def test_activation_offload_keeps_gradients():
+    from cosmos_rl_b200.utils.activation_offloading import OffloadActivations
+    torch.manual_seed(0)
+    lin = nn.Sequential(nn.Linear(64, 64), nn.GELU(), nn.Linear(64, 64))
+    x = torch.randn(32, 64, requires_grad=True)
+    lin(x).pow(2).sum().backward()
+    g0 = [p.grad.clone() for p in lin.parameters()]
+    lin.zero_grad()
+    with OffloadActivations(min_bytes=0, use_pinned=False, params={id(p) for p in lin.parameters()}):
+        y = lin(x).pow(2).sum()
+    y.backward()
+    for a, p in zip(g0, lin.parameters()):
+        assert torch.allclose(a, p.grad)
