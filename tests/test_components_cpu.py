@@ -177,3 +177,40 @@ def test_activation_offload_keeps_gradients():
     y.backward()
     for a, p in zip(g0, lin.parameters()):
         assert torch.allclose(a, p.grad)
+
+
+def test_payload_transport_registry_prefetch_and_discard():
+    from cosmos_rl_b200.utils.payload_transport import (HealthSkipList, PayloadPrefetcher,
+                                                        PayloadTransportRegistry as R, get_payload_transfer_mode)
+    R.reset()
+    b = InProcessBroker()
+    kv = R.get("kv")
+    kv.setup(broker=b)
+    assert R.get("broker").publish("text") == "text" and R.active_for_completion("text") is None
+    payloads = [torch.arange(10) * i for i in range(4)]
+    refs = [kv.publish(p) for p in payloads]
+    assert all(r.startswith("kv://") for r in refs) and R.active_for_completion(refs[0]) is kv
+    pf = PayloadPrefetcher(kv)
+    try:
+        assert pf.prefetch(refs[:3] + ["inline"]) == 3
+        assert pf.drain(5.0)
+        time.sleep(0.05)
+        got = [pf.resolve(r) for r in refs]
+        assert all(torch.equal(g, p) for g, p in zip(got, payloads))
+        assert pf.hits == 3 and pf.misses == 1 and pf.failed == 0
+        assert pf.resolve("inline") == "inline"
+        assert R.handle_discarded([refs[0], "inline"]) == 1
+        time.sleep(0.01)
+        assert pf.resolve(refs[0]) is None and pf.failed == 1
+    finally:
+        pf.shutdown()
+    with pytest.raises(KeyError):
+        R.get("ucxx")
+    c = Config.from_dict(load_toml(CFG))
+    assert get_payload_transfer_mode(c) == "broker"
+    now = [0.0]
+    sk = HealthSkipList(cooldown_s=10, clock=lambda: now[0])
+    sk.quarantine("a")
+    assert sk.healthy(["a", "b"]) == ["b"] and sk.healthy(["a"]) == ["a"] and len(sk) == 1
+    now[0] = 11.0
+    assert not sk.is_quarantined("a") and len(sk) == 0
