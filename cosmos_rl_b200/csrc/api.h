@@ -89,6 +89,14 @@ int b200_adamw(float* master, float* m, float* v, const void* grad, int grad_fp3
 int b200_sumsq(const void* x, int is_fp32, long long n, float* out_accum, cudaStream_t stream);
 int b200_clip_coef(const float* sumsq, float max_norm, float* coef_out, float* norm_out, cudaStream_t stream);
 
+// Fused per-token GRPO objective (grpo_loss.cu). per_tok/dlp/kl_out are [n] fp32, stats is [3] fp32
+// {clipped-token count, sum of ratios, sum of kl*mask}. ref_lp / roll_lp / mask may be null.
+int b200_grpo_loss(const float* lp, const float* old_lp, const float* ref_lp, const float* roll_lp,
+                   const float* adv, const float* mask, int n, float eps_lo, float eps_hi, float lower_bound,
+                   int use_dual_clip, float kl_beta, int unbiased_kl, int use_aipo, float aipo_rho, int decoupled,
+                   int use_cap, float behav_cap, float* per_tok, float* dlp, float* kl_out, float* stats,
+                   cudaStream_t stream);
+
 // Data-parallel step over peer memory (n_ranks <= 8): gradient reduce-scatter + sum of squares, and AdamW whose
 // bf16 store goes to every rank's parameter buffer. Pointers are device addresses valid in this process
 // (own buffer or IPC-mapped peers); lo and n are multiples of 8 elements.
@@ -159,6 +167,13 @@ struct B200CopyDesc {
 };
 int b200_reshard_pull(const B200CopyDesc* descs_dev, const int* tile_prefix_dev, int n_desc, int total_tiles,
                       uint32_t* status, cudaStream_t stream);
+
+// Row-parallel GEMM fused with the tensor-parallel all-reduce (mode 0) or reduce-scatter over rows (mode 1)
+// through peer-mapped staging slots and arrival counters (tp_gemm.cu). ctrl: two local uint32 words.
+int b200_tp_gemm(const void* A, const void* W, void* out, const void* residual, int M, int N, int K, long long lda,
+                 long long ldw, long long ldo, long long ldr, void* const* stage_ptrs, void* const* flag_ptrs,
+                 uint32_t* ctrl, int tp, int rank, int mode, long long slot_elems, int max_tiles,
+                 unsigned long long wait_ns, uint32_t* status, int num_sms, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

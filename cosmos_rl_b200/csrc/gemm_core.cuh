@@ -46,9 +46,12 @@ struct TileInfo {
 // row-major). MN-major: the M (or N) index is contiguous, i.e. the operand is stored transposed
 // ([K, M] row-major); this is what dgrad (B = W[N,K] contracted over N) and wgrad (both operands contracted
 // over the token dimension) need, so no transposed copies are ever made.
-template <bool A_MN_ = false, bool B_MN_ = false, bool A_3D_ = false, bool B_3D_ = false>
+// SIDE_WARPS > 0: the CTA is launched with GEMM_THREADS + 32 * SIDE_WARPS threads and warps 6.. run
+// Epi::side() concurrently with the pipeline (used by the fused GEMM + cross-GPU reduction kernel).
+template <bool A_MN_ = false, bool B_MN_ = false, bool A_3D_ = false, bool B_3D_ = false, int SIDE_WARPS_ = 0>
 struct GemmTraits {
   static constexpr bool A_MN = A_MN_, B_MN = B_MN_, A_3D = A_3D_, B_3D = B_3D_;
+  static constexpr int SIDE_WARPS = SIDE_WARPS_;
 };
 
 // Default schedule: grouped raster over (m, n) tiles, strided over the grid.
@@ -220,7 +223,7 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------ epilogue (warps 2..5) ---------------------
     const int quad = warp & 3;  // TMEM lane quadrant this warp may access
     const int row = quad * 32 + lane;
@@ -253,6 +256,12 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     epi.finish(ep);
+  } else {
+    // ------------------------------ side warps (6..) --------------------------
+    if constexpr (Traits::SIDE_WARPS > 0) {
+      Epi epi;
+      epi.side(ep, sched, warp - 6, lane, status);
+    }
   }
 
   // ------------------------------ teardown ------------------------------------

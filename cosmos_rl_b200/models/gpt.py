@@ -129,8 +129,8 @@ class Attention(nn.Module):
     def forward(self, x, positions, cu_seqlens, max_seqlen, tp=None):
         q, k, v = self.project_qkv(x, positions)
         o = F.varlen_attention(q, k, v, cu_seqlens, max_seqlen)
-        out = _linear(o.reshape(x.shape[0], -1), self.o_proj.weight)
-        return tp.reduce_output(out) if tp is not None else out
+        o = o.reshape(x.shape[0], -1)
+        return tp.row_linear(o, self.o_proj.weight) if tp is not None else _linear(o, self.o_proj.weight)
 
 
 class FeedForward(nn.Module):
@@ -142,8 +142,8 @@ class FeedForward(nn.Module):
         self.down_proj = nn.Linear(self.I, a.dim, bias=False)
 
     def forward(self, x, tp=None):
-        out = _linear(F.swiglu(_linear(x, self.gate_up_proj.weight)), self.down_proj.weight)
-        return tp.reduce_output(out) if tp is not None else out
+        act = F.swiglu(_linear(x, self.gate_up_proj.weight))
+        return tp.row_linear(act, self.down_proj.weight) if tp is not None else _linear(act, self.down_proj.weight)
 
 
 class GPTBlock(nn.Module):
@@ -175,9 +175,8 @@ class GPTBlock(nn.Module):
             x, res = checkpoint(self._attn_part, h, res, positions, cu_seqlens, max_seqlen, tp, use_reentrant=False)
             gu = _linear(x, self.mlp.gate_up_proj.weight)
             act = checkpoint(F.swiglu, gu, use_reentrant=False)
-            h = _linear(act, self.mlp.down_proj.weight)
-            if tp is not None:
-                h = tp.reduce_output(h)
+            h = tp.row_linear(act, self.mlp.down_proj.weight) if tp is not None else \
+                _linear(act, self.mlp.down_proj.weight)
             return h, res
         x, res = self._attn_part(h, res, positions, cu_seqlens, max_seqlen, tp)
         h = self.mlp(x, tp)

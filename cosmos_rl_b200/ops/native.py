@@ -72,6 +72,11 @@ _SIGS = {
                    c_float, c_float, c_float, c_float, c_void_p, c_void_p],
     "b200_sumsq": [c_void_p, c_int, c_longlong, c_void_p, c_void_p],
     "b200_clip_coef": [c_void_p, c_float, c_void_p, c_void_p, c_void_p],
+    "b200_tp_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
+                     c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_int, c_ulonglong,
+                     c_void_p, c_int, c_void_p],
+    "b200_grpo_loss": [c_void_p] * 6 + [c_int, c_float, c_float, c_float, c_int, c_float, c_int, c_int, c_float,
+                       c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200_sample": [c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_ulonglong,
                     c_ulonglong, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200_kv_append": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int,

@@ -1,8 +1,8 @@
 """Tensor parallelism of the dense decoder: column-parallel qkv / gate_up, row-parallel o / down,
 vocabulary-parallel embedding and lm_head (plan of cosmos_rl/policy/model/gpt/parallelize.py:233-340).
 
-The collectives here are the NCCL (library) statements; the fused sm_100a all-gather->GEMM and
-GEMM->reduce-scatter kernels plug in through ``fused`` when a peer-memory context is attached.
+The collectives here are the NCCL (library) statements; the fused sm_100a GEMM + all-reduce / reduce-scatter
+kernel (``tp_fused.FusedTP``) replaces them for row-parallel projections once ``attach_fused`` has been called.
 """
 from __future__ import annotations
 
@@ -63,9 +63,20 @@ class TensorParallel:
 
     def reduce_output(self, x):
         """Sum the partial outputs of a row-parallel projection."""
-        if self.fused is not None and not torch.is_grad_enabled():
-            return self.fused.all_reduce(x)
         return _AllReduce.apply(x, self.group)
+
+    def row_linear(self, x, w):
+        """Row-parallel projection + reduction. Inference on GPU with a peer-memory context attached runs the
+        fused tcgen05 GEMM + all-reduce kernel; otherwise a GEMM followed by the library all-reduce."""
+        f = self.fused
+        if (f is not None and x.is_cuda and not torch.is_grad_enabled() and x.dtype == torch.bfloat16
+                and x.dim() == 2 and f.fits(x.shape[0], w.shape[0])):
+            return f.gemm_all_reduce(x.contiguous(), w)
+        return _AllReduce.apply(torch.nn.functional.linear(x, w), self.group)
+
+    def attach_fused(self, device, max_rows: int, max_cols: int) -> None:
+        from .tp_fused import FusedTP
+        self.fused = FusedTP(self.group, self.size, self.rank, device, max_rows, max_cols)
 
     def gather_vocab(self, logits_local):
         return _AllGatherLast.apply(logits_local, self.group, self.size)

@@ -1,0 +1,100 @@
+"""Peer-memory context of the fused row-parallel GEMM + tensor-parallel reduction kernel (``csrc/tp_gemm.cu``).
+
+One workspace per TP rank holds two call-counter words, the per-tile arrival counters (two sets) and the
+staging slots (two sets x tp source ranks). Workspaces are exchanged as CUDA IPC handles over the TP process
+group; afterwards ``gemm_all_reduce`` / ``gemm_reduce_scatter`` are single kernel launches with no library
+collective (the reference's path is nn.Linear + NCCL all-reduce / reduce-scatter,
+cosmos_rl/policy/model/gpt/parallelize.py:233-340).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+from .peer import PeerBuffer, PeerMapping
+
+_HEADER = 256
+
+
+class FusedTP:
+    def __init__(self, group, size: int, rank: int, device: torch.device, max_rows: int, max_cols: int,
+                 wait_s: float = 10.0):
+        assert 1 <= size <= 8
+        self.group, self.size, self.rank, self.device = group, size, rank, device
+        self.max_tiles = ((max_rows + 127) // 128) * ((max_cols + 127) // 128)
+        self.slot_elems = ((max_rows + 127) // 128) * 128 * max_cols
+        self.flag_bytes = ((2 * self.max_tiles * 4 + 255) // 256) * 256
+        self.nbytes = _HEADER + self.flag_bytes + 2 * size * self.slot_elems * 2
+        self.wait_ns = int(wait_s * 1e9)
+        self.buf = PeerBuffer(self.nbytes, device)          # zero-filled
+        torch.cuda.synchronize(device)
+        handles: List[Optional[bytes]] = [None] * size
+        dist.all_gather_object(handles, self.buf.export(), group=group)
+        self.maps: List[Optional[PeerMapping]] = []
+        bases = []
+        for r, h in enumerate(handles):
+            if r == rank:
+                self.maps.append(None)
+                bases.append(self.buf.ptr)
+            else:
+                m = PeerMapping(h, self.nbytes, device)
+                self.maps.append(m)
+                bases.append(m.ptr)
+        arr = ctypes.c_void_p * 8
+        self._flags = arr(*[b + _HEADER for b in bases] + [None] * (8 - size))
+        self._stage = arr(*[b + _HEADER + self.flag_bytes for b in bases] + [None] * (8 - size))
+        self._ctrl = self.buf.ptr
+        dist.barrier(group=group)
+
+    def fits(self, rows: int, cols: int, mode: int = 0) -> bool:
+        r = rows if mode == 0 else rows // self.size
+        return (r * cols <= self.slot_elems and cols % 8 == 0
+                and ((rows + 127) // 128) * ((cols + 127) // 128) <= self.max_tiles)
+
+    def _launch(self, a, w, out, residual, mode):
+        M, K = a.shape
+        N = w.shape[0]
+        st = native.status_word(a.device)
+        dev = a.device.index if a.device.index is not None else torch.cuda.current_device()
+        native.check(native.lib().b200_tp_gemm(
+            native.ptr(a), native.ptr(w), native.ptr(out), native.ptr(residual) if residual is not None else None,
+            M, N, K, a.stride(0), w.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
+            self._stage, self._flags, self._ctrl, self.size, self.rank, mode, self.slot_elems, self.max_tiles,
+            self.wait_ns, native.ptr(st), native.num_sms(dev), native.stream()), "tp_gemm")
+        return out
+
+    def gemm_all_reduce(self, a: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``sum_r a_r @ w_r^T (+ residual)`` on every rank; a [M, K/tp], w [N, K/tp], bf16."""
+        assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.stride(-1) == 1 and w.stride(-1) == 1
+        if out is None:
+            out = torch.empty(a.shape[0], w.shape[0], dtype=torch.bfloat16, device=a.device)
+        return self._launch(a, w, out, residual, 0)
+
+    def gemm_reduce_scatter(self, a: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Rows ``[rank * M/tp, (rank+1) * M/tp)`` of the summed product (sequence-parallel layout)."""
+        assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[0] % (128 * self.size) == 0
+        if out is None:
+            out = torch.empty(a.shape[0] // self.size, w.shape[0], dtype=torch.bfloat16, device=a.device)
+        return self._launch(a, w, out, residual, 1)
+
+    def reset(self) -> None:
+        """Re-arm after an error status (all ranks, between steps)."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        self.buf.tensor(torch.uint8)[:_HEADER + self.flag_bytes].zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for m in self.maps:
+            if m is not None:
+                m.close()
+        self.buf.free()

@@ -40,30 +40,8 @@ class GrpoLossConfig:
         return cls(**{k: getattr(tp, k) for k in cls.__dataclass_fields__ if hasattr(tp, k)})
 
 
-def grpo_loss(logprob: torch.Tensor, old_logprob: torch.Tensor, advantages: torch.Tensor, seq_ids: torch.Tensor,
-              n_seq: int, cfg: GrpoLossConfig, ref_logprob: Optional[torch.Tensor] = None,
-              rollout_logprob: Optional[torch.Tensor] = None, entropy: Optional[torch.Tensor] = None,
-              seq_rewards: Optional[torch.Tensor] = None, total_tokens: Optional[torch.Tensor] = None,
-              ) -> Tuple[torch.Tensor, Dict[str, torch.Tensor]]:
-    """``advantages`` is per token (sequence advantage broadcast). Returns (scalar loss, metrics).
-
-    ``total_tokens`` overrides the denominator of ``token-mean`` (token count balanced across data-parallel
-    ranks and replicas)."""
-    lp = logprob.float()
-    old = old_logprob.float()
-    A = advantages.float()
-    ntok = lp.numel()
-    tok_per_seq = _seg_sum(torch.ones_like(lp), seq_ids, n_seq).clamp_min(1.0)
-    mask = torch.ones_like(lp)
-
-    if cfg.off_policy_masking_delta is not None:
-        # drop negative-advantage sequences whose behaviour policy drifted too far from the current one
-        src = rollout_logprob.float() if rollout_logprob is not None else old
-        drift = _seg_sum((src - lp).detach(), seq_ids, n_seq) / tok_per_seq
-        seq_adv = _seg_sum(A, seq_ids, n_seq) / tok_per_seq
-        drop = (seq_adv < 0) & (drift > cfg.off_policy_masking_delta)
-        mask = (~drop)[seq_ids].float()
-
+def _per_token_terms_torch(lp, old, A, seq_ids, n_seq, tok_per_seq, cfg, ref_logprob, rollout_logprob):
+    """Op-by-op per-token surrogate + KL (every variant; the oracle of the fused kernel)."""
     diff = lp - old
     if cfg.variant == "gspo":
         seq_diff = (_seg_sum(diff, seq_ids, n_seq) / tok_per_seq).clamp(max=10.0)
@@ -100,6 +78,77 @@ def grpo_loss(logprob: torch.Tensor, old_logprob: torch.Tensor, advantages: torc
             kl = kl * torch.exp(diff.clamp(-20.0, 20.0)).detach()
         per_tok = per_tok + cfg.kl_beta * kl
 
+    return per_tok, kl, clip_frac.detach(), ratio.detach().mean()
+
+
+class _FusedGrpoTerms(torch.autograd.Function):
+    """One kernel for surrogate, KL, their derivative w.r.t. the current log-prob and the metric sums."""
+
+    @staticmethod
+    def forward(ctx, lp, old, A, ref, roll, mask, cfg):
+        from ..ops import native
+        n = lp.numel()
+        out = torch.empty(3, n, dtype=torch.float32, device=lp.device)
+        stats = torch.empty(3, dtype=torch.float32, device=lp.device)
+        decoupled = bool(cfg.use_decoupled_loss and roll is not None)
+        cap = cfg.behav_imp_weight_cap
+        P = lambda t: native.ptr(t) if t is not None else None
+        native.check(native.lib().b200_grpo_loss(
+            P(lp), P(old), P(ref if cfg.kl_beta != 0.0 else None), P(roll if decoupled else None), P(A), P(mask), n,
+            cfg.epsilon_low, cfg.epsilon_high, cfg.lower_bound_ratio, 1, cfg.kl_beta,
+            int(cfg.unbiased_kl_estimate), int(cfg.aipo_rho is not None), float(cfg.aipo_rho or 0.0), int(decoupled),
+            int(cap is not None), float(cap or 0.0), P(out[0]), P(out[1]), P(out[2]), P(stats), native.stream()),
+            "grpo_loss")
+        ctx.save_for_backward(out[1])
+        ctx.mark_non_differentiable(stats)
+        return out[0], out[2].detach(), stats
+
+    @staticmethod
+    def backward(ctx, g_per, g_kl, g_stats):
+        (dlp,) = ctx.saved_tensors
+        return g_per * dlp, None, None, None, None, None, None
+
+
+USE_FUSED_KERNEL = True
+
+
+def _fusable(lp: torch.Tensor, cfg: "GrpoLossConfig") -> bool:
+    return USE_FUSED_KERNEL and lp.is_cuda and cfg.variant != "gspo"
+
+
+def grpo_loss(logprob: torch.Tensor, old_logprob: torch.Tensor, advantages: torch.Tensor, seq_ids: torch.Tensor,
+              n_seq: int, cfg: GrpoLossConfig, ref_logprob: Optional[torch.Tensor] = None,
+              rollout_logprob: Optional[torch.Tensor] = None, entropy: Optional[torch.Tensor] = None,
+              seq_rewards: Optional[torch.Tensor] = None, total_tokens: Optional[torch.Tensor] = None,
+              ) -> Tuple[torch.Tensor, Dict[str, torch.Tensor]]:
+    """``advantages`` is per token (sequence advantage broadcast). Returns (scalar loss, metrics).
+
+    ``total_tokens`` overrides the denominator of ``token-mean`` (token count balanced across data-parallel
+    ranks and replicas)."""
+    lp = logprob.float()
+    old = old_logprob.float()
+    A = advantages.float()
+    ntok = lp.numel()
+    tok_per_seq = _seg_sum(torch.ones_like(lp), seq_ids, n_seq).clamp_min(1.0)
+    mask = torch.ones_like(lp)
+
+    if cfg.off_policy_masking_delta is not None:
+        # drop negative-advantage sequences whose behaviour policy drifted too far from the current one
+        src = rollout_logprob.float() if rollout_logprob is not None else old
+        drift = _seg_sum((src - lp).detach(), seq_ids, n_seq) / tok_per_seq
+        seq_adv = _seg_sum(A, seq_ids, n_seq) / tok_per_seq
+        drop = (seq_adv < 0) & (drift > cfg.off_policy_masking_delta)
+        mask = (~drop)[seq_ids].float()
+
+    if _fusable(lp, cfg):
+        f32 = lambda t: None if t is None else t.float().contiguous()
+        per_tok, kl, stats = _FusedGrpoTerms.apply(lp.contiguous(), old.contiguous(), A.contiguous(),
+                                                   f32(ref_logprob), f32(rollout_logprob), mask, cfg)
+        clip_frac, ratio_mean = stats[0] / ntok, stats[1] / ntok
+    else:
+        per_tok, kl, clip_frac, ratio_mean = _per_token_terms_torch(lp, old, A, seq_ids, n_seq, tok_per_seq, cfg,
+                                                                    ref_logprob, rollout_logprob)
+
     per_tok = per_tok * mask
     if cfg.loss_type == "token-mean":
         denom = total_tokens if total_tokens is not None else mask.sum().clamp_min(1.0)
@@ -116,7 +165,7 @@ def grpo_loss(logprob: torch.Tensor, old_logprob: torch.Tensor, advantages: torc
         raise ValueError(f"unknown loss_type {cfg.loss_type!r}")
 
     metrics: Dict[str, torch.Tensor] = {"kl": (kl * mask).sum() / mask.sum().clamp_min(1.0),
-                                        "clip_frac": clip_frac.detach(), "ratio_mean": ratio.detach().mean()}
+                                        "clip_frac": clip_frac, "ratio_mean": ratio_mean}
     if entropy is not None:
         ent_mean = (entropy.float() * mask).sum() / mask.sum().clamp_min(1.0)
         metrics["entropy"] = ent_mean.detach()

@@ -18,6 +18,8 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Any, Deque, Dict, List, Optional, Sequence, Tuple
 
+import os
+
 import torch
 
 from ..ops import functional as F
@@ -105,6 +107,10 @@ class RolloutEngine:
         self.check_interval = check_interval if self.cuda else 1
         self.seed = seed
         self.tp = tp if tp is not None else getattr(model, "tp", None)
+        if (self.tp is not None and self.cuda and getattr(self.tp, "fused", None) is None
+                and os.environ.get("COSMOS_B200_FUSED_TP", "1") != "0"):
+            # row-parallel projections run as one GEMM + all-reduce kernel over peer memory
+            self.tp.attach_fused(self.device, max(max_prefill_tokens, max_num_seqs), a.dim)
         self.weight_version = 0
         # ---- static decode state (device)
         S = self.S
@@ -160,9 +166,11 @@ class RolloutEngine:
             q, k, v = layer.self_attn.project_qkv(x, positions)
             F.kv_append(k, v, self.kv[li], slot_mapping, self.kv_vt)
             o = attn(li, q, k, v)
-            h = torch.nn.functional.linear(o.reshape(o.shape[0], -1), layer.self_attn.o_proj.weight)
+            o = o.reshape(o.shape[0], -1)
             if self.tp is not None:
-                h = self.tp.reduce_output(h)
+                h = self.tp.row_linear(o, layer.self_attn.o_proj.weight)
+            else:
+                h = torch.nn.functional.linear(o, layer.self_attn.o_proj.weight)
             x, res = F.rms_norm(h, layer.post_attention_layernorm, eps, residual=res)
             h = layer.mlp(x, self.tp)
         out, _ = F.rms_norm(h, m.norm, eps, residual=res)

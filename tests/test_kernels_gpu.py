@@ -342,3 +342,40 @@ def test_rope_separate_qk_autograd_on_views():
     (qe.sum() + 2 * ke.sum()).backward()
     assert torch.allclose(qb.grad.float().cpu(), qr.grad, rtol=2e-2, atol=2e-2)
     assert torch.allclose(kb.grad.float().cpu(), kr.grad, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("over", [
+    {}, {"kl_beta": 0.05}, {"kl_beta": 0.05, "unbiased_kl_estimate": True}, {"aipo_rho": 1.1},
+    {"use_decoupled_loss": True, "behav_imp_weight_cap": 1.3, "kl_beta": 0.01},
+    {"loss_type": "seq-mean-token-mean", "off_policy_masking_delta": 0.05},
+    {"loss_type": "seq-mean-token-sum", "epsilon_high": 0.28, "lower_bound_ratio": 1.2},
+])
+def test_fused_grpo_loss_matches_op_by_op(over):
+    from cosmos_rl_b200.policy import loss as L
+    torch.manual_seed(3)
+    n, n_seq = 5000, 37
+    dev = torch.device("cuda")
+    base = torch.randn(n, device=dev) - 2.0
+    old = base + 0.25 * torch.randn(n, device=dev)
+    old[::17] = base[::17]                               # exact ties: ratio == 1
+    old[5] = base[5] + 30.0                              # clamp region
+    ref = base + 0.1 * torch.randn(n, device=dev)
+    roll = old + 0.2 * torch.randn(n, device=dev)
+    seq_ids = torch.sort(torch.randint(0, n_seq, (n,), device=dev)).values
+    A = torch.randn(n_seq, device=dev)[seq_ids]
+    ent = torch.rand(n, device=dev)
+    cfg = L.GrpoLossConfig(**over)
+    res = {}
+    for fused in (False, True):
+        L.USE_FUSED_KERNEL = fused
+        lp = base.clone().requires_grad_(True)
+        loss, m = L.grpo_loss(lp, old, A, seq_ids, n_seq, cfg, ref_logprob=ref, rollout_logprob=roll, entropy=ent)
+        loss.backward()
+        res[fused] = (loss.detach(), lp.grad.clone(), {k: v.detach() for k, v in m.items()})
+    L.USE_FUSED_KERNEL = True
+    (l0, g0, m0), (l1, g1, m1) = res[False], res[True]
+    assert torch.allclose(l0, l1, rtol=1e-4, atol=1e-6), (l0, l1)
+    assert torch.allclose(g0, g1, rtol=1e-4, atol=1e-8), (g0 - g1).abs().max()
+    for k in m0:
+        assert torch.allclose(m0[k].float(), m1[k].float(), rtol=1e-4, atol=1e-6), k
