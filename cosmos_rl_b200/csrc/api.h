@@ -138,14 +138,13 @@ int b200_paged_decode_tc(const void* q, const void* cache, long long num_pages, 
 int b200_paged_decode_static(const void* q, const void* cache, const int* block_table, const int* seq_lens,
                              void* out, int B, int hq, int hkv, int d, int page_size, int max_pages, int nsplit,
                              float scale, cudaStream_t stream);
-// Varlen causal flash attention (packed sequences, GQA). q [T,hq,d], k/v [T,hkv,d] with row strides.
-int b200_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_seqlens,
-                   int n_seqs, int T, int hq, int hkv, int d, long long q_stride, long long kv_stride,
-                   long long o_stride, float scale, int max_seqlen, cudaStream_t stream);
-int b200_flash_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
-                   void* dq, void* dk, void* dv, float* dq_accum, float* delta, const int* cu_seqlens, int n_seqs,
-                   int T, int hq, int hkv, int d, long long q_stride, long long kv_stride, long long o_stride,
-                   float scale, int max_seqlen, cudaStream_t stream);
+// Varlen causal flash attention forward on tcgen05 (flash_fwd.cu): packed sequences, GQA, head_dim 128.
+// q [Tq,hq,d], k/v [Tk,hkv,d] with token strides; out [Tq,hq,d]; lse [hq,Tq] fp32; queries are aligned to the
+// end of their sequence's keys.
+int b200_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_q,
+                   const int* cu_k, int B, int Tq, int Tk, int hq, int hkv, int d, long long ldq, long long ldk,
+                   long long ldv, long long ldo, int max_q, int causal, float scale, uint32_t* status,
+                   cudaStream_t stream);
 
 // ---- quantisation ----------------------------------------------------------------------------------------------
 // bf16 [R, C] -> e4m3 [R, C] with one fp32 scale per 128 x 128 block (weights) or per 1 x 128 (activations).

@@ -1,28 +1,72 @@
 """Packed-sequence (varlen) causal attention on CUDA.
 
-Training and prefill attention go through :func:`varlen_attention_cuda`. The hand-written sm_100a kernel is
-used when the library exports it; until then the call is served by the flash-attn library kernel, which is
-the same kernel the reference calls (cosmos_rl/policy/model/gpt/__init__.py:264-273) and therefore the
-baseline, not the product.
+Forward runs the hand-written tcgen05 kernel (``csrc/flash_fwd.cu``: head_dim 128, GQA, packed sequences, queries
+aligned to the end of the keys). It returns the output and the log-sum-exp the backward pass and the
+context-parallel merge need. Head dims other than 128 (tiny test models) are served by the flash-attn library
+kernel, which is what the reference calls (cosmos_rl/policy/kernel/modeling_utils.py:65-173).
 """
 from __future__ import annotations
 
 import math
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
 from . import native
 
 
-def _have_native_flash() -> bool:
-    return hasattr(native.lib(), "b200_flash_fwd")
+def native_flash_supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
+    return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 128 and q.stride(-1) == 1
+            and k.stride(-1) == 1 and v.stride(-1) == 1 and q.stride(1) == 128 and k.stride(1) == 128
+            and v.stride(1) == 128 and q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0 and v.stride(0) % 8 == 0
+            and q.shape[1] % k.shape[1] == 0)
+
+
+def flash_fwd(q, k, v, cu_q, cu_k, max_q: int, scale: float, causal: bool = True
+              ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """q [Tq, hq, 128], k / v [Tk, hkv, 128] (token-strided views are fine). Returns (out [Tq, hq, 128] bf16,
+    lse [hq, Tq] fp32)."""
+    Tq, hq, d = q.shape
+    Tk, hkv = k.shape[0], k.shape[1]
+    out = torch.empty(Tq, hq, d, dtype=q.dtype, device=q.device)
+    lse = torch.empty(hq, Tq, dtype=torch.float32, device=q.device)
+    st = native.status_word(q.device)
+    native.check(native.lib().b200_flash_fwd(
+        native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(out), native.ptr(lse), native.ptr(cu_q),
+        native.ptr(cu_k), cu_q.numel() - 1, Tq, Tk, hq, hkv, d, q.stride(0), k.stride(0), v.stride(0), out.stride(0),
+        int(max_q), 1 if causal else 0, float(scale), native.ptr(st), native.stream()), "flash_fwd")
+    return out, lse
+
+
+class _FlashAttn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu, max_seqlen, scale):
+        out, lse = flash_fwd(q, k, v, cu, cu, max_seqlen, scale, True)
+        ctx.save_for_backward(q, k, v, out, lse, cu)
+        ctx.max_seqlen, ctx.scale = max_seqlen, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse, cu = ctx.saved_tensors
+        return flash_bwd(dout.contiguous(), q, k, v, out, lse, cu, ctx.max_seqlen, ctx.scale) + (None, None, None)
+
+
+def flash_bwd(dout, q, k, v, out, lse, cu, max_seqlen: int, scale: float):
+    """Gradients of packed causal attention from the saved output and log-sum-exp."""
+    from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    _flash_attn_varlen_backward(dout, q, k, v, out, lse, dq, dk, dv, cu, cu, max_seqlen, max_seqlen, 0.0, scale,
+                                True, -1, -1, 0.0, None, False, None)
+    return dq, dk, dv
 
 
 def varlen_attention_cuda(q, k, v, cu_seqlens, max_seqlen: int, scale: Optional[float] = None):
     d = q.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    cu = cu_seqlens if cu_seqlens.dtype == torch.int32 else cu_seqlens.to(torch.int32)
+    if native_flash_supported(q, k, v):
+        return _FlashAttn.apply(q, k, v, cu, int(max_seqlen), scale)
     from flash_attn import flash_attn_varlen_func
-    cu = cu_seqlens.to(torch.int32)
     return flash_attn_varlen_func(q, k, v, cu, cu, max_seqlen, max_seqlen, dropout_p=0.0, softmax_scale=scale,
                                   causal=True)

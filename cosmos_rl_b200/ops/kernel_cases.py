@@ -165,7 +165,25 @@ def case_sample(iters):
     report(f"sample B={B} V={V} (no truncation: 3 passes over the row, 2 served by L2)", t, nbytes=B * V * 4.0)
 
 
-CASES = {"gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
+def case_flash(iters):
+    """Packed causal attention forward, Qwen2.5-7B head layout: 16 sequences x 4096 tokens."""
+    from . import attention
+    B, L, hq, hkv, d = 16, 4096, 28, 4, 128
+    T = B * L
+    qkv = bf(T, (hq + 2 * hkv) * d)
+    q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
+    q, k, v = q.unflatten(-1, (hq, d)), k.unflatten(-1, (hkv, d)), v.unflatten(-1, (hkv, d))
+    cu = torch.arange(0, T + 1, L, device="cuda", dtype=torch.int32)
+    flops = 4.0 * B * hq * d * L * L / 2            # causal: half of the score matrix
+    t = timed(lambda: attention.flash_fwd(q, k, v, cu, cu, L, 1.0 / math.sqrt(d)), iters)
+    report(f"flash_fwd tcgen05 B={B} L={L} hq={hq} hkv={hkv}", t, flops=flops)
+    from flash_attn import flash_attn_varlen_func
+    t = timed(lambda: flash_attn_varlen_func(q, k, v, cu, cu, L, L, causal=True), iters)
+    report(f"flash_attn library fwd (same shape)", t, flops=flops)
+    assert native.read_status(q.device) == 0
+
+
+CASES = {"flash": case_flash, "gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
          "reshard": case_reshard, "quant": case_quant, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu,
          "rope": case_rope, "adamw": case_adamw, "sample": case_sample}
 

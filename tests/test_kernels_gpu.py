@@ -379,3 +379,73 @@ def test_fused_grpo_loss_matches_op_by_op(over):
     assert torch.allclose(g0, g1, rtol=1e-4, atol=1e-8), (g0 - g1).abs().max()
     for k in m0:
         assert torch.allclose(m0[k].float(), m1[k].float(), rtol=1e-4, atol=1e-6), k
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("lens,hq,hkv", [([128], 2, 1), ([300, 17, 129, 1000], 4, 2), ([2048, 512], 28, 4),
+                                         ([1, 1, 5], 8, 8)])
+def test_flash_attention_forward_and_lse(lens, hq, hkv):
+    from cosmos_rl_b200.ops import attention
+    torch.manual_seed(11)
+    d, T = 128, sum(lens)
+    qkv = torch.randn(T, (hq + 2 * hkv) * d, device="cuda").to(torch.bfloat16)
+    q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)         # strided views, as the model passes them
+    q, k, v = q.unflatten(-1, (hq, d)), k.unflatten(-1, (hkv, d)), v.unflatten(-1, (hkv, d))
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    scale = 1.0 / math.sqrt(d)
+    out, lse = attention.flash_fwd(q, k, v, cu, cu, max(lens), scale)
+    torch.cuda.synchronize()
+    assert native.read_status(q.device) == 0
+    ref = R.varlen_attention(q.float(), k.float(), v.float(), cu, scale)
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), (out.float() - ref).abs().max()
+    # log-sum-exp of the scaled scores per (head, token)
+    g = hq // hkv
+    for b in range(len(lens)):
+        s0, s1 = int(cu[b]), int(cu[b + 1])
+        qs, ks = q[s0:s1].float(), k[s0:s1].float().repeat_interleave(g, dim=1)
+        sc = torch.einsum("qhd,khd->hqk", qs, ks) * scale
+        sc = sc.masked_fill(torch.ones(s1 - s0, s1 - s0, device="cuda").triu(1).bool(), float("-inf"))
+        assert torch.allclose(lse[:, s0:s1], torch.logsumexp(sc, -1), atol=2e-2, rtol=1e-3)
+
+
+@pytest.mark.gpu
+def test_flash_attention_prefix_aligned_queries():
+    """Queries aligned to the end of a longer key sequence (prefill on top of cached keys, CP chunks)."""
+    from cosmos_rl_b200.ops import attention
+    torch.manual_seed(12)
+    d, hq, hkv = 128, 4, 2
+    lq, lk = [100, 256], [356, 300]
+    q = torch.randn(sum(lq), hq, d, device="cuda").to(torch.bfloat16)
+    k = torch.randn(sum(lk), hkv, d, device="cuda").to(torch.bfloat16)
+    v = torch.randn(sum(lk), hkv, d, device="cuda").to(torch.bfloat16)
+    cq = torch.tensor([0, 100, 356], dtype=torch.int32, device="cuda")
+    ck = torch.tensor([0, 356, 656], dtype=torch.int32, device="cuda")
+    scale = 1.0 / math.sqrt(d)
+    out, _ = attention.flash_fwd(q, k, v, cq, ck, 256, scale)
+    assert native.read_status(q.device) == 0
+    for b in range(2):
+        qs = q[int(cq[b]):int(cq[b + 1])].float()
+        ks = k[int(ck[b]):int(ck[b + 1])].float().repeat_interleave(2, dim=1)
+        vs = v[int(ck[b]):int(ck[b + 1])].float().repeat_interleave(2, dim=1)
+        sc = torch.einsum("qhd,khd->hqk", qs, ks) * scale
+        nq, nk = qs.shape[0], ks.shape[0]
+        mask = torch.arange(nk, device="cuda")[None, :] > (torch.arange(nq, device="cuda")[:, None] + nk - nq)
+        ref = torch.einsum("hqk,khd->qhd", torch.softmax(sc.masked_fill(mask, float("-inf")), -1), vs)
+        got = out[int(cq[b]):int(cq[b + 1])].float()
+        assert torch.allclose(got, ref, atol=2e-2, rtol=2e-2), (got - ref).abs().max()
+
+
+@pytest.mark.gpu
+def test_flash_attention_autograd_matches_reference():
+    torch.manual_seed(13)
+    d, hq, hkv, lens = 128, 4, 2, [200, 56]
+    T = sum(lens)
+    cu = torch.tensor([0, 200, 256], dtype=torch.int32, device="cuda")
+    base = [torch.randn(T, h, d, device="cuda").to(torch.bfloat16) for h in (hq, hkv, hkv)]
+    go = torch.randn(T, hq, d, device="cuda").to(torch.bfloat16)
+    leaves = [t.clone().requires_grad_(True) for t in base]
+    F.varlen_attention(*leaves, cu, 200).backward(go)
+    ref_leaves = [t.float().requires_grad_(True) for t in base]
+    R.varlen_attention(*ref_leaves, cu, 1.0 / math.sqrt(d)).backward(go.float())
+    for a, b in zip(leaves, ref_leaves):
+        assert torch.allclose(a.grad.float(), b.grad, atol=3e-2, rtol=3e-2), (a.grad.float() - b.grad).abs().max()
