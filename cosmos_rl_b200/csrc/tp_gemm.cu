@@ -22,15 +22,12 @@
 namespace b200 {
 
 constexpr int TP_MAX = 8;
-constexpr int TP_BN = 128;
-constexpr int TP_STAGES = 5;
 constexpr int TP_SIDE_WARPS = 4;
 constexpr int TP_THREADS = GEMM_THREADS + 32 * TP_SIDE_WARPS;
-constexpr int TP_ROW_BYTES = TP_BN * 2 + 16;                 // padded: conflict-free 16-byte row writes
-constexpr int TP_XPOSE_BYTES = 4 * 32 * TP_ROW_BYTES;        // one 32-row slab per epilogue warp
+constexpr int TP_ROW_BYTES = 256;                            // 128 bf16 columns; 16-byte pieces XOR-swizzled by row
+constexpr int TP_XPOSE_BYTES = 128 * TP_ROW_BYTES;           // one 32-row slab per epilogue warp
 
-struct TpEpilogue {
-  struct Params {
+struct TpParams {
     __nv_bfloat16* stage[TP_MAX];   // staging base of every rank (own included), peer-mapped
     uint32_t* flags[TP_MAX];        // arrival counters of every rank: [2][max_tiles]
     uint32_t* seq;                  // local call counter
@@ -40,14 +37,18 @@ struct TpEpilogue {
     long long slot_elems;           // elements per (set, source rank) slot
     unsigned long long wait_ns;     // limit of one wait for a tile's partials
     int M, N, tp, rank, mode, max_tiles, rows_per_rank, num_n;
-  };
+};
 
+// BN = 256 (4 stages) is the wide tile for large M; BN = 128 (5 stages) gives more tiles for small M.
+template <int BN, int STAGES>
+struct TpEpilogue {
+  using Params = TpParams;
   int set = -1;
 
   static __device__ __forceinline__ uint8_t* xpose_base() {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    return smem + TP_STAGES * GemmSmem<TP_BN, TP_STAGES>::STAGE_BYTES + GemmSmem<TP_BN, TP_STAGES>::BAR_BYTES;
+    return smem + STAGES * GemmSmem<BN, STAGES>::STAGE_BYTES + GemmSmem<BN, STAGES>::BAR_BYTES;
   }
   static __device__ __forceinline__ int owner_of(const Params& p, int m_blk) {
     return (m_blk * GEMM_BM) / p.rows_per_rank;
@@ -57,20 +58,23 @@ struct TpEpilogue {
     if (set < 0) set = (int)(*reinterpret_cast<volatile uint32_t*>(p.seq) & 1u);
   }
 
-  __device__ __forceinline__ void chunk(const Params&, const TileInfo&, int row, int col0, const float (&v)[32]) {
-    uint8_t* dst = xpose_base() + (size_t)row * TP_ROW_BYTES + col0 * 2;
+  // 32 fp32 columns of this thread's row -> bf16 in the transposition slab; a full 128-column half is pushed
+  __device__ __forceinline__ void chunk(const Params& p, const TileInfo& t, int row, int col0, const float (&v)[32]) {
+    uint8_t* dst = xpose_base() + (size_t)row * TP_ROW_BYTES;
+    const int piece0 = (col0 & 127) >> 3;
 #pragma unroll
-    for (int i = 0; i < 32; i += 8) {
+    for (int g = 0; g < 4; ++g) {
       uint4 o;
-      o.x = pack_bf16x2(v[i], v[i + 1]);
-      o.y = pack_bf16x2(v[i + 2], v[i + 3]);
-      o.z = pack_bf16x2(v[i + 4], v[i + 5]);
-      o.w = pack_bf16x2(v[i + 6], v[i + 7]);
-      *reinterpret_cast<uint4*>(dst + i * 2) = o;
+      o.x = pack_bf16x2(v[8 * g + 0], v[8 * g + 1]);
+      o.y = pack_bf16x2(v[8 * g + 2], v[8 * g + 3]);
+      o.z = pack_bf16x2(v[8 * g + 4], v[8 * g + 5]);
+      o.w = pack_bf16x2(v[8 * g + 6], v[8 * g + 7]);
+      *reinterpret_cast<uint4*>(dst + (((piece0 + g) ^ (row & 15)) << 4)) = o;
     }
+    if ((col0 & 127) == 96) push_half(p, t, row, col0 >> 7);
   }
 
-  __device__ __forceinline__ void tile_end(const Params& p, const TileInfo& t, int row) {
+  __device__ __forceinline__ void push_half(const Params& p, const TileInfo& t, int row, int half) {
     const int lane = threadIdx.x & 31;
     const int slab0 = row - lane;                 // first tile row of this warp's 32-row slab
     __syncwarp();
@@ -78,17 +82,25 @@ struct TpEpilogue {
     const int last = p.mode == 0 ? p.tp : first + 1;
     const long long row_base = p.mode == 0 ? 0 : (long long)first * p.rows_per_rank;
     const int piece = lane & 15;
-    const int col = t.n_blk * TP_BN + piece * 8;
+    const int col = t.n_blk * BN + half * 128 + piece * 8;
 #pragma unroll 4
     for (int rr = 0; rr < 32; rr += 2) {
       const int rt = slab0 + rr + (lane >> 4);
       const long long grow = (long long)t.m_blk * GEMM_BM + rt;
       if (grow < p.M && col < p.N) {
-        const uint4 val = *reinterpret_cast<const uint4*>(xpose_base() + (size_t)rt * TP_ROW_BYTES + piece * 16);
+        const uint4 val = *reinterpret_cast<const uint4*>(xpose_base() + (size_t)rt * TP_ROW_BYTES +
+                                                          ((piece ^ (rt & 15)) << 4));
         const long long off = ((long long)set * p.tp + p.rank) * p.slot_elems + (grow - row_base) * p.N + col;
         for (int d = first; d < last; ++d) *reinterpret_cast<uint4*>(p.stage[d] + off) = val;
       }
     }
+    __syncwarp();                                 // slab is free for the next half
+  }
+
+  __device__ __forceinline__ void tile_end(const Params& p, const TileInfo& t, int) {
+    const int lane = threadIdx.x & 31;
+    const int first = p.mode == 0 ? 0 : owner_of(p, t.m_blk);
+    const int last = p.mode == 0 ? p.tp : first + 1;
     __threadfence_system();
     __syncwarp();
     if (lane == 0) {
@@ -98,7 +110,6 @@ struct TpEpilogue {
         asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(f) : "memory");
       }
     }
-    __syncwarp();
   }
 
   __device__ __forceinline__ void finish(const Params&) {}
@@ -136,9 +147,10 @@ struct TpEpilogue {
       }
       asm volatile("bar.sync 1, %0;" ::"n"(32 * TP_SIDE_WARPS) : "memory");
       if (!side_ok) break;
-      const int col = t.n_blk * TP_BN + piece * 8;
-#pragma unroll 2
-      for (int rr = 0; rr < 32; rr += 2) {
+#pragma unroll 1
+      for (int it2 = 0; it2 < 16 * (BN / 128); ++it2) {
+        const int rr = (it2 & 15) * 2;
+        const int col = t.n_blk * BN + (it2 >> 4) * 128 + piece * 8;
         const long long grow = (long long)t.m_blk * GEMM_BM + w * 32 + rr + (lane >> 4);
         if (grow >= p.M || col >= p.N) continue;
         float acc[8];
@@ -180,11 +192,12 @@ struct TpEpilogue {
   }
 };
 
+template <int BN, int STAGES>
 __global__ void __launch_bounds__(TP_THREADS, 1)
 tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N, int K,
-               TpEpilogue::Params ep, uint32_t* exit_count, uint32_t* status) {
-  gemm_mainloop<TP_BN, TP_STAGES, TpEpilogue, RasterSchedule, GemmTraits<false, false, false, false, TP_SIDE_WARPS>>(
-      &tmA, &tmB, M, N, K, ep, status);
+               TpParams ep, uint32_t* exit_count, uint32_t* status) {
+  gemm_mainloop<BN, STAGES, TpEpilogue<BN, STAGES>, RasterSchedule,
+                GemmTraits<false, false, false, false, TP_SIDE_WARPS>>(&tmA, &tmB, M, N, K, ep, status);
   // every role of every CTA has read the call counter by now; the last CTA to leave advances it
   if (threadIdx.x == 0) {
     __threadfence();
@@ -194,6 +207,30 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       atomicAdd(ep.seq, 1u);
     }
   }
+}
+
+template <int BN, int STAGES>
+static int launch_tp(const void* A, const void* W, int M, int N, int K, long long lda, long long ldw, TpParams ep,
+                     uint32_t* ctrl, uint32_t* status, int num_sms, cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  if (make_tmap_2d(&tmA, A, M, K, lda, GEMM_BM, GEMM_BK, 2)) return B200_ERR_TENSORMAP;
+  if (make_tmap_2d(&tmB, W, N, K, ldw, BN, GEMM_BK, 2)) return B200_ERR_TENSORMAP;
+  constexpr int SMEM = GemmSmem<BN, STAGES>::TOTAL + TP_XPOSE_BYTES;
+  static_assert(SMEM <= 232448, "shared memory budget");
+  auto kern = tp_gemm_kernel<BN, STAGES>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+      return B200_ERR_LAUNCH;
+    attr_set = true;
+  }
+  const int num_m = (M + GEMM_BM - 1) / GEMM_BM;
+  ep.num_n = (N + BN - 1) / BN;
+  const int tiles = num_m * ep.num_n;
+  if (tiles > ep.max_tiles) return B200_ERR_ARG;
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  kern<<<grid, TP_THREADS, SMEM, stream>>>(tmA, tmB, M, N, K, ep, ctrl + 1, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : B200_ERR_LAUNCH;
 }
 
 }  // namespace b200
@@ -210,8 +247,6 @@ extern "C" int b200_tp_gemm(const void* A, const void* W, void* out, const void*
   using namespace b200;
   if (M <= 0 || N <= 0 || K <= 0 || tp < 1 || tp > TP_MAX || rank < 0 || rank >= tp) return B200_ERR_ARG;
   if ((lda & 7) || (ldw & 7) || (N & 7) || (ldo & 7) || (ldr & 7)) return B200_ERR_ARG;
-  const int num_m = (M + GEMM_BM - 1) / GEMM_BM, num_n = (N + TP_BN - 1) / TP_BN;
-  if (num_m * num_n > max_tiles) return B200_ERR_ARG;
   int rows_per_rank = M;
   if (mode == 1) {
     if (M % tp) return B200_ERR_ARG;
@@ -219,17 +254,7 @@ extern "C" int b200_tp_gemm(const void* A, const void* W, void* out, const void*
     if (rows_per_rank % GEMM_BM) return B200_ERR_ARG;
   }
   if ((long long)rows_per_rank * N > slot_elems || (slot_elems & 7)) return B200_ERR_ARG;
-  CUtensorMap tmA, tmB;
-  if (make_tmap_2d(&tmA, A, M, K, lda, GEMM_BM, GEMM_BK, 2)) return B200_ERR_TENSORMAP;
-  if (make_tmap_2d(&tmB, W, N, K, ldw, TP_BN, GEMM_BK, 2)) return B200_ERR_TENSORMAP;
-  constexpr int SMEM = GemmSmem<TP_BN, TP_STAGES>::TOTAL + TP_XPOSE_BYTES;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(tp_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
-      return B200_ERR_LAUNCH;
-    attr_set = true;
-  }
-  TpEpilogue::Params ep{};
+  TpParams ep{};
   for (int r = 0; r < tp; ++r) {
     ep.stage[r] = reinterpret_cast<__nv_bfloat16*>(stage_ptrs[r]);
     ep.flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
@@ -243,9 +268,9 @@ extern "C" int b200_tp_gemm(const void* A, const void* W, void* out, const void*
   ep.wait_ns = wait_ns ? wait_ns : WAIT_LIMIT_NS;
   ep.M = M; ep.N = N; ep.tp = tp; ep.rank = rank; ep.mode = mode; ep.max_tiles = max_tiles;
   ep.rows_per_rank = rows_per_rank;
-  ep.num_n = num_n;
-  const int tiles = num_m * num_n;
-  const int grid = tiles < num_sms ? tiles : num_sms;
-  tp_gemm_kernel<<<grid, TP_THREADS, SMEM, stream>>>(tmA, tmB, M, N, K, ep, ctrl + 1, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : B200_ERR_LAUNCH;
+  // wide tiles once there are enough of them to fill the machine; narrow tiles otherwise
+  const long long wide_tiles = (long long)((M + GEMM_BM - 1) / GEMM_BM) * ((N + 255) / 256);
+  if (wide_tiles >= num_sms)
+    return launch_tp<256, 4>(A, W, M, N, K, lda, ldw, ep, ctrl, status, num_sms, stream);
+  return launch_tp<128, 5>(A, W, M, N, K, lda, ldw, ep, ctrl, status, num_sms, stream);
 }

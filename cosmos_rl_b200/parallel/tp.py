@@ -57,6 +57,7 @@ class TensorParallel:
     def __init__(self, group: dist.ProcessGroup, size: int, rank: int, fused=None):
         self.group, self.size, self.rank = group, size, rank
         self.fused = fused
+        self.fused_min_rows = 4096
 
     def copy_to_region(self, x):
         return _CopyToTP.apply(x, self.group)
@@ -69,8 +70,10 @@ class TensorParallel:
         """Row-parallel projection + reduction. Inference on GPU with a peer-memory context attached runs the
         fused tcgen05 GEMM + all-reduce kernel; otherwise a GEMM followed by the library all-reduce."""
         f = self.fused
+        # below ~4k rows the projection is launch/latency bound and the library pair is faster (measured
+        # crossover on 2 GPUs between 2048 and 8192 rows); prefill and training shapes take the fused kernel
         if (f is not None and x.is_cuda and not torch.is_grad_enabled() and x.dtype == torch.bfloat16
-                and x.dim() == 2 and f.fits(x.shape[0], w.shape[0])):
+                and x.dim() == 2 and x.shape[0] >= self.fused_min_rows and f.fits(x.shape[0], w.shape[0])):
             return f.gemm_all_reduce(x.contiguous(), w)
         return _AllReduce.apply(torch.nn.functional.linear(x, w), self.group)
 

@@ -108,10 +108,11 @@ def main():
 
     # ------------------------------------------------------------ 2b. fused row-parallel GEMM + all-reduce / reduce-scatter
     from cosmos_rl_b200.parallel.tp_fused import FusedTP
-    ftp = FusedTP(grp, world, rank, dev, max_rows=1024, max_cols=3584, wait_s=3.0)
+    ftp = FusedTP(grp, world, rank, dev, max_rows=2560, max_cols=3584, wait_s=3.0)
     gen = torch.Generator(device=dev).manual_seed(77 + rank)
     for call, (M, N, K, mode) in enumerate([(300, 3584, 1024, 0), (512, 3584, 2048, 1), (64, 512, 512, 0),
-                                            (1024, 1536, 4736, 0), (1024, 3584, 512, 1), (8, 3584, 9472, 0)]):
+                                            (1024, 1536, 4736, 0), (1024, 3584, 512, 1), (8, 3584, 9472, 0),
+                                            (2500, 3584, 512, 0), (2560, 3584, 1024, 1), (2304, 3080, 256, 0)]):
         a = (torch.randn(M, K, device=dev, generator=gen) * 0.5).to(torch.bfloat16)
         w = (torch.randn(N, K, device=dev, generator=gen) * 0.05).to(torch.bfloat16)
         res = torch.randn(M if mode == 0 else M // world, N, device=dev, generator=gen).to(torch.bfloat16) \
@@ -164,6 +165,7 @@ def main():
 
     # ------------------------------------------------------------ 3. TP engine == single-GPU engine (greedy)
     rm.tp = TensorParallel(grp, world, rank)
+    rm.tp.fused_min_rows = 1          # exercise the fused GEMM + all-reduce kernel at the test's small shapes
     eng = RolloutEngine(rm, max_num_seqs=8, max_model_len=512, page_size=128)
     g = torch.Generator().manual_seed(5)
     prompts = [torch.randint(0, 4096, (40 + 7 * i,), generator=g).tolist() for i in range(3)]
