@@ -146,6 +146,14 @@ int b200_flash_fwd(const void* q, const void* k, const void* v, void* out, float
                    long long ldv, long long ldo, int max_q, int causal, float scale, uint32_t* status,
                    cudaStream_t stream);
 
+// Gradients of b200_flash_fwd (flash_bwd.cu). dq_accum [Tq,hq,d] fp32 must be zero on entry; dk/dv are overwritten;
+// delta [hq,Tq] fp32 is scratch.
+int b200_flash_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+                   float* dq_accum, void* dk, void* dv, float* delta, const int* cu_q, const int* cu_k, int B, int Tq,
+                   int Tk, int hq, int hkv, int d, long long ldq, long long ldk, long long ldv, long long ldo,
+                   long long lddo, long long lddk, long long lddv, int max_k, int causal, float scale,
+                   uint32_t* status, cudaStream_t stream);
+
 // ---- quantisation ----------------------------------------------------------------------------------------------
 // bf16 [R, C] -> e4m3 [R, C] with one fp32 scale per 128 x 128 block (weights) or per 1 x 128 (activations).
 int b200_quant_fp8_block(const void* src, long long ld_src, void* dst, long long ld_dst, float* scales, int R, int C,

@@ -278,6 +278,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (ok && n > 0) {
       if (!mbar_wait(o_done, (n - 1) & 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_TMEM_FULL); *abort_flag = 1; ok = false; }
     }
+    ok = __all_sync(0xffffffffu, ok);               // tcgen05.ld below is warp-collective
     if (ok) {
       tc_fence_after_sync();
       const bool live = q_idx < len_q;

@@ -52,8 +52,28 @@ class _FlashAttn(torch.autograd.Function):
         return flash_bwd(dout.contiguous(), q, k, v, out, lse, cu, ctx.max_seqlen, ctx.scale) + (None, None, None)
 
 
-def flash_bwd(dout, q, k, v, out, lse, cu, max_seqlen: int, scale: float):
-    """Gradients of packed causal attention from the saved output and log-sum-exp."""
+def flash_bwd(dout, q, k, v, out, lse, cu, max_seqlen: int, scale: float, cu_k=None, max_k=None,
+              causal: bool = True):
+    """Gradients of packed causal attention from the saved output and log-sum-exp (tcgen05 kernel)."""
+    Tq, hq, d = q.shape
+    Tk, hkv = k.shape[0], k.shape[1]
+    cu_k = cu if cu_k is None else cu_k
+    dq_acc = torch.zeros(Tq, hq, d, dtype=torch.float32, device=q.device)
+    dk = torch.empty(Tk, hkv, d, dtype=k.dtype, device=q.device)
+    dv = torch.empty(Tk, hkv, d, dtype=v.dtype, device=q.device)
+    delta = torch.empty(hq, Tq, dtype=torch.float32, device=q.device)
+    st = native.status_word(q.device)
+    native.check(native.lib().b200_flash_bwd(
+        native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(out), native.ptr(dout), native.ptr(lse),
+        native.ptr(dq_acc), native.ptr(dk), native.ptr(dv), native.ptr(delta), native.ptr(cu), native.ptr(cu_k),
+        cu.numel() - 1, Tq, Tk, hq, hkv, d, q.stride(0), k.stride(0), v.stride(0), out.stride(0), dout.stride(0),
+        dk.stride(0), dv.stride(0), int(max_k if max_k is not None else max_seqlen), 1 if causal else 0, float(scale),
+        native.ptr(st), native.stream()), "flash_bwd")
+    return dq_acc.to(q.dtype), dk, dv
+
+
+def flash_bwd_library(dout, q, k, v, out, lse, cu, max_seqlen: int, scale: float):
+    """The flash-attn library's backward on the same saved tensors (comparison baseline in the kernel cases)."""
     from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     _flash_attn_varlen_backward(dout, q, k, v, out, lse, dq, dk, dv, cu, cu, max_seqlen, max_seqlen, 0.0, scale,

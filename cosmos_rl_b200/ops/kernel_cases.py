@@ -180,6 +180,12 @@ def case_flash(iters):
     from flash_attn import flash_attn_varlen_func
     t = timed(lambda: flash_attn_varlen_func(q, k, v, cu, cu, L, L, causal=True), iters)
     report(f"flash_attn library fwd (same shape)", t, flops=flops)
+    out, lse = attention.flash_fwd(q, k, v, cu, cu, L, 1.0 / math.sqrt(d))
+    go = torch.randn_like(out)
+    t = timed(lambda: attention.flash_bwd(go, q, k, v, out, lse, cu, L, 1.0 / math.sqrt(d)), iters)
+    report(f"flash_bwd tcgen05 (same shape, incl. delta pre-pass and dQ cast)", t, flops=2.5 * flops)
+    t = timed(lambda: attention.flash_bwd_library(go, q, k, v, out, lse, cu, L, 1.0 / math.sqrt(d)), iters)
+    report(f"flash_attn library bwd (same shape)", t, flops=2.5 * flops)
     assert native.read_status(q.device) == 0
 
 
