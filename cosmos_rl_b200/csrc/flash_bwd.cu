@@ -25,7 +25,7 @@ constexpr int FB_B = 128;
 constexpr int FB_D = 128;
 constexpr int FB_TILE = FB_B * FB_D * 2;            // 32 KiB
 constexpr int FB_SMEM = 6 * FB_TILE + 1024 /*lse, delta*/ + 256 + 1024;
-constexpr int FB_THREADS = 192;
+constexpr int FB_THREADS = 320;   // TMA warp, MMA warp, 8 softmax warps (two per TMEM lane quadrant)
 constexpr float FB_LOG2E = 1.4426950408889634f;
 
 struct FbParams {
@@ -98,9 +98,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     mbar_init(qdo_full, 1);
     mbar_init(s_ready, 1);
     mbar_init(dp_ready, 1);
-    mbar_init(pds_ready, 4);
+    mbar_init(pds_ready, 8);
     mbar_init(mma3_done, 1);
-    mbar_init(dq_drained, 4);
+    mbar_init(dq_drained, 8);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tm_q);
@@ -182,27 +182,30 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       } while (false);
     }
   } else {
-    // ------------------------------------------------ softmax / dS / drains (warps 2..5)
+    // ------------------------------------------------ softmax / dS / drains (warps 2..9)
+    // Two warps share a TMEM lane quadrant (a warp may only touch lanes 32 * (warp % 4) ..+31) and split the
+    // 128 columns between them, so the TMEM-load latency of one overlaps the arithmetic of the other.
     const int quad = warp & 3;
+    const int chalf = (warp - 2) >> 2;                // column half handled by this warp
     const int row = quad * 32 + lane;                 // key row of S^T / dP^T / dV / dK; query row of dQ
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     const int key = kv0 + row;
     const bool key_ok = key < len_k;
     bool ok = true;
-    for (int i = 0; i < n_iter && ok; ++i) {
+    for (int i = 0; i < n_iter; ++i) {               // never left early: see the note on failed waits below
       const int h = hk * G + i / per_head, qb = qb_first + i % per_head;
       const int q0 = qb * FB_B;
       // statistics of the 128 queries of this block
-      {
+      if (chalf == 0) {
         const int qi = q0 + row;
         const long long o = (long long)h * p.Tq + q_beg + qi;
         lse_sh[row] = qi < len_q ? p.lse[o] * FB_LOG2E : INFINITY;
         dlt_sh[row] = qi < len_q ? p.delta[o] : 0.f;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      // A failed wait never leaves the loop early: the four warps meet at the named barriers of every
-      // iteration and leave together once the abort flag is seen after the closing barrier.
-      if (!mbar_wait(s_ready, i & 1) || !mbar_wait(dp_ready, i & 1)) {
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      // A failed wait never leaves the loop early: the eight warps meet at the named barriers of every
+      // iteration; after a failure a warp only skips its work, so each warp sits out at most one timeout.
+      if (ok && (!mbar_wait(s_ready, i & 1) || !mbar_wait(dp_ready, i & 1))) {
         atomicCAS(p.status, ST_OK, ST_TIMEOUT_TMEM_FULL); *abort_flag = 1; ok = false;
       }
       ok = __all_sync(0xffffffffu, ok);           // tcgen05.ld below is warp-collective
@@ -212,7 +215,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const int q_min = p.causal ? key - shift : -(1 << 30);
       const bool need_mask = !key_ok || (q0 < q_min) || (q0 + FB_B > len_q);
 #pragma unroll 1
-      for (int c = 0; c < FB_B; c += 32) {
+      for (int c = chalf * 64; c < chalf * 64 + 64; c += 32) {
         uint32_t rs[32], rd[32];
         tmem_ld_32x32b_x32(tm_s + lane_addr + c, rs);
         tmem_ld_32x32b_x32(tm_dp + lane_addr + c, rd);
@@ -254,7 +257,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int qi = q0 + row;
         float* dst = p.dq_accum + ((long long)(q_beg + qi) * p.hq + h) * FB_D;
 #pragma unroll 1
-        for (int c = 0; c < FB_D; c += 32) {
+        for (int c = chalf * 64; c < chalf * 64 + 64; c += 32) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(tm_dp + lane_addr + c, r);
           tmem_ld_wait();
@@ -270,7 +273,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_drained);
-      asm volatile("bar.sync 1, 128;" ::: "memory");   // lse_sh / dlt_sh are rewritten next iteration
+      asm volatile("bar.sync 1, 256;" ::: "memory");   // lse_sh / dlt_sh are rewritten next iteration
       if (*abort_flag) ok = false;
     }
     // ---- dK, dV of the key block
@@ -278,7 +281,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       __nv_bfloat16* dkr = p.dk + (long long)(k_beg + key) * p.lddk + hk * FB_D;
       __nv_bfloat16* dvr = p.dv + (long long)(k_beg + key) * p.lddv + hk * FB_D;
 #pragma unroll 1
-      for (int c = 0; c < FB_D; c += 32) {
+      for (int c = chalf * 64; c < chalf * 64 + 64; c += 32) {
         uint32_t a[32], bb[32];
         if (n_iter > 0) {
           tmem_ld_32x32b_x32(tm_dk + lane_addr + c, a);

@@ -7,7 +7,7 @@
 //                              [token, d] layout of the packed activations is used as stored (no transpose)
 // S is double-buffered in TMEM so the tensor core computes S_{j+1} while the softmax warps work on S_j; O stays
 // in TMEM for the whole item and is rescaled lazily: the running maximum only moves when it grows by more than
-// 2^8, so the TMEM read-modify-write of O is rare. Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5
+// 2^8, so the TMEM read-modify-write of O is rare. Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-9
 // softmax + epilogue. K and V have separate 2-deep rings (a K tile is released right after its S MMA).
 // Outputs O [T, hq, d] bf16 and LSE [hq, T] fp32 (natural log of the softmax denominator of the scaled scores).
 // Queries are aligned to the END of the keys of their sequence (len_k >= len_q: prefill with a prefix cache,
@@ -22,8 +22,8 @@ namespace b200 {
 constexpr int FA_B = 128;                         // block of queries / keys
 constexpr int FA_D = 128;
 constexpr int FA_TILE = FA_B * FA_D * 2;          // 32 KiB
-constexpr int FA_SMEM = 6 * FA_TILE + 256 + 1024; // Q, K x2, V x2, P, barriers, alignment
-constexpr int FA_THREADS = 192;
+constexpr int FA_SMEM = 6 * FA_TILE + 256 + 3072 + 1024; // Q, K x2, V x2, P, barriers, row statistics, alignment
+constexpr int FA_THREADS = 320;   // TMA warp, MMA warp, 8 softmax warps (two per TMEM lane quadrant)
 constexpr float FA_LOG2E = 1.4426950408889634f;
 constexpr float FA_LN2 = 0.6931471805599453f;
 constexpr float FA_RESCALE_TAU = 8.0f;
@@ -84,6 +84,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   uint64_t* o_done = bars + 12;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  float* max_sh = reinterpret_cast<float*>(smem + 6 * FA_TILE + 256);   // [2 buffers][2 column halves][128 rows]
+  float* l_sh = max_sh + 512;                                            // [2][128]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -95,7 +97,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(&vempty[s], 1);
       mbar_init(&s_ready[s], 1);
     }
-    mbar_init(p_ready, 4);
+    mbar_init(p_ready, 8);
     mbar_init(o_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -183,39 +185,53 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       } while (false);
     }
   } else {
-    // ------------------------------------------------ softmax + epilogue (warps 2..5)
+    // ------------------------------------------------ softmax + epilogue (warps 2..9)
+    // Two warps share a TMEM lane quadrant and split the 128 columns of a row; they exchange their partial row
+    // maxima through shared memory (one named barrier per key block) and keep partial row sums. A failed wait
+    // never leaves the loop early: all eight warps meet at the barrier and leave together.
     const int quad = warp & 3;
+    const int chalf = (warp - 2) >> 2;
+    const int c_lo = chalf * 64;
     const int row = quad * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     const int q_idx = q0 + row;                    // position inside the sequence's queries
     const int k_limit = p.causal ? min(len_k, q_idx + shift + 1) : len_k;   // keys [0, k_limit) are visible
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
-    for (int j = 0; j < n && ok; ++j) {
+    for (int j = 0; j < n; ++j) {
       const int s = j & 1;
-      if (!mbar_wait(&s_ready[s], (j >> 1) & 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_TMEM_FULL); *abort_flag = 1; ok = false; break; }
+      if (ok && !mbar_wait(&s_ready[s], (j >> 1) & 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_TMEM_FULL); *abort_flag = 1; ok = false; }
+      ok = __all_sync(0xffffffffu, ok);
       tc_fence_after_sync();
       const uint32_t ts = tmem_base + s * FA_B + lane_addr;
       const int kbase = j * FA_B;
       const bool need_mask = kbase + FA_B > k_limit;
-      // pass 1: row maximum
+      // pass 1: maximum over this warp's half of the row
       float mx = -INFINITY;
+      if (ok) {
 #pragma unroll 1
-      for (int c = 0; c < FA_B; c += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(ts + c, r);
-        tmem_ld_wait();
-        if (!need_mask) {
+        for (int c = c_lo; c < c_lo + 64; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(ts + c, r);
+          tmem_ld_wait();
+          if (!need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+          } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (kbase + c + i < k_limit) mx = fmaxf(mx, __uint_as_float(r[i]));
+            for (int i = 0; i < 32; ++i)
+              if (kbase + c + i < k_limit) mx = fmaxf(mx, __uint_as_float(r[i]));
+          }
         }
       }
-      mx *= p.scale_log2;                           // scale > 0
-      // lazy rescale of the running state
+      max_sh[s * 256 + chalf * 128 + row] = mx;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      // never leave the loop early (the barrier count must match in all eight warps): after a failure a warp
+      // only skips its work, and every warp sits out at most one timed-out wait
+      if (*abort_flag) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      mx = fmaxf(mx, max_sh[s * 256 + (chalf ^ 1) * 128 + row]) * p.scale_log2;   // scale > 0
+      // lazy rescale of the running state (identical decision in both warps of a row)
       float corr = 1.f;
       const bool grow = mx > m_run + FA_RESCALE_TAU || (m_run == -INFINITY && mx != -INFINITY);
       if (grow) {
@@ -225,11 +241,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
       if (j > 0) {
         // PV_{j-1} must have finished reading P and updating O before either is touched
-        if (!mbar_wait(o_done, (j - 1) & 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_TMEM_FULL); *abort_flag = 1; ok = false; break; }
+        if (!mbar_wait(o_done, (j - 1) & 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_TMEM_FULL); *abort_flag = 1; ok = false; }
+        ok = __all_sync(0xffffffffu, ok);
         tc_fence_after_sync();
-        if (__any_sync(0xffffffffu, grow)) {
+        if (ok && __any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-          for (int c = 0; c < FA_D; c += 16) {
+          for (int c = c_lo; c < c_lo + 64; c += 16) {
             uint32_t r[16];
             tmem_ld_32x32b_x16(tmem_o + lane_addr + c, r);
             tmem_ld_wait();
@@ -240,11 +257,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           tmem_st_wait();
         }
       }
-      // pass 2: probabilities -> shared memory (K-major, two 64-key halves, 128-byte swizzle)
+      if (!ok) continue;                            // meet the others at the next barrier
+      // pass 2: probabilities of this warp's 64 keys -> shared memory (K-major, 128-byte swizzle)
       float sum = 0.f;
       const float mref = (m_run == -INFINITY) ? 0.f : m_run;
 #pragma unroll 1
-      for (int c = 0; c < FA_B; c += 32) {
+      for (int c = c_lo; c < c_lo + 64; c += 32) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(ts + c, r);
         tmem_ld_wait();
@@ -274,7 +292,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);
     }
-    // ---- epilogue: O / l -> bf16, LSE
+    // ---- epilogue: combine the two partial row sums, O / l -> bf16, LSE
+    l_sh[chalf * 128 + row] = l_run;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (*abort_flag) ok = false;
+    l_run += l_sh[(chalf ^ 1) * 128 + row];
     if (ok && n > 0) {
       if (!mbar_wait(o_done, (n - 1) & 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_TMEM_FULL); *abort_flag = 1; ok = false; }
     }
@@ -285,7 +307,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       __nv_bfloat16* orow = p.out + (long long)(q_beg + q_idx) * p.ldo + h * FA_D;
 #pragma unroll 1
-      for (int c = 0; c < FA_D; c += 32) {
+      for (int c = c_lo; c < c_lo + 64; c += 32) {
         uint32_t r[32];
         if (n > 0) {
           tmem_ld_32x32b_x32(tmem_o + lane_addr + c, r);
@@ -306,7 +328,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           }
         }
       }
-      if (live)
+      if (live && chalf == 0)
         p.lse[(long long)h * p.Tq + q_beg + q_idx] = l_run > 0.f ? (m_run + log2f(l_run)) * FA_LN2 : INFINITY;
     }
     tc_fence_before_sync();

@@ -165,10 +165,15 @@ def case_sample(iters):
     report(f"sample B={B} V={V} (no truncation: 3 passes over the row, 2 served by L2)", t, nbytes=B * V * 4.0)
 
 
-def case_flash(iters):
-    """Packed causal attention forward, Qwen2.5-7B head layout: 16 sequences x 4096 tokens."""
+def case_flash_small(iters):
+    """Profiling-sized variant of ``flash`` (4 sequences x 2048 tokens)."""
+    case_flash(iters, B=4, L=2048, library=False)
+
+
+def case_flash(iters, B=16, L=4096, library=True):
+    """Packed causal attention forward + backward, Qwen2.5-7B head layout: 16 sequences x 4096 tokens."""
     from . import attention
-    B, L, hq, hkv, d = 16, 4096, 28, 4, 128
+    hq, hkv, d = 28, 4, 128
     T = B * L
     qkv = bf(T, (hq + 2 * hkv) * d)
     q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
@@ -177,19 +182,21 @@ def case_flash(iters):
     flops = 4.0 * B * hq * d * L * L / 2            # causal: half of the score matrix
     t = timed(lambda: attention.flash_fwd(q, k, v, cu, cu, L, 1.0 / math.sqrt(d)), iters)
     report(f"flash_fwd tcgen05 B={B} L={L} hq={hq} hkv={hkv}", t, flops=flops)
-    from flash_attn import flash_attn_varlen_func
-    t = timed(lambda: flash_attn_varlen_func(q, k, v, cu, cu, L, L, causal=True), iters)
-    report(f"flash_attn library fwd (same shape)", t, flops=flops)
+    if library:
+        from flash_attn import flash_attn_varlen_func
+        t = timed(lambda: flash_attn_varlen_func(q, k, v, cu, cu, L, L, causal=True), iters)
+        report(f"flash_attn library fwd (same shape)", t, flops=flops)
     out, lse = attention.flash_fwd(q, k, v, cu, cu, L, 1.0 / math.sqrt(d))
     go = torch.randn_like(out)
     t = timed(lambda: attention.flash_bwd(go, q, k, v, out, lse, cu, L, 1.0 / math.sqrt(d)), iters)
     report(f"flash_bwd tcgen05 (same shape, incl. delta pre-pass and dQ cast)", t, flops=2.5 * flops)
-    t = timed(lambda: attention.flash_bwd_library(go, q, k, v, out, lse, cu, L, 1.0 / math.sqrt(d)), iters)
-    report(f"flash_attn library bwd (same shape)", t, flops=2.5 * flops)
+    if library:
+        t = timed(lambda: attention.flash_bwd_library(go, q, k, v, out, lse, cu, L, 1.0 / math.sqrt(d)), iters)
+        report(f"flash_attn library bwd (same shape)", t, flops=2.5 * flops)
     assert native.read_status(q.device) == 0
 
 
-CASES = {"flash": case_flash, "gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
+CASES = {"flash": case_flash, "flash_small": case_flash_small, "gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
          "reshard": case_reshard, "quant": case_quant, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu,
          "rope": case_rope, "adamw": case_adamw, "sample": case_sample}
 
