@@ -126,9 +126,14 @@ class Attention(nn.Module):
         q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
         return q.unflatten(-1, (hq, d)), k.unflatten(-1, (hkv, d)), v.unflatten(-1, (hkv, d))
 
+    cp = None    # ContextParallel, set by GPT.attach_context_parallel: tokens are this rank's chunk of every sequence
+
     def forward(self, x, positions, cu_seqlens, max_seqlen, tp=None):
         q, k, v = self.project_qkv(x, positions)
-        o = F.varlen_attention(q, k, v, cu_seqlens, max_seqlen)
+        if self.cp is not None:
+            o = self.cp.attention(q, k, v, cu_seqlens, max_seqlen)
+        else:
+            o = F.varlen_attention(q, k, v, cu_seqlens, max_seqlen)
         o = o.reshape(x.shape[0], -1)
         return tp.row_linear(o, self.o_proj.weight) if tp is not None else _linear(o, self.o_proj.weight)
 
@@ -281,6 +286,12 @@ class GPT(BaseModel):
                 h, res = layer(h, res, position_ids, cu_seqlens, max_seqlen, self.tp)
         out, _ = F.rms_norm(h, self.norm, self.args.norm_eps, residual=res)
         return out
+
+    def attach_context_parallel(self, cp) -> None:
+        """Inputs of ``forward`` become this rank's chunk of every sequence (``ContextParallel.shard``), with global
+        position ids and local ``cu_seqlens``; only the attention layers communicate."""
+        for layer in self.layers:
+            layer.self_attn.cp = cp
 
     def logprobs(self, hidden: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0):
         """Per-token log-prob of ``labels`` and entropy from hidden states, through the fused lm_head kernel."""

@@ -40,16 +40,26 @@ def flash_fwd(q, k, v, cu_q, cu_k, max_q: int, scale: float, causal: bool = True
 
 class _FlashAttn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, cu, max_seqlen, scale):
-        out, lse = flash_fwd(q, k, v, cu, cu, max_seqlen, scale, True)
-        ctx.save_for_backward(q, k, v, out, lse, cu)
-        ctx.max_seqlen, ctx.scale = max_seqlen, scale
+    def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, scale):
+        out, lse = flash_fwd(q, k, v, cu_q, cu_k, max_q, scale, True)
+        ctx.save_for_backward(q, k, v, out, lse, cu_q, cu_k)
+        ctx.max_q, ctx.max_k, ctx.scale = max_q, max_k, scale
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        q, k, v, out, lse, cu = ctx.saved_tensors
-        return flash_bwd(dout.contiguous(), q, k, v, out, lse, cu, ctx.max_seqlen, ctx.scale) + (None, None, None)
+        q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
+        return flash_bwd(dout.contiguous(), q, k, v, out, lse, cu_q, ctx.max_q, ctx.scale, cu_k=cu_k,
+                         max_k=ctx.max_k) + (None, None, None, None, None)
+
+
+def flash_attention(q, k, v, cu_q, cu_k, max_q: int, scale: Optional[float] = None, max_k: Optional[int] = None):
+    """Differentiable causal attention with the queries of a sequence aligned to the end of its keys."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    i32 = lambda t: t if t.dtype == torch.int32 else t.to(torch.int32)
+    if max_k is None:
+        max_k = int((cu_k[1:] - cu_k[:-1]).max().item()) if cu_k is not cu_q else max_q
+    return _FlashAttn.apply(q, k, v, i32(cu_q), i32(cu_k), int(max_q), int(max_k), scale)
 
 
 def flash_bwd(dout, q, k, v, out, lse, cu, max_seqlen: int, scale: float, cu_k=None, max_k=None,
@@ -86,7 +96,7 @@ def varlen_attention_cuda(q, k, v, cu_seqlens, max_seqlen: int, scale: Optional[
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
     cu = cu_seqlens if cu_seqlens.dtype == torch.int32 else cu_seqlens.to(torch.int32)
     if native_flash_supported(q, k, v):
-        return _FlashAttn.apply(q, k, v, cu, int(max_seqlen), scale)
+        return _FlashAttn.apply(q, k, v, cu, cu, int(max_seqlen), int(max_seqlen), scale)
     from flash_attn import flash_attn_varlen_func
     return flash_attn_varlen_func(q, k, v, cu, cu, max_seqlen, max_seqlen, dropout_p=0.0, softmax_scale=scale,
                                   causal=True)

@@ -67,29 +67,37 @@ def logprob_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Te
     return lp, ent
 
 
-def varlen_attention(q, k, v, cu_seqlens, scale: Optional[float] = None, causal: bool = True):
-    """Packed-sequence causal GQA attention; ``q [T, hq, d]``, ``k/v [T, hkv, d]``
-    (semantics of flash_attn_varlen_func as used at cosmos_rl/policy/model/gpt/__init__.py:264-273)."""
+def varlen_attention(q, k, v, cu_seqlens, scale: Optional[float] = None, causal: bool = True, cu_k=None,
+                     return_lse: bool = False):
+    """Packed-sequence causal GQA attention; ``q [Tq, hq, d]``, ``k/v [Tk, hkv, d]``
+    (semantics of flash_attn_varlen_func as used at cosmos_rl/policy/model/gpt/__init__.py:264-273).
+    With ``cu_k`` the keys of a sequence may be longer than its queries; the queries are then aligned to the END
+    of the keys (query i sees keys ``0 .. i + len_k - len_q``)."""
     T, hq, d = q.shape
     hkv = k.shape[1]
     g = hq // hkv
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
-    out = torch.empty_like(q)
+    out = torch.zeros_like(q)
+    lse = torch.full((hq, T), float("inf"), dtype=torch.float32, device=q.device)
     cs = cu_seqlens.tolist()
+    ck = cs if cu_k is None else cu_k.tolist()
     for i in range(len(cs) - 1):
         s, e = cs[i], cs[i + 1]
-        if e <= s:
+        ks, ke = ck[i], ck[i + 1]
+        if e <= s or ke <= ks:
             continue
-        qi = q[s:e].transpose(0, 1).float()                       # [hq, L, d]
-        ki = k[s:e].transpose(0, 1).float().repeat_interleave(g, dim=0)
-        vi = v[s:e].transpose(0, 1).float().repeat_interleave(g, dim=0)
+        qi = q[s:e].transpose(0, 1).float()                       # [hq, Lq, d]
+        ki = k[ks:ke].transpose(0, 1).float().repeat_interleave(g, dim=0)
+        vi = v[ks:ke].transpose(0, 1).float().repeat_interleave(g, dim=0)
         sc = (qi @ ki.transpose(-1, -2)) * scale
         if causal:
-            L = e - s
-            mask = torch.ones(L, L, dtype=torch.bool, device=q.device).tril()
+            Lq, Lk = e - s, ke - ks
+            mask = torch.ones(Lq, Lk, dtype=torch.bool, device=q.device).tril(Lk - Lq)
             sc = sc.masked_fill(~mask, float("-inf"))
         out[s:e] = (torch.softmax(sc, dim=-1) @ vi).transpose(0, 1).to(q.dtype)
-    return out
+        if return_lse:
+            lse[:, s:e] = torch.logsumexp(sc, dim=-1)
+    return (out, lse) if return_lse else out
 
 
 def paged_decode(q, cache, block_table, seq_lens, scale: Optional[float] = None, v_transposed: bool = False):

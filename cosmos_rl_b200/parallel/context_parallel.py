@@ -1,0 +1,175 @@
+"""Context parallelism for packed (varlen) causal attention.
+
+Every sequence of the packed batch is split into ``cp`` equal contiguous chunks (sequences are padded to a
+multiple of ``cp`` tokens by the caller); rank ``r`` of the CP group holds chunk ``r`` of every sequence, so all
+token-wise layers (norms, projections, MLP, log-probs) run on ``T / cp`` tokens without communication. Attention
+is the only layer that mixes positions. Two exchanges are provided:
+
+* ``ulysses``: all-to-all that trades the sequence split for a head split (each rank attends the full sequences
+  with ``heads / cp`` heads) and back; the reference's CP mode (cosmos_rl/utils/ulysses.py:30-545). Needs the
+  number of KV heads to divide by ``cp``.
+* ``kv-gather``: every rank gathers the K/V chunks of the ranks before it (K/V are small under GQA) and runs ONE
+  attention call whose queries are aligned to the end of the keys of their sequence; the key prefix is exactly
+  what a ring schedule would stream past this rank. Gradients of the gathered K/V flow back through a
+  reduce-scatter. On GPUs the attention call is the tcgen05 kernel, which takes separate query/key offsets.
+
+Both are autograd functions over ``torch.distributed`` collectives, so they run on NCCL and (for tests) on gloo.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as F
+from ..ops import reference
+
+
+def split_for_cp(x: torch.Tensor, cu_seqlens: torch.Tensor, cp: int, rank: int) -> torch.Tensor:
+    """Rows of the packed tensor ``x [T, ...]`` that belong to ``rank``: chunk ``rank`` of every sequence."""
+    cs = cu_seqlens.tolist()
+    parts = []
+    for s, e in zip(cs[:-1], cs[1:]):
+        n = (e - s) // cp
+        assert n * cp == e - s, "sequence lengths must be multiples of the CP degree"
+        parts.append(x[s + rank * n:s + (rank + 1) * n])
+    return torch.cat(parts) if parts else x[:0]
+
+
+def local_cu_seqlens(cu_seqlens: torch.Tensor, cp: int) -> torch.Tensor:
+    return (cu_seqlens // cp).to(cu_seqlens.dtype)
+
+
+def _attention(q, k, v, cu_q, cu_k, max_q: int, scale: Optional[float]):
+    """Attention with queries aligned to the end of the keys; differentiable."""
+    if q.is_cuda:
+        from ..ops import attention
+        if attention.native_flash_supported(q, k, v):
+            return attention.flash_attention(q, k, v, cu_q, cu_k, max_q, scale)
+    return reference.varlen_attention(q, k, v, cu_q, scale, True, cu_k)
+
+
+# ------------------------------------------------------------------------------------------------ all-to-all
+class _SeqToHead(torch.autograd.Function):
+    """[T_local, H, d] (all heads, my chunk of every sequence) -> [T, H / cp, d] (my heads, whole sequences)."""
+
+    @staticmethod
+    def forward(ctx, x, cu_local, group, cp):
+        ctx.group, ctx.cp = group, cp
+        ctx.save_for_backward(cu_local)
+        return _a2a_seq_to_head(x, cu_local, group, cp)
+
+    @staticmethod
+    def backward(ctx, g):
+        (cu_local,) = ctx.saved_tensors
+        return _a2a_head_to_seq(g.contiguous(), cu_local, ctx.group, ctx.cp), None, None, None
+
+
+class _HeadToSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cu_local, group, cp):
+        ctx.group, ctx.cp = group, cp
+        ctx.save_for_backward(cu_local)
+        return _a2a_head_to_seq(x, cu_local, group, cp)
+
+    @staticmethod
+    def backward(ctx, g):
+        (cu_local,) = ctx.saved_tensors
+        return _a2a_seq_to_head(g.contiguous(), cu_local, ctx.group, ctx.cp), None, None, None
+
+
+def _interleave_index(cu_local: torch.Tensor, cp: int, device) -> torch.Tensor:
+    """Permutation that turns rank-major order ([rank][sequence][chunk rows]) into sequence-major order."""
+    cs = cu_local.tolist()
+    t_local = cs[-1]
+    idx = []
+    for s, e in zip(cs[:-1], cs[1:]):
+        for r in range(cp):
+            idx.append(torch.arange(r * t_local + s, r * t_local + e))
+    return torch.cat(idx).to(device) if idx else torch.zeros(0, dtype=torch.long, device=device)
+
+
+def _a2a_seq_to_head(x, cu_local, group, cp):
+    t, h, d = x.shape
+    assert h % cp == 0, "heads must divide by the CP degree for the all-to-all exchange"
+    send = x.view(t, cp, h // cp, d).transpose(0, 1).contiguous()          # [cp (dest rank), t, h/cp, d]
+    recv = torch.empty_like(send)                                            # [cp (source rank), t, h/cp, d]
+    dist.all_to_all_single(recv, send, group=group)
+    return recv.view(cp * t, h // cp, d)[_interleave_index(cu_local, cp, x.device)]
+
+
+def _a2a_head_to_seq(x, cu_local, group, cp):
+    T, hl, d = x.shape
+    t = T // cp
+    inv = torch.empty(T, dtype=torch.long, device=x.device)
+    inv[_interleave_index(cu_local, cp, x.device)] = torch.arange(T, device=x.device)
+    send = x[inv].view(cp, t, hl, d).contiguous()                            # [cp (dest = owner of the rows), t, hl, d]
+    recv = torch.empty_like(send)                                            # [cp (source = owner of the heads), ...]
+    dist.all_to_all_single(recv, send, group=group)
+    return recv.transpose(0, 1).reshape(t, cp * hl, d)
+
+
+def ulysses_attention(q, k, v, cu_local, max_local: int, group, scale: Optional[float] = None):
+    cp = dist.get_world_size(group)
+    qf = _SeqToHead.apply(q.contiguous(), cu_local, group, cp)
+    kf = _SeqToHead.apply(k.contiguous(), cu_local, group, cp)
+    vf = _SeqToHead.apply(v.contiguous(), cu_local, group, cp)
+    cu_full = cu_local * cp
+    o = _attention(qf, kf, vf, cu_full, cu_full, max_local * cp, scale)
+    return _HeadToSeq.apply(o.contiguous(), cu_local, group, cp)
+
+
+# ------------------------------------------------------------------------------------------------ KV gather
+class _GatherKV(torch.autograd.Function):
+    """All-gather the K (or V) chunks of the group and lay the chunks of ranks ``0 .. rank`` of every sequence
+    out contiguously. Backward: scatter the gradient back to chunk order and reduce-scatter it."""
+
+    @staticmethod
+    def forward(ctx, x, cu_local, group, cp, rank):
+        parts = [torch.empty_like(x) for _ in range(cp)]
+        dist.all_gather(parts, x.contiguous(), group=group)
+        full = torch.cat(parts)                                              # rank-major
+        cs = cu_local.tolist()
+        t_local = cs[-1]
+        idx = []
+        for s, e in zip(cs[:-1], cs[1:]):
+            for r in range(rank + 1):
+                idx.append(torch.arange(r * t_local + s, r * t_local + e))
+        idx = torch.cat(idx).to(x.device) if idx else torch.zeros(0, dtype=torch.long, device=x.device)
+        ctx.group, ctx.cp, ctx.shape = group, cp, full.shape
+        ctx.save_for_backward(idx)
+        return full[idx]
+
+    @staticmethod
+    def backward(ctx, g):
+        (idx,) = ctx.saved_tensors
+        full = torch.zeros(ctx.shape, dtype=g.dtype, device=g.device)
+        full[idx] = g
+        chunks = [c.contiguous() for c in full.chunk(ctx.cp, dim=0)]
+        out = torch.empty_like(chunks[0])
+        dist.reduce_scatter(out, chunks, group=ctx.group)
+        return out, None, None, None, None
+
+
+def kv_gather_attention(q, k, v, cu_local, max_local: int, group, scale: Optional[float] = None):
+    cp, rank = dist.get_world_size(group), dist.get_rank(group)
+    kg = _GatherKV.apply(k, cu_local, group, cp, rank)
+    vg = _GatherKV.apply(v, cu_local, group, cp, rank)
+    cu_k = cu_local * (rank + 1)
+    return _attention(q, kg, vg, cu_local, cu_k, max_local, scale)
+
+
+class ContextParallel:
+    """Attached to a model as ``model.cp``; the attention layer calls ``attention`` instead of the local kernel."""
+
+    def __init__(self, group, size: int, rank: int, mode: str = "kv-gather"):
+        assert mode in ("kv-gather", "ulysses")
+        self.group, self.size, self.rank, self.mode = group, size, rank, mode
+
+    def attention(self, q, k, v, cu_local, max_local: int, scale: Optional[float] = None):
+        fn = ulysses_attention if self.mode == "ulysses" else kv_gather_attention
+        return fn(q, k, v, cu_local, max_local, self.group, scale)
+
+    def shard(self, x, cu_seqlens):
+        return split_for_cp(x, cu_seqlens, self.size, self.rank)
