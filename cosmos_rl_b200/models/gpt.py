@@ -43,10 +43,18 @@ class GPTArgs:
     model_type: str = "qwen2"
     tp_size: int = 1
     tp_rank: int = 0
+    pp_size: int = 1        # pipeline stages: a stage owns a contiguous range of blocks (+ embedding / head)
+    pp_rank: int = 0
 
     def __post_init__(self):
         if self.head_dim is None:
             self.head_dim = self.dim // self.n_heads
+
+    def stage_layers(self) -> Tuple[int, int]:
+        """[lo, hi) block indices of this pipeline stage (earlier stages take the remainder)."""
+        base, rem = divmod(self.n_layers, self.pp_size)
+        lo = self.pp_rank * base + min(self.pp_rank, rem)
+        return lo, lo + base + (1 if self.pp_rank < rem else 0)
 
     @classmethod
     def from_hf_config(cls, c, **over) -> "GPTArgs":
@@ -196,9 +204,14 @@ class GPTWeightMapper(WeightMapper):
               "self_attn.q_norm": "self_attn.q_norm.weight", "self_attn.k_norm": "self_attn.k_norm.weight",
               "norm": "norm.weight"}
 
+    layer_offset = 0    # first block index of this pipeline stage
+
     def hf_names(self, local: str) -> List[str]:
         """HF parameter names a local parameter is assembled from (in row order)."""
         name = local
+        if self.layer_offset and name.startswith("layers."):
+            idx, rest = name[len("layers."):].split(".", 1)
+            name = f"layers.{int(idx) + self.layer_offset}.{rest}"
         for k, v in self.RENAME.items():
             if name == k or name.endswith("." + k):
                 name = name[: len(name) - len(k)] + v
@@ -219,10 +232,14 @@ class GPT(BaseModel):
         a = args
         assert a.vocab_size % a.tp_size == 0 or a.tp_size == 1
         self.v_local = a.vocab_size // a.tp_size if a.tp_size > 1 else a.vocab_size
-        self.embed_tokens = nn.Embedding(self.v_local, a.dim)
-        self.layers = nn.ModuleList([GPTBlock(a) for _ in range(a.n_layers)])
-        self.norm = nn.Parameter(torch.ones(a.dim))
-        if a.tie_word_embeddings:
+        lo, hi = a.stage_layers()
+        self.layer_offset = lo
+        self.is_first_stage, self.is_last_stage = a.pp_rank == 0, a.pp_rank == a.pp_size - 1
+        assert a.pp_size == 1 or not a.tie_word_embeddings, "tied embeddings live on both ends of a pipeline"
+        self.embed_tokens = nn.Embedding(self.v_local, a.dim) if self.is_first_stage else None
+        self.layers = nn.ModuleList([GPTBlock(a) for _ in range(hi - lo)])
+        self.norm = nn.Parameter(torch.ones(a.dim)) if self.is_last_stage else None
+        if a.tie_word_embeddings or not self.is_last_stage:
             self.lm_head = None
         else:
             self.lm_head = nn.Linear(a.dim, self.v_local, bias=False)
@@ -275,7 +292,7 @@ class GPT(BaseModel):
     def forward(self, input_ids: torch.Tensor, position_ids: torch.Tensor, cu_seqlens: torch.Tensor,
                 max_seqlen: int) -> torch.Tensor:
         """Packed forward: ``input_ids [T]`` -> final hidden states ``[T, H]`` (after the last norm)."""
-        h = self.embed(input_ids)
+        h = self.embed(input_ids) if self.is_first_stage else input_ids   # later stages receive hidden states
         res = None
         for layer in self.layers:
             if self.gradient_checkpointing == "selective" and torch.is_grad_enabled():
@@ -284,6 +301,8 @@ class GPT(BaseModel):
                 h, res = checkpoint(layer, h, res, position_ids, cu_seqlens, max_seqlen, self.tp, use_reentrant=False)
             else:
                 h, res = layer(h, res, position_ids, cu_seqlens, max_seqlen, self.tp)
+        if not self.is_last_stage:
+            return h + res if res is not None else h                        # one tensor crosses the stage boundary
         out, _ = F.rms_norm(h, self.norm, self.args.norm_eps, residual=res)
         return out
 

@@ -80,6 +80,7 @@ def load_hf_state(model, read, available, cfg: Dict[str, Any], tp: int = 1, r: i
     from .base import ModelRegistry
     mapper = ModelRegistry.mapper(cfg.get("model_type"))(cfg)
     mapper.ep_rank = getattr(getattr(model, "args", None), "ep_rank", 0)
+    mapper.layer_offset = getattr(model, "layer_offset", 0)
     missing = []
     with torch.no_grad():
         for name, p in model.named_parameters():
@@ -123,6 +124,7 @@ def hf_state_dict(model, hf_config: Dict[str, Any]) -> Dict[str, torch.Tensor]:
     """HF-named tensors of an unsharded (tp = 1) model: fused parameters are split back."""
     from .base import ModelRegistry
     mapper = ModelRegistry.mapper(hf_config.get("model_type"))(hf_config)
+    mapper.layer_offset = getattr(model, "layer_offset", 0)
     a = model.args
     out: Dict[str, torch.Tensor] = {}
     if hasattr(model, "export_items"):
@@ -150,6 +152,7 @@ def export_safetensors(model, hf_config: Dict[str, Any], output_dir: str, parall
     from safetensors.torch import save_file
     from .base import ModelRegistry
     mapper = ModelRegistry.mapper(hf_config.get("model_type"))(hf_config)
+    mapper.layer_offset = getattr(model, "layer_offset", 0)
     tp = parallel_dims.tp if parallel_dims is not None else 1
     rank = parallel_dims.global_rank if parallel_dims is not None else 0
     writer = rank == 0

@@ -57,3 +57,62 @@ def _cp_worker(rank, world, store, mode):
 @pytest.mark.parametrize("mode", ["kv-gather", "ulysses"])
 def test_context_parallel_matches_full_model(tmp_path, mode):
     _spawn(_cp_worker, 2, tmp_path, mode)
+
+
+def _pp_worker(rank, world, store):
+    import copy
+    from cosmos_rl_b200.parallel.pipeline import MicroBatch, PipelineStage, schedule_1f1b
+    _init(rank, world, store)
+    full = GPT(_tiny())
+    full.init_weights(0)
+    a = copy.deepcopy(full.args)
+    a.pp_size, a.pp_rank = world, rank
+    stage = GPT(a)
+    sd = full.state_dict()
+    off = stage.layer_offset
+    with torch.no_grad():
+        for name, p in stage.named_parameters():
+            src = name
+            if name.startswith("layers."):
+                idx, rest = name[len("layers."):].split(".", 1)
+                src = f"layers.{int(idx) + off}.{rest}"
+            p.copy_(sd[src])
+    g = torch.Generator().manual_seed(3)
+    mbs, ref_loss = [], 0.0
+    for lens in ([5, 9], [12], [3, 3, 4]):
+        T = sum(lens)
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)))
+        ids = torch.randint(0, 512, (T,), generator=g)
+        labels = torch.randint(0, 512, (T,), generator=g)
+        mbs.append(MicroBatch(ids, full.get_position_ids(cu, T), cu, max(lens), labels))
+
+    def loss_fn(model):
+        return lambda hidden, mb: -model.logprobs(hidden, mb.extra)[0].mean() / len(mbs)
+
+    for mb in mbs:
+        l = loss_fn(full)(full(mb.input_ids, mb.position_ids, mb.cu_seqlens, mb.max_seqlen), mb)
+        l.backward()
+        ref_loss += l.item()
+    ref = {n: p.grad for n, p in full.named_parameters()}
+    runner = PipelineStage(stage, dist.group.WORLD, rank, world, a.dim, torch.float32, torch.device("cpu"))
+    losses = runner.run(mbs, loss_fn(stage))
+    if rank == world - 1:
+        assert abs(sum(x.item() for x in losses) - ref_loss) < 1e-5
+    for name, p in stage.named_parameters():
+        src = name
+        if name.startswith("layers."):
+            idx, rest = name[len("layers."):].split(".", 1)
+            src = f"layers.{int(idx) + off}.{rest}"
+        assert torch.allclose(p.grad, ref[src], atol=1e-5), (name, (p.grad - ref[src]).abs().max())
+    # every forward precedes its backward and the number of in-flight micro-batches never exceeds the depth
+    for s in range(4):
+        steps, live = schedule_1f1b(s, 4, 8), 0
+        for kind, i in steps:
+            live += 1 if kind == "F" else -1
+            assert 0 <= live <= 4 - s
+        assert sorted(i for k, i in steps if k == "F") == list(range(8)) == sorted(i for k, i in steps if k == "B")
+    dist.destroy_process_group()
+
+
+def test_pipeline_1f1b_matches_full_model(tmp_path):
+    _spawn(_pp_worker, 2, tmp_path)
