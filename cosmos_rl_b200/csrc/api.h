@@ -175,6 +175,12 @@ struct B200CopyDesc {
 int b200_reshard_pull(const B200CopyDesc* descs_dev, const int* tile_prefix_dev, int n_desc, int total_tiles,
                       uint32_t* status, cudaStream_t stream);
 
+// Block-scaled fp8 GEMM (gemm_fp8_block.cu): A [M,K] e4m3 + sa [M, ldsa] (1 x 128 blocks), B [N,K] e4m3 +
+// sb [ceil(N/128), ldsb] (128 x 128 blocks), C [M,N] bf16.
+int b200_gemm_fp8_block(const void* A, const float* sa, const void* B, const float* sb, void* C, int M, int N, int K,
+                        long long lda, long long ldb, long long ldc, int ldsa, int ldsb, uint32_t* status, int num_sms,
+                        cudaStream_t stream);
+
 // Row-parallel GEMM fused with the tensor-parallel all-reduce (mode 0) or reduce-scatter over rows (mode 1)
 // through peer-mapped staging slots and arrival counters (tp_gemm.cu). ctrl: two local uint32 words.
 int b200_tp_gemm(const void* A, const void* W, void* out, const void* residual, int M, int N, int K, long long lda,

@@ -462,3 +462,31 @@ def quant_fp8_block(w: torch.Tensor, block_rows: int = 128):
                                                    native.ptr(scales), R, C, block_rows, native.stream()),
                  "quant_fp8_block")
     return q, scales
+
+
+def gemm_fp8_block(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: torch.Tensor,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``(aq * sa) @ (bq * sb)^T`` with aq [M, K] e4m3 + 1x128 scales [M, K/128] and bq [N, K] e4m3 + 128x128
+    scales [N/128, K/128]; fp32 accumulation with per-k-block promotion, bf16 result."""
+    if not aq.is_cuda:
+        a = reference.dequant_fp8_block(aq, sa, 1, 128)
+        b = reference.dequant_fp8_block(bq, sb, 128, 128)
+        return (a @ b.t()).to(torch.bfloat16)
+    M, K = aq.shape
+    N = bq.shape[0]
+    assert aq.stride(-1) == 1 and bq.stride(-1) == 1 and sa.stride(-1) == 1 and sb.stride(-1) == 1
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=aq.device)
+    st = native.status_word(aq.device)
+    dev = aq.device.index if aq.device.index is not None else torch.cuda.current_device()
+    native.check(native.lib().b200_gemm_fp8_block(native.ptr(aq), native.ptr(sa), native.ptr(bq), native.ptr(sb),
+                                                  native.ptr(out), M, N, K, aq.stride(0), bq.stride(0), out.stride(0),
+                                                  sa.stride(0), sb.stride(0), native.ptr(st), native.num_sms(dev),
+                                                  native.stream()), "gemm_fp8_block")
+    return out
+
+
+def fp8_linear(x: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor) -> torch.Tensor:
+    """Inference linear layer on block-scaled fp8 weights: the activation is quantised 1x128 on the fly."""
+    xq, xs = quant_fp8_block(x.contiguous(), 1)
+    return gemm_fp8_block(xq, xs, wq, ws)

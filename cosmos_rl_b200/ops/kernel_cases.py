@@ -65,6 +65,17 @@ def case_gemm(iters):
     report(f"gemm_bf16_nt {M}x{N}x{K}", t, flops=2.0 * M * N * K)
 
 
+def case_gemm_fp8(iters):
+    M, N, K = 8192, 8192, 8192
+    a, b = bf(M, K), bf(N, K, scale=0.05)
+    aq, sa = F.quant_fp8_block(a, 1)
+    bq, sb = F.quant_fp8_block(b, 128)
+    t = timed(lambda: F.gemm_fp8_block(aq, sa, bq, sb), iters)
+    report(f"gemm_fp8_block (1x128 / 128x128 scales) {M}x{N}x{K}", t, flops=2.0 * M * N * K)
+    t = timed(lambda: F.quant_fp8_block(a, 1), iters)
+    report(f"quant_fp8 1x128 activations {M}x{K}", t, nbytes=M * K * 3.0)
+
+
 def case_logprob(iters):
     T, V, H = 4096, 152064, 3584
     h, w = bf(T, H), bf(V, H, scale=0.02)
@@ -196,7 +207,7 @@ def case_flash(iters, B=16, L=4096, library=True):
     assert native.read_status(q.device) == 0
 
 
-CASES = {"flash": case_flash, "flash_small": case_flash_small, "gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
+CASES = {"gemm_fp8": case_gemm_fp8, "flash": case_flash, "flash_small": case_flash_small, "gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
          "reshard": case_reshard, "quant": case_quant, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu,
          "rope": case_rope, "adamw": case_adamw, "sample": case_sample}
 

@@ -455,3 +455,24 @@ def test_flash_attention_autograd_matches_reference(lens, hq, hkv):
                        1.0 / math.sqrt(d)).backward(go.float())
     err = (qkv.grad.float() - ref.grad).abs().max().item()
     assert err <= 3e-2 * ref.grad.abs().max().item() + 2e-2, err
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 520, 1040), (1024, 3584, 3584), (17, 256, 4096)])
+def test_gemm_fp8_block_scaled(M, N, K):
+    torch.manual_seed(5)
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    a[:, : K // 2] *= 8.0                                  # different scales along K: exercises the promotion
+    b = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    aq, sa = F.quant_fp8_block(a, 1)
+    bq, sb = F.quant_fp8_block(b, 128)
+    got = F.gemm_fp8_block(aq, sa, bq, sb)
+    torch.cuda.synchronize()
+    assert native.read_status(a.device) == 0
+    ref = R.dequant_fp8_block(aq, sa, 1, 128) @ R.dequant_fp8_block(bq, sb, 128, 128).t()   # same quantised inputs
+    err = (got.float() - ref).abs().max().item()
+    assert err <= 1e-2 * ref.abs().max().item() + 1e-3, err
+    full = a.float() @ b.float().t()                       # and fp8 itself is close to the bf16 product
+    assert (got.float() - full).abs().mean().item() <= 0.05 * full.abs().mean().item()
+    y = F.fp8_linear(a, bq, sb)
+    assert torch.equal(y, got)
