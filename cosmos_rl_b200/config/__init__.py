@@ -429,8 +429,10 @@ class B200Config(_Section):
     fused_logprob: bool = True           # tcgen05 fused lm_head + log-prob kernel
     nvls: bool = True                    # allow multimem (NVSwitch) reductions where available
     dlogits_chunk: int = 16384
-    recompute: str = "selective"         # with policy.model_gradient_checkpointing: "selective" (attention half +
-                                         # SwiGLU only) or "full" (whole block, least memory)
+    recompute: str = "auto"              # with policy.model_gradient_checkpointing: "selective" (attention half +
+                                         # SwiGLU only), "full" (whole block, least memory), "none", or "auto":
+                                         # no recomputation when the activations of one micro-batch fit in the
+                                         # memory that is free after weights and optimizer state, else selective
 
 
 class Config(_Section):

@@ -139,6 +139,7 @@ class GRPOTrainer(LLMTrainer):
         for ch in chunks:
             sub = [samples[i] for i in ch]
             chunk_batches.append([self._pack([sub[i] for i in idxs]) for idxs in self._mini_batches(sub)])
+        self.resolve_recompute(max(int(b["input_ids"].numel()) for bs in chunk_batches for b in bs))
 
         ref_lps = old_lps = None
         if self.tp_cfg.kl_beta != 0.0:

@@ -52,8 +52,9 @@ class LLMTrainer(Trainer):
         dp = parallel_dims.dp_shard
         self.flat = FlatParams(model, self.param_dtype, self.device, shard_multiple=dp,
                                allocator=kw.get("allocator"))
-        model.gradient_checkpointing = (config.b200.recompute if config.policy.model_gradient_checkpointing
-                                        else False)
+        rc = config.b200.recompute if config.policy.model_gradient_checkpointing else "none"
+        self._recompute_auto = rc == "auto"
+        model.gradient_checkpointing = {"none": False, "auto": "selective"}.get(rc, rc)
         if tp > 1:
             from ...parallel.tp import TensorParallel
             model.tp = TensorParallel(parallel_dims.group("tp"), tp, parallel_dims.tp_coord)
@@ -72,6 +73,27 @@ class LLMTrainer(Trainer):
         self.weights_ready = False
 
     # ------------------------------------------------------------------
+    def resolve_recompute(self, max_tokens: int) -> None:
+        """``recompute = "auto"``: decide once, before the first backward pass, from the memory that is actually
+        free. Activations kept per token and block without recomputation: the two norm inputs and residuals (4 H),
+        q/k/v and the attention output, the gate/up product (2 I) and the SwiGLU output (I), all bf16."""
+        if not self._recompute_auto:
+            return
+        self._recompute_auto = False
+        a = getattr(self.model, "args", None)
+        if self.device.type != "cuda" or a is None or not hasattr(a, "ffn_dim"):
+            return
+        tp = max(1, getattr(a, "tp_size", 1))
+        per_tok = (4 * a.dim + ((2 * a.n_heads + 2 * a.n_kv_heads) * a.head_dim + 3 * a.ffn_dim) // tp) * 2
+        need = int(max_tokens * len(self.model.layers) * per_tok * 1.15)
+        need += self.config.b200.dlogits_chunk * (a.vocab_size // tp) * 6 + (6 << 30)   # lm_head backward, slack
+        free, _ = torch.cuda.mem_get_info(self.device)
+        free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+        choice = False if need < free else "selective"
+        self.model.gradient_checkpointing = choice
+        logger.info("[Policy] recompute=auto -> %s (activations need %.1f GB, %.1f GB free)",
+                    choice or "none", need / 2**30, free / 2**30)
+
     def _apply_trainable_patterns(self) -> None:
         import re
         pc = self.config.policy
