@@ -184,8 +184,12 @@ class GPTBlock(nn.Module):
         ``recompute="selective"`` keeps the output of the gate/up GEMM (the expensive one) and recomputes only
         the attention half of the block (12 % of its forward FLOPs) and the SwiGLU product in backward, instead
         of re-running the whole block as full activation checkpointing does."""
-        if recompute == "selective" and torch.is_grad_enabled():
-            x, res = checkpoint(self._attn_part, h, res, positions, cu_seqlens, max_seqlen, tp, use_reentrant=False)
+        if recompute in ("selective", "swiglu") and torch.is_grad_enabled():
+            if recompute == "swiglu":      # keep the attention half's activations, recompute only the SwiGLU product
+                x, res = self._attn_part(h, res, positions, cu_seqlens, max_seqlen, tp)
+            else:
+                x, res = checkpoint(self._attn_part, h, res, positions, cu_seqlens, max_seqlen, tp,
+                                    use_reentrant=False)
             gu = _linear(x, self.mlp.gate_up_proj.weight)
             act = checkpoint(F.swiglu, gu, use_reentrant=False)
             h = tp.row_linear(act, self.mlp.down_proj.weight) if tp is not None else \
@@ -295,8 +299,9 @@ class GPT(BaseModel):
         h = self.embed(input_ids) if self.is_first_stage else input_ids   # later stages receive hidden states
         res = None
         for layer in self.layers:
-            if self.gradient_checkpointing == "selective" and torch.is_grad_enabled():
-                h, res = layer(h, res, position_ids, cu_seqlens, max_seqlen, self.tp, recompute="selective")
+            if self.gradient_checkpointing in ("selective", "swiglu") and torch.is_grad_enabled():
+                h, res = layer(h, res, position_ids, cu_seqlens, max_seqlen, self.tp,
+                               recompute=self.gradient_checkpointing)
             elif self.gradient_checkpointing and torch.is_grad_enabled():
                 h, res = checkpoint(layer, h, res, position_ids, cu_seqlens, max_seqlen, self.tp, use_reentrant=False)
             else:

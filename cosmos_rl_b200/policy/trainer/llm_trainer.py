@@ -84,15 +84,17 @@ class LLMTrainer(Trainer):
         if self.device.type != "cuda" or a is None or not hasattr(a, "ffn_dim"):
             return
         tp = max(1, getattr(a, "tp_size", 1))
-        per_tok = (4 * a.dim + ((2 * a.n_heads + 2 * a.n_kv_heads) * a.head_dim + 3 * a.ffn_dim) // tp) * 2
-        need = int(max_tokens * len(self.model.layers) * per_tok * 1.15)
-        need += self.config.b200.dlogits_chunk * (a.vocab_size // tp) * 6 + (6 << 30)   # lm_head backward, slack
+        attn = 4 * a.dim + ((2 * a.n_heads + 2 * a.n_kv_heads) * a.head_dim) // tp     # elements per token and block
+        fixed = self.config.b200.dlogits_chunk * (a.vocab_size // tp) * 6 + (6 << 30)     # lm_head backward, slack
+        n = max_tokens * len(self.model.layers) * 2 * 1.15
+        need_none = int(n * (attn + 3 * a.ffn_dim // tp)) + fixed
+        need_swiglu = int(n * (attn + 2 * a.ffn_dim // tp)) + fixed                    # SwiGLU output recomputed
         free, _ = torch.cuda.mem_get_info(self.device)
         free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
-        choice = False if need < free else "selective"
+        choice = False if need_none < free else ("swiglu" if need_swiglu < free else "selective")
         self.model.gradient_checkpointing = choice
-        logger.info("[Policy] recompute=auto -> %s (activations need %.1f GB, %.1f GB free)",
-                    choice or "none", need / 2**30, free / 2**30)
+        logger.info("[Policy] recompute=auto -> %s (no recomputation needs %.1f GB, SwiGLU-only %.1f GB, %.1f GB free)",
+                    choice or "none", need_none / 2**30, need_swiglu / 2**30, free / 2**30)
 
     def _apply_trainable_patterns(self) -> None:
         import re

@@ -45,13 +45,14 @@ def test_recompute_modes_give_identical_gradients():
     ids, cu = torch.randint(0, 32000, (20,)), torch.tensor([0, 8, 20])
     lab = torch.randint(0, 32000, (20,))
     grads = {}
-    for mode in (False, "full", "selective"):
+    for mode in (False, "full", "selective", "swiglu"):
         m.gradient_checkpointing = mode
         m.zero_grad()
         lp, _ = m.logprobs(m(ids, m.get_position_ids(cu, 20), cu, 12), lab)
         lp.sum().backward()
         grads[mode] = torch.cat([p.grad.flatten() for p in m.parameters()])
     assert torch.equal(grads[False], grads["full"]) and torch.equal(grads[False], grads["selective"])
+    assert torch.equal(grads[False], grads["swiglu"])
 
 
 @pytest.mark.parametrize("kind", ["dense", "moe"])
