@@ -2,6 +2,7 @@
 from .base import BaseModel, ModelRegistry, WeightMapper  # noqa: F401
 from . import gpt  # noqa: F401
 from . import qwen3_moe  # noqa: F401
+from . import hf_model  # noqa: F401  (fallback for every other transformers causal LM)
 
 
 def named_architectures():

@@ -228,7 +228,7 @@ class GPTWeightMapper(WeightMapper):
         return [name]
 
 
-@ModelRegistry.register(GPTWeightMapper, default=True)
+@ModelRegistry.register(GPTWeightMapper)
 class GPT(BaseModel):
     def __init__(self, args: GPTArgs):
         super().__init__()

@@ -29,7 +29,7 @@ from ..reward.dispatcher import LocalRewardCalculator, RewardDispatcher
 from ..utils import constant
 from ..utils.logging import logger
 from .base import RolloutRegistry
-from . import b200_rollout  # noqa: F401  (registers the built-in backend)
+from . import b200_rollout, hf_rollout  # noqa: F401  (register the built-in backends)
 
 
 class DisaggregatedRolloutControlWorker(CommMixin):
@@ -47,6 +47,13 @@ class DisaggregatedRolloutControlWorker(CommMixin):
         self.data_fetcher = WorkerDataFetcher(config, ds, vds)
         self.tokenizer = tokenizer
         backend = config.rollout.backend
+        if backend != "hf":
+            # families without a native model are served by the generic transformers wrapper and its backend
+            from ..models import hf_io
+            from ..models.base import ModelRegistry
+            mtype = hf_io.load_hf_config(config.policy.model_name_or_path, config.custom.get("model_config")).get("model_type")
+            if ModelRegistry.get(mtype).__name__ == "HFModel":
+                backend = "hf"
         self.rollout = RolloutRegistry.get(backend)(config, parallel_dims, self.device, tokenizer=tokenizer)
         self.rollout.init_engine(load_format="dummy", seed=(config.rollout.seed or 0) + hash(self.replica_name) % 9973)
         mt = getattr(self.rollout.model.args, "model_type", "hfmodel")

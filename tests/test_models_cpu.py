@@ -158,3 +158,34 @@ def test_named_architectures_shapes():
     with torch.device("meta"):
         n = sum(p.numel() for p in GPT(a).parameters())
     assert 7.5e9 < n < 7.7e9
+
+
+@pytest.mark.parametrize("cfg", [
+    {"model_type": "deepseek_v3", "vocab_size": 512, "hidden_size": 64, "intermediate_size": 128,
+     "moe_intermediate_size": 32, "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 4,
+     "n_routed_experts": 4, "n_shared_experts": 1, "num_experts_per_tok": 2, "first_k_dense_replace": 1,
+     "kv_lora_rank": 16, "q_lora_rank": 24, "qk_rope_head_dim": 8, "qk_nope_head_dim": 8, "v_head_dim": 16,
+     "n_group": 1, "topk_group": 1},
+    {"model_type": "mistral", "vocab_size": 512, "hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 2,
+     "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16},
+])
+def test_generic_hf_wrapper_packed_forward_and_training(cfg):
+    """Families without a native implementation go through the transformers wrapper (registry fallback)."""
+    from cosmos_rl_b200.models.base import ModelRegistry
+    from cosmos_rl_b200.parallel.flat import FlatParams
+    with torch.device("meta"):
+        m = ModelRegistry.build_model(dict(cfg))
+    assert type(m).__name__ == "HFModel"
+    flat = FlatParams(m, torch.float32, torch.device("cpu"))
+    m.init_weights(0)
+    m.eval()
+    a, b = torch.randint(0, 512, (7,)), torch.randint(0, 512, (12,))
+    ids, cu = torch.cat([a, b]), torch.tensor([0, 7, 19])
+    packed = m(ids, m.get_position_ids(cu, 19), cu, 12)
+    with torch.no_grad():
+        ha = m(a, torch.arange(7), torch.tensor([0, 7]), 7)
+        hb = m(b, torch.arange(12), torch.tensor([0, 12]), 12)
+    assert torch.allclose(packed.detach(), torch.cat([ha, hb]), atol=1e-4)
+    lp, ent = m.logprobs(packed, torch.randint(0, 512, (19,)))
+    lp.sum().backward()
+    assert flat.grad.abs().sum() > 0 and torch.isfinite(flat.grad).all()
