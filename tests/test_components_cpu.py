@@ -214,3 +214,57 @@ def test_payload_transport_registry_prefetch_and_discard():
     assert sk.healthy(["a", "b"]) == ["b"] and sk.healthy(["a"]) == ["a"] and len(sk) == 1
     now[0] = 11.0
     assert not sk.is_quarantined("a") and len(sk) == 0
+
+
+def test_launcher_gpu_math_and_placement():
+    import types
+    from cosmos_rl_b200.launcher import launch_all as L
+    c = Config.from_dict({"policy": {"model_name_or_path": "tiny-qwen2", "parallelism": {"tp_size": 1, "dp_shard_size": 4,
+                                                                                     "n_init_replicas": 1}},
+                          "rollout": {"parallelism": {"tp_size": 2, "n_init_replicas": 2}},
+                          "train": {"train_policy": {"type": "grpo"}}})
+    assert L.gpus_per_replica(c.policy.parallelism) == 4 and L.gpus_per_replica(c.rollout.parallelism) == 2
+    args = types.SimpleNamespace(policy=None, rollout=None, reference=None, p2r_ratio=None)
+    assert L.replica_counts(c, args, 8) == (1, 2, 0)
+    place = L.place_replicas(1, 2, 0, c, 8, colocated=False)
+    assert [p["gpus"] for p in place] == [[0, 1, 2, 3], [4, 5], [6, 7]]
+    with pytest.raises(ValueError):
+        L.place_replicas(1, 3, 0, c, 8, colocated=False)          # one rollout replica too many for the node
+    args.p2r_ratio = "1:2"
+    assert L.replica_counts(c, args, 16) == (2, 4, 0)              # two units of (4 + 2 * 2) GPUs
+    c.train.train_policy.type = "sft"
+    args.p2r_ratio = None
+    assert L.replica_counts(c, args, 8)[1] == 0                    # SFT launches no rollout replicas
+    import signal
+    assert L.is_coordinated_controller_exit(-signal.SIGTERM) and not L.is_coordinated_controller_exit(1)
+    sock, port = L.reserve_port(None)
+    assert port > 0 and sock.get_inheritable()
+    sock.close()
+
+
+def test_reward_calculator_dapo_validity_and_shared_prefix():
+    from cosmos_rl_b200.dispatcher.data.schema import RLPayload
+    from cosmos_rl_b200.reward.dispatcher import LocalRewardCalculator, RewardDispatcher, shared_prefix_ignore
+    c = Config.from_dict({"train": {"train_policy": {"type": "grpo", "variant": "dapo",
+                                                     "reward_function": ["even_token_fraction"],
+                                                     "min_filter_prefix_tokens": 2}},
+                          "rollout": {"max_response_length": 8}})
+    calc = LocalRewardCalculator(c)
+    def payload(tok_lists):
+        return RLPayload(prompt=[1, 2], prompt_idx=0, completions=tok_lists,
+                         completion_token_ids=[[[t] for t in tl] for tl in tok_lists])
+    same = calc.compute(payload([[2, 4], [6, 8]]))                 # identical rewards: no signal, group dropped
+    assert same.valid is False and same.rewards == [1.0, 1.0]
+    mixed = calc.compute(payload([[2, 4, 6, 1], [2, 4, 6, 8], [1, 3, 5, 7]]))
+    assert mixed.valid is True and abs(sum(mixed.advantages)) < 1e-5
+    assert mixed.n_ignore_prefix_tokens == [3, 3, 0]               # first two share 3 tokens, rewards differ
+    assert shared_prefix_ignore([[1, 2, 3], [1, 2, 4]], [0.0, 0.0], 1) == [0, 0]
+    d = RewardDispatcher(calc, num_workers=1)
+    d.enqueue_rewards_cal([payload([[2, 2], [1, 1]])], step=3)
+    got = []
+    for _ in range(200):
+        got += d.dequeue(block=True, timeout=0.05)
+        if got:
+            break
+    assert len(got) == 1 and got[0].rewards == [1.0, 0.0]
+    d.shutdown()

@@ -116,3 +116,41 @@ def _pp_worker(rank, world, store):
 
 def test_pipeline_1f1b_matches_full_model(tmp_path):
     _spawn(_pp_worker, 2, tmp_path)
+
+
+def _failure_worker(rank, world, store_path):
+    """Host-side failure injection: rank 1 leaves between two steps (no collective in flight); rank 0's next
+    collective ends with CommTimeout within its limit, the communicator is aborted and a smaller one is built."""
+    import time
+    from datetime import timedelta
+    from cosmos_rl_b200.parallel import dyncomm
+    store = dist.FileStore(store_path, world)
+    events = []
+    dyncomm.add_phase_observer(lambda name, phase, info: events.append((name, phase)))
+    comm = dyncomm.DynComm("policy-mesh-v1", store, rank, world, torch.device("cpu"), timeout_s=2.0)
+    t = torch.ones(4) * (rank + 1)
+    comm.all_reduce(t)                                   # step 1: everybody is here
+    assert torch.equal(t, torch.full((4,), 3.0))
+    store.set(f"step1_done_{rank}", b"1")
+    if rank == 1:
+        store.wait(["step1_done_0"], timedelta(seconds=20))
+        return                                           # rank 1 "dies" cleanly between steps
+    store.wait(["step1_done_1"], timedelta(seconds=20))
+    time.sleep(0.2)
+    t0 = time.time()
+    with pytest.raises(dyncomm.CommTimeout):
+        comm.all_reduce(torch.ones(4))                   # step 2: the peer never joins
+    assert time.time() - t0 < 15.0
+    assert comm.aborted and "policy-mesh-v1" not in dyncomm.live_comms()
+    assert ("policy-mesh-v1", "abort") in events
+    with pytest.raises(dyncomm.CommTimeout):
+        comm.all_reduce(torch.ones(4))                   # an aborted communicator refuses further work at once
+    solo = dyncomm.DynComm("policy-mesh-v2", store, 0, 1, torch.device("cpu"), timeout_s=2.0)   # mesh rebuilt
+    x = torch.ones(4)
+    solo.all_reduce(x)
+    assert torch.equal(x, torch.ones(4))
+    solo.destroy()
+
+
+def test_rank_leaving_between_steps_times_out_and_mesh_is_rebuilt(tmp_path):
+    mp.spawn(_failure_worker, args=(2, str(tmp_path / "fstore")), nprocs=2, join=True)
