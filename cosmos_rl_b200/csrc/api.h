@@ -181,6 +181,12 @@ int b200_gemm_fp8_block(const void* A, const float* sa, const void* B, const flo
                         long long lda, long long ldb, long long ldc, int ldsa, int ldsb, uint32_t* status, int num_sms,
                         cudaStream_t stream);
 
+// Column-parallel GEMM fused with the tensor-parallel all-gather of its input rows (ag_gemm.cu).
+int b200_ag_gemm(const void* x, const void* W, void* out, int M, int N, int K, long long ldx, long long ldw,
+                 long long ldc, void* const* gathered_ptrs, void* const* flag_ptrs, uint32_t* ctrl, int tp, int rank,
+                 long long set_elems, int max_blocks, unsigned long long wait_ns, uint32_t* status, int num_sms,
+                 cudaStream_t stream);
+
 // Row-parallel GEMM fused with the tensor-parallel all-reduce (mode 0) or reduce-scatter over rows (mode 1)
 // through peer-mapped staging slots and arrival counters (tp_gemm.cu). ctrl: two local uint32 words.
 int b200_tp_gemm(const void* A, const void* W, void* out, const void* residual, int M, int N, int K, long long lda,

@@ -48,10 +48,14 @@ struct TileInfo {
 // over the token dimension) need, so no transposed copies are ever made.
 // SIDE_WARPS > 0: the CTA is launched with GEMM_THREADS + 32 * SIDE_WARPS threads and warps 6.. run
 // Epi::side() concurrently with the pipeline (used by the fused GEMM + cross-GPU reduction kernel).
-template <bool A_MN_ = false, bool B_MN_ = false, bool A_3D_ = false, bool B_3D_ = false, int SIDE_WARPS_ = 0>
+// PRODUCER_HOOK: the TMA producer calls sched.before_tile_load(tile, ep, status) before the first load of a tile
+// and gives up (abort) when it returns false (used to wait for operand rows that another GPU is still sending).
+template <bool A_MN_ = false, bool B_MN_ = false, bool A_3D_ = false, bool B_3D_ = false, int SIDE_WARPS_ = 0,
+          bool PRODUCER_HOOK_ = false>
 struct GemmTraits {
   static constexpr bool A_MN = A_MN_, B_MN = B_MN_, A_3D = A_3D_, B_3D = B_3D_;
   static constexpr int SIDE_WARPS = SIDE_WARPS_;
+  static constexpr bool PRODUCER_HOOK = PRODUCER_HOOK_;
 };
 
 // Default schedule: grouped raster over (m, n) tiles, strided over the grid.
@@ -143,6 +147,12 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
       uint32_t stage = 0, phase = 0;
       TileInfo t;
       for (int it = 0; sched.get(it, t) && !*abort_flag; ++it) {
+        if constexpr (Traits::PRODUCER_HOOK) {
+          if (!sched.before_tile_load(t, ep, status)) {
+            *abort_flag = 1;
+            break;
+          }
+        }
         for (int kb = 0; kb < t.num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
             atomicCAS(status, ST_OK, ST_TIMEOUT_EMPTY);

@@ -95,6 +95,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// Orders generic-proxy accesses (plain loads / stores, also those of another GPU made visible by an acquire) with
+// async-proxy accesses (TMA) to global memory.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------
 // TMA (tiled, 2D / 3D). Loads never use cluster multicast.

@@ -78,6 +78,8 @@ _SIGS = {
     "b200_flash_fwd": [c_void_p] * 7 + [c_int] * 6 + [c_longlong] * 4 + [c_int, c_int, c_float, c_void_p, c_void_p],
     "b200_flash_bwd": [c_void_p] * 12 + [c_int] * 6 + [c_longlong] * 7 + [c_int, c_int, c_float, c_void_p, c_void_p],
     "b200_gemm_fp8_block": [c_void_p] * 5 + [c_int] * 3 + [c_longlong] * 3 + [c_int, c_int, c_void_p, c_int, c_void_p],
+    "b200_ag_gemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p,
+                     c_void_p, c_void_p, c_int, c_int, c_longlong, c_int, c_ulonglong, c_void_p, c_int, c_void_p],
     "b200_grpo_loss": [c_void_p] * 6 + [c_int, c_float, c_float, c_float, c_int, c_float, c_int, c_int, c_float,
                        c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200_sample": [c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_ulonglong,

@@ -20,6 +20,68 @@ from .peer import PeerBuffer, PeerMapping
 _HEADER = 256
 
 
+class FusedAllGatherGemm:
+    """Workspace of ``csrc/ag_gemm.cu``: per rank two call-counter words, per-row-block arrival counters (two sets)
+    and the gathered-activation buffer (two sets of ``max_rows x max_k`` bf16)."""
+
+    def __init__(self, group, size: int, rank: int, device: torch.device, max_rows: int, max_k: int,
+                 wait_s: float = 10.0):
+        assert 1 <= size <= 8 and max_rows % (128 * size) == 0
+        self.group, self.size, self.rank, self.device = group, size, rank, device
+        self.max_blocks = max_rows // 128
+        self.set_elems = max_rows * max_k
+        self.flag_bytes = ((2 * self.max_blocks * 4 + 255) // 256) * 256
+        self.nbytes = _HEADER + self.flag_bytes + 2 * self.set_elems * 2
+        self.wait_ns = int(wait_s * 1e9)
+        self.buf = PeerBuffer(self.nbytes, device)
+        torch.cuda.synchronize(device)
+        handles: List[Optional[bytes]] = [None] * size
+        dist.all_gather_object(handles, self.buf.export(), group=group)
+        self.maps: List[Optional[PeerMapping]] = []
+        bases = []
+        for r, h in enumerate(handles):
+            if r == rank:
+                self.maps.append(None)
+                bases.append(self.buf.ptr)
+            else:
+                m = PeerMapping(h, self.nbytes, device)
+                self.maps.append(m)
+                bases.append(m.ptr)
+        arr = ctypes.c_void_p * 8
+        self._flags = arr(*[b + _HEADER for b in bases] + [None] * (8 - size))
+        self._gathered = arr(*[b + _HEADER + self.flag_bytes for b in bases] + [None] * (8 - size))
+        self._ctrl = self.buf.ptr
+        dist.barrier(group=group)
+
+    def fits(self, rows_total: int, k: int) -> bool:
+        return (rows_total % (128 * self.size) == 0 and rows_total // 128 <= self.max_blocks
+                and rows_total * k <= self.set_elems and k % 8 == 0)
+
+    def gemm(self, x_local: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``gather(x) @ w^T``: x_local [M / tp, K] are this rank's rows, w [N, K]; returns [M, N] bf16."""
+        assert x_local.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+        assert x_local.stride(-1) == 1 and w.stride(-1) == 1
+        m_local, K = x_local.shape
+        M, N = m_local * self.size, w.shape[0]
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=x_local.device)
+        st = native.status_word(x_local.device)
+        dev = x_local.device.index if x_local.device.index is not None else torch.cuda.current_device()
+        native.check(native.lib().b200_ag_gemm(
+            native.ptr(x_local), native.ptr(w), native.ptr(out), M, N, K, x_local.stride(0), w.stride(0),
+            out.stride(0), self._gathered, self._flags, self._ctrl, self.size, self.rank, self.set_elems,
+            self.max_blocks, self.wait_ns, native.ptr(st), native.num_sms(dev), native.stream()), "ag_gemm")
+        return out
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for m in self.maps:
+            if m is not None:
+                m.close()
+        self.buf.free()
+
+
 class FusedTP:
     def __init__(self, group, size: int, rank: int, device: torch.device, max_rows: int, max_cols: int,
                  wait_s: float = 10.0):

@@ -16,7 +16,7 @@ import torch.distributed as dist
 from ..ops import functional as F
 from ..ops import native
 from ..ops.kernel_cases import peaks
-from .tp_fused import FusedTP
+from .tp_fused import FusedAllGatherGemm, FusedTP
 
 NVLINK_BPS = 770e9
 
@@ -48,7 +48,7 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=grp)
         return t.item() * 1e-3
 
-    for M in (64, 512, 2048, 8192, 16384):
+    for M in (512, 8192):
         pool = max(2, int(300e6 // (N * K * 2)) + 1)
         ws = [(torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16) for _ in range(pool)]
         a = torch.randn(M, K, device=dev).to(torch.bfloat16)
@@ -85,6 +85,32 @@ def main() -> None:
         if rank == 0:
             print(line, flush=True)
         del ws
+    # ---- all-gather -> column-parallel GEMM (sequence-parallel input of gate/up: N = 2 * 18944 / tp, K = 3584)
+    Kc, Nc = 3584, 2 * 18944 // world
+    ag = FusedAllGatherGemm(grp, world, rank, dev, max_rows=16384, max_k=Kc)
+    for M in (2048, 8192, 16384):
+        pool = max(2, int(300e6 // (Nc * Kc * 2)) + 1)
+        ws = [(torch.randn(Nc, Kc, device=dev) * 0.02).to(torch.bfloat16) for _ in range(pool)]
+        xl = torch.randn(M // world, Kc, device=dev).to(torch.bfloat16)
+        full = torch.empty(M, Kc, dtype=torch.bfloat16, device=dev)
+        iters = 20 if M <= 2048 else 8
+
+        def lib_ag(i):
+            dist.all_gather_into_tensor(full, xl, group=grp)
+            torch.nn.functional.linear(full, ws[i % pool])
+
+        t_fused = timed(lambda i: ag.gemm(xl, ws[i % pool]), iters)
+        t_lib = timed(lib_ag, iters)
+        t_own = timed(lambda i: F.gemm_nt(full, ws[i % pool]), iters)
+        flops = 2.0 * M * Nc * Kc
+        roof = max(flops / gemm_peak, (world - 1) / world * M * Kc * 2 / NVLINK_BPS)
+        assert native.read_status(dev) == 0
+        if rank == 0:
+            print(f"M={M:6d} all-gather->gemm [N={Nc}, K={Kc}]: fused {t_fused * 1e6:8.1f} us | all_gather+linear "
+                  f"{t_lib * 1e6:8.1f} us | own gemm on gathered input {t_own * 1e6:8.1f} us | roofline "
+                  f"{roof * 1e6:.1f} us -> {roof / t_fused:.2f} of {kind} roofline", flush=True)
+        del ws
+    ag.close()
     ftp.close()
     f1.close()
     from ..utils.dist_util import safe_destroy

@@ -163,6 +163,27 @@ def main():
               flush=True)
     ftp.close()
 
+    # ------------------------------------------------------------ 2c. fused all-gather -> column-parallel GEMM
+    from cosmos_rl_b200.parallel.tp_fused import FusedAllGatherGemm
+    ag = FusedAllGatherGemm(grp, world, rank, dev, max_rows=4096, max_k=3584, wait_s=3.0)
+    for call, (M, N, K) in enumerate([(256, 512, 512), (4096, 2304, 3584), (1024, 9472, 3584), (256, 96, 1024),
+                                      (2048, 640, 2040)]):
+        xl = torch.randn(M // world, K, device=dev, generator=gen).to(torch.bfloat16)
+        w = (torch.randn(N, K, device=dev, generator=gen) * 0.05).to(torch.bfloat16)
+        parts = [torch.empty_like(xl) for _ in range(world)]
+        dist.all_gather(parts, xl, group=grp)
+        want = torch.cat(parts).float() @ w.float().t()
+        got = ag.gemm(xl, w)
+        torch.cuda.synchronize(dev)
+        st = native.read_status(dev)
+        assert st == 0, f"fused ag gemm call {call}: status {st}"
+        err = (got.float() - want).abs().max().item()
+        tol = 1e-2 * want.abs().max().item() + 1e-3
+        assert err <= tol, f"fused ag gemm call {call} {(M, N, K)}: max err {err} > {tol}"
+    if rank == 0:
+        print("fused all-gather -> gemm: ok", flush=True)
+    ag.close()
+
     # ------------------------------------------------------------ 3. TP engine == single-GPU engine (greedy)
     rm.tp = TensorParallel(grp, world, rank)
     rm.tp.fused_min_rows = 1          # exercise the fused GEMM + all-reduce kernel at the test's small shapes
