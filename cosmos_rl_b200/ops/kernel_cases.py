@@ -76,6 +76,27 @@ def case_gemm_fp8(iters):
     report(f"quant_fp8 1x128 activations {M}x{K}", t, nbytes=M * K * 3.0)
 
 
+def case_moe(iters):
+    """One MoE layer of the Qwen3-30B-A3B architecture: 128 experts, top-8, hidden 2048, expert FFN 768."""
+    from . import moe
+    T, H, I, E, k = 16384, 2048, 768, 128, 8
+    x = bf(T, H).requires_grad_(True)
+    wgu = bf(E, 2 * I, H, scale=0.02).requires_grad_(True)
+    wd = bf(E, H, I, scale=0.02).requires_grad_(True)
+    logits = torch.randn(T, E, device="cuda")
+    t = timed(lambda: moe.route_topk(logits, k), iters)
+    report(f"moe route_topk T={T} E={E} k={k}", t, nbytes=T * E * 4.0)
+    probs, idx = moe.route_topk(logits, k)
+    flops_fwd = 2.0 * T * k * H * 3 * I
+    with torch.no_grad():
+        t = timed(lambda: moe.moe_experts(x, probs, idx, wgu, wd), iters)
+    report(f"moe experts fwd (permute + grouped GEMM + SwiGLU + grouped GEMM + combine) T={T}", t, flops=flops_fwd)
+    y = moe.moe_experts(x, probs, idx, wgu, wd)
+    g = torch.randn_like(y)
+    t = timed(lambda: torch.autograd.grad(y, (x, wgu, wd), g, retain_graph=True), iters)
+    report(f"moe experts bwd (dgrad + wgrad grouped GEMMs, recomputed SwiGLU) T={T}", t, flops=2 * flops_fwd)
+
+
 def case_logprob(iters):
     T, V, H = 4096, 152064, 3584
     h, w = bf(T, H), bf(V, H, scale=0.02)
@@ -207,7 +228,7 @@ def case_flash(iters, B=16, L=4096, library=True):
     assert native.read_status(q.device) == 0
 
 
-CASES = {"gemm_fp8": case_gemm_fp8, "flash": case_flash, "flash_small": case_flash_small, "gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
+CASES = {"moe": case_moe, "gemm_fp8": case_gemm_fp8, "flash": case_flash, "flash_small": case_flash_small, "gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
          "reshard": case_reshard, "quant": case_quant, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu,
          "rope": case_rope, "adamw": case_adamw, "sample": case_sample}
 
