@@ -128,6 +128,12 @@ int b200_kv_append_vt(const void* k, const void* v, void* cache, const int* slot
 int b200_paged_decode_tc(const void* q, const void* cache, long long num_pages, const int* block_table,
                          const int* seq_lens, void* out, float* scratch, int B, int hq, int hkv, int d, int page_size,
                          int max_pages, int nsplit, float scale, uint32_t* status, int num_sms, cudaStream_t stream);
+// Same with a shared-prefix pass: prefix_pages[b] leading pages of sequence b are shared by the `group` consecutive
+// sequences of its group and are read once per group (scratch: B * hq * (max_shared + nsplit) * (d + 2) floats).
+int b200_paged_decode_prefix_tc(const void* q, const void* cache, long long num_pages, const int* block_table,
+                                const int* seq_lens, void* out, float* scratch, int B, int hq, int hkv, int d,
+                                int page_size, int max_pages, int nsplit, float scale, const int* prefix_pages,
+                                int group, int max_shared, uint32_t* status, int num_sms, cudaStream_t stream);
 // Decode attention for callers that cannot allocate device memory (a host that gave the whole device to
 // weights and KV cache at start-up, or plain-C callers without a device allocator). Same computation and
 // arguments as b200_paged_decode, minus `scratch`: the split-merge scratch is a 16 MiB array inside the

@@ -311,13 +311,13 @@ inline PFN_encodeTiled get_encode_tiled() {
 // Generic tiled map over a row-major tensor [d2][rows][cols] (d2 = 1 for 2-D): box = box_rows x box_cols with the
 // 128-byte swizzle (box_cols * elem_bytes == 128). ld = elements between rows, ld2 = elements between slices.
 inline int make_tmap_3d(CUtensorMap* out, const void* ptr, uint64_t d2, uint64_t rows, uint64_t cols, uint64_t ld,
-                        uint64_t ld2, uint32_t box_rows, uint32_t box_cols, int elem_bytes) {
+                        uint64_t ld2, uint32_t box_rows, uint32_t box_cols, int elem_bytes, uint32_t box_d2 = 1) {
   PFN_encodeTiled enc = get_encode_tiled();
   if (!enc) return -1;
   if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * elem_bytes) & 15) || ((ld2 * elem_bytes) & 15)) return -2;
   cuuint64_t gdim[3] = {cols, rows, d2};
   cuuint64_t gstr[2] = {ld * (uint64_t)elem_bytes, ld2 * (uint64_t)elem_bytes};
-  cuuint32_t box[3] = {box_cols, box_rows, 1};
+  cuuint32_t box[3] = {box_cols, box_rows, box_d2};
   cuuint32_t estr[3] = {1, 1, 1};
   CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   CUresult r = enc(out, dt, 3, const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,

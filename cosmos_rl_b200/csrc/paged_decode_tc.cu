@@ -44,6 +44,10 @@ struct PdtParams {
   int B, hq, hkv, max_pages, nsplit;
   float scale_log2;
   uint32_t* status;
+  // shared-prefix mode (prefix_pages != nullptr): the first prefix_pages[b] pages of sequence b are handled by
+  // paged_prefix_tc_kernel; this kernel covers the remaining tokens and writes split (max_shared + split) of ns_total
+  const int* prefix_pages;
+  int max_shared, ns_total;
 };
 
 __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -109,9 +113,10 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
     h = bh % p.hkv;
     b = bh / p.hkv;
     const int len = p.seq_lens[b];
-    int chunk = (len + p.nsplit - 1) / p.nsplit;
+    const int tb = p.prefix_pages ? min(p.prefix_pages[b] * PDT_PAGE, len) : 0;
+    int chunk = (len - tb + p.nsplit - 1) / p.nsplit;
     chunk = (chunk + PDT_PAGE - 1) / PDT_PAGE * PDT_PAGE;
-    t0 = split * chunk;
+    t0 = tb + split * chunk;
     t1 = min(len, t0 + chunk);
     if (t1 < t0) t1 = t0;
   };
@@ -315,10 +320,12 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
       for (int g = 0; g < 8; ++g) {
         if (g < G) {
           const long long head = (long long)b * p.hq + h * G + g;
-          if (p.nsplit == 1) {
+          if (p.nsplit == 1 && !p.prefix_pages) {
             p.out[head * PDT_D + row] = __float2bfloat16(l_run[g] > 0.f ? o[g] / l_run[g] : 0.f);
           } else {
-            float* sp = p.scratch + (head * p.nsplit + split) * (PDT_D + 2);
+            const int ns = p.prefix_pages ? p.ns_total : p.nsplit;
+            const int si = p.prefix_pages ? p.max_shared + split : split;
+            float* sp = p.scratch + (head * ns + si) * (PDT_D + 2);
             sp[row] = o[g];
             if (row == 0) { sp[PDT_D] = m_run[g]; sp[PDT_D + 1] = l_run[g]; }
           }
@@ -340,20 +347,218 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
   }
 }
 
-__global__ void pdt_merge_kernel(const float* __restrict__ scratch, __nv_bfloat16* __restrict__ out, int nsplit) {
+// Merge of the partial results of one (sequence, head). Without prefix_pages: splits [0, nsplit). With it: the
+// prefix pages [0, prefix_pages[b]) and the suffix splits [max_shared, max_shared + nsplit) out of ns slots.
+__global__ void pdt_merge_kernel(const float* __restrict__ scratch, __nv_bfloat16* __restrict__ out, int nsplit,
+                                 const int* __restrict__ prefix_pages, int max_shared, int hq) {
   const long long head = blockIdx.x;
   const int c = threadIdx.x;
-  const float* sp = scratch + head * nsplit * (PDT_D + 2);
+  const int ns = prefix_pages ? max_shared + nsplit : nsplit;
+  const int npre = prefix_pages ? min(prefix_pages[head / hq], max_shared) : 0;
+  const float* sp = scratch + head * ns * (PDT_D + 2);
   float M = -INFINITY;
-  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, sp[s * (PDT_D + 2) + PDT_D]);
+  for (int s = 0; s < ns; ++s) {
+    if (prefix_pages && s >= npre && s < max_shared) continue;
+    M = fmaxf(M, sp[s * (PDT_D + 2) + PDT_D]);
+  }
   float L = 0.f, A = 0.f;
-  for (int s = 0; s < nsplit; ++s) {
+  for (int s = 0; s < ns; ++s) {
+    if (prefix_pages && s >= npre && s < max_shared) continue;
     const float ms = sp[s * (PDT_D + 2) + PDT_D];
     const float cw = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
     L += sp[s * (PDT_D + 2) + PDT_D + 1] * cw;
     A += sp[s * (PDT_D + 2) + c] * cw;
   }
   out[head * PDT_D + c] = __float2bfloat16(L > 0.f ? A / L : 0.f);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Shared-prefix pass. The n samples of a prompt group share the prompt's full pages; instead of every sequence
+// streaming those pages again, one CTA per (shared page, kv head, group) loads the page once and attends ALL
+// query rows of the group that use this kv head: rows (sample j, head g) = n * G <= 128 rows of one MMA.
+//     S[rows, 128 tokens] = Q K^T,  P = exp2(S c - rowmax),  O[rows, d] = P V        (V^T slab = K-major B operand)
+// Every row's (o, m, l) goes to split slot `page` of that (sequence, head); the merge kernel combines them with
+// the per-sequence suffix. The group's sequences occupy consecutive slots [grp * n, grp * n + n).
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int PPF_SMEM = 4 * PDT_SLAB_BYTES + 256 + 1024;    // Q, K, V^T, P + barriers + alignment
+
+struct PpfParams {
+  const int* block_table;
+  const int* prefix_pages;
+  float* scratch;
+  int B, hq, hkv, max_pages, n, ns_total;
+  float scale_log2;
+  uint32_t* status;
+};
+
+__global__ void __launch_bounds__(PDT_THREADS, 1)
+paged_prefix_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __grid_constant__ CUtensorMap tm_q3,
+                       PpfParams p) {
+  const int pg = blockIdx.x, hk = blockIdx.y, s0 = blockIdx.z * p.n;
+  if (s0 >= p.B) return;
+  // the group's shared page count / page list come from its first member that still has a prefix
+  int shared = 0, owner = s0;
+  for (int j = 0; j < p.n && s0 + j < p.B; ++j) {
+    const int v = p.prefix_pages[s0 + j];
+    if (v > shared) { shared = v; owner = s0 + j; }
+  }
+  if (pg >= shared) return;
+  const int page = p.block_table[(long long)owner * p.max_pages + pg];
+  const int G = p.hq / p.hkv;
+  const int rows_used = p.n * G;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_sh = smem;
+  uint8_t* k_sh = smem + PDT_SLAB_BYTES;
+  uint8_t* v_sh = smem + 2 * PDT_SLAB_BYTES;
+  uint8_t* p_sh = smem + 3 * PDT_SLAB_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 4 * PDT_SLAB_BYTES);
+  uint64_t* qk_full = bars;
+  uint64_t* v_full = bars + 1;
+  uint64_t* s_ready = bars + 2;
+  uint64_t* p_ready = bars + 3;
+  uint64_t* o_ready = bars + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(qk_full, 1);
+    mbar_init(v_full, 1);
+    mbar_init(s_ready, 1);
+    mbar_init(p_ready, 4);
+    mbar_init(o_ready, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  // rows of the query tile that the TMA box does not cover must not hold NaN bit patterns
+  for (int i = threadIdx.x; i < PDT_SLAB_BYTES / 16; i += blockDim.x) reinterpret_cast<uint4*>(q_sh)[i] = make_uint4(0, 0, 0, 0);
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  fence_proxy_async_smem();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t q_bytes = 2u * (uint32_t)rows_used * 128u;
+      mbar_arrive_expect_tx(qk_full, q_bytes + PDT_SLAB_BYTES);
+      tma_load_3d(q_sh, &tm_q3, qk_full, 0, hk * G, s0);
+      tma_load_3d(q_sh + PDT_SLAB_BYTES / 2, &tm_q3, qk_full, 64, hk * G, s0);
+      const int krow = ((page * 2 + 0) * p.hkv + hk) * PDT_PAGE;
+      const int vrow = ((page * 2 + 1) * p.hkv + hk) * PDT_PAGE;
+      tma_load_2d(k_sh, &tm_cache, qk_full, 0, krow);
+      tma_load_2d(k_sh + PDT_SLAB_BYTES / 2, &tm_cache, qk_full, 64, krow);
+      mbar_arrive_expect_tx(v_full, PDT_SLAB_BYTES);
+      tma_load_2d(v_sh, &tm_cache, v_full, 0, vrow);
+      tma_load_2d(v_sh + PDT_SLAB_BYTES / 2, &tm_cache, v_full, 64, vrow);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(128, 128);
+      const uint32_t q_a = smem_u32(q_sh), k_a = smem_u32(k_sh), v_a = smem_u32(v_sh), p_a = smem_u32(p_sh);
+      do {
+        if (!mbar_wait(qk_full, 0)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_FULL); *abort_flag = 1; break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * (PDT_SLAB_BYTES / 2) + (k & 3) * 32;
+          umma_bf16_ss(tmem_s, umma_desc_kmajor_sw128(q_a + off), umma_desc_kmajor_sw128(k_a + off), idesc, k > 0 ? 1u : 0u);
+        }
+        tc_commit(s_ready);
+        if (!mbar_wait(p_ready, 0) || !mbar_wait(v_full, 0)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_FULL); *abort_flag = 1; break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * (PDT_SLAB_BYTES / 2) + (k & 3) * 32;
+          umma_bf16_ss(tmem_o, umma_desc_kmajor_sw128(p_a + off), umma_desc_kmajor_sw128(v_a + off), idesc, k > 0 ? 1u : 0u);
+        }
+        tc_commit(o_ready);
+      } while (false);
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    bool ok = mbar_wait(s_ready, 0);
+    if (!ok) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_TMEM_FULL); *abort_flag = 1; }
+    ok = __all_sync(0xffffffffu, ok);
+    float m = -INFINITY, l = 0.f;
+    if (ok) {
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int c = 0; c < PDT_PAGE; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_s + lane_addr + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) m = fmaxf(m, __uint_as_float(r[i]));
+      }
+      m *= p.scale_log2;
+#pragma unroll 1
+      for (int c = 0; c < PDT_PAGE; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_s + lane_addr + c, r);
+        tmem_ld_wait();
+        float e[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          e[i] = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, -m));
+          l += e[i];
+        }
+        uint8_t* dst = p_sh + (c >> 6) * (PDT_SLAB_BYTES / 2) + row * 128;
+        const int chunk0 = (c & 63) >> 3;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 o;
+          o.x = pack_bf16x2(e[8 * g + 0], e[8 * g + 1]);
+          o.y = pack_bf16x2(e[8 * g + 2], e[8 * g + 3]);
+          o.z = pack_bf16x2(e[8 * g + 4], e[8 * g + 5]);
+          o.w = pack_bf16x2(e[8 * g + 6], e[8 * g + 7]);
+          *reinterpret_cast<uint4*>(dst + (((chunk0 + g) ^ (row & 7)) << 4)) = o;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready);
+      if (!mbar_wait(o_ready, 0)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_TMEM_FULL); *abort_flag = 1; ok = false; }
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after_sync();
+      const int j = row / G, g = row % G;
+      const bool live = row < rows_used && s0 + j < p.B;
+      float* sp = p.scratch + (((long long)(s0 + j) * p.hq + hk * G + g) * p.ns_total + pg) * (PDT_D + 2);
+#pragma unroll 1
+      for (int c = 0; c < PDT_D; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_o + lane_addr + c, r);
+        tmem_ld_wait();
+        if (live) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) *reinterpret_cast<float2*>(sp + c + i) = make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+        }
+      }
+      if (live) { sp[PDT_D] = m; sp[PDT_D + 1] = l; }
+    }
+    tc_fence_before_sync();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    for (int i = 0; i < 100; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 256);
+  }
 }
 
 // V is stored transposed: slab (page, 1, h) = [d, token]
@@ -396,11 +601,23 @@ int b200_kv_append_vt(const void* k, const void* v, void* cache, const int* slot
 int b200_paged_decode_tc(const void* q, const void* cache, long long num_pages, const int* block_table,
                          const int* seq_lens, void* out, float* scratch, int B, int hq, int hkv, int d, int page_size,
                          int max_pages, int nsplit, float scale, uint32_t* status, int num_sms, cudaStream_t stream) {
+  return b200_paged_decode_prefix_tc(q, cache, num_pages, block_table, seq_lens, out, scratch, B, hq, hkv, d, page_size,
+                                     max_pages, nsplit, scale, nullptr, 0, 0, status, num_sms, stream);
+}
+
+// prefix_pages (int32 [B], nullable): number of leading pages of each sequence that are shared by the `group`
+// consecutive sequences of its group (0 = none). max_shared bounds it. scratch: B * hq * (max_shared + nsplit) * (d + 2).
+int b200_paged_decode_prefix_tc(const void* q, const void* cache, long long num_pages, const int* block_table,
+                                const int* seq_lens, void* out, float* scratch, int B, int hq, int hkv, int d,
+                                int page_size, int max_pages, int nsplit, float scale, const int* prefix_pages,
+                                int group, int max_shared, uint32_t* status, int num_sms, cudaStream_t stream) {
   using namespace b200;
   if (B <= 0) return 0;
   if (d != PDT_D || page_size != PDT_PAGE || hkv <= 0 || hq % hkv || hq / hkv > 8 || nsplit <= 0 ||
-      (nsplit > 1 && !scratch))
+      ((nsplit > 1 || prefix_pages) && !scratch))
     return B200_ERR_ARG;
+  const int G = hq / hkv;
+  if (prefix_pages && (group <= 0 || group * G > 128 || max_shared <= 0)) return B200_ERR_ARG;
   CUtensorMap tm_cache, tm_q;
   if (make_tmap_2d(&tm_cache, cache, (uint64_t)num_pages * 2 * hkv * PDT_PAGE, PDT_D, PDT_D, PDT_PAGE, 64, 2))
     return B200_ERR_TENSORMAP;
@@ -408,16 +625,27 @@ int b200_paged_decode_tc(const void* q, const void* cache, long long num_pages, 
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(paged_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PDT_SMEM) !=
-        cudaSuccess)
+            cudaSuccess ||
+        cudaFuncSetAttribute(paged_prefix_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PPF_SMEM) !=
+            cudaSuccess)
       return B200_ERR_LAUNCH;
     attr_set = true;
   }
+  const int ns_total = prefix_pages ? max_shared + nsplit : nsplit;
+  if (prefix_pages) {
+    CUtensorMap tm_q3;
+    if (make_tmap_3d(&tm_q3, q, B, hq, PDT_D, PDT_D, (uint64_t)hq * PDT_D, G, 64, 2, group)) return B200_ERR_TENSORMAP;
+    PpfParams pp{block_table, prefix_pages, scratch, B, hq, hkv, max_pages, group, ns_total, scale * PDT_LOG2E, status};
+    dim3 grid(max_shared, hkv, (B + group - 1) / group);
+    paged_prefix_tc_kernel<<<grid, PDT_THREADS, PPF_SMEM, stream>>>(tm_cache, tm_q3, pp);
+  }
   PdtParams p{block_table, seq_lens, (__nv_bfloat16*)out, scratch, B, hq, hkv, max_pages, nsplit, scale * PDT_LOG2E,
-              status};
+              status, prefix_pages, max_shared, ns_total};
   const int items = B * hkv * nsplit;
   const int grid = items < num_sms ? items : num_sms;
   paged_decode_tc_kernel<<<grid, PDT_THREADS, PDT_SMEM, stream>>>(tm_cache, tm_q, p);
-  if (nsplit > 1) pdt_merge_kernel<<<B * hq, PDT_D, 0, stream>>>(scratch, (__nv_bfloat16*)out, nsplit);
+  if (nsplit > 1 || prefix_pages)
+    pdt_merge_kernel<<<B * hq, PDT_D, 0, stream>>>(scratch, (__nv_bfloat16*)out, nsplit, prefix_pages, max_shared, hq);
   return cudaGetLastError() == cudaSuccess ? 0 : B200_ERR_LAUNCH;
 }
 

@@ -392,9 +392,14 @@ def kv_append(k, v, cache, slot_mapping, v_transposed: bool = False):
 
 def paged_decode(q, cache, block_table, seq_lens, scale: Optional[float] = None, nsplit: Optional[int] = None,
                  scratch: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                 v_transposed: bool = False):
+                 v_transposed: bool = False, prefix_pages: Optional[torch.Tensor] = None, group: int = 0,
+                 max_shared: int = 0):
     """Decode attention of ``q [B, hq, d]`` against the paged cache ``[pages, 2, hkv, page_size, d]``.
-    ``v_transposed`` selects the tcgen05 kernel (V slabs stored ``[d, page_size]``)."""
+    ``v_transposed`` selects the tcgen05 kernel (V slabs stored ``[d, page_size]``).
+
+    Shared-prefix mode (tcgen05 kernel only): sequences ``[g * group, (g + 1) * group)`` form a group whose first
+    ``prefix_pages[b]`` pages (int32 [B], at most ``max_shared``) are the same physical pages; they are read once
+    per group instead of once per sequence. The result is the same attention over all ``seq_lens[b]`` tokens."""
     if not q.is_cuda:
         return reference.paged_decode(q, cache, block_table, seq_lens, scale, v_transposed)
     B, hq, d = q.shape
@@ -413,6 +418,16 @@ def paged_decode(q, cache, block_table, seq_lens, scale: Optional[float] = None,
     if nsplit > 1 and scratch is None:
         scratch = torch.empty(B * hq * nsplit * (d + 2), dtype=torch.float32, device=q.device)
     qc = _c(q)
+    if v_transposed and prefix_pages is not None and group > 1 and max_shared > 0 and group * (hq // hkv) <= 128:
+        need = B * hq * (max_shared + nsplit) * (d + 2)
+        if scratch is None or scratch.numel() < need:
+            scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+        st = native.status_word(q.device)
+        native.check(native.lib().b200_paged_decode_prefix_tc(
+            native.ptr(qc), native.ptr(cache), cache.shape[0], native.ptr(block_table), native.ptr(seq_lens),
+            native.ptr(out), native.ptr(scratch), B, hq, hkv, d, page_size, block_table.shape[1], nsplit, scale,
+            native.ptr(prefix_pages), group, max_shared, native.ptr(st), sms, native.stream()), "paged_decode_prefix_tc")
+        return out
     if v_transposed:
         st = native.status_word(q.device)
         native.check(native.lib().b200_paged_decode_tc(

@@ -92,6 +92,9 @@ _SIGS = {
                           c_void_p],
     "b200_paged_decode_tc": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                              c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
+    "b200_paged_decode_prefix_tc": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                    c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int,
+                                    c_void_p, c_int, c_void_p],
     "b200_moe_route_topk": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200_moe_offsets": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "b200_moe_permute": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],

@@ -123,6 +123,11 @@ class RolloutEngine:
         self.top_p = torch.ones(S, dtype=torch.float32, device=self.device)
         self.top_k = torch.full((S,), -1, **i32)
         self.step_counter = torch.zeros(1, dtype=torch.int64, device=self.device)
+        # shared-prefix decode: the n samples of a prompt occupy consecutive slots and read the prompt's full pages
+        # once per group (tcgen05 decode kernel only)
+        self.prefix_pages = torch.zeros(S, **i32)
+        self.group_n = 1
+        self.max_shared = max(1, min(16, max_model_len // self.P))
         self.ring = max(self.check_interval, 1)
         self.out_tok = torch.zeros(self.ring, S, dtype=torch.int64, device=self.device)
         self.out_lp = torch.zeros(self.ring, S, dtype=torch.float32, device=self.device)
@@ -211,8 +216,13 @@ class RolloutEngine:
         seq_lens = torch.where(act > 0, cur + 1, torch.ones_like(cur))
         h = self.model.embed(self.last_tok[:B])
         bt = self.block_table[:B]
+        prefix, scratch = {}, None
+        if self.kv_vt and self.group_n > 1 and self.group_n * (self.hq // self.hkv) <= 128:
+            prefix = dict(prefix_pages=self.prefix_pages[:B], group=self.group_n, max_shared=self.max_shared, nsplit=1)
+            scratch = self._prefix_scratch(B)
         out = self._layers(h, cur.long(), slot,
-                           lambda li, q, k, v: F.paged_decode(q, self.kv[li], bt, seq_lens, v_transposed=self.kv_vt))
+                           lambda li, q, k, v: F.paged_decode(q, self.kv[li], bt, seq_lens, v_transposed=self.kv_vt,
+                                                              scratch=scratch, **prefix))
         logits = self.model.logits(out)
         r = (self.step_counter % self.ring).long()
         if self.cuda:
@@ -229,6 +239,14 @@ class RolloutEngine:
         self.last_tok[:B] = torch.where(act > 0, toks, self.last_tok[:B])
         self.cur_len[:B] += act
         self.step_counter += 1
+
+    def _prefix_scratch(self, B: int) -> torch.Tensor:
+        need = B * self.hq * (self.max_shared + 1) * (self.d + 2)
+        buf = getattr(self, "_pfx_scratch", None)
+        if buf is None or buf.numel() < need:
+            buf = self._pfx_scratch = torch.empty(self.S * self.hq * (self.max_shared + 1) * (self.d + 2),
+                                                  dtype=torch.float32, device=self.device)
+        return buf
 
     def _bucket(self, n: int) -> int:
         b = 8
@@ -274,7 +292,15 @@ class RolloutEngine:
         results: List[List[Optional[Completion]]] = [[None] * n for _ in prompts]
         waiting: Deque[int] = deque(range(len(prompts)))
         running: Dict[int, _Seq] = {}
-        free_slots = list(range(self.S - 1, -1, -1))
+        if n > self.S:
+            raise ValueError(f"{n} samples per prompt do not fit in {self.S} sequence slots")
+        # a prompt's samples take one block of n consecutive slots; the block is reused when all of them finished
+        free_groups = list(range(self.S // n - 1, -1, -1))
+        group_live: Dict[int, int] = {}
+        if n != self.group_n:
+            self.group_n = n
+            self.invalidate_graphs()        # the decode graphs bake the group size into the attention launch
+        self.prefix_pages.zero_()
         stop = set(sp.stop_token_ids)
         if sp.seed is not None:
             self.seed = sp.seed
@@ -284,7 +310,8 @@ class RolloutEngine:
         def admit() -> None:
             nonlocal host_step
             batch, page_lists, tok_budget = [], [], self.max_prefill_tokens
-            while waiting and len(free_slots) >= n:
+            batch_groups: List[int] = []
+            while waiting and free_groups:
                 pi = waiting[0]
                 p = prompts[pi] if torch.is_tensor(prompts[pi]) else list(prompts[pi])
                 if len(p) + sp.max_tokens > self.max_model_len:
@@ -298,8 +325,7 @@ class RolloutEngine:
                 batch.append((pi, p, pp))
                 page_lists.append(pp)
                 tok_budget -= len(p)
-                for _ in range(n):
-                    free_slots.pop()  # reserve; the real slot ids are assigned below
+                batch_groups.append(free_groups.pop())
             if not batch:
                 return
             logits = self._prefill([b[1] for b in batch], page_lists)
@@ -315,8 +341,10 @@ class RolloutEngine:
             slots_taken = []
             for bi, (pi, p, pp) in enumerate(batch):
                 shared = len(p) // self.P
+                grp = batch_groups[bi]
+                group_live[grp] = n
                 for si in range(n):
-                    slot = self._take_slot(running)
+                    slot = grp * n + si
                     own_n = total_per_seq(len(p)) - shared
                     own = self._alloc(own_n)
                     for q in pp[:shared]:
@@ -331,30 +359,35 @@ class RolloutEngine:
                     seq.lps.append(first_lp_h[k])
                     seq.n_generated = 1
                     running[slot] = seq
-                    slots_taken.append((slot, pages, len(p), first_tok_h[k]))
+                    slots_taken.append((slot, pages, len(p), first_tok_h[k], min(shared, self.max_shared)))
                 self._release(pp)  # drop the prefill's own reference; children hold theirs
             # publish the new sequences' state to the device in one shot
             idx = torch.tensor([s[0] for s in slots_taken], dtype=torch.long, device=self.device)
             bt = torch.zeros(len(slots_taken), self.max_pages_per_seq, dtype=torch.int32)
-            for i, (_, pages, _, _) in enumerate(slots_taken):
+            for i, (_, pages, _, _, _) in enumerate(slots_taken):
                 bt[i, : len(pages)] = torch.tensor(pages, dtype=torch.int32)
             self.block_table.index_copy_(0, idx, bt.to(self.device))
             self.cur_len.index_copy_(0, idx, torch.tensor([s[2] for s in slots_taken], dtype=torch.int32, device=self.device))
             self.last_tok.index_copy_(0, idx, torch.tensor([s[3] for s in slots_taken], dtype=torch.int64, device=self.device))
             self.active.index_fill_(0, idx, 1)
+            self.prefix_pages.index_copy_(0, idx, torch.tensor([s[4] for s in slots_taken], dtype=torch.int32,
+                                                                device=self.device))
             self.temp.index_fill_(0, idx, sp.temperature)
             self.top_p.index_fill_(0, idx, sp.top_p)
             self.top_k.index_fill_(0, idx, sp.top_k)
-
-        self._free_slots = free_slots
 
         def retire(seq: _Seq, reason: str) -> None:
             seq.done, seq.finish_reason = True, reason
             results[seq.prompt_idx][seq.sample_idx] = Completion(seq.tokens, seq.lps, reason)
             self._release(seq.pages)
             del running[seq.slot]
-            free_slots.append(seq.slot)
             self.active[seq.slot] = 0
+            self.prefix_pages[seq.slot] = 0
+            grp = seq.slot // n
+            group_live[grp] -= 1
+            if group_live[grp] == 0:
+                del group_live[grp]
+                free_groups.append(grp)
 
         def harvest(n_steps: int) -> None:
             """Read the last ``n_steps`` rows of the token ring and retire finished sequences."""
@@ -406,13 +439,6 @@ class RolloutEngine:
                 if waiting:
                     admit()
         return [[c for c in row] for row in results]
-
-    def _take_slot(self, running: Dict[int, _Seq]) -> int:
-        # lowest free slot keeps the active range dense (smaller decode buckets)
-        s = 0
-        while s in running:
-            s += 1
-        return s
 
     def release_cache(self) -> None:
         """Free the KV cache memory (colocated mode hands the memory to training)."""

@@ -476,3 +476,51 @@ def test_gemm_fp8_block_scaled(M, N, K):
     assert (got.float() - full).abs().mean().item() <= 0.05 * full.abs().mean().item()
     y = F.fp8_linear(a, bq, sb)
     assert torch.equal(y, got)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("hq,hkv,n", [(28, 4, 4), (8, 8, 8), (64, 8, 3), (28, 4, 8)])
+def test_paged_decode_shared_prefix_groups(hq, hkv, n):
+    """Groups of n sequences share their first pages; the prefix pass + suffix pass + merge must equal plain
+    attention over each sequence's whole block table."""
+    torch.manual_seed(14)
+    d, P, max_pages, max_shared = 128, 128, 8, 5
+    groups = [(3, [400, 385, 500, 700, 384 + 1, 600, 900, 1000]), (0, [5, 100, 128, 129, 300, 1, 7, 64]),
+              (5, [641, 700, 1024, 800, 650, 900, 1000, 777])]
+    B = len(groups) * n
+    n_pages = 1 + len(groups) * (5 + n * max_pages)
+    cache = torch.zeros(n_pages, 2, hkv, P, d, dtype=torch.bfloat16, device=DEV)
+    free = list(range(1, n_pages))
+    bt = torch.zeros(B, max_pages, dtype=torch.int32)
+    lens, pref = [], []
+    for gi, (shared, ls) in enumerate(groups):
+        shared_pages = [free.pop() for _ in range(shared)]
+        for j in range(n):
+            L = ls[j]
+            own = [free.pop() for _ in range(max_pages - shared)]
+            bt[gi * n + j] = torch.tensor(shared_pages + own)
+            lens.append(L)
+            pref.append(shared)
+    # fill every page that any sequence can see with random K/V (shared pages hold the same data for the group)
+    used = sorted(set(bt.flatten().tolist()))
+    for pg in used:
+        cache[pg, 0] = _bf16(hkv, P, d)
+        cache[pg, 1] = _bf16(hkv, d, P)             # V slabs are stored transposed
+    bt_d = bt.to(DEV)
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    prefix = torch.tensor(pref, dtype=torch.int32, device=DEV)
+    q = _bf16(B, hq, d)
+    ref = R.paged_decode(q.cpu(), cache.cpu(), bt, seq_lens.cpu(), v_transposed=True)
+    out = F.paged_decode(q, cache, bt_d, seq_lens, nsplit=1, v_transposed=True, prefix_pages=prefix, group=n,
+                         max_shared=max_shared)
+    torch.cuda.synchronize()
+    assert native.read_status(q.device) == 0
+    err = (out.float().cpu() - ref.float()).abs().max().item()
+    assert err < 3e-2, err
+    # a retired member (prefix 0) must not disturb the others
+    prefix2 = prefix.clone()
+    prefix2[0] = 0
+    out2 = F.paged_decode(q, cache, bt_d, seq_lens, nsplit=1, v_transposed=True, prefix_pages=prefix2, group=n,
+                          max_shared=max_shared)
+    assert native.read_status(q.device) == 0
+    assert (out2[1:].float().cpu() - ref[1:].float()).abs().max().item() < 3e-2
