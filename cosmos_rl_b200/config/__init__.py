@@ -426,6 +426,9 @@ class B200Config(_Section):
     peer_weight_sync: bool = True        # pull policy shards over NVLink peer memory instead of NCCL send/recv
     rollout_page_size: int = 128         # tokens per KV-cache page
     cuda_graph_decode: bool = True       # capture the decode step in a CUDA graph
+    shared_prefix_decode: bool = False   # read a group's shared prompt pages once per group in decode attention
+                                         # (correct, but slower than the plain kernel at 8 x 512-token prompts:
+                                         # three launches per layer instead of one)
     fused_logprob: bool = True           # tcgen05 fused lm_head + log-prob kernel
     nvls: bool = True                    # allow multimem (NVSwitch) reductions where available
     dlogits_chunk: int = 16384

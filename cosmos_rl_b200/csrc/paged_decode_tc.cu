@@ -380,7 +380,9 @@ __global__ void pdt_merge_kernel(const float* __restrict__ scratch, __nv_bfloat1
 // Every row's (o, m, l) goes to split slot `page` of that (sequence, head); the merge kernel combines them with
 // the per-sequence suffix. The group's sequences occupy consecutive slots [grp * n, grp * n + n).
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int PPF_SMEM = 4 * PDT_SLAB_BYTES + 256 + 1024;    // Q, K, V^T, P + barriers + alignment
+// RMAX = 64 keeps only 64 query / probability rows in shared memory (two CTAs per SM); the M = 128 MMAs then read
+// rows 64..127 from whatever follows, and those accumulator rows are never used.
+template <int RMAX> constexpr int ppf_smem() { return 2 * PDT_SLAB_BYTES + 2 * (RMAX * 256) + 256 + 1024; }
 
 struct PpfParams {
   const int* block_table;
@@ -391,9 +393,12 @@ struct PpfParams {
   uint32_t* status;
 };
 
-__global__ void __launch_bounds__(PDT_THREADS, 1)
+template <int RMAX>
+__global__ void __launch_bounds__(PDT_THREADS, RMAX == 64 ? 2 : 1)
 paged_prefix_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __grid_constant__ CUtensorMap tm_q3,
                        PpfParams p) {
+  constexpr int QP_BYTES = RMAX * 256;         // two halves of RMAX rows x 128 bytes
+  constexpr int QP_HALF = RMAX * 128;
   const int pg = blockIdx.x, hk = blockIdx.y, s0 = blockIdx.z * p.n;
   if (s0 >= p.B) return;
   // the group's shared page count / page list come from its first member that still has a prefix
@@ -409,11 +414,12 @@ paged_prefix_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // order: Q, P, K, V^T so that the over-reads of the 64-row variant stay inside the allocation
   uint8_t* q_sh = smem;
-  uint8_t* k_sh = smem + PDT_SLAB_BYTES;
-  uint8_t* v_sh = smem + 2 * PDT_SLAB_BYTES;
-  uint8_t* p_sh = smem + 3 * PDT_SLAB_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 4 * PDT_SLAB_BYTES);
+  uint8_t* p_sh = smem + QP_BYTES;
+  uint8_t* k_sh = smem + 2 * QP_BYTES;
+  uint8_t* v_sh = k_sh + PDT_SLAB_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_sh + PDT_SLAB_BYTES);
   uint64_t* qk_full = bars;
   uint64_t* v_full = bars + 1;
   uint64_t* s_ready = bars + 2;
@@ -432,7 +438,7 @@ paged_prefix_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
     mbar_fence_init();
   }
   // rows of the query tile that the TMA box does not cover must not hold NaN bit patterns
-  for (int i = threadIdx.x; i < PDT_SLAB_BYTES / 16; i += blockDim.x) reinterpret_cast<uint4*>(q_sh)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = threadIdx.x; i < QP_BYTES / 16; i += blockDim.x) reinterpret_cast<uint4*>(q_sh)[i] = make_uint4(0, 0, 0, 0);
   if (warp == 1) {
     tmem_alloc(tmem_slot, 256);
     tmem_relinquish();
@@ -449,7 +455,7 @@ paged_prefix_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
       const uint32_t q_bytes = 2u * (uint32_t)rows_used * 128u;
       mbar_arrive_expect_tx(qk_full, q_bytes + PDT_SLAB_BYTES);
       tma_load_3d(q_sh, &tm_q3, qk_full, 0, hk * G, s0);
-      tma_load_3d(q_sh + PDT_SLAB_BYTES / 2, &tm_q3, qk_full, 64, hk * G, s0);
+      tma_load_3d(q_sh + QP_HALF, &tm_q3, qk_full, 64, hk * G, s0);
       const int krow = ((page * 2 + 0) * p.hkv + hk) * PDT_PAGE;
       const int vrow = ((page * 2 + 1) * p.hkv + hk) * PDT_PAGE;
       tma_load_2d(k_sh, &tm_cache, qk_full, 0, krow);
@@ -468,7 +474,8 @@ paged_prefix_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = (k >> 2) * (PDT_SLAB_BYTES / 2) + (k & 3) * 32;
-          umma_bf16_ss(tmem_s, umma_desc_kmajor_sw128(q_a + off), umma_desc_kmajor_sw128(k_a + off), idesc, k > 0 ? 1u : 0u);
+          const uint32_t qoff = (k >> 2) * QP_HALF + (k & 3) * 32;
+          umma_bf16_ss(tmem_s, umma_desc_kmajor_sw128(q_a + qoff), umma_desc_kmajor_sw128(k_a + off), idesc, k > 0 ? 1u : 0u);
         }
         tc_commit(s_ready);
         if (!mbar_wait(p_ready, 0) || !mbar_wait(v_full, 0)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_FULL); *abort_flag = 1; break; }
@@ -476,7 +483,8 @@ paged_prefix_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = (k >> 2) * (PDT_SLAB_BYTES / 2) + (k & 3) * 32;
-          umma_bf16_ss(tmem_o, umma_desc_kmajor_sw128(p_a + off), umma_desc_kmajor_sw128(v_a + off), idesc, k > 0 ? 1u : 0u);
+          const uint32_t poff = (k >> 2) * QP_HALF + (k & 3) * 32;
+          umma_bf16_ss(tmem_o, umma_desc_kmajor_sw128(p_a + poff), umma_desc_kmajor_sw128(v_a + off), idesc, k > 0 ? 1u : 0u);
         }
         tc_commit(o_ready);
       } while (false);
@@ -511,16 +519,18 @@ paged_prefix_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
           e[i] = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, -m));
           l += e[i];
         }
-        uint8_t* dst = p_sh + (c >> 6) * (PDT_SLAB_BYTES / 2) + row * 128;
+        uint8_t* dst = p_sh + (c >> 6) * QP_HALF + row * 128;
         const int chunk0 = (c & 63) >> 3;
+        if (row < RMAX) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 o;
-          o.x = pack_bf16x2(e[8 * g + 0], e[8 * g + 1]);
-          o.y = pack_bf16x2(e[8 * g + 2], e[8 * g + 3]);
-          o.z = pack_bf16x2(e[8 * g + 4], e[8 * g + 5]);
-          o.w = pack_bf16x2(e[8 * g + 6], e[8 * g + 7]);
-          *reinterpret_cast<uint4*>(dst + (((chunk0 + g) ^ (row & 7)) << 4)) = o;
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            o.x = pack_bf16x2(e[8 * g + 0], e[8 * g + 1]);
+            o.y = pack_bf16x2(e[8 * g + 2], e[8 * g + 3]);
+            o.z = pack_bf16x2(e[8 * g + 4], e[8 * g + 5]);
+            o.w = pack_bf16x2(e[8 * g + 6], e[8 * g + 7]);
+            *reinterpret_cast<uint4*>(dst + (((chunk0 + g) ^ (row & 7)) << 4)) = o;
+          }
         }
       }
       fence_proxy_async_smem();
@@ -626,8 +636,10 @@ int b200_paged_decode_prefix_tc(const void* q, const void* cache, long long num_
   if (!attr_set) {
     if (cudaFuncSetAttribute(paged_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PDT_SMEM) !=
             cudaSuccess ||
-        cudaFuncSetAttribute(paged_prefix_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PPF_SMEM) !=
-            cudaSuccess)
+        cudaFuncSetAttribute(paged_prefix_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             ppf_smem<64>()) != cudaSuccess ||
+        cudaFuncSetAttribute(paged_prefix_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             ppf_smem<128>()) != cudaSuccess)
       return B200_ERR_LAUNCH;
     attr_set = true;
   }
@@ -637,7 +649,10 @@ int b200_paged_decode_prefix_tc(const void* q, const void* cache, long long num_
     if (make_tmap_3d(&tm_q3, q, B, hq, PDT_D, PDT_D, (uint64_t)hq * PDT_D, G, 64, 2, group)) return B200_ERR_TENSORMAP;
     PpfParams pp{block_table, prefix_pages, scratch, B, hq, hkv, max_pages, group, ns_total, scale * PDT_LOG2E, status};
     dim3 grid(max_shared, hkv, (B + group - 1) / group);
-    paged_prefix_tc_kernel<<<grid, PDT_THREADS, PPF_SMEM, stream>>>(tm_cache, tm_q3, pp);
+    if (group * G <= 64)
+      paged_prefix_tc_kernel<64><<<grid, PDT_THREADS, ppf_smem<64>(), stream>>>(tm_cache, tm_q3, pp);
+    else
+      paged_prefix_tc_kernel<128><<<grid, PDT_THREADS, ppf_smem<128>(), stream>>>(tm_cache, tm_q3, pp);
   }
   PdtParams p{block_table, seq_lens, (__nv_bfloat16*)out, scratch, B, hq, hkv, max_pages, nsplit, scale * PDT_LOG2E,
               status, prefix_pages, max_shared, ns_total};

@@ -79,7 +79,7 @@ class _Seq:
 class RolloutEngine:
     def __init__(self, model, *, max_num_seqs: int = 128, max_model_len: int = 2048, page_size: int = 128,
                  num_pages: Optional[int] = None, max_prefill_tokens: int = 16384, use_cuda_graph: bool = True,
-                 check_interval: int = 16, seed: int = 0, tp=None):
+                 check_interval: int = 16, seed: int = 0, tp=None, shared_prefix_decode: bool = False):
         self.model = model
         self.args = model.args
         self.device = model.norm.device
@@ -127,6 +127,7 @@ class RolloutEngine:
         # once per group (tcgen05 decode kernel only)
         self.prefix_pages = torch.zeros(S, **i32)
         self.group_n = 1
+        self.shared_prefix_decode = shared_prefix_decode
         self.max_shared = max(1, min(16, max_model_len // self.P))
         self.ring = max(self.check_interval, 1)
         self.out_tok = torch.zeros(self.ring, S, dtype=torch.int64, device=self.device)
@@ -217,7 +218,8 @@ class RolloutEngine:
         h = self.model.embed(self.last_tok[:B])
         bt = self.block_table[:B]
         prefix, scratch = {}, None
-        if self.kv_vt and self.group_n > 1 and self.group_n * (self.hq // self.hkv) <= 128:
+        if (self.shared_prefix_decode and self.kv_vt and self.group_n > 1
+                and self.group_n * (self.hq // self.hkv) <= 128):
             prefix = dict(prefix_pages=self.prefix_pages[:B], group=self.group_n, max_shared=self.max_shared, nsplit=1)
             scratch = self._prefix_scratch(B)
         out = self._layers(h, cur.long(), slot,

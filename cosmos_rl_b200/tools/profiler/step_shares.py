@@ -23,6 +23,7 @@ def main(argv=None) -> None:
     ap.add_argument("--max-response", type=int, default=1024)
     ap.add_argument("--mb-tokens", type=int, default=8192)
     ap.add_argument("--top", type=int, default=25)
+    ap.add_argument("--phase", default="both", choices=["both", "rollout"])
     a = ap.parse_args(argv)
     from ...bench_grpo import make_config
     from ...colocated import ColocatedGRPO
@@ -41,7 +42,7 @@ def main(argv=None) -> None:
     torch.cuda.synchronize()
     from torch.profiler import ProfilerActivity, profile
     phases = {}
-    for phase, fn in (("rollout", lambda: job.rollout(prompts(1))), ("train", None)):
+    for phase, fn in (("rollout", lambda: job.rollout(prompts(1))), ("train", None))[:1 if a.phase == "rollout" else 2]:
         with profile(activities=[ProfilerActivity.CUDA]) as prof:
             if phase == "rollout":
                 out = fn()
