@@ -89,6 +89,8 @@ class GPTArgs:
 ARCHS: Dict[str, GPTArgs] = {
     "tiny-qwen2": GPTArgs(vocab_size=32000, dim=256, n_layers=2, n_heads=4, n_kv_heads=2, ffn_dim=688,
                           rope_theta=1e6, qkv_bias=True, model_type="qwen2"),
+    "tiny-qwen2-d128": GPTArgs(vocab_size=32000, dim=512, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=128,
+                               ffn_dim=1024, rope_theta=1e6, qkv_bias=True, model_type="qwen2"),
     "qwen2.5-7b": GPTArgs(vocab_size=152064, dim=3584, n_layers=28, n_heads=28, n_kv_heads=4, ffn_dim=18944,
                           rope_theta=1e6, qkv_bias=True, model_type="qwen2", max_seq_len=32768),
     "qwen3-32b": GPTArgs(vocab_size=151936, dim=5120, n_layers=64, n_heads=64, n_kv_heads=8, head_dim=128,
