@@ -32,7 +32,7 @@ constexpr int PDT_SLAB_BYTES = PDT_PAGE * PDT_D * 2;        // 32 KiB
 constexpr int PDT_STAGE_BYTES = 2 * PDT_SLAB_BYTES;         // K + V^T
 constexpr int PDT_Q_BYTES = 2 * PDT_N * 64 * 2;             // two 16 x 64 boxes
 constexpr int PDT_P_BYTES = 2 * PDT_N * 64 * 2;             // two 16 x 64-token halves
-constexpr int PDT_SMEM = PDT_STAGES * PDT_STAGE_BYTES + PDT_Q_BYTES + PDT_P_BYTES + 1024 /*barriers, reductions*/ + 1024;
+constexpr int PDT_SMEM = PDT_STAGES * PDT_STAGE_BYTES + 2 * PDT_Q_BYTES + 2 * PDT_P_BYTES + 1024 /*barriers, reductions*/ + 1024;
 constexpr int PDT_THREADS = 192;
 constexpr float PDT_LOG2E = 1.4426950408889634f;
 
@@ -57,17 +57,17 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
                        PdtParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* q_sh = smem + PDT_STAGES * PDT_STAGE_BYTES;
-  uint8_t* p_sh = q_sh + PDT_Q_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_sh + PDT_P_BYTES);
+  uint8_t* q_sh = smem + PDT_STAGES * PDT_STAGE_BYTES;     // [2] query tiles (current / next work item)
+  uint8_t* p_sh = q_sh + 2 * PDT_Q_BYTES;                  // [2] probability tiles (even / odd key tile)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_sh + 2 * PDT_P_BYTES);
   uint64_t* kfull = bars;                    // [STAGES]
   uint64_t* vfull = kfull + PDT_STAGES;      // [STAGES]
-  uint64_t* kvempty = vfull + PDT_STAGES;    // [STAGES]
-  uint64_t* qfull = kvempty + PDT_STAGES;
-  uint64_t* qempty = qfull + 1;
-  uint64_t* s_ready = qempty + 1;
-  uint64_t* p_ready = s_ready + 1;
-  uint64_t* o_ready = p_ready + 1;
+  uint64_t* kvempty = vfull + PDT_STAGES;    // [STAGES]  also "PV of this tile is done" for the softmax warps
+  uint64_t* qfull = kvempty + PDT_STAGES;    // [2]
+  uint64_t* qempty = qfull + 2;              // [2]
+  uint64_t* s_ready = qempty + 2;            // [2]
+  uint64_t* p_ready = s_ready + 2;           // [2]
+  uint64_t* o_ready = p_ready + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   float* red = reinterpret_cast<float*>(tmem_slot + 2);  // [2][4 warps][8 heads]
@@ -82,20 +82,22 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
       mbar_init(&vfull[s], 1);
       mbar_init(&kvempty[s], 1);
     }
-    mbar_init(qfull, 1);
-    mbar_init(qempty, 1);
-    mbar_init(s_ready, 1);
-    mbar_init(p_ready, 4);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&qfull[s], 1);
+      mbar_init(&qempty[s], 1);
+      mbar_init(&s_ready[s], 1);
+      mbar_init(&p_ready[s], 4);
+    }
     mbar_init(o_ready, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tm_cache);
     tma_prefetch_desc(&tm_q);
   }
-  // rows G..15 of P stay zero for the whole kernel
-  for (int i = threadIdx.x; i < PDT_P_BYTES / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(p_sh)[i] = 0;
+  // rows G..15 of both P tiles stay zero for the whole kernel
+  for (int i = threadIdx.x; i < 2 * PDT_P_BYTES / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(p_sh)[i] = 0;
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 32);
+    tmem_alloc(tmem_slot, 64);
     tmem_relinquish();
   }
   fence_proxy_async_smem();
@@ -103,8 +105,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base;        // S^T: columns [0, 16)
-  const uint32_t tmem_o = tmem_base + 16;   // O^T: columns [16, 32)
+  const uint32_t tmem_o = tmem_base + 32;   // S^T: columns [0,16) and [16,32) (even / odd tile); O^T: [32,48)
 
   // item -> (b, h, split) and its token range, identical in every role
   auto item_range = [&](int item, int& b, int& h, int& split, int& t0, int& t1) {
@@ -120,20 +121,28 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
     t1 = min(len, t0 + chunk);
     if (t1 < t0) t1 = t0;
   };
+  auto item_tiles = [&](int item) -> int {
+    int b, h, split, t0, t1;
+    item_range(item, b, h, split, t0, t1);
+    return (t1 - t0 + PDT_PAGE - 1) / PDT_PAGE;
+  };
 
   if (warp == 0) {
     // ------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t kv_it = 0, item_it = 0;
-      for (int item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x, ++item_it) {
+      // work items with an empty token range are skipped by every role (item_it counts the others)
+      for (int item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
         int b, h, split, t0, t1;
         item_range(item, b, h, split, t0, t1);
         const int ntiles = (t1 - t0 + PDT_PAGE - 1) / PDT_PAGE;
-        if (!mbar_wait(qempty, (item_it & 1) ^ 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_EMPTY); *abort_flag = 1; break; }
-        mbar_arrive_expect_tx(qfull, PDT_Q_BYTES);
+        if (ntiles == 0) continue;
+        const uint32_t qs = item_it & 1;
+        if (!mbar_wait(&qempty[qs], ((item_it >> 1) & 1) ^ 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_EMPTY); *abort_flag = 1; break; }
+        mbar_arrive_expect_tx(&qfull[qs], PDT_Q_BYTES);
         const int qrow = b * p.hq + h * G;
-        tma_load_2d(q_sh, &tm_q, qfull, 0, qrow);
-        tma_load_2d(q_sh + PDT_N * 128, &tm_q, qfull, 64, qrow);
+        tma_load_2d(q_sh + qs * PDT_Q_BYTES, &tm_q, &qfull[qs], 0, qrow);
+        tma_load_2d(q_sh + qs * PDT_Q_BYTES + PDT_N * 128, &tm_q, &qfull[qs], 64, qrow);
         const int* bt = p.block_table + (long long)b * p.max_pages + t0 / PDT_PAGE;
         for (int j = 0; j < ntiles; ++j, ++kv_it) {
           const uint32_t st = kv_it % PDT_STAGES, ph = (kv_it / PDT_STAGES) & 1;
@@ -150,70 +159,79 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
           tma_load_2d(vs, &tm_cache, &vfull[st], 0, vrow);
           tma_load_2d(vs + PDT_D * 128, &tm_cache, &vfull[st], 64, vrow);
         }
+        ++item_it;
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------ MMA issuer
+    // S^T of tile t+1 (also the first tile of the next work item) is issued before the softmax warps have finished
+    // tile t: S, P and the query tile are double-buffered, so the K.Q^T product never waits for the softmax.
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16_f32(128, PDT_N);
-      uint32_t kv_it = 0, item_it = 0, tile_it = 0;
-      const uint32_t q_addr = smem_u32(q_sh), p_addr = smem_u32(p_sh);
-      auto mma1 = [&](uint32_t st) {  // S^T = K . Q^T
-        const uint32_t ks = smem_u32(smem + st * PDT_STAGE_BYTES);
+      uint32_t kv_it = 0, item_it = 0;
+      const uint32_t q_base = smem_u32(q_sh), p_base = smem_u32(p_sh);
+      // issue S^T for global tile index `t` (ring stage / S buffer from t) with the query tile of item `it`
+      auto mma1 = [&](uint32_t t, uint32_t it) -> bool {
+        const uint32_t st = t % PDT_STAGES, ph = (t / PDT_STAGES) & 1;
+        if (!mbar_wait(&kfull[st], ph)) return false;
+        tc_fence_after_sync();
+        const uint32_t ks = smem_u32(smem + st * PDT_STAGE_BYTES), qa = q_base + (it & 1) * PDT_Q_BYTES;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t half = k >> 2, off = (k & 3) * 32;
-          umma_bf16_ss(tmem_s, umma_desc_kmajor_sw128(ks + half * (PDT_PAGE * 128) + off),
-                       umma_desc_kmajor_sw128(q_addr + half * (PDT_N * 128) + off), idesc, k > 0 ? 1u : 0u);
+          umma_bf16_ss(tmem_base + (t & 1) * 16, umma_desc_kmajor_sw128(ks + half * (PDT_PAGE * 128) + off),
+                       umma_desc_kmajor_sw128(qa + half * (PDT_N * 128) + off), idesc, k > 0 ? 1u : 0u);
         }
+        tc_commit(&s_ready[t & 1]);
+        return true;
       };
-      auto mma2 = [&](uint32_t st, bool first) {  // O^T += V^T . P^T
-        const uint32_t vs = smem_u32(smem + st * PDT_STAGE_BYTES + PDT_SLAB_BYTES);
+      auto mma2 = [&](uint32_t t, bool first) {  // O^T += V^T . P^T
+        const uint32_t st = t % PDT_STAGES;
+        const uint32_t vs = smem_u32(smem + st * PDT_STAGE_BYTES + PDT_SLAB_BYTES), pa = p_base + (t & 1) * PDT_P_BYTES;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t half = k >> 2, off = (k & 3) * 32;
           umma_bf16_ss(tmem_o, umma_desc_kmajor_sw128(vs + half * (PDT_D * 128) + off),
-                       umma_desc_kmajor_sw128(p_addr + half * (PDT_N * 128) + off), idesc,
-                       (first && k == 0) ? 0u : 1u);
+                       umma_desc_kmajor_sw128(pa + half * (PDT_N * 128) + off), idesc, (first && k == 0) ? 0u : 1u);
         }
       };
-      bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok && !*abort_flag; item += gridDim.x, ++item_it) {
-        int b, h, split, t0, t1;
-        item_range(item, b, h, split, t0, t1);
-        const int ntiles = (t1 - t0 + PDT_PAGE - 1) / PDT_PAGE;
-        if (!mbar_wait(qfull, item_it & 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_FULL); *abort_flag = 1; break; }
-        tc_fence_after_sync();
-        if (ntiles == 0) {
-          mbar_arrive(qempty);
-          mbar_arrive(o_ready);
-          continue;
-        }
-        {
-          const uint32_t st = kv_it % PDT_STAGES, ph = (kv_it / PDT_STAGES) & 1;
-          if (!mbar_wait(&kfull[st], ph)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_FULL); *abort_flag = 1; break; }
+      bool ok = true, s_issued = false;
+      for (int item = blockIdx.x; item < n_items && ok && !*abort_flag; item += gridDim.x) {
+        const int ntiles = item_tiles(item);
+        if (ntiles == 0) continue;
+        const uint32_t qs = item_it & 1;
+        if (!s_issued) {
+          if (!mbar_wait(&qfull[qs], (item_it >> 1) & 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_FULL); *abort_flag = 1; break; }
           tc_fence_after_sync();
-          mma1(st);
-          tc_commit(s_ready);
+          if (!mma1(kv_it, item_it)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_FULL); *abort_flag = 1; break; }
         }
-        for (int j = 0; j < ntiles; ++j, ++kv_it, ++tile_it) {
+        s_issued = false;
+        for (int j = 0; j < ntiles; ++j, ++kv_it) {
           const uint32_t st = kv_it % PDT_STAGES, ph = (kv_it / PDT_STAGES) & 1;
-          if (!mbar_wait(p_ready, tile_it & 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_TMEM_EMPTY); *abort_flag = 1; ok = false; break; }
+          // look ahead: S^T of the next tile, possibly the first tile of the next non-empty work item
+          if (j + 1 < ntiles) {
+            if (!mma1(kv_it + 1, item_it)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_FULL); *abort_flag = 1; ok = false; break; }
+          } else {
+            int nxt = item + gridDim.x;
+            while (nxt < n_items && item_tiles(nxt) == 0) nxt += gridDim.x;
+            if (nxt < n_items) {
+              if (!mbar_wait(&qfull[(item_it + 1) & 1], ((item_it + 1) >> 1) & 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_FULL); *abort_flag = 1; ok = false; break; }
+              tc_fence_after_sync();
+              if (!mma1(kv_it + 1, item_it + 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_FULL); *abort_flag = 1; ok = false; break; }
+              s_issued = true;
+            }
+          }
+          if (!mbar_wait(&p_ready[kv_it & 1], (kv_it >> 1) & 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_TMEM_EMPTY); *abort_flag = 1; ok = false; break; }
           if (!mbar_wait(&vfull[st], ph)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_FULL); *abort_flag = 1; ok = false; break; }
           tc_fence_after_sync();
-          mma2(st, j == 0);
+          mma2(kv_it, j == 0);
           tc_commit(&kvempty[st]);
-          if (j + 1 < ntiles) {
-            const uint32_t st2 = (kv_it + 1) % PDT_STAGES, ph2 = ((kv_it + 1) / PDT_STAGES) & 1;
-            if (!mbar_wait(&kfull[st2], ph2)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_FULL); *abort_flag = 1; ok = false; break; }
-            tc_fence_after_sync();
-            mma1(st2);
-            tc_commit(s_ready);
-          } else {
-            tc_commit(qempty);
+          if (j + 1 == ntiles) {
+            tc_commit(&qempty[qs]);
             tc_commit(o_ready);
           }
         }
+        ++item_it;
       }
     }
   } else {
@@ -223,18 +241,35 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     uint32_t item_it = 0, tile_it = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok && !*abort_flag; item += gridDim.x, ++item_it) {
+    for (int item = blockIdx.x; item < n_items && ok && !*abort_flag; item += gridDim.x) {
       int b, h, split, t0, t1;
       item_range(item, b, h, split, t0, t1);
       const int ntiles = (t1 - t0 + PDT_PAGE - 1) / PDT_PAGE;
+      if (ntiles == 0) {
+        // empty split: an empty partial result (only reachable in the scratch modes), no barrier is touched
+        for (int g = 0; g < G; ++g) {
+          const long long head = (long long)b * p.hq + h * G + g;
+          if (p.nsplit == 1 && !p.prefix_pages) {      // a sequence of length 0: define the output as zero
+            p.out[head * PDT_D + row] = __float2bfloat16(0.f);
+            continue;
+          }
+          const int ns = p.prefix_pages ? p.ns_total : p.nsplit;
+          const int si = p.prefix_pages ? p.max_shared + split : split;
+          float* sp = p.scratch + (head * ns + si) * (PDT_D + 2);
+          sp[row] = 0.f;
+          if (row == 0) { sp[PDT_D] = -INFINITY; sp[PDT_D + 1] = 0.f; }
+        }
+        continue;
+      }
       float m_run[8], l_run[8];
 #pragma unroll
       for (int g = 0; g < 8; ++g) { m_run[g] = -INFINITY; l_run[g] = 0.f; }
       for (int j = 0; j < ntiles; ++j, ++tile_it) {
-        if (!mbar_wait(s_ready, tile_it & 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_TMEM_FULL); *abort_flag = 1; ok = false; break; }
+        const uint32_t tb = tile_it & 1;
+        if (!mbar_wait(&s_ready[tb], (tile_it >> 1) & 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_TMEM_FULL); *abort_flag = 1; ok = false; break; }
         tc_fence_after_sync();
         uint32_t sr[16];
-        tmem_ld_32x32b_x16(tmem_s + lane_addr, sr);
+        tmem_ld_32x32b_x16(tmem_base + tb * 16 + lane_addr, sr);
         tmem_ld_wait();
         const bool valid = (t0 + j * PDT_PAGE + row) < t1;
         float s[8], wmax[8];
@@ -268,11 +303,18 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
 #pragma unroll
           for (int g = 0; g < 8; ++g) red[32 + quad * 8 + g] = wsum[g];
         }
+        // The P tile written two tiles ago and the running output are in use until the PV product of the previous
+        // tile has finished (kvempty of its ring stage).
+        if (tile_it > 0) {
+          const uint32_t pt = tile_it - 1;
+          if (!mbar_wait(&kvempty[pt % PDT_STAGES], (pt / PDT_STAGES) & 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_TMEM_FULL); *abort_flag = 1; ok = false; }
+          tc_fence_after_sync();
+        }
         // P[head g][token row] -> shared memory, K-major rows of 64 tokens (128 bytes), 128-byte swizzle
         {
           const int half = row >> 6, tk = row & 63;
           const int chunk = tk >> 3, within = (tk & 7) * 2;
-          uint8_t* base = p_sh + half * (PDT_N * 128);
+          uint8_t* base = p_sh + tb * PDT_P_BYTES + half * (PDT_N * 128);
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             if (g < G) {
@@ -298,22 +340,20 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
         fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(p_ready);
+        if (lane == 0) mbar_arrive(&p_ready[tb]);
+        if (!ok) break;
       }
       if (!ok) break;
       // ---- item epilogue
       if (!mbar_wait(o_ready, item_it & 1)) { atomicCAS(p.status, ST_OK, ST_TIMEOUT_TMEM_FULL); *abort_flag = 1; break; }
       tc_fence_after_sync();
       float o[8];
-      if (ntiles > 0) {
+      {
         uint32_t orr[16];
         tmem_ld_32x32b_x16(tmem_o + lane_addr, orr);
         tmem_ld_wait();
 #pragma unroll
         for (int g = 0; g < 8; ++g) o[g] = __uint_as_float(orr[g]);
-      } else {
-#pragma unroll
-        for (int g = 0; g < 8; ++g) o[g] = 0.f;
       }
       tc_fence_before_sync();
 #pragma unroll
@@ -332,6 +372,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
         }
       }
       softmax_bar();  // `red` and TMEM reads are done before the next item starts overwriting
+      ++item_it;
     }
   }
 
@@ -343,7 +384,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 32);
+    tmem_dealloc(tmem_base, 64);
   }
 }
 
