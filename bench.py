@@ -100,7 +100,7 @@ def run_reference(args):
     ref = os.path.join(ROOT, "baseline", "_ref")
     out = {"impl": "reference"}
     if not os.path.isdir(os.path.join(ref, "cosmos_rl")):
-        out["unavailable"] = "baseline/_ref is absent (pip install --no-deps of /root/reference was not done on this box)"
+        out["unavailable"] = "baseline/_ref is absent (the offline pip install --no-deps of the reference source tree was not done on this box)"
         print(json.dumps(out))
         return 0
     sys.path.insert(0, ref)
