@@ -128,8 +128,13 @@ class Attention(nn.Module):
         hq, hkv, d = self.hq, self.hkv, self.d
         if self.qk_norm:
             q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
-            q = F.rms_norm(q.reshape(T * hq, d), self.q_norm, self.eps)[0].view(T, hq, d)
-            k = F.rms_norm(k.reshape(T * hkv, d), self.k_norm, self.eps)[0].view(T, hkv, d)
+            qw, kw = self.q_norm, self.k_norm
+            tp = getattr(self, "tp_for_replicated", None)
+            if tp is not None and torch.is_grad_enabled():
+                # replicated weights applied to this rank's heads only: their gradient is summed over the TP ranks
+                qw, kw = tp.copy_to_region(qw), tp.copy_to_region(kw)
+            q = F.rms_norm(q.reshape(T * hq, d), qw, self.eps)[0].view(T, hq, d)
+            k = F.rms_norm(k.reshape(T * hkv, d), kw, self.eps)[0].view(T, hkv, d)
             q, k = F.apply_rope(q, k, positions, self.theta)
             return q, k, v.reshape(T, hkv, d)
         qkv = F.rope_qkv_(qkv, positions, hq, hkv, d, self.theta)
@@ -139,6 +144,9 @@ class Attention(nn.Module):
     cp = None    # ContextParallel, set by GPT.attach_context_parallel: tokens are this rank's chunk of every sequence
 
     def forward(self, x, positions, cu_seqlens, max_seqlen, tp=None):
+        if tp is not None and torch.is_grad_enabled():
+            x = tp.copy_to_region(x)          # column-parallel input: the gradient is summed over the TP ranks
+        self.tp_for_replicated = tp
         q, k, v = self.project_qkv(x, positions)
         if self.cp is not None:
             o = self.cp.attention(q, k, v, cu_seqlens, max_seqlen)
@@ -157,6 +165,8 @@ class FeedForward(nn.Module):
         self.down_proj = nn.Linear(self.I, a.dim, bias=False)
 
     def forward(self, x, tp=None):
+        if tp is not None and torch.is_grad_enabled():
+            x = tp.copy_to_region(x)
         act = F.swiglu(_linear(x, self.gate_up_proj.weight))
         return tp.row_linear(act, self.down_proj.weight) if tp is not None else _linear(act, self.down_proj.weight)
 
@@ -192,7 +202,7 @@ class GPTBlock(nn.Module):
             else:
                 x, res = checkpoint(self._attn_part, h, res, positions, cu_seqlens, max_seqlen, tp,
                                     use_reentrant=False)
-            gu = _linear(x, self.mlp.gate_up_proj.weight)
+            gu = _linear(tp.copy_to_region(x) if tp is not None else x, self.mlp.gate_up_proj.weight)
             act = checkpoint(F.swiglu, gu, use_reentrant=False)
             h = tp.row_linear(act, self.mlp.down_proj.weight) if tp is not None else \
                 _linear(act, self.mlp.down_proj.weight)

@@ -154,3 +154,52 @@ def _failure_worker(rank, world, store_path):
 
 def test_rank_leaving_between_steps_times_out_and_mesh_is_rebuilt(tmp_path):
     mp.spawn(_failure_worker, args=(2, str(tmp_path / "fstore")), nprocs=2, join=True)
+
+
+def _tp_worker(rank, world, store, qk_norm):
+    """Tensor-parallel training step == unsharded model: log-probs and (gathered) gradients."""
+    import copy
+    from cosmos_rl_b200.models import hf_io
+    from cosmos_rl_b200.parallel.tp import TensorParallel
+    _init(rank, world, store)
+    base = _tiny()
+    if qk_norm:
+        base.qk_norm, base.qkv_bias, base.model_type = True, False, "qwen3"
+    full = GPT(base)
+    full.init_weights(0)
+    a = copy.deepcopy(full.args)
+    a.tp_size, a.tp_rank = world, rank
+    shard = GPT(a)
+    cfg = full.args.to_hf_config()
+    state = hf_io.hf_state_dict(full, cfg)
+    hf_io.load_hf_state(shard, lambda k: state[k], state, cfg, world, rank)
+    shard.tp = TensorParallel(dist.group.WORLD, world, rank)
+    g = torch.Generator().manual_seed(2)
+    cu = torch.tensor([0, 9, 21])
+    ids = torch.randint(0, 512, (21,), generator=g)
+    labels = torch.randint(0, 512, (21,), generator=g)
+    pos = full.get_position_ids(cu, 21)
+    lp_full, ent_full = full.logprobs(full(ids, pos, cu, 12), labels)
+    lp_full.sum().backward()
+    lp, ent = shard.logprobs(shard(ids, pos, cu, 12), labels)
+    assert torch.allclose(lp, lp_full.detach(), atol=1e-4), (lp - lp_full).abs().max()
+    assert torch.allclose(ent, ent_full.detach(), atol=1e-4)
+    lp.sum().backward()
+    # replicated parameters (norms) carry the full gradient on every rank; sharded ones carry their slice
+    ref = dict(full.named_parameters())
+    checked = 0
+    for name, p in shard.named_parameters():
+        r = ref[name].grad
+        if p.shape == r.shape:
+            assert torch.allclose(p.grad, r, atol=2e-4), (name, (p.grad - r).abs().max())
+            checked += 1
+    assert checked >= 5
+    down = dict(shard.named_parameters())["layers.0.mlp.down_proj.weight"]
+    cols = ref["layers.0.mlp.down_proj.weight"].grad.chunk(world, dim=1)[rank]
+    assert torch.allclose(down.grad, cols, atol=2e-4)
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("qk_norm", [False, True])
+def test_tensor_parallel_training_matches_full_model(tmp_path, qk_norm):
+    _spawn(_tp_worker, 2, tmp_path, qk_norm)
