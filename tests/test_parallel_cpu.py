@@ -203,3 +203,77 @@ def _tp_worker(rank, world, store, qk_norm):
 @pytest.mark.parametrize("qk_norm", [False, True])
 def test_tensor_parallel_training_matches_full_model(tmp_path, qk_norm):
     _spawn(_tp_worker, 2, tmp_path, qk_norm)
+
+
+def _ep_worker(rank, world, store):
+    """Expert-parallel MoE layer (all-to-all dispatch) == the same layer with every expert local."""
+    import copy
+    from cosmos_rl_b200.models.qwen3_moe import ARCHS, MoEFeedForward
+    _init(rank, world, store)
+    a = copy.deepcopy(ARCHS["tiny-qwen3-moe"])
+    a.aux_loss_coeff = 0.0
+    torch.manual_seed(0)
+    full = MoEFeedForward(a)
+    for p in full.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    b = copy.deepcopy(a)
+    b.ep_size, b.ep_rank = world, rank
+    local = MoEFeedForward(b)
+    El = a.n_experts // world
+    with torch.no_grad():
+        local.gate.weight.copy_(full.gate.weight)
+        local.w_gate_up.copy_(full.w_gate_up[rank * El:(rank + 1) * El])
+        local.w_down.copy_(full.w_down[rank * El:(rank + 1) * El])
+    local.ep_group = dist.group.WORLD
+    g = torch.Generator().manual_seed(10 + rank)          # every rank has its own tokens
+    x = torch.randn(11 + rank, a.dim, generator=g)
+    xf = x.clone().requires_grad_(True)
+    yf = full(xf)
+    yf.pow(2).sum().backward()
+    xl = x.clone().requires_grad_(True)
+    yl = local(xl)
+    assert torch.allclose(yl, yf.detach(), atol=1e-5), (yl - yf).abs().max()
+    yl.pow(2).sum().backward()
+    assert torch.allclose(xl.grad, xf.grad, atol=1e-5)
+    # expert gradients: the local experts received tokens from both ranks; compare with the sum over ranks
+    want = full.w_down.grad[rank * El:(rank + 1) * El].clone()
+    others = [torch.zeros_like(full.w_down.grad) for _ in range(world)]
+    dist.all_gather(others, full.w_down.grad)
+    want = sum(o[rank * El:(rank + 1) * El] for o in others)
+    assert torch.allclose(local.w_down.grad, want, atol=1e-5), (local.w_down.grad - want).abs().max()
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_moe_matches_local_experts(tmp_path):
+    _spawn(_ep_worker, 2, tmp_path)
+
+
+def _zero_worker(rank, world, store):
+    """Sharded flat AdamW (optimizer state split over dp ranks, library collectives) == unsharded AdamW on the
+    averaged gradient."""
+    from cosmos_rl_b200.ops import reference as R
+    from cosmos_rl_b200.parallel.flat import FlatParams
+    from cosmos_rl_b200.policy.optim import FlatAdamW
+    _init(rank, world, store)
+    m = GPT(_tiny())
+    flat = FlatParams(m, torch.float32, torch.device("cpu"), shard_multiple=world)
+    m.init_weights(0)
+    opt = FlatAdamW(flat, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, max_grad_norm=1.0,
+                    dp_group=dist.group.WORLD)
+    w = flat.data.clone()
+    mm, vv = torch.zeros_like(w), torch.zeros_like(w)
+    for step in range(1, 4):
+        g = torch.Generator().manual_seed(100 * step + rank)
+        flat.grad.copy_(torch.randn(flat.total, generator=g) * 0.01)
+        gs = [torch.zeros_like(flat.grad) for _ in range(world)]
+        dist.all_gather(gs, flat.grad)
+        avg = torch.stack(gs).mean(0)
+        norm = opt.step()
+        assert abs(norm.item() - avg.norm().item()) < 1e-5
+        R.adamw_step(w, mm, vv, avg, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, grad_scale=min(1.0, 1.0 / (avg.norm().item() + 1e-6)))
+        assert torch.allclose(flat.data, w, atol=1e-6), (flat.data - w).abs().max()
+    dist.destroy_process_group()
+
+
+def test_sharded_flat_adamw_matches_unsharded(tmp_path):
+    _spawn(_zero_worker, 2, tmp_path)

@@ -1,0 +1,90 @@
+"""CPU tests of the SFT and DPO trainers and of the GRPO loss variants against hand-written statements."""
+import math
+
+import torch
+
+from cosmos_rl_b200.config import Config
+from cosmos_rl_b200.parallel.dims import ParallelDims
+from cosmos_rl_b200.policy import loss as L
+
+
+def _config(tmp_path, kind):
+    return Config.from_dict({
+        "policy": {"model_name_or_path": "tiny-qwen2", "model_max_length": 64, "model_gradient_checkpointing": False},
+        "train": {"seed": 0, "optm_lr": 1e-3, "optm_warmup_steps": 0, "output_dir": str(tmp_path),
+                  "train_policy": {"type": "sft", "trainer_type": kind, "mini_batch": 2},
+                  "ckpt": {"enable_checkpoint": False}},
+        "custom": {"dpo_beta": 0.2},
+    })
+
+
+def test_sft_trainer_reduces_loss_on_a_fixed_batch(tmp_path):
+    from cosmos_rl_b200.policy.trainer.sft_trainer import SFTTrainer
+    tr = SFTTrainer(_config(tmp_path, "sft"), ParallelDims(world_size=1, device=torch.device("cpu")),
+                    device=torch.device("cpu"))
+    tr.model_load_from_hf()
+    g = torch.Generator().manual_seed(0)
+    batch = [{"input_ids": torch.randint(0, 32000, (n,), generator=g).tolist()} for n in (12, 20, 7, 16)]
+    batch[1]["label_ids"] = [-100] * 8 + batch[1]["input_ids"][8:]            # prompt part is not learned
+    losses = [tr.step_training(batch, total_steps=10, train_step=i + 1)["train/loss_avg"] for i in range(4)]
+    assert all(math.isfinite(x) for x in losses) and losses[-1] < losses[0] - 0.05, losses
+    assert abs(losses[0] - math.log(32000)) < 0.5                              # random init: about ln(V)
+    assert tr.step_validation(batch)["val/loss"] < losses[0]
+
+
+def test_dpo_trainer_step_and_reference_is_frozen(tmp_path):
+    from cosmos_rl_b200.policy.trainer.dpo_trainer import DPOTrainer
+    tr = DPOTrainer(_config(tmp_path, "dpo"), ParallelDims(world_size=1, device=torch.device("cpu")),
+                    device=torch.device("cpu"))
+    tr.model_load_from_hf()
+    g = torch.Generator().manual_seed(1)
+    tok = lambda n: torch.randint(0, 32000, (n,), generator=g).tolist()
+    batch = [{"prompt": tok(6), "chosen": tok(5), "rejected": tok(7)} for _ in range(4)]
+    r0 = tr.step_training(batch, total_steps=10, train_step=1)
+    assert abs(r0["train/loss_avg"] - math.log(2.0)) < 1e-4                    # policy == reference at step 1
+    ref_state = tr.reference_state.clone()
+    r1 = tr.step_training(batch, total_steps=10, train_step=2)
+    r2 = tr.step_training(batch, total_steps=10, train_step=3)
+    assert torch.equal(tr.reference_state, ref_state)                          # the reference never moves
+    assert r2["train/loss_avg"] < r0["train/loss_avg"] and r2["train/reward_acc"] >= 0.5
+    assert math.isfinite(r1["train/grad_norm"])
+
+
+def test_grpo_loss_variants_by_hand():
+    lp = torch.tensor([-1.0, -2.0, -0.5, -1.5], requires_grad=True)
+    old = torch.tensor([-1.2, -1.5, -0.5, -3.0])
+    A = torch.tensor([1.0, 1.0, -2.0, -2.0])
+    seq = torch.tensor([0, 0, 1, 1])
+    cfg = L.GrpoLossConfig(epsilon_low=0.2, epsilon_high=0.2, lower_bound_ratio=3.0)
+    loss, m = L.grpo_loss(lp, old, A, seq, 2, cfg)
+    ratio = torch.exp(lp.detach() - old)
+    want = []
+    for r, a in zip(ratio.tolist(), A.tolist()):
+        v = -min(r * a, max(min(r, 1.2), 0.8) * a)
+        if a < 0:
+            v = min(v, -3.0 * a)
+        want.append(v)
+    assert abs(loss.item() - sum(want) / 4) < 1e-6
+    assert abs(m["clip_frac"].item() - 0.25) < 1e-6                # token 0 (ratio 1.22 > 1.2); token 3 is cut by the dual clip
+    loss.backward()
+    assert lp.grad[0].item() == 0.0 and lp.grad[3].item() == 0.0   # clipped tokens carry no gradient
+    assert abs(lp.grad[1].item() + ratio[1].item() / 4) < 1e-6
+    # sequence-level reductions
+    per = torch.tensor(want)
+    cfg2 = L.GrpoLossConfig(loss_type="seq-mean-token-mean")
+    l2, _ = L.grpo_loss(lp.detach(), old, A, seq, 2, cfg2)
+    assert abs(l2.item() - ((per[0] + per[1]) / 2 + (per[2] + per[3]) / 2).item() / 2) < 1e-6
+    # k3 KL term
+    ref = torch.tensor([-1.1, -2.5, -0.4, -1.0])
+    l3, m3 = L.grpo_loss(lp.detach(), old, A, seq, 2, L.GrpoLossConfig(kl_beta=0.5), ref_logprob=ref)
+    r = ref - lp.detach()
+    kl = (torch.exp(r) - r - 1).mean()
+    assert abs(m3["kl"].item() - kl.item()) < 1e-6 and abs(l3.item() - (sum(want) / 4 + 0.5 * kl.item())) < 1e-6
+    # GSPO: one ratio per sequence
+    l4, m4 = L.grpo_loss(lp.detach(), old, A, seq, 2, L.GrpoLossConfig(variant="gspo"))
+    sr = torch.exp(torch.tensor([((lp.detach() - old)[:2]).mean(), ((lp.detach() - old)[2:]).mean()]))
+    w4 = [-min(sr[s].item() * a, max(min(sr[s].item(), 1.2), 0.8) * a) for s, a in zip([0, 0, 1, 1], A.tolist())]
+    assert abs(l4.item() - sum(w4) / 4) < 1e-6
+    # DPO loss
+    d, dm = L.dpo_loss(torch.tensor([-3.0]), torch.tensor([-5.0]), torch.tensor([-4.0]), torch.tensor([-4.5]), beta=0.5)
+    assert abs(d.item() + math.log(1 / (1 + math.exp(-0.5 * (2.0 - 0.5))))) < 1e-6 and dm["reward_acc"].item() == 1.0
