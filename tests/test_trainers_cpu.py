@@ -88,3 +88,33 @@ def test_grpo_loss_variants_by_hand():
     # DPO loss
     d, dm = L.dpo_loss(torch.tensor([-3.0]), torch.tensor([-5.0]), torch.tensor([-4.0]), torch.tensor([-4.5]), beta=0.5)
     assert abs(d.item() + math.log(1 / (1 + math.exp(-0.5 * (2.0 - 0.5))))) < 1e-6 and dm["reward_acc"].item() == 1.0
+
+
+def test_grpo_trainer_with_reference_kl_mu_iterations_and_variants(tmp_path):
+    """A GRPO step with a KL reference phase, an old-log-prob phase (mu = 2) and the loss variants runs end to end:
+    finite loss, weights move, the reference copy does not."""
+    import pytest
+    from cosmos_rl_b200.colocated import ColocatedGRPO
+    for over in ({"kl_beta": 0.05, "mu_iterations": 2},
+                 {"variant": "dapo", "loss_type": "seq-mean-token-mean", "epsilon_high": 0.28},
+                 {"variant": "gspo", "kl_beta": 0.01, "unbiased_kl_estimate": True},
+                 {"aipo_rho": 1.5, "entropy_coeff": 0.001, "positive_nll_coef": 0.1}):
+        tp = {"type": "grpo", "reward_function": ["even_token_fraction"], "mini_batch": 4, "temperature": 1.0}
+        tp.update(over)
+        cfg = Config.from_dict({
+            "mode": "colocated",
+            "policy": {"model_name_or_path": "tiny-qwen2", "model_max_length": 96, "model_gradient_checkpointing": False},
+            "rollout": {"n_generation": 4, "batch_size": 2, "max_response_length": 16, "seed": 3},
+            "train": {"seed": 0, "optm_lr": 1e-3, "optm_warmup_steps": 0, "output_dir": str(tmp_path),
+                      "train_policy": tp, "ckpt": {"enable_checkpoint": False}}})
+        job = ColocatedGRPO(cfg, device=torch.device("cpu"), max_num_seqs=8)
+        g = torch.Generator().manual_seed(0)
+        prompts = [torch.randint(0, 32000, (10,), generator=g) for _ in range(2)]
+        w0 = job.trainer.flat.data.clone()
+        ref0 = None if job.trainer.reference_state is None else job.trainer.reference_state.clone()
+        rep = job.step(prompts)
+        assert math.isfinite(rep["train/loss_avg"]) and math.isfinite(rep["train/grad_norm"]), (over, rep)
+        assert not torch.equal(job.trainer.flat.data, w0), over
+        if ref0 is not None:
+            assert torch.equal(job.trainer.reference_state, ref0)
+            assert rep["train/kl"] >= 0.0
