@@ -102,7 +102,7 @@ ARCHS: Dict[str, GPTArgs] = {
 
 
 def _linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -> torch.Tensor:
-    return tF.linear(x, w, b)
+    return F.linear_maybe_fp8(x, w, b)
 
 
 class Attention(nn.Module):

@@ -505,3 +505,14 @@ def fp8_linear(x: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor) -> torch.Ten
     """Inference linear layer on block-scaled fp8 weights: the activation is quantised 1x128 on the fly."""
     xq, xs = quant_fp8_block(x.contiguous(), 1)
     return gemm_fp8_block(xq, xs, wq, ws)
+
+
+def linear_maybe_fp8(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ w^T + b``. A weight that carries block-scaled fp8 data (``w._fp8 = (e4m3 [N, K], scales)``, attached
+    by the rollout's fp8 weight store) is used through the fp8 GEMM in inference; everything else is the bf16
+    library GEMM."""
+    f8 = getattr(w, "_fp8", None)
+    if f8 is not None and x.is_cuda and not torch.is_grad_enabled() and x.dtype == torch.bfloat16:
+        y = fp8_linear(x.reshape(-1, x.shape[-1]), f8[0], f8[1]).view(*x.shape[:-1], f8[0].shape[0])
+        return y if b is None else y + b
+    return torch.nn.functional.linear(x, w, b)

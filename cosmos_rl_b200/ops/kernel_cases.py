@@ -142,6 +142,23 @@ def case_reshard(iters):
     report(f"reshard_pull (local source) {rows}x{cols} bf16", t, nbytes=2.0 * rows * cols * 2)
 
 
+def case_reshard_fp8(iters):
+    """Weight-sync pull fused with 128x128 block-scaled fp8 quantisation (local source)."""
+    import torch.nn as nn
+    from ..parallel.flat import FlatParams
+    from ..rollout.weight_sync import Fp8WeightStore, PeerWeightSync
+    rows, cols = 16384, 16384
+    with torch.device("meta"):
+        lin = nn.Linear(cols, rows, bias=False)
+    flat = FlatParams(lin, torch.bfloat16, torch.device("cuda"), with_grad=False)
+    src = bf(rows * cols)
+    store = Fp8WeightStore(flat, skip=())
+    ws = PeerWeightSync(flat.data, [[0, 0, cols, 0, cols, rows, cols]], {0: src.data_ptr()}, fp8=store)
+    assert ws.n_quant == 1
+    t = timed(ws.pull, iters)
+    report(f"reshard_pull + fp8 128x128 quantisation (local source) {rows}x{cols}", t, nbytes=3.0 * rows * cols)
+
+
 def case_quant(iters):
     R, C = 16384, 16384
     w = bf(R, C)
@@ -228,7 +245,7 @@ def case_flash(iters, B=16, L=4096, library=True):
     assert native.read_status(q.device) == 0
 
 
-CASES = {"moe": case_moe, "gemm_fp8": case_gemm_fp8, "flash": case_flash, "flash_small": case_flash_small, "gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
+CASES = {"reshard_fp8": case_reshard_fp8, "moe": case_moe, "gemm_fp8": case_gemm_fp8, "flash": case_flash, "flash_small": case_flash_small, "gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
          "reshard": case_reshard, "quant": case_quant, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu,
          "rope": case_rope, "adamw": case_adamw, "sample": case_sample}
 

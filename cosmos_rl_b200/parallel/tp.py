@@ -73,9 +73,11 @@ class TensorParallel:
         # below ~4k rows the projection is launch/latency bound and the library pair is faster (measured
         # crossover on 2 GPUs between 2048 and 8192 rows); prefill and training shapes take the fused kernel
         if (f is not None and x.is_cuda and not torch.is_grad_enabled() and x.dtype == torch.bfloat16
+                and getattr(w, "_fp8", None) is None
                 and x.dim() == 2 and x.shape[0] >= self.fused_min_rows and f.fits(x.shape[0], w.shape[0])):
             return f.gemm_all_reduce(x.contiguous(), w)
-        return _AllReduce.apply(torch.nn.functional.linear(x, w), self.group)
+        from ..ops.functional import linear_maybe_fp8
+        return _AllReduce.apply(linear_maybe_fp8(x, w), self.group)
 
     def attach_fused(self, device, max_rows: int, max_cols: int) -> None:
         from .tp_fused import FusedTP

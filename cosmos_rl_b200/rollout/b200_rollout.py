@@ -42,6 +42,13 @@ class B200Rollout(RolloutBase):
             import os
             if load_format != "dummy" and os.path.isdir(path) and hf_io.has_safetensors(path):
                 hf_io.load_hf_weights(self.model, path, self.parallel_dims)
+        self.fp8 = None
+        if cfg.rollout.quantization == "fp8" and shared_model is None and self.device.type == "cuda":
+            # linear weights are served from block-scaled fp8 copies; the weight sync writes them directly
+            from .weight_sync import Fp8WeightStore
+            self.fp8 = Fp8WeightStore(self.flat)
+            self.fp8.attach(self.model)
+            self.fp8.quantize_local()
         r = cfg.rollout
         self.engine = RolloutEngine(
             self.model, max_num_seqs=max(8, r.batch_size * r.n_generation),

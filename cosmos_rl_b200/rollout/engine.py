@@ -176,7 +176,7 @@ class RolloutEngine:
             if self.tp is not None:
                 h = self.tp.row_linear(o, layer.self_attn.o_proj.weight)
             else:
-                h = torch.nn.functional.linear(o, layer.self_attn.o_proj.weight)
+                h = F.linear_maybe_fp8(o, layer.self_attn.o_proj.weight)
             x, res = F.rms_norm(h, layer.post_attention_layernorm, eps, residual=res)
             h = layer.mlp(x, self.tp)
         out, _ = F.rms_norm(h, m.norm, eps, residual=res)

@@ -22,14 +22,72 @@ from ..parallel.reshard import merge_descriptors
 TILE = 128
 
 
+class Fp8WeightStore:
+    """Block-scaled fp8 copies of the rollout model's linear weights (the reference re-quantises after the
+    sync, cosmos_rl/rollout/vllm_rollout/vllm_rollout.py:989-999; here the sync kernel writes them directly).
+
+    ``q`` mirrors the element offsets of the bf16 flat buffer (one byte per element); ``scales`` holds one fp32 per
+    128 x 128 block of every quantised matrix, row-major ``[N / 128, K / 128]``. Quantised: 2-D parameters with
+    both dimensions multiples of 128, except embeddings and the output head (kept in bf16, as fp8 serving stacks do).
+    ``attach`` hangs ``_fp8`` views on the parameters; ``ops.functional.linear_maybe_fp8`` picks them up."""
+
+    def __init__(self, flat, skip=("embed", "lm_head")):
+        self.flat = flat
+        dev = flat.device
+        self.q = torch.zeros(flat.total, dtype=torch.uint8, device=dev)
+        self.table = []           # (offset, N, K, scale_offset), sorted by offset
+        n_scales = 0
+        for s in flat.slots:
+            if len(s.shape) == 2 and s.shape[0] % TILE == 0 and s.shape[1] % TILE == 0 \
+                    and not any(k in s.name for k in skip):
+                self.table.append((s.offset, s.shape[0], s.shape[1], n_scales, s.name))
+                n_scales += (s.shape[0] // TILE) * (s.shape[1] // TILE)
+        self.table.sort()
+        self._offsets = [t[0] for t in self.table]
+        self.scales = torch.zeros(max(n_scales, 1), dtype=torch.float32, device=dev)
+
+    def lookup(self, dst_off: int):
+        """The quantised matrix that contains flat offset ``dst_off`` (or None)."""
+        import bisect
+        i = bisect.bisect_right(self._offsets, dst_off) - 1
+        if i < 0:
+            return None
+        off, N, K, so, _ = self.table[i]
+        return (off, N, K, so) if dst_off < off + N * K else None
+
+    def views(self, entry):
+        off, N, K, so = entry[:4]
+        q = self.q[off:off + N * K].view(torch.float8_e4m3fn).view(N, K)
+        return q, self.scales[so:so + (N // TILE) * (K // TILE)].view(N // TILE, K // TILE)
+
+    def attach(self, module) -> int:
+        by_name = dict(module.named_parameters())
+        for e in self.table:
+            by_name[e[4]]._fp8 = self.views(e)
+        return len(self.table)
+
+    def quantize_local(self) -> None:
+        """Quantise from the bf16 flat buffer (weights that arrived by another route: checkpoint, collectives)."""
+        from ..ops import functional as F
+        for e in self.table:
+            off, N, K = e[0], e[1], e[2]
+            q, sc = F.quant_fp8_block(self.flat.data[off:off + N * K].view(N, K), TILE)
+            qv, sv = self.views(e)
+            qv.copy_(q)
+            sv.copy_(sc)
+
+
 class PeerWeightSync:
     def __init__(self, dst_flat: torch.Tensor, plan: List[List[int]], src_ptrs: Dict[int, int],
-                 fp8_dst: Optional[torch.Tensor] = None, fp8_scales: Optional[torch.Tensor] = None):
-        """``plan`` rows: [src_rank, src_off, src_ld, dst_off, dst_ld, rows, cols] (elements of bf16)."""
+                 fp8: Optional[Fp8WeightStore] = None):
+        """``plan`` rows: [src_rank, src_off, src_ld, dst_off, dst_ld, rows, cols] (elements of bf16). With an
+        ``fp8`` store, rectangles that land block-aligned inside a quantised matrix are written as e4m3 + scales by
+        the same kernel pass (their bf16 copy is not refreshed); the rest stays bf16."""
         self.device = dst_flat.device
         self.dst = dst_flat
-        plan = merge_descriptors(plan)
+        plan = merge_descriptors(plan) if fp8 is None else [list(d) for d in plan]
         self.n = len(plan)
+        self.n_quant = 0
         self.bytes = sum(d[5] * d[6] for d in plan) * 2
         descs = (native.CopyDesc * self.n)()
         prefix = []
@@ -43,6 +101,19 @@ class PeerWeightSync:
             descs[i].src_ld, descs[i].dst_ld = sld, dld
             descs[i].rows, descs[i].cols = rows, cols
             descs[i].ld_scale, descs[i].quant = 0, 0
+            ent = fp8.lookup(do) if fp8 is not None else None
+            if ent is not None:
+                off, N, K, sc_off = ent
+                r0, c0 = divmod(do - off, K)
+                aligned = (dld == K and r0 % TILE == 0 and c0 % TILE == 0 and r0 + rows <= N and c0 + cols <= K
+                           and (rows % TILE == 0 or r0 + rows == N) and (cols % TILE == 0 or c0 + cols == K))
+                if not aligned:
+                    raise ValueError(f"weight-sync rectangle at flat offset {do} is not 128-aligned inside its "
+                                     f"{N}x{K} matrix: cannot be quantised in flight")
+                descs[i].dst = fp8.q.data_ptr() + do
+                descs[i].dst_scale = fp8.scales.data_ptr() + 4 * (sc_off + (r0 // TILE) * (K // TILE) + c0 // TILE)
+                descs[i].ld_scale, descs[i].quant = K // TILE, 1
+                self.n_quant += 1
             prefix.append(tiles)
             tiles += ((rows + TILE - 1) // TILE) * ((cols + TILE - 1) // TILE)
         self.total_tiles = tiles

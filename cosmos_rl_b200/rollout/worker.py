@@ -141,7 +141,7 @@ class DisaggregatedRolloutControlWorker(CommMixin):
                 m = PeerMapping(info["ipc_handle"], info["nbytes"], self.device)
                 self._peer_maps.append(m)
                 ptrs[info["rank"]] = m.ptr
-            self.peer_sync = PeerWeightSync(self.rollout.flat.data, infos, ptrs)
+            self.peer_sync = PeerWeightSync(self.rollout.flat.data, infos, ptrs, fp8=getattr(self.rollout, "fp8", None))
         self.peer_sync.pull()
         torch.cuda.synchronize()
         from ..ops import native
@@ -166,6 +166,8 @@ class DisaggregatedRolloutControlWorker(CommMixin):
             buf = torch.empty(d[5], d[6], dtype=tdt, device=self.device)
             comm.recv(buf, d[0])
             torch.as_strided(flat, (d[5], d[6]), (d[4], 1), flat.storage_offset() + d[3]).copy_(buf)
+        if getattr(self.rollout, "fp8", None) is not None:
+            self.rollout.fp8.quantize_local()      # no in-flight quantisation on this route: second pass
 
     def rollout_to_rollout_broadcast(self, c: cmd.RolloutToRolloutBroadcastCommand) -> bool:
         """Commit a weight version. With peer sync every replica has already pulled its own copy, so this
