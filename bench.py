@@ -39,6 +39,9 @@ def parse_args():
     ap.add_argument("--max-response", type=int, default=1024)
     ap.add_argument("--mb-tokens", type=int, default=8192, help="token budget of one training micro-batch")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--layout", default="auto", choices=["auto", "colocated", "disaggregated"],
+                    help="auto: 8 GPUs use the named disaggregated layout (policy FSDP4 + rollout TP2 x 2); 1, 2 and 4 "
+                         "GPUs run colocated data-parallel replicas (each GPU generates and trains its own prompts)")
     return ap.parse_args()
 
 

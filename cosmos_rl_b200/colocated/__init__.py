@@ -40,7 +40,7 @@ class ColocatedGRPO:
         self.engine = RolloutEngine(
             self.trainer.model, max_num_seqs=n_seqs, max_model_len=config.policy.model_max_length,
             page_size=config.b200.rollout_page_size, use_cuda_graph=config.b200.cuda_graph_decode,
-            seed=r.seed or 0)
+            seed=(r.seed or 0) + 7919 * int(getattr(self.dims, "global_rank", 0) or 0))
         reward = Reward(tp.reward_function, explicit_fns=reward_fns)
         self.algo = GRPO(reward, unbiased=tp.unbiased_advantage)
         self.step_idx = 0
