@@ -181,6 +181,10 @@ struct B200CopyDesc {
 int b200_reshard_pull(const B200CopyDesc* descs_dev, const int* tile_prefix_dev, int n_desc, int total_tiles,
                       uint32_t* status, cudaStream_t stream);
 
+// In-place averaging all-reduce of a flat bf16 buffer over peer memory (fsdp_fused.cu): this rank reduces and
+// republishes [lo, lo + n).
+int b200_peer_all_reduce(void* const* bufs, int n_ranks, long long lo, long long n, float scale, cudaStream_t stream);
+
 // Block-scaled fp8 GEMM (gemm_fp8_block.cu): A [M,K] e4m3 + sa [M, ldsa] (1 x 128 blocks), B [N,K] e4m3 +
 // sb [ceil(N/128), ldsb] (128 x 128 blocks), C [M,N] bf16.
 int b200_gemm_fp8_block(const void* A, const float* sa, const void* B, const float* sb, void* C, int M, int N, int K,

@@ -119,9 +119,57 @@ adamw_publish_kernel(float* __restrict__ master, float* __restrict__ m, float* _
   }
 }
 
+// Two-shot all-reduce in ONE launch and in place: this rank owns elements [lo, lo + n) of the flat buffer, reads
+// them from every rank (peer loads), averages in fp32 and stores the bf16 result into every rank's buffer (peer
+// stores). A rank only ever writes its own range, and only the owner reads that range, so no barrier is needed
+// between the reduce and the gather halves; the caller orders whole calls with stream barriers. This is the
+// on-box form of the inter-replica gradient all-reduce (cosmos_rl/policy/trainer/llm_trainer/grpo_trainer.py:2112-2147).
+__global__ void __launch_bounds__(256)
+peer_all_reduce_kernel(PeerPtrs bufs, long long lo, long long n, float scale) {
+  const long long stride = (long long)gridDim.x * blockDim.x * 8;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n; i += stride) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int r = 0; r < MAX_PEERS; ++r) {
+      if (r < bufs.n) {
+        const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(bufs.p[r]) + lo + i);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[2 * j] * scale, acc[2 * j + 1] * scale);
+#pragma unroll
+    for (int r = 0; r < MAX_PEERS; ++r)
+      if (r < bufs.n) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(bufs.p[r]) + lo + i) = o;
+  }
+}
+
 }  // namespace
 
 extern "C" {
+
+// bufs[r]: base of rank r's flat bf16 buffer; [lo, lo + n) is the range this rank reduces and republishes.
+int b200_peer_all_reduce(void* const* bufs, int n_ranks, long long lo, long long n, float scale, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n_ranks <= 0 || n_ranks > MAX_PEERS || (n & 7) || (lo & 7)) return B200_ERR_ARG;
+  PeerPtrs pp;
+  pp.n = n_ranks;
+  for (int r = 0; r < n_ranks; ++r) pp.p[r] = bufs[r];
+  long long want = (n / 8 + 255) / 256;
+  int grid = (int)(want < 148 * 16 ? want : 148 * 16);
+  peer_all_reduce_kernel<<<grid, 256, 0, stream>>>(pp, lo, n, scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : B200_ERR_LAUNCH;
+}
 
 // grads[r]: base of rank r's flat bf16 gradient buffer (this rank's own included). Shard = [lo, lo + n), n % 8 == 0.
 int b200_reduce_scatter_sumsq(void* const* grads, int n_ranks, long long lo, long long n, float* out_shard,

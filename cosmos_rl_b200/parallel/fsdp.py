@@ -78,6 +78,23 @@ class PeerCollective:
             weight_decay, bias1, bias2, grad_scale.data_ptr(), native.stream()), "adamw_publish")
         self.stream_barrier()   # every shard has landed everywhere before the next forward
 
+    def all_reduce_grads(self, average: bool = True) -> None:
+        """In-place (averaging) all-reduce of the flat gradient buffer over peer memory: one launch per rank, each
+        rank reduces and republishes its own 1/world range. Used for gradient averaging between policy replicas that
+        share a box; ``torch.distributed`` all-reduce is the route between boxes."""
+        n = self.flat.total
+        per = (n // self.world) // 8 * 8
+        lo = self.rank * per
+        cnt = per if self.rank < self.world - 1 else n - lo
+        self.stream_barrier()
+        L = native.lib()
+        L.b200_peer_all_reduce.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_longlong,
+                                           ctypes.c_float, ctypes.c_void_p]
+        L.b200_peer_all_reduce.restype = ctypes.c_int
+        native.check(L.b200_peer_all_reduce(ctypes.cast(self.grad_ptrs, ctypes.c_void_p), self.world, lo, cnt,
+                                            1.0 / self.world if average else 1.0, native.stream()), "peer_all_reduce")
+        self.stream_barrier()
+
     def close(self) -> None:
         for m in self.maps:
             m.close()

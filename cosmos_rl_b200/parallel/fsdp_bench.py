@@ -70,6 +70,12 @@ def main() -> None:
     # AdamW + publish: master/m/v read+write (24 B), grad shard read (4 B), bf16 shard written locally and to P-1 peers
     pub_link = (world - 1) * shard * 2 / NVLINK_BPS
     pub_hbm = shard * (24 + 4 + 2) / hbm
+    t_ar = timed(lambda: coll.all_reduce_grads())
+    t_ar_lib = timed(lambda: dist.all_reduce(flat.grad, group=grp))
+    ar_link = (world - 1) * shard * 2 / NVLINK_BPS           # each direction carries (P-1) shards
+    if rank == 0:
+        print(f"peer all-reduce (in place, one launch): {t_ar * 1e3:.2f} ms (incl. two stream barriers) | NCCL all_reduce "
+              f"{t_ar_lib * 1e3:.2f} ms | roofline {ar_link * 1e3:.2f} ms -> {ar_link / t_ar:.2f} of NVLink roofline")
     if rank == 0:
         gb = shard * 2 / 1e9
         print(f"flat {flat.total / 2**30:.2f} Gi params, {world} ranks, shard {gb:.2f} GB (bf16)")

@@ -69,6 +69,17 @@ def main():
     native.read_status(dev)
     if rank == 0:
         print("fused reduce-scatter + adamw publish: ok", flush=True)
+    # in-place two-shot all-reduce of the gradient buffer over peer memory
+    gen_ar = torch.Generator(device=dev).manual_seed(900 + rank)
+    flat.grad.copy_((torch.randn(flat.total, device=dev, generator=gen_ar) * 0.01).to(torch.bfloat16))
+    parts_ar = [torch.empty_like(flat.grad) for _ in range(world)]
+    dist.all_gather(parts_ar, flat.grad, group=grp)
+    want_ar = torch.stack([x.float() for x in parts_ar]).mean(0)
+    coll.all_reduce_grads()
+    torch.cuda.synchronize()
+    assert torch.allclose(flat.grad.float(), want_ar, atol=2e-4, rtol=1e-2), (flat.grad.float() - want_ar).abs().max()
+    if rank == 0:
+        print("peer-memory all-reduce of the flat gradients: ok", flush=True)
 
     # ------------------------------------------------------------ 2. weight sync: tp1 policy -> tp2 rollout
     # rank 0 holds the policy (the flat buffer above); both ranks are rollout TP ranks pulling from it
