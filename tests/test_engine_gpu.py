@@ -42,3 +42,29 @@ def test_engine_logprobs_match_teacher_forcing(shared_prefix):
                 assert abs(lsm[len(p) - 1 + i, tok].item() - lp) < 0.08, (i, lsm[len(p) - 1 + i, tok].item(), lp)
                 n_tok += 1
     assert n_tok == 4 * 4 * 40
+
+
+@pytest.mark.parametrize("arch", ["tiny-qwen3-moe", "tiny-qwen2-d128"])
+def test_colocated_grpo_step_on_gpu(arch, tmp_path):
+    """One full GRPO step (generate, score, train, publish) of a tiny dense and a tiny MoE model on the GPU."""
+    import math
+    from cosmos_rl_b200.colocated import ColocatedGRPO
+    from cosmos_rl_b200.config import Config
+    cfg = Config.from_dict({
+        "mode": "colocated",
+        "policy": {"model_name_or_path": arch, "model_max_length": 192, "parallelism": {"tp_size": 1}},
+        "rollout": {"n_generation": 4, "batch_size": 4, "max_response_length": 32, "parallelism": {"tp_size": 1}},
+        "train": {"seed": 0, "optm_lr": 1e-4, "output_dir": str(tmp_path),
+                  "train_policy": {"type": "grpo", "reward_function": ["even_token_fraction"], "mini_batch": 8,
+                                   "kl_beta": 0.01}}})
+    job = ColocatedGRPO(cfg, device=torch.device("cuda", 0), max_num_seqs=16)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 32000, (48,), generator=g) for _ in range(4)]
+    w0 = job.trainer.flat.data.clone()
+    for _ in range(2):
+        rep = job.step(prompts)
+    torch.cuda.synchronize()
+    assert native.read_status(torch.device("cuda", 0)) == 0
+    assert math.isfinite(rep["train/loss_avg"]) and math.isfinite(rep["train/grad_norm"]) and rep["train/grad_norm"] > 0
+    assert not torch.equal(job.trainer.flat.data, w0)
+    assert 0.0 <= rep["rollout/reward_mean"] <= 1.0
