@@ -185,6 +185,12 @@ int b200_reshard_pull(const B200CopyDesc* descs_dev, const int* tile_prefix_dev,
 // republishes [lo, lo + n).
 int b200_peer_all_reduce(void* const* bufs, int n_ranks, long long lo, long long n, float scale, cudaStream_t stream);
 
+// All-to-all-v of rows over peer memory (a2av.cu): push the rows owed to every rank into its receive buffer and add
+// the delivered row count to its arrival counter.
+int b200_a2av_push(const void* src, long long src_ld_bytes, int row_bytes, int ep, const int* send_off,
+                   void* const* dst_ptrs, const long long* dst_row, long long dst_ld_bytes, void* const* flag_ptrs,
+                   cudaStream_t stream);
+
 // Block-scaled fp8 GEMM (gemm_fp8_block.cu): A [M,K] e4m3 + sa [M, ldsa] (1 x 128 blocks), B [N,K] e4m3 +
 // sb [ceil(N/128), ldsb] (128 x 128 blocks), C [M,N] bf16.
 int b200_gemm_fp8_block(const void* A, const float* sa, const void* B, const float* sb, void* C, int M, int N, int K,

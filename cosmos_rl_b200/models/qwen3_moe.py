@@ -80,6 +80,7 @@ class MoEFeedForward(nn.Module):
         self.w_gate_up = nn.Parameter(torch.empty(self.E_local, 2 * self.I, a.dim))
         self.w_down = nn.Parameter(torch.empty(self.E_local, a.dim, self.I))
         self.ep_group: Optional[dist.ProcessGroup] = None
+        self.peer_a2a = None       # parallel.peer_a2a.PeerAllToAll: token exchange over NVLink peer memory
         self.last_aux_loss: Optional[torch.Tensor] = None
 
     def route(self, x: torch.Tensor):
@@ -118,33 +119,52 @@ class MoEFeedForward(nn.Module):
         send_x = x[tok]
         dest = flat_e[order] // El
         send_counts = torch.bincount(dest, minlength=ep)
-        recv_counts = torch.empty_like(send_counts)
-        dist.all_to_all_single(recv_counts, send_counts, group=self.ep_group)
-        sc, rc = send_counts.tolist(), recv_counts.tolist()
+        peer = self.peer_a2a if (self.peer_a2a is not None and x.is_cuda) else None
+        if peer is not None:
+            # full split-size matrix (row s = what rank s sends to each rank): both sides derive row offsets from it
+            allc = [torch.empty_like(send_counts) for _ in range(ep)]
+            dist.all_gather(allc, send_counts, group=self.ep_group)
+            mat = torch.stack(allc).tolist()
+            sc, rc = mat[self.ep_rank], [mat[s][self.ep_rank] for s in range(ep)]
+        else:
+            mat = None
+            recv_counts = torch.empty_like(send_counts)
+            dist.all_to_all_single(recv_counts, send_counts, group=self.ep_group)
+            sc, rc = send_counts.tolist(), recv_counts.tolist()
         recv_e = torch.empty(sum(rc), dtype=torch.long, device=x.device)
-        recv_x = _A2A.apply(send_x, None, sc, rc, self.ep_group)
+        recv_x = _A2A.apply(send_x, peer, sc, rc, self.ep_group, mat)
         dist.all_to_all_single(recv_e, (flat_e[order] % El).contiguous(), rc, sc, group=self.ep_group)
         ones = torch.ones(recv_x.shape[0], 1, dtype=torch.float32, device=x.device)
         y = M.moe_experts(recv_x, ones, recv_e[:, None].to(torch.int32), self.w_gate_up, self.w_down)
-        back = _A2A.apply(y, None, rc, sc, self.ep_group)
+        matT = [list(r) for r in zip(*mat)] if mat is not None else None
+        back = _A2A.apply(y, peer, rc, sc, self.ep_group, matT)
         w = probs.flatten()[order].to(back.dtype)[:, None]
         out = torch.zeros(T, H, dtype=back.dtype, device=x.device).index_add_(0, tok, back * w)
         return out
 
 
 class _A2A(torch.autograd.Function):
+    """Rows sorted by destination rank out, rows sorted by source rank back. ``peer`` (a ``PeerAllToAll``) moves the
+    payload with the peer-memory push kernel; without it the library collective does. ``mat[s][d]`` is the split-size
+    matrix of the forward direction (only needed by the peer path)."""
+
     @staticmethod
-    def forward(ctx, x, _unused, send_counts, recv_counts, group):
-        ctx.sc, ctx.rc, ctx.group = send_counts, recv_counts, group
+    def forward(ctx, x, peer, send_counts, recv_counts, group, mat=None):
+        ctx.sc, ctx.rc, ctx.group, ctx.peer, ctx.mat = send_counts, recv_counts, group, peer, mat
+        if peer is not None:
+            return peer.exchange(x.contiguous(), send_counts, mat)
         out = torch.empty(sum(recv_counts), x.shape[1], dtype=x.dtype, device=x.device)
         dist.all_to_all_single(out, x.contiguous(), recv_counts, send_counts, group=group)
         return out
 
     @staticmethod
     def backward(ctx, g):
+        if ctx.peer is not None:
+            matT = [list(r) for r in zip(*ctx.mat)]
+            return ctx.peer.exchange(g.contiguous(), ctx.rc, matT), None, None, None, None, None
         out = torch.empty(sum(ctx.sc), g.shape[1], dtype=g.dtype, device=g.device)
         dist.all_to_all_single(out, g.contiguous(), ctx.sc, ctx.rc, group=ctx.group)
-        return out, None, None, None, None
+        return out, None, None, None, None, None
 
 
 class Qwen3MoEBlock(nn.Module):

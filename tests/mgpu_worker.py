@@ -284,6 +284,53 @@ def main():
         print(f"pipeline 1F1B over {world} stages (NCCL p2p): gradients match the unsplit model", flush=True)
     del full, stage, fflat, sflat
 
+    # ------------------------------------------------------------ 2e. expert parallelism: peer-memory token exchange
+    from cosmos_rl_b200.models.qwen3_moe import ARCHS as MOE_ARCHS, MoEFeedForward
+    from cosmos_rl_b200.parallel.peer_a2a import PeerAllToAll
+    ma = copy.deepcopy(MOE_ARCHS["tiny-qwen3-moe"])
+    ma.aux_loss_coeff, ma.dim, ma.moe_ffn_dim, ma.n_experts, ma.top_k = 0.0, 512, 256, 8, 2
+    torch.manual_seed(0)
+    full_moe = MoEFeedForward(ma).to(dev).to(torch.bfloat16)
+    for p_ in full_moe.parameters():
+        torch.nn.init.normal_(p_, std=0.05)
+    mb_ = copy.deepcopy(ma)
+    mb_.ep_size, mb_.ep_rank = world, rank
+    loc = MoEFeedForward(mb_).to(dev).to(torch.bfloat16)
+    El = ma.n_experts // world
+    with torch.no_grad():
+        for t_ in (full_moe.gate.weight, full_moe.w_gate_up, full_moe.w_down):
+            dist.broadcast(t_, src=0, group=grp)
+        loc.gate.weight.copy_(full_moe.gate.weight)
+        loc.w_gate_up.copy_(full_moe.w_gate_up[rank * El:(rank + 1) * El])
+        loc.w_down.copy_(full_moe.w_down[rank * El:(rank + 1) * El])
+    loc.ep_group = grp
+    n_tok = 3000 + 500 * rank
+    loc.peer_a2a = PeerAllToAll(grp, world, rank, dev, max_rows=2 * 2 * 3600, row_bytes=ma.dim * 2, wait_s=3.0)
+    results = {}
+    for mode in ("peer", "nccl"):
+        if mode == "nccl":
+            saved_peer, loc.peer_a2a = loc.peer_a2a, None
+        gx = torch.Generator(device=dev).manual_seed(40 + rank)
+        x_ = torch.randn(n_tok, ma.dim, device=dev, generator=gx).to(torch.bfloat16)
+        xl_ = x_.clone().requires_grad_(True)
+        loc.zero_grad()
+        for rep_ in range(3):                      # several exchanges: exercises the two-set ring
+            yl_ = loc(xl_)
+        yl_.float().pow(2).sum().backward()
+        torch.cuda.synchronize(dev)
+        assert native.read_status(dev) == 0
+        results[mode] = (yl_.detach().float(), xl_.grad.float(), loc.w_down.grad.float().clone())
+    loc.peer_a2a = saved_peer
+    for a_, b_ in zip(results["peer"], results["nccl"]):
+        assert torch.allclose(a_, b_, atol=2e-2, rtol=2e-2), (a_ - b_).abs().max()
+    xf_ = x_.clone().requires_grad_(True)
+    yf_ = full_moe(xf_)
+    assert (results["peer"][0] - yf_.detach().float()).abs().max().item() <= 0.05 * yf_.abs().max().item() + 1e-2
+    if rank == 0:
+        print("expert-parallel MoE layer with the peer-memory all-to-all-v: forward and gradients match the "
+              "library exchange and the unsharded layer", flush=True)
+    loc.peer_a2a.close()
+
     # ------------------------------------------------------------ 3. TP engine == single-GPU engine (greedy)
     rm.tp = TensorParallel(grp, world, rank)
     rm.tp.fused_min_rows = 1          # exercise the fused GEMM + all-reduce kernel at the test's small shapes
