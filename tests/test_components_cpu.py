@@ -268,3 +268,16 @@ def test_reward_calculator_dapo_validity_and_shared_prefix():
             break
     assert len(got) == 1 and got[0].rewards == [1.0, 0.0]
     d.shutdown()
+
+
+def test_reference_import_paths_resolve_to_this_package():
+    """Entry scripts written against the reference's module paths import this framework unchanged."""
+    import importlib
+    from cosmos_rl.launcher.worker_entry import main
+    from cosmos_rl.dispatcher.data.packer import BaseDataPacker
+    from cosmos_rl.policy.config import Config as RefPathConfig
+    import cosmos_rl_b200.data.packer as pk
+    import cosmos_rl_b200.launcher.worker_entry as we
+    assert main is we.main and BaseDataPacker is pk.BaseDataPacker and RefPathConfig is Config
+    with pytest.raises(ImportError):
+        importlib.import_module("cosmos_rl.no_such_module")
