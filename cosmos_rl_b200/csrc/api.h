@@ -191,6 +191,19 @@ int b200_a2av_push(const void* src, long long src_ld_bytes, int row_bytes, int e
                    void* const* dst_ptrs, const long long* dst_row, long long dst_ld_bytes, void* const* flag_ptrs,
                    cudaStream_t stream);
 
+// Expert-parallel MoE forward over peer memory (ep_gemm.cu): device-side layout from the all-gathered counts, token
+// dispatch fused into the first grouped GEMM, combine push.
+int b200_ep_layout(const int* counts, int ep, int E, int rank, int max_tiles, int* send_off, int* dst_base,
+                   int* ret_base, int* block_start, int* tile_expert, int* block_target, int* n_tiles,
+                   cudaStream_t stream);
+int b200_ep_dispatch_gemm(const void* x, long long ldx, const void* W, void* Y, long long ldy, int max_rows, int N,
+                          int H, int E, int ep, int rank, const int* send_off, const int* dst_base,
+                          void* const* recv_ptrs, void* const* flag_ptrs, const int* tile_expert,
+                          const int* block_target, const int* n_tiles, unsigned long long wait_ns, uint32_t* status,
+                          int num_sms, cudaStream_t stream);
+int b200_ep_combine_push(const void* y, int H, int E, int ep, int rank, const int* counts, const int* block_start,
+                         const int* ret_base, void* const* ret_ptrs, void* const* flag_ptrs, cudaStream_t stream);
+
 // Block-scaled fp8 GEMM (gemm_fp8_block.cu): A [M,K] e4m3 + sa [M, ldsa] (1 x 128 blocks), B [N,K] e4m3 +
 // sb [ceil(N/128), ldsb] (128 x 128 blocks), C [M,N] bf16.
 int b200_gemm_fp8_block(const void* A, const float* sa, const void* B, const float* sb, void* C, int M, int N, int K,

@@ -330,6 +330,25 @@ def main():
         print("expert-parallel MoE layer with the peer-memory all-to-all-v: forward and gradients match the "
               "library exchange and the unsharded layer", flush=True)
     loc.peer_a2a.close()
+    # fused dispatch + grouped GEMM + combine (inference path) against the library exchange
+    from cosmos_rl_b200.parallel.ep_fused import FusedEPForward
+    fe = FusedEPForward(grp, world, rank, dev, ma.n_experts, ma.dim, max_tokens=4096, top_k=ma.top_k, wait_s=3.0)
+    loc.peer_a2a = None
+    with torch.no_grad():
+        for trial in range(3):                     # three calls: both buffer sets and their re-arming
+            gx = torch.Generator(device=dev).manual_seed(70 + 10 * trial + rank)
+            xt = torch.randn(1500 + 700 * trial + 300 * rank, ma.dim, device=dev, generator=gx).to(torch.bfloat16)
+            pr, ix, _, _ = loc.route(xt)
+            want_ep = loc._forward_ep(xt, pr, ix)
+            got_ep = fe.forward(xt, pr, ix, loc.w_gate_up, loc.w_down)
+            torch.cuda.synchronize(dev)
+            assert native.read_status(dev) == 0, f"fused EP forward trial {trial}"
+            err = (got_ep.float() - want_ep.float()).abs().max().item()
+            assert err <= 0.03 * want_ep.float().abs().max().item() + 1e-2, (trial, err)
+    if rank == 0:
+        print("fused expert-parallel forward (dispatch in the grouped GEMM, peer combine): matches the library path",
+              flush=True)
+    fe.close()
 
     # ------------------------------------------------------------ 3. TP engine == single-GPU engine (greedy)
     rm.tp = TensorParallel(grp, world, rank)
