@@ -81,6 +81,7 @@ class MoEFeedForward(nn.Module):
         self.w_down = nn.Parameter(torch.empty(self.E_local, a.dim, self.I))
         self.ep_group: Optional[dist.ProcessGroup] = None
         self.peer_a2a = None       # parallel.peer_a2a.PeerAllToAll: token exchange over NVLink peer memory
+        self.fused_ep = None       # parallel.ep_fused.FusedEPForward: inference path, dispatch fused into the GEMM
         self.last_aux_loss: Optional[torch.Tensor] = None
 
     def route(self, x: torch.Tensor):
@@ -104,6 +105,10 @@ class MoEFeedForward(nn.Module):
         probs, idx, counts, _ = self.route(x)
         if self.ep_size == 1:
             return M.moe_experts(x, probs, idx, self.w_gate_up, self.w_down, counts)
+        if (self.fused_ep is not None and x.is_cuda and not torch.is_grad_enabled()
+                and x.shape[0] * self.k <= self.fused_ep.max_send):
+            # inference: dispatch fused into the first grouped GEMM, no host read of the split sizes
+            return self.fused_ep.forward(x, probs, idx, self.w_gate_up, self.w_down)
         return self._forward_ep(x, probs, idx)
 
     # ------------------------------------------------------------------ expert parallel (library all-to-all)
