@@ -116,28 +116,43 @@ struct EpgEpilogue {
     }
   }
 
-  // side warps: one warp per token row
+  // side warps: a warp pushes batches of EPG_BATCH token rows, then one system fence, then the arrival counts.
+  // Rows are visited starting with those owed to the NEXT rank (they have the longest way), this rank's own last.
   template <class Sched>
   __device__ __forceinline__ void side(const Params& p, const Sched&, int w, int lane, uint32_t*) {
+    constexpr int EPG_BATCH = 4;
     const int n_rows = p.send_off[p.E];
     const int vec = p.H >> 3;
-    for (int r = blockIdx.x * EPG_SIDE_WARPS + w; r < n_rows; r += gridDim.x * EPG_SIDE_WARPS) {
-      int lo = 0, hi = p.E - 1;                       // last expert whose first row <= r
-      while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (p.send_off[mid] <= r) lo = mid; else hi = mid - 1;
+    const int rot = p.send_off[((p.rank + 1) % p.ep) * p.El];
+    const int n_warps = gridDim.x * EPG_SIDE_WARPS, me = blockIdx.x * EPG_SIDE_WARPS + w;
+    for (int base = me * EPG_BATCH; base < n_rows; base += n_warps * EPG_BATCH) {
+      uint32_t* fl[EPG_BATCH];
+#pragma unroll
+      for (int q = 0; q < EPG_BATCH; ++q) {
+        fl[q] = nullptr;
+        const int i = base + q;
+        if (i >= n_rows) continue;
+        int r = i + rot;
+        if (r >= n_rows) r -= n_rows;
+        int lo = 0, hi = p.E - 1;                     // last expert whose first row <= r
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (p.send_off[mid] <= r) lo = mid; else hi = mid - 1;
+        }
+        const int e = lo, d = e / p.El;
+        const long long drow = (long long)p.dst_base[e] + (r - p.send_off[e]);
+        const uint4* src = reinterpret_cast<const uint4*>(p.x + (long long)r * p.ldx);
+        uint4* dst = reinterpret_cast<uint4*>(p.recv[d] + drow * p.H);
+        for (int v = lane; v < vec; v += 32) dst[v] = src[v];
+        fl[q] = p.flags[d] + drow / GEMM_BM;
       }
-      const int e = lo, d = e / p.El;
-      const long long drow = (long long)p.dst_base[e] + (r - p.send_off[e]);
-      const uint4* src = reinterpret_cast<const uint4*>(p.x + (long long)r * p.ldx);
-      uint4* dst = reinterpret_cast<uint4*>(p.recv[d] + drow * p.H);
-      for (int v = lane; v < vec; v += 32) dst[v] = src[v];
       __threadfence_system();
       fence_proxy_async_all();
       __syncwarp();
       if (lane == 0) {
-        uint32_t* f = p.flags[d] + drow / GEMM_BM;
-        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(f) : "memory");
+#pragma unroll
+        for (int q = 0; q < EPG_BATCH; ++q)
+          if (fl[q]) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(fl[q]) : "memory");
       }
     }
   }

@@ -124,10 +124,10 @@ class FusedEPForward:
         flags, ret = self._set_view(st)
         flag_wait(flags.data_ptr(), T * k, dev, self.wait_s)                # every copy of my tokens is back
         back = ret[:T * k * H * 2].view(torch.bfloat16).view(T * k, H)
-        w = probs.flatten()[order].to(torch.float32)[:, None]
-        out = torch.zeros(T, H, dtype=torch.float32, device=dev).index_add_(0, tok, back.float() * w)
+        w = probs.flatten()[order].to(back.dtype)[:, None]
+        out = torch.zeros(T, H, dtype=back.dtype, device=dev).index_add_(0, tok, back * w)   # as the library path
         flags.zero_()                                                       # re-arm this set (reused two calls later)
-        return out.to(x.dtype)
+        return out
 
     def close(self) -> None:
         torch.cuda.synchronize(self.device)
