@@ -238,6 +238,13 @@ class Qwen3MoE(GPT):
 
     def init_weights(self, seed: int = 0, std: float = 0.02) -> None:
         super().init_weights(seed, std)
+        if self.args.ep_size > 1:
+            # every rank draws the same stream: give the experts this rank owns their own values
+            g = torch.Generator(device="cpu").manual_seed(seed * 1000003 + 17 + self.args.ep_rank)
+            with torch.no_grad():
+                for name, p in self.named_parameters():
+                    if name.endswith("w_gate_up") or name.endswith("w_down"):
+                        p.copy_(torch.randn(p.shape, generator=g, dtype=torch.float32).mul_(std).to(p.dtype))
 
     def aux_loss(self) -> Optional[torch.Tensor]:
         losses = [l.mlp.last_aux_loss for l in self.layers if l.mlp.last_aux_loss is not None]

@@ -31,12 +31,14 @@ class FlatParams:
 
     def __init__(self, module: nn.Module, dtype: torch.dtype, device: torch.device, shard_multiple: int = 1,
                  allocator: Optional[Callable[[int, torch.dtype, torch.device], torch.Tensor]] = None,
-                 with_grad: bool = True):
+                 with_grad: bool = True, local_filter: Optional[Callable[[str], bool]] = None):
+        """``local_filter(name)`` marks parameters that are NOT replicas across the data-parallel ranks (the experts
+        an expert-parallel rank owns). They are laid out after everything else: ``[0, shared_total)`` is the region
+        the sharded optimizer reduces and republishes, ``[shared_total, total)`` stays local to the rank."""
         self.module = module
         self.dtype = dtype
         self.device = device
         self.slots: List[FlatSlot] = []
-        off = 0
         seen: Dict[int, int] = {}
         owners: List[List[Tuple[nn.Module, str]]] = []
         olds: List[nn.Parameter] = []
@@ -53,10 +55,23 @@ class FlatParams:
                 owners.append([(mod, pname)])
                 olds.append(p)
                 names.append(full)
-                self.slots.append(FlatSlot(full, off, p.numel(), tuple(p.shape)))
-                off += (p.numel() + ALIGN_ELEMS - 1) // ALIGN_ELEMS * ALIGN_ELEMS
         unit = ALIGN_ELEMS * max(1, shard_multiple)
-        self.total = (off + unit - 1) // unit * unit
+        is_local = [bool(local_filter and local_filter(n)) for n in names]
+        offsets = [0] * len(names)
+        off = 0
+        for i, (n, p) in enumerate(zip(names, olds)):
+            if not is_local[i]:
+                offsets[i] = off
+                off += (p.numel() + ALIGN_ELEMS - 1) // ALIGN_ELEMS * ALIGN_ELEMS
+        self.shared_total = (off + unit - 1) // unit * unit
+        off = self.shared_total
+        for i, (n, p) in enumerate(zip(names, olds)):
+            if is_local[i]:
+                offsets[i] = off
+                off += (p.numel() + ALIGN_ELEMS - 1) // ALIGN_ELEMS * ALIGN_ELEMS
+        for n, p, o in zip(names, olds, offsets):
+            self.slots.append(FlatSlot(n, o, p.numel(), tuple(p.shape)))
+        self.total = (off + unit - 1) // unit * unit if any(is_local) else self.shared_total
         alloc = allocator or (lambda n, dt, dev: torch.zeros(n, dtype=dt, device=dev))
         self.data = alloc(self.total, dtype, device)
         self.grad = alloc(self.total, dtype, device) if with_grad else None
@@ -91,7 +106,8 @@ class FlatParams:
                     p.grad = self.grad[slot.offset: slot.offset + slot.numel].view(slot.shape)
 
     def shard_range(self, rank: int, world: int) -> Tuple[int, int]:
-        per = self.total // world
+        """This rank's slice of the replicated region (the rank-local tail is never sharded)."""
+        per = self.shared_total // world
         return rank * per, (rank + 1) * per
 
     def trainable_mask(self) -> Optional[torch.Tensor]:

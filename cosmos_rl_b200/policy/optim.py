@@ -66,6 +66,14 @@ class FlatAdamW:
         self.m = torch.zeros(n, dtype=torch.float32, device=dev)
         self.v = torch.zeros(n, dtype=torch.float32, device=dev)
         self.grad_shard = torch.zeros(n, dtype=torch.float32, device=dev) if self.world > 1 else None
+        # rank-local tail (expert-parallel experts): full optimizer state here, no reduction, no publication
+        self.t0, self.t1 = flat.shared_total, flat.total
+        self.tail = None
+        if self.t1 > self.t0:
+            nt = self.t1 - self.t0
+            self.tail = {"master": flat.data[self.t0:self.t1].to(torch.float32, copy=True),
+                         "m": torch.zeros(nt, dtype=torch.float32, device=dev),
+                         "v": torch.zeros(nt, dtype=torch.float32, device=dev)}
         self.step_count = 0
         self.last_grad_norm: Optional[torch.Tensor] = None
         self.trainable = flat.trainable_mask()
@@ -74,6 +82,8 @@ class FlatAdamW:
     def refresh_master_from_params(self) -> None:
         """After loading weights into the bf16 buffer (HF load, weight resume)."""
         self.master.copy_(self.flat.data[self.lo:self.hi].to(torch.float32))
+        if self.tail is not None:
+            self.tail["master"].copy_(self.flat.data[self.t0:self.t1].to(torch.float32))
 
     def _reduce_grads(self) -> torch.Tensor:
         """Returns this rank's averaged gradient shard (fp32 when dp > 1, a bf16 view otherwise)."""
@@ -105,6 +115,13 @@ class FlatAdamW:
         else:
             g = self._reduce_grads()
             sumsq = K.grad_sumsq([g])
+        if self.tail is not None:
+            # experts see the tokens of every rank: their gradient already is the sum over ranks, so it takes the
+            # same 1/world factor as the averaged replicated gradients; each rank adds its own experts to the norm
+            gt = self.flat.grad[self.t0:self.t1]
+            if self.trainable is not None:
+                gt.mul_(self.trainable[self.t0:self.t1].to(gt.dtype))
+            sumsq = sumsq + K.grad_sumsq([gt]) / float(self.world * self.world)
         if self.world > 1:
             dist.all_reduce(sumsq, group=self.group)
         for grp in extra_norm_groups:  # e.g. tensor-/pipeline-parallel groups that hold disjoint parameters
@@ -118,7 +135,11 @@ class FlatAdamW:
             shadow = self.flat.data[self.lo:self.hi]
             K.adamw_flat(self.master, self.m, self.v, g, shadow, **hp)
             if self.world > 1:
-                dist.all_gather_into_tensor(self.flat.data, shadow.clone(), group=self.group)
+                dist.all_gather_into_tensor(self.flat.data[:self.t0], shadow.clone(), group=self.group)
+        if self.tail is not None:
+            hp_t = dict(hp, grad_scale=coef / float(self.world))
+            K.adamw_flat(self.tail["master"], self.tail["m"], self.tail["v"], self.flat.grad[self.t0:self.t1],
+                         self.flat.data[self.t0:self.t1], **hp_t)
         self.last_grad_norm = norm
         return norm
 
@@ -127,8 +148,11 @@ class FlatAdamW:
 
     # ------------------------------------------------------------------ state (per-rank shard)
     def state_dict(self) -> Dict[str, Any]:
-        return {"master": self.master, "m": self.m, "v": self.v, "step": self.step_count, "lo": self.lo,
-                "hi": self.hi, "world": self.world}
+        sd = {"master": self.master, "m": self.m, "v": self.v, "step": self.step_count, "lo": self.lo,
+              "hi": self.hi, "world": self.world}
+        if self.tail is not None:
+            sd["tail"] = dict(self.tail)
+        return sd
 
     def load_state_dict(self, sd: Dict[str, Any]) -> None:
         if sd["hi"] - sd["lo"] != self.hi - self.lo:
@@ -138,7 +162,14 @@ class FlatAdamW:
         self.v.copy_(sd["v"])
         self.step_count = int(sd["step"])
         self.flat.data[self.lo:self.hi].copy_(self.master.to(self.flat.dtype))
+        if self.tail is not None and "tail" in sd:
+            for k in ("master", "m", "v"):
+                self.tail[k].copy_(sd["tail"][k])
+            self.flat.data[self.t0:self.t1].copy_(self.tail["master"].to(self.flat.dtype))
 
     def state_tensors(self):
         """Named tensors shipped to a new replica on elastic scale-up (policy-to-policy unicast)."""
-        return [("optim.master", self.master), ("optim.m", self.m), ("optim.v", self.v)]
+        out = [("optim.master", self.master), ("optim.m", self.m), ("optim.v", self.v)]
+        if self.tail is not None:
+            out += [(f"optim.tail.{k}", t) for k, t in self.tail.items()]
+        return out

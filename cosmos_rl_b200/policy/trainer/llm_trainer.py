@@ -43,15 +43,28 @@ class LLMTrainer(Trainer):
         mt = self.hf_config.get("model_type") if isinstance(self.hf_config, dict) else self.hf_config.model_type
         self.model_type = mt
         tp = parallel_dims.tp
+        ep = getattr(parallel_dims, "ep", 1)
+        build_kw = {}
+        if ep > 1:
+            # experts are spread over the dp_shard ranks (the layout of the reference's Qwen3-MoE plan,
+            # cosmos_rl/policy/model/qwen3_moe/parallelize.py:120-190, with ep == dp_shard)
+            if ep != parallel_dims.dp_shard or parallel_dims.cp > 1:
+                raise NotImplementedError("expert parallelism needs ep_size == dp_shard_size and cp_size == 1")
+            build_kw = dict(ep_size=ep, ep_rank=parallel_dims.dp_shard_coord)
         with torch.device("meta"):
-            model = ModelRegistry.build_model(self.hf_config, tp_size=tp, tp_rank=parallel_dims.tp_coord)
+            model = ModelRegistry.build_model(self.hf_config, tp_size=tp, tp_rank=parallel_dims.tp_coord, **build_kw)
+        if ep > 1 and not hasattr(model, "set_ep_group"):
+            raise NotImplementedError(f"model type {mt} has no expert-parallel plan")
         # the model stays on the meta device here: FlatParams materialises every parameter as a view of
         # one flat buffer, so no second copy of the weights is ever allocated
         self.model = model
         self._apply_trainable_patterns()
         dp = parallel_dims.dp_shard
+        is_expert = (lambda n: n.endswith("w_gate_up") or n.endswith("w_down")) if ep > 1 else None
         self.flat = FlatParams(model, self.param_dtype, self.device, shard_multiple=dp,
-                               allocator=kw.get("allocator"))
+                               allocator=kw.get("allocator"), local_filter=is_expert)
+        if ep > 1:
+            model.set_ep_group(parallel_dims.group("dp_shard"))
         rc = config.b200.recompute if config.policy.model_gradient_checkpointing else "none"
         self._recompute_auto = rc == "auto"
         model.gradient_checkpointing = {"none": False, "auto": "selective"}.get(rc, rc)

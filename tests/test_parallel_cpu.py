@@ -277,3 +277,104 @@ def _zero_worker(rank, world, store):
 
 def test_sharded_flat_adamw_matches_unsharded(tmp_path):
     _spawn(_zero_worker, 2, tmp_path)
+
+
+def _ep_train_worker(rank, world, store):
+    """Training with expert parallelism: experts live in a rank-local tail of the flat buffer (full optimizer state,
+    no reduction), everything else is reduced and sharded as usual. Two optimizer steps must reproduce plain AdamW on
+    the unsharded model fed with both ranks' data."""
+    import copy
+    from cosmos_rl_b200.models.qwen3_moe import ARCHS, MoEFeedForward, Qwen3MoE
+    from cosmos_rl_b200.ops import reference as R
+    from cosmos_rl_b200.parallel.flat import FlatParams
+    from cosmos_rl_b200.policy.optim import FlatAdamW
+    _init(rank, world, store)
+    a = copy.deepcopy(ARCHS["tiny-qwen3-moe"])
+    a.vocab_size, a.aux_loss_coeff = 512, 0.0
+    ref = Qwen3MoE(a)
+    ref.init_weights(0)
+    rflat = FlatParams(ref, torch.float32, torch.device("cpu"))
+    b = copy.deepcopy(a)
+    b.ep_size, b.ep_rank = world, rank
+    ep = Qwen3MoE(b)
+    is_expert = lambda n: n.endswith("w_gate_up") or n.endswith("w_down")
+    flat = FlatParams(ep, torch.float32, torch.device("cpu"), shard_multiple=world, local_filter=is_expert)
+    assert flat.total > flat.shared_total and flat.shared_total % world == 0
+    El = a.n_experts // world
+    rp = dict(ref.named_parameters())
+    with torch.no_grad():
+        for n, p in ep.named_parameters():
+            p.copy_(rp[n][rank * El:(rank + 1) * El] if is_expert(n) else rp[n])
+    for mod in ep.modules():
+        if isinstance(mod, MoEFeedForward):
+            mod.ep_group = dist.group.WORLD
+    hp = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, max_grad_norm=0.5)
+    opt = FlatAdamW(flat, dp_group=dist.group.WORLD, **hp)
+    w = rflat.data.clone()
+    mm, vv = torch.zeros_like(w), torch.zeros_like(w)
+    data = []
+    for r in range(world):
+        g = torch.Generator().manual_seed(50 + r)
+        n = 14 + 5 * r
+        data.append((torch.randint(0, 512, (n,), generator=g), torch.randint(0, 512, (n,), generator=g),
+                     torch.tensor([0, n])))
+    loss_of = lambda model, d: -model.logprobs(model(d[0], torch.arange(d[0].numel()), d[2], int(d[0].numel())), d[1])[0].mean()
+    for step in range(1, 3):
+        rflat.zero_grad()
+        (sum(loss_of(ref, d) for d in data) / world).backward()
+        gn = rflat.grad.double().norm().item()  # the fp32 CPU norm of a long vector is off by 3e-4
+        R.adamw_step(w, mm, vv, rflat.grad, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, grad_scale=min(1.0, 0.5 / (gn + 1e-6)))
+        rflat.data.copy_(w)
+        flat.zero_grad()
+        loss_of(ep, data[rank]).backward()
+        norm = opt.step()
+        assert abs(norm.item() - gn) < 1e-4 * max(1.0, gn), (norm.item(), gn)
+        for n, p in ep.named_parameters():
+            want = rp[n][rank * El:(rank + 1) * El] if is_expert(n) else rp[n]
+            # Adam divides by |g|: elements whose gradient is near eps amplify reduction-order noise, a wiring error is ~lr
+            assert torch.allclose(p, want, atol=5e-4), (step, n, (p - want).abs().max())
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_training_matches_unsharded_adamw(tmp_path):
+    _spawn(_ep_train_worker, 2, tmp_path)
+
+
+def _ep_trainer_worker(rank, world, store, out_dir):
+    """The SFT trainer with ``policy.parallelism.ep_size = dp_shard_size = 2``: experts are split over the ranks,
+    the loss falls, and the replicated parameters stay bit-identical on both ranks."""
+    from cosmos_rl_b200.config import Config
+    from cosmos_rl_b200.parallel.dims import ParallelDims
+    from cosmos_rl_b200.policy.trainer.sft_trainer import SFTTrainer
+    _init(rank, world, store)
+    cfg = Config.from_dict({
+        "policy": {"model_name_or_path": "tiny-qwen3-moe", "model_max_length": 64, "model_gradient_checkpointing": False,
+                   "parallelism": {"dp_shard_size": 2, "ep_size": 2, "tp_size": 1}},
+        "train": {"seed": 0, "optm_lr": 2e-3, "optm_warmup_steps": 0, "output_dir": out_dir,
+                  "train_policy": {"type": "sft", "trainer_type": "sft", "mini_batch": 2},
+                  "ckpt": {"enable_checkpoint": False}},
+    })
+    dims = ParallelDims.from_config_parallelism(cfg.policy.parallelism, world, rank, torch.device("cpu"))
+    dims.build_groups()
+    tr = SFTTrainer(cfg, dims, device=torch.device("cpu"))
+    tr.model_load_from_hf()
+    a = tr.model.args
+    assert a.ep_size == 2 and a.ep_rank == rank and tr.flat.total > tr.flat.shared_total
+    V = a.vocab_size
+    g = torch.Generator().manual_seed(10 + rank)
+    batch = [{"input_ids": torch.randint(0, V, (n,), generator=g).tolist()} for n in (12, 9, 15, 7)]
+    losses = [tr.step_training(batch, total_steps=10, train_step=i + 1)["train/loss_avg"] for i in range(4)]
+    assert losses[-1] < losses[0] - 0.05, losses
+    shared = tr.flat.data[:tr.flat.shared_total].clone()
+    both = [torch.empty_like(shared) for _ in range(world)]
+    dist.all_gather(both, shared)
+    assert torch.equal(both[0], both[1])
+    tail = tr.flat.data[tr.flat.shared_total:].clone()
+    tails = [torch.empty_like(tail) for _ in range(world)]
+    dist.all_gather(tails, tail)
+    assert not torch.equal(tails[0], tails[1])                       # each rank owns different experts
+    dist.destroy_process_group()
+
+
+def test_sft_trainer_with_expert_parallelism(tmp_path):
+    _spawn(_ep_trainer_worker, 2, tmp_path, str(tmp_path))
