@@ -51,8 +51,14 @@ def lr_factor(step: int, total_steps: int, warmup_steps, warmup_start_factor: fl
 class FlatAdamW:
     def __init__(self, flat: FlatParams, lr: float, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
                  max_grad_norm: float = 1.0, dp_group: Optional[dist.ProcessGroup] = None,
-                 master_dtype: torch.dtype = torch.float32, collective=None):
+                 master_dtype: torch.dtype = torch.float32, collective=None,
+                 replicate_group: Optional[dist.ProcessGroup] = None):
+        """``dp_group`` shards optimizer state (ZeRO-2 style); ``replicate_group`` is the outer data-parallel axis of
+        HSDP / DDP (cosmos_rl/policy/model/gpt/parallelize.py:80-113, 426-442): ranks of it hold the same shard and
+        average their reduced gradient shard before the update, so the all-reduce moves 1/dp_shard of the gradient."""
         self.flat = flat
+        self.replicate_group = replicate_group
+        self.n_replicas = dist.get_world_size(replicate_group) if replicate_group is not None else 1
         self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
         self.max_grad_norm = max_grad_norm
         self.group = dp_group
@@ -115,6 +121,19 @@ class FlatAdamW:
         else:
             g = self._reduce_grads()
             sumsq = K.grad_sumsq([g])
+        if self.n_replicas > 1:
+            if g.dtype != torch.float32:           # dp_shard == 1: the shard is the bf16 gradient buffer itself
+                g32 = g.to(torch.float32)
+                dist.all_reduce(g32, group=self.replicate_group)
+                g.copy_(g32.div_(self.n_replicas))
+            else:
+                dist.all_reduce(g, group=self.replicate_group)
+                g.div_(self.n_replicas)
+            sumsq = K.grad_sumsq([g])
+            if self.tail is not None:
+                gt32 = self.flat.grad[self.t0:self.t1].to(torch.float32)
+                dist.all_reduce(gt32, group=self.replicate_group)
+                self.flat.grad[self.t0:self.t1].copy_(gt32.div_(self.n_replicas))
         if self.tail is not None:
             # experts see the tokens of every rank: their gradient already is the sum over ranks, so it takes the
             # same 1/world factor as the averaged replicated gradients; each rank adds its own experts to the norm

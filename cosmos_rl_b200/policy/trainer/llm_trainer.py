@@ -76,7 +76,8 @@ class LLMTrainer(Trainer):
         self.optimizer = FlatAdamW(
             self.flat, lr=lr, betas=tuple(config.train.optm_betas), eps=config.train.epsilon,
             weight_decay=config.train.optm_weight_decay, max_grad_norm=config.train.optm_grad_norm_clip,
-            dp_group=parallel_dims.group("dp_shard") if dp > 1 else None, collective=kw.get("collective"))
+            dp_group=parallel_dims.group("dp_shard") if dp > 1 else None, collective=kw.get("collective"),
+            replicate_group=parallel_dims.group("dp_replicate") if parallel_dims.dp_replicate > 1 else None)
         self.data_packer = data_packer or BaseDataPacker.get_default(mt)()
         self.tokenizer = kw.get("tokenizer")
         self.data_packer.setup(config, self.tokenizer)

@@ -378,3 +378,41 @@ def _ep_trainer_worker(rank, world, store, out_dir):
 
 def test_sft_trainer_with_expert_parallelism(tmp_path):
     _spawn(_ep_trainer_worker, 2, tmp_path, str(tmp_path))
+
+
+def _hsdp_worker(rank, world, store):
+    """HSDP on 4 ranks (dp_replicate 2 x dp_shard 2) and DDP (dp_replicate 4): the update equals plain AdamW on the
+    gradient averaged over all four ranks, and every rank ends with identical parameters."""
+    from cosmos_rl_b200.ops import reference as R
+    from cosmos_rl_b200.parallel.dims import ParallelDims
+    from cosmos_rl_b200.parallel.flat import FlatParams
+    from cosmos_rl_b200.policy.optim import FlatAdamW
+    _init(rank, world, store)
+    for rep, shard in ((2, 2), (4, 1)):
+        dims = ParallelDims(dp_replicate=rep, dp_shard=shard, world_size=world, global_rank=rank,
+                            device=torch.device("cpu"))
+        dims.build_groups()
+        m = GPT(_tiny())
+        flat = FlatParams(m, torch.float32, torch.device("cpu"), shard_multiple=shard)
+        m.init_weights(0)
+        opt = FlatAdamW(flat, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, max_grad_norm=1.0,
+                        dp_group=dims.group("dp_shard") if shard > 1 else None,
+                        replicate_group=dims.group("dp_replicate"))
+        w = flat.data.clone()
+        mm, vv = torch.zeros_like(w), torch.zeros_like(w)
+        for step in range(1, 3):
+            g = torch.Generator().manual_seed(100 * step + rank)
+            flat.grad.copy_(torch.randn(flat.total, generator=g) * 0.01)
+            gs = [torch.zeros_like(flat.grad) for _ in range(world)]
+            dist.all_gather(gs, flat.grad)
+            avg = torch.stack(gs).mean(0)
+            n = avg.double().norm().item()
+            norm = opt.step()
+            assert abs(norm.item() - n) < 1e-5, (rep, shard, norm.item(), n)
+            R.adamw_step(w, mm, vv, avg, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, grad_scale=min(1.0, 1.0 / (n + 1e-6)))
+            assert torch.allclose(flat.data, w, atol=1e-4), (rep, shard, (flat.data - w).abs().max())   # updates are ~1e-2
+    dist.destroy_process_group()
+
+
+def test_hsdp_and_ddp_match_unsharded_adamw(tmp_path):
+    _spawn(_hsdp_worker, 4, tmp_path)
