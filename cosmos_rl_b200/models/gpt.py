@@ -60,11 +60,12 @@ class GPTArgs:
     def from_hf_config(cls, c, **over) -> "GPTArgs":
         g = (lambda k, d=None: c.get(k, d)) if isinstance(c, dict) else (lambda k, d=None: getattr(c, k, d))
         mt = g("model_type", "qwen2")
+        theta = _rope_theta(g, 1e4)
         a = cls(
             vocab_size=g("vocab_size"), dim=g("hidden_size"), n_layers=g("num_hidden_layers"),
             n_heads=g("num_attention_heads"), n_kv_heads=g("num_key_value_heads") or g("num_attention_heads"),
             head_dim=g("head_dim"), ffn_dim=g("intermediate_size"), norm_eps=g("rms_norm_eps", 1e-6),
-            rope_theta=float(g("rope_theta", 1e4) or 1e4),
+            rope_theta=theta,
             qkv_bias=bool(g("attention_bias", mt == "qwen2")), qk_norm=(mt == "qwen3"),
             tie_word_embeddings=bool(g("tie_word_embeddings", False)),
             max_seq_len=g("max_position_embeddings", 4096), model_type=mt)
@@ -99,6 +100,13 @@ ARCHS: Dict[str, GPTArgs] = {
     "llama3-8b": GPTArgs(vocab_size=128256, dim=4096, n_layers=32, n_heads=32, n_kv_heads=8, ffn_dim=14336,
                          rope_theta=5e5, qkv_bias=False, model_type="llama", max_seq_len=8192),
 }
+
+
+def _rope_theta(g, default: float) -> float:
+    """``rope_theta`` of a config.json: top level (transformers 4) or inside ``rope_parameters`` (transformers 5)."""
+    rp = g("rope_parameters") or g("rope_scaling") or {}
+    t = g("rope_theta") or (rp.get("rope_theta") if isinstance(rp, dict) else getattr(rp, "rope_theta", None))
+    return float(t or default)
 
 
 def _linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -> torch.Tensor:

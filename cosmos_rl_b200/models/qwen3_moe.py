@@ -20,7 +20,7 @@ import torch.nn.functional as tF
 from ..ops import functional as F
 from ..ops import moe as M
 from .base import ModelRegistry, WeightMapper
-from .gpt import GPT, Attention, GPTArgs, GPTWeightMapper, _linear
+from .gpt import GPT, Attention, GPTArgs, GPTWeightMapper, _linear, _rope_theta
 
 
 @dataclass
@@ -39,11 +39,11 @@ class Qwen3MoEArgs(GPTArgs):
         a = cls(vocab_size=g("vocab_size"), dim=g("hidden_size"), n_layers=g("num_hidden_layers"),
                 n_heads=g("num_attention_heads"), n_kv_heads=g("num_key_value_heads"), head_dim=g("head_dim"),
                 ffn_dim=g("intermediate_size", 0) or 0, norm_eps=g("rms_norm_eps", 1e-6),
-                rope_theta=float(g("rope_theta", 1e6)), qkv_bias=bool(g("attention_bias", False)), qk_norm=True,
+                rope_theta=_rope_theta(g, 1e6), qkv_bias=bool(g("attention_bias", False)), qk_norm=True,
                 tie_word_embeddings=bool(g("tie_word_embeddings", False)),
                 max_seq_len=g("max_position_embeddings", 40960), model_type="qwen3_moe",
-                n_experts=g("num_experts"), top_k=g("num_experts_per_tok"), moe_ffn_dim=g("moe_intermediate_size"),
-                norm_topk_prob=bool(g("norm_topk_prob", True)))
+                n_experts=g("num_experts") or g("num_local_experts"), top_k=g("num_experts_per_tok"), moe_ffn_dim=g("moe_intermediate_size"),
+                norm_topk_prob=bool(g("norm_topk_prob", False)))
         for k, v in over.items():
             setattr(a, k, v)
         a.__post_init__()
@@ -203,7 +203,11 @@ class Qwen3MoEWeightMapper(GPTWeightMapper):
 
     def expert_names(self, local: str, n_experts: int, e0: int) -> List[Tuple[int, List[str]]]:
         """For a stacked expert parameter: [(global expert id, hf names in row order)] of its local experts."""
-        prefix = "model." + local.rsplit(".", 1)[0] + ".experts."
+        stem = local.rsplit(".", 1)[0]
+        if self.layer_offset and stem.startswith("layers."):
+            i, rest = stem[len("layers."):].split(".", 1)
+            stem = f"layers.{int(i) + self.layer_offset}.{rest}"
+        prefix = "model." + stem + ".experts."
         parts = ("gate_proj", "up_proj") if local.endswith("w_gate_up") else ("down_proj",)
         return [(e0 + i, [f"{prefix}{e0 + i}.{p}.weight" for p in parts]) for i in range(n_experts)]
 

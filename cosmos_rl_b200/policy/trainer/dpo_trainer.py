@@ -68,7 +68,7 @@ class DPOTrainer(LLMTrainer):
             accs.append(m["reward_acc"])
         if self.inter_replica is not None:
             self.inter_replica.all_reduce_grads(self.flat.grad)
-        norm = self.optimizer.step(self.lr_scale(self.train_step))
+        norm = self.optimizer_step()
         self.train_step = train_step
         if do_save:
             self.save_checkpoint(train_step, total_steps, is_final=train_step >= total_steps)

@@ -177,7 +177,7 @@ class GRPOTrainer(LLMTrainer):
                         metrics_acc.setdefault(k, []).append(v.detach())
                 if self.inter_replica is not None:
                     self.inter_replica.all_reduce_grads(self.flat.grad)
-                grad_norms.append(self.optimizer.step(self.lr_scale(self.train_step)))
+                grad_norms.append(self.optimizer_step())
             # mu-iterations re-use the same old log-probs
         self.train_step = current_step
 

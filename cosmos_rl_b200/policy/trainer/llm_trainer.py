@@ -121,6 +121,16 @@ class LLMTrainer(Trainer):
             if pc.trainable_map and name in pc.trainable_map:
                 p.requires_grad_(bool(pc.trainable_map[name]))
 
+    def optimizer_step(self) -> torch.Tensor:
+        """One optimizer step plus what rides on it (the router bias of DeepSeek-style MoE blocks, moved from the
+        expert load of the batch summed over the data-parallel ranks). Returns the gradient norm."""
+        norm = self.optimizer.step(self.lr_scale(self.train_step))
+        rate = self.config.b200.router_bias_update_rate
+        if rate > 0 and hasattr(self.model, "update_router_bias"):
+            dims = self.parallel_dims
+            self.model.update_router_bias(rate, dims.group("dp_shard") if dims.dp_shard > 1 else None)
+        return norm
+
     def lr_scale(self, step: int) -> float:
         t = self.config.train
         return lr_factor(step, self.total_steps, t.optm_warmup_steps, t.optm_warmup_start_factor, t.optm_decay_ratio,

@@ -66,7 +66,7 @@ class SFTTrainer(LLMTrainer):
             losses.append(loss.detach())
         if inter is not None:
             inter.all_reduce_grads(self.flat.grad)
-        norm = self.optimizer.step(self.lr_scale(self.train_step))
+        norm = self.optimizer_step()
         self.train_step = train_step
         if do_save:
             self.save_checkpoint(train_step, total_steps, is_final=train_step >= total_steps)

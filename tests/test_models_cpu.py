@@ -161,11 +161,8 @@ def test_named_architectures_shapes():
 
 
 @pytest.mark.parametrize("cfg", [
-    {"model_type": "deepseek_v3", "vocab_size": 512, "hidden_size": 64, "intermediate_size": 128,
-     "moe_intermediate_size": 32, "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 4,
-     "n_routed_experts": 4, "n_shared_experts": 1, "num_experts_per_tok": 2, "first_k_dense_replace": 1,
-     "kv_lora_rank": 16, "q_lora_rank": 24, "qk_rope_head_dim": 8, "qk_nope_head_dim": 8, "v_head_dim": 16,
-     "n_group": 1, "topk_group": 1},
+    {"model_type": "olmo2", "vocab_size": 512, "hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 2,
+     "num_attention_heads": 4, "num_key_value_heads": 2},
     {"model_type": "mistral", "vocab_size": 512, "hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 2,
      "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16},
 ])
@@ -189,3 +186,42 @@ def test_generic_hf_wrapper_packed_forward_and_training(cfg):
     lp, ent = m.logprobs(packed, torch.randint(0, 512, (19,)))
     lp.sum().backward()
     assert flat.grad.abs().sum() > 0 and torch.isfinite(flat.grad).all()
+
+
+def test_deepseek_v3_trains_exports_and_balances(tmp_path):
+    """The native DeepSeek-V3 family through the SFT trainer (named tiny architecture), the HF-name export / reload
+    round trip, and the load-balancing bias update."""
+    from cosmos_rl_b200.config import Config
+    from cosmos_rl_b200.models.deepseek_v3 import DeepseekV3
+    from cosmos_rl_b200.policy.trainer.sft_trainer import SFTTrainer
+    cfg = Config.from_dict({
+        "policy": {"model_name_or_path": "tiny-deepseek-v3", "model_max_length": 64, "model_gradient_checkpointing": False},
+        "train": {"seed": 0, "optm_lr": 2e-3, "optm_warmup_steps": 0, "output_dir": str(tmp_path),
+                  "train_policy": {"type": "sft", "trainer_type": "sft", "mini_batch": 2},
+                  "ckpt": {"enable_checkpoint": False}}})
+    tr = SFTTrainer(cfg, ParallelDims(world_size=1, device=torch.device("cpu")), device=torch.device("cpu"))
+    tr.model_load_from_hf()
+    assert isinstance(tr.model, DeepseekV3)
+    g = torch.Generator().manual_seed(0)
+    batch = [{"input_ids": torch.randint(0, 32000, (n,), generator=g).tolist()} for n in (12, 20, 7, 16)]
+    losses = [tr.step_training(batch, total_steps=10, train_step=i + 1)["train/loss_avg"] for i in range(4)]
+    assert losses[-1] < losses[0] - 0.05, losses
+    bias = tr.model.layers[1].mlp.gate.e_score_correction_bias
+    # moved only by the load-balancing rule (4 steps of 1e-3), never by AdamW
+    assert not bias.requires_grad and 0 < bias.abs().max() <= 4e-3 + 1e-9
+    before = bias.clone()
+    tr.model.update_router_bias(1e-2)
+    load = tr.model.layers[1].mlp.last_load
+    assert torch.equal(torch.sign(bias - before), torch.sign(load.mean() - load))
+    # export with HF names, reload into a fresh model, same hidden states
+    hf_cfg = tr.model.args.to_hf_config()
+    state = hf_io.hf_state_dict(tr.model, hf_cfg)
+    assert "model.layers.1.mlp.experts.3.up_proj.weight" in state and "model.layers.0.mlp.gate_proj.weight" in state
+    assert "model.layers.2.mlp.shared_experts.down_proj.weight" in state
+    fresh = DeepseekV3.from_hf_config(hf_cfg)
+    hf_io.load_hf_state(fresh, lambda n: state[n], state, hf_cfg)
+    ids, cu = torch.randint(0, 32000, (15,), generator=g), torch.tensor([0, 6, 15])
+    with torch.no_grad():
+        a = tr.model(ids, tr.model.get_position_ids(cu, 15), cu, 9)
+        b = fresh(ids, fresh.get_position_ids(cu, 15), cu, 9)
+    assert torch.allclose(a, b, atol=1e-6)
