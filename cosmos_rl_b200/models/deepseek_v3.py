@@ -299,6 +299,8 @@ class DeepseekV3WeightMapper(Qwen3MoEWeightMapper):
 
 @ModelRegistry.register(DeepseekV3WeightMapper)
 class DeepseekV3(GPT):
+    paged_engine = False    # latent attention has no paged KV path in the generation engine: rollouts recompute
+
     def __init__(self, args: DeepseekV3Args):
         super().__init__(args)
         lo, hi = args.stage_layers()

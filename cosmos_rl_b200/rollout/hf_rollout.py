@@ -63,3 +63,57 @@ class HFRollout(RolloutBase):
             results.append(RolloutResult(prompt=p.prompt, completions=texts, completion_token_ids=toks,
                                          completion_logprobs=logps, cumulative_logprob=[sum(l) for l in logps]))
         return results
+
+
+@RolloutRegistry.register("recompute")
+class RecomputeRollout(HFRollout):
+    """Generation for native families the paged engine has no attention path for (DeepSeek-V3's latent attention):
+    every step re-runs the packed forward over all live sequences and samples with the engine's sampling kernel. No KV
+    cache, so a step costs O(length); it keeps such families usable end to end (rollouts, weight sync, validation)
+    at small scale. The reference serves them through vLLM (cosmos_rl/rollout/vllm_rollout/vllm_rollout.py:262-326)."""
+
+    @torch.no_grad()
+    def rollout_generation(self, payloads, data_packer, data_fetcher=None, is_validation: bool = False, **kw
+                           ) -> List[RolloutResult]:
+        from ..ops import functional as F
+        sp = SamplingParams.from_config(self.config, validation=is_validation)
+        model, dev = self.model, self.device
+        prompts = [list(data_packer.get_rollout_input(p.prompt)) for p in payloads]
+        seqs = [list(pr) for pr in prompts for _ in range(sp.n)]
+        plen = [len(s) for s in seqs]
+        logps: List[List[float]] = [[] for _ in seqs]
+        live = list(range(len(seqs)))
+        gen = torch.Generator(device="cpu").manual_seed(int(sp.seed or 0)) if dev.type != "cuda" else None
+        w = model.lm_head_weight
+        for step in range(sp.max_tokens):
+            if not live:
+                break
+            lens = [len(seqs[i]) for i in live]
+            ids = torch.tensor([t for i in live for t in seqs[i]], dtype=torch.long, device=dev)
+            cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0).tolist()), dtype=torch.int32, device=dev)
+            h = model(ids, model.get_position_ids(cu, int(ids.numel())), cu, max(lens))
+            last = h[(cu[1:] - 1).long()]
+            logits = torch.nn.functional.linear(last, w).float().contiguous()
+            B = len(live)
+            t = torch.full((B,), float(sp.temperature), dtype=torch.float32, device=dev)
+            tp = torch.full((B,), float(sp.top_p), dtype=torch.float32, device=dev)
+            tk = torch.full((B,), int(sp.top_k), dtype=torch.int32, device=dev)
+            toks, lps = F.sample(logits, t, tp, tk, seed=int(sp.seed or 0), offset=step, generator=gen)
+            nxt = []
+            for j, i in enumerate(live):
+                tok = int(toks[j])
+                seqs[i].append(tok)
+                logps[i].append(float(lps[j]))
+                if tok not in sp.stop_token_ids and len(seqs[i]) < self.config.policy.model_max_length:
+                    nxt.append(i)
+            live = nxt
+        results = []
+        for pi, p in enumerate(payloads):
+            rng = range(pi * sp.n, (pi + 1) * sp.n)
+            toks = [seqs[i][plen[i]:] for i in rng]
+            texts = toks if self.tokenizer is None or self.config.train.train_policy.rollout_as_token_ids else \
+                [self.tokenizer.decode(t, skip_special_tokens=True) for t in toks]
+            lp = [logps[i] for i in rng]
+            results.append(RolloutResult(prompt=p.prompt, completions=texts, completion_token_ids=toks,
+                                         completion_logprobs=lp, cumulative_logprob=[sum(l) for l in lp]))
+        return results

@@ -52,8 +52,11 @@ class DisaggregatedRolloutControlWorker(CommMixin):
             from ..models import hf_io
             from ..models.base import ModelRegistry
             mtype = hf_io.load_hf_config(config.policy.model_name_or_path, config.custom.get("model_config")).get("model_type")
-            if ModelRegistry.get(mtype).__name__ == "HFModel":
+            cls = ModelRegistry.get(mtype)
+            if cls.__name__ == "HFModel":
                 backend = "hf"
+            elif not getattr(cls, "paged_engine", True):
+                backend = "recompute"      # native family without a paged-attention path in the engine
         self.rollout = RolloutRegistry.get(backend)(config, parallel_dims, self.device, tokenizer=tokenizer)
         self.rollout.init_engine(load_format="dummy", seed=(config.rollout.seed or 0) + hash(self.replica_name) % 9973)
         mt = getattr(self.rollout.model.args, "model_type", "hfmodel")

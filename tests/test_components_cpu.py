@@ -281,3 +281,38 @@ def test_reference_import_paths_resolve_to_this_package():
     assert main is we.main and BaseDataPacker is pk.BaseDataPacker and RefPathConfig is Config
     with pytest.raises(ImportError):
         importlib.import_module("cosmos_rl.no_such_module")
+
+
+def test_recompute_rollout_backend_for_deepseek_v3(tmp_path):
+    """Families without a paged-engine path generate by re-running the packed forward; greedy decoding must follow
+    the model's own argmax and the reported log-probs must be those of the chosen tokens."""
+    from cosmos_rl_b200.data.packer import BaseDataPacker
+    from cosmos_rl_b200.dispatcher.data.schema import RLPayload
+    from cosmos_rl_b200.models.base import ModelRegistry
+    from cosmos_rl_b200.parallel.dims import ParallelDims
+    from cosmos_rl_b200.rollout import hf_rollout  # noqa: F401  (registers the backend)
+    from cosmos_rl_b200.rollout.base import RolloutRegistry
+    cfg = Config.from_dict({
+        "policy": {"model_name_or_path": "tiny-deepseek-v3", "model_max_length": 64},
+        "rollout": {"n_generation": 2, "max_response_length": 5, "seed": 3,
+                    "sampling_config": {"temperature": 0.0, "top_p": 1.0, "top_k": -1}},
+        "train": {"output_dir": str(tmp_path), "train_policy": {"type": "grpo", "rollout_as_token_ids": True}}})
+    assert not ModelRegistry.get("deepseek_v3").paged_engine
+    ro = RolloutRegistry.get("recompute")(cfg, ParallelDims(world_size=1, device=torch.device("cpu")), torch.device("cpu"))
+    ro.init_engine()
+    packer = BaseDataPacker.get_default("deepseek_v3")()
+    packer.setup(cfg, None)
+    res = ro.rollout_generation([RLPayload(prompt=[5, 6, 7], prompt_idx=0), RLPayload(prompt=[9, 10], prompt_idx=1)], packer)
+    assert len(res) == 2 and all(len(r.completion_token_ids) == 2 for r in res)
+    m = ro.model
+    for r, prompt in zip(res, ([5, 6, 7], [9, 10])):
+        toks = r.completion_token_ids[0]
+        assert toks == r.completion_token_ids[1] and len(toks) == 5          # greedy: both samples agree
+        seq = list(prompt)
+        for t, lp in zip(toks, r.completion_logprobs[0]):
+            ids = torch.tensor(seq)
+            with torch.no_grad():
+                h = m(ids, torch.arange(len(seq)), torch.tensor([0, len(seq)]), len(seq))
+            ls = torch.log_softmax((h[-1] @ m.lm_head_weight.detach().t()).float(), -1)
+            assert int(ls.argmax()) == t and abs(float(ls[t]) - lp) < 1e-4
+            seq.append(t)
