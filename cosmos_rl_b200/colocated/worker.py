@@ -26,7 +26,8 @@ from ..parallel.dims import ParallelDims
 from ..policy.trainer import grpo_trainer  # noqa: F401
 from ..policy.trainer.base import TrainerRegistry
 from ..reward.dispatcher import LocalRewardCalculator
-from ..rollout.b200_rollout import B200Rollout
+from ..rollout import b200_rollout, hf_rollout  # noqa: F401  (register the built-in backends)
+from ..rollout.base import RolloutRegistry
 from ..utils.logging import logger
 
 
@@ -43,9 +44,16 @@ class ColocatedRLControlWorker:
         tp = config.train.train_policy
         self.trainer = TrainerRegistry.get_trainer_cls(tp.trainer_type)(config, self.dims, device=self.device,
                                                                         data_packer=data_packer, tokenizer=tokenizer)
-        self.rollout = B200Rollout(config, self.dims, self.device, tokenizer=tokenizer)
+        # custom workloads register their own trainer type and rollout backend (non-LLM policies, environments)
+        backend = config.rollout.backend
+        model_cls = type(self.trainer.model)
+        if backend == "b200" and model_cls.__name__ == "HFModel":
+            backend = "hf"
+        elif backend == "b200" and not getattr(model_cls, "paged_engine", True):
+            backend = "recompute"
+        self.rollout = RolloutRegistry.get(backend)(config, self.dims, self.device, tokenizer=tokenizer)
         self.rollout.init_engine(shared_model=self.trainer.model)
-        mt = getattr(self.trainer.model.args, "model_type", "hfmodel")
+        mt = getattr(getattr(self.trainer.model, "args", None), "model_type", "hfmodel")
         self.packer = data_packer or BaseDataPacker.get_default(mt)()
         self.packer.setup(config, tokenizer)
         self.fetcher = WorkerDataFetcher(config, CosmosDataset(dataset, config))
@@ -83,8 +91,11 @@ class ColocatedRLControlWorker:
         results = self.rollout.rollout_generation(payloads, self.packer)
         for p, r in zip(payloads, results):
             p.completions = r.completions
-            p.completion_token_ids = [[[t] for t in toks] for toks in r.completion_token_ids]
-            p.completion_logprobs = [[[l] for l in lps] for lps in r.completion_logprobs]
+            if r.completion_token_ids is not None:
+                p.completion_token_ids = [[[t] for t in toks] for toks in r.completion_token_ids]
+                p.completion_logprobs = [[[l] for l in lps] for lps in r.completion_logprobs]
+            if r.extra_info is not None:
+                p.extra_info = r.extra_info
             p.weight_version = self.weight_version
             self.rewards.compute(p)
         self.api.post_rollout_completion(self.rollout_name, payloads, is_end=is_end)
@@ -124,7 +135,8 @@ class ColocatedRLControlWorker:
             # prompts are exhausted: keep serving policy commands until the controller has none left
             if not self.controller.broker.read(command_stream(self.policy_name), self._cmd_pos[self.policy_name], 1, 0):
                 break
-        self.trainer.ckpt_manager.finalize()
+        if getattr(self.trainer, "ckpt_manager", None) is not None:
+            self.trainer.ckpt_manager.finalize()
         self.controller.unregister(self.policy_name)
         self.controller.unregister(self.rollout_name)
         return self.reports

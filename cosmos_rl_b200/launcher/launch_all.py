@@ -159,6 +159,22 @@ def main(argv=None) -> int:
         procs.append((name, p))
         return p
 
+    if config.mode == "colocated" and config.train.train_policy.type != "sft":
+        # policy, rollout and the controller logic share one process (and one set of weights): no controller
+        # process, no rollout replicas (cosmos_rl/colocated/rl_worker.py:41-229)
+        env = dict(env_base, COSMOS_ROLE="Colocated", COSMOS_CONFIG=tmp_cfg.name)
+        if args.cpu or not n_gpus:
+            env["CUDA_VISIBLE_DEVICES"] = ""
+        target = script if script else ["-m", "cosmos_rl_b200.launcher.worker_entry"]
+        p = spawn("colocated_0", [sys.executable] + target, env)
+        try:
+            rc = p.wait()
+        except KeyboardInterrupt:
+            p.terminate()
+            rc = p.wait()
+        os.unlink(tmp_cfg.name)
+        return rc
+
     controller = None
     if args.url:
         host = args.url

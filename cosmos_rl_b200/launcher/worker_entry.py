@@ -102,6 +102,21 @@ def reference_entry(**kw):
         worker.handle_shutdown()
 
 
+def colocated_entry(dataset=None, val_dataset=None, data_packer=None, reward_fns=None, custom_logger_fns=None, **kw):
+    """Single-process job: controller logic, trainer and rollout backend in this process."""
+    import torch
+    from ..colocated.worker import ColocatedRLControlWorker
+    from ..config import Config, load_toml
+    config = Config.from_dict(load_toml(os.environ["COSMOS_CONFIG"]))
+    device = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+    worker = ColocatedRLControlWorker(config, dataset, val_dataset=val_dataset, reward_fns=reward_fns,
+                                      data_packer=data_packer, device=device, custom_logger_fns=custom_logger_fns,
+                                      tokenizer=_tokenizer(config))
+    reports = worker.run()
+    logger.info("[Colocated] finished after %d training steps", len(reports))
+    return reports
+
+
 def controller_entry(dataset=None, val_dataset=None, custom_logger_fns=None, sampler=None, args=None, **kw):
     from ..dispatcher.run_web_panel import main as controller_main
     controller_main(args, dataset=dataset, val_dataset=val_dataset, custom_logger_fns=custom_logger_fns,
@@ -124,6 +139,9 @@ def main(dataset=None, val_dataset=None, data_packer=None, val_data_packer=None,
                              filter_reward_fns=filter_reward_fns, val_reward_fns=val_reward_fns)
     if role == "reference":
         return reference_entry()
+    if role == "colocated":
+        return colocated_entry(dataset=dataset, val_dataset=val_dataset, data_packer=data_packer,
+                               reward_fns=reward_fns, custom_logger_fns=custom_logger_fns)
     raise ValueError(f"unknown COSMOS_ROLE {role!r}")
 
 
