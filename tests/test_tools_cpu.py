@@ -1,0 +1,81 @@
+"""Graders, the sandboxed code verifier and the dataset entry modules."""
+import json
+
+from cosmos_rl_b200.config import Config
+from cosmos_rl_b200.tools.dataset import code_grpo, countdown_distill, dummy_sft, gsm8k_grpo, math_dapo, math_grpo
+from cosmos_rl_b200.tools.dataset.common import load_rows
+from cosmos_rl_b200.tools.eval_utils import extract_boxed, math_equal, run_code_tests
+
+
+def test_math_grader():
+    assert extract_boxed(r"so \boxed{\frac{1}{2}} and finally \boxed{ \dfrac{3}{4} }").strip() == r"\dfrac{3}{4}"
+    assert extract_boxed("no box") is None
+    cases = [("0.5", r"\frac{1}{2}", True), ("1,234", "1234", True), (r"\$5.00", "5", True), ("50%", "0.5", True),
+             ("(1,2)", "(1, 2)", True), ("[1,2)", "(1,2)", False), (r"2\sqrt{2}", r"\sqrt{8}", True), ("x=3", "3", True),
+             ("12 cm", "12", True), ("7", "8", False), (r"\frac{\pi}{2}", "pi/2", True), (r"90^\circ", "90", True),
+             (r"\text{yes}", "Yes", True), ("1/3", "0.3333", True), ("2x+1", "1+2x", True), ("2x+1", "2x-1", False)]
+    for a, b, want in cases:
+        assert math_equal(a, b) == want, (a, b)
+
+
+def test_code_verifier_sandbox():
+    r = run_code_tests("def f(x):\n    return x*x\n", [{"assert": "assert f(3) == 9"}, {"assert": "assert f(2) == 5"}])
+    assert r["status"] == ["pass", "error"] and r["pass_rate"] == 0.5
+    assert run_code_tests("n=int(input())\nprint(n*2)\n", [{"input": "4\n", "output": "8"}])["all_passed"]
+    assert run_code_tests("print(3)\n", [{"input": "", "output": "4"}])["status"] == ["wrong"]
+    assert run_code_tests("while True: pass\n", [{"input": "", "output": ""}], timeout_s=1.0)["status"] == ["timeout"]
+    resp = "Here you go:\n```python\nprint(int(input()) + 1)\n```"
+    assert code_grpo.code_reward(resp, json.dumps([{"input": "1", "output": "2"}, {"input": "5", "output": "7"}])) == 0.5
+
+
+def test_dataset_modules(tmp_path):
+    rows = [{"question": "2+2?", "answer": "It is four.\n#### 4"}, {"question": "3*3?", "answer": "#### 9"}]
+    f = tmp_path / "train.jsonl"
+    f.write_text("\n".join(json.dumps(r) for r in rows))
+    assert load_rows(str(tmp_path), None, "train") == rows
+    cfg = Config.from_dict({"train": {"train_policy": {"type": "grpo", "dataset": {"name": str(tmp_path), "split": "train"}}}})
+    ds = gsm8k_grpo.gsm8k_dataset()
+    ds.setup(cfg, None)
+    assert len(ds) == 2 and ds[0][-1]["content"] == "2+2?" and ds.get_reference_answer(0) == "4"
+    good = "<think>2 and 2</think><answer>4</answer>"
+    assert abs(gsm8k_grpo.reward_fn(good, "4") - 1.1) < 1e-9 and gsm8k_grpo.reward_fn("5", "4") == 0.0
+    m = math_grpo.math_dataset([{"problem": "p", "solution": r"thus \boxed{\frac{1}{2}}"}])
+    assert m.get_reference_answer(0) == r"\frac{1}{2}" and math_grpo.direct_math_reward(r"\boxed{0.5}", r"\frac{1}{2}") == 1.0
+    d = math_dapo.dapo_dataset([{"prompt": [{"role": "user", "content": "q"}], "reward_model": {"ground_truth": "34"}}])
+    assert d[0][0]["role"] == "user" and math_dapo.dapo_reward("work...\nAnswer: 34", "34") == 1.0
+    assert math_dapo.dapo_reward("Answer: 35", "34") == -1.0
+    c = countdown_distill.countdown_dataset(n_synth=8)
+    ref = c.get_reference_answer(0)
+    assert len(c) == 8 and set(ref) == {"nums", "target"}
+    assert countdown_distill.countdown_reward("<answer>(1+2)*3 = 9</answer>", {"nums": [3, 2, 1], "target": 9}) == 1.0
+    assert countdown_distill.countdown_reward("<answer>1+2+3</answer>", {"nums": [3, 2, 1], "target": 9}) == 0.1
+    assert countdown_distill.countdown_reward("<answer>__import__('os')</answer>", {"nums": [1], "target": 1}) == 0.0
+    s = dummy_sft.DummySFTDataset(4)
+    s.setup(cfg, None)
+    assert "input_ids" in s[0]
+
+
+def test_slurm_plan_script_and_node_commands(tmp_path, capsys):
+    from cosmos_rl_b200.config import dump_toml
+    from cosmos_rl_b200.tools.slurm import dispatch_job, node_launch
+    cfg = tmp_path / "job.toml"
+    cfg.write_text(dump_toml({"policy": {"parallelism": {"dp_shard_size": 8, "tp_size": 2}},
+                              "rollout": {"parallelism": {"tp_size": 2}},
+                              "train": {"train_policy": {"type": "grpo"}}}))
+    conf = Config.from_dict({"policy": {"parallelism": {"dp_shard_size": 8, "tp_size": 2}},
+                             "rollout": {"parallelism": {"tp_size": 2}}, "train": {"train_policy": {"type": "grpo"}}})
+    plan = dispatch_job.plan_nodes(conf, n_policy=2, n_rollout=6, ngpu_per_node=8)
+    assert plan["policy"] == 4 and plan["rollout"] == 2            # 16-GPU policy replicas; 4 rollout replicas per node
+    rc = dispatch_job.main(["--job-name", "j", "--config-path", str(cfg), "--output-root-path", str(tmp_path),
+                            "--n-policy-replicas", "2", "--n-rollout-replicas", "6", "--dry-run"])
+    out = capsys.readouterr().out
+    assert rc == 0 and "#SBATCH --nodes=6" in out and "--signal=B:USR1@300" in out and "scontrol requeue" in out
+    assert node_launch.expand_nodelist("n[01-03,07],gpu5") == ["n01", "n02", "n03", "n07", "gpu5"]
+    a = [node_launch.node_assignment(i, 4, 2, 2, 6) for i in range(6)]
+    assert [x["policy"] for x in a] == [1, 0, 1, 0, 0, 0] and [x["rollout"] for x in a] == [0, 0, 0, 0, 3, 3]
+    ns = type("A", (), dict(policy_nodes=4, rollout_nodes=2, n_policy_replicas=2, n_rollout_replicas=6,
+                            config=str(cfg), log_dir=None, script=None))
+    env = {"SLURM_JOB_NODELIST": "n[01-06]", "SLURM_NODEID": "4"}
+    cmd = node_launch.build_command(ns, env)
+    assert "--no-controller" in cmd and cmd[cmd.index("--url") + 1] == "n01:8000" and cmd[cmd.index("--rollout") + 1] == "3"
+    assert node_launch.build_command(ns, {"SLURM_JOB_NODELIST": "n[01-06]", "SLURM_NODEID": "1"}) is None
