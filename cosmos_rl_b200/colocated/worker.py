@@ -23,7 +23,7 @@ from ..dispatcher.data.schema import RLPayload, Rollout
 from ..dispatcher.protocol import RegisterRequest, Role
 from ..data.packer import BaseDataPacker
 from ..parallel.dims import ParallelDims
-from ..policy.trainer import grpo_trainer  # noqa: F401
+from ..policy.trainer import diffusion_trainer, grpo_trainer  # noqa: F401
 from ..policy.trainer.base import TrainerRegistry
 from ..reward.dispatcher import LocalRewardCalculator
 from ..rollout import b200_rollout, hf_rollout  # noqa: F401  (register the built-in backends)
@@ -53,6 +53,8 @@ class ColocatedRLControlWorker:
             backend = "recompute"
         self.rollout = RolloutRegistry.get(backend)(config, self.dims, self.device, tokenizer=tokenizer)
         self.rollout.init_engine(shared_model=self.trainer.model)
+        if hasattr(self.trainer, "attach_rollout"):
+            self.trainer.attach_rollout(self.rollout)
         mt = getattr(getattr(self.trainer.model, "args", None), "model_type", "hfmodel")
         self.packer = data_packer or BaseDataPacker.get_default(mt)()
         self.packer.setup(config, tokenizer)

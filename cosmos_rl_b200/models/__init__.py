@@ -3,6 +3,7 @@ from .base import BaseModel, ModelRegistry, WeightMapper  # noqa: F401
 from . import gpt  # noqa: F401
 from . import qwen3_moe  # noqa: F401
 from . import deepseek_v3  # noqa: F401
+from . import dit  # noqa: F401
 from . import hf_model  # noqa: F401  (fallback for every other transformers causal LM)
 
 
@@ -13,6 +14,7 @@ def named_architectures():
         from . import qwen3_moe
         out.update(qwen3_moe.ARCHS)
         out.update(deepseek_v3.ARCHS)
+        out.update(dit.ARCHS)
     except ImportError:
         pass
     return out

@@ -40,26 +40,29 @@ def flash_fwd(q, k, v, cu_q, cu_k, max_q: int, scale: float, causal: bool = True
 
 class _FlashAttn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, scale):
-        out, lse = flash_fwd(q, k, v, cu_q, cu_k, max_q, scale, True)
+    def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, scale, causal=True):
+        out, lse = flash_fwd(q, k, v, cu_q, cu_k, max_q, scale, causal)
         ctx.save_for_backward(q, k, v, out, lse, cu_q, cu_k)
-        ctx.max_q, ctx.max_k, ctx.scale = max_q, max_k, scale
+        ctx.max_q, ctx.max_k, ctx.scale, ctx.causal = max_q, max_k, scale, causal
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
         return flash_bwd(dout.contiguous(), q, k, v, out, lse, cu_q, ctx.max_q, ctx.scale, cu_k=cu_k,
-                         max_k=ctx.max_k) + (None, None, None, None, None)
+                         max_k=ctx.max_k, causal=ctx.causal) + (None, None, None, None, None, None)
 
 
-def flash_attention(q, k, v, cu_q, cu_k, max_q: int, scale: Optional[float] = None, max_k: Optional[int] = None):
-    """Differentiable causal attention with the queries of a sequence aligned to the end of its keys."""
+def flash_attention(q, k, v, cu_q, cu_k, max_q: int, scale: Optional[float] = None, max_k: Optional[int] = None,
+                    causal: bool = True):
+    """Differentiable attention over packed sequences. Causal: the queries of a sequence are aligned to the end of
+    its keys. Non-causal (``causal=False``): every query sees every key of its sequence (bidirectional self-attention
+    of diffusion transformers, cross-attention onto a text sequence of another length)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     i32 = lambda t: t if t.dtype == torch.int32 else t.to(torch.int32)
     if max_k is None:
         max_k = int((cu_k[1:] - cu_k[:-1]).max().item()) if cu_k is not cu_q else max_q
-    return _FlashAttn.apply(q, k, v, i32(cu_q), i32(cu_k), int(max_q), int(max_k), scale)
+    return _FlashAttn.apply(q, k, v, i32(cu_q), i32(cu_k), int(max_q), int(max_k), scale, bool(causal))
 
 
 def flash_bwd(dout, q, k, v, out, lse, cu, max_seqlen: int, scale: float, cu_k=None, max_k=None,
@@ -89,6 +92,17 @@ def flash_bwd_library(dout, q, k, v, out, lse, cu, max_seqlen: int, scale: float
     _flash_attn_varlen_backward(dout, q, k, v, out, lse, dq, dk, dv, cu, cu, max_seqlen, max_seqlen, 0.0, scale,
                                 True, -1, -1, 0.0, None, False, None)
     return dq, dk, dv
+
+
+def full_attention_cuda(q, k, v, cu_q, cu_k, max_q: int, max_k: int, scale: Optional[float] = None):
+    """Non-causal packed attention (own kernel for head_dim 128, the flash-attn library otherwise)."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    i32 = lambda t: t if t.dtype == torch.int32 else t.to(torch.int32)
+    if native_flash_supported(q, k, v):
+        return _FlashAttn.apply(q, k, v, i32(cu_q), i32(cu_k), int(max_q), int(max_k), scale, False)
+    from flash_attn import flash_attn_varlen_func
+    return flash_attn_varlen_func(q, k, v, i32(cu_q), i32(cu_k), max_q, max_k, dropout_p=0.0, softmax_scale=scale,
+                                  causal=False)
 
 
 def varlen_attention_cuda(q, k, v, cu_seqlens, max_seqlen: int, scale: Optional[float] = None):

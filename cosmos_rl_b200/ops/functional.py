@@ -372,6 +372,15 @@ def varlen_attention(q, k, v, cu_seqlens, max_seqlen: int, scale: Optional[float
     return reference.varlen_attention(q, k, v, cu_seqlens, scale)
 
 
+def full_attention(q, k, v, cu_q, cu_k, max_q: int, max_k: int, scale: Optional[float] = None):
+    """Bidirectional attention over packed sequences: ``q [Tq, hq, d]``, ``k/v [Tk, hkv, d]``; sequence i owns queries
+    ``cu_q[i]:cu_q[i+1]`` and keys ``cu_k[i]:cu_k[i+1]`` (self-attention when ``cu_q is cu_k``, else cross-attention)."""
+    if q.is_cuda:
+        from . import attention
+        return attention.full_attention_cuda(q, k, v, cu_q, cu_k, max_q, max_k, scale)
+    return reference.varlen_attention(q, k, v, cu_q, scale, causal=False, cu_k=cu_k)
+
+
 def tc_decode_supported(d: int, page_size: int, hq: int, hkv: int) -> bool:
     """The tcgen05 decode kernel needs head_dim 128, 128-token pages and a GQA group of at most 8."""
     return d == 128 and page_size == 128 and hq % hkv == 0 and hq // hkv <= 8

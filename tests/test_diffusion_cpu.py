@@ -1,0 +1,137 @@
+"""Diffusion transformer, flow-matching SFT, and the two diffusion RL algorithms (DiffusionNFT, FlowGRPO) through the
+colocated worker on CPU with a tiny DiT."""
+import math
+
+import pytest
+import torch
+
+from cosmos_rl_b200.config import Config
+from cosmos_rl_b200.models.dit import ARCHS, DiT
+from cosmos_rl_b200.parallel.dims import ParallelDims
+from cosmos_rl_b200.policy import diffusion as D
+from cosmos_rl_b200.rollout.diffusion_rollout import LatentStore
+
+
+def _dit(seed=0, randomize_zero_init=True):
+    torch.manual_seed(seed)
+    m = DiT(ARCHS["tiny-dit"])
+    m.init_weights(seed)
+    if randomize_zero_init:                      # adaLN-zero starts as the zero map: make the blocks matter
+        with torch.no_grad():
+            for n, p in m.named_parameters():
+                if "modulation" in n or n.startswith("patch_out"):
+                    p.normal_(0, 0.05)
+    return m.eval()
+
+
+def test_dit_shapes_zero_init_and_text_padding():
+    m0 = _dit(randomize_zero_init=False)
+    z = torch.randn(2, 4, 3, 8, 8)
+    text = torch.randn(2, 5, 64)
+    assert m0(z, torch.tensor([0.3, 0.9]), text).abs().max() == 0          # adaLN-zero
+    m = _dit()
+    v = m(z, torch.tensor([0.3, 0.9]), text)
+    assert v.shape == z.shape and v.abs().max() > 0
+    img = m(z[:, :, 0], torch.tensor([0.3, 0.9]), text)
+    assert img.shape == (2, 4, 8, 8)
+    # padded text positions are invisible; samples do not see each other
+    pad = torch.cat([text, torch.randn(2, 3, 64)], 1)
+    mask = torch.tensor([[1] * 5 + [0] * 3] * 2, dtype=torch.bool)
+    assert torch.allclose(m(z, torch.tensor([0.3, 0.9]), pad, mask), v, atol=1e-5)
+    assert torch.allclose(m(z[:1], torch.tensor([0.3]), text[:1]), v[:1], atol=1e-5)
+    tok, grid = m.patchify(z)
+    assert grid == (3, 4, 4) and torch.equal(m.unpatchify(tok, grid), z)
+
+
+def test_flow_math():
+    t = D.sample_timesteps(4096, "logit_normal", shift=3.0)
+    assert 0 < t.min() and t.max() < 1 and t.mean() > 0.6                       # shift moves mass to the noisy end
+    x0, eps = torch.randn(3, 4, 8, 8), torch.randn(3, 4, 8, 8)
+    # a model that knows the true velocity transports noise exactly onto the data, with any step count
+    oracle = lambda x, tt, text, mask: eps - x0
+    assert torch.allclose(D.euler_sample(oracle, eps, None, steps=3), x0, atol=1e-5)
+    # SDE transition: the recorded log-prob is the Gaussian density of the step actually taken
+    out = D.sde_sample(oracle, eps, None, steps=4, noise_level=0.5)
+    ts = out["timesteps"].tolist()
+    assert out["states"].shape == (3, 3, 4, 8, 8) and out["logprobs"].shape == (3, 3)
+    mean = D.sde_mean(out["states"][:, 1], eps - x0, ts[1], ts[2], 0.5)
+    _, std = D.sde_coeffs(ts[1], ts[2], 0.5)
+    assert torch.allclose(D.sde_logprob(out["next_states"][:, 1], mean, std), out["logprobs"][:, 1], atol=1e-5)
+    # NFT: with v == v_old the two branches coincide, the gradient pushes good samples' x0-prediction to x0
+    v = torch.zeros_like(x0, requires_grad=True)
+    tt = torch.tensor([0.5, 0.5, 0.5])
+    xt = D.add_noise(x0, tt, eps)
+    loss, m = D.nft_loss(v, torch.zeros_like(x0), torch.zeros_like(x0), xt, x0, tt, torch.tensor([5.0, -5.0, 0.0]),
+                         beta=1.0, adv_clip=5.0, kl_beta=0.1)
+    loss.backward()
+    err = xt - x0                                                               # x0-prediction error at v = 0
+    cos = lambda a, b: torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0)
+    assert cos(-v.grad[0], err[0]) > 0.99 and cos(-v.grad[1], -err[1]) > 0.99   # good: towards x0; bad: away
+    assert v.grad[2].abs().max() < 1e-6 and m["kl_loss"] == 0                   # r = 1/2: branches cancel
+
+
+def _config(tmp_path, trainer_type, **diff):
+    d = {"latent_shape": [4, 8, 8], "sample_steps": 4, "train_timesteps": 2, "nft_beta": 1.0, "old_decay": "copy"}
+    d.update(diff)
+    return Config.from_dict({
+        "mode": "colocated", "custom": {"diffusion": d},
+        "policy": {"model_name_or_path": "tiny-dit", "model_gradient_checkpointing": False},
+        "rollout": {"backend": "diffusion", "batch_size": 4, "n_generation": 4, "seed": 0},
+        "train": {"seed": 0, "optm_lr": 2e-3, "optm_warmup_steps": 0, "output_dir": str(tmp_path),
+                  "train_batch_per_replica": 16, "epoch": 1, "optm_weight_decay": 0.0,
+                  "train_policy": {"type": "grpo", "trainer_type": trainer_type, "mini_batch": 8, "kl_beta": 1e-3,
+                                   "advantage_high": 2.0, "advantage_low": -2.0},
+                  "ckpt": {"enable_checkpoint": False}}})
+
+
+def test_flow_matching_sft_learns_a_fixed_batch(tmp_path):
+    from cosmos_rl_b200.policy.trainer.diffusion_trainer import DiffusionSFTTrainer
+    c = _config(tmp_path, "diffusion_sft")
+    c.train.train_policy.type = "sft"
+    tr = DiffusionSFTTrainer(c, ParallelDims(world_size=1, device=torch.device("cpu")), device=torch.device("cpu"))
+    tr.model_load_from_hf()
+    g = torch.Generator().manual_seed(0)
+    base = torch.randn(4, 8, 8, generator=g)
+    batch = [{"latents": (base + 0.05 * torch.randn(4, 8, 8, generator=g)).tolist(),
+              "text_embeds": torch.randn(3, 64, generator=g).tolist()} for _ in range(8)]
+    torch.manual_seed(0)
+    losses = [tr.step_training(batch, total_steps=40, train_step=i + 1)["train/loss_avg"] for i in range(40)]
+    assert sum(losses[-5:]) / 5 < 0.8 * sum(losses[:5]) / 5, (losses[:5], losses[-5:])
+
+
+class _Prompts:
+    def __init__(self, n):
+        g = torch.Generator().manual_seed(5)
+        self.rows = [{"text_embeds": torch.randn(3, 64, generator=g).tolist(), "seed": i} for i in range(n)]
+
+    def __len__(self):
+        return len(self.rows)
+
+    def __getitem__(self, i):
+        return self.rows[i]
+
+    def get_reference_answer(self, i):
+        return ""
+
+
+def brightness_reward(completion, reference=None, **kw) -> float:
+    return float(LatentStore.get(completion)["x0"].float().mean())
+
+
+@pytest.mark.parametrize("trainer_type,extra", [("diffusion_nft", {}), ("flow_grpo", {"sampler": "sde", "noise_level": 0.7})])
+def test_diffusion_rl_raises_the_reward(tmp_path, trainer_type, extra):
+    from cosmos_rl_b200.colocated.worker import ColocatedRLControlWorker
+    torch.manual_seed(0)
+    c = _config(tmp_path, trainer_type, **extra)
+    w = ColocatedRLControlWorker(c, _Prompts(96), reward_fns=[brightness_reward], device=torch.device("cpu"))
+    reports = w.run(max_iterations=400)
+    assert len(reports) == 24 and all(math.isfinite(r["train/loss_avg"]) for r in reports)
+    assert not LatentStore._items                                    # every latent was released after its step
+    # the trained model generates brighter latents than the initial one from the same noise
+    g = torch.Generator().manual_seed(1)
+    noise, text = torch.randn(16, 4, 8, 8, generator=g), torch.randn(16, 3, 64, generator=g)
+    after = D.euler_sample(w.trainer.model.eval(), noise, text, steps=4).mean().item()
+    fresh = DiT(ARCHS["tiny-dit"])
+    fresh.init_weights(0)
+    before = D.euler_sample(fresh.eval(), noise, text, steps=4).mean().item()
+    assert after > before + 0.02, (before, after)

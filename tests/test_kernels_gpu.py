@@ -458,6 +458,34 @@ def test_flash_attention_autograd_matches_reference(lens, hq, hkv):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("lq,lk,hq,hkv", [([200, 56], None, 4, 2), ([300, 130], [77, 200], 4, 4), ([64], [333], 2, 1)])
+def test_bidirectional_attention_self_and_cross(lq, lk, hq, hkv):
+    """Non-causal mode of the attention kernels: every query sees all keys of its sequence, the key sequence may be
+    shorter or longer than the query sequence (cross-attention)."""
+    torch.manual_seed(14)
+    d = 128
+    cum = lambda l: torch.tensor([0] + list(torch.tensor(l).cumsum(0)), dtype=torch.int32, device="cuda")
+    cq = cum(lq)
+    ck = cq if lk is None else cum(lk)
+    lk = lq if lk is None else lk
+    q = torch.randn(sum(lq), hq, d, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    k = torch.randn(sum(lk), hkv, d, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    v = torch.randn(sum(lk), hkv, d, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    go = torch.randn(sum(lq), hq, d, device="cuda").to(torch.bfloat16)
+    out = F.full_attention(q, k, v, cq, ck, max(lq), max(lk))
+    out.backward(go)
+    torch.cuda.synchronize()
+    assert native.read_status(q.device) == 0
+    rq, rk, rv = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = R.varlen_attention(rq, rk, rv, cq, 1.0 / math.sqrt(d), causal=False, cu_k=ck)
+    ref.backward(go.float())
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), (out.float() - ref).abs().max()
+    for got, want in ((q.grad, rq.grad), (k.grad, rk.grad), (v.grad, rv.grad)):
+        err = (got.float() - want).abs().max().item()
+        assert err <= 3e-2 * want.abs().max().item() + 2e-2, err
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 520, 1040), (1024, 3584, 3584), (17, 256, 4096)])
 def test_gemm_fp8_block_scaled(M, N, K):
     torch.manual_seed(5)
@@ -524,3 +552,32 @@ def test_paged_decode_shared_prefix_groups(hq, hkv, n):
                           max_shared=max_shared)
     assert native.read_status(q.device) == 0
     assert (out2[1:].float().cpu() - ref[1:].float()).abs().max().item() < 3e-2
+
+
+@pytest.mark.gpu
+def test_dit_bf16_on_gpu_matches_fp32_reference():
+    """Diffusion transformer with head_dim 128: self- and cross-attention run the non-causal tcgen05 kernels."""
+    from cosmos_rl_b200.models.dit import DiT, DiTArgs
+    torch.manual_seed(0)
+    a = DiTArgs(in_channels=4, patch_size=(1, 2, 2), dim=256, n_layers=2, n_heads=2, head_dim=128, ffn_dim=512,
+                text_dim=128, freq_dim=64)
+    ref = DiT(a)
+    ref.init_weights(0)
+    with torch.no_grad():
+        for n, p in ref.named_parameters():
+            if "modulation" in n or n.startswith("patch_out"):
+                p.normal_(0, 0.05)
+    z, t, text = torch.randn(2, 4, 2, 16, 16), torch.tensor([0.2, 0.8]), torch.randn(2, 9, 128)
+    mask = torch.tensor([[1] * 9, [1] * 4 + [0] * 5], dtype=torch.bool)
+    want = ref(z, t, text, mask)
+    want.square().mean().backward()
+    import copy
+    gpu = copy.deepcopy(ref).to("cuda", torch.bfloat16)
+    gpu.zero_grad()
+    got = gpu(z.cuda().to(torch.bfloat16), t.cuda(), text.cuda().to(torch.bfloat16), mask.cuda())
+    got.square().mean().backward()
+    torch.cuda.synchronize()
+    assert native.read_status(torch.device("cuda")) == 0
+    assert (got.float().cpu() - want).abs().max() < 0.05 * want.abs().max() + 0.02
+    g_ref, g_gpu = ref.layers[0].qkv.weight.grad, gpu.layers[0].qkv.weight.grad.float().cpu()
+    assert torch.nn.functional.cosine_similarity(g_ref.flatten(), g_gpu.flatten(), dim=0) > 0.98
