@@ -165,6 +165,12 @@ int b200_flash_bwd(const void* q, const void* k, const void* v, const void* out,
 int b200_quant_fp8_block(const void* src, long long ld_src, void* dst, long long ld_dst, float* scales, int R, int C,
                          int block_rows, cudaStream_t stream);
 
+// bf16 [R, C] <-> microscaling fp4 (E2M1 elements, one E8M0 scale per 32 elements; mxfp4.cu). swizzle = 1 stores the
+// scales in the 128 x 4 tile interleaving block-scaled tensor-core MMA reads.
+int b200_quant_mxfp4(const void* x, long long ldx, void* q, void* sf, int R, int C, int swizzle, cudaStream_t stream);
+int b200_dequant_mxfp4(const void* q, const void* sf, void* out, long long ldo, int R, int C, int swizzle,
+                       cudaStream_t stream);
+
 // ---- peer-memory weight sync -------------------------------------------------------------------------------------
 // One descriptor = copy a [rows, cols] bf16 rectangle from (possibly another GPU's) memory into a local
 // destination, optionally quantising to block-scaled fp8 on the way.

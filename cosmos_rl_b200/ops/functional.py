@@ -525,3 +525,34 @@ def linear_maybe_fp8(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor]
         y = fp8_linear(x.reshape(-1, x.shape[-1]), f8[0], f8[1]).view(*x.shape[:-1], f8[0].shape[0])
         return y if b is None else y + b
     return torch.nn.functional.linear(x, w, b)
+
+
+# --------------------------------------------------------------------------------------------------
+# microscaling fp4 (weights of mxfp4-served experts: cosmos_rl/rollout/vllm_rollout/monkey_patch_for_mxfp4.py)
+# --------------------------------------------------------------------------------------------------
+def mxfp4_scale_bytes(R: int, C: int, swizzle: bool) -> int:
+    return ((R + 127) // 128) * ((C // 32 + 3) // 4) * 512 if swizzle else R * (C // 32)
+
+
+def quant_mxfp4(w: torch.Tensor, swizzle: bool = False):
+    """bf16 ``[R, C]`` -> (packed E2M1 ``[R, C/2]`` uint8, E8M0 scale bytes). ``swizzle`` stores the scales in the
+    128 x 4 tile interleaving of block-scaled tensor-core MMA; otherwise row-major ``[R, C/32]``."""
+    if not w.is_cuda:
+        return reference.quant_mxfp4(w, swizzle)
+    R, C = w.shape
+    assert w.dtype == torch.bfloat16 and w.stride(-1) == 1 and C % 32 == 0
+    q = torch.empty(R, C // 2, dtype=torch.uint8, device=w.device)
+    sf = torch.zeros(mxfp4_scale_bytes(R, C, swizzle), dtype=torch.uint8, device=w.device)
+    native.check(native.lib().b200_quant_mxfp4(native.ptr(w), w.stride(0), native.ptr(q), native.ptr(sf), R, C,
+                                               1 if swizzle else 0, native.stream()), "quant_mxfp4")
+    return q, sf
+
+
+def dequant_mxfp4(q: torch.Tensor, sf: torch.Tensor, swizzle: bool = False) -> torch.Tensor:
+    if not q.is_cuda:
+        return reference.dequant_mxfp4(q, sf, swizzle)
+    R, C = q.shape[0], q.shape[1] * 2
+    out = torch.empty(R, C, dtype=torch.bfloat16, device=q.device)
+    native.check(native.lib().b200_dequant_mxfp4(native.ptr(q), native.ptr(sf), native.ptr(out), out.stride(0), R, C,
+                                                 1 if swizzle else 0, native.stream()), "dequant_mxfp4")
+    return out

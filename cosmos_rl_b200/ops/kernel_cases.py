@@ -166,6 +166,17 @@ def case_quant(iters):
     report(f"quant_fp8_block 128x128 {R}x{C}", t, nbytes=R * C * 3.0)
 
 
+def case_quant_mxfp4(iters):
+    """bf16 -> mxfp4 with the tensor-core scale layout, shape of one gpt-oss style expert stack (512 MB in)."""
+    R, C = 32768, 8192
+    w = bf(R, C)
+    t = timed(lambda: F.quant_mxfp4(w, True), iters)
+    report(f"quant_mxfp4 (swizzled scales) {R}x{C}", t, nbytes=R * C * (2.0 + 0.5 + 1.0 / 32))
+    q, sf = F.quant_mxfp4(w, True)
+    t = timed(lambda: F.dequant_mxfp4(q, sf, True), iters)
+    report(f"dequant_mxfp4 {R}x{C}", t, nbytes=R * C * (2.0 + 0.5 + 1.0 / 32))
+
+
 def case_rmsnorm(iters):
     T, H = 65536, 3584
     x, r, w = bf(T, H), bf(T, H), bf(H)
@@ -245,7 +256,7 @@ def case_flash(iters, B=16, L=4096, library=True):
     assert native.read_status(q.device) == 0
 
 
-CASES = {"reshard_fp8": case_reshard_fp8, "moe": case_moe, "gemm_fp8": case_gemm_fp8, "flash": case_flash, "flash_small": case_flash_small, "gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
+CASES = {"quant_mxfp4": case_quant_mxfp4, "reshard_fp8": case_reshard_fp8, "moe": case_moe, "gemm_fp8": case_gemm_fp8, "flash": case_flash, "flash_small": case_flash_small, "gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
          "reshard": case_reshard, "quant": case_quant, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu,
          "rope": case_rope, "adamw": case_adamw, "sample": case_sample}
 

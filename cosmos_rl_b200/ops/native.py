@@ -105,6 +105,8 @@ _SIGS = {
                           c_void_p, c_int, c_int, c_void_p, c_int, c_void_p],
     "b200_grouped_wgrad": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong,
                            c_void_p, c_int, c_int, c_void_p, c_int, c_void_p],
+    "b200_quant_mxfp4": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "b200_dequant_mxfp4": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p],
     "b200_quant_fp8_block": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
     "b200_reshard_pull": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
 }

@@ -210,3 +210,49 @@ def adamw_step(master, m, v, grad, lr, beta1, beta2, eps, weight_decay, step, gr
     bias2 = 1.0 - beta2 ** step
     denom = v.sqrt() / math.sqrt(bias2) + eps
     master.addcdiv_(m, denom, value=-lr / bias1)
+
+
+# ---------------------------------------------------------------------------------------------- microscaling fp4
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def mxfp4_sf_index(R: int, n_cb: int, swizzle: bool, device=None) -> torch.Tensor:
+    """Byte offset of the scale of (row, 32-element block) for every pair, ``[R, n_cb]`` int64."""
+    r = torch.arange(R, device=device)[:, None]
+    cb = torch.arange(n_cb, device=device)[None, :]
+    if not swizzle:
+        return r * n_cb + cb
+    tiles_c = (n_cb + 3) // 4
+    rr = r % 128
+    return ((r // 128) * tiles_c + cb // 4) * 512 + (rr % 32) * 16 + (rr // 32) * 4 + cb % 4
+
+
+def quant_mxfp4(w: torch.Tensor, swizzle: bool = False):
+    """bf16/fp32 ``[R, C]`` (C % 32 == 0) -> (packed E2M1 ``[R, C/2]`` uint8, E8M0 scales uint8). Scale exponent
+    ``floor(log2(amax)) - 2`` per 32 elements, elements rounded to nearest (ties to the even code), saturating at 6."""
+    R, C = w.shape
+    n_cb = C // 32
+    x = w.float().view(R, n_cb, 32)
+    amax = x.abs().amax(-1)
+    ex = torch.where(amax > 0, torch.floor(torch.log2(amax.clamp_min(1e-45))) - 2, torch.full_like(amax, -127.0))
+    ex = ex.clamp(-127, 127)
+    a = (x.double() * torch.exp2(-ex.double())[..., None]).abs()
+    code = ((a > 0.25).int() + (a >= 0.75).int() + (a > 1.25).int() + (a >= 1.75).int() + (a > 2.5).int()
+            + (a >= 3.5).int() + (a > 5.0).int())
+    code = code | ((x < 0).int() << 3)
+    code = code.view(R, C)
+    q = (code[:, 0::2] | (code[:, 1::2] << 4)).to(torch.uint8)
+    n_sf = ((R + 127) // 128) * ((n_cb + 3) // 4) * 512 if swizzle else R * n_cb
+    sf = torch.zeros(n_sf, dtype=torch.uint8, device=w.device)
+    sf[mxfp4_sf_index(R, n_cb, swizzle, w.device).flatten()] = (ex + 127).to(torch.uint8).flatten()
+    return q, sf
+
+
+def dequant_mxfp4(q: torch.Tensor, sf: torch.Tensor, swizzle: bool = False) -> torch.Tensor:
+    R, C = q.shape[0], q.shape[1] * 2
+    n_cb = C // 32
+    lut = torch.tensor(_E2M1, dtype=torch.float32, device=q.device)
+    code = torch.stack([q & 0xF, q >> 4], dim=-1).view(R, C).long()
+    val = lut[code & 7] * torch.where((code & 8) > 0, -1.0, 1.0)
+    ex = sf[mxfp4_sf_index(R, n_cb, swizzle, q.device)].float() - 127.0
+    return (val.view(R, n_cb, 32) * torch.exp2(ex)[..., None]).view(R, C)

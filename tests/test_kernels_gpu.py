@@ -581,3 +581,23 @@ def test_dit_bf16_on_gpu_matches_fp32_reference():
     assert (got.float().cpu() - want).abs().max() < 0.05 * want.abs().max() + 0.02
     g_ref, g_gpu = ref.layers[0].qkv.weight.grad, gpu.layers[0].qkv.weight.grad.float().cpu()
     assert torch.nn.functional.cosine_similarity(g_ref.flatten(), g_gpu.flatten(), dim=0) > 0.98
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("R,C,swizzle", [(128, 128, False), (300, 2880, True), (1, 32, True), (257, 96, False)])
+def test_mxfp4_quant_matches_reference_bit_for_bit(R, C, swizzle):
+    torch.manual_seed(9)
+    w = (torch.randn(R, C, device="cuda") * torch.logspace(-3, 2, R, device="cuda")[:, None]).to(torch.bfloat16)
+    w[0, :32] = 0                                          # an all-zero block takes the smallest scale
+    if R > 2:
+        w[2, :8] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -5.0], device="cuda") * 4   # ties, amax 20 -> scale 4
+        w[2, 8:32] = 0
+    q, sf = F.quant_mxfp4(w, swizzle)
+    rq, rsf = R.quant_mxfp4(w, swizzle)
+    assert torch.equal(q, rq) and torch.equal(sf, rsf)
+    back = F.dequant_mxfp4(q, sf, swizzle)
+    assert torch.equal(back.float(), R.dequant_mxfp4(rq, rsf, swizzle).to(torch.bfloat16).float())
+    # every element is within half a quantisation step of its block: the largest gap of the E2M1 grid is 2 scales
+    blk = w.float().view(R, C // 32, 32)
+    scale = torch.exp2(torch.floor(torch.log2(blk.abs().amax(-1).clamp_min(1e-30))) - 2)
+    assert ((back.float().view(R, C // 32, 32) - blk).abs() <= scale[..., None] * 1.0 + 1e-30).all()

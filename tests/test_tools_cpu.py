@@ -79,3 +79,22 @@ def test_slurm_plan_script_and_node_commands(tmp_path, capsys):
     cmd = node_launch.build_command(ns, env)
     assert "--no-controller" in cmd and cmd[cmd.index("--url") + 1] == "n01:8000" and cmd[cmd.index("--rollout") + 1] == "3"
     assert node_launch.build_command(ns, {"SLURM_JOB_NODELIST": "n[01-06]", "SLURM_NODEID": "1"}) is None
+
+
+def test_mxfp4_reference_quantiser():
+    import torch
+    from cosmos_rl_b200.ops import functional as F
+    from cosmos_rl_b200.ops import reference as R
+    w = torch.zeros(2, 32)
+    w[0, :8] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -6.0])       # amax 6 -> scale 1; ties go to even codes
+    w[1, :3] = torch.tensor([20.0, 3.0, -1.0])                                    # amax 20 -> scale 4
+    q, sf = F.quant_mxfp4(w)
+    back = F.dequant_mxfp4(q, sf)
+    assert back[0, :8].tolist() == [0.0, 1.0, 1.0, 2.0, 2.0, 4.0, 4.0, -6.0]
+    assert sf.tolist() == [127, 129] and back[1, :3].tolist() == [16.0, 4.0, 0.0]   # 20 / 4 = 5 ties down to 4; 0.75 up to 1
+    big = torch.randn(300, 256)
+    qs, sfs = F.quant_mxfp4(big, swizzle=True)
+    assert sfs.numel() == 3 * 2 * 512 and torch.equal(F.dequant_mxfp4(qs, sfs, True), F.dequant_mxfp4(*F.quant_mxfp4(big)))
+    idx = R.mxfp4_sf_index(256, 8, True)
+    assert idx[0, 0] == 0 and idx[1, 0] == 16 and idx[32, 0] == 4 and idx[0, 1] == 1 and idx[0, 4] == 512 and idx[128, 0] == 1024
+    assert idx.flatten().unique().numel() == 256 * 8
