@@ -19,6 +19,7 @@ from ..comm.broker import InProcessBroker, StreamBroker
 from ..config import Config
 from ..utils import constant
 from ..utils.logging import logger
+from ..utils.report import build_report_hooks
 from . import command as cmd
 from .data import ControllerDataFetcher, CosmosDataset
 from .data.schema import RLPayload, Rollout, payload_to_rollouts
@@ -39,7 +40,7 @@ class Controller:
         self.rollout_status_manager = RolloutStatusManager(config, self.broker)
         self.policy_status_manager = PolicyStatusManager(
             config, self.broker, self.data_fetcher, self.rollout_status_manager,
-            report_hooks=list(custom_logger_fns or []))
+            report_hooks=list(custom_logger_fns or []) + build_report_hooks(config))
         self.rollout_status_manager.policy_manager = self.policy_status_manager
         self.reference_replicas: Dict[str, Any] = {}
         self.policy_status_manager.recompute_total_steps()

@@ -17,6 +17,7 @@ from typing import Any, Callable, Deque, Dict, List, Optional
 import numpy as np
 
 from ..comm.broker import StreamBroker, command_stream, rollout_stream
+from ..utils import constant
 from ..utils.logging import logger
 from . import command as cmd
 from .data.schema import Rollout
@@ -507,8 +508,11 @@ class RolloutStatusManager(_ManagerBase):
             self.publish(r.name, c)
 
     def _p2r(self, src: Replica, dst: Replica, step: int, total: int, trainable_only: bool) -> None:
+        first = not getattr(dst, "sync_checked", False)
+        dst.sync_checked = True
         c = cmd.PolicyToRolloutUnicastCommand(src.name, dst.name, src.n_gpus, dst.n_gpus, weight_step=step,
-                                              total_steps=total, trainable_only=trainable_only)
+                                              total_steps=total, trainable_only=trainable_only,
+                                              do_weight_sync_check=bool(first and constant.COSMOS_WEIGHT_SYNC_CHECK))
         self.publish(src.name, c)
         self.publish(dst.name, c)
         dst.weights_loaded = True

@@ -41,6 +41,10 @@ def _worker_setup(role: str):
 
 def _tokenizer(config):
     path = config.policy.model_name_or_path
+    from ..utils.extension import load_tokenizer
+    tok, handled = load_tokenizer(path)
+    if handled:
+        return tok
     if os.path.isdir(path):
         try:
             from transformers import AutoTokenizer

@@ -25,6 +25,10 @@ def load_hf_config(name_or_path: str, override: Optional[Dict[str, Any]] = None)
     a built-in architecture name (``qwen2.5-7b``, ``qwen3-30b-a3b`` ...)."""
     if override:
         return dict(override)
+    from ..utils.extension import local_model_config
+    custom = local_model_config(name_or_path)
+    if custom is not None:
+        return custom
     if name_or_path and os.path.isdir(name_or_path) and os.path.exists(os.path.join(name_or_path, "config.json")):
         with open(os.path.join(name_or_path, "config.json")) as f:
             return json.load(f)

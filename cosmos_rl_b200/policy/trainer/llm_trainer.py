@@ -71,6 +71,10 @@ class LLMTrainer(Trainer):
         if tp > 1:
             from ...parallel.tp import TensorParallel
             model.tp = TensorParallel(parallel_dims.group("tp"), tp, parallel_dims.tp_coord)
+        from ...utils.extension import parallelism_strategy
+        custom_plan = parallelism_strategy(mt)
+        if custom_plan is not None:
+            custom_plan(model, parallel_dims, config)
         lr = config.train.optm_lr if isinstance(config.train.optm_lr, float) else float(
             list(config.train.optm_lr.values())[0] if isinstance(config.train.optm_lr, dict) else config.train.optm_lr[0])
         self.optimizer = FlatAdamW(

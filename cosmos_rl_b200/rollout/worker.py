@@ -118,10 +118,19 @@ class DisaggregatedRolloutControlWorker(CommMixin):
         t0 = time.perf_counter()
         key = f"p2r:{c.uuid_value}"
         peer = bool(self.config.b200.peer_weight_sync and self.device.type == "cuda")
+        check = None
+        if getattr(c, "do_weight_sync_check", False) and getattr(self.rollout, "flat", None) is not None \
+                and not c.trainable_only:
+            from ..utils.debug import WeightSyncCheck
+            check = WeightSyncCheck(self.rollout.flat.data, slots=self.rollout.flat.slots)
         if peer:
             self._peer_pull(c, key)
         else:
             self._collective_recv(c)
+        if check is not None:
+            if self.device.type == "cuda":
+                torch.cuda.synchronize()
+            self.stats["sync_check"] = check.finish()
         self.weights_ready = True
         self._pending_version = c.weight_step if c.weight_step is not None else 0
         self.total_steps = c.total_steps

@@ -316,3 +316,57 @@ def test_recompute_rollout_backend_for_deepseek_v3(tmp_path):
             ls = torch.log_softmax((h[-1] @ m.lm_head_weight.detach().t()).float(), -1)
             assert int(ls.argmax()) == t and abs(float(ls[t]) - lp) < 1e-4
             seq.append(t)
+
+
+def test_nan_hooks_weight_sync_check_report_sinks_and_extension_points(tmp_path):
+    import json
+    from cosmos_rl_b200.parallel.flat import FlatParams
+    from cosmos_rl_b200.utils import extension as X
+    from cosmos_rl_b200.utils.debug import NonFiniteError, WeightSyncCheck, add_nan_checks
+    from cosmos_rl_b200.utils.report import build_report_hooks
+    # NaN hooks name the first module that goes non-finite
+    net = nn.Sequential(nn.Linear(4, 4), nn.ReLU(), nn.Linear(4, 2))
+    hs = add_nan_checks(net)
+    net(torch.randn(3, 4))
+    with torch.no_grad():
+        net[2].weight.fill_(float("nan"))
+    with pytest.raises(NonFiniteError, match="output of 2"):
+        net(torch.randn(3, 4))
+    for h in hs:
+        h.remove()
+    # weight-sync verifier: full coverage passes, an unwritten parameter is named
+    m = nn.Sequential(nn.Linear(8, 8), nn.Linear(8, 8))
+    flat = FlatParams(m, torch.float32, torch.device("cpu"), with_grad=False)
+    flat.data.normal_()
+    src = flat.data.clone()
+    chk = WeightSyncCheck(flat.data, slots=flat.slots)
+    assert flat.data.abs().sum() == 0
+    flat.data.copy_(src)
+    assert chk.finish()["equal"]
+    chk = WeightSyncCheck(flat.data, slots=flat.slots)
+    hole = flat.slots[2]
+    flat.data.copy_(src)
+    flat.data[hole.offset:hole.offset + hole.numel] = 0
+    with pytest.raises(RuntimeError, match=hole.name):
+        chk.finish()
+    # report sinks
+    c = _config(tmp_path)
+    c.logging.logger = ["console", "jsonl"]
+    hooks = build_report_hooks(c)
+    hooks[0]({"train/loss_avg": 1.5, "note": "x", "skip": [1]}, 3)
+    row = json.loads(open(os.path.join(str(tmp_path), "metrics.jsonl")).read())
+    assert row["step"] == 3 and row["train/loss_avg"] == 1.5 and "skip" not in row
+    c.logging.logger = ["tensorboard"]
+    with pytest.raises(ValueError):
+        build_report_hooks(c)
+    # extension points: model config and tokenizer for a non-HF model name
+    from cosmos_rl_b200.models import hf_io
+    X.register_local_model_config("toy://", lambda name: {"model_type": "gym_mlp", "name": name})
+    X.register_tokenizer_loader("toy://", lambda name: None)
+    assert hf_io.load_hf_config("toy://cartpole")["model_type"] == "gym_mlp"
+    assert X.load_tokenizer("toy://cartpole") == (None, True) and X.load_tokenizer("other") == (None, False)
+
+    @X.register_parallelism_strategy("toy")
+    def plan(model, dims, config):
+        model.planned = True
+    assert X.parallelism_strategy("toy") is plan and X.parallelism_strategy("qwen2") is None
