@@ -1,8 +1,6 @@
 // Microscaling fp4 (OCP MX: 32 elements share one power-of-two E8M0 scale, elements are E2M1) quantisation of bf16
 // weights, the scale-factor layout block-scaled tensor-core MMA consumes, and the inverse (for numerics tests and for
-// serving through bf16 GEMMs). One thread owns one 32-element block: 64 B in (4 x 16-byte loads), 16 B + 1 B out, so a
-// warp reads 2 KB of contiguous row data per instruction group; the kernel is a pure stream (1.27 B moved per
-// element quantised) and is sized as a grid-stride loop over 148 SMs.
+// serving through bf16 GEMMs). Pure streaming kernels (2.53 bytes moved per element), grid-stride over 148 SMs.
 //
 // Scale-factor layouts:
 //   swizzle = 0: row-major [R, C/32].
@@ -29,39 +27,49 @@ __device__ __forceinline__ uint32_t e2m1_code(float a) {   // |x| / scale -> 3-b
   return (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) + (a >= 3.5f) + (a > 5.0f);
 }
 
+// Work item = 8 consecutive elements (one 16-byte load, one 4-byte store); the 4 lanes of a 32-element block share
+// the block maximum with two shuffles. Consecutive lanes take consecutive items, so every warp instruction reads 512
+// and writes 128 contiguous bytes.
 __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                                                            uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int R,
                                                            int C, int swizzle) {
   const int n_cb = C / 32;
-  const long long total = (long long)R * n_cb;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int r = (int)(i / n_cb), cb = (int)(i % n_cb);
-    const uint4* src = reinterpret_cast<const uint4*>(x + (long long)r * ldx + cb * 32);
-    uint4 v[4];
+  const long long total = (long long)R * n_cb * 4;           // multiple of 4: the lanes of a block stay together
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
+  // the loop condition is warp-uniform (first lane's index): every lane reaches the full-mask shuffles below
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x - lane; i0 < total; i0 += stride) {
+    const long long i = i0 + lane;
+    const bool valid = i < total;
+    const long long blk = i >> 2;
+    const int part = (int)(i & 3);
+    const int r = (int)(blk / n_cb), cb = (int)(blk % n_cb);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (valid) v = __ldg(reinterpret_cast<const uint4*>(x + (long long)r * ldx + cb * 32 + part * 8));
+    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+    float f[8], amax = 0.f;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) v[k] = __ldg(src + k);
-    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(v);
-    float f[32], amax = 0.f;
-#pragma unroll
-    for (int k = 0; k < 32; ++k) {
+    for (int k = 0; k < 8; ++k) {
       f[k] = __bfloat162float(e[k]);
       amax = fmaxf(amax, fabsf(f[k]));
     }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     // shared exponent: floor(log2(amax)) - 2 (the largest E2M1 magnitude is 6 = 1.5 * 2^2); zero / denormal blocks
     // take the smallest scale
     int ex = amax > 0.f ? (int)((__float_as_uint(amax) >> 23) & 0xff) - 127 - 2 : -127;
     ex = max(-127, min(127, ex));
-    const float inv = __uint_as_float((uint32_t)(127 - ex) << 23);   // 2^-ex, exact (ex in [-127, 127] -> exp 0..254)
-    uint32_t w[4] = {0, 0, 0, 0};
+    const float inv = __uint_as_float((uint32_t)(127 - ex) << 23);   // 2^-ex: exponent field 2..254 for finite input
+    uint32_t w = 0;
 #pragma unroll
-    for (int k = 0; k < 32; ++k) {
-      const float s = ex == -127 ? f[k] * 1.7014118e38f : f[k] * inv;   // 2^127 when the scale is 2^-127
-      const uint32_t code = e2m1_code(fabsf(s)) | (s < 0.f ? 8u : 0u);
-      w[k / 8] |= code << (4 * (k % 8));
+    for (int k = 0; k < 8; ++k) {
+      const float s = f[k] * inv;
+      w |= (e2m1_code(fabsf(s)) | (s < 0.f ? 8u : 0u)) << (4 * k);
     }
-    *reinterpret_cast<uint4*>(q + ((long long)r * C + cb * 32) / 2) = make_uint4(w[0], w[1], w[2], w[3]);
-    sf[sf_index(r, cb, n_cb, swizzle)] = (uint8_t)(ex + 127);
+    if (valid) {
+      reinterpret_cast<uint32_t*>(q)[((long long)r * C + cb * 32) / 8 + part] = w;
+      if (part == 0) sf[sf_index(r, cb, n_cb, swizzle)] = (uint8_t)(ex + 127);
+    }
   }
 }
 
@@ -70,25 +78,26 @@ __global__ void __launch_bounds__(256) dequant_mxfp4_kernel(const uint8_t* __res
                                                              __nv_bfloat16* __restrict__ out, long long ldo, int R,
                                                              int C, int swizzle) {
   const int n_cb = C / 32;
-  const long long total = (long long)R * n_cb;
-  const float lut[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int r = (int)(i / n_cb), cb = (int)(i % n_cb);
-    const uint4 pk = __ldg(reinterpret_cast<const uint4*>(q + ((long long)r * C + cb * 32) / 2));
-    const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
+  const long long total = (long long)R * n_cb * 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long blk = i >> 2;
+    const int part = (int)(i & 3);
+    const int r = (int)(blk / n_cb), cb = (int)(blk % n_cb);
+    const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(q) + ((long long)r * C + cb * 32) / 8 + part);
     const int eb = sf[sf_index(r, cb, n_cb, swizzle)];
     const float scale = eb == 0 ? 5.877471754e-39f : __uint_as_float((uint32_t)eb << 23);   // 2^(eb - 127)
-    __align__(16) __nv_bfloat16 o[32];
+    __align__(16) __nv_bfloat16 o[8];
 #pragma unroll
-    for (int k = 0; k < 32; ++k) {
-      const uint32_t c = (w[k / 8] >> (4 * (k % 8))) & 0xf;
-      const float val = lut[c & 7] * scale;
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t c = (w >> (4 * k)) & 0xf;
+      // E2M1 magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6: codes 0/1 are the subnormal pair, the rest (1 + m/2) * 2^(e-1)
+      const uint32_t m = c & 7;
+      const float mag = m < 2 ? 0.5f * (float)m : (1.f + 0.5f * (float)(m & 1)) * (float)(1 << ((m >> 1) - 1));
+      const float val = mag * scale;
       o[k] = __float2bfloat16((c & 8) ? -val : val);
     }
-    uint4* dst = reinterpret_cast<uint4*>(out + (long long)r * ldo + cb * 32);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) dst[k] = reinterpret_cast<const uint4*>(o)[k];
+    *reinterpret_cast<uint4*>(out + (long long)r * ldo + cb * 32 + part * 8) = *reinterpret_cast<const uint4*>(o);
   }
 }
 
@@ -101,8 +110,8 @@ extern "C" {
 int b200_quant_mxfp4(const void* x, long long ldx, void* q, void* sf, int R, int C, int swizzle, cudaStream_t stream) {
   if (R <= 0 || C <= 0) return 0;
   if (C % 32 != 0 || ldx % 8 != 0) return B200_ERR_ARG;
-  const long long total = (long long)R * (C / 32);
-  const int grid = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  const long long total = (long long)R * (C / 32) * 4;
+  const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   quant_mxfp4_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, (uint8_t*)sf, R, C, swizzle);
   return cudaGetLastError() == cudaSuccess ? 0 : B200_ERR_LAUNCH;
 }
@@ -111,8 +120,8 @@ int b200_dequant_mxfp4(const void* q, const void* sf, void* out, long long ldo, 
                        cudaStream_t stream) {
   if (R <= 0 || C <= 0) return 0;
   if (C % 32 != 0 || ldo % 8 != 0) return B200_ERR_ARG;
-  const long long total = (long long)R * (C / 32);
-  const int grid = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  const long long total = (long long)R * (C / 32) * 4;
+  const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   dequant_mxfp4_kernel<<<grid, 256, 0, stream>>>((const uint8_t*)q, (const uint8_t*)sf, (__nv_bfloat16*)out, ldo, R, C,
                                                  swizzle);
   return cudaGetLastError() == cudaSuccess ? 0 : B200_ERR_LAUNCH;

@@ -584,12 +584,12 @@ def test_dit_bf16_on_gpu_matches_fp32_reference():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("R,C,swizzle", [(128, 128, False), (300, 2880, True), (1, 32, True), (257, 96, False)])
-def test_mxfp4_quant_matches_reference_bit_for_bit(R, C, swizzle):
+@pytest.mark.parametrize("rows,cols,swizzle", [(128, 128, False), (300, 2880, True), (1, 32, True), (257, 96, False)])
+def test_mxfp4_quant_matches_reference_bit_for_bit(rows, cols, swizzle):
     torch.manual_seed(9)
-    w = (torch.randn(R, C, device="cuda") * torch.logspace(-3, 2, R, device="cuda")[:, None]).to(torch.bfloat16)
+    w = (torch.randn(rows, cols, device="cuda") * torch.logspace(-3, 2, rows, device="cuda")[:, None]).to(torch.bfloat16)
     w[0, :32] = 0                                          # an all-zero block takes the smallest scale
-    if R > 2:
+    if rows > 2:
         w[2, :8] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -5.0], device="cuda") * 4   # ties, amax 20 -> scale 4
         w[2, 8:32] = 0
     q, sf = F.quant_mxfp4(w, swizzle)
@@ -598,6 +598,6 @@ def test_mxfp4_quant_matches_reference_bit_for_bit(R, C, swizzle):
     back = F.dequant_mxfp4(q, sf, swizzle)
     assert torch.equal(back.float(), R.dequant_mxfp4(rq, rsf, swizzle).to(torch.bfloat16).float())
     # every element is within half a quantisation step of its block: the largest gap of the E2M1 grid is 2 scales
-    blk = w.float().view(R, C // 32, 32)
+    blk = w.float().view(rows, cols // 32, 32)
     scale = torch.exp2(torch.floor(torch.log2(blk.abs().amax(-1).clamp_min(1e-30))) - 2)
-    assert ((back.float().view(R, C // 32, 32) - blk).abs() <= scale[..., None] * 1.0 + 1e-30).all()
+    assert ((back.float().view(rows, cols // 32, 32) - blk).abs() <= scale[..., None] * 1.0 + 1e-30).all()
