@@ -432,6 +432,8 @@ class B200Config(_Section):
     fused_logprob: bool = True           # tcgen05 fused lm_head + log-prob kernel
     nvls: bool = True                    # allow multimem (NVSwitch) reductions where available
     dlogits_chunk: int = 16384
+    sequence_parallel: bool = True       # with tp_size > 1 (dense models, no pp / cp): residual stream and norms hold
+                                         # T / tp rows; projections run all-gather -> GEMM / GEMM -> reduce-scatter
     router_bias_update_rate: float = 1e-3  # DeepSeek-V3 load-balancing bias step per optimizer step (0 = frozen)
     recompute: str = "auto"              # with policy.model_gradient_checkpointing: "selective" (attention half +
                                          # SwiGLU only), "full" (whole block, least memory), "none", or "auto":

@@ -131,8 +131,10 @@ class Attention(nn.Module):
 
     def project_qkv(self, x: torch.Tensor, positions: torch.Tensor):
         """x [T, H] -> q [T, hq, d], k, v [T, hkv, d] with RoPE (and per-head q/k norm) applied."""
-        T = x.shape[0]
-        qkv = _linear(x, self.qkv_proj.weight, self.qkv_proj.bias)
+        return self.split_qkv(_linear(x, self.qkv_proj.weight, self.qkv_proj.bias), positions)
+
+    def split_qkv(self, qkv: torch.Tensor, positions: torch.Tensor):
+        T = qkv.shape[0]
         hq, hkv, d = self.hq, self.hkv, self.d
         if self.qk_norm:
             q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
@@ -152,15 +154,18 @@ class Attention(nn.Module):
     cp = None    # ContextParallel, set by GPT.attach_context_parallel: tokens are this rank's chunk of every sequence
 
     def forward(self, x, positions, cu_seqlens, max_seqlen, tp=None):
-        if tp is not None and torch.is_grad_enabled():
-            x = tp.copy_to_region(x)          # column-parallel input: the gradient is summed over the TP ranks
+        """``x`` is [T, H], or this rank's [T / tp, H] rows under sequence parallelism (the column-parallel projection
+        gathers the sequence, the row-parallel one scatters it again)."""
         self.tp_for_replicated = tp
-        q, k, v = self.project_qkv(x, positions)
+        if tp is not None:
+            q, k, v = self.split_qkv(tp.col_linear(x, self.qkv_proj.weight, self.qkv_proj.bias), positions)
+        else:
+            q, k, v = self.project_qkv(x, positions)
         if self.cp is not None:
             o = self.cp.attention(q, k, v, cu_seqlens, max_seqlen)
         else:
             o = F.varlen_attention(q, k, v, cu_seqlens, max_seqlen)
-        o = o.reshape(x.shape[0], -1)
+        o = o.reshape(q.shape[0], -1)
         return tp.row_linear(o, self.o_proj.weight) if tp is not None else _linear(o, self.o_proj.weight)
 
 
@@ -173,10 +178,9 @@ class FeedForward(nn.Module):
         self.down_proj = nn.Linear(self.I, a.dim, bias=False)
 
     def forward(self, x, tp=None):
-        if tp is not None and torch.is_grad_enabled():
-            x = tp.copy_to_region(x)
-        act = F.swiglu(_linear(x, self.gate_up_proj.weight))
-        return tp.row_linear(act, self.down_proj.weight) if tp is not None else _linear(act, self.down_proj.weight)
+        if tp is None:
+            return _linear(F.swiglu(_linear(x, self.gate_up_proj.weight)), self.down_proj.weight)
+        return tp.row_linear(F.swiglu(tp.col_linear(x, self.gate_up_proj.weight)), self.down_proj.weight)
 
 
 class GPTBlock(nn.Module):
@@ -189,13 +193,16 @@ class GPTBlock(nn.Module):
         self.mlp = FeedForward(a)
 
     def _attn_part(self, h, res, positions, cu_seqlens, max_seqlen, tp):
+        w_in, w_post = self.input_layernorm, self.post_attention_layernorm
+        if tp is not None:
+            w_in, w_post = tp.shared_weight(w_in), tp.shared_weight(w_post)
         if res is None:
-            x, _ = F.rms_norm(h, self.input_layernorm, self.eps)
+            x, _ = F.rms_norm(h, w_in, self.eps)
             res = h
         else:
-            x, res = F.rms_norm(h, self.input_layernorm, self.eps, residual=res)
+            x, res = F.rms_norm(h, w_in, self.eps, residual=res)
         h = self.self_attn(x, positions, cu_seqlens, max_seqlen, tp)
-        x, res = F.rms_norm(h, self.post_attention_layernorm, self.eps, residual=res)
+        x, res = F.rms_norm(h, w_post, self.eps, residual=res)
         return x, res
 
     def forward(self, h, res, positions, cu_seqlens, max_seqlen, tp=None, recompute: str = "none"):
@@ -210,7 +217,8 @@ class GPTBlock(nn.Module):
             else:
                 x, res = checkpoint(self._attn_part, h, res, positions, cu_seqlens, max_seqlen, tp,
                                     use_reentrant=False)
-            gu = _linear(tp.copy_to_region(x) if tp is not None else x, self.mlp.gate_up_proj.weight)
+            gu = tp.col_linear(x, self.mlp.gate_up_proj.weight) if tp is not None else \
+                _linear(x, self.mlp.gate_up_proj.weight)
             act = checkpoint(F.swiglu, gu, use_reentrant=False)
             h = tp.row_linear(act, self.mlp.down_proj.weight) if tp is not None else \
                 _linear(act, self.mlp.down_proj.weight)
@@ -315,7 +323,23 @@ class GPT(BaseModel):
 
     def forward(self, input_ids: torch.Tensor, position_ids: torch.Tensor, cu_seqlens: torch.Tensor,
                 max_seqlen: int) -> torch.Tensor:
-        """Packed forward: ``input_ids [T]`` -> final hidden states ``[T, H]`` (after the last norm)."""
+        """Packed forward: ``input_ids [T]`` -> final hidden states ``[T, H]`` (after the last norm).
+
+        Under sequence parallelism the token axis is padded to the rank multiple with a dummy sequence, every block
+        works on this rank's rows, and the final hidden states are gathered (and un-padded) before they are returned."""
+        sp = self.tp is not None and self.tp.sequence_parallel
+        T = input_ids.shape[0]
+        if sp:
+            if not (self.is_first_stage and self.is_last_stage):
+                raise NotImplementedError("sequence parallelism is not combined with pipeline stages")
+            mult = self.tp.row_multiple(input_ids.is_cuda)
+            pad = (-T) % mult
+            if pad:
+                input_ids = torch.nn.functional.pad(input_ids, (0, pad))
+                position_ids = torch.cat([position_ids, torch.arange(pad, device=position_ids.device,
+                                                                     dtype=position_ids.dtype)])
+                cu_seqlens = torch.cat([cu_seqlens, cu_seqlens.new_tensor([T + pad])])
+                max_seqlen = max(int(max_seqlen), pad)
         h = self.embed(input_ids) if self.is_first_stage else input_ids   # later stages receive hidden states
         res = None
         for layer in self.layers:
@@ -328,7 +352,10 @@ class GPT(BaseModel):
                 h, res = layer(h, res, position_ids, cu_seqlens, max_seqlen, self.tp)
         if not self.is_last_stage:
             return h + res if res is not None else h                        # one tensor crosses the stage boundary
-        out, _ = F.rms_norm(h, self.norm, self.args.norm_eps, residual=res)
+        norm_w = self.tp.shared_weight(self.norm) if self.tp is not None else self.norm
+        out, _ = F.rms_norm(h, norm_w, self.args.norm_eps, residual=res)
+        if sp:
+            out = self.tp.gather_rows(out)[:T]
         return out
 
     def attach_context_parallel(self, cp) -> None:

@@ -53,11 +53,146 @@ class _AllGatherLast(torch.autograd.Function):
         return g.chunk(ctx.world, dim=-1)[r].contiguous(), None, None
 
 
+def _gather_rows(x: torch.Tensor, group, world: int) -> torch.Tensor:
+    parts = [torch.empty_like(x) for _ in range(world)]
+    dist.all_gather(parts, x.contiguous(), group=group)
+    return torch.cat(parts, dim=0)
+
+
+def _reduce_scatter_rows(x: torch.Tensor, group, world: int, rank: int) -> torch.Tensor:
+    """Sum over ranks, keep this rank's block of rows. NCCL has the collective; gloo takes all-reduce + slice."""
+    x = x.contiguous()
+    n = x.shape[0] // world
+    if x.is_cuda:
+        out = torch.empty((n,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, x, group=group)
+        return out
+    dist.all_reduce(x, group=group)
+    return x[rank * n:(rank + 1) * n].clone()
+
+
+class _GatherRows(torch.autograd.Function):
+    """Sequence shards -> full sequence. What follows is computed identically on every rank (or reduces its own
+    gradient, as the vocabulary-parallel log-prob does), so the backward pass just takes this rank's rows."""
+
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return _gather_rows(x, tp.group, tp.size)
+
+    @staticmethod
+    def backward(ctx, g):
+        tp = ctx.tp
+        n = g.shape[0] // tp.size
+        return g[tp.rank * n:(tp.rank + 1) * n].contiguous(), None
+
+
+class _ScatterRowsSum(torch.autograd.Function):
+    """Partial sums over the full sequence -> summed rows of this rank (embedding output); backward all-gathers."""
+
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return _reduce_scatter_rows(x, tp.group, tp.size, tp.rank)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _gather_rows(g, ctx.tp.group, ctx.tp.size), None
+
+
+class _GatherGemm(torch.autograd.Function):
+    """Column-parallel projection on a sequence-sharded input: ``Y = gather(x) @ w^T`` with x [T/tp, K], w [N/tp, K].
+    Forward and the input gradient (``dx = reduce_scatter(dY @ w)``) run the fused all-gather -> GEMM and
+    GEMM -> reduce-scatter kernels when attached; the weight gradient re-gathers x (cheaper than keeping the gathered
+    activations of every layer alive)."""
+
+    @staticmethod
+    def forward(ctx, x, w, tp):
+        ctx.tp = tp
+        ctx.save_for_backward(x, w)
+        ag = tp.fused_ag
+        if ag is not None and x.is_cuda and x.dtype == torch.bfloat16 and ag.fits(x.shape[0] * tp.size, x.shape[1]):
+            return ag.gemm(x.contiguous(), w)
+        return torch.nn.functional.linear(_gather_rows(x, tp.group, tp.size), w)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, w = ctx.saved_tensors
+        tp = ctx.tp
+        gy = gy.contiguous()
+        f = tp.fused
+        if (f is not None and gy.is_cuda and gy.dtype == torch.bfloat16 and gy.shape[0] % (128 * tp.size) == 0
+                and f.fits(gy.shape[0], w.shape[1], 1)):
+            gx = f.gemm_reduce_scatter(gy, w.t().contiguous())
+        else:
+            gx = _reduce_scatter_rows(gy @ w, tp.group, tp.size, tp.rank)
+        gw = gy.t() @ _gather_rows(x, tp.group, tp.size)
+        return gx, gw, None
+
+
+class _GemmScatter(torch.autograd.Function):
+    """Row-parallel projection back to sequence shards: ``y = reduce_scatter(x @ w^T)`` with x [T, K/tp], w [N, K/tp];
+    the input gradient is ``gather(dy) @ w`` (fused all-gather -> GEMM), the weight gradient ``gather(dy)^T x``."""
+
+    @staticmethod
+    def forward(ctx, x, w, tp):
+        ctx.tp = tp
+        ctx.save_for_backward(x, w)
+        f = tp.fused
+        if (f is not None and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[0] % (128 * tp.size) == 0
+                and f.fits(x.shape[0], w.shape[0], 1)):
+            return f.gemm_reduce_scatter(x.contiguous(), w)
+        return _reduce_scatter_rows(torch.nn.functional.linear(x, w), tp.group, tp.size, tp.rank)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, w = ctx.saved_tensors
+        tp = ctx.tp
+        gy = gy.contiguous()
+        ag = tp.fused_ag
+        gy_full = _gather_rows(gy, tp.group, tp.size)
+        if ag is not None and gy.is_cuda and gy.dtype == torch.bfloat16 and ag.fits(gy.shape[0] * tp.size, gy.shape[1]):
+            gx = ag.gemm(gy, w.t().contiguous())
+        else:
+            gx = gy_full @ w
+        return gx, gy_full.t() @ x, None
+
+
 class TensorParallel:
     def __init__(self, group: dist.ProcessGroup, size: int, rank: int, fused=None):
         self.group, self.size, self.rank = group, size, rank
         self.fused = fused
+        self.fused_ag = None
         self.fused_min_rows = 4096
+        # sequence parallelism: the residual stream, norms and dropout-free elementwise work hold T/tp rows per rank;
+        # column-parallel projections gather the sequence, row-parallel ones scatter it again
+        # (cosmos_rl/policy/model/gpt/parallelize.py:244-327)
+        self.sequence_parallel = False
+
+    # ------------------------------------------------------------------ sequence-parallel building blocks
+    def row_multiple(self, cuda: bool) -> int:
+        """Token counts are padded to a multiple of this (the fused kernels work on 128-row blocks per rank)."""
+        return self.size * (128 if cuda and (self.fused is not None or self.fused_ag is not None) else 1)
+
+    def col_linear(self, x, w, b=None):
+        """Column-parallel projection; ``x`` is a sequence shard in sequence-parallel mode, replicated otherwise."""
+        if self.sequence_parallel:
+            y = _GatherGemm.apply(x, w, self)
+            return y if b is None else y + b
+        if torch.is_grad_enabled():
+            x = self.copy_to_region(x)
+        from ..ops.functional import linear_maybe_fp8
+        return linear_maybe_fp8(x, w, b)
+
+    def gather_rows(self, x):
+        return _GatherRows.apply(x, self)
+
+    def scatter_rows_sum(self, x):
+        return _ScatterRowsSum.apply(x, self)
+
+    def shared_weight(self, w):
+        """A replicated weight applied to this rank's sequence shard only: its gradient is summed over the ranks."""
+        return self.copy_to_region(w) if (self.sequence_parallel and torch.is_grad_enabled()) else w
 
     def copy_to_region(self, x):
         return _CopyToTP.apply(x, self.group)
@@ -69,6 +204,8 @@ class TensorParallel:
     def row_linear(self, x, w):
         """Row-parallel projection + reduction. Inference on GPU with a peer-memory context attached runs the
         fused tcgen05 GEMM + all-reduce kernel; otherwise a GEMM followed by the library all-reduce."""
+        if self.sequence_parallel:
+            return _GemmScatter.apply(x, w, self)
         f = self.fused
         # below ~4k rows the projection is launch/latency bound and the library pair is faster (measured
         # crossover on 2 GPUs between 2048 and 8192 rows); prefill and training shapes take the fused kernel
@@ -79,9 +216,14 @@ class TensorParallel:
         from ..ops.functional import linear_maybe_fp8
         return _AllReduce.apply(linear_maybe_fp8(x, w), self.group)
 
-    def attach_fused(self, device, max_rows: int, max_cols: int) -> None:
-        from .tp_fused import FusedTP
+    def attach_fused(self, device, max_rows: int, max_cols: int, all_gather_k: int = 0) -> None:
+        """``all_gather_k`` > 0 also attaches the all-gather -> GEMM workspace (inner dimension up to that size),
+        which the sequence-parallel training plan uses."""
+        from .tp_fused import FusedAllGatherGemm, FusedTP
         self.fused = FusedTP(self.group, self.size, self.rank, device, max_rows, max_cols)
+        if all_gather_k > 0:
+            rows = (max_rows + 128 * self.size - 1) // (128 * self.size) * (128 * self.size)
+            self.fused_ag = FusedAllGatherGemm(self.group, self.size, self.rank, device, rows, all_gather_k)
 
     def gather_vocab(self, logits_local):
         return _AllGatherLast.apply(logits_local, self.group, self.size)
@@ -92,6 +234,8 @@ class TensorParallel:
         mask = (input_ids >= lo) & (input_ids < lo + v_local)
         local = torch.where(mask, input_ids - lo, torch.zeros_like(input_ids))
         out = torch.nn.functional.embedding(local, weight_local) * mask.unsqueeze(-1).to(weight_local.dtype)
+        if self.sequence_parallel:
+            return self.scatter_rows_sum(out)
         return _AllReduce.apply(out, self.group)
 
     def vocab_parallel_logprob(self, hidden, weight_local, labels, temperature: float = 1.0):

@@ -52,10 +52,17 @@ class FlatAdamW:
     def __init__(self, flat: FlatParams, lr: float, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
                  max_grad_norm: float = 1.0, dp_group: Optional[dist.ProcessGroup] = None,
                  master_dtype: torch.dtype = torch.float32, collective=None,
-                 replicate_group: Optional[dist.ProcessGroup] = None):
+                 replicate_group: Optional[dist.ProcessGroup] = None,
+                 tp_group: Optional[dist.ProcessGroup] = None, tp_replicated: Optional[torch.Tensor] = None,
+                 norm_groups=()):
         """``dp_group`` shards optimizer state (ZeRO-2 style); ``replicate_group`` is the outer data-parallel axis of
         HSDP / DDP (cosmos_rl/policy/model/gpt/parallelize.py:80-113, 426-442): ranks of it hold the same shard and
         average their reduced gradient shard before the update, so the all-reduce moves 1/dp_shard of the gradient."""
+        # gradient norm under model parallelism: parameters sharded over ``tp_group`` contribute once per rank, the
+        # ones every tensor-parallel rank holds (``tp_replicated``: bool mask over the flat buffer) only once;
+        # ``norm_groups`` are further groups whose ranks hold disjoint parameters (pipeline stages)
+        self.tp_group, self.norm_groups = tp_group, tuple(norm_groups)
+        self.tp_replicated = tp_replicated
         self.flat = flat
         self.replicate_group = replicate_group
         self.n_replicas = dist.get_world_size(replicate_group) if replicate_group is not None else 1
@@ -141,9 +148,19 @@ class FlatAdamW:
             if self.trainable is not None:
                 gt.mul_(self.trainable[self.t0:self.t1].to(gt.dtype))
             sumsq = sumsq + K.grad_sumsq([gt]) / float(self.world * self.world)
+        rep = None
+        if self.tp_group is not None and self.tp_replicated is not None:
+            rep = K.grad_sumsq([(g.float() * self.tp_replicated[self.lo:self.hi].to(torch.float32))])
+            sumsq = sumsq - rep
         if self.world > 1:
             dist.all_reduce(sumsq, group=self.group)
-        for grp in extra_norm_groups:  # e.g. tensor-/pipeline-parallel groups that hold disjoint parameters
+            if rep is not None:
+                dist.all_reduce(rep, group=self.group)
+        if self.tp_group is not None:
+            dist.all_reduce(sumsq, group=self.tp_group)
+            if rep is not None:
+                sumsq = sumsq + rep
+        for grp in tuple(extra_norm_groups) + self.norm_groups:  # groups whose ranks hold disjoint parameters
             dist.all_reduce(sumsq, group=grp)
         norm, coef = K.clip_coef_from_sumsq(sumsq, self.max_grad_norm)
         hp = dict(lr=self.lr * lr_scale, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps,

@@ -71,15 +71,27 @@ class LLMTrainer(Trainer):
         if tp > 1:
             from ...parallel.tp import TensorParallel
             model.tp = TensorParallel(parallel_dims.group("tp"), tp, parallel_dims.tp_coord)
+            from ...models.gpt import GPT
+            model.tp.sequence_parallel = bool(config.b200.sequence_parallel and type(model) is GPT
+                                              and parallel_dims.pp == 1 and parallel_dims.cp == 1)
         from ...utils.extension import parallelism_strategy
         custom_plan = parallelism_strategy(mt)
         if custom_plan is not None:
             custom_plan(model, parallel_dims, config)
         lr = config.train.optm_lr if isinstance(config.train.optm_lr, float) else float(
             list(config.train.optm_lr.values())[0] if isinstance(config.train.optm_lr, dict) else config.train.optm_lr[0])
+        tp_mask = None
+        if tp > 1:
+            # parameters every tensor-parallel rank holds in full (norm weights): counted once in the gradient norm
+            tp_mask = torch.zeros(self.flat.total, dtype=torch.bool, device=self.device)
+            for slot in self.flat.slots:
+                if "norm" in slot.name:
+                    tp_mask[slot.offset:slot.offset + slot.numel] = True
         self.optimizer = FlatAdamW(
             self.flat, lr=lr, betas=tuple(config.train.optm_betas), eps=config.train.epsilon,
             weight_decay=config.train.optm_weight_decay, max_grad_norm=config.train.optm_grad_norm_clip,
+            tp_group=parallel_dims.group("tp") if tp > 1 else None, tp_replicated=tp_mask,
+            norm_groups=[parallel_dims.group("pp")] if parallel_dims.pp > 1 else [],
             dp_group=parallel_dims.group("dp_shard") if dp > 1 else None, collective=kw.get("collective"),
             replicate_group=parallel_dims.group("dp_replicate") if parallel_dims.dp_replicate > 1 else None)
         self.data_packer = data_packer or BaseDataPacker.get_default(mt)()
@@ -95,6 +107,13 @@ class LLMTrainer(Trainer):
         """``recompute = "auto"``: decide once, before the first backward pass, from the memory that is actually
         free. Activations kept per token and block without recomputation: the two norm inputs and residuals (4 H),
         q/k/v and the attention output, the gate/up product (2 I) and the SwiGLU output (I), all bf16."""
+        tpo = getattr(self.model, "tp", None)
+        if (tpo is not None and tpo.sequence_parallel and self.device.type == "cuda" and tpo.fused_ag is None
+                and hasattr(self.model, "args")):
+            # peer-memory workspaces of the fused all-gather -> GEMM and GEMM -> reduce-scatter kernels, sized for the
+            # largest packed micro-batch (padded to whole 128-row blocks per rank)
+            rows = (max_tokens + 128 * tpo.size - 1) // (128 * tpo.size) * (128 * tpo.size)
+            tpo.attach_fused(self.device, rows, self.model.args.dim, all_gather_k=self.model.args.dim)
         if not self._recompute_auto:
             return
         self._recompute_auto = False

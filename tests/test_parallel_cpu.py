@@ -156,7 +156,7 @@ def test_rank_leaving_between_steps_times_out_and_mesh_is_rebuilt(tmp_path):
     mp.spawn(_failure_worker, args=(2, str(tmp_path / "fstore")), nprocs=2, join=True)
 
 
-def _tp_worker(rank, world, store, qk_norm):
+def _tp_worker(rank, world, store, qk_norm, seq_parallel=False):
     """Tensor-parallel training step == unsharded model: log-probs and (gathered) gradients."""
     import copy
     from cosmos_rl_b200.models import hf_io
@@ -174,6 +174,9 @@ def _tp_worker(rank, world, store, qk_norm):
     state = hf_io.hf_state_dict(full, cfg)
     hf_io.load_hf_state(shard, lambda k: state[k], state, cfg, world, rank)
     shard.tp = TensorParallel(dist.group.WORLD, world, rank)
+    shard.tp.sequence_parallel = seq_parallel        # 21 tokens on 2 ranks: exercises the padding sequence too
+    if seq_parallel:
+        shard.gradient_checkpointing = "swiglu"
     g = torch.Generator().manual_seed(2)
     cu = torch.tensor([0, 9, 21])
     ids = torch.randint(0, 512, (21,), generator=g)
@@ -203,6 +206,12 @@ def _tp_worker(rank, world, store, qk_norm):
 @pytest.mark.parametrize("qk_norm", [False, True])
 def test_tensor_parallel_training_matches_full_model(tmp_path, qk_norm):
     _spawn(_tp_worker, 2, tmp_path, qk_norm)
+
+
+@pytest.mark.parametrize("qk_norm", [False, True])
+def test_sequence_parallel_training_matches_full_model(tmp_path, qk_norm):
+    """Residual stream, norms and the embedding output hold T/tp rows per rank; same log-probs and gradients."""
+    _spawn(_tp_worker, 2, tmp_path, qk_norm, True)
 
 
 def _ep_worker(rank, world, store):
@@ -416,3 +425,49 @@ def _hsdp_worker(rank, world, store):
 
 def test_hsdp_and_ddp_match_unsharded_adamw(tmp_path):
     _spawn(_hsdp_worker, 4, tmp_path)
+
+
+def _tp_trainer_worker(rank, world, store, out_dir):
+    """The SFT trainer with tp_size = 2 (sequence-parallel plan): same losses, gradient norms and resulting weights as
+    the single-process trainer on the same batches."""
+    from cosmos_rl_b200.config import Config
+    from cosmos_rl_b200.models import hf_io
+    from cosmos_rl_b200.parallel.dims import ParallelDims
+    from cosmos_rl_b200.policy.trainer.sft_trainer import SFTTrainer
+    _init(rank, world, store)
+
+    def cfg(tp):
+        return Config.from_dict({
+            "policy": {"model_name_or_path": "tiny-qwen2", "model_max_length": 64, "model_gradient_checkpointing": False,
+                       "parallelism": {"tp_size": tp, "dp_shard_size": 1}},
+            "train": {"seed": 0, "optm_lr": 1e-3, "optm_warmup_steps": 0, "output_dir": out_dir, "optm_grad_norm_clip": 0.5,
+                      "train_policy": {"type": "sft", "trainer_type": "sft", "mini_batch": 4},
+                      "ckpt": {"enable_checkpoint": False}}})
+    dims = ParallelDims.from_config_parallelism(cfg(2).policy.parallelism, world, rank, torch.device("cpu"))
+    dims.build_groups()
+    tr = SFTTrainer(cfg(2), dims, device=torch.device("cpu"))
+    assert tr.model.tp.sequence_parallel and tr.optimizer.tp_replicated.any()
+    ref = SFTTrainer(cfg(1), ParallelDims(world_size=1, device=torch.device("cpu")), device=torch.device("cpu"))
+    ref.model_load_from_hf()
+    hf_cfg = ref.model.args.to_hf_config()
+    state = hf_io.hf_state_dict(ref.model, hf_cfg)
+    hf_io.load_hf_state(tr.model, lambda k: state[k], state, hf_cfg, world, rank)
+    tr.optimizer.refresh_master_from_params()
+    tr.weights_ready = True
+    g = torch.Generator().manual_seed(3)
+    batch = [{"input_ids": torch.randint(0, 32000, (n,), generator=g).tolist()} for n in (12, 9, 15, 7)]
+    for i in range(3):
+        a = tr.step_training(batch, total_steps=10, train_step=i + 1)
+        b = ref.step_training(batch, total_steps=10, train_step=i + 1)
+        assert abs(a["train/loss_avg"] - b["train/loss_avg"]) < 1e-4, (i, a["train/loss_avg"], b["train/loss_avg"])
+        assert abs(a["train/grad_norm"] - b["train/grad_norm"]) < 1e-3 * b["train/grad_norm"], (i, a["train/grad_norm"], b["train/grad_norm"])
+    want = hf_io.hf_state_dict(ref.model, hf_cfg)
+    probe = GPT(tr.model.args)
+    hf_io.load_hf_state(probe, lambda k: want[k], want, hf_cfg, world, rank)      # reference weights, this rank's slices
+    for (n, p), (_, q) in zip(tr.model.named_parameters(), probe.named_parameters()):
+        assert torch.allclose(p, q, atol=5e-4), (n, (p - q).abs().max())
+    dist.destroy_process_group()
+
+
+def test_sft_trainer_with_tensor_and_sequence_parallelism(tmp_path):
+    _spawn(_tp_trainer_worker, 2, tmp_path, str(tmp_path))
