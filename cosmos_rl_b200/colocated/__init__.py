@@ -49,7 +49,11 @@ class ColocatedGRPO:
 
     # ------------------------------------------------------------------
     def rollout(self, prompts: Sequence, references: Optional[Sequence] = None) -> List[Rollout]:
-        outs = self.engine.generate(prompts, self.sampling)
+        self.trainer.before_weight_sync()              # LoRA: the engine reads the base weights with adapters folded in
+        try:
+            outs = self.engine.generate(prompts, self.sampling)
+        finally:
+            self.trainer.after_weight_sync()
         rollouts: List[Rollout] = []
         for pi, comps in enumerate(outs):
             ref = references[pi] if references is not None else None

@@ -90,7 +90,14 @@ class ColocatedRLControlWorker:
         if not batch:
             return not is_end
         payloads = [self.fetcher.fill(p) for _, p in batch]
-        results = self.rollout.rollout_generation(payloads, self.packer)
+        sync = getattr(self.trainer, "before_weight_sync", None)      # LoRA: generate with the adapters folded in
+        if sync is not None:
+            sync()
+        try:
+            results = self.rollout.rollout_generation(payloads, self.packer)
+        finally:
+            if sync is not None:
+                self.trainer.after_weight_sync()
         for p, r in zip(payloads, results):
             p.completions = r.completions
             if r.completion_token_ids is not None:

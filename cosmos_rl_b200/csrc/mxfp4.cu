@@ -41,9 +41,9 @@ __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const __nv_bfloat16* _
   for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x - lane; i0 < total; i0 += stride) {
     const long long i = i0 + lane;
     const bool valid = i < total;
-    const long long blk = i >> 2;
+    const uint32_t blk = (uint32_t)(i >> 2);                // block index fits 32 bits (checked by the launcher)
     const int part = (int)(i & 3);
-    const int r = (int)(blk / n_cb), cb = (int)(blk % n_cb);
+    const uint32_t r = blk / (uint32_t)n_cb, cb = blk - r * (uint32_t)n_cb;   // 32-bit divide: 64-bit costs 5x more
     uint4 v = make_uint4(0, 0, 0, 0);
     if (valid) v = __ldg(reinterpret_cast<const uint4*>(x + (long long)r * ldx + cb * 32 + part * 8));
     const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
@@ -67,8 +67,8 @@ __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const __nv_bfloat16* _
       w |= (e2m1_code(fabsf(s)) | (s < 0.f ? 8u : 0u)) << (4 * k);
     }
     if (valid) {
-      reinterpret_cast<uint32_t*>(q)[((long long)r * C + cb * 32) / 8 + part] = w;
-      if (part == 0) sf[sf_index(r, cb, n_cb, swizzle)] = (uint8_t)(ex + 127);
+      reinterpret_cast<uint32_t*>(q)[i] = w;                // packed output is dense: item i = word i
+      if (part == 0) sf[sf_index((int)r, (int)cb, n_cb, swizzle)] = (uint8_t)(ex + 127);
     }
   }
 }
@@ -81,11 +81,11 @@ __global__ void __launch_bounds__(256) dequant_mxfp4_kernel(const uint8_t* __res
   const long long total = (long long)R * n_cb * 4;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += stride) {
-    const long long blk = i >> 2;
+    const uint32_t blk = (uint32_t)(i >> 2);
     const int part = (int)(i & 3);
-    const int r = (int)(blk / n_cb), cb = (int)(blk % n_cb);
-    const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(q) + ((long long)r * C + cb * 32) / 8 + part);
-    const int eb = sf[sf_index(r, cb, n_cb, swizzle)];
+    const uint32_t r = blk / (uint32_t)n_cb, cb = blk - r * (uint32_t)n_cb;
+    const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(q) + i);
+    const int eb = sf[sf_index((int)r, (int)cb, n_cb, swizzle)];
     const float scale = eb == 0 ? 5.877471754e-39f : __uint_as_float((uint32_t)eb << 23);   // 2^(eb - 127)
     __align__(16) __nv_bfloat16 o[8];
 #pragma unroll
@@ -109,7 +109,7 @@ extern "C" {
 // even element), sf E8M0 bytes (layout by `swizzle`; the swizzled buffer holds ceil(R/128) * ceil(C/128) * 512 bytes).
 int b200_quant_mxfp4(const void* x, long long ldx, void* q, void* sf, int R, int C, int swizzle, cudaStream_t stream) {
   if (R <= 0 || C <= 0) return 0;
-  if (C % 32 != 0 || ldx % 8 != 0) return B200_ERR_ARG;
+  if (C % 32 != 0 || ldx % 8 != 0 || (long long)R * (C / 32) >= (1ll << 31)) return B200_ERR_ARG;
   const long long total = (long long)R * (C / 32) * 4;
   const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   quant_mxfp4_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, (uint8_t*)sf, R, C, swizzle);
@@ -119,7 +119,7 @@ int b200_quant_mxfp4(const void* x, long long ldx, void* q, void* sf, int R, int
 int b200_dequant_mxfp4(const void* q, const void* sf, void* out, long long ldo, int R, int C, int swizzle,
                        cudaStream_t stream) {
   if (R <= 0 || C <= 0) return 0;
-  if (C % 32 != 0 || ldo % 8 != 0) return B200_ERR_ARG;
+  if (C % 32 != 0 || ldo % 8 != 0 || (long long)R * (C / 32) >= (1ll << 31)) return B200_ERR_ARG;
   const long long total = (long long)R * (C / 32) * 4;
   const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   dequant_mxfp4_kernel<<<grid, 256, 0, stream>>>((const uint8_t*)q, (const uint8_t*)sf, (__nv_bfloat16*)out, ldo, R, C,

@@ -110,7 +110,9 @@ def _rope_theta(g, default: float) -> float:
 
 
 def _linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -> torch.Tensor:
-    return F.linear_maybe_fp8(x, w, b)
+    y = F.linear_maybe_fp8(x, w, b)
+    lora = getattr(w, "_lora", None)       # policy.lora.LoraRef: low-rank path of an adapted projection
+    return y if lora is None else lora.apply(x, y)
 
 
 class Attention(nn.Module):

@@ -88,6 +88,8 @@ def load_hf_state(model, read, available, cfg: Dict[str, Any], tp: int = 1, r: i
     missing = []
     with torch.no_grad():
         for name, p in model.named_parameters():
+            if ".lora_" in name:               # adapters are not part of the base checkpoint
+                continue
             if hasattr(mapper, "load_param") and mapper.load_param(name, p, read, available, tp, r):
                 continue
             hf_names = mapper.hf_names(name)
@@ -134,6 +136,8 @@ def hf_state_dict(model, hf_config: Dict[str, Any]) -> Dict[str, torch.Tensor]:
     if hasattr(model, "export_items"):
         return {k: v.detach() for k, v in model.export_items()}
     for name, p in model.named_parameters():
+        if ".lora_" in name:
+            continue
         for hf_name, piece in _split_fused(name, p.detach(), mapper, hf_config, a.n_heads, a.n_kv_heads, a.head_dim):
             out[hf_name] = piece
     return out
@@ -181,6 +185,8 @@ def export_safetensors(model, hf_config: Dict[str, Any], output_dir: str, parall
     export_items = model.export_items() if hasattr(model, "export_items") else None
     named = export_items if export_items is not None else list(model.named_parameters())
     for name, p in named:
+        if ".lora_" in name:                   # adapters are exported separately (adapter_model.safetensors)
+            continue
         t = p.detach()
         pieces = _split_fused(name, t, mapper, hf_config, hq, hkv, d) if export_items is None else [(name, t)]
         for hf_name, piece in pieces:

@@ -90,6 +90,26 @@ class FlatAdamW:
         self.step_count = 0
         self.last_grad_norm: Optional[torch.Tensor] = None
         self.trainable = flat.trainable_mask()
+        # frozen parameters must not even decay: the update runs over the trainable stretches of this rank's shard only
+        self.segments = None
+        if self.trainable is not None:
+            self.segments = self._trainable_segments(self.lo, self.hi)
+            self.tail_segments = self._trainable_segments(self.t0, self.t1) if self.t1 > self.t0 else []
+
+    def _trainable_segments(self, lo: int, hi: int):
+        """[(start, end)] relative to ``lo``: maximal runs of trainable parameter slots inside [lo, hi)."""
+        segs = []
+        for (name, p), slot in sorted(zip(self.flat.params, self.flat.slots), key=lambda t: t[1].offset):
+            if not p.requires_grad:
+                continue
+            a, b = max(slot.offset, lo), min(slot.offset + slot.numel, hi)
+            if a >= b:
+                continue
+            if segs and segs[-1][1] == a - lo:
+                segs[-1] = (segs[-1][0], b - lo)
+            else:
+                segs.append((a - lo, b - lo))
+        return segs
 
     # ------------------------------------------------------------------
     def refresh_master_from_params(self) -> None:
@@ -165,17 +185,21 @@ class FlatAdamW:
         norm, coef = K.clip_coef_from_sumsq(sumsq, self.max_grad_norm)
         hp = dict(lr=self.lr * lr_scale, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps,
                   weight_decay=self.wd, step=self.step_count, grad_scale=coef)
-        if fused:
+        segs = self.segments if self.segments is not None else [(0, self.hi - self.lo)]
+        if fused and self.segments is None:
             self.collective.adamw_publish(self.master, self.m, self.v, g, self.lo, self.hi, **hp)
         else:
             shadow = self.flat.data[self.lo:self.hi]
-            K.adamw_flat(self.master, self.m, self.v, g, shadow, **hp)
+            for a, b in segs:
+                K.adamw_flat(self.master[a:b], self.m[a:b], self.v[a:b], g[a:b], shadow[a:b], **hp)
             if self.world > 1:
                 dist.all_gather_into_tensor(self.flat.data[:self.t0], shadow.clone(), group=self.group)
         if self.tail is not None:
             hp_t = dict(hp, grad_scale=coef / float(self.world))
-            K.adamw_flat(self.tail["master"], self.tail["m"], self.tail["v"], self.flat.grad[self.t0:self.t1],
-                         self.flat.data[self.t0:self.t1], **hp_t)
+            gt, dt_ = self.flat.grad[self.t0:self.t1], self.flat.data[self.t0:self.t1]
+            for a, b in (self.tail_segments if self.segments is not None else [(0, self.t1 - self.t0)]):
+                K.adamw_flat(self.tail["master"][a:b], self.tail["m"][a:b], self.tail["v"][a:b], gt[a:b], dt_[a:b],
+                             **hp_t)
         self.last_grad_norm = norm
         return norm
 

@@ -37,6 +37,12 @@ class Trainer(ABC):
     def step_validation(self, *a, **kw) -> Dict[str, Any]:
         return {}
 
+    def before_weight_sync(self) -> None:
+        """Called before the weights are handed to a rollout replica (LoRA folds its adapters in)."""
+
+    def after_weight_sync(self) -> None:
+        pass
+
     @abstractmethod
     def export_safetensors(self, output_dir: str, **kw) -> None: ...
 

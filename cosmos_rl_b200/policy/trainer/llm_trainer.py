@@ -58,13 +58,24 @@ class LLMTrainer(Trainer):
         # the model stays on the meta device here: FlatParams materialises every parameter as a view of
         # one flat buffer, so no second copy of the weights is ever allocated
         self.model = model
-        self._apply_trainable_patterns()
+        self.lora_targets: List[str] = []
+        if config.policy.lora is not None:
+            # adapters become parameters of the projections before the flat buffer is laid out; the base is frozen
+            from .. import lora
+            if tp > 1 or not hasattr(model, "layers"):
+                raise NotImplementedError("policy.lora needs a native model and tp_size == 1")
+            self.lora_targets = lora.attach_lora(model, config.policy.lora)
+        else:
+            self._apply_trainable_patterns()
         dp = parallel_dims.dp_shard
         is_expert = (lambda n: n.endswith("w_gate_up") or n.endswith("w_down")) if ep > 1 else None
         self.flat = FlatParams(model, self.param_dtype, self.device, shard_multiple=dp,
                                allocator=kw.get("allocator"), local_filter=is_expert)
         if ep > 1:
             model.set_ep_group(parallel_dims.group("dp_shard"))
+        if self.lora_targets:
+            from .. import lora
+            lora.bind_lora(model)
         rc = config.b200.recompute if config.policy.model_gradient_checkpointing else "none"
         self._recompute_auto = rc == "auto"
         model.gradient_checkpointing = {"none": False, "auto": "selective"}.get(rc, rc)
@@ -172,8 +183,24 @@ class LLMTrainer(Trainer):
             else:
                 self.model.init_weights(seed)
             logger.info("[Policy] no checkpoint at %r: random-init weights from seed %d", path, seed)
+        if self.lora_targets:
+            from .. import lora
+            lora.reset_lora_parameters(self.model, self.config.train.seed or 0)
         self.optimizer.refresh_master_from_params()
         self.weights_ready = True
+
+    # ------------------------------------------------------------------ adapters around weight hand-over
+    def before_weight_sync(self) -> None:
+        """Rollout replicas receive plain dense weights: adapters are folded into the base weights for the duration of
+        a policy-to-rollout transfer (cosmos_rl/policy/worker/rl_worker.py:455-466, 548-551)."""
+        if self.lora_targets:
+            from .. import lora
+            lora.merge_native(self.model)
+
+    def after_weight_sync(self) -> None:
+        if self.lora_targets:
+            from .. import lora
+            lora.unmerge_native(self.model)
 
     def model_resume_from_checkpoint(self) -> bool:
         state = self.ckpt_manager.load_latest(self.device)
@@ -214,6 +241,17 @@ class LLMTrainer(Trainer):
 
     def export_safetensors(self, output_dir: str, **kw) -> None:
         from ...models import hf_io
+        if self.lora_targets:
+            # LoRA run: the export is the adapter in PEFT layout (adapter_model.safetensors + adapter_config.json)
+            import json
+            from safetensors.torch import save_file
+            from .. import lora
+            if self.parallel_dims.global_rank == 0:
+                os.makedirs(output_dir, exist_ok=True)
+                save_file(lora.native_adapter_state_dict(self.model), os.path.join(output_dir, "adapter_model.safetensors"))
+                with open(os.path.join(output_dir, "adapter_config.json"), "w") as f:
+                    json.dump(lora.adapter_config(self.config.policy.lora, self.lora_targets), f, indent=1)
+            return
         hf_io.export_safetensors(self.model, self.hf_config, output_dir, self.parallel_dims,
                                  source_dir=self.config.policy.model_name_or_path)
 

@@ -149,6 +149,13 @@ class RLPolicyWorker(CommMixin):
         if self.replica_name != c.src_replica_name:
             return False
         self.post_shard_infos()
+        self.trainer.before_weight_sync()
+        try:
+            return self._serve_weights(c)
+        finally:
+            self.trainer.after_weight_sync()
+
+    def _serve_weights(self, c: cmd.PolicyToRolloutUnicastCommand) -> bool:
         if self.device.type == "cuda":
             torch.cuda.synchronize()
         key = f"p2r:{c.uuid_value}"

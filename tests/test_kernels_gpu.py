@@ -597,7 +597,8 @@ def test_mxfp4_quant_matches_reference_bit_for_bit(rows, cols, swizzle):
     assert torch.equal(q, rq) and torch.equal(sf, rsf)
     back = F.dequant_mxfp4(q, sf, swizzle)
     assert torch.equal(back.float(), R.dequant_mxfp4(rq, rsf, swizzle).to(torch.bfloat16).float())
-    # every element is within half a quantisation step of its block: the largest gap of the E2M1 grid is 2 scales
+    # error bound: the grid's largest gap is 2 scales (half of it when rounding), and a block maximum just under
+    # 8 scales saturates at 6 scales
     blk = w.float().view(rows, cols // 32, 32)
     scale = torch.exp2(torch.floor(torch.log2(blk.abs().amax(-1).clamp_min(1e-30))) - 2)
-    assert ((back.float().view(rows, cols // 32, 32) - blk).abs() <= scale[..., None] * 1.0 + 1e-30).all()
+    assert ((back.float().view(rows, cols // 32, 32) - blk).abs() <= scale[..., None] * 2.0 + 1e-30).all()

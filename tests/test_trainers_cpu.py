@@ -118,3 +118,52 @@ def test_grpo_trainer_with_reference_kl_mu_iterations_and_variants(tmp_path):
         if ref0 is not None:
             assert torch.equal(job.trainer.reference_state, ref0)
             assert rep["train/kl"] >= 0.0
+
+
+def test_lora_on_native_model_through_the_trainer(tmp_path):
+    """[policy.lora] on the native GPT: adapters on the fused projections, base weights frozen, merge / unmerge around
+    weight hand-over, PEFT-layout export with the fused adapters split back."""
+    import os
+    import torch
+    from safetensors.torch import load_file
+    from cosmos_rl_b200.policy import lora
+    from cosmos_rl_b200.policy.trainer.sft_trainer import SFTTrainer
+    c = _config(tmp_path, "sft")
+    c = Config.from_dict({**c.model_dump(), "policy": {**c.policy.model_dump(),
+                          "lora": {"r": 4, "lora_alpha": 8, "target_modules": ["q_proj", "v_proj", "down_proj"]}}})
+    tr = SFTTrainer(c, ParallelDims(world_size=1, device=torch.device("cpu")), device=torch.device("cpu"))
+    tr.model_load_from_hf()
+    assert tr.lora_targets == ["layers.0.self_attn.qkv_proj", "layers.0.mlp.down_proj",
+                               "layers.1.self_attn.qkv_proj", "layers.1.mlp.down_proj"]
+    trainable = [n for n, p in tr.model.named_parameters() if p.requires_grad]
+    assert trainable and all(".lora_" in n for n in trainable)
+    g = torch.Generator().manual_seed(0)
+    ids, cu = torch.randint(0, 32000, (20,), generator=g), torch.tensor([0, 8, 20])
+    fwd = lambda: tr.model(ids, tr.model.get_position_ids(cu, 20), cu, 12).detach()
+    with lora.adapters_disabled(tr.model):
+        base_out = fwd()
+    assert torch.equal(fwd(), base_out)                                  # B = 0: the adapted model is the base model
+    base_w = {n: p.detach().clone() for n, p in tr.model.named_parameters() if ".lora_" not in n}
+    batch = [{"input_ids": torch.randint(0, 32000, (n,), generator=g).tolist()} for n in (12, 20, 7, 16)]
+    losses = [tr.step_training(batch, total_steps=10, train_step=i + 1)["train/loss_avg"] for i in range(5)]
+    assert losses[-1] < losses[0]
+    for n, p in tr.model.named_parameters():
+        if ".lora_" not in n:
+            assert torch.equal(p, base_w[n]), n                          # the base never moves
+    qkv = tr.model.layers[0].self_attn.qkv_proj
+    a = tr.model.args
+    k_rows = slice(a.n_heads * a.head_dim, (a.n_heads + a.n_kv_heads) * a.head_dim)
+    assert qkv.lora_B.abs().sum() > 0 and (qkv.weight._lora.delta()[k_rows] == 0).all()   # k_proj was not targeted
+    out = fwd()
+    assert not torch.allclose(out, base_out, atol=1e-4)
+    tr.before_weight_sync()                                              # merged: dense weights carry the adapters
+    assert not torch.equal(qkv.weight, base_w["layers.0.self_attn.qkv_proj.weight"])
+    assert torch.allclose(fwd(), out, atol=1e-4)
+    tr.after_weight_sync()
+    assert torch.allclose(qkv.weight, base_w["layers.0.self_attn.qkv_proj.weight"], atol=1e-6)
+    tr.export_safetensors(str(tmp_path / "adapter"))
+    sd = load_file(os.path.join(str(tmp_path / "adapter"), "adapter_model.safetensors"))
+    q = "base_model.model.model.layers.0.self_attn.q_proj.lora_B.weight"
+    assert q in sd and sd[q].shape == (a.n_heads * a.head_dim, 4)
+    assert "base_model.model.model.layers.0.self_attn.v_proj.lora_A.weight" in sd
+    assert not any("k_proj" in k or "gate_proj" in k for k in sd) and any("down_proj" in k for k in sd)
