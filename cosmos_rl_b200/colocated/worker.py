@@ -100,6 +100,7 @@ class ColocatedRLControlWorker:
                 self.trainer.after_weight_sync()
         for p, r in zip(payloads, results):
             p.completions = r.completions
+            p.completed_conversations = r.completed_conversations
             if r.completion_token_ids is not None:
                 p.completion_token_ids = [[[t] for t in toks] for toks in r.completion_token_ids]
                 p.completion_logprobs = [[[l] for l in lps] for lps in r.completion_logprobs]

@@ -103,7 +103,20 @@ class DecoderOnlyLLMDataPacker(BaseDataPacker):
     def get_rollout_input(self, item):
         return self._encode_prompt(item)
 
+    def extend_conversation(self, conversation, response: str, ground_truth=None):
+        """Multi-turn rollouts: append the response (and the results of its tool calls). Returns (conversation,
+        finished)."""
+        from .multi_turn import extend_conversation
+        mt = self.config.rollout.multi_turn_config
+        return extend_conversation(conversation, response, mt.enable_tools)
+
     def get_policy_input(self, sample, rollout_output, n_ignore_prefix_tokens: int = 0, **kw):
+        if isinstance(rollout_output, (list, tuple)) and rollout_output and isinstance(rollout_output[0], dict):
+            # a completed multi-turn conversation: every assistant turn is scored, the rest is context
+            from .multi_turn import ToolRegistry, assistant_token_mask
+            tools = ToolRegistry.schemas() if self.config.rollout.multi_turn_config.enable_tools else None
+            ids, m = assistant_token_mask(self.tokenizer, list(rollout_output), tools)
+            return self.PolicyInput(ids, m[1:] + [0])       # mask[i] == 1 <=> token i + 1 is scored
         p = self._encode_prompt(sample)
         c = self._encode_completion(rollout_output)
         n_ign = min(n_ignore_prefix_tokens, len(c))

@@ -47,7 +47,9 @@ class GRPOTrainer(LLMTrainer):
         out = []
         for r in rollouts:
             comp = r.completion
-            if r.completion_token_ids:
+            if r.completed_conversation:
+                comp = r.completed_conversation        # multi-turn: the packer scores every assistant turn
+            elif r.completion_token_ids:
                 comp = [pos[0] for pos in r.completion_token_ids]
             pi = self.data_packer.get_policy_input(r.prompt, comp, r.n_ignore_prefix_tokens)
             lp = None

@@ -60,12 +60,50 @@ class B200Rollout(RolloutBase):
     def get_underlying_model(self):
         return self.model
 
+    def rollout_generation_multi_turn(self, payloads, data_packer, sp: SamplingParams) -> List[RolloutResult]:
+        """Every (prompt, sample) pair is its own conversation path; all live paths of a turn are generated in one
+        engine call, then each response is appended and its tool calls are executed
+        (cosmos_rl/rollout/vllm_rollout/vllm_rollout.py:768-955 walks one conversation at a time)."""
+        mt = self.config.rollout.multi_turn_config
+        if self.tokenizer is None:
+            raise RuntimeError("multi-turn rollouts need a tokenizer with a chat template")
+        n = max(1, sp.n)
+        one = copy.copy(sp)
+        one.n = 1
+        paths = []
+        for pi, p in enumerate(payloads):
+            conv = p.conversation if p.conversation is not None else p.prompt
+            if isinstance(conv, str):
+                conv = [{"role": "user", "content": conv}]
+            for _ in range(n):
+                paths.append({"payload": pi, "conv": list(conv), "done": False, "turns": 0, "last": ""})
+        for _ in range(mt.max_assistant_turns):
+            live = [q for q in paths if not q["done"]]
+            if not live:
+                break
+            prompts = [data_packer.get_rollout_input(q["conv"]) for q in live]
+            outs = self.engine.generate(prompts, one)
+            for q, comps in zip(live, outs):
+                text = self.tokenizer.decode(comps[0].token_ids, skip_special_tokens=True)
+                q["conv"], q["done"] = data_packer.extend_conversation(q["conv"], text, payloads[q["payload"]].reference_answer)
+                q["turns"] += 1
+                q["last"] = text
+        results = []
+        for pi, p in enumerate(payloads):
+            mine = [q for q in paths if q["payload"] == pi]
+            results.append(RolloutResult(prompt=p.prompt, completions=[q["last"] for q in mine],
+                                         completed_conversations=[q["conv"] for q in mine],
+                                         extra_info={"assistant_turns": [q["turns"] for q in mine]}))
+        return results
+
     def rollout_generation(self, payloads, data_packer, data_fetcher=None, is_validation: bool = False, **kw
                            ) -> List[RolloutResult]:
         sp = SamplingParams.from_config(self.config, validation=is_validation)
         eos = getattr(self.tokenizer, "eos_token_id", None)
         if eos is not None:
             sp.stop_token_ids = (eos,)
+        if self.config.rollout.multi_turn_config.enable:
+            return self.rollout_generation_multi_turn(payloads, data_packer, sp)
         prompts = [data_packer.get_rollout_input(p.prompt) for p in payloads]
         outs = self.engine.generate(prompts, sp)
         results = []

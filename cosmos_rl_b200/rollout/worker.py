@@ -256,13 +256,17 @@ class DisaggregatedRolloutControlWorker(CommMixin):
         reporter = self.parallel_dims.tp_coord == 0 and self.parallel_dims.pp_coord == self.parallel_dims.pp - 1
         for p, r in zip(payloads, results):
             p.completions = r.completions
-            p.completion_token_ids = [[[t] for t in toks] for toks in r.completion_token_ids]
-            if self.config.train.train_policy.collect_rollout_logprobs or \
-                    self.config.train.train_policy.use_rollout_logprobs_for_loss:
-                p.completion_logprobs = [[[l] for l in lps] for lps in r.completion_logprobs]
+            p.completed_conversations = r.completed_conversations      # multi-turn paths (None otherwise)
+            if r.extra_info is not None:
+                p.extra_info = r.extra_info
+            if r.completion_token_ids is not None:
+                p.completion_token_ids = [[[t] for t in toks] for toks in r.completion_token_ids]
+                if self.config.train.train_policy.collect_rollout_logprobs or \
+                        self.config.train.train_policy.use_rollout_logprobs_for_loss:
+                    p.completion_logprobs = [[[l] for l in lps] for lps in r.completion_logprobs]
+                self.stats["generated_tokens"] += sum(len(t) for t in r.completion_token_ids)
             p.cumulative_logprob = r.cumulative_logprob
             p.weight_version = self.current_weight_version
-            self.stats["generated_tokens"] += sum(len(t) for t in r.completion_token_ids)
         self.stats["batches"] += 1
         if reporter:
             self.reward_dispatcher.enqueue_rewards_cal(payloads)
