@@ -516,10 +516,51 @@ def fp8_linear(x: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor) -> torch.Ten
     return gemm_fp8_block(xq, xs, wq, ws)
 
 
+class _Fp8TrainLinear(torch.autograd.Function):
+    """``y = x @ w^T`` with all three GEMMs of the layer on the block-scaled fp8 kernel: activations and output
+    gradients are quantised 1 x 128 along the contraction axis of the GEMM they enter, weights (and the second
+    operand of the weight-gradient GEMM) 128 x 128. bf16 copies of x and w are what is saved, so memory matches bf16
+    training (train.fp8: cosmos_rl/utils/fp8/fp8_util.py:139-153 does this through torchao row-wise scaling)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        xq, xs = quant_fp8_block(x.contiguous(), 1)
+        wq, ws = quant_fp8_block(w.contiguous(), 128)
+        return gemm_fp8_block(xq, xs, wq, ws).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, w = ctx.saved_tensors
+        gy = gy.contiguous()
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gq, gs = quant_fp8_block(gy, 1)                           # along N
+            wtq, wts = quant_fp8_block(w.t().contiguous(), 128)       # [K, N]
+            gx = gemm_fp8_block(gq, gs, wtq, wts).to(x.dtype)
+        if ctx.needs_input_grad[1]:
+            if x.shape[0] % 16 == 0:
+                gtq, gts = quant_fp8_block(gy.t().contiguous(), 1)    # [N, M], along the token axis
+                xtq, xts = quant_fp8_block(x.t().contiguous(), 128)   # [K, M]
+                gw = gemm_fp8_block(gtq, gts, xtq, xts).to(w.dtype)
+            else:                                                     # ragged token count: 16-byte rows are needed
+                gw = gy.t() @ x
+        return gx, gw
+
+
+def fp8_train_supported(w: torch.Tensor) -> bool:
+    """Both dimensions of the weight are contraction axes of one of the three GEMMs: they must give 16-byte rows."""
+    return w.dim() == 2 and w.shape[0] % 16 == 0 and w.shape[1] % 16 == 0
+
+
 def linear_maybe_fp8(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x @ w^T + b``. A weight that carries block-scaled fp8 data (``w._fp8 = (e4m3 [N, K], scales)``, attached
-    by the rollout's fp8 weight store) is used through the fp8 GEMM in inference; everything else is the bf16
+    by the rollout's fp8 weight store) is used through the fp8 GEMM in inference; a weight marked ``_fp8_train`` (by
+    the trainer, ``train.fp8.enable_fp8``) runs forward and both backward GEMMs in fp8; everything else is the bf16
     library GEMM."""
+    if getattr(w, "_fp8_train", False) and x.dtype in (torch.bfloat16, torch.float32):
+        y = _Fp8TrainLinear.apply(x.reshape(-1, x.shape[-1]), w).view(*x.shape[:-1], w.shape[0])
+        return y if b is None else y + b
     f8 = getattr(w, "_fp8", None)
     if f8 is not None and x.is_cuda and not torch.is_grad_enabled() and x.dtype == torch.bfloat16:
         y = fp8_linear(x.reshape(-1, x.shape[-1]), f8[0], f8[1]).view(*x.shape[:-1], f8[0].shape[0])

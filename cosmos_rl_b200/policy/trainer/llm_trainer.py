@@ -76,6 +76,16 @@ class LLMTrainer(Trainer):
         if self.lora_targets:
             from .. import lora
             lora.bind_lora(model)
+        self.n_fp8_weights = 0
+        if config.train.fp8.enable_fp8:
+            # every projection of the blocks runs its three GEMMs on the block-scaled fp8 kernel; embeddings, norms and
+            # lm_head stay in bf16 (cosmos_rl/policy/model/gpt/__init__.py:795-797 excludes lm_head too). All recipes
+            # of the reference map to block scaling here: 1 x 128 activations, 128 x 128 weights.
+            from ...ops.functional import fp8_train_supported
+            for name, p in model.named_parameters():
+                if name.startswith("layers.") and name.endswith("_proj.weight") and fp8_train_supported(p):
+                    p._fp8_train = True
+                    self.n_fp8_weights += 1
         rc = config.b200.recompute if config.policy.model_gradient_checkpointing else "none"
         self._recompute_auto = rc == "auto"
         model.gradient_checkpointing = {"none": False, "auto": "selective"}.get(rc, rc)

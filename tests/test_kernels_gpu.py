@@ -602,3 +602,23 @@ def test_mxfp4_quant_matches_reference_bit_for_bit(rows, cols, swizzle):
     blk = w.float().view(rows, cols // 32, 32)
     scale = torch.exp2(torch.floor(torch.log2(blk.abs().amax(-1).clamp_min(1e-30))) - 2)
     assert ((back.float().view(rows, cols // 32, 32) - blk).abs() <= scale[..., None] * 2.0 + 1e-30).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(1024, 4608, 3584), (304, 256, 1040)])
+def test_fp8_training_linear_on_gpu(M, N, K):
+    """All three GEMMs of a projection on the block-scaled fp8 kernel against the exact fp32 products."""
+    torch.manual_seed(6)
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(N, K, device="cuda") * 0.03).to(torch.bfloat16).requires_grad_(True)
+    w._fp8_train = True
+    go = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+    y = F.linear_maybe_fp8(x, w)
+    y.backward(go)
+    torch.cuda.synchronize()
+    assert native.read_status(x.device) == 0
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    (xr @ wr.t()).backward(go.float())
+    rel = lambda a, b: ((a.float() - b).norm() / b.norm()).item()
+    assert rel(y.detach(), (xr @ wr.t()).detach()) < 0.05
+    assert rel(x.grad, xr.grad) < 0.05 and rel(w.grad, wr.grad) < 0.05
