@@ -13,7 +13,13 @@ is the only layer that mixes positions. Two exchanges are provided:
   what a ring schedule would stream past this rank. Gradients of the gathered K/V flow back through a
   reduce-scatter. On GPUs the attention call is the tcgen05 kernel, which takes separate query/key offsets.
 
-Both are autograd functions over ``torch.distributed`` collectives, so they run on NCCL and (for tests) on gloo.
+* ``ring``: K/V chunks travel around the ring one hop per step (point-to-point send / receive posted before the
+  attention call on the chunk that is already here, so the transfer hides behind the math); every step yields a
+  partial output and its log-sum-exp, merged on the fly. Only one foreign K/V chunk is resident at a time, so the
+  key length per GPU stays ``T / cp`` however long the sequences are. The backward pass runs the ring again: each
+  step's dK/dV chunk is computed from the global log-sum-exp and handed on to its owner.
+
+All are autograd functions over ``torch.distributed`` collectives, so they run on NCCL and (for tests) on gloo.
 """
 from __future__ import annotations
 
@@ -160,15 +166,134 @@ def kv_gather_attention(q, k, v, cu_local, max_local: int, group, scale: Optiona
     return _attention(q, kg, vg, cu_local, cu_k, max_local, scale)
 
 
+# ------------------------------------------------------------------------------------------------ ring
+def _fwd_with_lse(q, k, v, cu, max_len: int, scale: float, causal: bool):
+    """(out fp32-mergeable, lse [h, T] natural log) of one chunk pair; equal query and key segmentation."""
+    if q.is_cuda:
+        from ..ops import attention
+        if attention.native_flash_supported(q, k, v):
+            i32 = cu if cu.dtype == torch.int32 else cu.to(torch.int32)
+            return attention.flash_fwd(q, k, v, i32, i32, max_len, scale, causal)
+    return reference.varlen_attention(q, k, v, cu, scale, causal, None, return_lse=True)
+
+
+def _bwd_from_lse(dout, q, k, v, out, lse, cu, max_len: int, scale: float, causal: bool):
+    """Gradients of one chunk pair given the GLOBAL output and log-sum-exp of the queries (the probabilities of this
+    chunk are exp(s - lse), the softmax correction term is rowsum(dout * out) over the whole row)."""
+    if q.is_cuda:
+        from ..ops import attention
+        if attention.native_flash_supported(q, k, v):
+            i32 = cu if cu.dtype == torch.int32 else cu.to(torch.int32)
+            return attention.flash_bwd(dout, q, k, v, out, lse, i32, max_len, scale, causal=causal)
+    hq, hkv = q.shape[1], k.shape[1]
+    g = hq // hkv
+    dq, dk, dv = torch.zeros_like(q, dtype=torch.float32), torch.zeros_like(k, dtype=torch.float32), \
+        torch.zeros_like(v, dtype=torch.float32)
+    cs = cu.tolist()
+    for s, e in zip(cs[:-1], cs[1:]):
+        if e <= s:
+            continue
+        qi = q[s:e].float().transpose(0, 1)                               # [hq, L, d]
+        ki = k[s:e].float().transpose(0, 1).repeat_interleave(g, dim=0)
+        vi = v[s:e].float().transpose(0, 1).repeat_interleave(g, dim=0)
+        do, o = dout[s:e].float().transpose(0, 1), out[s:e].float().transpose(0, 1)
+        sc = (qi @ ki.transpose(-1, -2)) * scale
+        if causal:
+            L = e - s
+            sc = sc.masked_fill(~torch.ones(L, L, dtype=torch.bool, device=q.device).tril(), float("-inf"))
+        p = torch.exp(sc - lse[:, s:e, None])
+        delta = (do * o).sum(-1, keepdim=True)
+        ds = p * (do @ vi.transpose(-1, -2) - delta)
+        dq[s:e] = ((ds @ ki) * scale).transpose(0, 1)
+        dk[s:e] = ((ds.transpose(-1, -2) @ qi) * scale).view(hkv, g, e - s, -1).sum(1).transpose(0, 1)
+        dv[s:e] = (p.transpose(-1, -2) @ do).view(hkv, g, e - s, -1).sum(1).transpose(0, 1)
+    return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
+
+
+def _ring_exchange(send: torch.Tensor, group, cp: int, rank: int):
+    """Post send-to-next / receive-from-previous; returns (recv buffer, requests)."""
+    recv = torch.empty_like(send)
+    nxt, prv = dist.get_global_rank(group, (rank + 1) % cp), dist.get_global_rank(group, (rank - 1) % cp)
+    ops = [dist.P2POp(dist.isend, send, nxt, group), dist.P2POp(dist.irecv, recv, prv, group)]
+    return recv, dist.batch_isend_irecv(ops)
+
+
+class _RingAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_local, max_local, group, scale):
+        cp, rank = dist.get_world_size(group), dist.get_rank(group)
+        d = q.shape[-1]
+        scale = scale if scale is not None else d ** -0.5
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        kv = torch.stack([k, v])                                           # one message per hop
+        out = lse = None
+        for step in range(cp):
+            src = (rank - step) % cp                                       # owner of the chunk held now
+            if step < cp - 1:
+                nxt_kv, reqs = _ring_exchange(kv, group, cp, rank)         # in flight during the attention below
+            if src <= rank:                                                # later chunks are entirely in the future
+                o_j, lse_j = _fwd_with_lse(q, kv[0], kv[1], cu_local, max_local, scale, causal=(src == rank))
+                o_j = o_j.float()
+                if out is None:
+                    out, lse = o_j, lse_j
+                else:
+                    new = torch.logaddexp(lse, lse_j)
+                    wa, wb = torch.exp(lse - new), torch.exp(lse_j - new)  # [h, T]
+                    out = out * wa.t()[..., None] + o_j * wb.t()[..., None]
+                    lse = new
+            if step < cp - 1:
+                for r_ in reqs:
+                    r_.wait()
+                kv = nxt_kv
+        out = out.to(q.dtype)
+        ctx.save_for_backward(q, k, v, out, lse, cu_local)
+        ctx.group, ctx.max_local, ctx.scale = group, max_local, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse, cu_local = ctx.saved_tensors
+        group = ctx.group
+        cp, rank = dist.get_world_size(group), dist.get_rank(group)
+        dout = dout.contiguous()
+        dq = torch.zeros_like(q, dtype=torch.float32)
+        kv = torch.stack([k, v])
+        dkv = torch.zeros_like(kv, dtype=torch.float32)                    # gradient of the chunk held now
+        for step in range(cp):
+            src = (rank - step) % cp
+            if step < cp - 1:
+                nxt_kv, reqs = _ring_exchange(kv, group, cp, rank)
+            if src <= rank:
+                dq_j, dk_j, dv_j = _bwd_from_lse(dout, q, kv[0], kv[1], out, lse, cu_local, ctx.max_local, ctx.scale,
+                                                 causal=(src == rank))
+                dq += dq_j.float()
+                dkv[0] += dk_j.float()
+                dkv[1] += dv_j.float()
+            # the gradient travels with its chunk: after cp hops in total it is back at the owner
+            nxt_dkv, greqs = _ring_exchange(dkv, group, cp, rank)
+            if step < cp - 1:
+                for r_ in reqs:
+                    r_.wait()
+                kv = nxt_kv
+            for r_ in greqs:
+                r_.wait()
+            dkv = nxt_dkv
+        return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None, None, None, None
+
+
+def ring_attention(q, k, v, cu_local, max_local: int, group, scale: Optional[float] = None):
+    return _RingAttention.apply(q, k, v, cu_local, max_local, group, scale)
+
+
 class ContextParallel:
     """Attached to a model as ``model.cp``; the attention layer calls ``attention`` instead of the local kernel."""
 
     def __init__(self, group, size: int, rank: int, mode: str = "kv-gather"):
-        assert mode in ("kv-gather", "ulysses")
+        assert mode in ("kv-gather", "ulysses", "ring")
         self.group, self.size, self.rank, self.mode = group, size, rank, mode
 
     def attention(self, q, k, v, cu_local, max_local: int, scale: Optional[float] = None):
-        fn = ulysses_attention if self.mode == "ulysses" else kv_gather_attention
+        fn = {"ulysses": ulysses_attention, "ring": ring_attention}.get(self.mode, kv_gather_attention)
         return fn(q, k, v, cu_local, max_local, self.group, scale)
 
     def shard(self, x, cu_seqlens):

@@ -54,9 +54,14 @@ def _cp_worker(rank, world, store, mode):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["kv-gather", "ulysses"])
+@pytest.mark.parametrize("mode", ["kv-gather", "ulysses", "ring"])
 def test_context_parallel_matches_full_model(tmp_path, mode):
     _spawn(_cp_worker, 2, tmp_path, mode)
+
+
+def test_ring_attention_on_four_ranks(tmp_path):
+    """K/V chunks pass three hops, their gradients four; chunks from the future are skipped."""
+    _spawn(_cp_worker, 4, tmp_path, "ring")
 
 
 def _pp_worker(rank, world, store):
