@@ -432,6 +432,7 @@ class B200Config(_Section):
     fused_logprob: bool = True           # tcgen05 fused lm_head + log-prob kernel
     nvls: bool = True                    # allow multimem (NVSwitch) reductions where available
     dlogits_chunk: int = 16384
+    cp_mode: str = "kv-gather"           # context-parallel attention exchange: kv-gather | ring | ulysses
     sequence_parallel: bool = True       # with tp_size > 1 (dense models, no pp / cp): residual stream and norms hold
                                          # T / tp rows; projections run all-gather -> GEMM / GEMM -> reduce-scatter
     router_bias_update_rate: float = 1e-3  # DeepSeek-V3 load-balancing bias step per optimizer step (0 = frozen)

@@ -54,13 +54,15 @@ class FlatAdamW:
                  master_dtype: torch.dtype = torch.float32, collective=None,
                  replicate_group: Optional[dist.ProcessGroup] = None,
                  tp_group: Optional[dist.ProcessGroup] = None, tp_replicated: Optional[torch.Tensor] = None,
-                 norm_groups=()):
+                 norm_groups=(), sum_groups=()):
         """``dp_group`` shards optimizer state (ZeRO-2 style); ``replicate_group`` is the outer data-parallel axis of
         HSDP / DDP (cosmos_rl/policy/model/gpt/parallelize.py:80-113, 426-442): ranks of it hold the same shard and
         average their reduced gradient shard before the update, so the all-reduce moves 1/dp_shard of the gradient."""
         # gradient norm under model parallelism: parameters sharded over ``tp_group`` contribute once per rank, the
         # ones every tensor-parallel rank holds (``tp_replicated``: bool mask over the flat buffer) only once;
         # ``norm_groups`` are further groups whose ranks hold disjoint parameters (pipeline stages)
+        # ``sum_groups``: ranks that hold partial gradients of the SAME samples (context-parallel chunks): summed
+        self.sum_groups = tuple(g for g in sum_groups if g is not None)
         self.tp_group, self.norm_groups = tp_group, tuple(norm_groups)
         self.tp_replicated = tp_replicated
         self.flat = flat
@@ -147,6 +149,13 @@ class FlatAdamW:
             g = self.grad_shard
         else:
             g = self._reduce_grads()
+            sumsq = K.grad_sumsq([g])
+        if self.sum_groups:
+            g32 = g if g.dtype == torch.float32 else g.to(torch.float32)
+            for grp in self.sum_groups:
+                dist.all_reduce(g32, group=grp)
+            if g32 is not g:
+                g.copy_(g32)
             sumsq = K.grad_sumsq([g])
         if self.n_replicas > 1:
             if g.dtype != torch.float32:           # dp_shard == 1: the shard is the bf16 gradient buffer itself

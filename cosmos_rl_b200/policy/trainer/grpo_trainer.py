@@ -73,6 +73,13 @@ class GRPOTrainer(LLMTrainer):
         pad_mult = self.parallel_dims.cp * self.parallel_dims.tp
         b = pack_sequences([s.ids for s in samples], [s.mask for s in samples], device=self.device,
                            pad_multiple=1 if pad_mult == 1 else pad_mult)
+        rlp_full = None
+        if all(s.rollout_lp is not None and len(s.rollout_lp) == s.n_scored for s in samples):
+            flat = [x for s in samples for x in s.rollout_lp]
+            rlp_full = torch.zeros(b["label_ids"].numel(), dtype=torch.float32, device=self.device)
+            rlp_full[(b["label_ids"] >= 0)] = torch.tensor(flat, dtype=torch.float32, device=self.device)
+        cu_full = b["cu_seqlens"]
+        b = self.cp_shard(b)
         sel = (b["label_ids"] >= 0).nonzero(as_tuple=True)[0]
         b["sel"] = sel
         b["labels_sel"] = b["label_ids"][sel]
@@ -80,9 +87,11 @@ class GRPOTrainer(LLMTrainer):
         adv = torch.tensor([s.advantage for s in samples], dtype=torch.float32, device=self.device)
         b["adv_tok"] = adv[b["seq_ids_sel"]]
         b["seq_rewards"] = torch.tensor([s.reward for s in samples], dtype=torch.float32, device=self.device)
-        if all(s.rollout_lp is not None and len(s.rollout_lp) == s.n_scored for s in samples):
-            flat = [x for s in samples for x in s.rollout_lp]
-            b["rollout_lp"] = torch.tensor(flat, dtype=torch.float32, device=self.device)
+        if rlp_full is not None:
+            if self.parallel_dims.cp > 1:
+                from ...parallel.context_parallel import split_for_cp
+                rlp_full = split_for_cp(rlp_full, cu_full, self.parallel_dims.cp, self.parallel_dims.cp_coord)
+            b["rollout_lp"] = rlp_full[sel]
         return b
 
     def _forward_logprobs(self, b: Dict[str, Any]):
@@ -123,6 +132,9 @@ class GRPOTrainer(LLMTrainer):
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record()
         self.total_steps = total_steps
+        if self.parallel_dims.cp > 1 and (self.loss_cfg.loss_type != "token-mean" or self.loss_cfg.variant == "gspo"):
+            raise NotImplementedError("context parallelism supports the token-mean loss (per-sequence reductions would "
+                                      "need sums across the cp ranks)")
         samples = self._prepare(rollouts)
         n = len(samples)
         per_opt = self.tp_cfg.batch_size_per_optimize or n
@@ -151,7 +163,7 @@ class GRPOTrainer(LLMTrainer):
 
         for it in range(mu):
             for ci, batches in enumerate(chunk_batches):
-                tok = torch.tensor(float(sum(int(b["sel"].numel()) for b in batches)), device=self.device)
+                tok = torch.tensor(float(sum(b["n_scored"] for b in batches)), device=self.device)
                 if self.tp_cfg.balance_dp_token and dp_world > 1:
                     dist.all_reduce(tok, group=self.parallel_dims.group("dp_shard"))
                     tok = tok / dp_world

@@ -95,6 +95,12 @@ class LLMTrainer(Trainer):
             from ...models.gpt import GPT
             model.tp.sequence_parallel = bool(config.b200.sequence_parallel and type(model) is GPT
                                               and parallel_dims.pp == 1 and parallel_dims.cp == 1)
+        if parallel_dims.cp > 1:
+            if not hasattr(model, "attach_context_parallel") or tp > 1 or parallel_dims.pp > 1:
+                raise NotImplementedError("cp_size > 1 needs a native model with tp_size == pp_size == 1")
+            from ...parallel.context_parallel import ContextParallel
+            model.attach_context_parallel(ContextParallel(parallel_dims.group("cp"), parallel_dims.cp,
+                                                          parallel_dims.cp_coord, config.b200.cp_mode))
         from ...utils.extension import parallelism_strategy
         custom_plan = parallelism_strategy(mt)
         if custom_plan is not None:
@@ -113,6 +119,7 @@ class LLMTrainer(Trainer):
             weight_decay=config.train.optm_weight_decay, max_grad_norm=config.train.optm_grad_norm_clip,
             tp_group=parallel_dims.group("tp") if tp > 1 else None, tp_replicated=tp_mask,
             norm_groups=[parallel_dims.group("pp")] if parallel_dims.pp > 1 else [],
+            sum_groups=[parallel_dims.group("cp")] if parallel_dims.cp > 1 else [],
             dp_group=parallel_dims.group("dp_shard") if dp > 1 else None, collective=kw.get("collective"),
             replicate_group=parallel_dims.group("dp_replicate") if parallel_dims.dp_replicate > 1 else None)
         self.data_packer = data_packer or BaseDataPacker.get_default(mt)()
@@ -174,6 +181,16 @@ class LLMTrainer(Trainer):
             dims = self.parallel_dims
             self.model.update_router_bias(rate, dims.group("dp_shard") if dims.dp_shard > 1 else None)
         return norm
+
+    def cp_shard(self, b: Dict[str, Any]) -> Dict[str, Any]:
+        """Under context parallelism: keep this rank's chunk of every sequence of a packed batch; the number of scored
+        tokens of the whole batch is kept for the loss normalisation (gradients are summed over the cp ranks)."""
+        b["n_scored"] = int((b["label_ids"] >= 0).sum())
+        dims = self.parallel_dims
+        if dims.cp == 1:
+            return b
+        from ...utils.sequence_packing import shard_packed
+        return shard_packed(b, dims.cp, dims.cp_coord)
 
     def lr_scale(self, step: int) -> float:
         t = self.config.train

@@ -23,6 +23,7 @@ class SFTTrainer(LLMTrainer):
                   for i in range(len(s["input_ids"]))] for s in samples]
         b = pack_sequences(seqs, masks, device=self.device,
                            pad_multiple=max(1, self.parallel_dims.cp * self.parallel_dims.tp))
+        b = self.cp_shard(b)
         sel = (b["label_ids"] >= 0).nonzero(as_tuple=True)[0]
         b["sel"], b["labels_sel"] = sel, b["label_ids"][sel]
         return b
@@ -49,7 +50,7 @@ class SFTTrainer(LLMTrainer):
         for p in processed:
             p["input_ids"], p["label_ids"] = p["input_ids"][:max_len], p["label_ids"][:max_len]
         packed = [self._pack([processed[i] for i in idxs]) for idxs in self._batches(processed)]
-        tok = torch.tensor(float(sum(int(b["sel"].numel()) for b in packed)), device=self.device)
+        tok = torch.tensor(float(sum(b["n_scored"] for b in packed)), device=self.device)
         dp = self.parallel_dims.dp_shard
         if dp > 1 and getattr(self.config.train.train_policy, "balance_dp_token", True):
             dist.all_reduce(tok, group=self.parallel_dims.group("dp_shard"))
@@ -71,6 +72,8 @@ class SFTTrainer(LLMTrainer):
         if do_save:
             self.save_checkpoint(train_step, total_steps, is_final=train_step >= total_steps)
         loss_sum = torch.stack(losses).sum()
+        if self.parallel_dims.cp > 1:                       # every cp rank saw a part of every sequence
+            dist.all_reduce(loss_sum, group=self.parallel_dims.group("cp"))
         return {"train/loss_avg": float(loss_sum), "train/loss_max": float(loss_sum),
                 "train/learning_rate": self.optimizer.lr * self.lr_scale(max(train_step - 1, 0)),
                 "train/iteration_time": time.perf_counter() - t0, "train/grad_norm": float(norm),
@@ -81,9 +84,11 @@ class SFTTrainer(LLMTrainer):
         self.model.eval()
         processed = [self.data_packer.sft_process_sample(s) for s in batch]
         packed = [self._pack([processed[i] for i in idxs]) for idxs in self._batches(processed)]
-        tok = torch.tensor(float(sum(int(b["sel"].numel()) for b in packed)), device=self.device).clamp_min(1.0)
-        loss = sum(float(self._loss_on(b, tok)) for b in packed)
-        return {"val/loss": loss}
+        tok = torch.tensor(float(sum(b["n_scored"] for b in packed)), device=self.device).clamp_min(1.0)
+        loss = torch.tensor(sum(float(self._loss_on(b, tok)) for b in packed), device=self.device)
+        if self.parallel_dims.cp > 1:
+            dist.all_reduce(loss, group=self.parallel_dims.group("cp"))
+        return {"val/loss": float(loss)}
 
     def __init__(self, config, parallel_dims, **kw):
         self.inter_replica = kw.pop("inter_replica", None)

@@ -476,3 +476,60 @@ def _tp_trainer_worker(rank, world, store, out_dir):
 
 def test_sft_trainer_with_tensor_and_sequence_parallelism(tmp_path):
     _spawn(_tp_trainer_worker, 2, tmp_path, str(tmp_path))
+
+
+def _cp_trainer_worker(rank, world, store, out_dir, mode):
+    """SFT and GRPO trainers with cp_size = 2: same loss, gradient norm and weights as single-process trainers."""
+    from cosmos_rl_b200.config import Config
+    from cosmos_rl_b200.dispatcher.data.schema import Rollout
+    from cosmos_rl_b200.parallel.dims import ParallelDims
+    from cosmos_rl_b200.policy.trainer.grpo_trainer import GRPOTrainer
+    from cosmos_rl_b200.policy.trainer.sft_trainer import SFTTrainer
+    _init(rank, world, store)
+
+    def cfg(cp, kind):
+        return Config.from_dict({
+            "policy": {"model_name_or_path": "tiny-qwen2", "model_max_length": 64, "model_gradient_checkpointing": False,
+                       "parallelism": {"cp_size": cp, "dp_shard_size": 1, "tp_size": 1}},
+            "b200": {"cp_mode": mode},
+            "train": {"seed": 0, "optm_lr": 1e-3, "optm_warmup_steps": 0, "output_dir": out_dir, "optm_grad_norm_clip": 0.5,
+                      "train_policy": {"type": kind, "trainer_type": kind, "mini_batch": 4},
+                      "ckpt": {"enable_checkpoint": False}}})
+    cpu = torch.device("cpu")
+    dims = ParallelDims.from_config_parallelism(cfg(2, "sft").policy.parallelism, world, rank, cpu)
+    dims.build_groups()
+    one = ParallelDims(world_size=1, device=cpu)
+    g = torch.Generator().manual_seed(3)
+    batch = [{"input_ids": torch.randint(0, 32000, (n,), generator=g).tolist()} for n in (12, 9, 15, 7)]
+    tr, ref = SFTTrainer(cfg(2, "sft"), dims, device=cpu), SFTTrainer(cfg(1, "sft"), one, device=cpu)
+    for t in (tr, ref):
+        t.model_load_from_hf()                                   # same seed: identical weights
+    assert tr.model.layers[0].self_attn.cp.mode == mode
+    for i in range(2):
+        a = tr.step_training(batch, total_steps=10, train_step=i + 1)
+        b = ref.step_training(batch, total_steps=10, train_step=i + 1)
+        assert abs(a["train/loss_avg"] - b["train/loss_avg"]) < 1e-4, (a["train/loss_avg"], b["train/loss_avg"])
+        assert abs(a["train/grad_norm"] - b["train/grad_norm"]) < 1e-3 * b["train/grad_norm"]
+    assert torch.allclose(tr.flat.data, ref.flat.data, atol=5e-4)
+    # GRPO: rollouts with behaviour log-probs (exercises the sharding of per-token side inputs)
+    ros = []
+    for i in range(4):
+        n = [6, 11, 4, 9][i]
+        toks = torch.randint(0, 32000, (n,), generator=g).tolist()
+        ros.append(Rollout(prompt=torch.randint(0, 32000, (5 + i,), generator=g).tolist(), completion=toks,
+                           advantage=[0.5, -1.0, 1.5, -0.2][i], reward=float(i),
+                           completion_token_ids=[[t] for t in toks], completion_logprobs=[[-10.3 - 0.01 * j] for j in range(n)]))
+    gt, gref = GRPOTrainer(cfg(2, "grpo"), dims, device=cpu), GRPOTrainer(cfg(1, "grpo"), one, device=cpu)
+    for t in (gt, gref):
+        t.model_load_from_hf()
+        t.tp_cfg.use_rollout_logprobs_for_loss = True
+    a = gt.step_training(ros, 1, 10)
+    b = gref.step_training(ros, 1, 10)
+    assert abs(a["train/grad_norm"] - b["train/grad_norm"]) < 1e-3 * b["train/grad_norm"], (a["train/grad_norm"], b["train/grad_norm"])
+    assert torch.allclose(gt.flat.data, gref.flat.data, atol=5e-4)
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["kv-gather", "ring"])
+def test_trainers_with_context_parallelism(tmp_path, mode):
+    _spawn(_cp_trainer_worker, 2, tmp_path, str(tmp_path), mode)
