@@ -103,3 +103,24 @@ class PipelineStage:
         for w in pending:
             w.wait()
         return losses
+
+    @torch.no_grad()
+    def forward_only(self, micro_batches: Sequence[MicroBatch], fn: Optional[Callable] = None) -> List[Any]:
+        """Fill-drain forward pass without gradients (old / reference log-probs, validation: the reference uses a
+        GPipe schedule there). Returns ``fn(hidden, micro_batch)`` per micro-batch on the last stage, ``[]`` elsewhere."""
+        first, last = self.stage == 0, self.stage == self.n - 1
+        outs: List[Any] = []
+        pending: List[Any] = []
+        keep: List[torch.Tensor] = []
+        for mb in micro_batches:
+            x = mb.input_ids if first else self._recv(mb.tokens, self.prev)
+            out = self.model(x, mb.position_ids, mb.cu_seqlens, mb.max_seqlen)
+            if last:
+                outs.append(fn(out, mb) if fn is not None else out)
+            else:
+                send = out.contiguous()
+                keep.append(send)
+                pending.append(dist.isend(send, dst=self.next, group=self.group))
+        for w in pending:
+            w.wait()
+        return outs

@@ -94,13 +94,17 @@ class GRPOTrainer(LLMTrainer):
             b["rollout_lp"] = rlp_full[sel]
         return b
 
+    def _logprobs_of(self, hidden, b: Dict[str, Any]):
+        return self.model.logprobs(hidden[b["sel"]], b["labels_sel"], self.temperature)
+
     def _forward_logprobs(self, b: Dict[str, Any]):
         hidden = self.model(b["input_ids"], b["position_ids"], b["cu_seqlens"], b["max_seqlen"])
-        return self.model.logprobs(hidden[b["sel"]], b["labels_sel"], self.temperature)
+        return self._logprobs_of(hidden, b)
 
     @torch.no_grad()
     def _compute_logprobs_nograd(self, batches: List[Dict[str, Any]]) -> List[torch.Tensor]:
-        return [self._forward_logprobs(b)[0].detach() for b in batches]
+        """Per-batch log-probs without gradients (on the last stage only under pipeline parallelism)."""
+        return self.run_batches_nograd(batches, lambda h, i, b: self._logprobs_of(h, b)[0].detach())
 
     # ------------------------------------------------------------------ reference policy (KL)
     def _swap_flat(self, other: torch.Tensor) -> torch.Tensor:
@@ -170,8 +174,10 @@ class GRPOTrainer(LLMTrainer):
                 if self.inter_replica is not None and self.tp_cfg.balance_dp_token:
                     tok = self.inter_replica.balance_token_count(tok)
                 self.optimizer.zero_grad()
-                for bi, b in enumerate(batches):
-                    lp, ent = self._forward_logprobs(b)
+                n_seq_total = max(1, sum(len(x["seq_rewards"]) for x in batches))
+
+                def loss_of(hidden, bi, b, ci=ci, tok=tok, n_seq_total=n_seq_total):
+                    lp, ent = self._logprobs_of(hidden, b)
                     if use_rollout_lp and "rollout_lp" in b:
                         old = b["rollout_lp"]
                     elif old_lps is not None:
@@ -184,11 +190,12 @@ class GRPOTrainer(LLMTrainer):
                         rollout_logprob=b.get("rollout_lp"), entropy=ent, seq_rewards=b["seq_rewards"],
                         total_tokens=tok if self.loss_cfg.loss_type == "token-mean" else None)
                     if self.loss_cfg.loss_type != "token-mean":
-                        loss = loss * (len(b["seq_rewards"]) / max(1, sum(len(x["seq_rewards"]) for x in batches)))
-                    loss.backward()
-                    losses.append(loss.detach())
+                        loss = loss * (len(b["seq_rewards"]) / n_seq_total)
                     for k, v in m.items():
                         metrics_acc.setdefault(k, []).append(v.detach())
+                    return loss
+
+                losses.extend(self.run_batches_train(batches, loss_of))
                 if self.inter_replica is not None:
                     self.inter_replica.all_reduce_grads(self.flat.grad)
                 grad_norms.append(self.optimizer_step())
@@ -210,8 +217,9 @@ class GRPOTrainer(LLMTrainer):
             iter_time = time.perf_counter() - t0
         loss_t = torch.stack(losses) if losses else torch.zeros(1, device=self.device)
         n_mb = max(1, len(losses) // max(1, len(chunks) * mu))
+        loss_sum = self.pp_sum(loss_t.sum().clone())             # only the last pipeline stage has the losses
         report = {
-            "train/loss_avg": float(loss_t.sum() / max(1, len(chunks) * mu)),
+            "train/loss_avg": float(loss_sum / max(1, len(chunks) * mu)),
             "train/loss_max": float(loss_t.max() * n_mb),
             "train/learning_rate": self.optimizer.lr * self.lr_scale(max(self.train_step - 1, 0)),
             "train/iteration_time": iter_time,

@@ -51,6 +51,8 @@ class LLMTrainer(Trainer):
             if ep != parallel_dims.dp_shard or parallel_dims.cp > 1:
                 raise NotImplementedError("expert parallelism needs ep_size == dp_shard_size and cp_size == 1")
             build_kw = dict(ep_size=ep, ep_rank=parallel_dims.dp_shard_coord)
+        if parallel_dims.pp > 1:
+            build_kw.update(pp_size=parallel_dims.pp, pp_rank=parallel_dims.pp_coord)
         with torch.device("meta"):
             model = ModelRegistry.build_model(self.hf_config, tp_size=tp, tp_rank=parallel_dims.tp_coord, **build_kw)
         if ep > 1 and not hasattr(model, "set_ep_group"):
@@ -101,6 +103,13 @@ class LLMTrainer(Trainer):
             from ...parallel.context_parallel import ContextParallel
             model.attach_context_parallel(ContextParallel(parallel_dims.group("cp"), parallel_dims.cp,
                                                           parallel_dims.cp_coord, config.b200.cp_mode))
+        self.pipeline = None
+        if parallel_dims.pp > 1:
+            if not hasattr(getattr(model, "args", None), "pp_size") or tp > 1:
+                raise NotImplementedError("pp_size > 1 needs a native model and tp_size == 1")
+            from ...parallel.pipeline import PipelineStage
+            self.pipeline = PipelineStage(model, parallel_dims.group("pp"), parallel_dims.pp_coord, parallel_dims.pp,
+                                          model.args.dim, self.param_dtype, self.device)
         from ...utils.extension import parallelism_strategy
         custom_plan = parallelism_strategy(mt)
         if custom_plan is not None:
@@ -181,6 +190,39 @@ class LLMTrainer(Trainer):
             dims = self.parallel_dims
             self.model.update_router_bias(rate, dims.group("dp_shard") if dims.dp_shard > 1 else None)
         return norm
+
+    # ------------------------------------------------------------------ running packed batches (with or without pp)
+    def _micro(self, batches):
+        from ...parallel.pipeline import MicroBatch
+        return [MicroBatch(b["input_ids"], b["position_ids"], b["cu_seqlens"], b["max_seqlen"], extra=(i, b))
+                for i, b in enumerate(batches)]
+
+    def run_batches_train(self, batches, loss_of) -> List[torch.Tensor]:
+        """Forward + backward over packed batches; ``loss_of(hidden, index, batch) -> scalar`` (already scaled for
+        accumulation). With pipeline stages the batches are the micro-batches of a 1F1B schedule and the loss is
+        evaluated on the last stage only; the returned (detached) losses are empty on the other stages."""
+        if self.pipeline is not None:
+            return self.pipeline.run(self._micro(batches), lambda h, mb: loss_of(h, mb.extra[0], mb.extra[1]))
+        losses = []
+        for i, b in enumerate(batches):
+            loss = loss_of(self.model(b["input_ids"], b["position_ids"], b["cu_seqlens"], b["max_seqlen"]), i, b)
+            loss.backward()
+            losses.append(loss.detach())
+        return losses
+
+    @torch.no_grad()
+    def run_batches_nograd(self, batches, fn) -> List[Any]:
+        """``fn(hidden, index, batch)`` per packed batch without gradients (last stage only under pp)."""
+        if self.pipeline is not None:
+            return self.pipeline.forward_only(self._micro(batches), lambda h, mb: fn(h, mb.extra[0], mb.extra[1]))
+        return [fn(self.model(b["input_ids"], b["position_ids"], b["cu_seqlens"], b["max_seqlen"]), i, b)
+                for i, b in enumerate(batches)]
+
+    def pp_sum(self, value: torch.Tensor) -> torch.Tensor:
+        """A value only the last stage has (losses, metrics): summed over the stages so every rank reports it."""
+        if self.pipeline is not None:
+            dist.all_reduce(value, group=self.parallel_dims.group("pp"))
+        return value
 
     def cp_shard(self, b: Dict[str, Any]) -> Dict[str, Any]:
         """Under context parallelism: keep this rank's chunk of every sequence of a packed batch; the number of scored

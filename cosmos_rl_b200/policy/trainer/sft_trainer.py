@@ -36,10 +36,11 @@ class SFTTrainer(LLMTrainer):
         mb = max(1, tp.mini_batch)
         return [list(range(i, min(i + mb, len(processed)))) for i in range(0, len(processed), mb)]
 
-    def _loss_on(self, b, total_tokens):
-        hidden = self.model(b["input_ids"], b["position_ids"], b["cu_seqlens"], b["max_seqlen"])
-        lp, _ = self.model.logprobs(hidden[b["sel"]], b["labels_sel"], 1.0)
-        return sft_ce_loss(lp, total_tokens)
+    def _loss_of(self, total_tokens):
+        def loss_of(hidden, i, b):
+            lp, _ = self.model.logprobs(hidden[b["sel"]], b["labels_sel"], 1.0)
+            return sft_ce_loss(lp, total_tokens)
+        return loss_of
 
     def step_training(self, global_batch: Sequence[Any], total_steps: int, train_step: int, save_freq: int = 0,
                       do_save: bool = False, **kw) -> Dict[str, Any]:
@@ -60,18 +61,14 @@ class SFTTrainer(LLMTrainer):
             tok = inter.balance_token_count(tok)
         self.model.train()
         self.optimizer.zero_grad()
-        losses = []
-        for b in packed:
-            loss = self._loss_on(b, tok.clamp_min(1.0))
-            loss.backward()
-            losses.append(loss.detach())
+        losses = self.run_batches_train(packed, self._loss_of(tok.clamp_min(1.0)))
         if inter is not None:
             inter.all_reduce_grads(self.flat.grad)
         norm = self.optimizer_step()
         self.train_step = train_step
         if do_save:
             self.save_checkpoint(train_step, total_steps, is_final=train_step >= total_steps)
-        loss_sum = torch.stack(losses).sum()
+        loss_sum = self.pp_sum(torch.stack(losses).sum() if losses else torch.zeros((), device=self.device))
         if self.parallel_dims.cp > 1:                       # every cp rank saw a part of every sequence
             dist.all_reduce(loss_sum, group=self.parallel_dims.group("cp"))
         return {"train/loss_avg": float(loss_sum), "train/loss_max": float(loss_sum),
@@ -85,7 +82,8 @@ class SFTTrainer(LLMTrainer):
         processed = [self.data_packer.sft_process_sample(s) for s in batch]
         packed = [self._pack([processed[i] for i in idxs]) for idxs in self._batches(processed)]
         tok = torch.tensor(float(sum(b["n_scored"] for b in packed)), device=self.device).clamp_min(1.0)
-        loss = torch.tensor(sum(float(self._loss_on(b, tok)) for b in packed), device=self.device)
+        loss = self.pp_sum(torch.tensor(float(sum(float(x) for x in self.run_batches_nograd(packed, self._loss_of(tok)))),
+                                        device=self.device))
         if self.parallel_dims.cp > 1:
             dist.all_reduce(loss, group=self.parallel_dims.group("cp"))
         return {"val/loss": float(loss)}

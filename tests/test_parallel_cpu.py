@@ -533,3 +533,77 @@ def _cp_trainer_worker(rank, world, store, out_dir, mode):
 @pytest.mark.parametrize("mode", ["kv-gather", "ring"])
 def test_trainers_with_context_parallelism(tmp_path, mode):
     _spawn(_cp_trainer_worker, 2, tmp_path, str(tmp_path), mode)
+
+
+def _pp_trainer_worker(rank, world, store, out_dir):
+    """SFT and GRPO trainers with pp_size = 2 (1F1B over the packed mini-batches): same loss, gradient norm and
+    weights as the single-process trainers."""
+    from cosmos_rl_b200.config import Config
+    from cosmos_rl_b200.dispatcher.data.schema import Rollout
+    from cosmos_rl_b200.models import hf_io
+    from cosmos_rl_b200.parallel.dims import ParallelDims
+    from cosmos_rl_b200.policy.trainer.grpo_trainer import GRPOTrainer
+    from cosmos_rl_b200.policy.trainer.sft_trainer import SFTTrainer
+    _init(rank, world, store)
+
+    def cfg(pp, kind):
+        return Config.from_dict({
+            "policy": {"model_name_or_path": "tiny-qwen2", "model_max_length": 64, "model_gradient_checkpointing": False,
+                       "parallelism": {"pp_size": pp, "dp_shard_size": 1, "tp_size": 1}},
+            "train": {"seed": 0, "optm_lr": 1e-3, "optm_warmup_steps": 0, "output_dir": out_dir, "optm_grad_norm_clip": 0.5,
+                      "train_policy": {"type": kind, "trainer_type": kind, "mini_batch": 2},
+                      "ckpt": {"enable_checkpoint": False}}})
+    cpu = torch.device("cpu")
+    dims = ParallelDims.from_config_parallelism(cfg(2, "sft").policy.parallelism, world, rank, cpu)
+    dims.build_groups()
+    one = ParallelDims(world_size=1, device=cpu)
+
+    def same_weights(stage_tr, ref_tr):
+        hf_cfg = ref_tr.model.args.to_hf_config()
+        state = hf_io.hf_state_dict(ref_tr.model, hf_cfg)
+        hf_io.load_hf_state(stage_tr.model, lambda k: state[k], state, hf_cfg)
+        stage_tr.optimizer.refresh_master_from_params()
+        stage_tr.weights_ready = True
+
+    def check_weights(stage_tr, ref_tr):
+        ref_p = dict(ref_tr.model.named_parameters())
+        off = stage_tr.model.layer_offset
+        for n, p in stage_tr.model.named_parameters():
+            if n.startswith("layers."):
+                i, rest = n[len("layers."):].split(".", 1)
+                n = f"layers.{int(i) + off}.{rest}"
+            assert torch.allclose(p, ref_p[n], atol=5e-4), (n, (p - ref_p[n]).abs().max())
+
+    g = torch.Generator().manual_seed(3)
+    batch = [{"input_ids": torch.randint(0, 32000, (n,), generator=g).tolist()} for n in (12, 9, 15, 7, 10, 6)]
+    tr, ref = SFTTrainer(cfg(2, "sft"), dims, device=cpu), SFTTrainer(cfg(1, "sft"), one, device=cpu)
+    ref.model_load_from_hf()
+    same_weights(tr, ref)
+    assert len(tr.model.layers) == 1 and (tr.model.embed_tokens is None) == (rank == 1)
+    for i in range(2):
+        a = tr.step_training(batch, total_steps=10, train_step=i + 1)          # 3 micro-batches through 2 stages
+        b = ref.step_training(batch, total_steps=10, train_step=i + 1)
+        assert abs(a["train/loss_avg"] - b["train/loss_avg"]) < 1e-4, (a["train/loss_avg"], b["train/loss_avg"])
+        assert abs(a["train/grad_norm"] - b["train/grad_norm"]) < 1e-3 * b["train/grad_norm"]
+    check_weights(tr, ref)
+    assert abs(tr.step_validation(batch)["val/loss"] - ref.step_validation(batch)["val/loss"]) < 1e-4
+    ros = []
+    for i in range(4):
+        n = [6, 11, 4, 9][i]
+        ros.append(Rollout(prompt=torch.randint(0, 32000, (5 + i,), generator=g).tolist(),
+                           completion=torch.randint(0, 32000, (n,), generator=g).tolist(),
+                           advantage=[0.5, -1.0, 1.5, -0.2][i], reward=float(i)))
+    gt, gref = GRPOTrainer(cfg(2, "grpo"), dims, device=cpu), GRPOTrainer(cfg(1, "grpo"), one, device=cpu)
+    gref.model_load_from_hf()
+    same_weights(gt, gref)
+    for t in (gt, gref):
+        t.tp_cfg.mu_iterations = 2                         # old log-probs come from the forward-only pipeline pass
+    a, b = gt.step_training(ros, 1, 10), gref.step_training(ros, 1, 10)
+    assert abs(a["train/grad_norm"] - b["train/grad_norm"]) < 1e-3 * b["train/grad_norm"], (a["train/grad_norm"], b["train/grad_norm"])
+    assert abs(a["train/loss_avg"] - b["train/loss_avg"]) < 1e-5
+    check_weights(gt, gref)
+    dist.destroy_process_group()
+
+
+def test_trainers_with_pipeline_parallelism(tmp_path):
+    _spawn(_pp_trainer_worker, 2, tmp_path, str(tmp_path))
