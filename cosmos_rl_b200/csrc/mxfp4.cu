@@ -8,6 +8,7 @@
 //                the scale of (row r, block c) sits at (r % 32) * 16 + (r / 32) * 4 + c. This is the interleaving the
 //                tcgen05 block-scaled MMA reads scale factors in (one 32-lane x 16-byte TMEM column group per tile).
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -21,10 +22,6 @@ __device__ __forceinline__ long long sf_index(int r, int cb, int n_cb, int swizz
   const long long tile = (long long)(r / 128) * tiles_c + cb / 4;
   const int rr = r % 128;
   return tile * 512 + (rr % 32) * 16 + (rr / 32) * 4 + (cb % 4);
-}
-
-__device__ __forceinline__ uint32_t e2m1_code(float a) {   // |x| / scale -> 3-bit magnitude code, round-to-nearest-even
-  return (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) + (a >= 3.5f) + (a > 5.0f);
 }
 
 // Work item = 8 consecutive elements (one 16-byte load, one 4-byte store); the 4 lanes of a 32-element block share
@@ -60,12 +57,20 @@ __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const __nv_bfloat16* _
     int ex = amax > 0.f ? (int)((__float_as_uint(amax) >> 23) & 0xff) - 127 - 2 : -127;
     ex = max(-127, min(127, ex));
     const float inv = __uint_as_float((uint32_t)(127 - ex) << 23);   // 2^-ex: exponent field 2..254 for finite input
-    uint32_t w = 0;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const float s = f[k] * inv;
-      w |= (e2m1_code(fabsf(s)) | (s < 0.f ? 8u : 0u)) << (4 * k);
-    }
+    // eight scaled values -> four e2m1x2 bytes with the sm_100a conversion instruction (round to nearest even,
+    // saturating at 6); the first source operand lands in the high nibble
+    uint32_t w;
+    asm("{\n"
+        ".reg .b8 b0, b1, b2, b3;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+        "mov.b32 %0, {b0, b1, b2, b3};\n"
+        "}"
+        : "=r"(w)
+        : "f"(f[0] * inv), "f"(f[1] * inv), "f"(f[2] * inv), "f"(f[3] * inv), "f"(f[4] * inv), "f"(f[5] * inv),
+          "f"(f[6] * inv), "f"(f[7] * inv));
     if (valid) {
       reinterpret_cast<uint32_t*>(q)[i] = w;                // packed output is dense: item i = word i
       if (part == 0) sf[sf_index((int)r, (int)cb, n_cb, swizzle)] = (uint8_t)(ex + 127);
@@ -87,15 +92,23 @@ __global__ void __launch_bounds__(256) dequant_mxfp4_kernel(const uint8_t* __res
     const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(q) + i);
     const int eb = sf[sf_index((int)r, (int)cb, n_cb, swizzle)];
     const float scale = eb == 0 ? 5.877471754e-39f : __uint_as_float((uint32_t)eb << 23);   // 2^(eb - 127)
-    __align__(16) __nv_bfloat16 o[8];
+    // four e2m1x2 bytes -> four f16x2 pairs with the sm_100a conversion instruction (low nibble first), then scale
+    uint32_t h[4];
+    asm("{\n"
+        ".reg .b8 b0, b1, b2, b3;\n"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
+        "}"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+        : "r"(w));
+    __align__(16) __nv_bfloat162 o[4];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const uint32_t c = (w >> (4 * k)) & 0xf;
-      // E2M1 magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6: codes 0/1 are the subnormal pair, the rest (1 + m/2) * 2^(e-1)
-      const uint32_t m = c & 7;
-      const float mag = m < 2 ? 0.5f * (float)m : (1.f + 0.5f * (float)(m & 1)) * (float)(1 << ((m >> 1) - 1));
-      const float val = mag * scale;
-      o[k] = __float2bfloat16((c & 8) ? -val : val);
+    for (int k = 0; k < 4; ++k) {
+      const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&h[k]));
+      o[k] = __floats2bfloat162_rn(v2.x * scale, v2.y * scale);
     }
     *reinterpret_cast<uint4*>(out + (long long)r * ldo + cb * 32 + part * 8) = *reinterpret_cast<const uint4*>(o);
   }
