@@ -30,35 +30,34 @@ __device__ __forceinline__ long long sf_index(int r, int cb, int n_cb, int swizz
 __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                                                            uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int R,
                                                            int C, int swizzle) {
-  const int n_cb = C / 32;
-  const long long total = (long long)R * n_cb * 4;           // multiple of 4: the lanes of a block stay together
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  const int lane = threadIdx.x & 31;
+  const uint32_t n_cb = (uint32_t)C / 32;
+  const uint32_t total = (uint32_t)R * n_cb * 4;               // items of 8 elements; < 2^32 (checked by the launcher)
+  const uint32_t stride = gridDim.x * blockDim.x;
+  const uint32_t lane = threadIdx.x & 31;
   // the loop condition is warp-uniform (first lane's index): every lane reaches the full-mask shuffles below
-  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x - lane; i0 < total; i0 += stride) {
-    const long long i = i0 + lane;
+  for (uint32_t i0 = blockIdx.x * blockDim.x + threadIdx.x - lane; i0 < total; i0 += stride) {
+    const uint32_t i = i0 + lane;
     const bool valid = i < total;
-    const uint32_t blk = (uint32_t)(i >> 2);                // block index fits 32 bits (checked by the launcher)
-    const int part = (int)(i & 3);
-    const uint32_t r = blk / (uint32_t)n_cb, cb = blk - r * (uint32_t)n_cb;   // 32-bit divide: 64-bit costs 5x more
+    const uint32_t blk = i >> 2, part = i & 3;
+    const uint32_t r = blk / n_cb, cb = blk - r * n_cb;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (valid) v = __ldg(reinterpret_cast<const uint4*>(x + (long long)r * ldx + cb * 32 + part * 8));
-    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
-    float f[8], amax = 0.f;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      f[k] = __bfloat162float(e[k]);
-      amax = fmaxf(amax, fabsf(f[k]));
-    }
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+    // block maximum of |x| on packed bf16 pairs (sign bits cleared), then across the 4 lanes of the block
+    const uint32_t a4[4] = {w4[0] & 0x7fff7fffu, w4[1] & 0x7fff7fffu, w4[2] & 0x7fff7fffu, w4[3] & 0x7fff7fffu};
+    const __nv_bfloat162* ab = reinterpret_cast<const __nv_bfloat162*>(a4);
+    const __nv_bfloat162 m2 = __hmax2(__hmax2(ab[0], ab[1]), __hmax2(ab[2], ab[3]));
+    uint32_t mb = *reinterpret_cast<const uint32_t*>(&m2);
+    uint32_t amax_bits = max(mb & 0xffffu, mb >> 16);             // non-negative bf16 bit patterns order like integers
+    amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, 1));
+    amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, 2));
     // shared exponent: floor(log2(amax)) - 2 (the largest E2M1 magnitude is 6 = 1.5 * 2^2); zero / denormal blocks
-    // take the smallest scale
-    int ex = amax > 0.f ? (int)((__float_as_uint(amax) >> 23) & 0xff) - 127 - 2 : -127;
+    // take the smallest scale. bf16 keeps the fp32 exponent field in bits 7..14.
+    int ex = (amax_bits >> 7) ? (int)(amax_bits >> 7) - 127 - 2 : -127;
     ex = max(-127, min(127, ex));
     const float inv = __uint_as_float((uint32_t)(127 - ex) << 23);   // 2^-ex: exponent field 2..254 for finite input
     // eight scaled values -> four e2m1x2 bytes with the sm_100a conversion instruction (round to nearest even,
-    // saturating at 6); the first source operand lands in the high nibble
+    // saturating at 6); the first source operand lands in the high nibble. bf16 -> fp32 is a 16-bit shift.
     uint32_t w;
     asm("{\n"
         ".reg .b8 b0, b1, b2, b3;\n"
@@ -69,11 +68,13 @@ __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const __nv_bfloat16* _
         "mov.b32 %0, {b0, b1, b2, b3};\n"
         "}"
         : "=r"(w)
-        : "f"(f[0] * inv), "f"(f[1] * inv), "f"(f[2] * inv), "f"(f[3] * inv), "f"(f[4] * inv), "f"(f[5] * inv),
-          "f"(f[6] * inv), "f"(f[7] * inv));
+        : "f"(__uint_as_float(w4[0] << 16) * inv), "f"(__uint_as_float(w4[0] & 0xffff0000u) * inv),
+          "f"(__uint_as_float(w4[1] << 16) * inv), "f"(__uint_as_float(w4[1] & 0xffff0000u) * inv),
+          "f"(__uint_as_float(w4[2] << 16) * inv), "f"(__uint_as_float(w4[2] & 0xffff0000u) * inv),
+          "f"(__uint_as_float(w4[3] << 16) * inv), "f"(__uint_as_float(w4[3] & 0xffff0000u) * inv));
     if (valid) {
       reinterpret_cast<uint32_t*>(q)[i] = w;                // packed output is dense: item i = word i
-      if (part == 0) sf[sf_index((int)r, (int)cb, n_cb, swizzle)] = (uint8_t)(ex + 127);
+      if (part == 0) sf[sf_index((int)r, (int)cb, (int)n_cb, swizzle)] = (uint8_t)(ex + 127);
     }
   }
 }
@@ -122,7 +123,7 @@ extern "C" {
 // even element), sf E8M0 bytes (layout by `swizzle`; the swizzled buffer holds ceil(R/128) * ceil(C/128) * 512 bytes).
 int b200_quant_mxfp4(const void* x, long long ldx, void* q, void* sf, int R, int C, int swizzle, cudaStream_t stream) {
   if (R <= 0 || C <= 0) return 0;
-  if (C % 32 != 0 || ldx % 8 != 0 || (long long)R * (C / 32) >= (1ll << 31)) return B200_ERR_ARG;
+  if (C % 32 != 0 || ldx % 8 != 0 || (long long)R * (C / 32) >= (1ll << 29)) return B200_ERR_ARG;
   const long long total = (long long)R * (C / 32) * 4;
   const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   quant_mxfp4_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, (uint8_t*)sf, R, C, swizzle);
