@@ -50,6 +50,13 @@ class CommMixin:
         if self.world_size > 1:
             dist.barrier()
         if self.global_rank == 0:
+            if constant.COSMOS_HEARTBEAT_PROCESS and hasattr(self.api, "base_urls"):
+                # a separate process keeps reporting while this one sits in a long native call that holds the
+                # interpreter; it is killed by the kernel when this process dies, so a dead worker falls silent
+                from .heartbeat_process import start_heartbeat_process
+                self._heartbeat_proc = start_heartbeat_process(self.api.base_urls, self.replica_name,
+                                                               constant.COSMOS_HEARTBEAT_SEND_INTERVAL)
+                return
             t = threading.Thread(target=self._heartbeat_loop, name="heartbeat", daemon=True)
             t.start()
             self._threads.append(t)

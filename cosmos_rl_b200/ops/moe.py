@@ -173,3 +173,51 @@ def moe_experts(x: torch.Tensor, probs: torch.Tensor, idx: torch.Tensor, w_gate_
     if x.is_cuda:
         return _MoEExperts.apply(x, probs, idx, w_gate_up, w_down, counts)
     return moe_experts_reference(x, probs, idx, w_gate_up, w_down)
+
+
+# ---------------------------------------------------------------------------------------------- index utilities
+def indices_to_multihot(idx: torch.Tensor, probs: torch.Tensor, n_experts: int):
+    """Top-k ``idx [T, k]`` / ``probs [T, k]`` -> dense ``(mask [T, E] bool, weights [T, E])``; negative indices are
+    padding (the layout dense dispatchers take; cosmos_rl/policy/kernel/megatron_moe/fused_indices_converter.py:24-178)."""
+    T = idx.shape[0]
+    valid = idx >= 0
+    safe = idx.clamp_min(0).long()
+    mask = torch.zeros(T, n_experts, dtype=torch.bool, device=idx.device)
+    w = torch.zeros(T, n_experts, dtype=probs.dtype, device=idx.device)
+    rows = torch.arange(T, device=idx.device)[:, None].expand_as(safe)
+    mask[rows[valid], safe[valid]] = True
+    w[rows[valid], safe[valid]] = probs[valid]
+    return mask, w
+
+
+def multihot_to_indices(mask: torch.Tensor, weights: torch.Tensor, k: int):
+    """Inverse of ``indices_to_multihot``: ``(idx [T, k] int32, probs [T, k])`` in ascending expert order, padded
+    with -1 / 0 for tokens routed to fewer than k experts."""
+    T, E = mask.shape
+    order = torch.where(mask, torch.arange(E, device=mask.device)[None, :], torch.full_like(mask, E, dtype=torch.long))
+    pos = order.sort(dim=1).values[:, :k]
+    valid = pos < E
+    idx = torch.where(valid, pos, torch.full_like(pos, -1)).to(torch.int32)
+    probs = torch.where(valid, weights.gather(1, pos.clamp_max(E - 1)), torch.zeros_like(weights[:, :k]))
+    return idx, probs
+
+
+def fill_indices(tokens_per_expert_group: torch.Tensor, experts_per_rank: int, ep_size: int,
+                 max_len: Optional[int] = None) -> torch.Tensor:
+    """Permutation that turns rows received in (source rank, local expert) order into (local expert, source rank)
+    order, i.e. groups each local expert's tokens together for the grouped GEMM.
+    ``tokens_per_expert_group[r * experts_per_rank + e]`` = rows rank r sent for local expert e. Returns the source
+    row of every output row (-1 beyond the total when ``max_len`` pads); the reference builds it with a Triton kernel,
+    cosmos_rl/policy/kernel/moe/indices.py:25-111."""
+    counts = tokens_per_expert_group.view(ep_size, experts_per_rank).long()
+    starts = (counts.flatten().cumsum(0) - counts.flatten()).view(ep_size, experts_per_rank)
+    pieces = []
+    for e in range(experts_per_rank):
+        for r in range(ep_size):
+            n = int(counts[r, e])
+            if n:
+                pieces.append(torch.arange(n, device=counts.device) + starts[r, e])
+    out = torch.cat(pieces) if pieces else torch.zeros(0, dtype=torch.long, device=counts.device)
+    if max_len is not None and max_len > out.numel():
+        out = torch.cat([out, torch.full((max_len - out.numel(),), -1, dtype=torch.long, device=counts.device)])
+    return out

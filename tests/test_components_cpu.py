@@ -370,3 +370,33 @@ def test_nan_hooks_weight_sync_check_report_sinks_and_extension_points(tmp_path)
     def plan(model, dims, config):
         model.planned = True
     assert X.parallelism_strategy("toy") is plan and X.parallelism_strategy("qwen2") is None
+
+
+def test_heartbeat_child_process_posts_and_is_daemonic():
+    """The heartbeat child posts to the controller address and stops with its parent."""
+    import http.server
+    import json
+    import threading
+    from cosmos_rl_b200.comm.heartbeat_process import start_heartbeat_process
+    seen = []
+
+    class H(http.server.BaseHTTPRequestHandler):
+        def do_POST(self):
+            body = json.loads(self.rfile.read(int(self.headers["Content-Length"])))
+            seen.append((self.path, body["replica_name"]))
+            self.send_response(200)
+            self.end_headers()
+
+        def log_message(self, *a):
+            pass
+
+    srv = http.server.HTTPServer(("127.0.0.1", 0), H)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    p = start_heartbeat_process([f"http://127.0.0.1:{srv.server_port}"], "policy-0", 0.1)
+    deadline = time.time() + 30
+    while len(seen) < 2 and time.time() < deadline:
+        time.sleep(0.05)
+    assert p.daemon and len(seen) >= 2 and seen[0] == ("/api/heartbeat", "policy-0")
+    p.terminate()
+    p.join(timeout=10)
+    srv.shutdown()

@@ -98,3 +98,18 @@ def test_mxfp4_reference_quantiser():
     idx = R.mxfp4_sf_index(256, 8, True)
     assert idx[0, 0] == 0 and idx[1, 0] == 16 and idx[32, 0] == 4 and idx[0, 1] == 1 and idx[0, 4] == 512 and idx[128, 0] == 1024
     assert idx.flatten().unique().numel() == 256 * 8
+
+
+def test_moe_index_utilities():
+    import torch
+    from cosmos_rl_b200.ops import moe as M
+    idx = torch.tensor([[2, 0], [3, -1], [1, 2]])
+    probs = torch.tensor([[0.7, 0.3], [1.0, 0.0], [0.4, 0.6]])
+    mask, w = M.indices_to_multihot(idx, probs, 4)
+    assert mask.tolist() == [[True, False, True, False], [False, False, False, True], [False, True, True, False]]
+    assert w[0, 2] == 0.7 and w[0, 0] == 0.3 and w[1].sum() == 1.0
+    i2, p2 = M.multihot_to_indices(mask, w, 2)
+    assert i2.tolist() == [[0, 2], [3, -1], [1, 2]] and torch.allclose(p2, torch.tensor([[0.3, 0.7], [1.0, 0.0], [0.4, 0.6]]))
+    # 2 ranks x 2 local experts; received order: r0e0 (2 rows), r0e1 (1), r1e0 (1), r1e1 (2)
+    perm = M.fill_indices(torch.tensor([2, 1, 1, 2]), experts_per_rank=2, ep_size=2, max_len=8)
+    assert perm.tolist() == [0, 1, 3, 2, 4, 5, -1, -1]           # expert 0: r0 rows 0,1 + r1 row 3; expert 1: 2, 4, 5
