@@ -20,6 +20,13 @@ _MOVED = {
     "rollout.rollout_base": "rollout.base",
     "policy.model.base": "models.base",
     "policy.model": "models",
+    "dispatcher.data.packer.multi_turn": "data.multi_turn",
+    "policy.lora.plugin": "policy.lora",
+    "policy.model.deepseek_v3": "models.deepseek_v3",
+    "policy.model.qwen3_moe": "models.qwen3_moe",
+    "policy.model.gpt": "models.gpt",
+    "utils.ulysses": "parallel.context_parallel",
+    "utils.trace": "utils.trace",
 }
 
 
