@@ -53,7 +53,10 @@ class _AliasFinder(importlib.abc.MetaPathFinder):
         except (ImportError, ValueError):
             return None
         spec = importlib.util.spec_from_loader(fullname, _AliasLoader(real))
-        spec.submodule_search_locations = getattr(importlib.import_module(real), "__path__", None)
+        locations = getattr(importlib.import_module(real), "__path__", None)
+        if locations is None and any(k.startswith(rest + ".") for k in _MOVED):
+            locations = []          # a plain module here, a package in the reference: its moved children resolve too
+        spec.submodule_search_locations = locations
         return spec
 
 
