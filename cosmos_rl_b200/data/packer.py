@@ -170,3 +170,74 @@ class DecoderOnlyLLMDataPacker(BaseDataPacker):
 
 
 BaseDataPacker.register(["llama", "qwen2", "qwen3", "qwen3_moe", "hfmodel"], DecoderOnlyLLMDataPacker)
+
+MM_KEYS = ("pixel_values", "image_grid_thw", "pixel_values_videos", "video_grid_thw")
+
+
+def merge_mm(items: List[Optional[Dict[str, Any]]]) -> Dict[str, torch.Tensor]:
+    """Concatenate the vision inputs of several samples in sample order (what HF vision-language models expect for a
+    batch: all patches / grids of the batch stacked along dim 0)."""
+    out: Dict[str, torch.Tensor] = {}
+    for k in MM_KEYS:
+        parts = [torch.as_tensor(it[k]) for it in items if it and it.get(k) is not None]
+        if parts:
+            out[k] = torch.cat(parts, dim=0)
+    return out
+
+
+class HFVLMDataPacker(DecoderOnlyLLMDataPacker):
+    """Vision-language samples (cosmos_rl/dispatcher/data/packer/hf_vlm_data_packer.py). A sample is either already
+    processed, ``{"input_ids": [...], "pixel_values": ..., "image_grid_thw": ...}`` (image placeholder tokens in
+    place), or a conversation that the model's processor turns into that form (``setup(..., processor=...)`` or a
+    processor loadable from the model folder)."""
+
+    class PolicyInput(DecoderOnlyLLMDataPacker.PolicyInput):
+        __slots__ = ("mm",)
+
+        def __init__(self, input_ids, logprob_masks, mm=None):
+            super().__init__(input_ids, logprob_masks)
+            self.mm = mm
+
+    def setup(self, config, tokenizer=None, processor=None, *a, **kw):
+        super().setup(config, tokenizer)
+        self.processor = processor
+        path = getattr(config.policy, "model_name_or_path", "")
+        if self.processor is None and path and __import__("os").path.isdir(path):
+            try:
+                from transformers import AutoProcessor
+                self.processor = AutoProcessor.from_pretrained(path)
+            except Exception:  # noqa: BLE001  (pre-processed samples need no processor)
+                self.processor = None
+
+    def _process(self, sample) -> Dict[str, Any]:
+        if isinstance(sample, dict) and "prompt" in sample and "input_ids" not in sample:
+            sample = sample["prompt"]
+        if isinstance(sample, dict) and "input_ids" in sample:
+            return {"input_ids": list(sample["input_ids"]), "mm": {k: sample[k] for k in MM_KEYS if sample.get(k) is not None}}
+        if self.processor is None:
+            raise RuntimeError("conversation samples of a vision-language model need its processor")
+        enc = self.processor.apply_chat_template(sample, tokenize=True, add_generation_prompt=True, return_dict=True,
+                                                 return_tensors="pt")
+        return {"input_ids": enc["input_ids"][0].tolist(), "mm": {k: enc[k] for k in MM_KEYS if k in enc}}
+
+    def get_rollout_input(self, item):
+        return self._process(item)
+
+    def get_policy_input(self, sample, rollout_output, n_ignore_prefix_tokens: int = 0, **kw):
+        pr = self._process(sample)
+        p, c = pr["input_ids"], self._encode_completion(rollout_output)
+        n_ign = min(n_ignore_prefix_tokens, len(c))
+        mask = [0] * (len(p) - 1 + n_ign) + [1] * (len(c) - n_ign) + [0]
+        return self.PolicyInput(p + c, mask, pr["mm"])
+
+    def sft_process_sample(self, sample):
+        if isinstance(sample, dict) and "input_ids" in sample:
+            out = {"input_ids": list(sample["input_ids"]), "label_ids": list(sample.get("label_ids", sample["input_ids"]))}
+            out["mm"] = {k: sample[k] for k in MM_KEYS if sample.get(k) is not None}
+            return out
+        pr = self._process(sample)
+        return {"input_ids": pr["input_ids"], "label_ids": list(pr["input_ids"]), "mm": pr["mm"]}
+
+
+BaseDataPacker.register(["qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "internvl", "llava", "gemma3"],
+                        HFVLMDataPacker)

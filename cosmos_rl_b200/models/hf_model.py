@@ -34,8 +34,16 @@ class HFModel(BaseModel):
         mt = cfg.pop("model_type")
         cfg.pop("architectures", None)
         self.hf_config = AutoConfig.for_model(mt, **cfg)
-        self.inner = AutoModelForCausalLM.from_config(self.hf_config, attn_implementation=attn_implementation)
-        c = self.hf_config
+        # vision-language families (a vision tower feeding image tokens into the decoder): same wrapper, the pixel
+        # inputs of the current packed batch are handed over through ``mm_inputs``
+        self.is_vlm = "vision_config" in cfg
+        if self.is_vlm:
+            from transformers import AutoModelForImageTextToText
+            self.inner = AutoModelForImageTextToText.from_config(self.hf_config, attn_implementation=attn_implementation)
+        else:
+            self.inner = AutoModelForCausalLM.from_config(self.hf_config, attn_implementation=attn_implementation)
+        self.mm_inputs: Dict[str, torch.Tensor] = {}
+        c = self.hf_config.get_text_config() if self.is_vlm else self.hf_config
         self.args = SimpleNamespace(model_type=mt, vocab_size=c.vocab_size, dim=c.hidden_size,
                                     n_layers=c.num_hidden_layers, n_heads=c.num_attention_heads,
                                     norm_eps=getattr(c, "rms_norm_eps", 1e-6), tp_size=1, tp_rank=0,
@@ -59,8 +67,8 @@ class HFModel(BaseModel):
         g = torch.Generator(device="cpu").manual_seed(seed)
         with torch.no_grad():
             for name, p in self.named_parameters():
-                if p.dim() == 1:
-                    p.fill_(1.0) if "norm" in name else p.zero_()
+                if p.dim() == 1:         # biases start at zero, every other vector is a scale (norm weights, ln_q ...)
+                    p.zero_() if name.endswith("bias") else p.fill_(1.0)
                 else:
                     p.copy_(torch.randn(p.shape, generator=g, dtype=torch.float32).mul_(std).to(p.dtype))
         self.materialize_buffers()
@@ -76,10 +84,14 @@ class HFModel(BaseModel):
             if inv is None or not (inv.is_meta or inv.device != dev) or any(True for _ in mod.parameters()):
                 continue
             # rotary-embedding modules own no parameters: building them again on the right device is exact
-            try:
-                type(mod).__init__(mod, mod.config, device=dev)
-            except TypeError:
-                type(mod).__init__(mod, config=mod.config)
+            if hasattr(mod, "config"):
+                try:
+                    type(mod).__init__(mod, mod.config, device=dev)
+                except TypeError:
+                    type(mod).__init__(mod, config=mod.config)
+                    mod.to(dev)
+            elif hasattr(mod, "dim") and hasattr(mod, "theta"):      # vision-tower rotary tables: (dim, theta)
+                type(mod).__init__(mod, mod.dim, mod.theta)
                 mod.to(dev)
         # any other buffer (router bias terms ...) is checkpoint state: zero until a checkpoint is loaded
         for mod in self.inner.modules():
@@ -111,7 +123,12 @@ class HFModel(BaseModel):
         ids[seq, col], pos[seq, col], mask[seq, col] = input_ids, position_ids.long(), 1
         if self.gradient_checkpointing and torch.is_grad_enabled() and not self.inner.is_gradient_checkpointing:
             self.inner.gradient_checkpointing_enable()
-        out = self.inner.model(input_ids=ids, attention_mask=mask, position_ids=pos, use_cache=False)
+        if self.is_vlm:
+            # multimodal rotary positions depend on the image grids: the model derives them from ids + mask
+            mm = {k: v.to(ids.device) for k, v in (self.mm_inputs or {}).items()}
+            out = self.inner.model(input_ids=ids, attention_mask=mask, use_cache=False, **mm)
+        else:
+            out = self.inner.model(input_ids=ids, attention_mask=mask, position_ids=pos, use_cache=False)
         return out.last_hidden_state[seq, col]
 
     def logprobs(self, hidden, labels, temperature: float = 1.0):

@@ -23,11 +23,12 @@ from .llm_trainer import LLMTrainer
 
 
 class _Sample:
-    __slots__ = ("ids", "mask", "advantage", "reward", "rollout_lp", "n_scored")
+    __slots__ = ("ids", "mask", "advantage", "reward", "rollout_lp", "n_scored", "mm")
 
-    def __init__(self, ids, mask, advantage, reward, rollout_lp):
+    def __init__(self, ids, mask, advantage, reward, rollout_lp, mm=None):
         self.ids, self.mask, self.advantage, self.reward, self.rollout_lp = ids, mask, advantage, reward, rollout_lp
         self.n_scored = int(sum(mask))
+        self.mm = mm            # vision inputs of a vision-language sample
 
 
 @TrainerRegistry.register("grpo")
@@ -56,10 +57,13 @@ class GRPOTrainer(LLMTrainer):
             if r.completion_logprobs:
                 lp = [pos[0] for pos in r.completion_logprobs][r.n_ignore_prefix_tokens:]
             max_len = self.config.policy.model_max_length
+            mm = getattr(pi, "mm", None)
+            if mm:                                  # image placeholders must stay in step with the pixel inputs
+                max_len = max(max_len, len(pi.input_ids))
             ids, mask = pi.input_ids[:max_len], pi.logprob_masks[:max_len]
             if len(ids) < len(pi.input_ids):
                 mask[-1] = 0
-            out.append(_Sample(ids, mask, float(r.advantage), float(r.reward), lp))
+            out.append(_Sample(ids, mask, float(r.advantage), float(r.reward), lp, mm))
         return out
 
     def _mini_batches(self, samples: List[_Sample]) -> List[List[int]]:
@@ -80,6 +84,9 @@ class GRPOTrainer(LLMTrainer):
             rlp_full[(b["label_ids"] >= 0)] = torch.tensor(flat, dtype=torch.float32, device=self.device)
         cu_full = b["cu_seqlens"]
         b = self.cp_shard(b)
+        if any(s.mm for s in samples):
+            from ...data.packer import merge_mm
+            b["mm"] = merge_mm([s.mm for s in samples])
         sel = (b["label_ids"] >= 0).nonzero(as_tuple=True)[0]
         b["sel"] = sel
         b["labels_sel"] = b["label_ids"][sel]

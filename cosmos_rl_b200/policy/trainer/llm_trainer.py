@@ -205,6 +205,7 @@ class LLMTrainer(Trainer):
             return self.pipeline.run(self._micro(batches), lambda h, mb: loss_of(h, mb.extra[0], mb.extra[1]))
         losses = []
         for i, b in enumerate(batches):
+            self._set_mm(b)
             loss = loss_of(self.model(b["input_ids"], b["position_ids"], b["cu_seqlens"], b["max_seqlen"]), i, b)
             loss.backward()
             losses.append(loss.detach())
@@ -215,8 +216,16 @@ class LLMTrainer(Trainer):
         """``fn(hidden, index, batch)`` per packed batch without gradients (last stage only under pp)."""
         if self.pipeline is not None:
             return self.pipeline.forward_only(self._micro(batches), lambda h, mb: fn(h, mb.extra[0], mb.extra[1]))
-        return [fn(self.model(b["input_ids"], b["position_ids"], b["cu_seqlens"], b["max_seqlen"]), i, b)
-                for i, b in enumerate(batches)]
+        out = []
+        for i, b in enumerate(batches):
+            self._set_mm(b)
+            out.append(fn(self.model(b["input_ids"], b["position_ids"], b["cu_seqlens"], b["max_seqlen"]), i, b))
+        return out
+
+    def _set_mm(self, b) -> None:
+        """Vision-language wrapper models read the pixel inputs of the batch they are about to run from here."""
+        if getattr(self.model, "is_vlm", False):
+            self.model.mm_inputs = b.get("mm") or {}
 
     def pp_sum(self, value: torch.Tensor) -> torch.Tensor:
         """A value only the last stage has (losses, metrics): summed over the stages so every rank reports it."""

@@ -26,6 +26,9 @@ class SFTTrainer(LLMTrainer):
         b = self.cp_shard(b)
         sel = (b["label_ids"] >= 0).nonzero(as_tuple=True)[0]
         b["sel"], b["labels_sel"] = sel, b["label_ids"][sel]
+        if any(s.get("mm") for s in samples):
+            from ...data.packer import merge_mm
+            b["mm"] = merge_mm([s.get("mm") for s in samples])
         return b
 
     def _batches(self, processed: List[Dict[str, Any]]) -> List[List[int]]:
@@ -49,7 +52,8 @@ class SFTTrainer(LLMTrainer):
         max_len = self.config.policy.model_max_length
         processed = [self.data_packer.sft_process_sample(s) for s in global_batch]
         for p in processed:
-            p["input_ids"], p["label_ids"] = p["input_ids"][:max_len], p["label_ids"][:max_len]
+            if not p.get("mm"):                 # image placeholder tokens must stay in step with the pixel inputs
+                p["input_ids"], p["label_ids"] = p["input_ids"][:max_len], p["label_ids"][:max_len]
         packed = [self._pack([processed[i] for i in idxs]) for idxs in self._batches(processed)]
         tok = torch.tensor(float(sum(b["n_scored"] for b in packed)), device=self.device)
         dp = self.parallel_dims.dp_shard

@@ -43,8 +43,13 @@ class HFRollout(RolloutBase):
         inner = self.model.inner
         results = []
         for p in payloads:
-            ids = torch.tensor([data_packer.get_rollout_input(p.prompt)], dtype=torch.long, device=self.device)
-            out = inner.generate(ids.expand(sp.n, -1), attention_mask=torch.ones_like(ids).expand(sp.n, -1),
+            item = data_packer.get_rollout_input(p.prompt)
+            mm = {}
+            if isinstance(item, dict):              # vision-language sample: ids + pixel inputs, repeated per sample
+                mm = {k: torch.cat([torch.as_tensor(v)] * sp.n, dim=0).to(self.device) for k, v in item["mm"].items()}
+                item = item["input_ids"]
+            ids = torch.tensor([item], dtype=torch.long, device=self.device)
+            out = inner.generate(ids.expand(sp.n, -1), attention_mask=torch.ones_like(ids).expand(sp.n, -1), **mm,
                                  do_sample=sp.temperature > 0, temperature=max(sp.temperature, 1e-5),
                                  top_p=sp.top_p, top_k=sp.top_k if sp.top_k > 0 else None,
                                  max_new_tokens=sp.max_tokens, output_scores=True, return_dict_in_generate=True,
