@@ -235,6 +235,14 @@ class GRPOTrainer(LLMTrainer):
         }
         for k, v in metrics_acc.items():
             report[f"train/{k}"] = float(torch.stack(v).mean())
+        if self.pipeline is not None:
+            # loss-side metrics exist on the last stage only; the replica's reporter is its first rank
+            pp_group = self.parallel_dims.group("pp")
+            last = dist.get_process_group_ranks(pp_group)[-1]
+            box = [{k: v for k, v in report.items() if k.startswith("train/") and k not in (
+                "train/iteration_time", "train/learning_rate", "train/grad_norm", "train/n_tokens")}]
+            dist.broadcast_object_list(box, src=last, group=pp_group)
+            report.update(box[0])
         if self.config.logging.report_mfu and self.device.type == "cuda":
             from ...utils.misc import peak_flops
             ntok = sum(len(s.ids) for s in samples)

@@ -601,6 +601,7 @@ def _pp_trainer_worker(rank, world, store, out_dir):
     a, b = gt.step_training(ros, 1, 10), gref.step_training(ros, 1, 10)
     assert abs(a["train/grad_norm"] - b["train/grad_norm"]) < 1e-3 * b["train/grad_norm"], (a["train/grad_norm"], b["train/grad_norm"])
     assert abs(a["train/loss_avg"] - b["train/loss_avg"]) < 1e-5
+    assert set(b) <= set(a) and abs(a["train/clip_frac"] - b["train/clip_frac"]) < 1e-6      # metrics reach every stage
     check_weights(gt, gref)
     dist.destroy_process_group()
 
