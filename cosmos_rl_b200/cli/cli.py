@@ -62,6 +62,14 @@ def cmd_status(args, api: APIClient):
     return 0
 
 
+def cmd_algo(args, api: APIClient):
+    """``cosmos-cli algo config``: the job configuration the controller serves to every worker
+    (cosmos_rl/cli/algo.py)."""
+    meta = api.get_controller_metadata()
+    print(json.dumps(meta.get("config", meta), indent=2, sort_keys=True))
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="cosmos-cli")
     ap.add_argument("--url", default="127.0.0.1:8000", help="controller address host:port")
@@ -79,9 +87,12 @@ def main(argv=None) -> int:
     np_ = sub.add_parser("nccl")
     np_.add_argument("action", choices=["ls"])
     sub.add_parser("status")
+    al = sub.add_parser("algo")
+    al.add_argument("action", choices=["config"])
     args = ap.parse_args(argv)
     api = _client(args.url)
-    return {"replica": cmd_replica, "profile": cmd_profile, "nccl": cmd_nccl, "status": cmd_status}[args.cmd](args, api)
+    return {"replica": cmd_replica, "profile": cmd_profile, "nccl": cmd_nccl, "status": cmd_status,
+            "algo": cmd_algo}[args.cmd](args, api)
 
 
 if __name__ == "__main__":

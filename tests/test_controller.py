@@ -257,3 +257,52 @@ def test_broker_blocking_read_and_groups():
     b.publish("q", b"2")
     assert b.read_group("q", "g", 1, 0) == [(1, b"1")] and b.read_group("q", "g", 5, 0) == [(2, b"2")]
     assert b.read_group("q", "g", 5, 0) == []
+
+
+def test_cosmos_cli_against_a_live_controller(tmp_path, capsys):
+    """`cosmos-cli` subcommands over HTTP against a controller served in this process."""
+    import json
+    import socket
+    import threading
+    import time
+
+    import uvicorn
+
+    from cosmos_rl_b200.cli import cli
+    from cosmos_rl_b200.config import Config
+    from cosmos_rl_b200.dispatcher.controller import Controller
+    from cosmos_rl_b200.dispatcher.data import SyntheticTokenDataset
+    from cosmos_rl_b200.dispatcher.protocol import RegisterRequest, Role
+    from cosmos_rl_b200.dispatcher.run_web_panel import create_app
+    cfg = Config.from_dict({"policy": {"model_name_or_path": "tiny-qwen2", "parallelism": {"tp_size": 1}},
+                            "rollout": {"parallelism": {"tp_size": 1}},
+                            "train": {"output_dir": str(tmp_path), "train_policy": {"type": "grpo"}}})
+    ctl = Controller(cfg, dataset=SyntheticTokenDataset(8, 4, 100))
+    ctl.register(RegisterRequest(replica_name="policy-a", role=Role.POLICY, mesh_names=["pp", "dp_shard", "cp", "tp"],
+                                 ranks=[0, 0, 0, 0], group_size=[1, 1, 1, 1], global_rank=0))
+    sock = socket.socket()
+    sock.bind(("127.0.0.1", 0))
+    port = sock.getsockname()[1]
+    server = uvicorn.Server(uvicorn.Config(create_app(ctl), log_level="warning"))
+    th = threading.Thread(target=server.run, kwargs={"sockets": [sock]}, daemon=True)
+    th.start()
+    url = f"127.0.0.1:{port}"
+    for _ in range(100):
+        try:
+            if cli.main(["--url", url, "status"]) == 0:
+                break
+        except Exception:
+            time.sleep(0.1)
+    capsys.readouterr()
+    assert cli.main(["--url", url, "replica", "ls"]) == 0
+    assert "policy-a" in capsys.readouterr().out
+    assert cli.main(["--url", url, "replica", "lsr", "policy-a"]) == 0
+    assert json.loads(capsys.readouterr().out)["name"] == "policy-a"
+    assert cli.main(["--url", url, "replica", "lsr", "nobody"]) == 1
+    capsys.readouterr()
+    assert cli.main(["--url", url, "algo", "config"]) == 0
+    assert json.loads(capsys.readouterr().out)["policy"]["model_name_or_path"] == "tiny-qwen2"
+    assert cli.main(["--url", url, "profile", "set", "policy-a", "--active-steps", "2"]) == 0
+    assert cli.main(["--url", url, "nccl", "ls"]) == 0
+    server.should_exit = True
+    th.join(timeout=10)
