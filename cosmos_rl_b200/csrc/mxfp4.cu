@@ -31,15 +31,16 @@ __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const __nv_bfloat16* _
                                                            uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int R,
                                                            int C, int swizzle) {
   const uint32_t n_cb = (uint32_t)C / 32;
-  const uint32_t total = (uint32_t)R * n_cb * 4;               // items of 8 elements; < 2^32 (checked by the launcher)
-  const uint32_t stride = gridDim.x * blockDim.x;
+  const uint32_t per_row = n_cb * 4;                          // items of 8 elements per row
   const uint32_t lane = threadIdx.x & 31;
-  // the loop condition is warp-uniform (first lane's index): every lane reaches the full-mask shuffles below
-  for (uint32_t i0 = blockIdx.x * blockDim.x + threadIdx.x - lane; i0 < total; i0 += stride) {
-    const uint32_t i = i0 + lane;
-    const bool valid = i < total;
-    const uint32_t blk = i >> 2, part = i & 3;
-    const uint32_t r = blk / n_cb, cb = blk - r * n_cb;
+  // blocks stride over rows, threads over the items of a row: no division anywhere. The inner loop condition is
+  // warp-uniform (first lane's item), so every lane reaches the full-mask shuffles below.
+  for (uint32_t r = blockIdx.x; r < (uint32_t)R; r += gridDim.x)
+  for (uint32_t it0 = threadIdx.x - lane; it0 < per_row; it0 += blockDim.x) {
+    const uint32_t it = it0 + lane;
+    const bool valid = it < per_row;
+    const uint32_t cb = it >> 2, part = it & 3;
+    const long long i = (long long)r * per_row + it;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (valid) v = __ldg(reinterpret_cast<const uint4*>(x + (long long)r * ldx + cb * 32 + part * 8));
     const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
@@ -124,8 +125,7 @@ extern "C" {
 int b200_quant_mxfp4(const void* x, long long ldx, void* q, void* sf, int R, int C, int swizzle, cudaStream_t stream) {
   if (R <= 0 || C <= 0) return 0;
   if (C % 32 != 0 || ldx % 8 != 0 || (long long)R * (C / 32) >= (1ll << 29)) return B200_ERR_ARG;
-  const long long total = (long long)R * (C / 32) * 4;
-  const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  const int grid = R < 148 * 16 ? R : 148 * 16;            // blocks stride over rows
   quant_mxfp4_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, (uint8_t*)sf, R, C, swizzle);
   return cudaGetLastError() == cudaSuccess ? 0 : B200_ERR_LAUNCH;
 }
