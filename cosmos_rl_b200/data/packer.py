@@ -82,6 +82,13 @@ class DecoderOnlyLLMDataPacker(BaseDataPacker):
             self.input_ids = input_ids
             self.logprob_masks = logprob_masks
 
+    def setup(self, config, tokenizer=None, *a, **kw):
+        super().setup(config, tokenizer, *a, **kw)
+        path = config.rollout.multi_turn_config.custom_chat_template_path
+        if path and tokenizer is not None and hasattr(tokenizer, "chat_template"):
+            with open(path) as f:
+                tokenizer.chat_template = f.read()      # e.g. tools/chat_templates/tool_chat_template.jinja2
+
     def _encode_prompt(self, prompt) -> List[int]:
         if isinstance(prompt, (list, tuple)) and (len(prompt) == 0 or isinstance(prompt[0], int)):
             return list(prompt)

@@ -101,8 +101,20 @@ class GRPOTrainer(LLMTrainer):
             b["rollout_lp"] = rlp_full[sel]
         return b
 
-    def _logprobs_of(self, hidden, b: Dict[str, Any]):
+    # ------------------------------------------------------------------ hooks a custom trainer may override
+    def compute_logprobs(self, hidden: torch.Tensor, b: Dict[str, Any]):
+        """(per-token log-probs, entropies) of the scored tokens of a packed batch from the final hidden states."""
         return self.model.logprobs(hidden[b["sel"]], b["labels_sel"], self.temperature)
+
+    def loss_fn(self, logprob, old_logprob, b: Dict[str, Any], ref_logprob=None, entropy=None, total_tokens=None):
+        """(scalar loss, metrics) of one packed batch; the default is the configured GRPO / DAPO / GSPO objective
+        (cosmos_rl/tools/custom_example/README.md lists the same override points)."""
+        return grpo_loss(logprob, old_logprob, b["adv_tok"], b["seq_ids_sel"], int(b["cu_seqlens"].numel() - 1),
+                         self.loss_cfg, ref_logprob=ref_logprob, rollout_logprob=b.get("rollout_lp"), entropy=entropy,
+                         seq_rewards=b["seq_rewards"], total_tokens=total_tokens)
+
+    def _logprobs_of(self, hidden, b: Dict[str, Any]):
+        return self.compute_logprobs(hidden, b)
 
     def _forward_logprobs(self, b: Dict[str, Any]):
         hidden = self.model(b["input_ids"], b["position_ids"], b["cu_seqlens"], b["max_seqlen"])
@@ -191,11 +203,9 @@ class GRPOTrainer(LLMTrainer):
                         old = old_lps[ci][bi]
                     else:
                         old = lp.detach()
-                    loss, m = grpo_loss(
-                        lp, old, b["adv_tok"], b["seq_ids_sel"], int(b["cu_seqlens"].numel() - 1), self.loss_cfg,
-                        ref_logprob=ref_lps[ci][bi] if ref_lps is not None else None,
-                        rollout_logprob=b.get("rollout_lp"), entropy=ent, seq_rewards=b["seq_rewards"],
-                        total_tokens=tok if self.loss_cfg.loss_type == "token-mean" else None)
+                    loss, m = self.loss_fn(lp, old, b, ref_logprob=ref_lps[ci][bi] if ref_lps is not None else None,
+                                           entropy=ent,
+                                           total_tokens=tok if self.loss_cfg.loss_type == "token-mean" else None)
                     if self.loss_cfg.loss_type != "token-mean":
                         loss = loss * (len(b["seq_rewards"]) / n_seq_total)
                     for k, v in m.items():

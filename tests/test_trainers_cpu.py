@@ -201,3 +201,27 @@ def test_fp8_training_linear_and_trainer_flag(tmp_path):
     batch = [{"input_ids": torch.randint(0, 32000, (n,), generator=g).tolist()} for n in (12, 20, 7, 16)]
     losses = [tr.step_training(batch, total_steps=10, train_step=i + 1)["train/loss_avg"] for i in range(4)]
     assert losses[-1] < losses[0] - 0.05, losses
+
+
+def test_custom_grpo_trainer_hooks(tmp_path):
+    """The example custom trainer: registered type, overridden loss and learning-rate hooks are what the step uses."""
+    import torch
+    from cosmos_rl_b200.dispatcher.data.schema import Rollout
+    from cosmos_rl_b200.policy.trainer.base import TrainerRegistry
+    from cosmos_rl_b200.tools.custom_example import CustomGRPOTrainer
+    assert TrainerRegistry.get_trainer_cls("custom_grpo") is CustomGRPOTrainer
+    c = Config.from_dict({
+        "policy": {"model_name_or_path": "tiny-qwen2", "model_max_length": 64, "model_gradient_checkpointing": False},
+        "custom": {"custom_grpo": {"entropy_bonus": 0.01, "length_penalty": 0.1, "lr_drop_every": 2}},
+        "train": {"seed": 0, "optm_lr": 1e-3, "optm_warmup_steps": 0, "output_dir": str(tmp_path),
+                  "train_policy": {"type": "grpo", "trainer_type": "custom_grpo", "mini_batch": 2},
+                  "ckpt": {"enable_checkpoint": False}}})
+    tr = CustomGRPOTrainer(c, ParallelDims(world_size=1, device=torch.device("cpu")), device=torch.device("cpu"))
+    tr.model_load_from_hf()
+    g = torch.Generator().manual_seed(0)
+    ros = [Rollout(prompt=torch.randint(0, 32000, (5,), generator=g).tolist(),
+                   completion=torch.randint(0, 32000, (n,), generator=g).tolist(), advantage=a, reward=a)
+           for n, a in ((6, 1.0), (9, -1.0), (4, 0.5), (7, -0.5))]
+    rep = tr.step_training(ros, 1, 10)
+    assert "train/entropy_bonus" in rep and "train/length_penalty" in rep and rep["train/grad_norm"] > 0
+    assert tr.lr_scale(0) == 1.0 and tr.lr_scale(2) == 0.5 and tr.lr_scale(5) == 0.25
