@@ -225,3 +225,25 @@ def test_custom_grpo_trainer_hooks(tmp_path):
     rep = tr.step_training(ros, 1, 10)
     assert "train/entropy_bonus" in rep and "train/length_penalty" in rep and rep["train/grad_norm"] > 0
     assert tr.lr_scale(0) == 1.0 and tr.lr_scale(2) == 0.5 and tr.lr_scale(5) == 0.25
+
+
+def test_freeze_and_trainable_patterns(tmp_path):
+    """policy.freeze_pattern / trainable_pattern: frozen parameters receive no update at all (no decay either) and
+    the gradient norm only counts what is trained."""
+    import torch
+    from cosmos_rl_b200.policy.trainer.sft_trainer import SFTTrainer
+    c = _config(tmp_path, "sft")
+    c.policy.freeze_pattern = [r"embed_tokens", r"layers\.0\."]
+    c.train.optm_weight_decay = 0.1
+    tr = SFTTrainer(c, ParallelDims(world_size=1, device=torch.device("cpu")), device=torch.device("cpu"))
+    tr.model_load_from_hf()
+    before = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+    g = torch.Generator().manual_seed(0)
+    batch = [{"input_ids": torch.randint(0, 32000, (n,), generator=g).tolist()} for n in (12, 20, 7, 16)]
+    for i in range(2):
+        tr.step_training(batch, total_steps=10, train_step=i + 1)
+    moved = {n for n, p in tr.model.named_parameters() if not torch.equal(p, before[n])}
+    assert moved and all(not n.startswith("layers.0.") and "embed_tokens" not in n for n in moved)
+    assert any(n.startswith("layers.1.") for n in moved) and "norm" in moved
+    segs = tr.optimizer.segments
+    assert segs and sum(b - a for a, b in segs) == sum(p.numel() for p in tr.model.parameters() if p.requires_grad)
