@@ -30,3 +30,25 @@ def test_tiny_grpo_job_runs_to_completion(tmp_path):
     ctrl = logs["controller.log"]
     assert "step 1/2" in ctrl and "step 2/2" in ctrl, detail
     assert "training finished at step 2" in ctrl, detail
+
+
+@pytest.mark.timeout(300)
+def test_tiny_grpo_job_colocated_single_process(tmp_path):
+    """The same job with ``mode = "colocated"``: the launcher starts ONE process that holds the controller logic,
+    the trainer and the generation engine (sharing one set of weights)."""
+    from cosmos_rl_b200.config import dump_toml, load_toml
+    raw = load_toml(os.path.join(HERE, "configs", "tiny_grpo_cpu.toml"))
+    raw["mode"] = "colocated"
+    raw["train"]["output_dir"] = str(tmp_path / "out")
+    cfg = tmp_path / "job.toml"
+    cfg.write_text(dump_toml(raw))
+    log_dir = tmp_path / "logs"
+    env = dict(os.environ, COSMOS_LOG_LEVEL="INFO", PYTHONPATH=ROOT, OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "cosmos_rl_b200.launcher.launch_all", "--config", str(cfg), "--cpu",
+           "--log-dir", str(log_dir), os.path.join(HERE, "e2e_script.py")]
+    r = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=280)
+    files = sorted(os.listdir(log_dir / "logs_latest"))
+    log = open(log_dir / "logs_latest" / "colocated_0.log").read()
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:] + log[-3000:]
+    assert files == ["colocated_0.log"]                                  # no controller / rollout processes
+    assert "[Colocated] finished after 2 training steps" in log, log[-3000:]
