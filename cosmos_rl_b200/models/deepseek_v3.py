@@ -344,6 +344,12 @@ class DeepseekV3(GPT):
         active = n - routed - embed + n_moe * a.top_k * 3 * a.dim * a.moe_ffn_dim
         return n, 6 * active + 12 * a.n_layers * a.n_heads * a.head_dim * seq_len
 
+    def shard_parts(self, flat):
+        """Weight-sync parts: stacked experts as per-expert rectangles (each expert-parallel rank publishes its own
+        experts), everything else as full or fused rectangles."""
+        from .qwen3_moe import Qwen3MoE
+        return Qwen3MoE.shard_parts(self, flat)
+
     def export_items(self):
         """(hf name, tensor) pairs: stacked experts and fused gate/up are split back."""
         mapper = DeepseekV3WeightMapper({"model_type": "deepseek_v3"})

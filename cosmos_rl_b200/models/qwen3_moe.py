@@ -282,7 +282,9 @@ class Qwen3MoE(GPT):
     def shard_parts(self, flat):
         """Weight-sync parts: the dense parameters as in the dense decoder, experts as per-expert rectangles."""
         from ..parallel.reshard import Part, gpt_parts
-        mapper = Qwen3MoEWeightMapper({"model_type": "qwen3_moe"})
+        from .base import ModelRegistry
+        mapper = ModelRegistry.mapper(self.args.model_type)({"model_type": self.args.model_type})
+        mapper.layer_offset = getattr(self, "layer_offset", 0)
         a = self.args
         dense = [(n, p) for n, p in flat.params if not (n.endswith("w_gate_up") or n.endswith("w_down"))]
         view = copy.copy(flat)

@@ -89,13 +89,13 @@ def gpt_parts(model, flat) -> List[Part]:
             add(hf[1], kv_lo * d, (kv_lo + hkv) * d, 0, cols, slot.offset, hq * d, 0, cols, tr)
             add(hf[2], kv_lo * d, (kv_lo + hkv) * d, 0, cols, slot.offset, (hq + hkv) * d, 0, cols, tr)
         elif "gate_up_proj.weight" in name:
-            il = il1 - il0
-            add(hf[0], il0, il1, 0, cols, slot.offset, 0, 0, cols, tr)
-            add(hf[1], il0, il1, 0, cols, slot.offset, il, 0, cols, tr)
+            il = rows // 2                 # local rows of each half (dense FFN, or the shared experts of an MoE block)
+            add(hf[0], r * il, (r + 1) * il, 0, cols, slot.offset, 0, 0, cols, tr)
+            add(hf[1], r * il, (r + 1) * il, 0, cols, slot.offset, il, 0, cols, tr)
         elif "o_proj.weight" in name:
             add(hf[0], 0, rows, r * hq * d, (r + 1) * hq * d, slot.offset, 0, 0, cols, tr)
         elif "down_proj.weight" in name:
-            add(hf[0], 0, rows, il0, il1, slot.offset, 0, 0, cols, tr)
+            add(hf[0], 0, rows, r * cols, (r + 1) * cols, slot.offset, 0, 0, cols, tr)
         elif "embed_tokens" in name or "lm_head" in name:
             v0 = r * rows if tp > 1 else 0
             add(hf[0], v0, v0 + rows, 0, cols, slot.offset, 0, 0, cols, tr)
