@@ -75,3 +75,44 @@ def test_plan_for_rank_roles_and_missing_source():
     broken = {"ranks": [dict(info, parts=info["parts"][1:])]}
     with pytest.raises(KeyError):
         plan_for_rank(broken, rol, "rollout", 0)
+
+
+@pytest.mark.parametrize("family", ["qwen3_moe", "deepseek_v3"])
+def test_plan_gathers_expert_parallel_shards(family):
+    """Policy ranks that each own a slice of the experts (expert parallelism) -> a rollout rank that holds all of
+    them: every expert is pulled from the rank that owns it, dense parameters from either."""
+    import copy
+    from cosmos_rl_b200.models.deepseek_v3 import ARCHS as DS, DeepseekV3
+    from cosmos_rl_b200.models.qwen3_moe import ARCHS as QM, Qwen3MoE
+    cls, base = (Qwen3MoE, QM["tiny-qwen3-moe"]) if family == "qwen3_moe" else (DeepseekV3, DS["tiny-deepseek-v3"])
+    base = copy.deepcopy(base)
+    base.vocab_size = 512
+    torch.manual_seed(0)
+    full = cls(base)
+    full.init_weights(2)
+    cfg = base.to_hf_config()
+    state = hf_io.hf_state_dict(full, cfg)
+    src_infos, src_flats = [], {}
+    for r in range(2):
+        a = copy.deepcopy(base)
+        a.ep_size, a.ep_rank = 2, r
+        with torch.device("meta"):
+            m = cls(a)
+        flat = FlatParams(m, torch.float32, torch.device("cpu"), with_grad=False)
+        hf_io.load_hf_state(m, lambda k: state[k], state, cfg)
+        src_infos.append(shard_info(r, model_parts(m, flat), flat.total))
+        src_flats[r] = flat.data
+    with torch.device("meta"):
+        dst = cls(copy.deepcopy(base))
+    dflat = FlatParams(dst, torch.float32, torch.device("cpu"), with_grad=False)
+    plan = merge_descriptors(build_plan(src_infos, shard_info(0, model_parts(dst, dflat), dflat.total)))
+    expert_sources = set()
+    for src_rank, so, sld, do, dld, rows, cols in plan:
+        torch.as_strided(dflat.data, (rows, cols), (dld, 1), do).copy_(
+            torch.as_strided(src_flats[src_rank], (rows, cols), (sld, 1), so))
+    for (n, p), (_, q) in zip(dst.named_parameters(), full.named_parameters()):
+        assert torch.equal(p, q), n
+    # the second half of the experts exists on rank 1 only
+    E = base.n_experts
+    late = next(p for p in model_parts(dst, dflat) if f"experts.{E - 1}." in p.key)
+    assert any(d[0] == 1 and d[3] <= late.off < d[3] + d[4] * d[5] for d in plan)
