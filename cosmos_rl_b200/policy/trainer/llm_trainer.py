@@ -116,6 +116,9 @@ class LLMTrainer(Trainer):
             custom_plan(model, parallel_dims, config)
         lr = config.train.optm_lr if isinstance(config.train.optm_lr, float) else float(
             list(config.train.optm_lr.values())[0] if isinstance(config.train.optm_lr, dict) else config.train.optm_lr[0])
+        if config.train.optm_name not in ("AdamW", "Adam"):
+            raise NotImplementedError(f"optimizer {config.train.optm_name!r}: the flat sharded optimizer implements AdamW "
+                                      f"(and Adam = AdamW without decoupled weight decay)")
         tp_mask = None
         if tp > 1:
             # parameters every tensor-parallel rank holds in full (norm weights): counted once in the gradient norm
@@ -125,7 +128,8 @@ class LLMTrainer(Trainer):
                     tp_mask[slot.offset:slot.offset + slot.numel] = True
         self.optimizer = FlatAdamW(
             self.flat, lr=lr, betas=tuple(config.train.optm_betas), eps=config.train.epsilon,
-            weight_decay=config.train.optm_weight_decay, max_grad_norm=config.train.optm_grad_norm_clip,
+            weight_decay=config.train.optm_weight_decay if config.train.optm_name == "AdamW" else 0.0,
+            max_grad_norm=config.train.optm_grad_norm_clip,
             tp_group=parallel_dims.group("tp") if tp > 1 else None, tp_replicated=tp_mask,
             norm_groups=[parallel_dims.group("pp")] if parallel_dims.pp > 1 else [],
             sum_groups=[parallel_dims.group("cp")] if parallel_dims.cp > 1 else [],
