@@ -433,8 +433,12 @@ class B200Config(_Section):
     nvls: bool = True                    # allow multimem (NVSwitch) reductions where available
     dlogits_chunk: int = 16384
     cp_mode: str = "kv-gather"           # context-parallel attention exchange: kv-gather | ring | ulysses
-    sequence_parallel: bool = True       # with tp_size > 1 (dense models, no pp / cp): residual stream and norms hold
-                                         # T / tp rows; projections run all-gather -> GEMM / GEMM -> reduce-scatter
+    sequence_parallel: bool = False      # with tp_size > 1 (dense models, no pp / cp): residual stream and norms hold
+                                         # T / tp rows (the reference's plan; halves activation memory at tp 2).
+                                         # Off by default: one 7B block fwd+bwd at tp 2 takes 6.57 ms without it,
+                                         # 7.17 ms with it (library collectives), 8.14 ms with the fused kernels
+    sp_fused_kernels: bool = False       # sequence-parallel projections through the all-gather -> GEMM and
+                                         # GEMM -> reduce-scatter kernels instead of library collectives + cuBLAS
     router_bias_update_rate: float = 1e-3  # DeepSeek-V3 load-balancing bias step per optimizer step (0 = frozen)
     recompute: str = "auto"              # with policy.model_gradient_checkpointing: "selective" (attention half +
                                          # SwiGLU only), "full" (whole block, least memory), "none", or "auto":

@@ -149,8 +149,8 @@ class LLMTrainer(Trainer):
         free. Activations kept per token and block without recomputation: the two norm inputs and residuals (4 H),
         q/k/v and the attention output, the gate/up product (2 I) and the SwiGLU output (I), all bf16."""
         tpo = getattr(self.model, "tp", None)
-        if (tpo is not None and tpo.sequence_parallel and self.device.type == "cuda" and tpo.fused_ag is None
-                and hasattr(self.model, "args")):
+        if (tpo is not None and tpo.sequence_parallel and self.config.b200.sp_fused_kernels
+                and self.device.type == "cuda" and tpo.fused_ag is None and hasattr(self.model, "args")):
             # peer-memory workspaces of the fused all-gather -> GEMM and GEMM -> reduce-scatter kernels, sized for the
             # largest packed micro-batch (padded to whole 128-row blocks per rank)
             rows = (max_tokens + 128 * tpo.size - 1) // (128 * tpo.size) * (128 * tpo.size)

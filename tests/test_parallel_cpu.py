@@ -445,6 +445,7 @@ def _tp_trainer_worker(rank, world, store, out_dir):
         return Config.from_dict({
             "policy": {"model_name_or_path": "tiny-qwen2", "model_max_length": 64, "model_gradient_checkpointing": False,
                        "parallelism": {"tp_size": tp, "dp_shard_size": 1}},
+            "b200": {"sequence_parallel": True},
             "train": {"seed": 0, "optm_lr": 1e-3, "optm_warmup_steps": 0, "output_dir": out_dir, "optm_grad_norm_clip": 0.5,
                       "train_policy": {"type": "sft", "trainer_type": "sft", "mini_batch": 4},
                       "ckpt": {"enable_checkpoint": False}}})
