@@ -113,3 +113,15 @@ def test_moe_index_utilities():
     # 2 ranks x 2 local experts; received order: r0e0 (2 rows), r0e1 (1), r1e0 (1), r1e1 (2)
     perm = M.fill_indices(torch.tensor([2, 1, 1, 2]), experts_per_rank=2, ep_size=2, max_len=8)
     assert perm.tolist() == [0, 1, 3, 2, 4, 5, -1, -1]           # expert 0: r0 rows 0,1 + r1 row 3; expert 1: 2, 4, 5
+
+
+def test_vlm_dataset_rows_to_conversations(tmp_path):
+    from cosmos_rl_b200.tools.dataset import hf_vlm
+    rows = [{"image": "a.jpg", "question": "What colour?", "answer": "B"},
+            {"conversation": [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "yo"}], "answer": "yo"}]
+    ds = hf_vlm.VLMDataset(sft=False, rows=rows, root=str(tmp_path))
+    conv = ds[0]
+    assert conv[0]["content"][0] == {"type": "image", "image": str(tmp_path / "a.jpg")} and len(conv) == 1
+    assert ds.get_reference_answer(0) == "B" and [m["role"] for m in ds[1]] == ["user"]
+    assert [m["role"] for m in hf_vlm.VLMDataset(True, rows, str(tmp_path))[0]] == ["user", "assistant"]
+    assert hf_vlm.vlm_reward("<answer>B</answer>", "B") == 1.0 and hf_vlm.vlm_reward("so \\\\boxed{12}", "12") == 1.0
