@@ -155,6 +155,13 @@ class HttpBrokerClient(StreamBroker):
                          timeout=block_ms / 1000.0 + 30.0)
         return [(m["id"], base64.b64decode(m["data"])) for m in r.get("messages", [])]
 
+    def read_group(self, stream, group, count=1, block_ms=0):
+        from ..utils.api_suffix import COSMOS_API_STREAM_READ_SUFFIX
+        r = self.api.get(COSMOS_API_STREAM_READ_SUFFIX,
+                         {"stream": stream, "group": group, "count": count, "block_ms": block_ms},
+                         timeout=block_ms / 1000.0 + 30.0)
+        return [(m["id"], base64.b64decode(m["data"])) for m in r.get("messages", [])]
+
     def kv_set(self, key, value, ttl_s=None):
         from ..utils.api_suffix import COSMOS_API_KV_SUFFIX
         self.api.post(COSMOS_API_KV_SUFFIX, {"key": key, "value": base64.b64encode(value).decode(), "ttl_s": ttl_s})

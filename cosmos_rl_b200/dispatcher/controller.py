@@ -98,7 +98,20 @@ class Controller:
         else:
             self.reference_replicas.pop(replica_name, None)
         self.rollout_status_manager.maybe_broadcast_stop(self.policy_status_manager)
+        self._stop_references_if_done()
         self._maybe_finalize()
+
+    def _stop_references_if_done(self) -> None:
+        """Teacher replicas serve until the job ends: once the stop broadcast went out to the rollout side (or no
+        policy and no rollout replica is left) they get a ``StopCommand`` too."""
+        done = self.rollout_status_manager.stop_broadcast_sent or (
+            self.policy_status_manager.had_replicas and not self.policy_status_manager.replicas
+            and not self.rollout_status_manager.replicas)
+        if done and not getattr(self, "_references_stopped", False):
+            self._references_stopped = True
+            from ..comm.broker import command_stream
+            for name in list(self.reference_replicas):
+                self.broker.publish(command_stream(name), cmd.StopCommand(name).pack())
 
     def heartbeat(self, replica_name: str) -> bool:
         return (self.policy_status_manager.heartbeat(replica_name)
@@ -106,7 +119,8 @@ class Controller:
                 or replica_name in self.reference_replicas)
 
     def _maybe_finalize(self) -> None:
-        no_replicas = not self.policy_status_manager.replicas and not self.rollout_status_manager.replicas
+        no_replicas = (not self.policy_status_manager.replicas and not self.rollout_status_manager.replicas
+                       and not self.reference_replicas)
         if no_replicas and self.policy_status_manager.had_replicas:
             self.finalized.set()
             if self.self_terminate:

@@ -185,8 +185,11 @@ def create_app(controller: Controller) -> FastAPI:
 
     # ---- stream broker (replaces the external Redis server)
     @app.get(S.COSMOS_API_STREAM_READ_SUFFIX)
-    async def stream_read(stream: str, last_id: int = 0, count: int = 1, block_ms: int = 0):
-        msgs = await asyncio.to_thread(c.broker.read, stream, last_id, count, min(block_ms, 5000))
+    async def stream_read(stream: str, last_id: int = 0, count: int = 1, block_ms: int = 0, group: str = ""):
+        if group:       # consumer-group read: every message goes to exactly one reader of the group (teacher requests)
+            msgs = await asyncio.to_thread(c.broker.read_group, stream, group, count, min(block_ms, 5000))
+        else:
+            msgs = await asyncio.to_thread(c.broker.read, stream, last_id, count, min(block_ms, 5000))
         return {"messages": [{"id": i, "data": base64.b64encode(d).decode()} for i, d in msgs]}
 
     @app.post(S.COSMOS_API_STREAM_PUBLISH_SUFFIX)

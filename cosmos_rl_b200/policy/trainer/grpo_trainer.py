@@ -23,12 +23,13 @@ from .llm_trainer import LLMTrainer
 
 
 class _Sample:
-    __slots__ = ("ids", "mask", "advantage", "reward", "rollout_lp", "n_scored", "mm")
+    __slots__ = ("ids", "mask", "advantage", "reward", "rollout_lp", "n_scored", "mm", "teacher_lp")
 
-    def __init__(self, ids, mask, advantage, reward, rollout_lp, mm=None):
+    def __init__(self, ids, mask, advantage, reward, rollout_lp, mm=None, teacher_lp=None):
         self.ids, self.mask, self.advantage, self.reward, self.rollout_lp = ids, mask, advantage, reward, rollout_lp
         self.n_scored = int(sum(mask))
         self.mm = mm            # vision inputs of a vision-language sample
+        self.teacher_lp = teacher_lp   # per scored token, from the distillation teacher
 
 
 @TrainerRegistry.register("grpo")
@@ -63,7 +64,10 @@ class GRPOTrainer(LLMTrainer):
             ids, mask = pi.input_ids[:max_len], pi.logprob_masks[:max_len]
             if len(ids) < len(pi.input_ids):
                 mask[-1] = 0
-            out.append(_Sample(ids, mask, float(r.advantage), float(r.reward), lp, mm))
+            tlp = None
+            if r.teacher_logprobs:
+                tlp = [pos[0] for pos in r.teacher_logprobs][r.n_ignore_prefix_tokens:]
+            out.append(_Sample(ids, mask, float(r.advantage), float(r.reward), lp, mm, tlp))
         return out
 
     def _mini_batches(self, samples: List[_Sample]) -> List[List[int]]:
@@ -82,6 +86,17 @@ class GRPOTrainer(LLMTrainer):
             flat = [x for s in samples for x in s.rollout_lp]
             rlp_full = torch.zeros(b["label_ids"].numel(), dtype=torch.float32, device=self.device)
             rlp_full[(b["label_ids"] >= 0)] = torch.tensor(flat, dtype=torch.float32, device=self.device)
+        tlp_full = None
+        if self.config.distillation.enable:
+            # teacher log-probs per scored token; samples without a teacher result are excluded from the KL term
+            tlp_full = torch.full((b["label_ids"].numel(),), float("nan"), dtype=torch.float32, device=self.device)
+            scored = (b["label_ids"] >= 0).nonzero(as_tuple=True)[0]
+            pos = 0
+            for s_ in samples:
+                if s_.teacher_lp is not None and len(s_.teacher_lp) == s_.n_scored:
+                    tlp_full[scored[pos:pos + s_.n_scored]] = torch.tensor(s_.teacher_lp, dtype=torch.float32,
+                                                                            device=self.device)
+                pos += s_.n_scored
         cu_full = b["cu_seqlens"]
         b = self.cp_shard(b)
         if any(s.mm for s in samples):
@@ -99,7 +114,34 @@ class GRPOTrainer(LLMTrainer):
                 from ...parallel.context_parallel import split_for_cp
                 rlp_full = split_for_cp(rlp_full, cu_full, self.parallel_dims.cp, self.parallel_dims.cp_coord)
             b["rollout_lp"] = rlp_full[sel]
+        if tlp_full is not None:
+            if self.parallel_dims.cp > 1:
+                from ...parallel.context_parallel import split_for_cp
+                tlp_full = split_for_cp(tlp_full, cu_full, self.parallel_dims.cp, self.parallel_dims.cp_coord)
+            b["teacher_lp"] = tlp_full[sel]
         return b
+
+    def teacher_kl_advantages(self, logprob: torch.Tensor, b: Dict[str, Any]):
+        """On-policy distillation: every scored token gets ``-kl_penalty_coef * (log p_student - log p_teacher)`` (the
+        per-token reverse-KL estimate on the sampled token) added to its advantage, optionally as a discounted sum over
+        the rest of its sequence (cosmos_rl/policy/trainer/llm_trainer/grpo_trainer.py:692-860). Returns the new
+        per-token advantages and the mean divergence."""
+        d = self.config.distillation
+        t = b["teacher_lp"]
+        have = ~torch.isnan(t)
+        div = torch.where(have, logprob.detach().float() - torch.nan_to_num(t), torch.zeros_like(t))
+        kl_adv = -d.kl_penalty_coef * div
+        if d.kl_discount_factor != 0.0:
+            # discounted future sum inside each sequence: suffix sums via a reversed scan per segment
+            vals, ids = kl_adv.tolist(), b["seq_ids_sel"].tolist()
+            acc, res = 0.0, [0.0] * len(vals)
+            for i in range(len(vals) - 1, -1, -1):
+                if i + 1 < len(vals) and ids[i + 1] != ids[i]:
+                    acc = 0.0
+                acc = vals[i] + d.kl_discount_factor * acc
+                res[i] = acc
+            kl_adv = torch.tensor(res, dtype=kl_adv.dtype, device=kl_adv.device)
+        return b["adv_tok"] + kl_adv, div.sum() / have.sum().clamp_min(1)
 
     # ------------------------------------------------------------------ hooks a custom trainer may override
     def compute_logprobs(self, hidden: torch.Tensor, b: Dict[str, Any]):
@@ -109,9 +151,15 @@ class GRPOTrainer(LLMTrainer):
     def loss_fn(self, logprob, old_logprob, b: Dict[str, Any], ref_logprob=None, entropy=None, total_tokens=None):
         """(scalar loss, metrics) of one packed batch; the default is the configured GRPO / DAPO / GSPO objective
         (cosmos_rl/tools/custom_example/README.md lists the same override points)."""
-        return grpo_loss(logprob, old_logprob, b["adv_tok"], b["seq_ids_sel"], int(b["cu_seqlens"].numel() - 1),
-                         self.loss_cfg, ref_logprob=ref_logprob, rollout_logprob=b.get("rollout_lp"), entropy=entropy,
-                         seq_rewards=b["seq_rewards"], total_tokens=total_tokens)
+        adv, teacher_kl = b["adv_tok"], None
+        if "teacher_lp" in b:
+            adv, teacher_kl = self.teacher_kl_advantages(logprob, b)
+        loss, metrics = grpo_loss(logprob, old_logprob, adv, b["seq_ids_sel"], int(b["cu_seqlens"].numel() - 1),
+                                  self.loss_cfg, ref_logprob=ref_logprob, rollout_logprob=b.get("rollout_lp"),
+                                  entropy=entropy, seq_rewards=b["seq_rewards"], total_tokens=total_tokens)
+        if teacher_kl is not None:
+            metrics["teacher_kl_reversed"] = teacher_kl.detach()
+        return loss, metrics
 
     def _logprobs_of(self, hidden, b: Dict[str, Any]):
         return self.compute_logprobs(hidden, b)

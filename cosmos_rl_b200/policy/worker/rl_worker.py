@@ -237,6 +237,14 @@ class RLPolicyWorker(CommMixin):
             for r in got:
                 if r.prompt is None:
                     self.data_fetcher.fill(r)
+                if self.config.distillation.enable and r.teacher_result_uuid and r.teacher_logprobs is None:
+                    from ...reference.teacher_worker import fetch_teacher_result
+                    res = fetch_teacher_result(self.broker, r.teacher_result_uuid, timeout_s=120.0)
+                    if res is not None:
+                        r.teacher_logprobs = [[v] for v in res["logprobs"]]
+                    else:
+                        logger.warning("[Policy] no teacher result for %s: the rollout trains without it",
+                                       r.teacher_result_uuid)
             for rank in range(self.world_size):
                 coords = self.parallel_dims.coords_of(rank)
                 dp_idx = coords["dp_replicate"] * self.parallel_dims.dp_shard + coords["dp_shard"]

@@ -105,8 +105,7 @@ class TeacherWorker(CommMixin):
 
     def serve_once(self, block_ms: int = 200) -> int:
         broker = self.broker
-        read = getattr(broker, "read_group", None)
-        msgs = read(TEACHER_REQUEST_STREAM, self.group, self.batch, block_ms) if read else []
+        msgs = broker.read_group(TEACHER_REQUEST_STREAM, self.group, self.batch, block_ms)
         if not msgs:
             return 0
         reqs = [msgpack.unpackb(d, raw=False) for _, d in msgs]
@@ -117,11 +116,25 @@ class TeacherWorker(CommMixin):
         return len(reqs)
 
     def execute(self) -> None:
+        """Serve until the controller sends ``StopCommand`` (job over) or stays unreachable."""
+        from ..dispatcher import command as cmd
+        self.start_command_thread()
+        failures = 0
         while not self.shutdown_signal.is_set():
+            c = self.next_command()
+            if isinstance(c, cmd.StopCommand):
+                logger.info("[Teacher] stop received after %d scored requests", self.served)
+                break
             try:
                 self.serve_once()
+                failures = 0
             except Exception as e:
+                failures += 1
                 logger.error("[Teacher] request failed: %s", e)
+                if failures >= 3:
+                    logger.error("[Teacher] the controller stays unreachable: leaving")
+                    break
+                time.sleep(0.5)          # do not spin on a persistent error
 
     def handle_shutdown(self) -> None:
         self.shutdown_signal.set()

@@ -267,6 +267,13 @@ class DisaggregatedRolloutControlWorker(CommMixin):
                 self.stats["generated_tokens"] += sum(len(t) for t in r.completion_token_ids)
             p.cumulative_logprob = r.cumulative_logprob
             p.weight_version = self.current_weight_version
+            if self.config.distillation.enable and r.completion_token_ids is not None and reporter:
+                # on-policy distillation: the teacher scores every sampled completion; the policy fetches the result
+                # by uuid when it trains on the rollout (cosmos_rl/rollout/worker/rollout_control.py teacher requests)
+                from ..reference.teacher_worker import submit_teacher_request
+                prompt_ids = list(self.data_packer.get_rollout_input(p.prompt))
+                p.teacher_result_uuids = [submit_teacher_request(self.broker, prompt_ids + list(toks), len(prompt_ids))
+                                          for toks in r.completion_token_ids]
         self.stats["batches"] += 1
         if reporter:
             self.reward_dispatcher.enqueue_rewards_cal(payloads)

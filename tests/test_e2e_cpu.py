@@ -52,3 +52,29 @@ def test_tiny_grpo_job_colocated_single_process(tmp_path):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:] + log[-3000:]
     assert files == ["colocated_0.log"]                                  # no controller / rollout processes
     assert "[Colocated] finished after 2 training steps" in log, log[-3000:]
+
+
+@pytest.mark.timeout(420)
+def test_tiny_grpo_job_with_distillation_teacher(tmp_path):
+    """On-policy distillation end to end: controller + policy + rollout + teacher replica; the rollout side asks the
+    teacher to score every completion, the policy fetches the scores and reports the teacher KL."""
+    from cosmos_rl_b200.config import dump_toml, load_toml
+    raw = load_toml(os.path.join(HERE, "configs", "tiny_grpo_cpu.toml"))
+    raw["train"]["output_dir"] = str(tmp_path / "out")
+    raw["distillation"] = {"enable": True, "model_name_or_path": "tiny-qwen2", "kl_penalty_coef": 1.0,
+                           "parallelism": {"tp_size": 1, "dp_shard_size": 1, "n_init_replicas": 1}}
+    cfg = tmp_path / "job.toml"
+    cfg.write_text(dump_toml(raw))
+    log_dir = tmp_path / "logs"
+    env = dict(os.environ, COSMOS_LOG_LEVEL="INFO", COSMOS_HEARTBEAT_SEND_INTERVAL="2", PYTHONPATH=ROOT,
+               OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "cosmos_rl_b200.launcher.launch_all", "--config", str(cfg), "--policy", "1",
+           "--rollout", "1", "--reference", "1", "--cpu", "--log-dir", str(log_dir), os.path.join(HERE, "e2e_script.py")]
+    r = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=400)
+    latest = log_dir / "logs_latest"
+    logs = {f: open(latest / f).read() for f in sorted(os.listdir(latest))}
+    detail = "\n".join(f"==== {k}\n{v[-2500:]}" for k, v in logs.items())
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:] + detail
+    assert "reference_0.log" in logs, list(logs)
+    ctrl = logs["controller.log"]
+    assert "training finished at step 2" in ctrl and "train/teacher_kl_reversed" in ctrl, detail

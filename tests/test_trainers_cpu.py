@@ -247,3 +247,35 @@ def test_freeze_and_trainable_patterns(tmp_path):
     assert any(n.startswith("layers.1.") for n in moved) and "norm" in moved
     segs = tr.optimizer.segments
     assert segs and sum(b - a for a, b in segs) == sum(p.numel() for p in tr.model.parameters() if p.requires_grad)
+
+
+def test_on_policy_distillation_advantages(tmp_path):
+    """Teacher log-probs per scored token become advantages: -coef * (student - teacher), discounted over the rest
+    of the sequence; samples without a teacher result only keep their own advantage."""
+    import torch
+    from cosmos_rl_b200.dispatcher.data.schema import Rollout
+    from cosmos_rl_b200.policy.trainer.grpo_trainer import GRPOTrainer
+    c = Config.from_dict({
+        "policy": {"model_name_or_path": "tiny-qwen2", "model_max_length": 64, "model_gradient_checkpointing": False},
+        "distillation": {"enable": True, "model_name_or_path": "tiny-qwen2", "kl_penalty_coef": 2.0, "kl_discount_factor": 0.5},
+        "train": {"seed": 0, "optm_lr": 1e-3, "optm_warmup_steps": 0, "output_dir": str(tmp_path),
+                  "train_policy": {"type": "grpo", "trainer_type": "grpo", "mini_batch": 4},
+                  "ckpt": {"enable_checkpoint": False}}})
+    tr = GRPOTrainer(c, ParallelDims(world_size=1, device=torch.device("cpu")), device=torch.device("cpu"))
+    tr.model_load_from_hf()
+    g = torch.Generator().manual_seed(0)
+    comp = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (3, 2)]
+    ros = [Rollout(prompt=[5, 6, 7], completion=comp[0], advantage=0.5, reward=1.0,
+                   teacher_logprobs=[[-1.0], [-2.0], [-3.0]]),
+           Rollout(prompt=[8, 9], completion=comp[1], advantage=-0.5, reward=0.0)]             # no teacher result
+    b = tr._pack(tr._prepare(ros))
+    t = b["teacher_lp"]
+    assert t[:3].tolist() == [-1.0, -2.0, -3.0] and torch.isnan(t[3:]).all()
+    lp = torch.tensor([-1.5, -1.0, -3.0, -0.7, -0.9])
+    adv, kl = tr.teacher_kl_advantages(lp, b)
+    d = [-2.0 * (-1.5 + 1.0), -2.0 * (-1.0 + 2.0), 0.0]                   # -coef * (student - teacher) = [1, -2, 0]
+    want = [d[0] + 0.5 * (d[1] + 0.5 * d[2]), d[1] + 0.5 * d[2], d[2]]
+    assert torch.allclose(adv[:3], torch.tensor(want) + 0.5) and torch.allclose(adv[3:], torch.tensor([-0.5, -0.5]))
+    assert abs(kl.item() - ((-0.5) + 1.0 + 0.0) / 3) < 1e-6
+    rep = tr.step_training(ros, 1, 10)
+    assert "train/teacher_kl_reversed" in rep and rep["train/grad_norm"] > 0
