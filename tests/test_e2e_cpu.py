@@ -12,6 +12,21 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 
 
+def _run_job(cmd, env, timeout):
+    """Run a launcher command in its own process group; on a timeout the whole group (launcher, controller, replicas)
+    is killed, so a hung job never leaves processes behind."""
+    import signal
+    p = subprocess.Popen(cmd, env=env, cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
+                         start_new_session=True)
+    try:
+        out, err = p.communicate(timeout=timeout)
+    except subprocess.TimeoutExpired:
+        os.killpg(p.pid, signal.SIGKILL)          # the group this test started, by its exact id
+        out, err = p.communicate()
+        return subprocess.CompletedProcess(cmd, -9, out, err + "\n[test] job timed out and was killed")
+    return subprocess.CompletedProcess(cmd, p.returncode, out, err)
+
+
 @pytest.mark.timeout(420)
 def test_tiny_grpo_job_runs_to_completion(tmp_path):
     log_dir = tmp_path / "logs"
@@ -20,7 +35,7 @@ def test_tiny_grpo_job_runs_to_completion(tmp_path):
     cmd = [sys.executable, "-m", "cosmos_rl_b200.launcher.launch_all", "--config",
            os.path.join(HERE, "configs", "tiny_grpo_cpu.toml"), "--policy", "1", "--rollout", "1", "--cpu",
            "--log-dir", str(log_dir), os.path.join(HERE, "e2e_script.py")]
-    r = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=400)
+    r = _run_job(cmd, env, 400)
     logs = {}
     latest = log_dir / "logs_latest"
     for f in sorted(os.listdir(latest)):
@@ -46,7 +61,7 @@ def test_tiny_grpo_job_colocated_single_process(tmp_path):
     env = dict(os.environ, COSMOS_LOG_LEVEL="INFO", PYTHONPATH=ROOT, OMP_NUM_THREADS="2")
     cmd = [sys.executable, "-m", "cosmos_rl_b200.launcher.launch_all", "--config", str(cfg), "--cpu",
            "--log-dir", str(log_dir), os.path.join(HERE, "e2e_script.py")]
-    r = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=280)
+    r = _run_job(cmd, env, 280)
     files = sorted(os.listdir(log_dir / "logs_latest"))
     log = open(log_dir / "logs_latest" / "colocated_0.log").read()
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:] + log[-3000:]
@@ -70,7 +85,7 @@ def test_tiny_grpo_job_with_distillation_teacher(tmp_path):
                OMP_NUM_THREADS="2")
     cmd = [sys.executable, "-m", "cosmos_rl_b200.launcher.launch_all", "--config", str(cfg), "--policy", "1",
            "--rollout", "1", "--reference", "1", "--cpu", "--log-dir", str(log_dir), os.path.join(HERE, "e2e_script.py")]
-    r = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=400)
+    r = _run_job(cmd, env, 400)
     latest = log_dir / "logs_latest"
     logs = {f: open(latest / f).read() for f in sorted(os.listdir(latest))}
     detail = "\n".join(f"==== {k}\n{v[-2500:]}" for k, v in logs.items())
