@@ -76,6 +76,27 @@ def case_gemm_fp8(iters):
     report(f"quant_fp8 1x128 activations {M}x{K}", t, nbytes=M * K * 3.0)
 
 
+def case_fp8_train(iters):
+    """A projection of the Qwen2.5-7B block (gate_up: 3584 -> 37888) forward + backward on 8192 tokens: the three
+    GEMMs on the block-scaled fp8 kernel (with the quantisation and transposes they need) against bf16 cuBLAS."""
+    M, N, K = 8192, 37888, 3584
+    go = bf(M, N)
+
+    def run(w):
+        x = bf(M, K).requires_grad_(True)
+        w.grad = None
+        F.linear_maybe_fp8(x, w).backward(go)
+
+    w16 = bf(N, K, scale=0.03).requires_grad_(True)
+    t16 = timed(lambda: run(w16), iters)
+    report(f"linear fwd+bwd bf16 (cuBLAS) {M}x{N}x{K}", t16, flops=6.0 * M * N * K)
+    w8 = bf(N, K, scale=0.03).requires_grad_(True)
+    w8._fp8_train = True
+    t8 = timed(lambda: run(w8), iters)
+    report(f"linear fwd+bwd fp8 block-scaled (incl. quantisation, transposes) {M}x{N}x{K}", t8, flops=6.0 * M * N * K)
+    print(f"fp8 / bf16 time: {t8 / t16:.2f}", flush=True)
+
+
 def case_moe(iters):
     """One MoE layer of the Qwen3-30B-A3B architecture: 128 experts, top-8, hidden 2048, expert FFN 768."""
     from . import moe
@@ -256,7 +277,7 @@ def case_flash(iters, B=16, L=4096, library=True):
     assert native.read_status(q.device) == 0
 
 
-CASES = {"quant_mxfp4": case_quant_mxfp4, "reshard_fp8": case_reshard_fp8, "moe": case_moe, "gemm_fp8": case_gemm_fp8, "flash": case_flash, "flash_small": case_flash_small, "gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
+CASES = {"quant_mxfp4": case_quant_mxfp4, "fp8_train": case_fp8_train, "reshard_fp8": case_reshard_fp8, "moe": case_moe, "gemm_fp8": case_gemm_fp8, "flash": case_flash, "flash_small": case_flash_small, "gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
          "reshard": case_reshard, "quant": case_quant, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu,
          "rope": case_rope, "adamw": case_adamw, "sample": case_sample}
 
