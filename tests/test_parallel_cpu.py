@@ -609,3 +609,53 @@ def _pp_trainer_worker(rank, world, store, out_dir):
 
 def test_trainers_with_pipeline_parallelism(tmp_path):
     _spawn(_pp_trainer_worker, 2, tmp_path, str(tmp_path))
+
+
+def _combo_worker(rank, world, store, out_dir, axis):
+    """Four ranks: dp_shard 2 combined with tp 2, cp 2 or pp 2 through the SFT trainer. Each data-parallel rank trains
+    on its half of the batch; losses, gradient norm and weights must equal the single-process trainer on all of it."""
+    from cosmos_rl_b200.config import Config
+    from cosmos_rl_b200.models import hf_io
+    from cosmos_rl_b200.parallel.dims import ParallelDims
+    from cosmos_rl_b200.policy.trainer.sft_trainer import SFTTrainer
+    _init(rank, world, store)
+
+    def cfg(par):
+        return Config.from_dict({
+            "policy": {"model_name_or_path": "tiny-qwen2", "model_max_length": 64, "model_gradient_checkpointing": False,
+                       "parallelism": dict({"tp_size": 1, "cp_size": 1, "pp_size": 1, "dp_shard_size": 1}, **par)},
+            "train": {"seed": 0, "optm_lr": 1e-3, "optm_warmup_steps": 0, "output_dir": out_dir, "optm_grad_norm_clip": 0.5,
+                      "train_policy": {"type": "sft", "trainer_type": "sft", "mini_batch": 2},
+                      "ckpt": {"enable_checkpoint": False}}})
+    cpu = torch.device("cpu")
+    c = cfg({axis + "_size": 2, "dp_shard_size": 2})
+    dims = ParallelDims.from_config_parallelism(c.policy.parallelism, world, rank, cpu)
+    dims.build_groups()
+    tr = SFTTrainer(c, dims, device=cpu)
+    ref = SFTTrainer(cfg({}), ParallelDims(world_size=1, device=cpu), device=cpu)
+    ref.model_load_from_hf()
+    hf_cfg = ref.model.args.to_hf_config()
+    state = hf_io.hf_state_dict(ref.model, hf_cfg)
+    hf_io.load_hf_state(tr.model, lambda k: state[k], state, hf_cfg, dims.tp, dims.tp_coord)
+    tr.optimizer.refresh_master_from_params()
+    g = torch.Generator().manual_seed(3)
+    batch = [{"input_ids": torch.randint(0, 32000, (n,), generator=g).tolist()} for n in (12, 9, 15, 7, 10, 6, 8, 14)]
+    mine = batch[dims.dp_shard_coord::2]                                   # this data-parallel rank's samples
+    for i in range(2):
+        a = tr.step_training(mine, total_steps=10, train_step=i + 1)
+        b = ref.step_training(batch, total_steps=10, train_step=i + 1)
+        loss = torch.tensor(a["train/loss_avg"])
+        dist.all_reduce(loss, group=dims.group("dp_shard"))                # each dp rank reports its share of the sum
+        assert abs(loss.item() / 2 - b["train/loss_avg"]) < 1e-4, (axis, loss.item() / 2, b["train/loss_avg"])
+        assert abs(a["train/grad_norm"] - b["train/grad_norm"]) < 2e-3 * b["train/grad_norm"], (axis, a["train/grad_norm"], b["train/grad_norm"])
+    want = hf_io.hf_state_dict(ref.model, hf_cfg)
+    probe = GPT(tr.model.args)
+    hf_io.load_hf_state(probe, lambda k: want[k], want, hf_cfg, dims.tp, dims.tp_coord)
+    for (n, p), (_, q) in zip(tr.model.named_parameters(), probe.named_parameters()):
+        assert torch.allclose(p, q, atol=5e-4), (axis, n, (p - q).abs().max())
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("axis", ["tp", "cp", "pp"])
+def test_data_parallel_combined_with_model_parallel_axes(tmp_path, axis):
+    _spawn(_combo_worker, 4, tmp_path, str(tmp_path), axis)
