@@ -19,6 +19,8 @@ class DPOTrainer(LLMTrainer):
     def __init__(self, config, parallel_dims, **kw):
         self.inter_replica = kw.pop("inter_replica", None)
         super().__init__(config, parallel_dims, **kw)
+        if parallel_dims.cp > 1 or parallel_dims.pp > 1:
+            raise NotImplementedError("the DPO trainer supports dp_shard / dp_replicate / tp; use cp_size = pp_size = 1")
         self.beta = float(config.custom.get("dpo_beta", 0.1))
         self.reference_state = None
 
