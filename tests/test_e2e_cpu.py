@@ -93,3 +93,27 @@ def test_tiny_grpo_job_with_distillation_teacher(tmp_path):
     assert "reference_0.log" in logs, list(logs)
     ctrl = logs["controller.log"]
     assert "training finished at step 2" in ctrl and "train/teacher_kl_reversed" in ctrl, detail
+
+
+@pytest.mark.timeout(420)
+def test_tiny_grpo_job_with_lora(tmp_path):
+    """[policy.lora] through the whole disaggregated flow: only adapters train, the policy folds them into the dense
+    weights while a rollout replica pulls them, and the job completes."""
+    from cosmos_rl_b200.config import dump_toml, load_toml
+    raw = load_toml(os.path.join(HERE, "configs", "tiny_grpo_cpu.toml"))
+    raw["train"]["output_dir"] = str(tmp_path / "out")
+    raw["policy"]["lora"] = {"r": 4, "lora_alpha": 8, "target_modules": ["q_proj", "v_proj", "down_proj"]}
+    cfg = tmp_path / "job.toml"
+    cfg.write_text(dump_toml(raw))
+    log_dir = tmp_path / "logs"
+    env = dict(os.environ, COSMOS_LOG_LEVEL="INFO", COSMOS_HEARTBEAT_SEND_INTERVAL="2", PYTHONPATH=ROOT,
+               OMP_NUM_THREADS="2", COSMOS_WEIGHT_SYNC_CHECK="1")
+    cmd = [sys.executable, "-m", "cosmos_rl_b200.launcher.launch_all", "--config", str(cfg), "--policy", "1",
+           "--rollout", "1", "--cpu", "--log-dir", str(log_dir), os.path.join(HERE, "e2e_script.py")]
+    r = _run_job(cmd, env, 400)
+    latest = log_dir / "logs_latest"
+    logs = {f: open(latest / f).read() for f in sorted(os.listdir(latest))}
+    detail = "\n".join(f"==== {k}\n{v[-2500:]}" for k, v in logs.items())
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:] + detail
+    assert "training finished at step 2" in logs["controller.log"], detail
+    assert "[WeightSyncCheck] coverage ok" in logs["rollout_0.log"], detail      # the first sync was verified too
