@@ -32,6 +32,41 @@ class _Sample:
         self.teacher_lp = teacher_lp   # per scored token, from the distillation teacher
 
 
+def discounted_suffix_sum(x: torch.Tensor, seq_ids: torch.Tensor, gamma: float) -> torch.Tensor:
+    """``y[i] = x[i] + gamma * y[i + 1]`` inside every run of equal ``seq_ids`` (tokens of one sequence are contiguous).
+    Vectorised: cumulative sums for gamma == 1, a scaled cumulative sum in float64 while ``gamma ** longest_run`` stays
+    above 1e-6 (the scaling costs that many digits), a plain backward loop beyond that."""
+    n = x.numel()
+    if n == 0:
+        return x
+    ids = seq_ids.to(torch.long)
+    start = torch.ones(n, dtype=torch.bool, device=x.device)
+    start[1:] = ids[1:] != ids[:-1]
+    seg = torch.cumsum(start.to(torch.long), 0) - 1                      # run index of every element
+    first = torch.nonzero(start, as_tuple=True)[0]                       # first element of every run
+    rel = torch.arange(n, device=x.device) - first[seg]                  # position inside the run
+    longest = int(rel.max()) + 1
+    xd = x.double()
+    if gamma == 1.0:
+        w = xd
+    elif gamma ** longest > 1e-6:        # late elements lose log10(gamma ** -rel) digits in the scaled sum
+        w = xd * torch.pow(torch.tensor(gamma, dtype=torch.float64, device=x.device), rel.double())
+    else:
+        vals, out, acc = x.tolist(), [0.0] * n, 0.0
+        st = start.tolist()
+        for i in range(n - 1, -1, -1):
+            acc = vals[i] + (gamma * acc if (i + 1 < n and not st[i + 1]) else 0.0)
+            out[i] = acc
+        return torch.tensor(out, dtype=x.dtype, device=x.device)
+    c = torch.cumsum(w, 0)
+    total = torch.zeros(first.numel(), dtype=torch.float64, device=x.device).index_add_(0, seg, w)
+    before = c - w - (c - w)[first][seg]                                  # sum of the run's earlier elements
+    suffix = total[seg] - before
+    if gamma != 1.0:
+        suffix = suffix / torch.pow(torch.tensor(gamma, dtype=torch.float64, device=x.device), rel.double())
+    return suffix.to(x.dtype)
+
+
 @TrainerRegistry.register("grpo")
 class GRPOTrainer(LLMTrainer):
     def __init__(self, config, parallel_dims, **kw):
@@ -132,15 +167,7 @@ class GRPOTrainer(LLMTrainer):
         div = torch.where(have, logprob.detach().float() - torch.nan_to_num(t), torch.zeros_like(t))
         kl_adv = -d.kl_penalty_coef * div
         if d.kl_discount_factor != 0.0:
-            # discounted future sum inside each sequence: suffix sums via a reversed scan per segment
-            vals, ids = kl_adv.tolist(), b["seq_ids_sel"].tolist()
-            acc, res = 0.0, [0.0] * len(vals)
-            for i in range(len(vals) - 1, -1, -1):
-                if i + 1 < len(vals) and ids[i + 1] != ids[i]:
-                    acc = 0.0
-                acc = vals[i] + d.kl_discount_factor * acc
-                res[i] = acc
-            kl_adv = torch.tensor(res, dtype=kl_adv.dtype, device=kl_adv.device)
+            kl_adv = discounted_suffix_sum(kl_adv, b["seq_ids_sel"], float(d.kl_discount_factor))
         return b["adv_tok"] + kl_adv, div.sum() / have.sum().clamp_min(1)
 
     # ------------------------------------------------------------------ hooks a custom trainer may override
