@@ -437,6 +437,8 @@ class B200Config(_Section):
                                          # T / tp rows (the reference's plan; halves activation memory at tp 2).
                                          # Off by default: one 7B block fwd+bwd at tp 2 takes 6.57 ms without it,
                                          # 7.17 ms with it (library collectives), 8.14 ms with the fused kernels
+    sp_keep_gathered: bool = True        # keep the gathered inputs of column-parallel projections for their weight
+                                         # gradients (one all-gather less per projection in backward)
     sp_fused_kernels: bool = False       # sequence-parallel projections through the all-gather -> GEMM and
                                          # GEMM -> reduce-scatter kernels instead of library collectives + cuBLAS
     router_bias_update_rate: float = 1e-3  # DeepSeek-V3 load-balancing bias step per optimizer step (0 = frozen)

@@ -4,7 +4,8 @@
 
 * ``tp``: replicated activations, row-parallel outputs all-reduced by the library (the plan without sequence
   parallelism);
-* ``sp-library``: sequence-parallel plan, all-gather / reduce-scatter by the library around cuBLAS GEMMs;
+* ``sp-library``: sequence-parallel plan, all-gather / reduce-scatter by the library around cuBLAS GEMMs, gathered
+  inputs kept for the weight gradients (``sp-library-regather``: gathered again in backward instead);
 * ``sp-fused``: the same plan with the all-gather -> GEMM and GEMM -> reduce-scatter kernels over peer memory in
   forward and for the input gradients.
 
@@ -73,6 +74,9 @@ def main() -> None:
     res["tp"] = timed("tp")
     model.tp.sequence_parallel = True
     res["sp-library"] = timed("sp-library")
+    model.tp.keep_gathered = False
+    res["sp-library-regather"] = timed("sp-library-regather")
+    model.tp.keep_gathered = True
     model.tp.attach_fused(dev, T, args.dim, all_gather_k=args.dim)
     res["sp-fused"] = timed("sp-fused")
     if rank == 0:

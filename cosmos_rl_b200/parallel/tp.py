@@ -109,11 +109,17 @@ class _GatherGemm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, tp):
         ctx.tp = tp
-        ctx.save_for_backward(x, w)
         ag = tp.fused_ag
         if ag is not None and x.is_cuda and x.dtype == torch.bfloat16 and ag.fits(x.shape[0] * tp.size, x.shape[1]):
+            ctx.kept = False
+            ctx.save_for_backward(x, w)
             return ag.gemm(x.contiguous(), w)
-        return torch.nn.functional.linear(_gather_rows(x, tp.group, tp.size), w)
+        xg = _gather_rows(x, tp.group, tp.size)
+        # keeping the gathered rows for the weight gradient saves an all-gather in backward (communication then equals
+        # the plain tensor-parallel plan); dropping them keeps only T / tp rows alive per projection
+        ctx.kept = bool(tp.keep_gathered)
+        ctx.save_for_backward(xg if ctx.kept else x, w)
+        return torch.nn.functional.linear(xg, w)
 
     @staticmethod
     def backward(ctx, gy):
@@ -126,7 +132,7 @@ class _GatherGemm(torch.autograd.Function):
             gx = f.gemm_reduce_scatter(gy, w.t().contiguous())
         else:
             gx = _reduce_scatter_rows(gy @ w, tp.group, tp.size, tp.rank)
-        gw = gy.t() @ _gather_rows(x, tp.group, tp.size)
+        gw = gy.t() @ (x if ctx.kept else _gather_rows(x, tp.group, tp.size))
         return gx, gw, None
 
 
@@ -168,6 +174,7 @@ class TensorParallel:
         # column-parallel projections gather the sequence, row-parallel ones scatter it again
         # (cosmos_rl/policy/model/gpt/parallelize.py:244-327)
         self.sequence_parallel = False
+        self.keep_gathered = True          # sequence parallelism: keep gathered inputs for the weight gradients
 
     # ------------------------------------------------------------------ sequence-parallel building blocks
     def row_multiple(self, cuda: bool) -> int:

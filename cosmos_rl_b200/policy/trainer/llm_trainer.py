@@ -97,6 +97,7 @@ class LLMTrainer(Trainer):
             from ...models.gpt import GPT
             model.tp.sequence_parallel = bool(config.b200.sequence_parallel and type(model) is GPT
                                               and parallel_dims.pp == 1 and parallel_dims.cp == 1)
+            model.tp.keep_gathered = bool(config.b200.sp_keep_gathered)
         if parallel_dims.cp > 1:
             if not hasattr(model, "attach_context_parallel") or tp > 1 or parallel_dims.pp > 1:
                 raise NotImplementedError("cp_size > 1 needs a native model with tp_size == pp_size == 1")

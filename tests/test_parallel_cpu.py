@@ -180,6 +180,7 @@ def _tp_worker(rank, world, store, qk_norm, seq_parallel=False):
     hf_io.load_hf_state(shard, lambda k: state[k], state, cfg, world, rank)
     shard.tp = TensorParallel(dist.group.WORLD, world, rank)
     shard.tp.sequence_parallel = seq_parallel        # 21 tokens on 2 ranks: exercises the padding sequence too
+    shard.tp.keep_gathered = not qk_norm             # one variant keeps the gathered rows, the other gathers again
     if seq_parallel:
         shard.gradient_checkpointing = "swiglu"
     g = torch.Generator().manual_seed(2)
