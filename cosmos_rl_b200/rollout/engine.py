@@ -106,6 +106,8 @@ class RolloutEngine:
         self.use_graph = use_cuda_graph and self.cuda
         self.check_interval = check_interval if self.cuda else 1
         self.seed = seed
+        self.rep_penalty = 1.0
+        self.seen: Optional[torch.Tensor] = None     # [slots, vocab] tokens already in prompt / output (repetition penalty)
         self.tp = tp if tp is not None else getattr(model, "tp", None)
         if (self.tp is not None and self.cuda and getattr(self.tp, "fused", None) is None
                 and os.environ.get("COSMOS_B200_FUSED_TP", "1") != "0"):
@@ -226,6 +228,8 @@ class RolloutEngine:
                            lambda li, q, k, v: F.paged_decode(q, self.kv[li], bt, seq_lens, v_transposed=self.kv_vt,
                                                               scratch=scratch, **prefix))
         logits = self.model.logits(out)
+        if self.rep_penalty != 1.0:
+            logits = self._penalise(logits.float(), self.seen[:B])
         r = (self.step_counter % self.ring).long()
         if self.cuda:
             toks = torch.empty(B, dtype=torch.int64, device=self.device)
@@ -239,8 +243,16 @@ class RolloutEngine:
         self.out_lp.index_copy_(0, r, lps.unsqueeze(0) if B == self.S else
                                 torch.cat([lps, self.out_lp[0, B:]]).unsqueeze(0))
         self.last_tok[:B] = torch.where(act > 0, toks, self.last_tok[:B])
+        if self.rep_penalty != 1.0:
+            self.seen[:B].scatter_(1, toks[:, None], True)      # rows of idle slots are reset when a sequence moves in
         self.cur_len[:B] += act
         self.step_counter += 1
+
+    def _penalise(self, logits: torch.Tensor, seen: torch.Tensor) -> torch.Tensor:
+        """Repetition penalty on tokens that already occur in the prompt or the output: positive logits are divided
+        by the penalty, negative ones multiplied (the rule of the transformers / vLLM samplers)."""
+        p = self.rep_penalty
+        return torch.where(seen, torch.where(logits > 0, logits / p, logits * p), logits)
 
     def _prefix_scratch(self, B: int) -> torch.Tensor:
         need = B * self.hq * (self.max_shared + 1) * (self.d + 2)
@@ -303,6 +315,11 @@ class RolloutEngine:
             self.group_n = n
             self.invalidate_graphs()        # the decode graphs bake the group size into the attention launch
         self.prefix_pages.zero_()
+        if float(sp.repetition_penalty) != self.rep_penalty:
+            self.rep_penalty = float(sp.repetition_penalty)
+            self.invalidate_graphs()        # the penalty branch is part of the captured decode step
+        if self.rep_penalty != 1.0 and self.seen is None:
+            self.seen = torch.zeros(self.S, self.model.args.vocab_size, dtype=torch.bool, device=self.device)
         stop = set(sp.stop_token_ids)
         if sp.seed is not None:
             self.seed = sp.seed
@@ -332,6 +349,11 @@ class RolloutEngine:
                 return
             logits = self._prefill([b[1] for b in batch], page_lists)
             # first token of each of the n samples comes from the prompt's last-position logits
+            if self.rep_penalty != 1.0:
+                pmask = torch.zeros(len(batch), logits.shape[1], dtype=torch.bool, device=self.device)
+                for bi, (_, p, _) in enumerate(batch):
+                    pmask[bi, torch.as_tensor(p, dtype=torch.long, device=self.device)] = True
+                logits = self._penalise(logits, pmask)
             rep = logits.repeat_interleave(n, dim=0)
             B0 = rep.shape[0]
             t = torch.full((B0,), sp.temperature, dtype=torch.float32, device=self.device)
@@ -365,6 +387,12 @@ class RolloutEngine:
                 self._release(pp)  # drop the prefill's own reference; children hold theirs
             # publish the new sequences' state to the device in one shot
             idx = torch.tensor([s[0] for s in slots_taken], dtype=torch.long, device=self.device)
+            if self.rep_penalty != 1.0:
+                rows = pmask.repeat_interleave(n, dim=0).clone()
+                rows.scatter_(1, first_tok[:, None], True)
+                order = {slot: k for k, slot in enumerate(grp * n + si for grp in batch_groups for si in range(n))}
+                self.seen.index_copy_(0, idx, rows[torch.tensor([order[s_[0]] for s_ in slots_taken],
+                                                               dtype=torch.long, device=self.device)])
             bt = torch.zeros(len(slots_taken), self.max_pages_per_seq, dtype=torch.int32)
             for i, (_, pages, _, _, _) in enumerate(slots_taken):
                 bt[i, : len(pages)] = torch.tensor(pages, dtype=torch.int32)

@@ -304,3 +304,32 @@ def test_vision_language_model_through_wrapper_packer_and_trainers(tmp_path):
     ros = [Rollout(prompt=prompt, completion=t, advantage=adv, reward=adv) for t, adv in zip(res[0].completion_token_ids, (1.0, -1.0))]
     rep = gt.step_training(ros, 1, 10)
     assert rep["train/grad_norm"] > 0 and torch.isfinite(torch.tensor(rep["train/loss_avg"]))
+
+
+def test_engine_repetition_penalty_matches_step_by_step_rule():
+    """Greedy decoding with a repetition penalty: the engine's tokens equal a plain loop that divides positive / multiplies
+    negative logits of every token already in the prompt or the output."""
+    m = _tiny()
+    eng = RolloutEngine(m, max_num_seqs=4, max_model_len=64, page_size=16, use_cuda_graph=False)
+    prompts = [[5, 9, 9, 120, 7], [31000, 2, 2]]
+    sp = SamplingParams(n=2, max_tokens=6, temperature=0.0, repetition_penalty=1.8)
+    out = eng.generate(prompts, sp)
+    assert eng.seen is not None and eng.rep_penalty == 1.8
+    plain = eng.generate(prompts, SamplingParams(n=1, max_tokens=6, temperature=0.0))
+    assert eng.rep_penalty == 1.0
+    for p, comps, base in zip(prompts, out, plain):
+        seq, seen = list(p), set(p)
+        want = []
+        for _ in range(6):
+            ids = torch.tensor(seq)
+            with torch.no_grad():
+                h = m(ids, torch.arange(len(seq)), torch.tensor([0, len(seq)]), len(seq))
+                logits = m.logits(h[-1:])[0].float()
+            idx = torch.tensor(sorted(seen))
+            logits[idx] = torch.where(logits[idx] > 0, logits[idx] / 1.8, logits[idx] * 1.8)
+            t = int(logits.argmax())
+            want.append(t)
+            seq.append(t)
+            seen.add(t)
+        assert comps[0].token_ids == want and comps[1].token_ids == want
+        assert len(base[0].token_ids) == 6
