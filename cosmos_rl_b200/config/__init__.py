@@ -409,10 +409,10 @@ class DistillationConfig(_Section):
     batch_size_per_replica: int = 8
     max_token_len_per_mini_batch: Optional[int] = None
     sequence_packing: bool = False
-    mini_batch: int = 2
+    mini_batch: int = 1
     seed: Optional[int] = None
     kl_penalty_coef: float = 1.0
-    kl_discount_factor: float = 1.0
+    kl_discount_factor: float = 0.0
     include_prompt: bool = False
     top_k: int = 0
     jsd_beta: float = 0.5

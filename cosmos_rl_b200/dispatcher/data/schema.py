@@ -51,6 +51,8 @@ class Rollout(BaseModel):
     completion: Any = ""
     teacher_result_uuid: str = ""
     teacher_logprobs: Optional[List[List[float]]] = None
+    teacher_topk_ids: Optional[List[List[int]]] = None        # per completion token: the teacher's k most likely ids
+    teacher_topk_logprobs: Optional[List[List[float]]] = None
     completed_conversation: Optional[ConversationType] = None
     is_end: bool = False
     reward: float = 0.0

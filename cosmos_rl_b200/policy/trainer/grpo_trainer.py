@@ -8,6 +8,8 @@ token budget (``max_token_len_per_mini_batch``) and always packed (no padding re
 """
 from __future__ import annotations
 
+import math
+
 import time
 from typing import Any, Dict, List, Optional, Sequence
 
@@ -23,13 +25,14 @@ from .llm_trainer import LLMTrainer
 
 
 class _Sample:
-    __slots__ = ("ids", "mask", "advantage", "reward", "rollout_lp", "n_scored", "mm", "teacher_lp")
+    __slots__ = ("ids", "mask", "advantage", "reward", "rollout_lp", "n_scored", "mm", "teacher_lp", "teacher_topk")
 
-    def __init__(self, ids, mask, advantage, reward, rollout_lp, mm=None, teacher_lp=None):
+    def __init__(self, ids, mask, advantage, reward, rollout_lp, mm=None, teacher_lp=None, teacher_topk=None):
         self.ids, self.mask, self.advantage, self.reward, self.rollout_lp = ids, mask, advantage, reward, rollout_lp
         self.n_scored = int(sum(mask))
         self.mm = mm            # vision inputs of a vision-language sample
         self.teacher_lp = teacher_lp   # per scored token, from the distillation teacher
+        self.teacher_topk = teacher_topk   # (ids [n_scored][k], log-probs [n_scored][k]) of the teacher's k best tokens
 
 
 def discounted_suffix_sum(x: torch.Tensor, seq_ids: torch.Tensor, gamma: float) -> torch.Tensor:
@@ -102,7 +105,10 @@ class GRPOTrainer(LLMTrainer):
             tlp = None
             if r.teacher_logprobs:
                 tlp = [pos[0] for pos in r.teacher_logprobs][r.n_ignore_prefix_tokens:]
-            out.append(_Sample(ids, mask, float(r.advantage), float(r.reward), lp, mm, tlp))
+            topk = None
+            if r.teacher_topk_ids and r.teacher_topk_logprobs:
+                topk = (r.teacher_topk_ids[r.n_ignore_prefix_tokens:], r.teacher_topk_logprobs[r.n_ignore_prefix_tokens:])
+            out.append(_Sample(ids, mask, float(r.advantage), float(r.reward), lp, mm, tlp, topk))
         return out
 
     def _mini_batches(self, samples: List[_Sample]) -> List[List[int]]:
@@ -132,6 +138,22 @@ class GRPOTrainer(LLMTrainer):
                     tlp_full[scored[pos:pos + s_.n_scored]] = torch.tensor(s_.teacher_lp, dtype=torch.float32,
                                                                             device=self.device)
                 pos += s_.n_scored
+        k = int(self.config.distillation.top_k) if self.config.distillation.enable else 0
+        tk_ids = tk_lp = None
+        if k > 0:
+            # the teacher's k best tokens per scored position (ids -1 where a sample came without a teacher result)
+            T_all = b["label_ids"].numel()
+            tk_ids = torch.full((T_all, k), -1, dtype=torch.long, device=self.device)
+            tk_lp = torch.zeros(T_all, k, dtype=torch.float32, device=self.device)
+            scored = (b["label_ids"] >= 0).nonzero(as_tuple=True)[0]
+            pos = 0
+            for s_ in samples:
+                tk = s_.teacher_topk
+                if tk is not None and len(tk[0]) == s_.n_scored and s_.n_scored and len(tk[0][0]) == k:
+                    rows = scored[pos:pos + s_.n_scored]
+                    tk_ids[rows] = torch.tensor(tk[0], dtype=torch.long, device=self.device)
+                    tk_lp[rows] = torch.tensor(tk[1], dtype=torch.float32, device=self.device)
+                pos += s_.n_scored
         cu_full = b["cu_seqlens"]
         b = self.cp_shard(b)
         if any(s.mm for s in samples):
@@ -154,6 +176,12 @@ class GRPOTrainer(LLMTrainer):
                 from ...parallel.context_parallel import split_for_cp
                 tlp_full = split_for_cp(tlp_full, cu_full, self.parallel_dims.cp, self.parallel_dims.cp_coord)
             b["teacher_lp"] = tlp_full[sel]
+        if tk_ids is not None:
+            if self.parallel_dims.cp > 1:
+                from ...parallel.context_parallel import split_for_cp
+                tk_ids = split_for_cp(tk_ids, cu_full, self.parallel_dims.cp, self.parallel_dims.cp_coord)
+                tk_lp = split_for_cp(tk_lp, cu_full, self.parallel_dims.cp, self.parallel_dims.cp_coord)
+            b["teacher_topk_ids"], b["teacher_topk_lp"] = tk_ids[sel], tk_lp[sel]
         return b
 
     def teacher_kl_advantages(self, logprob: torch.Tensor, b: Dict[str, Any]):
@@ -170,22 +198,62 @@ class GRPOTrainer(LLMTrainer):
             kl_adv = discounted_suffix_sum(kl_adv, b["seq_ids_sel"], float(d.kl_discount_factor))
         return b["adv_tok"] + kl_adv, div.sum() / have.sum().clamp_min(1)
 
+    def teacher_topk_jsd_advantages(self, b: Dict[str, Any]):
+        """Top-k distillation (``distillation.top_k > 0``): the divergence of a token is the generalised Jensen-Shannon
+        divergence between teacher and student restricted to the teacher's k most likely tokens,
+        ``beta * KL(t || m) + (1 - beta) * KL(s || m)`` with ``m = beta * t + (1 - beta) * s``; ``beta = 0`` is the
+        forward KL ``sum t (log t - log s)`` and ``beta = 1`` the reverse one. It is subtracted from the advantages
+        like the single-token estimate (cosmos_rl/policy/trainer/llm_trainer/grpo_trainer.py:716-787)."""
+        d = self.config.distillation
+        s, t, ids = b["student_topk_lp"], b["teacher_topk_lp"], b["teacher_topk_ids"]
+        have = ids[:, 0] >= 0
+        beta = float(d.jsd_beta)
+        if beta == 0.0:
+            div = t.exp() * (t - s)
+        elif beta == 1.0:
+            div = s.exp() * (s - t)
+        else:
+            m = torch.logaddexp(s + math.log1p(-beta), t + math.log(beta))
+            div = beta * t.exp() * (t - m) + (1.0 - beta) * s.exp() * (s - m)
+        div = torch.where(have, div.sum(-1), torch.zeros_like(div[:, 0]))
+        kl_adv = -d.kl_penalty_coef * div
+        if d.kl_discount_factor != 0.0:
+            kl_adv = discounted_suffix_sum(kl_adv, b["seq_ids_sel"], float(d.kl_discount_factor))
+        return b["adv_tok"] + kl_adv, div.sum() / have.sum().clamp_min(1)
+
+    @torch.no_grad()
+    def _student_topk_logprobs(self, hidden_sel: torch.Tensor, ids: torch.Tensor, chunk: int = 2048) -> torch.Tensor:
+        """Student log-probs at the teacher's top-k ids, [n, k] fp32; full-vocabulary logits exist for ``chunk`` rows
+        at a time only."""
+        out = torch.zeros(ids.shape, dtype=torch.float32, device=ids.device)
+        for i in range(0, ids.shape[0], chunk):
+            lg = self.model.logits(hidden_sel[i:i + chunk]).float() / self.temperature
+            out[i:i + chunk] = torch.log_softmax(lg, -1).gather(1, ids[i:i + chunk].clamp_min(0))
+        return out
+
     # ------------------------------------------------------------------ hooks a custom trainer may override
     def compute_logprobs(self, hidden: torch.Tensor, b: Dict[str, Any]):
         """(per-token log-probs, entropies) of the scored tokens of a packed batch from the final hidden states."""
-        return self.model.logprobs(hidden[b["sel"]], b["labels_sel"], self.temperature)
+        hs = hidden[b["sel"]]
+        if "teacher_topk_ids" in b and "student_topk_lp" not in b:
+            # advantage shaping only (no gradient): taken once, from the weights the batch is first scored with
+            b["student_topk_lp"] = self._student_topk_logprobs(hs.detach(), b["teacher_topk_ids"])
+        return self.model.logprobs(hs, b["labels_sel"], self.temperature)
 
     def loss_fn(self, logprob, old_logprob, b: Dict[str, Any], ref_logprob=None, entropy=None, total_tokens=None):
         """(scalar loss, metrics) of one packed batch; the default is the configured GRPO / DAPO / GSPO objective
         (cosmos_rl/tools/custom_example/README.md lists the same override points)."""
-        adv, teacher_kl = b["adv_tok"], None
-        if "teacher_lp" in b:
+        adv, teacher_kl, kl_name = b["adv_tok"], None, "teacher_kl_reversed"
+        if "student_topk_lp" in b:
+            adv, teacher_kl = self.teacher_topk_jsd_advantages(b)
+            kl_name = f"teacher_jsd_top{b['teacher_topk_ids'].shape[1]}"
+        elif "teacher_lp" in b:
             adv, teacher_kl = self.teacher_kl_advantages(logprob, b)
         loss, metrics = grpo_loss(logprob, old_logprob, adv, b["seq_ids_sel"], int(b["cu_seqlens"].numel() - 1),
                                   self.loss_cfg, ref_logprob=ref_logprob, rollout_logprob=b.get("rollout_lp"),
                                   entropy=entropy, seq_rewards=b["seq_rewards"], total_tokens=total_tokens)
         if teacher_kl is not None:
-            metrics["teacher_kl_reversed"] = teacher_kl.detach()
+            metrics[kl_name] = teacher_kl.detach()
         return loss, metrics
 
     def _logprobs_of(self, hidden, b: Dict[str, Any]):

@@ -242,6 +242,8 @@ class RLPolicyWorker(CommMixin):
                     res = fetch_teacher_result(self.broker, r.teacher_result_uuid, timeout_s=120.0)
                     if res is not None:
                         r.teacher_logprobs = [[v] for v in res["logprobs"]]
+                        if res.get("topk_ids"):
+                            r.teacher_topk_ids, r.teacher_topk_logprobs = res["topk_ids"], res["topk_logprobs"]
                     else:
                         logger.warning("[Policy] no teacher result for %s: the rollout trains without it",
                                        r.teacher_result_uuid)

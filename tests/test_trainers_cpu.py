@@ -1,6 +1,8 @@
 """CPU tests of the SFT and DPO trainers and of the GRPO loss variants against hand-written statements."""
 import math
 
+import pytest
+
 import torch
 
 from cosmos_rl_b200.config import Config
@@ -279,3 +281,59 @@ def test_on_policy_distillation_advantages(tmp_path):
     assert abs(kl.item() - ((-0.5) + 1.0 + 0.0) / 3) < 1e-6
     rep = tr.step_training(ros, 1, 10)
     assert "train/teacher_kl_reversed" in rep and rep["train/grad_norm"] > 0
+
+
+@pytest.mark.parametrize("beta", [0.0, 0.5, 1.0])
+def test_topk_jsd_distillation_advantages(tmp_path, beta):
+    """``distillation.top_k``: the teacher engine returns its k best tokens per completion token; the trainer scores
+    the student on the same ids and subtracts the generalised JSD (forward KL at beta 0, reverse KL at beta 1) from
+    the advantages. Checked against torch.nn.functional.kl_div on the same top-k slices."""
+    import torch
+    import torch.nn.functional as tF
+    from cosmos_rl_b200.dispatcher.data.schema import Rollout
+    from cosmos_rl_b200.policy.trainer.grpo_trainer import GRPOTrainer
+    from cosmos_rl_b200.reference.teacher_worker import TeacherEngine
+    k = 4
+    c = Config.from_dict({
+        "policy": {"model_name_or_path": "tiny-qwen2", "model_max_length": 64, "model_gradient_checkpointing": False},
+        "distillation": {"enable": True, "model_name_or_path": "tiny-qwen2", "kl_penalty_coef": 1.5, "top_k": k,
+                         "jsd_beta": beta, "seed": 7},
+        "train": {"seed": 0, "optm_lr": 1e-3, "optm_warmup_steps": 0, "output_dir": str(tmp_path),
+                  "train_policy": {"type": "grpo", "trainer_type": "grpo", "mini_batch": 4},
+                  "ckpt": {"enable_checkpoint": False}}})
+    dims = ParallelDims(world_size=1, device=torch.device("cpu"))
+    tr = GRPOTrainer(c, dims, device=torch.device("cpu"))
+    tr.model_load_from_hf()
+    teacher = TeacherEngine(c, torch.device("cpu"), dims)
+    g = torch.Generator().manual_seed(0)
+    prompts = [[5, 6, 7], [8, 9]]
+    comp = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (3, 2)]
+    res = teacher.score([p + c_ for p, c_ in zip(prompts, comp)], [len(p) for p in prompts])
+    assert len(res[0]["topk_ids"]) == 3 and len(res[0]["topk_ids"][0]) == k
+    ros = [Rollout(prompt=prompts[0], completion=comp[0], advantage=0.5, reward=1.0,
+                   teacher_logprobs=[[v] for v in res[0]["logprobs"]], teacher_topk_ids=res[0]["topk_ids"],
+                   teacher_topk_logprobs=res[0]["topk_logprobs"]),
+           Rollout(prompt=prompts[1], completion=comp[1], advantage=-0.5, reward=0.0)]        # no teacher result
+    b = tr._pack(tr._prepare(ros))
+    assert b["teacher_topk_ids"].shape == (5, k) and (b["teacher_topk_ids"][3:] == -1).all()
+    with torch.no_grad():
+        hidden = tr.model(b["input_ids"], b["position_ids"], b["cu_seqlens"], b["max_seqlen"])
+        tr.compute_logprobs(hidden, b)
+        full = torch.log_softmax(tr.model.logits(hidden[b["sel"]]).float(), -1)
+    s = full.gather(1, b["teacher_topk_ids"].clamp_min(0))
+    assert torch.allclose(b["student_topk_lp"], s, atol=1e-5)
+    t = b["teacher_topk_lp"]
+    if beta == 0.0:
+        want = tF.kl_div(s, t, reduction="none", log_target=True)
+    elif beta == 1.0:
+        want = tF.kl_div(t, s, reduction="none", log_target=True)
+    else:
+        m = torch.logsumexp(torch.stack([s + math.log(1 - beta), t + math.log(beta)]), 0)
+        want = beta * tF.kl_div(m, t, reduction="none", log_target=True) + \
+            (1 - beta) * tF.kl_div(m, s, reduction="none", log_target=True)
+    want = want.sum(-1)
+    adv, div = tr.teacher_topk_jsd_advantages(b)
+    assert torch.allclose(adv[:3], 0.5 - 1.5 * want[:3], atol=1e-5) and torch.allclose(adv[3:], torch.tensor([-0.5, -0.5]))
+    assert abs(div.item() - want[:3].mean().item()) < 1e-5     # truncated to k tokens the sum may be negative
+    rep = tr.step_training(ros, 1, 10)
+    assert f"train/teacher_jsd_top{k}" in rep and rep["train/grad_norm"] > 0
