@@ -18,12 +18,22 @@ class TrainerRegistry:
     @classmethod
     def get_trainer_cls(cls, trainer_type: str) -> Type["Trainer"]:
         if trainer_type not in cls._trainers:
+            cls._load_builtin()
+        if trainer_type not in cls._trainers:
             raise KeyError(f"unknown trainer type {trainer_type!r}; known: {sorted(cls._trainers)}")
         return cls._trainers[trainer_type]
 
     @classmethod
     def known(cls) -> List[str]:
+        cls._load_builtin()
         return sorted(cls._trainers)
+
+    @classmethod
+    def _load_builtin(cls) -> None:
+        """Import the trainers that ship with the package (each registers itself on import)."""
+        import importlib
+        for m in ("sft_trainer", "dpo_trainer", "grpo_trainer", "diffusion_trainer", "vla_trainer"):
+            importlib.import_module(f"{__package__}.{m}")
 
 
 class Trainer(ABC):

@@ -53,6 +53,20 @@ class SFTPolicyWorker(CommMixin):
         if config.train.max_num_steps:
             self.total_steps = min(self.total_steps, config.train.max_num_steps)
         self.history: List[dict] = []
+        self.balancer = None
+        if tp.enable_dp_load_balancing and self.dataset is not None:
+            # token-budgeted batches from a per-rank pool instead of a fixed sample count per rank; the cost of a
+            # batch is the sum of its lengths because the trainers concatenate sequences instead of padding them
+            from ...data.load_balanced import LoadBalancedBatcher
+            self.balancer = LoadBalancedBatcher(
+                self.dataset, pool_size=tp.load_balanced_pool_size,
+                max_tokens_for_batch=tp.load_balanced_max_tokens_for_batch or config.policy.model_max_length,
+                batching_strategy=tp.load_balanced_batching_strategy, max_tokens_len=config.policy.model_max_length,
+                packed=True, seed=tp.dataloader_seed, shuffle=tp.dataloader_shuffle, dp_rank=self.dp_rank,
+                dp_world_size=self.dp, accumulate_steps=tp.load_balanced_batches_per_optimizer_step,
+                process_fn=self.trainer.data_packer.sft_process_sample)
+            if self.start_step:
+                self.balancer.skip_steps(self.start_step)
 
     def _epoch_order(self, epoch: int) -> List[int]:
         tp = self.config.train.train_policy
@@ -63,6 +77,8 @@ class SFTPolicyWorker(CommMixin):
 
     def _batch(self, step: int) -> List[Any]:
         """Samples of this data-parallel rank for global step ``step`` (0-based)."""
+        if self.balancer is not None:
+            return [s for b in self.balancer.next_step() for s in b]
         epoch, k = divmod(step, max(1, self.steps_per_epoch))
         order = self._epoch_order(epoch)
         per_step = self.batch_per_rank * self.dp
