@@ -143,6 +143,7 @@ class LLMTrainer(Trainer):
         self.train_step = 0
         self.total_steps = 0
         self.weights_ready = False
+        self.ema = None          # ShardEMA when train.ema_enable (created once the weights are in place)
 
     # ------------------------------------------------------------------
     def resolve_recompute(self, max_tokens: int) -> None:
@@ -190,6 +191,8 @@ class LLMTrainer(Trainer):
         """One optimizer step plus what rides on it (the router bias of DeepSeek-style MoE blocks, moved from the
         expert load of the batch summed over the data-parallel ranks). Returns the gradient norm."""
         norm = self.optimizer.step(self.lr_scale(self.train_step))
+        if self.ema is not None:
+            self.ema.step(self.optimizer.step_count - 1)
         rate = self.config.b200.router_bias_update_rate
         if rate > 0 and hasattr(self.model, "update_router_bias"):
             dims = self.parallel_dims
@@ -270,7 +273,16 @@ class LLMTrainer(Trainer):
             from .. import lora
             lora.reset_lora_parameters(self.model, self.config.train.seed or 0)
         self.optimizer.refresh_master_from_params()
+        self._init_ema()
         self.weights_ready = True
+
+    def _init_ema(self) -> None:
+        """``train.ema_enable``: a moving average of the trained weights on the optimizer shard; exports and
+        validation read it (cosmos_rl/policy/trainer/diffusers_trainer/diffusers_trainer.py:130-146)."""
+        t = self.config.train
+        if t.ema_enable:
+            from ...utils.ema import ShardEMA
+            self.ema = ShardEMA(self.optimizer, t.ema_decay, t.ema_update_step_interval)
 
     # ------------------------------------------------------------------ adapters around weight hand-over
     def before_weight_sync(self) -> None:
@@ -291,6 +303,9 @@ class LLMTrainer(Trainer):
             return False
         self.flat.data.copy_(state["model"]["flat"].to(self.flat.dtype))
         self.optimizer.load_state_dict(state["optimizer"])
+        self._init_ema()
+        if self.ema is not None and state["model"].get("ema") is not None:
+            self.ema.load_state_dict(state["model"]["ema"])
         extra = state["extra_info"]
         self.train_step = int(extra.get("step", 0))
         self.total_steps = int(extra.get("total_steps", 0))
@@ -312,12 +327,19 @@ class LLMTrainer(Trainer):
                         **kw) -> None:
         extra = {"step": step, "total_steps": total_steps, "remain_samples_num": remain_samples_num,
                  "is_final": is_final}
-        self.ckpt_manager.save(step, model_state={"flat": self.flat.data, "slots": [s.__dict__ for s in self.flat.slots]},
+        model_state = {"flat": self.flat.data, "slots": [s.__dict__ for s in self.flat.slots]}
+        if self.ema is not None:
+            model_state["ema"] = self.ema.state_dict()
+        self.ckpt_manager.save(step, model_state=model_state,
                                optimizer_state=self.optimizer.state_dict(), scheduler_state={"step": step},
                                extra_info=extra, is_final=is_final)
         if self.config.train.ckpt.export_safetensors:
             out = os.path.join(self.config.train.output_dir, "safetensors", f"step_{step}")
-            self.export_safetensors(out)
+            if self.ema is not None:            # the exported model is the averaged one; training resumes from the raw one
+                with self.ema.swapped_in():
+                    self.export_safetensors(out)
+            else:
+                self.export_safetensors(out)
         hook = self.hook_fns.get("save_checkpoint_hook")
         if hook:
             hook(step=step, trainer=self)
@@ -343,7 +365,12 @@ class LLMTrainer(Trainer):
         """Every tensor a new policy replica needs to continue identically: weights, optimizer state, step."""
         meta = torch.tensor([self.train_step, self.total_steps, self.optimizer.step_count], dtype=torch.int64,
                             device=self.device)
-        return [("flat.data", self.flat.data), *self.optimizer.state_tensors(), ("meta", meta)]
+        if self.ema is None:
+            self._init_ema()                    # a receiving replica has not loaded weights yet
+        ema = [("ema.shard", self.ema.shard)] if self.ema is not None else []
+        if ema and self.ema.tail is not None:
+            ema.append(("ema.tail", self.ema.tail))
+        return [("flat.data", self.flat.data), *self.optimizer.state_tensors(), *ema, ("meta", meta)]
 
     def after_state_received(self, meta: torch.Tensor) -> None:
         self.train_step, self.total_steps, self.optimizer.step_count = (int(x) for x in meta.tolist())

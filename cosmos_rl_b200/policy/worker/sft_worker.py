@@ -4,6 +4,7 @@
 the elastic inter-replica communicator, as in cosmos_rl/policy/worker/multi_replica_sft_worker.py:44-565."""
 from __future__ import annotations
 
+import contextlib
 import random
 from typing import Any, List, Optional
 
@@ -90,10 +91,12 @@ class SFTPolicyWorker(CommMixin):
             return None
         bs = self.config.validation.batch_size or self.batch_per_rank
         total, n = 0.0, 0
-        for i in range(self.dp_rank * bs, len(self.val_dataset), bs * self.dp):
-            batch = [self.val_dataset[j] for j in range(i, min(i + bs, len(self.val_dataset)))]
-            total += self.trainer.step_validation(batch).get("val/loss", 0.0)
-            n += 1
+        ema = getattr(self.trainer, "ema", None)
+        with (ema.swapped_in() if ema is not None else contextlib.nullcontext()):   # the averaged weights are scored
+            for i in range(self.dp_rank * bs, len(self.val_dataset), bs * self.dp):
+                batch = [self.val_dataset[j] for j in range(i, min(i + bs, len(self.val_dataset)))]
+                total += self.trainer.step_validation(batch).get("val/loss", 0.0)
+                n += 1
         score = -total / max(n, 1)
         self.trainer.ckpt_manager.report_validation_score(step, score)
         logger.info("[SFT] validation at step %d: loss=%.4f", step, -score)

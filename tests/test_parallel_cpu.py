@@ -275,7 +275,10 @@ def _zero_worker(rank, world, store):
     m.init_weights(0)
     opt = FlatAdamW(flat, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, max_grad_norm=1.0,
                     dp_group=dist.group.WORLD)
+    from cosmos_rl_b200.utils.ema import ShardEMA
+    ema = ShardEMA(opt, decay=0.5)
     w = flat.data.clone()
+    ema_full = w.clone()
     mm, vv = torch.zeros_like(w), torch.zeros_like(w)
     for step in range(1, 4):
         g = torch.Generator().manual_seed(100 * step + rank)
@@ -287,6 +290,14 @@ def _zero_worker(rank, world, store):
         assert abs(norm.item() - avg.norm().item()) < 1e-5
         R.adamw_step(w, mm, vv, avg, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, grad_scale=min(1.0, 1.0 / (avg.norm().item() + 1e-6)))
         assert torch.allclose(flat.data, w, atol=1e-6), (flat.data - w).abs().max()
+        ema.step(step - 1)
+        d = min(step / (9 + step), 0.5)
+        ema_full = d * ema_full + (1 - d) * w
+    # the average lives on the shard; swapping it in gathers it into every rank's live buffer and back out again
+    assert ema.shard.numel() == flat.total // world
+    with ema.swapped_in():
+        assert torch.allclose(flat.data, ema_full, atol=1e-6)
+    assert torch.allclose(flat.data, w, atol=1e-6)
     dist.destroy_process_group()
 
 

@@ -337,3 +337,36 @@ def test_topk_jsd_distillation_advantages(tmp_path, beta):
     assert abs(div.item() - want[:3].mean().item()) < 1e-5     # truncated to k tokens the sum may be negative
     rep = tr.step_training(ros, 1, 10)
     assert f"train/teacher_jsd_top{k}" in rep and rep["train/grad_norm"] > 0
+
+
+def test_ema_tracks_weights_on_the_optimizer_shard_and_is_exported(tmp_path):
+    """``train.ema_enable``: after every optimizer step the average moves towards the fp32 master weights with the
+    warm-up decay; exports read the averaged weights and leave the trained ones in place; checkpoints carry it."""
+    import torch
+    from cosmos_rl_b200.policy.trainer.sft_trainer import SFTTrainer
+    c = _config(tmp_path, "sft")
+    c.train.ema_enable, c.train.ema_decay, c.train.ema_update_step_interval = True, 0.9, 1
+    c.train.ckpt.enable_checkpoint = True
+    dims = ParallelDims(world_size=1, device=torch.device("cpu"))
+    tr = SFTTrainer(c, dims, device=torch.device("cpu"))
+    tr.model_load_from_hf()
+    assert tr.ema is not None and torch.equal(tr.ema.shard, tr.optimizer.master)
+    g = torch.Generator().manual_seed(0)
+    batch = [{"input_ids": torch.randint(0, 32000, (12,), generator=g).tolist()} for _ in range(4)]
+    want = tr.optimizer.master.clone()
+    for step in range(3):
+        tr.step_training(batch, 10, step + 1)
+        d = min((1 + step) / (10 + step), 0.9)
+        want = d * want + (1 - d) * tr.optimizer.master
+    assert torch.allclose(tr.ema.shard, want, atol=1e-6)
+    assert not torch.allclose(tr.ema.shard, tr.optimizer.master)
+    live = tr.flat.data.clone()
+    with tr.ema.swapped_in():
+        assert torch.allclose(tr.flat.data.float(), tr.ema.shard, atol=1e-6)
+    assert torch.equal(tr.flat.data, live)
+    tr.save_checkpoint(3, 10)
+    tr.ckpt_manager.finalize()
+    c.train.resume = True
+    tr2 = SFTTrainer(c, dims, device=torch.device("cpu"))
+    assert tr2.weight_resume() and torch.equal(tr2.ema.shard, tr.ema.shard) and tr2.ema.updates == 3
+    assert any(n == "ema.shard" for n, _ in tr2.state_tensors())
