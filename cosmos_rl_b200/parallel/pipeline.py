@@ -45,6 +45,16 @@ def schedule_1f1b(stage: int, n_stages: int, n_micro: int) -> List[tuple]:
     return steps
 
 
+def schedule_gpipe(stage: int, n_stages: int, n_micro: int) -> List[tuple]:
+    """Fill-drain: every forward, then every backward (more activations alive than 1F1B, same bubble)."""
+    return [("F", i) for i in range(n_micro)] + [("B", i) for i in range(n_micro)]
+
+
+SCHEDULES = {"1F1B": schedule_1f1b, "GPipe": schedule_gpipe,
+             # one stage per rank here: the multi-stage name of the reference's default selects plain 1F1B
+             "Interleaved1F1B": schedule_1f1b}
+
+
 class PipelineStage:
     """Runs one stage of ``model`` (built with ``pp_size`` / ``pp_rank``) over a list of micro-batches.
 
@@ -52,7 +62,10 @@ class PipelineStage:
     for accumulation over micro-batches by the caller. Returns the list of losses (last stage) or ``[]``."""
 
     def __init__(self, model, group, stage: int, n_stages: int, hidden_dim: int, dtype: torch.dtype,
-                 device: torch.device):
+                 device: torch.device, schedule: str = "1F1B"):
+        if schedule not in SCHEDULES:
+            raise ValueError(f"pp_schedule must be one of {sorted(SCHEDULES)}, got {schedule!r}")
+        self.schedule = SCHEDULES[schedule]
         self.model, self.group, self.stage, self.n = model, group, stage, n_stages
         self.hidden_dim, self.dtype, self.device = hidden_dim, dtype, device
         ranks = dist.get_process_group_ranks(group) if group is not None else list(range(n_stages))
@@ -71,7 +84,7 @@ class PipelineStage:
         pending: List[Any] = []
         keep: List[torch.Tensor] = []          # buffers of sends in flight
         losses: List[torch.Tensor] = []
-        for kind, i in schedule_1f1b(self.stage, self.n, len(micro_batches)):
+        for kind, i in self.schedule(self.stage, self.n, len(micro_batches)):
             mb = micro_batches[i]
             if kind == "F":
                 if first:

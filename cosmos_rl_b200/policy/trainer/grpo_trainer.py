@@ -116,6 +116,8 @@ class GRPOTrainer(LLMTrainer):
         if budget:
             return token_budget_batches([len(s.ids) for s in samples], budget * self.parallel_dims.cp)
         mb = max(1, self.tp_cfg.mini_batch)
+        if self.parallel_dims.pp > 1:           # the packed batches are the micro-batches of the pipeline schedule
+            mb = max(1, self.config.policy.parallelism.pp_micro_batch_size)
         return [list(range(i, min(i + mb, len(samples)))) for i in range(0, len(samples), mb)]
 
     def _pack(self, samples: List[_Sample]) -> Dict[str, Any]:

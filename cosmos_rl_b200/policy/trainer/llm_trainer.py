@@ -110,7 +110,8 @@ class LLMTrainer(Trainer):
                 raise NotImplementedError("pp_size > 1 needs a native model and tp_size == 1")
             from ...parallel.pipeline import PipelineStage
             self.pipeline = PipelineStage(model, parallel_dims.group("pp"), parallel_dims.pp_coord, parallel_dims.pp,
-                                          model.args.dim, self.param_dtype, self.device)
+                                          model.args.dim, self.param_dtype, self.device,
+                                          schedule=config.policy.parallelism.pp_schedule)
         from ...utils.extension import parallelism_strategy
         custom_plan = parallelism_strategy(mt)
         if custom_plan is not None:
@@ -211,10 +212,13 @@ class LLMTrainer(Trainer):
         evaluated on the last stage only; the returned (detached) losses are empty on the other stages."""
         if self.pipeline is not None:
             return self.pipeline.run(self._micro(batches), lambda h, mb: loss_of(h, mb.extra[0], mb.extra[1]))
+        from ...utils.activation_offloading import maybe_offload
         losses = []
         for i, b in enumerate(batches):
             self._set_mm(b)
-            loss = loss_of(self.model(b["input_ids"], b["position_ids"], b["cu_seqlens"], b["max_seqlen"]), i, b)
+            # train.activation_offload: saved activations of at least 1 MiB wait in pinned host memory for backward
+            with maybe_offload(self.config.train.activation_offload, self.model):
+                loss = loss_of(self.model(b["input_ids"], b["position_ids"], b["cu_seqlens"], b["max_seqlen"]), i, b)
             loss.backward()
             losses.append(loss.detach())
         return losses

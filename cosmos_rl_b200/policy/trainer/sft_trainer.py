@@ -37,6 +37,8 @@ class SFTTrainer(LLMTrainer):
         if budget:
             return token_budget_batches([len(s["input_ids"]) for s in processed], budget)
         mb = max(1, tp.mini_batch)
+        if self.parallel_dims.pp > 1:           # the packed batches are the micro-batches of the pipeline schedule
+            mb = max(1, self.config.policy.parallelism.pp_micro_batch_size)
         return [list(range(i, min(i + mb, len(processed)))) for i in range(0, len(processed), mb)]
 
     def _loss_of(self, total_tokens):

@@ -55,7 +55,7 @@ class B200Rollout(RolloutBase):
             max_model_len=cfg.policy.model_max_length, page_size=cfg.b200.rollout_page_size,
             use_cuda_graph=cfg.b200.cuda_graph_decode and not r.enforce_eager or cfg.b200.cuda_graph_decode,
             seed=seed if seed is not None else (r.seed or 0),
-            shared_prefix_decode=cfg.b200.shared_prefix_decode)
+            shared_prefix_decode=cfg.b200.shared_prefix_decode, gpu_memory_utilization=r.gpu_memory_utilization)
 
     def get_underlying_model(self):
         return self.model

@@ -79,6 +79,7 @@ class _Seq:
 class RolloutEngine:
     def __init__(self, model, *, max_num_seqs: int = 128, max_model_len: int = 2048, page_size: int = 128,
                  num_pages: Optional[int] = None, max_prefill_tokens: int = 16384, use_cuda_graph: bool = True,
+                 gpu_memory_utilization: Optional[float] = None,
                  check_interval: int = 16, seed: int = 0, tp=None, shared_prefix_decode: bool = False):
         self.model = model
         self.args = model.args
@@ -96,6 +97,13 @@ class RolloutEngine:
         self.L = a.n_layers
         if num_pages is None:
             num_pages = 1 + self.S * self.max_pages_per_seq
+            if gpu_memory_utilization is not None and self.device.type == "cuda":
+                # rollout.gpu_memory_utilization: the KV pool takes what that share of the device leaves after the
+                # weights (never less than one full-length sequence); sequences wait for pages at admission
+                free, total = torch.cuda.mem_get_info(self.device)
+                budget = int(total * float(gpu_memory_utilization)) - (total - free)
+                page_bytes = self.L * 2 * self.hkv * self.P * self.d * torch.finfo(self.dtype).bits // 8
+                num_pages = max(1 + self.max_pages_per_seq, min(num_pages, 1 + max(0, budget) // page_bytes))
         self.num_pages = num_pages
         self.kv = torch.zeros(self.L, num_pages, 2, self.hkv, self.P, self.d, dtype=self.dtype, device=self.device)
         # tensor-core decode kernel: V slabs are stored transposed

@@ -562,7 +562,8 @@ def _pp_trainer_worker(rank, world, store, out_dir):
     def cfg(pp, kind):
         return Config.from_dict({
             "policy": {"model_name_or_path": "tiny-qwen2", "model_max_length": 64, "model_gradient_checkpointing": False,
-                       "parallelism": {"pp_size": pp, "dp_shard_size": 1, "tp_size": 1}},
+                       "parallelism": {"pp_size": pp, "dp_shard_size": 1, "tp_size": 1, "pp_micro_batch_size": 2,
+                                       "pp_schedule": "GPipe" if kind == "sft" else "1F1B"}},
             "train": {"seed": 0, "optm_lr": 1e-3, "optm_warmup_steps": 0, "output_dir": out_dir, "optm_grad_norm_clip": 0.5,
                       "train_policy": {"type": kind, "trainer_type": kind, "mini_batch": 2},
                       "ckpt": {"enable_checkpoint": False}}})
