@@ -58,7 +58,7 @@ class ColocatedRLControlWorker:
         mt = getattr(getattr(self.trainer.model, "args", None), "model_type", "hfmodel")
         self.packer = data_packer or BaseDataPacker.get_default(mt)()
         self.packer.setup(config, tokenizer)
-        self.fetcher = WorkerDataFetcher(config, CosmosDataset(dataset, config))
+        self.fetcher = WorkerDataFetcher(config, CosmosDataset.wrap(dataset, config))
         self.rewards = LocalRewardCalculator(config, reward_fns)
         self.policy_name, self.rollout_name = "colocated-policy", "colocated-rollout"
         self.weight_version = 0

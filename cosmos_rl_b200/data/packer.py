@@ -88,6 +88,16 @@ class DecoderOnlyLLMDataPacker(BaseDataPacker):
         if path and tokenizer is not None and hasattr(tokenizer, "chat_template"):
             with open(path) as f:
                 tokenizer.chat_template = f.read()      # e.g. tools/chat_templates/tool_chat_template.jinja2
+        # how a conversation becomes a generation prompt (multi-turn switches; defaults elsewhere)
+        mt = config.rollout.multi_turn_config
+        self.prompt_template_kwargs = {"add_generation_prompt": True}
+        if mt.enable:
+            self.prompt_template_kwargs["add_generation_prompt"] = bool(mt.add_generation_prompt
+                                                                        and not mt.continue_final_message)
+            if mt.continue_final_message:       # the model extends the last (assistant) message instead of opening one
+                self.prompt_template_kwargs["continue_final_message"] = True
+            if mt.enable_thinking:              # a variable of templates that gate a reasoning block on it
+                self.prompt_template_kwargs["enable_thinking"] = True
 
     def _encode_prompt(self, prompt) -> List[int]:
         if isinstance(prompt, (list, tuple)) and (len(prompt) == 0 or isinstance(prompt[0], int)):
@@ -96,7 +106,8 @@ class DecoderOnlyLLMDataPacker(BaseDataPacker):
             raise RuntimeError("a tokenizer is required for text prompts")
         if isinstance(prompt, str):
             return self.tokenizer.encode(prompt, add_special_tokens=False)
-        return self.tokenizer.apply_chat_template(prompt, tokenize=True, add_generation_prompt=True)
+        kw = getattr(self, "prompt_template_kwargs", {"add_generation_prompt": True})
+        return self.tokenizer.apply_chat_template(prompt, tokenize=True, **kw)
 
     def _encode_completion(self, completion) -> List[int]:
         if isinstance(completion, (list, tuple)) and (len(completion) == 0 or isinstance(completion[0], int)):

@@ -34,8 +34,8 @@ class Controller:
         self.config = config
         self.broker = broker or InProcessBroker()
         self.is_rl = config.train.train_policy.type == "grpo"
-        ds = CosmosDataset(dataset, config) if dataset is not None else None
-        vds = CosmosDataset(val_dataset, config) if val_dataset is not None else None
+        ds = CosmosDataset.wrap(dataset, config)
+        vds = CosmosDataset.wrap(val_dataset, config)
         self.data_fetcher = ControllerDataFetcher(config, ds, vds, sampler=sampler, is_rl=self.is_rl)
         self.rollout_status_manager = RolloutStatusManager(config, self.broker)
         self.policy_status_manager = PolicyStatusManager(

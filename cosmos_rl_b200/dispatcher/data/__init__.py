@@ -27,6 +27,19 @@ class CosmosDataset:
                 ds.setup(config)
         self.dataset = ds
 
+    @classmethod
+    def wrap(cls, dataset_or_factory, config=None, tokenizer=None) -> Optional["CosmosDataset"]:
+        """None stays None, and so does a factory that finds nothing to load (a config without ``dataset.name``)."""
+        if dataset_or_factory is None:
+            return None
+        if isinstance(dataset_or_factory, cls):
+            return dataset_or_factory
+        if callable(dataset_or_factory) and not hasattr(dataset_or_factory, "__getitem__"):
+            dataset_or_factory = dataset_or_factory(config)
+            if dataset_or_factory is None:
+                return None
+        return cls(dataset_or_factory, config, tokenizer)
+
     def __len__(self):
         return len(self.dataset)
 

@@ -140,6 +140,12 @@ def main(argv=None) -> int:
         os.symlink(os.path.basename(log_dir), tmp)
         os.replace(tmp, latest)
 
+    if raw.get("train", {}).get("timestamp") == "auto":
+        # a fresh sub-folder per launch, stamped once here so that every process of the job sees the same path
+        # (the reference stamps whenever train.timestamp is empty, cosmos_rl/policy/config/__init__.py:1883-1897;
+        # here an empty value keeps output_dir as written, which is what a resumed job needs)
+        raw["train"]["timestamp"] = time.strftime("%Y%m%d%H%M%S")
+        raw["train"]["output_dir"] = os.path.join(raw["train"].get("output_dir", "./outputs"), raw["train"]["timestamp"])
     # the job file the controller serves carries the replica counts actually launched
     raw.setdefault("policy", {}).setdefault("parallelism", {})["n_init_replicas"] = max(n_policy, 1)
     raw.setdefault("rollout", {}).setdefault("parallelism", {})["n_init_replicas"] = max(n_rollout, 1)

@@ -131,6 +131,12 @@ def main(dataset=None, val_dataset=None, data_packer=None, val_data_packer=None,
          filter_reward_fns=None, val_reward_fns=None, custom_logger_fns=None, hook_fns=None, sampler=None,
          batch_sampler=None, args=None, **kw):
     role = os.environ.get("COSMOS_ROLE", "Controller").lower()
+    if dataset is None:
+        # no dataset from the entry script: the rows of train_policy.dataset.name, read by the configured columns
+        from ..tools.dataset.common import config_dataset
+        dataset = lambda config: config_dataset(config)                                    # noqa: E731
+        if val_dataset is None:
+            val_dataset = lambda config: config_dataset(config, validation=True)          # noqa: E731
     if role == "controller":
         return controller_entry(dataset=dataset, val_dataset=val_dataset, custom_logger_fns=custom_logger_fns,
                                 sampler=sampler, args=args)

@@ -39,7 +39,7 @@ class RLPolicyWorker(CommMixin):
         self.parallel_dims = parallel_dims
         self.device = device or parallel_dims.device
         self.init_comm(api)
-        ds = CosmosDataset(dataset, config) if dataset is not None else None
+        ds = CosmosDataset.wrap(dataset, config)
         self.data_fetcher = WorkerDataFetcher(config, ds)
         tp = config.train.train_policy
         self.inter_replica = InterReplicaComm(self.api, self.replica_name, self.global_rank, self.device)

@@ -35,8 +35,8 @@ class SFTPolicyWorker(CommMixin):
             self.global_rank = dist.get_rank() if dist.is_initialized() else 0
             self.world_size = dist.get_world_size() if dist.is_initialized() else 1
             self.inter_replica = None
-        self.dataset = CosmosDataset(dataset, config, tokenizer) if dataset is not None else None
-        self.val_dataset = CosmosDataset(val_dataset, config, tokenizer) if val_dataset is not None else None
+        self.dataset = CosmosDataset.wrap(dataset, config, tokenizer)
+        self.val_dataset = CosmosDataset.wrap(val_dataset, config, tokenizer)
         tp = config.train.train_policy
         self.trainer = TrainerRegistry.get_trainer_cls(tp.trainer_type)(
             config, parallel_dims, device=self.device, data_packer=data_packer, val_data_packer=val_data_packer,
@@ -106,8 +106,11 @@ class SFTPolicyWorker(CommMixin):
         ck, val = self.config.train.ckpt, self.config.validation
         if val.enable and val.val_before_train:
             self.validate(self.start_step)
+        save_freq = max(1, ck.save_freq)
+        if ck.save_freq_in_epoch > 0:           # takes priority over the step cadence (sft_worker.py:739-746)
+            save_freq = max(1, ck.save_freq_in_epoch * max(1, self.steps_per_epoch))
         for step in range(self.start_step, self.total_steps):
-            do_save = ck.enable_checkpoint and ((step + 1) % max(1, ck.save_freq) == 0 or step + 1 == self.total_steps)
+            do_save = ck.enable_checkpoint and ((step + 1) % save_freq == 0 or step + 1 == self.total_steps)
             report = self.trainer.step_training(self._batch(step), self.total_steps, step + 1, do_save=do_save)
             self.history.append({"step": step + 1, **report})
             if (step + 1) % max(1, self.config.logging.log_interval) == 0 and self.global_rank == 0:

@@ -42,8 +42,8 @@ class DisaggregatedRolloutControlWorker(CommMixin):
         self.parallel_dims = parallel_dims
         self.device = device or parallel_dims.device
         self.init_comm(api)
-        ds = CosmosDataset(dataset, config) if dataset is not None else None
-        vds = CosmosDataset(val_dataset, config) if val_dataset is not None else None
+        ds = CosmosDataset.wrap(dataset, config)
+        vds = CosmosDataset.wrap(val_dataset, config)
         self.data_fetcher = WorkerDataFetcher(config, ds, vds)
         self.tokenizer = tokenizer
         backend = config.rollout.backend

@@ -73,3 +73,41 @@ class PromptDataset:
 def chat(system: Optional[str], user: str) -> List[Dict[str, str]]:
     msgs = [{"role": "system", "content": system}] if system else []
     return msgs + [{"role": "user", "content": user}]
+
+
+def config_dataset(config, validation: bool = False) -> Optional["PromptDataset"]:
+    """The dataset a job gets when its entry script passes none: rows of ``dataset.name`` read through the column
+    names of the training policy (cosmos_rl/dispatcher/data/__init__.py:83-170 builds the same from
+    ``prompt_column_name`` / ``response_column_name``; the SFT workers read ``conversation_column_name``,
+    cosmos_rl/policy/worker/sft_worker.py:60-110). ``system_prompt`` is put in front of string prompts and of
+    conversations that do not start with a system turn. Returns None when the config names no dataset."""
+    tp = config.train.train_policy
+    d = config.validation.dataset if validation else tp.dataset
+    if not getattr(d, "name", ""):
+        return None
+    system = getattr(tp, "system_prompt", "") or ""
+
+    def with_system(conv):
+        if system and not (conv and isinstance(conv[0], dict) and conv[0].get("role") == "system"):
+            return [{"role": "system", "content": system}] + list(conv)
+        return list(conv)
+
+    if tp.type == "sft":
+        col = tp.conversation_column_name
+
+        def to_prompt(row):
+            v = row[col]
+            return with_system(v) if isinstance(v, list) and v and isinstance(v[0], dict) else v
+
+        return PromptDataset(to_prompt, lambda row: None, validation=validation)
+    pcol, rcol = tp.prompt_column_name, tp.response_column_name
+    if not pcol:
+        raise ValueError("train.train_policy.prompt_column_name is needed to read prompts from dataset.name")
+
+    def to_prompt(row):
+        v = row[pcol]
+        if isinstance(v, list) and v and isinstance(v[0], dict):
+            return with_system(v)
+        return chat(system, v) if system else v
+
+    return PromptDataset(to_prompt, lambda row: row.get(rcol) if rcol else None, validation=validation)

@@ -125,3 +125,29 @@ def test_vlm_dataset_rows_to_conversations(tmp_path):
     assert ds.get_reference_answer(0) == "B" and [m["role"] for m in ds[1]] == ["user"]
     assert [m["role"] for m in hf_vlm.VLMDataset(True, rows, str(tmp_path))[0]] == ["user", "assistant"]
     assert hf_vlm.vlm_reward("<answer>B</answer>", "B") == 1.0 and hf_vlm.vlm_reward("so \\\\boxed{12}", "12") == 1.0
+
+
+def test_config_driven_dataset_reads_columns_and_system_prompt(tmp_path):
+    """A job whose entry script passes no dataset reads ``dataset.name`` through the configured column names."""
+    import json
+    from cosmos_rl_b200.config import Config
+    from cosmos_rl_b200.dispatcher.data import CosmosDataset
+    from cosmos_rl_b200.tools.dataset.common import config_dataset
+    f = tmp_path / "train.jsonl"
+    rows = [{"q": "2+2?", "a": "4", "conv": [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "yo"}]},
+            {"q": "3+3?", "a": "6", "conv": [{"role": "system", "content": "own"}, {"role": "user", "content": "x"}]}]
+    f.write_text("\n".join(json.dumps(r) for r in rows))
+    base = {"policy": {"model_name_or_path": "tiny-qwen2"}}
+    grpo = Config.from_dict({**base, "train": {"train_policy": {
+        "type": "grpo", "dataset": {"name": str(f)}, "prompt_column_name": "q", "response_column_name": "a",
+        "system_prompt": "Be brief."}}})
+    ds = CosmosDataset.wrap(lambda c: config_dataset(c), grpo)
+    assert len(ds) == 2 and ds.get_reference_answer(1) == "6"
+    assert ds[0] == [{"role": "system", "content": "Be brief."}, {"role": "user", "content": "2+2?"}]
+    sft = Config.from_dict({**base, "train": {"train_policy": {
+        "type": "sft", "dataset": {"name": str(f)}, "conversation_column_name": "conv", "system_prompt": "Be brief."}}})
+    ds = CosmosDataset.wrap(lambda c: config_dataset(c), sft)
+    assert ds[0][0] == {"role": "system", "content": "Be brief."} and ds[0][1]["content"] == "hi"
+    assert ds[1][0]["content"] == "own" and len(ds[1]) == 2                 # its own system turn is kept
+    none = Config.from_dict({**base, "train": {"train_policy": {"type": "grpo"}}})
+    assert CosmosDataset.wrap(lambda c: config_dataset(c), none) is None and CosmosDataset.wrap(None, none) is None
