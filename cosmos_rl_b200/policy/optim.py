@@ -48,13 +48,48 @@ def lr_factor(step: int, total_steps: int, warmup_steps, warmup_start_factor: fl
     return min_lr_factor + (1.0 - min_lr_factor) * f
 
 
+class _Quantized8:
+    """An Adam moment held in 8 bits: blocks of 256 values share one fp32 scale (absmax). The first moment is stored
+    as signed int8; the second moment spans many orders of magnitude inside a block, so its square root is stored
+    (uint8), which halves the exponent range. The reference offers torchao's 8-bit Adam for the same purpose
+    (cosmos_rl/policy/trainer/optm/__init__.py:36-41, 380-385)."""
+    BLOCK = 256
+
+    def __init__(self, n: int, device, sqrt: bool):
+        self.n, self.sqrt = n, sqrt
+        nb = -(-n // self.BLOCK)
+        self.q = torch.zeros(nb * self.BLOCK, dtype=torch.uint8 if sqrt else torch.int8, device=device)
+        self.scale = torch.zeros(nb, dtype=torch.float32, device=device)
+        self.levels = 255.0 if sqrt else 127.0
+
+    def window(self, a: int, b: int):
+        """Block-aligned range that covers [a, b)."""
+        return a // self.BLOCK * self.BLOCK, min(-(-b // self.BLOCK) * self.BLOCK, self.q.numel())
+
+    def load(self, A: int, B: int) -> torch.Tensor:
+        x = self.q[A:B].to(torch.float32).view(-1, self.BLOCK) * self.scale[A // self.BLOCK:B // self.BLOCK, None]
+        x = x.reshape(-1)
+        return x * x if self.sqrt else x
+
+    def store(self, A: int, x: torch.Tensor) -> None:
+        B = A + x.numel()
+        y = (x.sqrt() if self.sqrt else x).view(-1, self.BLOCK)
+        s = y.abs().amax(1) / self.levels
+        self.scale[A // self.BLOCK:B // self.BLOCK] = s
+        q = (y / s.clamp_min(1e-30)[:, None]).round_()
+        self.q[A:B] = q.to(self.q.dtype).view(-1)
+
+    def tensors(self, name: str):
+        return [(f"{name}.q", self.q), (f"{name}.scale", self.scale)]
+
+
 class FlatAdamW:
     def __init__(self, flat: FlatParams, lr: float, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
                  max_grad_norm: float = 1.0, dp_group: Optional[dist.ProcessGroup] = None,
                  master_dtype: torch.dtype = torch.float32, collective=None,
                  replicate_group: Optional[dist.ProcessGroup] = None,
                  tp_group: Optional[dist.ProcessGroup] = None, tp_replicated: Optional[torch.Tensor] = None,
-                 norm_groups=(), sum_groups=()):
+                 norm_groups=(), sum_groups=(), state_bits: int = 32):
         """``dp_group`` shards optimizer state (ZeRO-2 style); ``replicate_group`` is the outer data-parallel axis of
         HSDP / DDP (cosmos_rl/policy/model/gpt/parallelize.py:80-113, 426-442): ranks of it hold the same shard and
         average their reduced gradient shard before the update, so the all-reduce moves 1/dp_shard of the gradient."""
@@ -78,8 +113,15 @@ class FlatAdamW:
         n = self.hi - self.lo
         dev = flat.device
         self.master = flat.data[self.lo:self.hi].to(torch.float32, copy=True)
-        self.m = torch.zeros(n, dtype=torch.float32, device=dev)
-        self.v = torch.zeros(n, dtype=torch.float32, device=dev)
+        if state_bits not in (8, 32):
+            raise ValueError("state_bits must be 32 or 8")
+        self.state_bits = state_bits
+        if state_bits == 8:                      # block-quantised moments: 2 bytes per parameter instead of 8
+            self.m = self.v = None
+            self.m8, self.v8 = _Quantized8(n, dev, sqrt=False), _Quantized8(n, dev, sqrt=True)
+        else:
+            self.m = torch.zeros(n, dtype=torch.float32, device=dev)
+            self.v = torch.zeros(n, dtype=torch.float32, device=dev)
         self.grad_shard = torch.zeros(n, dtype=torch.float32, device=dev) if self.world > 1 else None
         # rank-local tail (expert-parallel experts): full optimizer state here, no reduction, no publication
         self.t0, self.t1 = flat.shared_total, flat.total
@@ -195,12 +237,15 @@ class FlatAdamW:
         hp = dict(lr=self.lr * lr_scale, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps,
                   weight_decay=self.wd, step=self.step_count, grad_scale=coef)
         segs = self.segments if self.segments is not None else [(0, self.hi - self.lo)]
-        if fused and self.segments is None:
+        if fused and self.segments is None and self.state_bits == 32:
             self.collective.adamw_publish(self.master, self.m, self.v, g, self.lo, self.hi, **hp)
         else:
             shadow = self.flat.data[self.lo:self.hi]
             for a, b in segs:
-                K.adamw_flat(self.master[a:b], self.m[a:b], self.v[a:b], g[a:b], shadow[a:b], **hp)
+                if self.state_bits == 8:
+                    self._step_quantised(a, b, g, shadow, hp)
+                else:
+                    K.adamw_flat(self.master[a:b], self.m[a:b], self.v[a:b], g[a:b], shadow[a:b], **hp)
             if self.world > 1:
                 dist.all_gather_into_tensor(self.flat.data[:self.t0], shadow.clone(), group=self.group)
         if self.tail is not None:
@@ -212,6 +257,18 @@ class FlatAdamW:
         self.last_grad_norm = norm
         return norm
 
+    def _step_quantised(self, a: int, b: int, g, shadow, hp, chunk: int = 1 << 24) -> None:
+        """[a, b) of the shard with 8-bit moments: block-aligned windows of at most ``chunk`` values are expanded to
+        fp32, updated by the same kernel as the fp32 path and stored back."""
+        A0, B0 = self.m8.window(a, b)
+        for A in range(A0, B0, chunk):
+            B = min(A + chunk, B0)
+            m, v = self.m8.load(A, B), self.v8.load(A, B)
+            lo, hi = max(a, A), min(b, B)
+            K.adamw_flat(self.master[lo:hi], m[lo - A:hi - A], v[lo - A:hi - A], g[lo:hi], shadow[lo:hi], **hp)
+            self.m8.store(A, m)
+            self.v8.store(A, v)
+
     def zero_grad(self) -> None:
         self.flat.zero_grad()
 
@@ -219,6 +276,8 @@ class FlatAdamW:
     def state_dict(self) -> Dict[str, Any]:
         sd = {"master": self.master, "m": self.m, "v": self.v, "step": self.step_count, "lo": self.lo,
               "hi": self.hi, "world": self.world}
+        if self.state_bits == 8:
+            sd.update(m=None, v=None, q8={k: t for k, t in self.m8.tensors("m") + self.v8.tensors("v")})
         if self.tail is not None:
             sd["tail"] = dict(self.tail)
         return sd
@@ -227,8 +286,14 @@ class FlatAdamW:
         if sd["hi"] - sd["lo"] != self.hi - self.lo:
             raise ValueError("optimizer shard size changed; re-shard the checkpoint first")
         self.master.copy_(sd["master"])
-        self.m.copy_(sd["m"])
-        self.v.copy_(sd["v"])
+        if self.state_bits == 8:
+            if "q8" not in sd:
+                raise ValueError("the checkpoint holds fp32 optimizer moments but the optimizer is configured for 8 bits")
+            for k, t in self.m8.tensors("m") + self.v8.tensors("v"):
+                t.copy_(sd["q8"][k])
+        else:
+            self.m.copy_(sd["m"])
+            self.v.copy_(sd["v"])
         self.step_count = int(sd["step"])
         self.flat.data[self.lo:self.hi].copy_(self.master.to(self.flat.dtype))
         if self.tail is not None and "tail" in sd:
@@ -238,7 +303,11 @@ class FlatAdamW:
 
     def state_tensors(self):
         """Named tensors shipped to a new replica on elastic scale-up (policy-to-policy unicast)."""
-        out = [("optim.master", self.master), ("optim.m", self.m), ("optim.v", self.v)]
+        if self.state_bits == 8:
+            out = [("optim.master", self.master)] + [(f"optim.{k}", t) for k, t in
+                                                     self.m8.tensors("m") + self.v8.tensors("v")]
+        else:
+            out = [("optim.master", self.master), ("optim.m", self.m), ("optim.v", self.v)]
         if self.tail is not None:
             out += [(f"optim.tail.{k}", t) for k, t in self.tail.items()]
         return out

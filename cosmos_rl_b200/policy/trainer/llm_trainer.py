@@ -118,9 +118,9 @@ class LLMTrainer(Trainer):
             custom_plan(model, parallel_dims, config)
         lr = config.train.optm_lr if isinstance(config.train.optm_lr, float) else float(
             list(config.train.optm_lr.values())[0] if isinstance(config.train.optm_lr, dict) else config.train.optm_lr[0])
-        if config.train.optm_name not in ("AdamW", "Adam"):
+        if config.train.optm_name not in ("AdamW", "Adam", "AdamW8bit", "Adam8bit"):
             raise NotImplementedError(f"optimizer {config.train.optm_name!r}: the flat sharded optimizer implements AdamW "
-                                      f"(and Adam = AdamW without decoupled weight decay)")
+                                      f"(Adam = AdamW without decoupled weight decay; the 8bit names keep block-quantised moments)")
         tp_mask = None
         if tp > 1:
             # parameters every tensor-parallel rank holds in full (norm weights): counted once in the gradient norm
@@ -130,7 +130,8 @@ class LLMTrainer(Trainer):
                     tp_mask[slot.offset:slot.offset + slot.numel] = True
         self.optimizer = FlatAdamW(
             self.flat, lr=lr, betas=tuple(config.train.optm_betas), eps=config.train.epsilon,
-            weight_decay=config.train.optm_weight_decay if config.train.optm_name == "AdamW" else 0.0,
+            weight_decay=config.train.optm_weight_decay if config.train.optm_name.startswith("AdamW") else 0.0,
+            state_bits=8 if config.train.optm_name.endswith("8bit") else 32,
             max_grad_norm=config.train.optm_grad_norm_clip,
             tp_group=parallel_dims.group("tp") if tp > 1 else None, tp_replicated=tp_mask,
             norm_groups=[parallel_dims.group("pp")] if parallel_dims.pp > 1 else [],

@@ -370,3 +370,60 @@ def test_ema_tracks_weights_on_the_optimizer_shard_and_is_exported(tmp_path):
     tr2 = SFTTrainer(c, dims, device=torch.device("cpu"))
     assert tr2.weight_resume() and torch.equal(tr2.ema.shard, tr.ema.shard) and tr2.ema.updates == 3
     assert any(n == "ema.shard" for n, _ in tr2.state_tensors())
+
+
+def test_8bit_optimizer_moments_track_the_fp32_optimizer(tmp_path):
+    """``optm_name = "AdamW8bit"``: moments in int8 / uint8 blocks of 256 with fp32 scales. After several steps on the
+    same gradients the weights stay close to the fp32 optimizer's, the state is a quarter of the size, frozen
+    stretches and unaligned segment edges are handled, and the state survives a save / load round trip."""
+    import torch
+    from cosmos_rl_b200.models.gpt import GPT, GPTArgs
+    from cosmos_rl_b200.parallel.flat import FlatParams
+    from cosmos_rl_b200.policy.optim import FlatAdamW
+
+    def make(bits, freeze):
+        m = GPT(GPTArgs(vocab_size=512, dim=64, n_layers=2, n_heads=4, n_kv_heads=2, ffn_dim=160))
+        if freeze:
+            for n, p in m.named_parameters():
+                if n.startswith("layers.0."):
+                    p.requires_grad_(False)
+        flat = FlatParams(m, torch.float32, torch.device("cpu"))
+        m.init_weights(0)
+        return flat, FlatAdamW(flat, lr=1e-2, weight_decay=0.1, max_grad_norm=1e9, state_bits=bits)
+
+    for freeze in (False, True):
+        (f32, o32), (f8, o8) = make(32, freeze), make(8, freeze)
+        w0 = f32.data.clone()
+        for step in range(6):
+            g = torch.Generator().manual_seed(step)
+            grad = torch.randn(f32.total, generator=g) * torch.logspace(-4, 0, f32.total)     # wide dynamic range
+            f32.grad.copy_(grad)
+            f8.grad.copy_(grad)
+            o32.step()
+            o8.step()
+        moved = (f32.data - w0).abs()
+        err = (f8.data - f32.data).abs()
+        assert moved.max() > 0.03 and err.max() < 0.3 * moved.max() and err.mean() < 0.05 * moved.mean()
+        if freeze:
+            assert torch.equal(f8.data[moved == 0], w0[moved == 0]) and (moved == 0).sum() > 1000
+    bytes8 = sum(t.numel() * t.element_size() for _, t in o8.m8.tensors("m") + o8.v8.tensors("v"))
+    assert bytes8 < 0.27 * (o32.m.numel() + o32.v.numel()) * 4
+    sd = o8.state_dict()
+    _, o8b = make(8, True)
+    o8b.load_state_dict(sd)
+    assert torch.equal(o8b.m8.q, o8.m8.q) and torch.equal(o8b.v8.scale, o8.v8.scale) and o8b.step_count == 6
+    assert [n for n, _ in o8.state_tensors()] == ["optim.master", "optim.m.q", "optim.m.scale", "optim.v.q", "optim.v.scale"]
+
+
+def test_sft_trainer_with_8bit_adam(tmp_path):
+    import torch
+    from cosmos_rl_b200.policy.trainer.sft_trainer import SFTTrainer
+    c = _config(tmp_path, "sft")
+    c.train.optm_name = "AdamW8bit"
+    tr = SFTTrainer(c, ParallelDims(world_size=1, device=torch.device("cpu")), device=torch.device("cpu"))
+    tr.model_load_from_hf()
+    assert tr.optimizer.state_bits == 8 and tr.optimizer.m is None
+    g = torch.Generator().manual_seed(0)
+    batch = [{"input_ids": torch.randint(0, 32000, (12,), generator=g).tolist()} for _ in range(4)]
+    losses = [tr.step_training(batch, 10, i + 1)["train/loss_avg"] for i in range(5)]
+    assert losses[-1] < losses[0] - 0.5
