@@ -364,6 +364,15 @@ class LLMTrainer(Trainer):
             return
         hf_io.export_safetensors(self.model, self.hf_config, output_dir, self.parallel_dims,
                                  source_dir=self.config.policy.model_name_or_path)
+        ck = self.config.train.ckpt
+        if self.parallel_dims.global_rank == 0 and (ck.upload_hf or ck.upload_s3):
+            from ...utils import upload
+            if ck.upload_hf:
+                upload.upload_folder_to_hub(output_dir, ck.hf_repo_name)
+            if upload.wants_s3(ck, bool(kw.get("is_final", False))):
+                rel = os.path.relpath(output_dir, self.config.train.output_dir)
+                upload.upload_folder_to_s3(output_dir, ck.s3_bucket, os.path.join(ck.s3_prefix, rel),
+                                           client=self.ckpt_manager.s3_client)
 
     # ------------------------------------------------------------------ state shipping (elastic scale-up)
     def state_tensors(self) -> List[Tuple[str, torch.Tensor]]:

@@ -53,6 +53,7 @@ class CheckpointManager:
         self.root = os.path.join(config.train.output_dir, "checkpoints")
         self.pool = concurrent.futures.ThreadPoolExecutor(max_workers=4) if self.save_mode == "async" else None
         self.pending: List[concurrent.futures.Future] = []
+        self.s3_client = None       # an injected client (tests); boto3's default client otherwise
         self.best_score: Optional[float] = None
         self._lock = threading.Lock()
 
@@ -85,6 +86,11 @@ class CheckpointManager:
                 os.replace(tmp, os.path.join(d, f"{name}_rank_{self.rank}.pth"))
             with open(self._marker(step), "w") as f:
                 f.write("ok")
+            ck = self.config.train.ckpt
+            from .upload import upload_folder_to_s3, wants_s3
+            if wants_s3(ck, is_final):          # this rank's files (and rank 0's config) of the step folder
+                upload_folder_to_s3(d, ck.s3_bucket, os.path.join(ck.s3_prefix, "checkpoints", f"step_{step}", self.role),
+                                    client=self.s3_client)
             self._prune()
 
         if self.pool is not None and not is_final:

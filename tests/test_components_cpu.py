@@ -400,3 +400,40 @@ def test_heartbeat_child_process_posts_and_is_daemonic():
     p.terminate()
     p.join(timeout=10)
     srv.shutdown()
+
+
+def test_checkpoints_are_mirrored_to_object_storage(tmp_path):
+    """``train.ckpt.upload_s3``: "all" uploads the files of every save, "final" only those of the last one; keys are
+    ``<s3_prefix>/checkpoints/step_N/policy/<file>``. A failing client is logged, the save itself stands."""
+    import torch
+    from cosmos_rl_b200.config import Config
+    from cosmos_rl_b200.utils.checkpoint import CheckpointManager
+
+    class FakeS3:
+        def __init__(self, fail=False):
+            self.calls, self.fail = [], fail
+
+        def upload_file(self, path, bucket, key):
+            if self.fail:
+                raise RuntimeError("no route")
+            self.calls.append((bucket, key))
+
+    def run(mode, fail=False):
+        out = tmp_path / f"{mode}_{fail}"
+        c = Config.from_dict({"policy": {"model_name_or_path": "tiny-qwen2"},
+                              "train": {"output_dir": str(out), "ckpt": {"enable_checkpoint": True, "save_mode": "sync",
+                                        "upload_s3": mode, "s3_bucket": "bkt", "s3_prefix": "runs/a"}}})
+        m = CheckpointManager(c, 0)
+        m.s3_client = FakeS3(fail)
+        for step, final in ((1, False), (2, True)):
+            m.save(step, {"w": torch.ones(2)}, {"m": torch.zeros(2)}, {"step": step}, {"step": step}, is_final=final)
+        m.finalize()
+        assert m.latest_valid_step() == 2
+        return m.s3_client.calls
+
+    all_ = run("all")
+    assert ("bkt", "runs/a/checkpoints/step_1/policy/model_rank_0.pth") in all_
+    assert ("bkt", "runs/a/checkpoints/step_2/policy/cosmos_config") in all_
+    final = run("final")
+    assert final and all("step_2" in k for _, k in final)
+    assert run("all", fail=True) == []
