@@ -70,6 +70,7 @@ class DisaggregatedRolloutControlWorker(CommMixin):
         self.prompt_queue: List[Tuple[int, RLPayload]] = []
         self.prompt_end = False
         self.stopped = False
+        self.scheduler = None          # RolloutTaskScheduler when rollout.mode == "async"
         self.total_steps: Optional[int] = None
         self.batch_size = config.rollout.batch_size
         self.handlers = cmd.RolloutCommandRegistry()
@@ -236,7 +237,11 @@ class DisaggregatedRolloutControlWorker(CommMixin):
                 return stop
             h = self.handlers.get_command_handler(c)
             if h is not None:
-                stop = bool(h(c)) or stop
+                if self.scheduler is not None:          # async mode: no engine call while weights or the mesh change
+                    with self.scheduler.paused():
+                        stop = bool(h(c)) or stop
+                else:
+                    stop = bool(h(c)) or stop
 
     def report_rollouts(self, block: bool = False, is_end: bool = False) -> None:
         done = self.reward_dispatcher.dequeue(block=block and not self.reward_dispatcher.is_empty())
@@ -253,6 +258,10 @@ class DisaggregatedRolloutControlWorker(CommMixin):
         del self.prompt_queue[:n]
         payloads = [p for _, p in batch]
         results = self.rollout.rollout_generation(payloads, self.data_packer, self.data_fetcher)
+        self._finish_generation(payloads, results, self.current_weight_version)
+
+    def _finish_generation(self, payloads, results, weight_version: int) -> None:
+        """Results into payloads, teacher requests, reward queue."""
         reporter = self.parallel_dims.tp_coord == 0 and self.parallel_dims.pp_coord == self.parallel_dims.pp - 1
         for p, r in zip(payloads, results):
             p.completions = r.completions
@@ -266,7 +275,7 @@ class DisaggregatedRolloutControlWorker(CommMixin):
                     p.completion_logprobs = [[[l] for l in lps] for lps in r.completion_logprobs]
                 self.stats["generated_tokens"] += sum(len(t) for t in r.completion_token_ids)
             p.cumulative_logprob = r.cumulative_logprob
-            p.weight_version = self.current_weight_version
+            p.weight_version = weight_version
             if self.config.distillation.enable and r.completion_token_ids is not None and reporter:
                 # on-policy distillation: the teacher scores every sampled completion; the policy fetches the result
                 # by uuid when it trains on the rollout (cosmos_rl/rollout/worker/rollout_control.py teacher requests)
@@ -278,9 +287,74 @@ class DisaggregatedRolloutControlWorker(CommMixin):
         if reporter:
             self.reward_dispatcher.enqueue_rewards_cal(payloads)
 
+    # ------------------------------------------------------------------ asynchronous generation
+    def _start_scheduler(self) -> None:
+        from .task_scheduler import RolloutTaskScheduler
+
+        def generate(payloads, is_validation):
+            version = self.current_weight_version        # fixed for the batch: updates wait in scheduler.paused()
+            results = self.rollout.rollout_generation(list(payloads), self.data_packer, self.data_fetcher)
+            return [(r, version) for r in results]
+
+        self.scheduler = RolloutTaskScheduler(generate, self.config.rollout.async_config.max_concurrent_requests)
+        self.scheduler.start()
+
+    def _async_step(self, allowed: int) -> bool:
+        """Feed the scheduler, collect what finished. Returns False when there was nothing to do."""
+        from .task_scheduler import RolloutTask
+        sch = self.scheduler
+        fed = 0
+        while self.prompt_queue and sch.pending() < 2 * sch.max_batch:
+            idx, payload = self.prompt_queue[0]
+            if payload.weight_version > self.current_weight_version + allowed:
+                break                                     # weight-version gate, as in the synchronous loop
+            self.prompt_queue.pop(0)
+            sch.put_rollout(RolloutTask(idx, payload))
+            fed += 1
+        done = sch.get_all()
+        ok = [c for c in done if c.error is None]
+        for c in done:
+            if c.error is not None:
+                logger.error("[Rollout] payload %s dropped after a generation error: %s", c.idx, c.error)
+        by_version = {}
+        for c in ok:
+            by_version.setdefault(c.result[1], []).append(c)
+        for version, cs in by_version.items():
+            self._finish_generation([c.payload for c in cs], [c.result[0] for c in cs], version)
+        return bool(fed or done)
+
     def main_loop(self) -> None:
         self.start_command_thread()
         allowed = getattr(self.config.train.train_policy, "allowed_outdated_steps", 0)
+        if self.config.rollout.mode == "async":
+            if self.world_size > 1:
+                logger.warning("[Rollout] rollout.mode = 'async' needs single-GPU rollout replicas (the ranks of a "
+                               "replica generate in lockstep): running synchronously")
+            else:
+                self._start_scheduler()
+        while self.scheduler is not None and not self.shutdown_signal.is_set():
+            if self.consume_commands(block=0.05 if not self.weights_ready else 0.0) or self.stopped:
+                break
+            if not self.weights_ready:
+                continue
+            if not self.prompt_queue and not self.prompt_end:
+                self.request_new_prompts(self.batch_size)
+            busy = self._async_step(allowed)
+            self.report_rollouts()
+            if not self.prompt_queue and self.prompt_end and self.scheduler.is_idle() \
+                    and self.scheduler.done.empty() and self.reward_dispatcher.is_empty():
+                break
+            if not busy:
+                time.sleep(constant.COSMOS_WEIGHT_GATE_SLEEP)
+        if self.scheduler is not None:
+            self.scheduler.stop(wait_for_queue=not self.stopped)
+            self._async_step(allowed)
+            st = self.scheduler.stats
+            logger.info("[Rollout] async scheduler: %d payloads in %d engine calls, %.1f s generating, %d errors",
+                        st["tasks"], st["batches"], st["busy_s"], st["errors"])
+            self.report_rollouts(block=True, is_end=True)
+            self.handle_shutdown()
+            return
         while not self.shutdown_signal.is_set():
             if self.consume_commands(block=0.05 if not self.weights_ready else 0.0) or self.stopped:
                 break

@@ -117,3 +117,28 @@ def test_tiny_grpo_job_with_lora(tmp_path):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:] + detail
     assert "training finished at step 2" in logs["controller.log"], detail
     assert "[WeightSyncCheck] coverage ok" in logs["rollout_0.log"], detail      # the first sync was verified too
+
+
+@pytest.mark.timeout(420)
+def test_tiny_grpo_job_with_async_rollout_scheduler(tmp_path):
+    """``rollout.mode = "async"``: generation runs on the scheduler's thread, the control loop feeds it and reports;
+    weight updates are fenced by the scheduler's pause."""
+    from cosmos_rl_b200.config import dump_toml, load_toml
+    raw = load_toml(os.path.join(HERE, "configs", "tiny_grpo_cpu.toml"))
+    raw["rollout"]["mode"] = "async"
+    raw["rollout"]["async_config"] = {"max_concurrent_requests": 2}
+    raw["train"]["output_dir"] = str(tmp_path / "out")
+    cfg = tmp_path / "job.toml"
+    cfg.write_text(dump_toml(raw))
+    log_dir = tmp_path / "logs"
+    env = dict(os.environ, COSMOS_LOG_LEVEL="INFO", COSMOS_HEARTBEAT_SEND_INTERVAL="2", PYTHONPATH=ROOT,
+               OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "cosmos_rl_b200.launcher.launch_all", "--config", str(cfg), "--policy", "1",
+           "--rollout", "1", "--cpu", "--log-dir", str(log_dir), os.path.join(HERE, "e2e_script.py")]
+    r = _run_job(cmd, env, 400)
+    latest = log_dir / "logs_latest"
+    logs = {f: open(latest / f).read() for f in sorted(os.listdir(latest))}
+    detail = "\n".join(f"==== {k}\n{v[-3000:]}" for k, v in logs.items())
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:] + detail
+    assert "training finished at step 2" in logs["controller.log"], detail
+    assert "async scheduler" in logs["rollout_0.log"], detail
