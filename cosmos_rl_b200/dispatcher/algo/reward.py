@@ -121,3 +121,18 @@ class Reward:
                 r = r[0]
             total += w * float(r)
         return total
+
+    def batch(self, to_be_evaluated: List[Any], reference, prompt=None, **kw) -> List[float]:
+        """``group_reward_calculation``: every function is called once with all completions of a prompt and returns
+        one value per completion, optionally ``(values, per-completion dicts)`` (cosmos_rl/dispatcher/algo/reward.py:
+        396-427). Useful when scoring shares work across the group (one verifier call, one judge request)."""
+        total = [0.0] * len(to_be_evaluated)
+        for fn, w in self.fns:
+            vals = fn(to_be_evaluated, reference, prompt=prompt, **kw)
+            if isinstance(vals, tuple) and len(vals) == 2:
+                vals = vals[0]
+            if not isinstance(vals, (list, tuple)) or len(vals) != len(to_be_evaluated):
+                raise ValueError("with group_reward_calculation a reward function returns one value per completion")
+            for i, v in enumerate(vals):
+                total[i] += w * float(v)
+        return total

@@ -53,6 +53,7 @@ class LocalRewardCalculator:
         self.variant = getattr(tp, "variant", "grpo")
         self.min_prefix = getattr(tp, "min_filter_prefix_tokens", None)
         self.bypass = bool(getattr(tp, "bypass_reward", False))
+        self.grouped = bool(getattr(tp, "group_reward_calculation", False))
         self.overlong = getattr(tp, "overlong_reward", None)
         self.max_response = config.rollout.max_response_length
         self.adv_low = getattr(tp, "advantage_low", -1e9)
@@ -68,9 +69,14 @@ class LocalRewardCalculator:
             payload.valid = True
             return payload
         rewards, filt = [], []
+        grouped = None
+        if self.grouped and comps and hasattr(self.algo.reward_fn, "batch"):
+            grouped = self.algo.reward_fn.batch(list(comps), payload.reference_answer, prompt=payload.prompt,
+                                                **({"token_ids": toks} if toks else {}))
         for i, c in enumerate(comps):
             kw = {"token_ids": toks[i]} if toks else {}
-            r = float(self.algo.compute_reward(c, payload.reference_answer, prompt=payload.prompt, **kw))
+            r = float(grouped[i]) if grouped is not None else float(
+                self.algo.compute_reward(c, payload.reference_answer, prompt=payload.prompt, **kw))
             if self.overlong is not None and self.overlong.enable_overlong_penalty and toks:
                 from ..dispatcher.algo.reward import overlong_reward
                 r += overlong_reward(c, length=len(toks[i]), max_length=self.max_response,

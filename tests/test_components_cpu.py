@@ -437,3 +437,23 @@ def test_checkpoints_are_mirrored_to_object_storage(tmp_path):
     final = run("final")
     assert final and all("step_2" in k for _, k in final)
     assert run("all", fail=True) == []
+
+
+def test_grouped_reward_calculation_calls_each_function_once_per_prompt():
+    """``group_reward_calculation``: a reward function gets all completions of a prompt in one call."""
+    from cosmos_rl_b200.dispatcher.data.schema import RLPayload
+    from cosmos_rl_b200.reward.dispatcher import LocalRewardCalculator
+    calls = []
+
+    def longest_wins(completions, reference, prompt=None, token_ids=None, **kw):
+        calls.append(len(completions))
+        best = max(len(t) for t in token_ids)
+        return [1.0 if len(t) == best else 0.0 for t in token_ids], [{"len": len(t)} for t in token_ids]
+
+    c = Config.from_dict({"train": {"train_policy": {"type": "grpo", "group_reward_calculation": True}},
+                          "rollout": {"max_response_length": 8}})
+    calc = LocalRewardCalculator(c, reward_fns=[longest_wins])
+    toks = [[1, 2, 3], [4], [5, 6, 7]]
+    p = calc.compute(RLPayload(prompt=[1], prompt_idx=0, completions=toks,
+                               completion_token_ids=[[[t] for t in tl] for tl in toks]))
+    assert calls == [3] and p.rewards == [1.0, 0.0, 1.0] and abs(sum(p.advantages)) < 1e-5
