@@ -50,6 +50,7 @@ class Controller:
         self.stat_completion_tokens = 0
         self.stat_samples = 0
         self.stat_invalid = 0
+        self._retry_warned = False
         self.shard_infos: Dict[str, Any] = {}
         self.nccl_errors: Dict[str, Tuple[float, str]] = {}
         self.trace_paths: Dict[str, Dict[int, str]] = {}
@@ -210,18 +211,27 @@ class Controller:
             n = min(n, room // n_gen)
             # never hand out more prompts than the remaining steps can consume
             if pm.total_steps:
-                budget = pm.total_steps * gb // n_gen - self.prompts_handed_out
+                # dropped groups (dynamic sampling found no signal in them) are replaced by fresh prompts
+                budget = pm.total_steps * gb // n_gen - (self.prompts_handed_out - self.stat_invalid)
                 if budget <= 0:
                     return [], True
                 n = min(n, budget)
             batch, is_end = self.data_fetcher.get_batched_prompt(n)
             pps = self.prompts_per_step()
             for _, payload in batch:
-                payload.weight_version = pm.start_step + self.prompts_handed_out // pps
+                payload.weight_version = pm.start_step + max(0, self.prompts_handed_out - self.stat_invalid) // pps
                 self.prompts_handed_out += 1
             pm.samples_on_the_fly += len(batch) * n_gen
-            if pm.total_steps and self.prompts_handed_out >= pm.total_steps * gb // n_gen:
-                is_end = True
+            if pm.total_steps and self.prompts_handed_out - self.stat_invalid >= pm.total_steps * gb // n_gen:
+                # nothing more to hand out for now; a group dropped later reopens the budget, so the stream of a
+                # job with dynamic sampling only ends with the training itself
+                is_end = tp.variant != "dapo"
+            retry = tp.max_retry_for_on_policy
+            if retry > 0 and self.stat_invalid > retry * max(1, pm.total_steps) * pps and not self._retry_warned:
+                self._retry_warned = True
+                logger.warning("[Controller] %d prompt groups were dropped for lack of reward signal, more than "
+                               "max_retry_for_on_policy (%d) per step on average: check the reward function",
+                               self.stat_invalid, retry)
             return batch, is_end
 
     # ------------------------------------------------------------------ rollouts

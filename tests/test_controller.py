@@ -306,3 +306,20 @@ def test_cosmos_cli_against_a_live_controller(tmp_path, capsys):
     assert cli.main(["--url", url, "nccl", "ls"]) == 0
     server.should_exit = True
     th.join(timeout=10)
+
+
+def test_dropped_groups_are_replaced_by_fresh_prompts():
+    """Dynamic sampling: a group without reward signal does not consume the job's prompt budget."""
+    cfg = _config(**{"train.train_policy.variant": "dapo"})
+    c = Controller(cfg, dataset=SyntheticTokenDataset(16, 8, 100))
+    c.policy_status_manager.total_steps = 2                       # 2 steps * 8 rollouts / 4 per prompt = 4 prompts
+    _reg(c, "p0", "POLICY")
+    _reg(c, "r0", "ROLLOUT")
+    batch, is_end = c.get_batched_prompt(4)
+    assert len(batch) == 4 and not is_end                          # dapo: the stream stays open for replacements
+    assert c.get_batched_prompt(4)[0] == []
+    bad = _payload(batch[0][0], 0)
+    bad.valid = False
+    c.put_rollouts("r0", [bad], is_end=False)
+    again, _ = c.get_batched_prompt(4)
+    assert len(again) == 1 and again[0][1].weight_version == batch[3][1].weight_version
