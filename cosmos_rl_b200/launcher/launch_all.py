@@ -63,6 +63,13 @@ def replica_counts(config: Config, args, n_gpus: int) -> Tuple[int, int, int]:
     if config.mode == "colocated":
         if n_policy != n_rollout and n_rollout != 0:
             raise ValueError("colocated mode needs as many rollout replicas as policy replicas")
+    if config.mode == "colocated_separated":
+        # separate policy and rollout processes on the SAME GPUs (weights reach the rollout process through a
+        # CUDA IPC mapping of the policy's buffer): replicas pair up one to one on equal GPU counts
+        gp, gr = gpus_per_replica(config.policy.parallelism), gpus_per_replica(config.rollout.parallelism)
+        if n_policy != n_rollout or gp != gr:
+            raise ValueError("colocated_separated mode needs as many rollout replicas as policy replicas, on the same "
+                             f"number of GPUs each (got {n_policy} x {gp} and {n_rollout} x {gr})")
     return n_policy, n_rollout, n_ref
 
 
@@ -130,7 +137,8 @@ def main(argv=None) -> int:
     except Exception:
         n_gpus = 0
     n_policy, n_rollout, n_ref = replica_counts(config, args, n_gpus)
-    placement = place_replicas(n_policy, n_rollout, n_ref, config, n_gpus, config.mode == "colocated")
+    placement = place_replicas(n_policy, n_rollout, n_ref, config, n_gpus,
+                               config.mode in ("colocated", "colocated_separated"))
     log_dir = None
     if args.log_dir:
         log_dir = os.path.join(args.log_dir, time.strftime("logs_%Y%m%d-%H%M%S"))

@@ -235,6 +235,18 @@ def test_launcher_gpu_math_and_placement():
     c.train.train_policy.type = "sft"
     args.p2r_ratio = None
     assert L.replica_counts(c, args, 8)[1] == 0                    # SFT launches no rollout replicas
+    # colocated_separated: paired policy / rollout processes share GPUs; unequal pairs are rejected
+    sep = Config.from_dict({"mode": "colocated_separated",
+                            "policy": {"model_name_or_path": "tiny-qwen2", "parallelism": {"tp_size": 1, "dp_shard_size": 2,
+                                                                                       "n_init_replicas": 2}},
+                            "rollout": {"parallelism": {"tp_size": 2, "n_init_replicas": 2}},
+                            "train": {"train_policy": {"type": "grpo"}}})
+    assert L.replica_counts(sep, args, 8) == (2, 2, 0)
+    place = L.place_replicas(2, 2, 0, sep, 8, colocated=True)
+    assert [p["gpus"] for p in place] == [[0, 1], [2, 3], [0, 1], [2, 3]]
+    sep.rollout.parallelism.n_init_replicas = 1
+    with pytest.raises(ValueError):
+        L.replica_counts(sep, args, 8)
     import signal
     assert L.is_coordinated_controller_exit(-signal.SIGTERM) and not L.is_coordinated_controller_exit(1)
     sock, port = L.reserve_port(None)
