@@ -101,10 +101,22 @@ class DiffusionRollout(RolloutGenerationMixin, RolloutBase):
         text, mask = text.to(self.device, dtype), mask.to(self.device)
         was_training = model.training
         model.eval()
-        if o["sampler"] == "sde" and not is_validation:
-            out = D.sde_sample(model, noise, text, mask, o["sample_steps"], o["shift"], o["noise_level"])
+        def sample(rows: slice):
+            if o["sampler"] == "sde" and not is_validation:
+                return D.sde_sample(model, noise[rows], text[rows], mask[rows], o["sample_steps"], o["shift"],
+                                    o["noise_level"])
+            return {"x0": D.euler_sample(model, noise[rows], text[rows], mask[rows], o["sample_steps"], o["shift"])}
+
+        # rollout.n_generation_mini_batch: the sampler sees that many latents at a time (activation memory of a large
+        # group). The starting noise of every row is drawn up front, so the ODE sampler returns the same latents as in
+        # one pass; the SDE sampler draws its per-step noise chunk by chunk
+        mb = int(getattr(self.config.rollout, "n_generation_mini_batch", None) or 0)
+        rows = text.shape[0]
+        if mb > 0 and rows > mb:
+            parts = [sample(slice(s_, min(s_ + mb, rows))) for s_ in range(0, rows, mb)]
+            out = {k: (parts[0][k] if k == "timesteps" else torch.cat([p[k] for p in parts], 0)) for k in parts[0]}
         else:
-            out = {"x0": D.euler_sample(model, noise, text, mask, o["sample_steps"], o["shift"])}
+            out = sample(slice(0, rows))
         model.train(was_training)
         out["text"], out["text_mask"] = text, mask
         return out, n

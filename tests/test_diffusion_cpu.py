@@ -135,3 +135,23 @@ def test_diffusion_rl_raises_the_reward(tmp_path, trainer_type, extra):
     fresh.init_weights(0)
     before = D.euler_sample(fresh.eval(), noise, text, steps=4).mean().item()
     assert after > before + 0.02, (before, after)
+
+
+def test_generation_mini_batches_give_the_same_latents(tmp_path):
+    """``rollout.n_generation_mini_batch``: the ODE sampler run on slices of a group returns the latents of one pass."""
+    from cosmos_rl_b200.parallel.dims import ParallelDims
+    from cosmos_rl_b200.rollout.diffusion_rollout import DiffusionRollout
+
+    def run(mb):
+        c = _config(tmp_path, "diffusion_nft", sampler="ode")
+        c.rollout.n_generation_mini_batch = mb
+        r = DiffusionRollout(c, ParallelDims(world_size=1, device=torch.device("cpu")), torch.device("cpu"))
+        r.init_engine()
+        g = torch.Generator().manual_seed(1)
+        samples = [(torch.randn(5, r.model.args.text_dim, generator=g), 7), (torch.randn(3, r.model.args.text_dim, generator=g), 8)]
+        out, n = r._generate(r._collate_batch(samples, False), False)
+        return out["x0"], n
+
+    full, n = run(None)
+    part, _ = run(3)
+    assert n == 4 and full.shape[0] == 8 and torch.allclose(full, part, atol=1e-5)
