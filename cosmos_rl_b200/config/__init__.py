@@ -432,6 +432,8 @@ class B200Config(_Section):
     fused_logprob: bool = True           # tcgen05 fused lm_head + log-prob kernel
     nvls: bool = True                    # allow multimem (NVSwitch) reductions where available
     dlogits_chunk: int = 16384
+    pp_head_weight: float = 0.0          # pipeline layer split: cost of final norm + lm_head / of the embedding in
+    pp_embed_weight: float = 0.0         # block-equivalents (the last / first stage get fewer blocks); -1 = from shapes
     cp_mode: str = "kv-gather"           # context-parallel attention exchange: kv-gather | ring | ulysses
     sequence_parallel: bool = False      # with tp_size > 1 (dense models, no pp / cp): residual stream and norms hold
                                          # T / tp rows (the reference's plan; halves activation memory at tp 2).

@@ -45,6 +45,8 @@ class GPTArgs:
     tp_rank: int = 0
     pp_size: int = 1        # pipeline stages: a stage owns a contiguous range of blocks (+ embedding / head)
     pp_rank: int = 0
+    pp_embed_weight: float = 0.0    # cost of the embedding (first stage) and of final norm + lm_head (last stage)
+    pp_head_weight: float = 0.0     # in units of one block, for the layer split; -1 = from the shapes
 
     def __post_init__(self):
         if self.head_dim is None:
@@ -52,9 +54,33 @@ class GPTArgs:
 
     def stage_layers(self) -> Tuple[int, int]:
         """[lo, hi) block indices of this pipeline stage (earlier stages take the remainder)."""
-        base, rem = divmod(self.n_layers, self.pp_size)
-        lo = self.pp_rank * base + min(self.pp_rank, rem)
-        return lo, lo + base + (1 if self.pp_rank < rem else 0)
+        bounds = self.stage_bounds()
+        return bounds[self.pp_rank], bounds[self.pp_rank + 1]
+
+    def stage_bounds(self) -> List[int]:
+        """Block index where every stage starts (plus n_layers). Without weights: an even split. With
+        ``pp_embed_weight`` / ``pp_head_weight`` the first / last stage are charged that many block-equivalents, so
+        they get fewer blocks (the reference balances its DeepSeek stages by per-layer weights in the same spirit,
+        cosmos_rl/utils/pipelining/pipelining_utils.py:36-110); every stage keeps at least one block."""
+        n, pp = self.n_layers, self.pp_size
+        head = self.pp_head_weight
+        if head < 0:        # lm_head GEMM against one block's GEMMs (attention projections + SwiGLU), per token
+            per_block = self.dim * (self.n_heads + 2 * self.n_kv_heads) * self.head_dim \
+                + self.n_heads * self.head_dim * self.dim + 3 * self.dim * self.ffn_dim
+            head = self.vocab_size * self.dim / per_block
+        embed = max(0.0, self.pp_embed_weight)
+        if pp == 1 or (head == 0 and embed == 0):
+            base, rem = divmod(n, pp)
+            return [r * base + min(r, rem) for r in range(pp)] + [n]
+        target = (n + head + embed) / pp
+        bounds, done = [0], 0
+        for r in range(pp - 1):
+            want = target * (r + 1) - embed            # blocks that should sit before the end of stage r
+            k = int(round(want)) - done
+            k = max(1, min(k, n - done - (pp - 1 - r)))     # at least one block here and on every later stage
+            done += k
+            bounds.append(done)
+        return bounds + [n]
 
     @classmethod
     def from_hf_config(cls, c, **over) -> "GPTArgs":

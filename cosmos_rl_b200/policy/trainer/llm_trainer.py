@@ -53,6 +53,8 @@ class LLMTrainer(Trainer):
             build_kw = dict(ep_size=ep, ep_rank=parallel_dims.dp_shard_coord)
         if parallel_dims.pp > 1:
             build_kw.update(pp_size=parallel_dims.pp, pp_rank=parallel_dims.pp_coord)
+            if config.b200.pp_head_weight or config.b200.pp_embed_weight:
+                build_kw.update(pp_head_weight=config.b200.pp_head_weight, pp_embed_weight=config.b200.pp_embed_weight)
         with torch.device("meta"):
             model = ModelRegistry.build_model(self.hf_config, tp_size=tp, tp_rank=parallel_dims.tp_coord, **build_kw)
         if ep > 1 and not hasattr(model, "set_ep_group"):

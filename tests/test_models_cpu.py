@@ -333,3 +333,17 @@ def test_engine_repetition_penalty_matches_step_by_step_rule():
             seen.add(t)
         assert comps[0].token_ids == want and comps[1].token_ids == want
         assert len(base[0].token_ids) == 6
+
+
+def test_weighted_pipeline_layer_split():
+    """The last / first pipeline stage can be charged for lm_head / embedding in block-equivalents."""
+    from cosmos_rl_b200.models.gpt import GPT, GPTArgs
+    kw = dict(vocab_size=152064, dim=3584, n_layers=28, n_heads=28, n_kv_heads=4, head_dim=128, ffn_dim=18944)
+    assert GPTArgs(pp_size=4, **kw).stage_bounds() == [0, 7, 14, 21, 28]
+    b = GPTArgs(pp_size=4, pp_head_weight=-1, **kw).stage_bounds()           # lm_head of this shape ~ 2.3 blocks
+    assert b == [0, 8, 15, 23, 28]
+    small = dict(vocab_size=512, dim=64, n_heads=4, n_kv_heads=2, ffn_dim=128)
+    assert GPTArgs(n_layers=7, pp_size=2, pp_head_weight=2, pp_embed_weight=1, **small).stage_bounds() == [0, 4, 7]
+    assert GPTArgs(n_layers=3, pp_size=3, pp_head_weight=50, **small).stage_bounds() == [0, 1, 2, 3]   # never empty
+    stages = [GPT(GPTArgs(n_layers=7, pp_size=2, pp_rank=r, pp_head_weight=2, pp_embed_weight=1, **small)) for r in (0, 1)]
+    assert [len(s.layers) for s in stages] == [4, 3] and stages[1].layer_offset == 4
