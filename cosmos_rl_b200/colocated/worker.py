@@ -25,7 +25,7 @@ from ..data.packer import BaseDataPacker
 from ..parallel.dims import ParallelDims
 from ..policy.trainer import diffusion_trainer, grpo_trainer, vla_trainer  # noqa: F401
 from ..policy.trainer.base import TrainerRegistry
-from ..reward.dispatcher import LocalRewardCalculator
+from ..reward.dispatcher import make_reward_calculator
 from ..rollout import b200_rollout, diffusion_rollout, hf_rollout, vla_rollout  # noqa: F401  (register the built-in backends)
 from ..rollout.base import RolloutRegistry
 from ..utils.logging import logger
@@ -59,7 +59,7 @@ class ColocatedRLControlWorker:
         self.packer = data_packer or BaseDataPacker.get_default(mt)()
         self.packer.setup(config, tokenizer)
         self.fetcher = WorkerDataFetcher(config, CosmosDataset.wrap(dataset, config))
-        self.rewards = LocalRewardCalculator(config, reward_fns)
+        self.rewards = make_reward_calculator(config, reward_fns)
         self.policy_name, self.rollout_name = "colocated-policy", "colocated-rollout"
         self.weight_version = 0
         self._cmd_pos = {self.policy_name: 0, self.rollout_name: 0}

@@ -96,26 +96,73 @@ class LocalRewardCalculator:
 
 
 class RemoteRewardCalculator:
-    """Scores completions through an HTTP reward service (cosmos_rl/reward/remote_calculator.py:41-436)."""
+    """Scores completions through the HTTP reward service (``train_policy.use_remote_reward``): the completions of a
+    prompt go out as one media tensor, every configured reward function returns one score per completion, and the
+    reward is ``clip(scale * sum_f weight_f * clip_f(score_f))`` (cosmos_rl/reward/remote_calculator.py:41-436; the
+    service address comes from the environment there as well: REMOTE_REWARD_ENQUEUE_URL / _FETCH_URL)."""
 
-    def __init__(self, config, url: str, timeout_s: float = 60.0):
-        self.config, self.url, self.timeout_s = config, url, timeout_s
+    def __init__(self, config, url: Optional[str] = None, timeout_s: float = 600.0, validation: bool = False):
+        import os
+        from ..reward_service.client import RewardClient
+        url = url or os.environ.get("REMOTE_REWARD_URL") or os.environ.get("REMOTE_REWARD_ENQUEUE_URL", "")
+        if not url:
+            raise ValueError("use_remote_reward needs the service address in REMOTE_REWARD_URL")
+        for suffix in ("/api/reward/enqueue", "/api/reward/pull"):
+            if url.endswith(suffix):
+                url = url[:-len(suffix)]
+        self.config, self.url = config, url
         self.rr = config.train.train_policy.remote_reward
-        self.local = LocalRewardCalculator(config, reward_fns=[lambda *a, **k: 0.0])
+        if not self.rr.reward_fns:
+            raise ValueError("train.train_policy.remote_reward.reward_fns names no reward function")
+        self.client = RewardClient(url, timeout_s=timeout_s)
+        self.local = LocalRewardCalculator(config, reward_fns=[lambda *a, **k: 0.0], validation=validation)
+
+    @staticmethod
+    def media_of(completions) -> "torch.Tensor":
+        """One tensor [n, ...] from the completions of a prompt: tensors, dicts that carry ``media`` or the handle of a
+        stored sample (diffusion rollouts keep their latents in the process-local store)."""
+        import torch
+        items = []
+        for c in completions:
+            if isinstance(c, dict) and "latent_id" in c:
+                from ..rollout.diffusion_rollout import LatentStore
+                c = LatentStore.get(c)["x0"]
+            elif isinstance(c, dict) and "media" in c:
+                c = c["media"]
+            items.append(torch.as_tensor(c).detach().float().cpu())
+        return torch.stack(items)
 
     def compute(self, payload: RLPayload) -> RLPayload:
-        import requests
-        body = {"prompt": payload.prompt, "completions": payload.completions, "reference": payload.reference_answer}
-        r = requests.post(self.url, json=body, timeout=self.timeout_s)
-        r.raise_for_status()
-        scores = r.json()["scores"]
         rr = self.rr
-        rewards = [min(max(float(s) * rr.scale, rr.reward_clip_min), rr.reward_clip_max) for s in scores]
+        comps = payload.completions or []
+        meta = {"prompt": payload.prompt if isinstance(payload.prompt, str) else None, "prompt_idx": payload.prompt_idx}
+        res = self.client.score([f.name for f in rr.reward_fns], meta, self.media_of(comps))
+        total = [0.0] * len(comps)
+        for f in rr.reward_fns:
+            scores = res[f.name]["scores"]
+            vals = scores[f.score_key] if f.score_key else next(iter(scores.values()))
+            if len(vals) != len(comps):
+                raise ValueError(f"reward {f.name!r} returned {len(vals)} scores for {len(comps)} completions")
+            for i, v in enumerate(vals):
+                total[i] += f.weight * min(max(float(v), f.clip_min), f.clip_max)
+        rewards = [min(max(t * rr.scale, rr.reward_clip_min), rr.reward_clip_max) for t in total]
         payload.rewards = rewards
-        payload.advantages = self.local.algo.compute_advantage(rewards)
+        payload.advantages = [min(max(a, self.local.adv_low), self.local.adv_high)
+                              for a in self.local.algo.compute_advantage(rewards)]
         payload.filter_rewards = list(rewards)
         payload.valid = True
         return payload
+
+
+def make_reward_calculator(config, reward_fns=None, filter_reward_fns=None, validation: bool = False):
+    """Local rule-based rewards, or the remote service when the (validation) policy asks for it."""
+    tp = config.train.train_policy
+    remote = config.validation.use_remote_reward if validation else getattr(tp, "use_remote_reward", False)
+    if remote:
+        return RemoteRewardCalculator(config, validation=validation)
+    if validation:
+        return LocalRewardCalculator(config, reward_fns, validation=True)
+    return LocalRewardCalculator(config, reward_fns, filter_reward_fns)
 
 
 class RewardDispatcher:

@@ -25,7 +25,7 @@ from ..dispatcher.data.schema import RLPayload
 from ..dispatcher.protocol import Role
 from ..parallel.dims import ParallelDims
 from ..parallel.reshard import build_plan, model_parts, shard_info
-from ..reward.dispatcher import LocalRewardCalculator, RewardDispatcher
+from ..reward.dispatcher import RewardDispatcher, make_reward_calculator
 from ..utils import constant
 from ..utils.logging import logger
 from .base import RolloutRegistry
@@ -62,9 +62,9 @@ class DisaggregatedRolloutControlWorker(CommMixin):
         mt = getattr(self.rollout.model.args, "model_type", "hfmodel")
         self.data_packer = data_packer or BaseDataPacker.get_default(mt)()
         self.data_packer.setup(config, tokenizer)
-        self.reward_dispatcher = RewardDispatcher(LocalRewardCalculator(config, reward_fns, filter_reward_fns))
+        self.reward_dispatcher = RewardDispatcher(make_reward_calculator(config, reward_fns, filter_reward_fns))
         self.val_reward_dispatcher = RewardDispatcher(
-            LocalRewardCalculator(config, val_reward_fns or reward_fns, validation=True))
+            make_reward_calculator(config, val_reward_fns or reward_fns, validation=True))
         self.current_weight_version = -1
         self.weights_ready = False
         self.prompt_queue: List[Tuple[int, RLPayload]] = []

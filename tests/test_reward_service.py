@@ -76,3 +76,42 @@ def test_http_round_trip(tmp_path):
     server.should_exit = True
     th.join(timeout=10)
     svc.close()
+
+
+def test_remote_reward_calculator_scores_a_group_through_the_service(monkeypatch):
+    """``use_remote_reward``: the completions of a prompt go to the service as one tensor; weights, per-function and
+    total clipping are applied; advantages are centred within the group."""
+    import uvicorn
+    from cosmos_rl_b200.config import Config
+    from cosmos_rl_b200.dispatcher.data.schema import RLPayload
+    from cosmos_rl_b200.reward.dispatcher import RemoteRewardCalculator, make_reward_calculator
+
+    @RewardHandlerRegistry.register("plain_mean")
+    class PlainMean(BaseRewardHandler):
+        def score(self, media, metadata):
+            return {"mean": media.float().mean(dim=tuple(range(1, media.dim()))).tolist()}
+
+    svc = RewardService(["plain_mean"], num_workers=1)
+    sock = socket.socket()
+    sock.bind(("127.0.0.1", 0))
+    port = sock.getsockname()[1]
+    server = uvicorn.Server(uvicorn.Config(build_app(svc), log_level="warning"))
+    threading.Thread(target=server.run, kwargs={"sockets": [sock]}, daemon=True).start()
+    cli = RewardClient(f"http://127.0.0.1:{port}", timeout_s=20)
+    for _ in range(100):
+        try:
+            cli.ping()
+            break
+        except Exception:
+            time.sleep(0.1)
+    c = Config.from_dict({"train": {"train_policy": {"type": "grpo", "use_remote_reward": True, "remote_reward": {
+        "scale": 2.0, "reward_clip_max": 1.5,
+        "reward_fns": [{"name": "plain_mean", "weight": 1.0, "score_key": "mean", "clip_max": 0.6}]}}}})
+    monkeypatch.setenv("REMOTE_REWARD_URL", f"http://127.0.0.1:{port}/api/reward/enqueue")
+    calc = make_reward_calculator(c)
+    assert isinstance(calc, RemoteRewardCalculator) and calc.url == f"http://127.0.0.1:{port}"
+    comps = [torch.full((3, 1, 4, 4), v) for v in (0.1, 0.5, 0.9)]
+    p = calc.compute(RLPayload(prompt="a cat", prompt_idx=0, completions=comps))
+    assert p.rewards == pytest.approx([0.2, 1.0, 1.2])        # 0.9 clipped to 0.6 before the scale of 2
+    assert abs(sum(p.advantages)) < 1e-5 and p.advantages[2] > p.advantages[0]
+    server.should_exit = True
