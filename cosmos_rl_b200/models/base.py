@@ -60,8 +60,11 @@ class ModelRegistry:
         return sorted(cls._models)
 
     @classmethod
-    def build_model(cls, hf_config, **kw) -> "BaseModel":
+    def build_model(cls, hf_config, force_hf: bool = False, **kw) -> "BaseModel":
+        """``force_hf`` (``train.force_use_hf``): the generic transformers wrapper even where a native model exists."""
         mt = getattr(hf_config, "model_type", None) or hf_config.get("model_type")
+        if force_hf and "hfmodel" in cls._models:
+            return cls._models["hfmodel"].from_hf_config(hf_config, **kw)
         return cls.get(mt).from_hf_config(hf_config, **kw)
 
 

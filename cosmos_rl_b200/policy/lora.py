@@ -210,15 +210,25 @@ def bind_lora(model: nn.Module) -> int:
 
 
 @torch.no_grad()
-def reset_lora_parameters(model: nn.Module, seed: int = 0) -> None:
-    """A ~ Kaiming-uniform, B = 0: the adapted model starts as the base model."""
+def reset_lora_parameters(model: nn.Module, seed: int = 0, init=True) -> None:
+    """``init`` follows PEFT's ``init_lora_weights``: True = A Kaiming-uniform, B = 0 (the adapted model starts as the
+    base model); "gaussian" = A ~ N(0, 1/r), B = 0; False = both random (debugging: the adapter is not a no-op)."""
+    if init not in (True, False, "gaussian"):
+        raise NotImplementedError(f"init_lora_weights = {init!r}: supported are true, false and \"gaussian\"")
     g = torch.Generator(device="cpu").manual_seed(seed)
     for mod in model.modules():
         if isinstance(mod, nn.Linear) and hasattr(mod, "lora_A"):
-            bound = 1.0 / math.sqrt(mod.in_features)        # kaiming_uniform with a = sqrt(5)
-            a = (torch.rand(mod.lora_A.shape, generator=g) * 2 - 1) * bound
+            if init == "gaussian":
+                a = torch.randn(mod.lora_A.shape, generator=g) / mod.lora_A.shape[0]
+            else:
+                bound = 1.0 / math.sqrt(mod.in_features)        # kaiming_uniform with a = sqrt(5)
+                a = (torch.rand(mod.lora_A.shape, generator=g) * 2 - 1) * bound
             mod.lora_A.copy_(a.to(mod.lora_A.dtype))
-            mod.lora_B.zero_()
+            if init is False:
+                bound_b = 1.0 / math.sqrt(mod.lora_B.shape[1])
+                mod.lora_B.copy_(((torch.rand(mod.lora_B.shape, generator=g) * 2 - 1) * bound_b).to(mod.lora_B.dtype))
+            else:
+                mod.lora_B.zero_()
 
 
 def lora_refs(model: nn.Module) -> List[LoraRef]:

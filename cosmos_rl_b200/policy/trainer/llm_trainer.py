@@ -56,7 +56,12 @@ class LLMTrainer(Trainer):
             if config.b200.pp_head_weight or config.b200.pp_embed_weight:
                 build_kw.update(pp_head_weight=config.b200.pp_head_weight, pp_embed_weight=config.b200.pp_embed_weight)
         with torch.device("meta"):
-            model = ModelRegistry.build_model(self.hf_config, tp_size=tp, tp_rank=parallel_dims.tp_coord, **build_kw)
+            if config.train.force_use_hf:
+                if tp > 1 or build_kw:
+                    raise NotImplementedError("train.force_use_hf: the generic wrapper trains with data parallelism only")
+                model = ModelRegistry.build_model(self.hf_config, force_hf=True)
+            else:
+                model = ModelRegistry.build_model(self.hf_config, tp_size=tp, tp_rank=parallel_dims.tp_coord, **build_kw)
         if ep > 1 and not hasattr(model, "set_ep_group"):
             raise NotImplementedError(f"model type {mt} has no expert-parallel plan")
         # the model stays on the meta device here: FlatParams materialises every parameter as a view of
@@ -278,7 +283,8 @@ class LLMTrainer(Trainer):
             logger.info("[Policy] no checkpoint at %r: random-init weights from seed %d", path, seed)
         if self.lora_targets:
             from .. import lora
-            lora.reset_lora_parameters(self.model, self.config.train.seed or 0)
+            lora.reset_lora_parameters(self.model, self.config.train.seed or 0,
+                                       init=self.config.policy.lora.init_lora_weights)
         self.optimizer.refresh_master_from_params()
         self._init_ema()
         self.weights_ready = True

@@ -427,3 +427,27 @@ def test_sft_trainer_with_8bit_adam(tmp_path):
     batch = [{"input_ids": torch.randint(0, 32000, (12,), generator=g).tolist()} for _ in range(4)]
     losses = [tr.step_training(batch, 10, i + 1)["train/loss_avg"] for i in range(5)]
     assert losses[-1] < losses[0] - 0.5
+
+
+def test_force_use_hf_and_lora_init_modes(tmp_path):
+    """``train.force_use_hf`` trains the generic transformers wrapper although a native model exists for the type;
+    ``policy.lora.init_lora_weights`` picks the adapter initialisation."""
+    import torch
+    from cosmos_rl_b200.models.hf_model import HFModel
+    from cosmos_rl_b200.policy.trainer.sft_trainer import SFTTrainer
+    dims = ParallelDims(world_size=1, device=torch.device("cpu"))
+    c = _config(tmp_path, "sft")
+    c.train.force_use_hf = True
+    tr = SFTTrainer(c, dims, device=torch.device("cpu"))
+    tr.model_load_from_hf()
+    assert isinstance(tr.model, HFModel)
+    g = torch.Generator().manual_seed(0)
+    batch = [{"input_ids": torch.randint(0, 32000, (12,), generator=g).tolist()} for _ in range(4)]
+    assert tr.step_training(batch, 10, 1)["train/grad_norm"] > 0
+    for init, b_zero in ((True, True), ("gaussian", True), (False, False)):
+        c = _config(tmp_path, "sft")
+        c.policy.lora = type(c.policy).model_fields["lora"].annotation.__args__[0](r=4, lora_alpha=8, init_lora_weights=init, target_modules=["q_proj", "v_proj"])
+        tr = SFTTrainer(c, dims, device=torch.device("cpu"))
+        tr.model_load_from_hf()
+        bs = [p for n, p in tr.model.named_parameters() if n.endswith("lora_B")]
+        assert bs and all((p.abs().sum() == 0) == b_zero for p in bs)
