@@ -17,7 +17,8 @@ class RolloutGenerationMixin:
         prefetch = bool(getattr(self.config.rollout, "prefetch_rollout", False))
         if prefetch and len(payloads) > 1:
             pool = self.__dict__.setdefault("_prep_pool", concurrent.futures.ThreadPoolExecutor(
-                max_workers=self.prefetch_workers, thread_name_prefix="rollout-prep"))
+                max_workers=max(1, int(getattr(self.config.rollout, "prefetch_queue_maxsize", self.prefetch_workers))),
+                thread_name_prefix="rollout-prep"))
             samples = list(pool.map(lambda p: self._prepare_sample(p, data_packer, is_validation), payloads))
         else:
             samples = [self._prepare_sample(p, data_packer, is_validation) for p in payloads]
