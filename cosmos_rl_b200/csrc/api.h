@@ -26,6 +26,36 @@ int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, l
                    long long ldc, int a_mn, int b_mn, int out_fp32, int accumulate, uint32_t* status, int num_sms,
                    cudaStream_t stream);
 
+// Same with the epilogues of the CTA-pair kernel (256 x 256 tiles over two SMs, TMA-store epilogue):
+//   bias      [N] added to every row (nullable; bf16 when bias_bf16 else fp32)
+//   epilogue  0: C[M, N] = A B^T (+ bias);  1: SwiGLU, C[M, N/2] = silu(A Bg^T) * (A Bu^T) where Bg = B[0 : N/2] and
+//             Bu = B[up_row0 : up_row0 + N/2] (the fused gate_up weight: up_row0 = intermediate size)
+//   path      0: choose (pairs when M > 128 and C is 16-byte aligned), 1: single-CTA kernel, 2: CTA pairs
+int b200_gemm_bf16_ex(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                      long long ldc, int a_mn, int b_mn, int out_fp32, int accumulate, const void* bias,
+                      int bias_bf16, int epilogue, int up_row0, int path, uint32_t* status, int num_sms,
+                      cudaStream_t stream);
+
+// Weight-streaming GEMM for decode-sized batches (M <= 256) and the reductions that finish a decode-layer step
+// (gemm_skinny.cu). x [M, K] bf16, W [rows, K] bf16. ws == NULL: out (bf16) = x W^T (+ bias), splits = 1; swiglu: W is a
+// fused gate/up weight with up rows at up_row0 and out = silu(x Wg^T) * (x Wu^T) of N columns. ws != NULL: fp32
+// partial results [splits, M, N] for one of the reduce kernels.
+int b200_gemm_skinny_splits(int M, int N, int K, int swiglu, int num_sms);
+int b200_gemm_skinny(const void* x, const void* W, void* out, float* ws, int M, int N, int K, long long ldx,
+                     long long ldw, long long ldo, const void* bias, int bias_bf16, int swiglu, int up_row0,
+                     int splits, uint32_t* status, int num_sms, cudaStream_t stream);
+int b200_splitk_reduce(const float* ws, int splits, int M, int N, const void* bias, int bias_bf16, void* out,
+                       long long ldo, cudaStream_t stream);
+// res_out = sum(ws) (+ res_in);  y = rmsnorm(res_out) * w   (bf16 rows of H <= 8192 values)
+int b200_splitk_reduce_residual_rmsnorm(const float* ws, int splits, int M, int H, const void* res_in, const void* w,
+                                        float eps, void* res_out, void* y, cudaStream_t stream);
+// q_out [M, hq * d] = rope(sum(ws) + bias); K and V rows go to cache [pages, 2, hkv, page_size, d] at slot_mapping[r]
+// (V slabs [d, page_size] when v_transposed; slot < 0 skips the write).
+int b200_splitk_reduce_qkv_rope_append(const float* ws, int splits, int M, int hq, int hkv, int d, const void* bias,
+                                       int bias_bf16, const long long* positions, const int* slot_mapping,
+                                       float theta, void* q_out, void* cache, int page_size, int v_transposed,
+                                       cudaStream_t stream);
+
 // Fused lm_head GEMM + per-token log-prob statistics, never materialising [T, V] logits.
 //   hidden [T, H] bf16, weight [V, H] bf16, labels [T] int64 (label < 0: row ignored)
 //   partial [T, nsplit, 4] fp32 scratch: (max, sumexp, label_logit, sum p_unnorm*logit)

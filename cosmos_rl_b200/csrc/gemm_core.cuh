@@ -14,6 +14,8 @@
 // same pipeline. All mbarrier waits are bounded; on a timeout the kernel records
 // a status code, frees its TMEM and returns.
 #pragma once
+#include <type_traits>
+
 #include "sm100.cuh"
 
 namespace b200 {
@@ -40,6 +42,7 @@ struct TileInfo {
   int k0;            // first contraction index
   int num_kb;        // number of 64-wide contraction blocks
   int batch;         // third tensor-map coordinate (expert / batch index) when a map is 3-D
+  int b_mn1;         // Traits::B_TWO_BOXES: first row of the second half of the B tile (rows b_mn0.. and b_mn1..)
 };
 
 // Operand layouts. K-major: the contraction index is contiguous in memory (x[M,K] row-major, W[N,K]
@@ -50,13 +53,23 @@ struct TileInfo {
 // Epi::side() concurrently with the pipeline (used by the fused GEMM + cross-GPU reduction kernel).
 // PRODUCER_HOOK: the TMA producer calls sched.before_tile_load(tile, ep, status) before the first load of a tile
 // and gives up (abort) when it returns false (used to wait for operand rows that another GPU is still sending).
+// B_TWO_BOXES (K-major 2-D B only): the B tile is fetched as two boxes of BN / 2 rows starting at rows t.b_mn0 and
+// t.b_mn1 (gate and up rows of a fused gate/up weight, so that one accumulator row holds both).
 template <bool A_MN_ = false, bool B_MN_ = false, bool A_3D_ = false, bool B_3D_ = false, int SIDE_WARPS_ = 0,
-          bool PRODUCER_HOOK_ = false>
+          bool PRODUCER_HOOK_ = false, bool B_TWO_BOXES_ = false>
 struct GemmTraits {
   static constexpr bool A_MN = A_MN_, B_MN = B_MN_, A_3D = A_3D_, B_3D = B_3D_;
   static constexpr int SIDE_WARPS = SIDE_WARPS_;
   static constexpr bool PRODUCER_HOOK = PRODUCER_HOOK_;
+  static constexpr bool B_TWO_BOXES = B_TWO_BOXES_;
 };
+
+// An epilogue that declares `static constexpr bool CUSTOM_TILE = true` reads its accumulator itself:
+//   __device__ void tile(const Params&, const TileInfo&, int row, uint32_t taddr /* this warp's lanes, column 0 */);
+template <class E, class = void>
+struct epi_custom_tile : std::false_type {};
+template <class E>
+struct epi_custom_tile<E, std::void_t<decltype(E::CUSTOM_TILE)>> : std::true_type {};
 
 // Default schedule: grouped raster over (m, n) tiles, strided over the grid.
 struct RasterSchedule {
@@ -173,7 +186,10 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
               else tma_load_2d(sa + i * 8192, tmA, &full_bar[stage], t.a_mn0 + i * 64, k);
             }
           }
-          if constexpr (!Traits::B_MN) {
+          if constexpr (Traits::B_TWO_BOXES) {
+            tma_load_2d(sb, tmB, &full_bar[stage], k, t.b_mn0);
+            tma_load_2d(sb + SM::B_BYTES / 2, tmB, &full_bar[stage], k, t.b_mn1);
+          } else if constexpr (!Traits::B_MN) {
             if constexpr (Traits::B_3D) tma_load_3d(sb, tmB, &full_bar[stage], k, t.b_mn0, t.batch);
             else tma_load_2d(sb, tmB, &full_bar[stage], k, t.b_mn0);
           } else {
@@ -247,19 +263,23 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
         break;
       }
       tc_fence_after_sync();
-      epi.tile_begin(ep, t, row);
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
+      if constexpr (epi_custom_tile<Epi>::value) {
+        epi.tile(ep, t, row, taddr);
+      } else {
+        epi.tile_begin(ep, t, row);
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + c, r);
-        tmem_ld_wait();
-        float v[32];
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c, r);
+          tmem_ld_wait();
+          float v[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = (t.num_kb > 0) ? __uint_as_float(r[i]) : 0.f;
-        epi.chunk(ep, t, row, c, v);
+          for (int i = 0; i < 32; ++i) v[i] = (t.num_kb > 0) ? __uint_as_float(r[i]) : 0.f;
+          epi.chunk(ep, t, row, c, v);
+        }
+        epi.tile_end(ep, t, row);
       }
-      epi.tile_end(ep, t, row);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);

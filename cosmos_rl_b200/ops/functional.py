@@ -214,34 +214,51 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = False,
-         out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, accumulate: bool = False) -> torch.Tensor:
-    """General tcgen05 GEMM ``C[M, N] (+)= A . B^T`` on row-major bf16 tensors.
-    ``a_mn``: ``a`` is stored ``[K, M]`` instead of ``[M, K]``; ``b_mn``: ``b`` is stored ``[K, N]`` instead of ``[N, K]``."""
+         out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, accumulate: bool = False,
+         bias: Optional[torch.Tensor] = None, swiglu: bool = False, path: int = 0) -> torch.Tensor:
+    """General tcgen05 GEMM ``C[M, N] (+)= A . B^T (+ bias)`` on row-major bf16 tensors.
+
+    ``a_mn``: ``a`` is stored ``[K, M]`` instead of ``[M, K]``; ``b_mn``: ``b`` is stored ``[K, N]`` instead of
+    ``[N, K]``. ``bias [N]`` (bf16 or fp32) is added in the epilogue. ``swiglu``: ``b`` is a fused gate/up weight
+    ``[2 I, K]`` and the result is ``silu(A Bg^T) * (A Bu^T)`` of shape ``[M, I]``. ``path``: 0 lets the library choose
+    between the CTA-pair kernel (256-row tiles over two SMs) and the single-CTA kernel, 1 / 2 force one of them."""
     assert a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert a.stride(-1) == 1 and b.stride(-1) == 1 and a.dim() == 2 and b.dim() == 2
     K, M = (a.shape[0], a.shape[1]) if a_mn else (a.shape[1], a.shape[0])
     Kb, N = (b.shape[0], b.shape[1]) if b_mn else (b.shape[1], b.shape[0])
     assert K == Kb, (a.shape, b.shape, a_mn, b_mn)
     if out is None:
-        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+        out = torch.empty(M, N // 2 if swiglu else N, dtype=out_dtype, device=a.device)
+    if bias is not None:
+        assert bias.is_contiguous() and bias.numel() == N and bias.dtype in (torch.bfloat16, torch.float32)
     st = native.status_word(a.device)
     dev = a.device.index if a.device.index is not None else torch.cuda.current_device()
-    native.check(native.lib().b200_gemm_bf16(native.ptr(a), native.ptr(b), native.ptr(out), M, N, K, a.stride(0),
-                                             b.stride(0), out.stride(0), int(a_mn), int(b_mn),
-                                             1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0,
-                                             native.ptr(st), native.num_sms(dev), native.stream()), "gemm_bf16")
+    native.check(native.lib().b200_gemm_bf16_ex(native.ptr(a), native.ptr(b), native.ptr(out), M, N, K, a.stride(0),
+                                                b.stride(0), out.stride(0), int(a_mn), int(b_mn),
+                                                1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0,
+                                                native.ptr(bias), 1 if bias is not None and bias.dtype == torch.bfloat16 else 0,
+                                                1 if swiglu else 0, N // 2 if swiglu else 0, path,
+                                                native.ptr(st), native.num_sms(dev), native.stream()), "gemm_bf16")
     return out
 
 
+def _tc_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """The tensor-core GEMMs move rows with TMA: feature dimensions must give 16-byte rows."""
+    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.dim() == 2
+            and weight.stride(-1) == 1 and weight.shape[0] % 8 == 0 and weight.shape[1] % 8 == 0
+            and weight.stride(0) % 8 == 0)
+
+
 class _LinearTC(torch.autograd.Function):
-    """``y = x W^T (+ b)`` with forward, dgrad and wgrad on the tcgen05 GEMM. When ``W.grad`` already exists
-    the weight gradient is accumulated into it by the GEMM epilogue itself (no separate add pass)."""
+    """``y = x W^T (+ b)`` with forward, dgrad and wgrad on the tcgen05 GEMM. The bias is added in the forward
+    epilogue; when ``W.grad`` already exists the weight gradient is accumulated into it by the GEMM epilogue itself
+    (no separate add pass)."""
 
     @staticmethod
     def forward(ctx, x, weight, bias):
         x2 = _c(x).view(-1, x.shape[-1])
-        y = gemm(x2, weight)
-        if bias is not None:
+        y = gemm(x2, weight, bias=bias if (bias is not None and x2.shape[0] > 128) else None)
+        if bias is not None and x2.shape[0] <= 128:
             y += bias
         ctx.save_for_backward(x2, weight)
         ctx.has_bias = bias is not None
@@ -255,20 +272,155 @@ class _LinearTC(torch.autograd.Function):
         dx = gemm(dy2, weight, b_mn=True) if ctx.needs_input_grad[0] else None
         dw = None
         if ctx.needs_input_grad[1]:
-            if weight.grad is not None and weight.grad.dtype in (torch.bfloat16, torch.float32):
+            if weight.grad is not None and weight.grad.dtype in (torch.bfloat16, torch.float32) \
+                    and weight.grad.stride(-1) == 1:
                 gemm(dy2, x2, a_mn=True, b_mn=True, out=weight.grad, accumulate=True)
                 dw = None  # accumulated in place
             else:
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True)
-        db = dy2.sum(0) if ctx.has_bias else None
+        db = dy2.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
         return (dx.view(ctx.shape) if dx is not None else None), dw, db
 
 
 def linear_tc(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Linear layer on this library's GEMM (CUDA bf16); CPU tensors use ``torch.nn.functional.linear``."""
-    if x.is_cuda and x.dtype == torch.bfloat16:
-        return _LinearTC.apply(x, weight, bias)
+    if _tc_ok(x, weight):
+        if torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad or
+                                        (bias is not None and bias.requires_grad)):
+            return _LinearTC.apply(x, weight, bias)
+        x2 = _c(x).view(-1, x.shape[-1])
+        return linear_infer(x2, weight, bias).view(*x.shape[:-1], weight.shape[0])
     return torch.nn.functional.linear(x, weight, bias)
+
+
+def _dims_ok(*ts: torch.Tensor) -> bool:
+    return all(t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(-1) == 1 and t.stride(0) % 8 == 0
+               and t.shape[1] % 8 == 0 for t in ts)
+
+
+def mm_nt(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x [M, K] @ w [N, K]^T`` (a forward projection) without autograd: this library's GEMM for bf16 CUDA tensors."""
+    return gemm(x, w) if _dims_ok(x, w) else x @ w.t()
+
+
+def mm_nn(gy: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``gy [M, N] @ w [N, K]`` (the input gradient of a projection): ``w`` is read as stored, no transposed copy."""
+    return gemm(gy, w, b_mn=True) if _dims_ok(gy, w) else gy @ w
+
+
+def mm_tn(gy: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16,
+          accumulate: bool = False) -> torch.Tensor:
+    """``gy [T, N]^T @ x [T, K]`` (the weight gradient of a projection), contracting over the token axis of both."""
+    if _dims_ok(gy, x) and (out is None or (out.is_cuda and out.stride(-1) == 1)):
+        return gemm(gy, x, a_mn=True, b_mn=True, out=out, out_dtype=out_dtype, accumulate=accumulate)
+    r = gy.t() @ x
+    if out is None:
+        return r.to(out_dtype)
+    return out.add_(r) if accumulate else out.copy_(r)
+
+
+def linear_infer(x2: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Inference linear on ``x2 [M, K]``: the CTA-pair kernel for wide batches, the weight-streaming split-K kernel
+    for decode-sized ones (``M <= 256``), where reading ``weight`` once is the whole cost."""
+    M = x2.shape[0]
+    if M <= _SKINNY_MAX_M:
+        return gemm_skinny(x2, weight, bias=bias, out=out)
+    return gemm(x2, weight, bias=bias, out=out)
+
+
+# --------------------------------------------------------------------------------------------------
+# decode-sized projections: weight-streaming split-K GEMM + fused reductions
+# --------------------------------------------------------------------------------------------------
+_SKINNY_MAX_M = 256
+_SKINNY_WS_FLOATS = 148 * 2 * 128 * 128      # splits * tiles <= SMs, a tile is 128 x 128 fp32: this bound always holds
+_skinny_ws: dict = {}
+
+
+def _skinny_workspace(device: torch.device) -> torch.Tensor:
+    """fp32 split-K workspace, one per (device, stream) so that concurrent streams never share partial sums. It is
+    created by the first decode-sized projection on that stream (do that once outside CUDA-graph capture)."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), native.stream())
+    w = _skinny_ws.get(key)
+    if w is None:
+        w = _skinny_ws[key] = torch.empty(_SKINNY_WS_FLOATS, dtype=torch.float32, device=device)
+    return w
+
+
+def _skinny_launch(x2, weight, N, swiglu, out, use_ws, bias=None):
+    M, K = x2.shape
+    assert x2.is_cuda and x2.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and M <= _SKINNY_MAX_M
+    assert x2.stride(-1) == 1 and weight.stride(-1) == 1
+    dev = x2.device.index if x2.device.index is not None else torch.cuda.current_device()
+    sms = native.num_sms(dev)
+    L = native.lib()
+    splits = 1 if swiglu else L.b200_gemm_skinny_splits(M, N, K, 0, sms)
+    ws = _skinny_workspace(x2.device) if (use_ws or splits > 1) else None
+    if ws is not None:
+        assert splits * M * N <= ws.numel()
+    st = native.status_word(x2.device)
+    native.check(L.b200_gemm_skinny(native.ptr(x2), native.ptr(weight), native.ptr(out) if ws is None else None,
+                                    native.ptr(ws), M, N, K, x2.stride(0), weight.stride(0),
+                                    out.stride(0) if out is not None else 0, native.ptr(bias),
+                                    1 if bias is not None and bias.dtype == torch.bfloat16 else 0,
+                                    1 if swiglu else 0, N if swiglu else 0, splits, native.ptr(st), sms,
+                                    native.stream()), "gemm_skinny")
+    return ws, splits
+
+
+def gemm_skinny(x2: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x2 [M <= 256, K] @ weight [N, K]^T (+ bias)`` in bf16 on the weight-streaming kernel."""
+    M, N = x2.shape[0], weight.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x2.device)
+    ws, splits = _skinny_launch(x2, weight, N, False, out, False, bias)
+    if ws is not None:
+        native.check(native.lib().b200_splitk_reduce(native.ptr(ws), splits, M, N, native.ptr(bias),
+                                                     1 if bias is not None and bias.dtype == torch.bfloat16 else 0,
+                                                     native.ptr(out), out.stride(0), native.stream()), "splitk_reduce")
+    return out
+
+
+def skinny_gate_up_swiglu(x2: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Tensor:
+    """``silu(x Wg^T) * (x Wu^T)`` for a fused ``[2 I, K]`` weight: the product is formed in the GEMM epilogue."""
+    M, I = x2.shape[0], gate_up_weight.shape[0] // 2
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=x2.device)
+    _skinny_launch(x2, gate_up_weight, I, True, out, False)
+    return out
+
+
+def skinny_linear_residual_rmsnorm(x2: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tensor],
+                                   norm_weight: torch.Tensor, eps: float):
+    """``res' = x2 @ weight^T + residual``; returns ``(rmsnorm(res') * norm_weight, res')``: the split-K reduction of
+    the projection, the residual add and the normalisation are one kernel."""
+    M, H = x2.shape[0], weight.shape[0]
+    ws, splits = _skinny_launch(x2, weight, H, False, None, True)
+    y = torch.empty(M, H, dtype=torch.bfloat16, device=x2.device)
+    res_out = torch.empty_like(y)
+    assert norm_weight.dtype == torch.bfloat16 and (residual is None or residual.is_contiguous())
+    native.check(native.lib().b200_splitk_reduce_residual_rmsnorm(native.ptr(ws), splits, M, H, native.ptr(residual),
+                                                                  native.ptr(norm_weight), float(eps),
+                                                                  native.ptr(res_out), native.ptr(y), native.stream()),
+                 "splitk_reduce_residual_rmsnorm")
+    return y, res_out
+
+
+def skinny_qkv_rope_append(x2: torch.Tensor, qkv_weight: torch.Tensor, bias: Optional[torch.Tensor],
+                           positions: torch.Tensor, slot_mapping: torch.Tensor, theta: float, hq: int, hkv: int, d: int,
+                           cache: torch.Tensor, v_transposed: bool) -> torch.Tensor:
+    """Fused qkv projection of a decode step: returns rotated ``q [M, hq, d]``; the rotated K rows and the V rows are
+    written into the paged ``cache [pages, 2, hkv, page, d]`` at ``slot_mapping`` by the reduction kernel."""
+    M, N = x2.shape[0], qkv_weight.shape[0]
+    assert N == (hq + 2 * hkv) * d and positions.dtype == torch.int64 and slot_mapping.dtype == torch.int32
+    ws, splits = _skinny_launch(x2, qkv_weight, N, False, None, True)
+    q = torch.empty(M, hq, d, dtype=torch.bfloat16, device=x2.device)
+    native.check(native.lib().b200_splitk_reduce_qkv_rope_append(
+        native.ptr(ws), splits, M, hq, hkv, d, native.ptr(bias),
+        1 if bias is not None and bias.dtype == torch.bfloat16 else 0, native.ptr(positions), native.ptr(slot_mapping),
+        float(theta), native.ptr(q), native.ptr(cache), cache.shape[3], 1 if v_transposed else 0, native.stream()),
+        "splitk_reduce_qkv_rope_append")
+    return q
 
 
 # --------------------------------------------------------------------------------------------------
@@ -344,10 +496,15 @@ class _FusedLogprob(torch.autograd.Function):
                                                hidden.stride(0), weight.stride(0), v0, vc, buf.stride(0),
                                                1.0 / ctx.temperature, native.ptr(st), ctx.sms, native.stream()),
                          "lmhead_dlogits")
+            # both products on this library's GEMM: dh accumulates in fp32 through the epilogue's reduce-add,
+            # dW of this vocabulary slice contracts dlogits^T and hidden over the token axis as stored
             if need_dh:
-                dh.add_(torch.mm(dl, weight[v0:v0 + vc]))
+                if _dims_ok(dl, weight):
+                    gemm(dl, weight[v0:v0 + vc], b_mn=True, out=dh, accumulate=True)
+                else:
+                    dh.add_(torch.mm(dl, weight[v0:v0 + vc]))
             if need_dw:
-                torch.mm(dl.t(), hidden, out=dw[v0:v0 + vc])
+                mm_tn(dl, hidden, out=dw[v0:v0 + vc])
         return (dh.to(hidden.dtype) if need_dh else None), dw, None, None, None
 
 
@@ -556,8 +713,8 @@ def fp8_train_supported(w: torch.Tensor) -> bool:
 def linear_maybe_fp8(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x @ w^T + b``. A weight that carries block-scaled fp8 data (``w._fp8 = (e4m3 [N, K], scales)``, attached
     by the rollout's fp8 weight store) is used through the fp8 GEMM in inference; a weight marked ``_fp8_train`` (by
-    the trainer, ``train.fp8.enable_fp8``) runs forward and both backward GEMMs in fp8; everything else is the bf16
-    library GEMM."""
+    the trainer, ``train.fp8.enable_fp8``) runs forward and both backward GEMMs in fp8; everything else runs this
+    library's bf16 tcgen05 GEMM (forward, dgrad and wgrad; ``linear_tc``)."""
     if getattr(w, "_fp8_train", False) and x.dtype in (torch.bfloat16, torch.float32):
         y = _Fp8TrainLinear.apply(x.reshape(-1, x.shape[-1]), w).view(*x.shape[:-1], w.shape[0])
         return y if b is None else y + b
@@ -565,7 +722,7 @@ def linear_maybe_fp8(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor]
     if f8 is not None and x.is_cuda and not torch.is_grad_enabled() and x.dtype == torch.bfloat16:
         y = fp8_linear(x.reshape(-1, x.shape[-1]), f8[0], f8[1]).view(*x.shape[:-1], f8[0].shape[0])
         return y if b is None else y + b
-    return torch.nn.functional.linear(x, w, b)
+    return linear_tc(x, w, b)
 
 
 # --------------------------------------------------------------------------------------------------

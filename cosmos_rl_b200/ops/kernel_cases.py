@@ -65,6 +65,82 @@ def case_gemm(iters):
     report(f"gemm_bf16_nt {M}x{N}x{K}", t, flops=2.0 * M * N * K)
 
 
+def case_gemm_shapes(iters):
+    """Every dense projection of the Qwen2.5-7B block on 8192 tokens (forward, input gradient, weight gradient) and
+    the lm_head-sized GEMM: the CTA-pair kernel, the single-CTA kernel and the library GEMM side by side."""
+    T, H, I, Q = 8192, 3584, 18944, 4608
+    shapes = [("qkv fwd", T, Q, H, 0, 0), ("o fwd", T, H, H, 0, 0), ("gate_up fwd", T, 2 * I, H, 0, 0),
+              ("down fwd", T, H, I, 0, 0), ("qkv dgrad", T, H, Q, 0, 1), ("gate_up dgrad", T, H, 2 * I, 0, 1),
+              ("down dgrad", T, I, H, 0, 1), ("qkv wgrad", Q, H, T, 1, 1), ("gate_up wgrad", 2 * I, H, T, 1, 1),
+              ("down wgrad", H, I, T, 1, 1), ("square 8192x8192x4096", 8192, 8192, 4096, 0, 0)]
+    _, fl, kind = peaks()
+    for name, M, N, K, a_mn, b_mn in shapes:
+        a = bf(K, M) if a_mn else bf(M, K)
+        b = bf(K, N) if b_mn else bf(N, K)
+        c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        tp = timed(lambda: F.gemm(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out=c, path=2), iters)
+        ts = timed(lambda: F.gemm(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out=c, path=1), iters)
+        at = a.t() if a_mn else a
+        bt = b if b_mn else b.t()
+        tl = timed(lambda: torch.matmul(at, bt, out=c), iters)
+        fl_ = 2.0 * M * N * K
+        print(f"{name} {M}x{N}x{K}: pair {tp * 1e6:.0f} us = {fl_ / tp / 1e12:.0f} TFLOP/s ({fl_ / tp / fl:.2f} of {kind} "
+              f"cuBLAS peak) | single-CTA {ts * 1e6:.0f} us = {fl_ / ts / 1e12:.0f} | library {tl * 1e6:.0f} us = "
+              f"{fl_ / tl / 1e12:.0f} | pair/library time {tp / tl:.2f}", flush=True)
+        del a, b, c
+
+
+def case_gemm_pair(iters):
+    """One shape on the CTA-pair kernel (profiling target)."""
+    M, N, K = 8192, 8192, 4096
+    a, b = bf(M, K), bf(N, K)
+    c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    t = timed(lambda: F.gemm(a, b, out=c, path=2), iters)
+    report(f"gemm_bf16 CTA pairs {M}x{N}x{K}", t, flops=2.0 * M * N * K)
+
+
+def case_decode_gemms(iters):
+    """The four projections of a Qwen2.5-7B block and the lm_head at a decode batch of 128 rows: weight-streaming
+    split-K kernel (with its fused reductions) against the library GEMM. Bytes = the weight matrix, read once."""
+    Bm, H, I, Q, V = 128, 3584, 18944, 4608, 152064
+    x, act, o = bf(Bm, H), bf(Bm, I), bf(Bm, H)
+    res = bf(Bm, H)
+    nw = torch.ones(H, dtype=torch.bfloat16, device="cuda")
+    # several copies of each weight so that consecutive launches do not find it in L2
+    n_copies = 4
+    ws = {"qkv": [bf(Q, H, scale=0.02) for _ in range(n_copies)], "o": [bf(H, H, scale=0.02) for _ in range(n_copies)],
+          "gate_up": [bf(2 * I, H, scale=0.02) for _ in range(n_copies)],
+          "down": [bf(H, I, scale=0.02) for _ in range(n_copies)], "lm_head": [bf(V, H, scale=0.02) for _ in range(2)]}
+    bq = bf(Q)
+    pos = torch.arange(Bm, device="cuda", dtype=torch.int64)
+    slots = torch.arange(Bm, device="cuda", dtype=torch.int32)
+    cache = torch.zeros(2, 2, 4, 128, 128, dtype=torch.bfloat16, device="cuda")
+    k = [0]
+
+    def rot(name):
+        k[0] += 1
+        return ws[name][k[0] % len(ws[name])]
+
+    cases = [
+        ("qkv + bias + rope + kv append", Q * H, lambda: F.skinny_qkv_rope_append(x, rot("qkv"), bq, pos, slots, 1e6, 28, 4, 128, cache, True),
+         lambda: torch.nn.functional.linear(x, rot("qkv"), bq)),
+        ("o_proj + residual + rmsnorm", H * H, lambda: F.skinny_linear_residual_rmsnorm(o, rot("o"), res, nw, 1e-6),
+         lambda: torch.nn.functional.linear(o, rot("o"))),
+        ("gate_up + swiglu", 2 * I * H, lambda: F.skinny_gate_up_swiglu(x, rot("gate_up")),
+         lambda: torch.nn.functional.linear(x, rot("gate_up"))),
+        ("down_proj + residual + rmsnorm", H * I, lambda: F.skinny_linear_residual_rmsnorm(act, rot("down"), res, nw, 1e-6),
+         lambda: torch.nn.functional.linear(act, rot("down"))),
+        ("lm_head", V * H, lambda: F.gemm_skinny(x, rot("lm_head")), lambda: torch.nn.functional.linear(x, rot("lm_head"))),
+    ]
+    bw, _, kind = peaks()
+    for name, nel, ours, lib in cases:
+        to = timed(ours, iters)
+        tl = timed(lib, iters)
+        nbytes = 2.0 * nel
+        print(f"decode M={Bm} {name}: ours {to * 1e6:.1f} us = {nbytes / to / 1e9:.0f} GB/s ({nbytes / to / bw:.2f} of {kind} "
+              f"HBM copy) | library GEMM alone {tl * 1e6:.1f} us = {nbytes / tl / 1e9:.0f} GB/s", flush=True)
+
+
 def case_gemm_fp8(iters):
     M, N, K = 8192, 8192, 8192
     a, b = bf(M, K), bf(N, K, scale=0.05)
@@ -277,7 +353,7 @@ def case_flash(iters, B=16, L=4096, library=True):
     assert native.read_status(q.device) == 0
 
 
-CASES = {"quant_mxfp4": case_quant_mxfp4, "fp8_train": case_fp8_train, "reshard_fp8": case_reshard_fp8, "moe": case_moe, "gemm_fp8": case_gemm_fp8, "flash": case_flash, "flash_small": case_flash_small, "gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
+CASES = {"gemm_shapes": case_gemm_shapes, "gemm_pair": case_gemm_pair, "decode_gemms": case_decode_gemms, "quant_mxfp4": case_quant_mxfp4, "fp8_train": case_fp8_train, "reshard_fp8": case_reshard_fp8, "moe": case_moe, "gemm_fp8": case_gemm_fp8, "flash": case_flash, "flash_small": case_flash_small, "gemm": case_gemm, "logprob": case_logprob, "dlogits": case_dlogits, "decode": case_decode,
          "reshard": case_reshard, "quant": case_quant, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu,
          "rope": case_rope, "adamw": case_adamw, "sample": case_sample}
 

@@ -52,6 +52,16 @@ _SIGS = {
                           c_int, c_int, c_void_p, c_int, c_void_p],
     "b200_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
                        c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "b200_gemm_bf16_ex": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
+                          c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "b200_gemm_skinny_splits": [c_int, c_int, c_int, c_int, c_int],
+    "b200_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
+                         c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "b200_splitk_reduce": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p],
+    "b200_splitk_reduce_residual_rmsnorm": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
+                                            c_void_p, c_void_p],
+    "b200_splitk_reduce_qkv_rope_append": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
+                                           c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "b200_lmhead_logprob_partial": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong,
                                     c_longlong, c_float, c_int, c_void_p, c_int, c_void_p],
     "b200_logprob_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],

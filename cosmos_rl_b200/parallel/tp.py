@@ -12,6 +12,11 @@ import torch
 import torch.distributed as dist
 
 
+def _F():
+    from ..ops import functional
+    return functional
+
+
 class _AllReduce(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
@@ -119,7 +124,7 @@ class _GatherGemm(torch.autograd.Function):
         # the plain tensor-parallel plan); dropping them keeps only T / tp rows alive per projection
         ctx.kept = bool(tp.keep_gathered)
         ctx.save_for_backward(xg if ctx.kept else x, w)
-        return torch.nn.functional.linear(xg, w)
+        return _F().mm_nt(xg, w)
 
     @staticmethod
     def backward(ctx, gy):
@@ -131,8 +136,8 @@ class _GatherGemm(torch.autograd.Function):
                 and f.fits(gy.shape[0], w.shape[1], 1)):
             gx = f.gemm_reduce_scatter(gy, w.t().contiguous())
         else:
-            gx = _reduce_scatter_rows(gy @ w, tp.group, tp.size, tp.rank)
-        gw = gy.t() @ (x if ctx.kept else _gather_rows(x, tp.group, tp.size))
+            gx = _reduce_scatter_rows(_F().mm_nn(gy, w), tp.group, tp.size, tp.rank)
+        gw = _F().mm_tn(gy, x if ctx.kept else _gather_rows(x, tp.group, tp.size), out_dtype=w.dtype)
         return gx, gw, None
 
 
@@ -148,7 +153,7 @@ class _GemmScatter(torch.autograd.Function):
         if (f is not None and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[0] % (128 * tp.size) == 0
                 and f.fits(x.shape[0], w.shape[0], 1)):
             return f.gemm_reduce_scatter(x.contiguous(), w)
-        return _reduce_scatter_rows(torch.nn.functional.linear(x, w), tp.group, tp.size, tp.rank)
+        return _reduce_scatter_rows(_F().mm_nt(x, w), tp.group, tp.size, tp.rank)
 
     @staticmethod
     def backward(ctx, gy):
@@ -160,8 +165,8 @@ class _GemmScatter(torch.autograd.Function):
         if ag is not None and gy.is_cuda and gy.dtype == torch.bfloat16 and ag.fits(gy.shape[0] * tp.size, gy.shape[1]):
             gx = ag.gemm(gy, w.t().contiguous())
         else:
-            gx = gy_full @ w
-        return gx, gy_full.t() @ x, None
+            gx = _F().mm_nn(gy_full, w)
+        return gx, _F().mm_tn(gy_full, x, out_dtype=w.dtype), None
 
 
 class TensorParallel:
@@ -254,7 +259,7 @@ class TensorParallel:
         in_range = (labels >= lo) & (labels < lo + v_local)
         local_labels = torch.where(in_range, labels - lo, torch.full_like(labels, -100))
         hidden = self.copy_to_region(hidden)
-        logits = torch.nn.functional.linear(hidden, weight_local).float() / temperature
+        logits = F.linear_tc(hidden, weight_local).float() / temperature
         m_local = logits.max(dim=-1).values.detach()
         m = m_local.clone()
         dist.all_reduce(m, op=dist.ReduceOp.MAX, group=self.group)

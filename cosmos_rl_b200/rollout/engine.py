@@ -192,6 +192,47 @@ class RolloutEngine:
         out, _ = F.rms_norm(h, m.norm, eps, residual=res)
         return out
 
+    def _fused_decode_ok(self, B: int) -> bool:
+        """The decode step can run on the weight-streaming GEMMs with fused reductions: bf16 weights on one GPU, no
+        adapters, no per-head q/k norm, and a batch that fits the skinny kernel."""
+        if not self.cuda or self.tp is not None or B > F._SKINNY_MAX_M or self.args.qk_norm or self.d % 2:
+            return False
+        if os.environ.get("COSMOS_B200_FUSED_DECODE", "1") == "0":
+            return False
+        ok = getattr(self, "_fused_ok", None)
+        if ok is None:
+            ok = True
+            for layer in self.model.layers:
+                for w in (layer.self_attn.qkv_proj.weight, layer.self_attn.o_proj.weight,
+                          layer.mlp.gate_up_proj.weight, layer.mlp.down_proj.weight):
+                    if (w.dtype != torch.bfloat16 or getattr(w, "_fp8", None) is not None
+                            or getattr(w, "_lora", None) is not None or w.shape[0] % 8 or w.shape[1] % 8):
+                        ok = False
+            ok = ok and self.args.dim % 4 == 0 and self.args.dim <= 8192 and self.model.norm.dtype == torch.bfloat16
+            self._fused_ok = ok
+        return ok
+
+    def _layers_decode_fused(self, h, positions, slot_mapping, attn):
+        """One decode step through the blocks with four GEMM launches and three reductions per block: the qkv
+        reduction applies bias and RoPE and appends K/V to the cache, the o_proj / down_proj reductions add the
+        residual and apply the next RMSNorm, the gate/up GEMM multiplies SwiGLU in its epilogue."""
+        m = self.model
+        eps = self.args.norm_eps
+        layers = list(m.layers)
+        x, _ = F.rms_norm(h, layers[0].input_layernorm, eps)
+        res = h
+        for li, layer in enumerate(layers):
+            at = layer.self_attn
+            q = F.skinny_qkv_rope_append(x, at.qkv_proj.weight, at.qkv_proj.bias, positions, slot_mapping, at.theta,
+                                         self.hq, self.hkv, self.d, self.kv[li], self.kv_vt)
+            o = attn(li, q, None, None)
+            x, res = F.skinny_linear_residual_rmsnorm(o.reshape(o.shape[0], -1), at.o_proj.weight, res,
+                                                      layer.post_attention_layernorm, eps)
+            act = F.skinny_gate_up_swiglu(x, layer.mlp.gate_up_proj.weight)
+            nxt = layers[li + 1].input_layernorm if li + 1 < len(layers) else m.norm
+            x, res = F.skinny_linear_residual_rmsnorm(act, layer.mlp.down_proj.weight, res, nxt, eps)
+        return x
+
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()
     def _prefill(self, prompts: List[List[int]], page_lists: List[List[int]]) -> torch.Tensor:
@@ -232,9 +273,10 @@ class RolloutEngine:
                 and self.group_n * (self.hq // self.hkv) <= 128):
             prefix = dict(prefix_pages=self.prefix_pages[:B], group=self.group_n, max_shared=self.max_shared, nsplit=1)
             scratch = self._prefix_scratch(B)
-        out = self._layers(h, cur.long(), slot,
-                           lambda li, q, k, v: F.paged_decode(q, self.kv[li], bt, seq_lens, v_transposed=self.kv_vt,
-                                                              scratch=scratch, **prefix))
+        layers = self._layers_decode_fused if self._fused_decode_ok(B) else self._layers
+        out = layers(h, cur.long(), slot,
+                     lambda li, q, k, v: F.paged_decode(q, self.kv[li], bt, seq_lens, v_transposed=self.kv_vt,
+                                                        scratch=scratch, **prefix))
         logits = self.model.logits(out)
         if self.rep_penalty != 1.0:
             logits = self._penalise(logits.float(), self.seen[:B])
@@ -487,3 +529,4 @@ class RolloutEngine:
 
     def invalidate_graphs(self) -> None:
         self.graphs.clear()
+        self._fused_ok = None       # adapters or quantised weights may have been attached since

@@ -20,8 +20,11 @@ def _model():
     return m
 
 
-@pytest.mark.parametrize("shared_prefix", [False, True])
-def test_engine_logprobs_match_teacher_forcing(shared_prefix):
+@pytest.mark.parametrize("shared_prefix,fused_decode", [(False, True), (True, True), (False, False)])
+def test_engine_logprobs_match_teacher_forcing(shared_prefix, fused_decode, monkeypatch):
+    """``fused_decode``: the decode step runs on the weight-streaming GEMMs whose reductions carry bias, RoPE, the
+    cache append, the residual add and the norms; off: the same step from the separate kernels."""
+    monkeypatch.setenv("COSMOS_B200_FUSED_DECODE", "1" if fused_decode else "0")
     m = _model()
     eng = RolloutEngine(m, max_num_seqs=16, max_model_len=1024, page_size=128, shared_prefix_decode=shared_prefix)
     g = torch.Generator().manual_seed(5)

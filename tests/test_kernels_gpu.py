@@ -622,3 +622,131 @@ def test_fp8_training_linear_on_gpu(M, N, K):
     rel = lambda a, b: ((a.float() - b).norm() / b.norm()).item()
     assert rel(y.detach(), (xr @ wr.t()).detach()) < 0.05
     assert rel(x.grad, xr.grad) < 0.05 and rel(w.grad, wr.grad) < 0.05
+
+
+# ---------------------------------------------------------------------------------------------------------
+# CTA-pair GEMM (cta_group::2), its epilogues, and the decode-sized split-K GEMM with fused reductions
+# ---------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("path", [1, 2])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 256), (300, 1000, 520), (77, 136, 64),
+                                   (1024, 3584, 3584), (2048, 4608, 1024), (129, 128, 4096)])
+def test_gemm_both_kernels(path, M, N, K):
+    torch.manual_seed(20)
+    a, b = _bf16(M, K), _bf16(N, K)
+    c = F.gemm(a, b, path=path)
+    native.read_status(a.device)
+    ref = a.float() @ b.float().t()
+    assert torch.allclose(c.float(), ref, rtol=2e-2, atol=1e-2 * math.sqrt(K)), (c.float() - ref).abs().max()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, True), (True, False)])
+def test_gemm_pair_kernel_operand_layouts(a_mn, b_mn):
+    torch.manual_seed(21)
+    M, N, K = 640, 904, 1100
+    a = _bf16(K, M) if a_mn else _bf16(M, K)
+    b = _bf16(K, N) if b_mn else _bf16(N, K)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = F.gemm(a, b, a_mn=a_mn, b_mn=b_mn, path=2, out_dtype=out_dtype)
+        native.read_status(a.device)
+        ref = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
+        assert torch.allclose(out.float(), ref, rtol=2e-2, atol=1e-2 * math.sqrt(K)), (out.float() - ref).abs().max()
+
+
+def test_gemm_pair_kernel_bias_accumulate_and_swiglu():
+    torch.manual_seed(22)
+    M, N, K = 520, 1280, 768
+    a, b = _bf16(M, K), _bf16(N, K, scale=0.05)
+    bias = _bf16(N)
+    ref = a.float() @ b.float().t()
+    y = F.gemm(a, b, bias=bias, path=2)
+    assert torch.allclose(y.float(), ref + bias.float(), rtol=2e-2, atol=0.1)
+    # accumulate: C += A B^T by TMA reduce-add, fp32 and bf16
+    acc = torch.full((M, N), 2.0, dtype=torch.float32, device=DEV)
+    F.gemm(a, b, out=acc, accumulate=True, path=2)
+    assert torch.allclose(acc, ref + 2.0, rtol=1e-3, atol=2e-2)
+    acc16 = torch.full((M, N), 2.0, dtype=torch.bfloat16, device=DEV)
+    F.gemm(a, b, out=acc16, accumulate=True, path=2)
+    assert torch.allclose(acc16.float(), ref + 2.0, rtol=3e-2, atol=0.15)
+    # SwiGLU epilogue on a fused gate/up weight
+    I = N // 2
+    g, u = ref[:, :I], ref[:, I:]
+    z = F.gemm(a, b, swiglu=True)
+    native.read_status(a.device)
+    assert z.shape == (M, I)
+    assert torch.allclose(z.float(), torch.nn.functional.silu(g) * u, rtol=3e-2, atol=0.05)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 4608, 3584), (100, 3584, 3584), (8, 1024, 18944), (256, 3584, 1024),
+                                   (200, 1000, 520), (128, 152064, 512)])
+def test_gemm_skinny_matches_fp32(M, N, K):
+    torch.manual_seed(23)
+    x, w = _bf16(M, K), _bf16(N, K, scale=0.05)
+    bias = _bf16(N)
+    y = F.gemm_skinny(x, w, bias=bias)
+    native.read_status(x.device)
+    ref = x.float() @ w.float().t() + bias.float()
+    assert torch.allclose(y.float(), ref, rtol=2e-2, atol=2e-2 * math.sqrt(K) * 0.05 + 0.05), (y.float() - ref).abs().max()
+
+
+def test_skinny_fused_reductions():
+    torch.manual_seed(24)
+    M, H, I = 96, 1024, 2816
+    hq, hkv, d, P = 6, 2, 128, 128
+    x = _bf16(M, H)
+    # o_proj / down_proj form: projection + residual + RMSNorm
+    w = _bf16(H, I, scale=0.03)
+    act = _bf16(M, I)
+    res = _bf16(M, H)
+    nw = (1.0 + 0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16)
+    y, res_out = F.skinny_linear_residual_rmsnorm(act, w, res, nw, 1e-6)
+    native.read_status(x.device)
+    r_ref = act.float() @ w.float().t() + res.float()
+    assert torch.allclose(res_out.float(), r_ref, rtol=2e-2, atol=0.1)
+    rr = res_out.float()
+    y_ref = rr * torch.rsqrt(rr.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()
+    assert torch.allclose(y.float(), y_ref, rtol=2e-2, atol=2e-2)
+    # gate/up form: SwiGLU in the GEMM epilogue
+    wgu = _bf16(2 * I, H, scale=0.03)
+    z = F.skinny_gate_up_swiglu(x, wgu)
+    gu = x.float() @ wgu.float().t()
+    assert torch.allclose(z.float(), torch.nn.functional.silu(gu[:, :I]) * gu[:, I:], rtol=3e-2, atol=0.05)
+    # qkv form: bias + RoPE + cache append against the separate kernels
+    wqkv = _bf16((hq + 2 * hkv) * d, H, scale=0.03)
+    bqkv = _bf16((hq + 2 * hkv) * d)
+    pos = torch.randint(0, 4000, (M,), device=DEV, dtype=torch.int64)
+    n_pages = 8
+    slots = torch.randperm(n_pages * P, device=DEV)[:M].to(torch.int32)
+    slots[5] = -1
+    for vt in (False, True):
+        cache = torch.zeros(n_pages, 2, hkv, P, d, dtype=torch.bfloat16, device=DEV)
+        q = F.skinny_qkv_rope_append(x, wqkv, bqkv, pos, slots, 1e6, hq, hkv, d, cache, vt)
+        native.read_status(x.device)
+        qkv_ref = (x.float() @ wqkv.float().t() + bqkv.float()).to(torch.bfloat16)
+        q_ref, k_ref, v_ref = qkv_ref.split([hq * d, hkv * d, hkv * d], dim=-1)
+        q_ref, k_ref = R.apply_rope(q_ref.reshape(M, hq, d).float(), k_ref.reshape(M, hkv, d).float(), pos, 1e6)
+        assert torch.allclose(q.float(), q_ref.float(), rtol=2e-2, atol=3e-2), (q.float() - q_ref.float()).abs().max()
+        cache_ref = torch.zeros_like(cache)
+        R.kv_append(k_ref.to(torch.bfloat16), v_ref.reshape(M, hkv, d), cache_ref, slots, vt)
+        assert torch.allclose(cache.float(), cache_ref.float(), rtol=2e-2, atol=3e-2)
+
+
+def test_linear_product_path_runs_own_gemm():
+    """The projection entry point of the models must reach this library's GEMM for bf16 CUDA tensors, in training
+    (autograd) and inference (wide and decode-sized batches)."""
+    torch.manual_seed(25)
+    w = _bf16(768, 1024, scale=0.05).requires_grad_(True)
+    b = _bf16(768).requires_grad_(True)
+    for M in (64, 512):
+        x = _bf16(M, 1024).requires_grad_(True)
+        before = native.LAUNCHES[0]
+        y = F.linear_maybe_fp8(x, w, b)
+        assert native.LAUNCHES[0] > before
+        y.float().sum().backward()
+        ref = torch.nn.functional.linear(x.detach().float(), w.detach().float(), b.detach().float())
+        assert torch.allclose(y.float(), ref, rtol=2e-2, atol=0.2)
+        with torch.no_grad():
+            before = native.LAUNCHES[0]
+            y2 = F.linear_maybe_fp8(x, w, b)
+            assert native.LAUNCHES[0] > before
+            assert torch.allclose(y2.float(), ref, rtol=2e-2, atol=0.2)
+    native.read_status(w.device)
