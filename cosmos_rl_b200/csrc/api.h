@@ -56,6 +56,8 @@ int b200_splitk_reduce_qkv_rope_append(const float* ws, int splits, int M, int h
                                        float theta, void* q_out, void* cache, int page_size, int v_transposed,
                                        cudaStream_t stream);
 
+int b200_last_tmap_error(void);
+
 // Fused lm_head GEMM + per-token log-prob statistics, never materialising [T, V] logits.
 //   hidden [T, H] bf16, weight [V, H] bf16, labels [T] int64 (label < 0: row ignored)
 //   partial [T, nsplit, 4] fp32 scratch: (max, sumexp, label_logit, sum p_unnorm*logit)

@@ -325,16 +325,22 @@ __device__ __forceinline__ void gemm2_mainloop(const CUtensorMap* tmA, const CUt
 // Row-major [rows, cols] tensor of fp32 / bf16 for the epilogue's TMA stores: box = 32 rows x 128 bytes, 128-byte swizzle.
 inline int make_tmap_out(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, int out_fp32) {
   PFN_encodeTiled enc = get_encode_tiled();
-  if (!enc) return -1;
+  if (!enc) { last_tmap_error() = 1 << 24; return -1; }
   const int eb = out_fp32 ? 4 : 2;
-  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * eb) & 15)) return -2;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * eb) & 15)) {
+    last_tmap_error() = (2 << 24) | 0x10000;
+    return -2;
+  }
   cuuint64_t gdim[2] = {cols, rows};
   cuuint64_t gstr[1] = {ld * (uint64_t)eb};
   cuuint32_t box[2] = {(cuuint32_t)(128 / eb), 32};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(out, out_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                   const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = encode_with_context([&] {
+    return enc(out, out_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+               const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  });
+  if (r != CUDA_SUCCESS) last_tmap_error() = (3 << 24) | 0x10000 | (int)r;
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 

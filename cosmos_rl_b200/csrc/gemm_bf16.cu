@@ -207,6 +207,9 @@ static bool pair_kernel_usable(const void* C, int M, long long ldc, int out_fp32
 //   b_mn = 0: B stored [N, K] (ldb = row stride)      b_mn = 1: B stored [K, N]
 // forward  y = x W^T      : a_mn 0, b_mn 0        dgrad dx = dy W : a_mn 0, b_mn 1 (W stored [N_contract, K_out])
 // wgrad dW = dy^T x       : a_mn 1, b_mn 1 (both stored [tokens, features])
+// (reason << 24) | CUresult of the last tensor-map encode that failed in this process (0: none); see gemm_core.cuh
+extern "C" int b200_last_tmap_error() { return b200::last_tmap_error(); }
+
 extern "C" int b200_gemm_bf16_ex(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                                  long long ldb, long long ldc, int a_mn, int b_mn, int out_fp32, int accumulate,
                                  const void* bias, int bias_bf16, int epilogue, int up_row0, int path,

@@ -32,6 +32,11 @@ struct GemmSmem {
   static constexpr int BAR_BYTES = 256;
   // +1024 so the ring can be aligned to 1024 bytes inside dynamic shared memory
   static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+  // Epilogues that stage their output in shared memory (TMA stores) get EPI_BYTES more, 1024-byte aligned, after
+  // the barriers: launch with TOTAL_WITH_EPI and read the pointer that the custom tile() call receives.
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES + 1024;
+  static constexpr int EPI_BYTES = 4 * 2 * 4096;  // 4 epilogue warps x 2 slabs of 32 rows x 128 bytes
+  static constexpr int TOTAL_WITH_EPI = EPI_OFFSET + EPI_BYTES + 1024;
 };
 
 // One output tile as seen by every role of the pipeline.
@@ -65,7 +70,8 @@ struct GemmTraits {
 };
 
 // An epilogue that declares `static constexpr bool CUSTOM_TILE = true` reads its accumulator itself:
-//   __device__ void tile(const Params&, const TileInfo&, int row, uint32_t taddr /* this warp's lanes, column 0 */);
+//   __device__ void tile(const Params&, const TileInfo&, int row, uint32_t taddr /* this warp's lanes, column 0 */,
+//                        uint8_t* epi_smem /* GemmSmem::EPI_BYTES, when launched with TOTAL_WITH_EPI */);
 template <class E, class = void>
 struct epi_custom_tile : std::false_type {};
 template <class E>
@@ -128,6 +134,7 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
   const int lane = threadIdx.x & 31;
   constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -150,6 +157,7 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // everything above touched only this CTA's own state; global memory comes next
 
   Sched sched;
   sched.init(M, N, K, BN, ep);
@@ -265,7 +273,7 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
       if constexpr (epi_custom_tile<Epi>::value) {
-        epi.tile(ep, t, row, taddr);
+        epi.tile(ep, t, row, taddr, smem + SM::EPI_OFFSET);
       } else {
         epi.tile_begin(ep, t, row);
 #pragma unroll 1
@@ -315,6 +323,25 @@ typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// Diagnostics of the last failed tensor-map encode of this process: (reason << 24) | CUresult, where reason is
+// 1 = no driver entry point, 2 = pointer or stride not 16-byte aligned, 3 = the driver refused the map.
+inline int& last_tmap_error() {
+  static int e = 0;
+  return e;
+}
+
+// The driver refuses to encode a map on a host thread that has no current context yet (CUDA_ERROR_INVALID_CONTEXT;
+// seen on autograd worker threads whose first CUDA call is this one): a runtime call binds the primary context.
+template <class F>
+inline CUresult encode_with_context(F&& call) {
+  CUresult r = call();
+  if (r == CUDA_ERROR_INVALID_CONTEXT || r == CUDA_ERROR_NOT_INITIALIZED) {
+    (void)cudaFree(nullptr);
+    r = call();
+  }
+  return r;
+}
+
 inline PFN_encodeTiled get_encode_tiled() {
   static PFN_encodeTiled fn = nullptr;
   if (!fn) {
@@ -333,15 +360,21 @@ inline PFN_encodeTiled get_encode_tiled() {
 inline int make_tmap_3d(CUtensorMap* out, const void* ptr, uint64_t d2, uint64_t rows, uint64_t cols, uint64_t ld,
                         uint64_t ld2, uint32_t box_rows, uint32_t box_cols, int elem_bytes, uint32_t box_d2 = 1) {
   PFN_encodeTiled enc = get_encode_tiled();
-  if (!enc) return -1;
-  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * elem_bytes) & 15) || ((ld2 * elem_bytes) & 15)) return -2;
+  if (!enc) { last_tmap_error() = 1 << 24; return -1; }
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * elem_bytes) & 15) || ((ld2 * elem_bytes) & 15)) {
+    last_tmap_error() = 2 << 24;
+    return -2;
+  }
   cuuint64_t gdim[3] = {cols, rows, d2};
   cuuint64_t gstr[2] = {ld * (uint64_t)elem_bytes, ld2 * (uint64_t)elem_bytes};
   cuuint32_t box[3] = {box_cols, box_rows, box_d2};
   cuuint32_t estr[3] = {1, 1, 1};
   CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-  CUresult r = enc(out, dt, 3, const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = encode_with_context([&] {
+    return enc(out, dt, 3, const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  });
+  if (r != CUDA_SUCCESS) last_tmap_error() = (3 << 24) | (int)r;
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
@@ -350,15 +383,21 @@ inline int make_tmap_3d(CUtensorMap* out, const void* ptr, uint64_t d2, uint64_t
 inline int make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
                         uint32_t box_rows, uint32_t box_cols, int elem_bytes) {
   PFN_encodeTiled enc = get_encode_tiled();
-  if (!enc) return -1;
-  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * elem_bytes) & 15)) return -2;
+  if (!enc) { last_tmap_error() = 1 << 24; return -1; }
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * elem_bytes) & 15)) {
+    last_tmap_error() = 2 << 24;
+    return -2;
+  }
   cuuint64_t gdim[2] = {cols, rows};
   cuuint64_t gstr[1] = {ld * (uint64_t)elem_bytes};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-  CUresult r = enc(out, dt, 2, const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = encode_with_context([&] {
+    return enc(out, dt, 2, const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  });
+  if (r != CUDA_SUCCESS) last_tmap_error() = (3 << 24) | (int)r;
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 

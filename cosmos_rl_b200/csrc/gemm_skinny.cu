@@ -18,26 +18,30 @@
 
 namespace b200 {
 
-constexpr int SK_BN = 128;
-constexpr int SK_STAGES = 6;
-
-struct SkinnyParams {
-  void* out;         // bf16 [M, ldo]: written when ws is null
-  float* ws;         // fp32 [splits, M, N] partial results (nullable): a b200_splitk_reduce* kernel follows
-  const void* bias;  // [N], nullable (direct output only; the reduce kernels add it otherwise)
-  int bias_bf16;
-  long long ldo;
-  int M, N;          // N = columns of the output (for SwiGLU: the intermediate size)
-  int splits;
-  int up_row0;       // SwiGLU: first "up" row of W
+// Tile widths: 128 columns (6 stages) when the contraction has to be split to occupy the machine, 256 columns (4
+// stages) when the column tiles alone do: a wider tile re-reads the activation rows half as often, and with 128
+// rows per tile that traffic out of L2 is as large as the weight stream itself.
+template <int BN>
+struct SkinnyCfg {
+  static constexpr int STAGES = BN == 256 ? 4 : 6;
 };
 
-template <bool SWIGLU>
+struct SkinnyParams {
+  const CUtensorMap* tm_out;  // bf16 [M, N] (direct output) or fp32 [splits, M, N] (partials), boxes of 32 rows x 128 bytes
+  const void* bias;           // [N], nullable (direct output only; the reduce kernels add it otherwise)
+  int bias_bf16;
+  int to_ws;                  // 1: fp32 partials through the 3-D map; 0: bf16 result through the 2-D map
+  int M, N;                   // N = columns of the output (for SwiGLU: the intermediate size)
+  int splits;
+  int up_row0;                // SwiGLU: first "up" row of W
+};
+
+template <int BN, bool SWIGLU>
 struct SkinnySchedule {
   int num_m, num_n, splits, num_kb, total, up_row0;
   __device__ __forceinline__ void init(int M, int N, int K, int, const SkinnyParams& p) {
     num_m = (M + GEMM_BM - 1) / GEMM_BM;
-    constexpr int OUT_BN = SWIGLU ? SK_BN / 2 : SK_BN;
+    constexpr int OUT_BN = SWIGLU ? BN / 2 : BN;
     num_n = (p.N + OUT_BN - 1) / OUT_BN;
     splits = p.splits;
     num_kb = (K + GEMM_BK - 1) / GEMM_BK;
@@ -57,10 +61,10 @@ struct SkinnySchedule {
     const int kb1 = (int)(((long long)(s + 1) * num_kb) / splits);
     t.a_mn0 = t.m_blk * GEMM_BM;
     if (SWIGLU) {
-      t.b_mn0 = t.n_blk * (SK_BN / 2);
-      t.b_mn1 = up_row0 + t.n_blk * (SK_BN / 2);
+      t.b_mn0 = t.n_blk * (BN / 2);
+      t.b_mn1 = up_row0 + t.n_blk * (BN / 2);
     } else {
-      t.b_mn0 = t.n_blk * SK_BN;
+      t.b_mn0 = t.n_blk * BN;
       t.b_mn1 = 0;
     }
     t.k0 = kb0 * GEMM_BK;
@@ -70,76 +74,135 @@ struct SkinnySchedule {
   }
 };
 
-template <bool SWIGLU>
+// Epilogue: each warp turns its 32 accumulator rows into slabs of 32 rows x 128 bytes (32 fp32 or 64 bf16 columns) in
+// swizzled shared memory and hands them to TMA stores, which clip rows >= M and columns >= N.
+template <int BN, bool SWIGLU>
 struct SkinnyEpilogue {
   using Params = SkinnyParams;
   static constexpr bool CUSTOM_TILE = true;
-  __device__ __forceinline__ void finish(const Params&) {}
-  __device__ __forceinline__ void tile(const Params& p, const TileInfo& t, int row, uint32_t taddr) {
-    const long long r = (long long)t.m_blk * GEMM_BM + row;
-    constexpr int OUT_BN = SWIGLU ? SK_BN / 2 : SK_BN;
+  uint32_t slab_idx = 0;
+  __device__ __forceinline__ void finish(const Params&) {
+    if ((threadIdx.x & 31) == 0) tma_store_wait<0>();
+  }
+  __device__ __forceinline__ void tile(const Params& p, const TileInfo& t, int row, uint32_t taddr, uint8_t* epi_smem) {
+    constexpr int OUT_BN = SWIGLU ? BN / 2 : BN;
+    const int lane = threadIdx.x & 31;
+    const int quad = (threadIdx.x >> 5) & 3;
+    uint8_t* slab0 = epi_smem + quad * 8192;
+    const uint32_t sw = (uint32_t)(lane & 7);
+    const int row0 = t.m_blk * GEMM_BM + quad * 32;
+    const int slab_cols = p.to_ws ? 32 : 64;
 #pragma unroll 1
-    for (int c = 0; c < OUT_BN; c += 32) {
-      uint32_t a[32];
-      float v[32];
-      tmem_ld_32x32b_x32(taddr + c, a);
-      if constexpr (SWIGLU) {
-        uint32_t u[32];
-        tmem_ld_32x32b_x32(taddr + SK_BN / 2 + c, u);
-        tmem_ld_wait();
+    for (int c = 0; c < OUT_BN; c += slab_cols) {
+      uint8_t* slab = slab0 + (slab_idx & 1) * 4096;
+      if (lane == 0) tma_store_wait_read<1>();  // the store issued two slabs ago has finished reading this buffer
+      __syncwarp();
+      uint8_t* my_row = slab + lane * 128;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float g = __uint_as_float(a[j]);
-          v[j] = g / (1.f + __expf(-g)) * __uint_as_float(u[j]);
-        }
-      } else {
-        tmem_ld_wait();
+      for (int h = 0; h < 2; ++h) {
+        if (p.to_ws && h == 1) break;
+        const int cc = c + h * 32;
+        uint32_t a[32];
+        float v[32];
+        tmem_ld_32x32b_x32(taddr + cc, a);
+        if constexpr (SWIGLU) {
+          uint32_t u[32];
+          tmem_ld_32x32b_x32(taddr + BN / 2 + cc, u);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = (t.num_kb > 0) ? __uint_as_float(a[j]) : 0.f;
-      }
-      const int col = t.n_blk * OUT_BN + c;
-      if (r >= p.M || col >= p.N) continue;
-      if (p.ws != nullptr) {
-        float* dst = p.ws + ((long long)t.batch * p.M + r) * p.N + col;
-        if (col + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        } else {
-          for (int j = 0; j < 32 && col + j < p.N; ++j) dst[j] = v[j];
-        }
-      } else {
-        if (p.bias != nullptr) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (col + j < p.N)
-              v[j] += p.bias_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[col + j])
-                                  : reinterpret_cast<const float*>(p.bias)[col + j];
-        }
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + r * p.ldo + col;
-        if (col + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            uint4 o;
-            o.x = pack_bf16x2(v[j], v[j + 1]);
-            o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-            o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-            o.w = pack_bf16x2(v[j + 6], v[j + 7]);
-            *reinterpret_cast<uint4*>(dst + j) = o;
+          for (int j = 0; j < 32; ++j) {
+            const float g = __uint_as_float(a[j]);
+            v[j] = g / (1.f + __expf(-g)) * __uint_as_float(u[j]);
           }
         } else {
-          for (int j = 0; j < 32 && col + j < p.N; ++j) dst[j] = __float2bfloat16(v[j]);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = (t.num_kb > 0) ? __uint_as_float(a[j]) : 0.f;
+        }
+        if (p.to_ws) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(my_row + ((((uint32_t)j) ^ sw) << 4)) =
+                make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+          if (p.bias != nullptr) {
+            const int gc = t.n_blk * OUT_BN + cc;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (gc + j < p.N)
+                v[j] += p.bias_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[gc + j])
+                                    : reinterpret_cast<const float*>(p.bias)[gc + j];
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            o.x = pack_bf16x2(v[8 * j], v[8 * j + 1]);
+            o.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+            o.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+            o.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+            *reinterpret_cast<uint4*>(my_row + ((((uint32_t)(4 * h + j)) ^ sw) << 4)) = o;
+          }
         }
       }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const int gc = t.n_blk * OUT_BN + c;
+        if (gc < p.N && row0 < p.M) {
+          if (p.to_ws) tma_store_3d(p.tm_out, slab, gc, row0, t.batch);
+          else tma_store_2d(p.tm_out, slab, gc, row0);
+        }
+        tma_store_commit();
+      }
+      ++slab_idx;
     }
   }
 };
 
-template <bool SWIGLU>
+template <int BN, bool SWIGLU>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N, int K,
-                   SkinnyParams ep, uint32_t* status) {
-  gemm_mainloop<SK_BN, SK_STAGES, SkinnyEpilogue<SWIGLU>, SkinnySchedule<SWIGLU>,
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const __grid_constant__ CUtensorMap tmO, int M, int N, int K, SkinnyParams ep, uint32_t* status) {
+  ep.tm_out = &tmO;
+  if (threadIdx.x == 0) tma_prefetch_desc(&tmO);
+  gemm_mainloop<BN, SkinnyCfg<BN>::STAGES, SkinnyEpilogue<BN, SWIGLU>, SkinnySchedule<BN, SWIGLU>,
                 GemmTraits<false, false, false, false, 0, false, SWIGLU>>(&tmA, &tmB, M, N, K, ep, status);
+}
+
+// fp32 [splits, M, N] partials: boxes of 32 rows x 32 columns, 128-byte swizzle
+static int make_tmap_ws(CUtensorMap* out, const float* ws, int splits, int M, int N) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  if (!enc) return -1;
+  if ((reinterpret_cast<uintptr_t>(ws) & 15) || (N & 3)) return -2;
+  cuuint64_t gdim[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)splits};
+  cuuint64_t gstr[2] = {(cuuint64_t)N * 4, (cuuint64_t)M * N * 4};
+  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = encode_with_context([&] {
+    return enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(ws), gdim, gstr, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  });
+  if (r != CUDA_SUCCESS) last_tmap_error() = (3 << 24) | 0x20000 | (int)r;
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+// bf16 [M, N] result: boxes of 32 rows x 64 columns, 128-byte swizzle
+static int make_tmap_out16(CUtensorMap* out, const void* ptr, int M, int N, long long ld) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  if (!enc) return -1;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (ld & 7)) return -2;
+  cuuint64_t gdim[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  cuuint64_t gstr[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode_with_context([&] {
+    return enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstr, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  });
+  if (r != CUDA_SUCCESS) last_tmap_error() = (3 << 24) | 0x30000 | (int)r;
+  return r == CUDA_SUCCESS ? 0 : -3;
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -153,10 +216,13 @@ __device__ __forceinline__ float bias_at(const void* bias, int bias_bf16, int i)
 // y[r, :] = sum_s ws[s, r, :] (+ bias); N % 4 == 0
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, int M, int N, const void* bias,
                                      int bias_bf16, __nv_bfloat16* __restrict__ out, long long ldo) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long n4 = (long long)M * (N / 4);
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
     const int r = (int)(i / (N / 4)), c = (int)(i % (N / 4)) * 4;
     float4 acc = *reinterpret_cast<const float4*>(ws + (long long)r * N + c);
+#pragma unroll 4
     for (int s = 1; s < splits; ++s) {
       const float4 v = *reinterpret_cast<const float4*>(ws + ((long long)s * M + r) * N + c);
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
@@ -180,6 +246,8 @@ __global__ void __launch_bounds__(RN_THREADS)
 splitk_reduce_residual_rmsnorm_kernel(const float* __restrict__ ws, int splits, int M, int H,
                                       const __nv_bfloat16* __restrict__ res_in, const __nv_bfloat16* __restrict__ w,
                                       float eps, __nv_bfloat16* __restrict__ res_out, __nv_bfloat16* __restrict__ y) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int n4 = H / 4;
   float4 v[RN_VPT];
@@ -190,6 +258,7 @@ splitk_reduce_residual_rmsnorm_kernel(const float* __restrict__ ws, int splits, 
     v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c4 < n4) {
       float4 acc = *reinterpret_cast<const float4*>(ws + (long long)r * H + c4 * 4);
+#pragma unroll 4
       for (int s = 1; s < splits; ++s) {
         const float4 t = *reinterpret_cast<const float4*>(ws + ((long long)s * M + r) * H + c4 * 4);
         acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
@@ -245,56 +314,80 @@ splitk_reduce_qkv_rope_append_kernel(const float* __restrict__ ws, int splits, i
                                      const int* __restrict__ slot_mapping, float log2_theta,
                                      __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ cache,
                                      int page_size, int v_transposed) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int half = d >> 1;
+  const int q4 = half >> 2;  // groups of four rotation pairs per head
   const int N = (hq + 2 * hkv) * d;
   const int heads = hq + 2 * hkv;
   const float pos = (float)positions[r];
   const int slot = slot_mapping[r];
   const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
   const long long slab = (long long)page_size * d;
-  // one thread per (head, rotation pair)
-  for (int idx = threadIdx.x; idx < heads * half; idx += blockDim.x) {
-    const int h = idx / half, i = idx % half;
-    const int c0 = h * d + i, c1 = c0 + half;
-    float a = 0.f, b = 0.f;
+  // one thread per (head, four rotation pairs): 16-byte loads of the partial sums. When the block size is a multiple
+  // of d / 8 a thread keeps the same pair indices for every head it visits and evaluates their sines once.
+  const bool fixed_i = (blockDim.x % q4) == 0;
+  float sn[4], cs[4];
+  if (fixed_i) {
+    const int i0 = (threadIdx.x % q4) * 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sincosf(pos * exp2f(-(2.0f * (float)(i0 + j) / (float)d) * log2_theta), &sn[j], &cs[j]);
+  }
+  const float* row0 = ws + (long long)r * N;
+  const long long split_stride = (long long)M * N;
+#pragma unroll 2
+  for (int idx = threadIdx.x; idx < heads * q4; idx += blockDim.x) {
+    const int h = idx / q4, i0 = (idx % q4) * 4;
+    const int c0 = h * d + i0, c1 = c0 + half;
+    float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f), b4 = a4;
+#pragma unroll 4
     for (int s = 0; s < splits; ++s) {
-      const float* row = ws + ((long long)s * M + r) * N;
-      a += row[c0];
-      b += row[c1];
+      const float4 x = *reinterpret_cast<const float4*>(row0 + s * split_stride + c0);
+      const float4 y = *reinterpret_cast<const float4*>(row0 + s * split_stride + c1);
+      a4.x += x.x; a4.y += x.y; a4.z += x.z; a4.w += x.w;
+      b4.x += y.x; b4.y += y.y; b4.z += y.z; b4.w += y.w;
     }
+    float a[4] = {a4.x, a4.y, a4.z, a4.w}, b[4] = {b4.x, b4.y, b4.z, b4.w};
     if (bias) {
-      a += bias_at(bias, bias_bf16, c0);
-      b += bias_at(bias, bias_bf16, c1);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        a[j] += bias_at(bias, bias_bf16, c0 + j);
+        b[j] += bias_at(bias, bias_bf16, c1 + j);
+      }
     }
     if (h < hq + hkv) {
-      // the unfused path rounds the projection to bf16 before rotating; do the same
-      a = __bfloat162float(__float2bfloat16(a));
-      b = __bfloat162float(__float2bfloat16(b));
-      const float inv_freq = exp2f(-(2.0f * (float)i / (float)d) * log2_theta);
-      float sn, cs;
-      sincosf(pos * inv_freq, &sn, &cs);
-      const float ra = a * cs - b * sn, rb = b * cs + a * sn;
-      a = ra;
-      b = rb;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        // the unfused path rounds the projection to bf16 before rotating; do the same
+        const float x = __bfloat162float(__float2bfloat16(a[j])), y = __bfloat162float(__float2bfloat16(b[j]));
+        if (!fixed_i) sincosf(pos * exp2f(-(2.0f * (float)(i0 + j) / (float)d) * log2_theta), &sn[j], &cs[j]);
+        a[j] = x * cs[j] - y * sn[j];
+        b[j] = y * cs[j] + x * sn[j];
+      }
     }
-    const __nv_bfloat16 oa = __float2bfloat16(a), ob = __float2bfloat16(b);
+    uint2 oa, ob;
+    oa.x = pack_bf16x2(a[0], a[1]); oa.y = pack_bf16x2(a[2], a[3]);
+    ob.x = pack_bf16x2(b[0], b[1]); ob.y = pack_bf16x2(b[2], b[3]);
     if (h < hq) {
-      q_out[(long long)r * hq * d + c0] = oa;
-      q_out[(long long)r * hq * d + c1] = ob;
+      *reinterpret_cast<uint2*>(q_out + (long long)r * hq * d + c0) = oa;
+      *reinterpret_cast<uint2*>(q_out + (long long)r * hq * d + c1) = ob;
     } else if (slot >= 0) {
       if (h < hq + hkv) {
         __nv_bfloat16* kd = cache + ((long long)(page * 2 + 0) * hkv + (h - hq)) * slab + (long long)off * d;
-        kd[i] = oa;
-        kd[i + half] = ob;
+        *reinterpret_cast<uint2*>(kd + i0) = oa;
+        *reinterpret_cast<uint2*>(kd + i0 + half) = ob;
       } else {
         __nv_bfloat16* vd = cache + ((long long)(page * 2 + 1) * hkv + (h - hq - hkv)) * slab;
         if (v_transposed) {
-          vd[(long long)i * page_size + off] = oa;
-          vd[(long long)(i + half) * page_size + off] = ob;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            vd[(long long)(i0 + j) * page_size + off] = __float2bfloat16(a[j]);
+            vd[(long long)(i0 + j + half) * page_size + off] = __float2bfloat16(b[j]);
+          }
         } else {
-          vd[(long long)off * d + i] = oa;
-          vd[(long long)off * d + i + half] = ob;
+          *reinterpret_cast<uint2*>(vd + (long long)off * d + i0) = oa;
+          *reinterpret_cast<uint2*>(vd + (long long)off * d + i0 + half) = ob;
         }
       }
     }
@@ -303,14 +396,44 @@ splitk_reduce_qkv_rope_append_kernel(const float* __restrict__ ws, int splits, i
 
 }  // namespace b200
 
+// Column tile width for a shape: 256 when that still leaves every SM at least two tiles (the second tile's main
+// loop hides the first one's epilogue), else 128 (with contraction splits where the tiles are too few). Measured on
+// the Qwen2.5-7B decode shapes at 128 rows: lm_head (594 wide tiles) 197 us against 210 us with narrow tiles;
+// gate/up (148 wide tiles = one per SM) 57 us against 55 us.
+static int skinny_bn(int M, int N, int swiglu, int num_sms) {
+  const int num_m = (M + b200::GEMM_BM - 1) / b200::GEMM_BM;
+  const int out_bn = swiglu ? 128 : 256;
+  const int tiles256 = num_m * ((N + out_bn - 1) / out_bn);
+  return tiles256 >= 2 * num_sms ? 256 : 128;
+}
+
+template <int BN, bool SWIGLU>
+static int launch_skinny(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmO, int M, int N, int K,
+                         const b200::SkinnyParams& ep, uint32_t* status, int num_sms, cudaStream_t stream) {
+  using namespace b200;
+  using SM = GemmSmem<BN, SkinnyCfg<BN>::STAGES>;
+  auto kern = gemm_skinny_kernel<BN, SWIGLU>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL_WITH_EPI) != cudaSuccess)
+      return B200_ERR_LAUNCH;
+    attr_set = true;
+  }
+  constexpr int OUT_BN = SWIGLU ? BN / 2 : BN;
+  const int units = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + OUT_BN - 1) / OUT_BN) * ep.splits;
+  const int grid = units < num_sms ? units : num_sms;
+  return launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), SM::TOTAL_WITH_EPI, stream, tmA, tmB, tmO, M, N, K, ep,
+                    status) == cudaSuccess ? 0 : B200_ERR_LAUNCH;
+}
+
 extern "C" {
 
-// How many contraction splits fill the machine for this shape (1 = the GEMM writes its result directly).
+// How many contraction splits fill the machine for this shape (1 = the GEMM can write its result directly).
 int b200_gemm_skinny_splits(int M, int N, int K, int swiglu, int num_sms) {
   using namespace b200;
-  const int out_bn = swiglu ? SK_BN / 2 : SK_BN;
-  const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + out_bn - 1) / out_bn);
   if (swiglu) return 1;
+  const int bn = skinny_bn(M, N, 0, num_sms);
+  const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + bn - 1) / bn);
   const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
   int s = num_sms / (tiles > 0 ? tiles : 1);
   if (s > num_kb / 4) s = num_kb / 4;  // at least four contraction blocks per unit
@@ -330,26 +453,18 @@ int b200_gemm_skinny(const void* x, const void* W, void* out, float* ws, int M, 
   if (splits > 1 && (!ws || swiglu)) return B200_ERR_ARG;
   if (!ws && !out) return B200_ERR_ARG;
   const int n_rows_w = swiglu ? up_row0 + N : N;
-  CUtensorMap tmA, tmB;
+  const int bn = skinny_bn(M, N, swiglu, num_sms);
+  CUtensorMap tmA, tmB, tmO;
   if (make_tmap_2d(&tmA, x, M, K, ldx, GEMM_BM, GEMM_BK, 2)) return B200_ERR_TENSORMAP;
-  if (make_tmap_2d(&tmB, W, n_rows_w, K, ldw, swiglu ? SK_BN / 2 : SK_BN, GEMM_BK, 2)) return B200_ERR_TENSORMAP;
-  using SM = GemmSmem<SK_BN, SK_STAGES>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_skinny_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL) !=
-            cudaSuccess ||
-        cudaFuncSetAttribute(gemm_skinny_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL) !=
-            cudaSuccess)
-      return B200_ERR_LAUNCH;
-    attr_set = true;
+  if (make_tmap_2d(&tmB, W, n_rows_w, K, ldw, swiglu ? bn / 2 : bn, GEMM_BK, 2)) return B200_ERR_TENSORMAP;
+  if (ws ? make_tmap_ws(&tmO, ws, splits, M, N) : make_tmap_out16(&tmO, out, M, N, ldo)) return B200_ERR_TENSORMAP;
+  SkinnyParams ep{nullptr, ws ? nullptr : bias, bias_bf16, ws ? 1 : 0, M, N, splits, up_row0};
+  if (bn == 256) {
+    if (swiglu) return launch_skinny<256, true>(tmA, tmB, tmO, M, N, K, ep, status, num_sms, stream);
+    return launch_skinny<256, false>(tmA, tmB, tmO, M, N, K, ep, status, num_sms, stream);
   }
-  SkinnyParams ep{out, ws, ws ? nullptr : bias, bias_bf16, ldo, M, N, splits, up_row0};
-  const int out_bn = swiglu ? SK_BN / 2 : SK_BN;
-  const int units = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + out_bn - 1) / out_bn) * splits;
-  const int grid = units < num_sms ? units : num_sms;
-  if (swiglu) gemm_skinny_kernel<true><<<grid, GEMM_THREADS, SM::TOTAL, stream>>>(tmA, tmB, M, N, K, ep, status);
-  else gemm_skinny_kernel<false><<<grid, GEMM_THREADS, SM::TOTAL, stream>>>(tmA, tmB, M, N, K, ep, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : B200_ERR_LAUNCH;
+  if (swiglu) return launch_skinny<128, true>(tmA, tmB, tmO, M, N, K, ep, status, num_sms, stream);
+  return launch_skinny<128, false>(tmA, tmB, tmO, M, N, K, ep, status, num_sms, stream);
 }
 
 int b200_splitk_reduce(const float* ws, int splits, int M, int N, const void* bias, int bias_bf16, void* out,
@@ -357,29 +472,27 @@ int b200_splitk_reduce(const float* ws, int splits, int M, int N, const void* bi
   if (M <= 0 || N <= 0 || (N & 3) || (ldo & 3) || splits < 1) return B200_ERR_ARG;
   const long long n4 = (long long)M * (N / 4);
   const int grid = (int)((n4 + 255) / 256 < 2048 ? (n4 + 255) / 256 : 2048);
-  b200::splitk_reduce_kernel<<<grid, 256, 0, stream>>>(ws, splits, M, N, bias, bias_bf16, (__nv_bfloat16*)out, ldo);
-  return cudaGetLastError() == cudaSuccess ? 0 : B200_ERR_LAUNCH;
+  return b200::launch_pdl(b200::splitk_reduce_kernel, dim3(grid), dim3(256), 0, stream, ws, splits, M, N, bias, bias_bf16,
+                          (__nv_bfloat16*)out, ldo) == cudaSuccess ? 0 : B200_ERR_LAUNCH;
 }
 
 int b200_splitk_reduce_residual_rmsnorm(const float* ws, int splits, int M, int H, const void* res_in, const void* w,
                                         float eps, void* res_out, void* y, cudaStream_t stream) {
   using namespace b200;
   if (M <= 0 || H <= 0 || (H & 3) || H > RN_THREADS * RN_VPT * 4 || splits < 1) return B200_ERR_ARG;
-  splitk_reduce_residual_rmsnorm_kernel<<<M, RN_THREADS, 0, stream>>>(
-      ws, splits, M, H, (const __nv_bfloat16*)res_in, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)res_out,
-      (__nv_bfloat16*)y);
-  return cudaGetLastError() == cudaSuccess ? 0 : B200_ERR_LAUNCH;
+  return launch_pdl(splitk_reduce_residual_rmsnorm_kernel, dim3(M), dim3(RN_THREADS), 0, stream, ws, splits, M, H,
+                    (const __nv_bfloat16*)res_in, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)res_out,
+                    (__nv_bfloat16*)y) == cudaSuccess ? 0 : B200_ERR_LAUNCH;
 }
 
 int b200_splitk_reduce_qkv_rope_append(const float* ws, int splits, int M, int hq, int hkv, int d, const void* bias,
                                        int bias_bf16, const long long* positions, const int* slot_mapping,
                                        float theta, void* q_out, void* cache, int page_size, int v_transposed,
                                        cudaStream_t stream) {
-  if (M <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || (d & 1) || splits < 1) return B200_ERR_ARG;
-  b200::splitk_reduce_qkv_rope_append_kernel<<<M, 256, 0, stream>>>(ws, splits, M, hq, hkv, d, bias, bias_bf16, positions,
-                                                                  slot_mapping, log2f(theta), (__nv_bfloat16*)q_out,
-                                                                  (__nv_bfloat16*)cache, page_size, v_transposed);
-  return cudaGetLastError() == cudaSuccess ? 0 : B200_ERR_LAUNCH;
+  if (M <= 0 || hq <= 0 || hkv <= 0 || d <= 0 || (d & 7) || splits < 1) return B200_ERR_ARG;
+  return b200::launch_pdl(b200::splitk_reduce_qkv_rope_append_kernel, dim3(M), dim3(192), 0, stream, ws, splits, M, hq,
+                          hkv, d, bias, bias_bf16, positions, slot_mapping, log2f(theta), (__nv_bfloat16*)q_out,
+                          (__nv_bfloat16*)cache, page_size, v_transposed) == cudaSuccess ? 0 : B200_ERR_LAUNCH;
 }
 
 }  // extern "C"

@@ -76,6 +76,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
   const int G = p.hq / p.hkv;
   const int n_items = p.B * p.hkv * p.nsplit;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < PDT_STAGES; ++s) {
       mbar_init(&kfull[s], 1);
@@ -106,6 +107,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 32;   // S^T: columns [0,16) and [16,32) (even / odd tile); O^T: [32,48)
+  pdl_wait();  // the set-up above is CTA-local; queries, cache pages and lengths are global memory
 
   // item -> (b, h, split) and its token range, identical in every role
   auto item_range = [&](int item, int& b, int& h, int& split, int& t0, int& t1) {
@@ -392,6 +394,8 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const __gri
 // prefix pages [0, prefix_pages[b]) and the suffix splits [max_shared, max_shared + nsplit) out of ns slots.
 __global__ void pdt_merge_kernel(const float* __restrict__ scratch, __nv_bfloat16* __restrict__ out, int nsplit,
                                  const int* __restrict__ prefix_pages, int max_shared, int hq) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long head = blockIdx.x;
   const int c = threadIdx.x;
   const int ns = prefix_pages ? max_shared + nsplit : nsplit;
@@ -699,9 +703,12 @@ int b200_paged_decode_prefix_tc(const void* q, const void* cache, long long num_
               status, prefix_pages, max_shared, ns_total};
   const int items = B * hkv * nsplit;
   const int grid = items < num_sms ? items : num_sms;
-  paged_decode_tc_kernel<<<grid, PDT_THREADS, PDT_SMEM, stream>>>(tm_cache, tm_q, p);
+  if (launch_pdl(paged_decode_tc_kernel, dim3(grid), dim3(PDT_THREADS), PDT_SMEM, stream, tm_cache, tm_q, p) != cudaSuccess)
+    return B200_ERR_LAUNCH;
   if (nsplit > 1 || prefix_pages)
-    pdt_merge_kernel<<<B * hq, PDT_D, 0, stream>>>(scratch, (__nv_bfloat16*)out, nsplit, prefix_pages, max_shared, hq);
+    if (launch_pdl(pdt_merge_kernel, dim3(B * hq), dim3(PDT_D), 0, stream, scratch, (__nv_bfloat16*)out, nsplit, prefix_pages,
+                   max_shared, hq) != cudaSuccess)
+      return B200_ERR_LAUNCH;
   return cudaGetLastError() == cudaSuccess ? 0 : B200_ERR_LAUNCH;
 }
 

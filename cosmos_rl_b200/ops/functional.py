@@ -257,13 +257,17 @@ class _LinearTC(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
         x2 = _c(x).view(-1, x.shape[-1])
-        y = gemm(x2, weight, bias=bias if (bias is not None and x2.shape[0] > 128) else None)
+        # the result is allocated in its final shape: callers rotate / scale it in place, which autograd forbids on
+        # a view returned by a custom function
+        y = torch.empty(*x.shape[:-1], weight.shape[0], dtype=torch.bfloat16, device=x.device)
+        y2 = y.view(-1, weight.shape[0])
+        gemm(x2, weight, out=y2, bias=bias if (bias is not None and x2.shape[0] > 128) else None)
         if bias is not None and x2.shape[0] <= 128:
-            y += bias
+            y2 += bias
         ctx.save_for_backward(x2, weight)
         ctx.has_bias = bias is not None
         ctx.shape = x.shape
-        return y.view(*x.shape[:-1], weight.shape[0])
+        return y
 
     @staticmethod
     def backward(ctx, dy):

@@ -43,6 +43,22 @@ def timed(fn, iters: int) -> float:
     return e0.elapsed_time(e1) / iters / 1e3
 
 
+def timed_graph(fn, iters: int, inner: int = 8) -> float:
+    """Device time per call of ``fn`` when ``inner`` calls are replayed from one CUDA graph (no host launch cost
+    between kernels, which is how the decode step runs them)."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(2):
+            fn()
+    torch.cuda.current_stream().wait_stream(s)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(inner):
+            fn()
+    return timed(g.replay, iters) / inner
+
+
 def report(name: str, seconds: float, nbytes: float = 0.0, flops: float = 0.0) -> None:
     bw, fl, kind = peaks()
     line = f"{name}: {seconds * 1e6:.1f} us"
@@ -134,8 +150,8 @@ def case_decode_gemms(iters):
     ]
     bw, _, kind = peaks()
     for name, nel, ours, lib in cases:
-        to = timed(ours, iters)
-        tl = timed(lib, iters)
+        to = timed_graph(ours, iters)
+        tl = timed_graph(lib, iters)
         nbytes = 2.0 * nel
         print(f"decode M={Bm} {name}: ours {to * 1e6:.1f} us = {nbytes / to / 1e9:.0f} GB/s ({nbytes / to / bw:.2f} of {kind} "
               f"HBM copy) | library GEMM alone {tl * 1e6:.1f} us = {nbytes / tl / 1e9:.0f} GB/s", flush=True)

@@ -162,7 +162,14 @@ def check(rc: int, what: str) -> None:
     if rc != 0:
         names = {-1: "bad argument", -2: "tensor map encode failed", -3: "kernel launch failed",
                  -4: "size beyond the supported maximum", -5: "CUDA runtime error"}
-        raise NativeError(f"{what}: {names.get(rc, rc)}")
+        detail = ""
+        if rc == -2:
+            try:
+                e = lib().b200_last_tmap_error()
+                detail = f" (reason {e >> 24}, site {(e >> 16) & 0xff}, CUresult {e & 0xffff})"
+            except Exception:
+                pass
+        raise NativeError(f"{what}: {names.get(rc, rc)}{detail}")
 
 
 @functools.lru_cache(maxsize=8)

@@ -195,7 +195,7 @@ class RolloutEngine:
     def _fused_decode_ok(self, B: int) -> bool:
         """The decode step can run on the weight-streaming GEMMs with fused reductions: bf16 weights on one GPU, no
         adapters, no per-head q/k norm, and a batch that fits the skinny kernel."""
-        if not self.cuda or self.tp is not None or B > F._SKINNY_MAX_M or self.args.qk_norm or self.d % 2:
+        if not self.cuda or self.tp is not None or B > F._SKINNY_MAX_M or self.args.qk_norm or self.d % 8:
             return False
         if os.environ.get("COSMOS_B200_FUSED_DECODE", "1") == "0":
             return False

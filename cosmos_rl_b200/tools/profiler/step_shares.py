@@ -60,7 +60,7 @@ def main(argv=None) -> None:
         total = sum(v[0] for v in agg.values())
         print(f"== {phase}: {total / 1e3:.1f} ms of kernel time, {sum(v[1] for v in agg.values())} launches")
         for name, (t, n) in sorted(agg.items(), key=lambda kv: -kv[1][0])[:a.top]:
-            print(f"{100 * t / total:5.1f}%  {t / 1e3:9.2f} ms  {n:7d}x  {name[:110]}")
+            print(f"{100 * t / total:5.1f}%  {t / 1e3:9.2f} ms  {n:7d}x  {t / max(n, 1):8.1f} us each  {name[:110]}")
 
 
 if __name__ == "__main__":
