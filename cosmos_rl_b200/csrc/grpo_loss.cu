@@ -55,24 +55,36 @@ grpo_loss_kernel(const float* __restrict__ lp, const float* __restrict__ old_lp,
             per *= w;
             d *= w;
         }
+        // off-policy sequence masking drops the surrogate of a masked sequence, never its KL penalty
+        const float m = mask ? mask[i] : 1.f;
+        per *= m;
+        d *= m;
         float kl = 0.f;
         if (ref_lp != nullptr) {
             const float rd = ref_lp[i] - l;
             const float r = fminf(fmaxf(rd, -20.f), 20.f);
             const float e = expf(r);
             const float raw = e - r - 1.f;
-            kl = fminf(fmaxf(raw, -10.f), 10.f);
-            float dkl = (rd >= -20.f && rd <= 20.f && raw >= -10.f && raw <= 10.f) ? -(e - 1.f) : 0.f;
-            if (p.unbiased_kl) { kl *= ratio; dkl *= ratio; }
+            const float draw = (rd >= -20.f && rd <= 20.f) ? -(e - 1.f) : 0.f;
+            float dkl;
+            if (p.unbiased_kl) {
+                // importance-weighted k3: the weight exp(lp - old) is differentiable and the PRODUCT is clamped
+                const float w = expf(diff);
+                const float prod = w * raw;
+                kl = fminf(fmaxf(prod, -10.f), 10.f);
+                dkl = (prod >= -10.f && prod <= 10.f) ? w * raw + w * draw : 0.f;
+            } else {
+                kl = fminf(fmaxf(raw, -10.f), 10.f);
+                dkl = (raw >= -10.f && raw <= 10.f) ? draw : 0.f;
+            }
             per += p.kl_beta * kl;
             d += p.kl_beta * dkl;
         }
-        const float m = mask ? mask[i] : 1.f;
         per_tok[i] = per;
         dlp[i] = d;
         kl_out[i] = kl;
         s_ratio += ratio;
-        s_kl += kl * m;
+        s_kl += kl;
     }
     __shared__ float red[3][8];
     #pragma unroll

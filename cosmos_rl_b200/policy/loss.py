@@ -40,8 +40,10 @@ class GrpoLossConfig:
         return cls(**{k: getattr(tp, k) for k in cls.__dataclass_fields__ if hasattr(tp, k)})
 
 
-def _per_token_terms_torch(lp, old, A, seq_ids, n_seq, tok_per_seq, cfg, ref_logprob, rollout_logprob):
-    """Op-by-op per-token surrogate + KL (every variant; the oracle of the fused kernel)."""
+def _per_token_terms_torch(lp, old, A, seq_ids, n_seq, tok_per_seq, cfg, ref_logprob, rollout_logprob, mask=None):
+    """Op-by-op per-token surrogate + KL (every variant; the oracle of the fused kernel). ``mask`` (off-policy
+    sequence masking) multiplies the surrogate only: a masked sequence keeps its KL penalty and its place in the
+    denominators (cosmos_rl/policy/trainer/llm_trainer/grpo_trainer.py:253-287)."""
     diff = lp - old
     if cfg.variant == "gspo":
         seq_diff = (_seg_sum(diff, seq_ids, n_seq) / tok_per_seq).clamp(max=10.0)
@@ -70,12 +72,17 @@ def _per_token_terms_torch(lp, old, A, seq_ids, n_seq, tok_per_seq, cfg, ref_log
             w = torch.where(w > cfg.behav_imp_weight_cap, torch.zeros_like(w), w)
         per_tok = per_tok * w
 
+    if mask is not None:
+        per_tok = per_tok * mask
+
     kl = torch.zeros_like(lp)
     if cfg.kl_beta != 0.0 and ref_logprob is not None:
         r = (ref_logprob.float() - lp).clamp(-20.0, 20.0)
-        kl = (torch.exp(r) - r - 1.0).clamp(-10.0, 10.0)
         if cfg.unbiased_kl_estimate:
-            kl = kl * torch.exp(diff.clamp(-20.0, 20.0)).detach()
+            # importance-weighted k3: the weight stays differentiable and the product is clamped
+            kl = (torch.exp(diff) * (torch.exp(r) - r - 1.0)).clamp(-10.0, 10.0)
+        else:
+            kl = (torch.exp(r) - r - 1.0).clamp(-10.0, 10.0)
         per_tok = per_tok + cfg.kl_beta * kl
 
     return per_tok, kl, clip_frac.detach(), ratio.detach().mean()
@@ -147,32 +154,32 @@ def grpo_loss(logprob: torch.Tensor, old_logprob: torch.Tensor, advantages: torc
         clip_frac, ratio_mean = stats[0] / ntok, stats[1] / ntok
     else:
         per_tok, kl, clip_frac, ratio_mean = _per_token_terms_torch(lp, old, A, seq_ids, n_seq, tok_per_seq, cfg,
-                                                                    ref_logprob, rollout_logprob)
+                                                                    ref_logprob, rollout_logprob, mask)
 
-    per_tok = per_tok * mask
+    # the mask is already inside per_tok (surrogate only); every denominator counts all scored tokens
     if cfg.loss_type == "token-mean":
-        denom = total_tokens if total_tokens is not None else mask.sum().clamp_min(1.0)
+        denom = total_tokens if total_tokens is not None else float(max(ntok, 1))
         loss = per_tok.sum() / denom
     elif cfg.loss_type == "token-sum":
         loss = per_tok.sum()
     elif cfg.loss_type == "seq-mean-token-sum":
         loss = _seg_sum(per_tok, seq_ids, n_seq).mean()
     elif cfg.loss_type == "seq-mean-token-mean":
-        div = tok_per_seq if cfg.unbiased_loss_max_tokens is None else \
-            torch.full_like(tok_per_seq, float(cfg.unbiased_loss_max_tokens))
+        cap = cfg.unbiased_loss_max_tokens
+        div = tok_per_seq if (cap is None or cap <= 0) else torch.full_like(tok_per_seq, float(cap))
         loss = (_seg_sum(per_tok, seq_ids, n_seq) / div).mean()
     else:
         raise ValueError(f"unknown loss_type {cfg.loss_type!r}")
 
-    metrics: Dict[str, torch.Tensor] = {"kl": (kl * mask).sum() / mask.sum().clamp_min(1.0),
+    metrics: Dict[str, torch.Tensor] = {"kl": kl.sum() / float(max(ntok, 1)),
                                         "clip_frac": clip_frac, "ratio_mean": ratio_mean}
     if entropy is not None:
-        ent_mean = (entropy.float() * mask).sum() / mask.sum().clamp_min(1.0)
+        ent_mean = entropy.float().sum() / float(max(ntok, 1))
         metrics["entropy"] = ent_mean.detach()
         if cfg.entropy_coeff != 0.0:
             loss = loss - cfg.entropy_coeff * ent_mean
     if cfg.positive_nll_coef and seq_rewards is not None:
-        pos = (seq_rewards > 0)[seq_ids].float() * mask
+        pos = (seq_rewards > 0)[seq_ids].float()
         if pos.sum() > 0:
             loss = loss + cfg.positive_nll_coef * (-(lp * pos).sum() / pos.sum())
     return loss, metrics

@@ -269,6 +269,19 @@ class FlatAdamW:
             self.m8.store(A, m)
             self.v8.store(A, v)
 
+    def zero_moments(self) -> None:
+        """Clear both Adam moments everywhere they live: the fp32 shard, the 8-bit blocks, the rank-local tail."""
+        if self.state_bits == 8:
+            for q8 in (self.m8, self.v8):
+                q8.q.zero_()
+                q8.scale.zero_()
+        else:
+            self.m.zero_()
+            self.v.zero_()
+        if self.tail is not None:
+            self.tail["m"].zero_()
+            self.tail["v"].zero_()
+
     def zero_grad(self) -> None:
         self.flat.zero_grad()
 

@@ -22,7 +22,9 @@ class DPOTrainer(LLMTrainer):
         if parallel_dims.cp > 1 or parallel_dims.pp > 1:
             raise NotImplementedError("the DPO trainer supports dp_shard / dp_replicate / tp; use cp_size = pp_size = 1")
         self.beta = float(config.custom.get("dpo_beta", 0.1))
-        self.reference_state = None
+
+    def needs_reference(self) -> bool:
+        return True
 
     def _encode(self, sample) -> Dict[str, Any]:
         pk = self.data_packer

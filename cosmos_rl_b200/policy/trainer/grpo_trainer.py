@@ -77,7 +77,6 @@ class GRPOTrainer(LLMTrainer):
         self.tp_cfg = config.train.train_policy
         self.loss_cfg = GrpoLossConfig.from_config(self.tp_cfg)
         self.temperature = float(self.tp_cfg.temperature)
-        self.reference_state: Optional[torch.Tensor] = None   # host copy of the reference weights (kl_beta != 0)
         if self.tp_cfg.kl_beta != 0.0:
             self._reference_pending = True
         self.inter_replica = kw.get("inter_replica")  # elastic data parallelism across policy replicas
@@ -285,12 +284,15 @@ class GRPOTrainer(LLMTrainer):
         finally:
             self.flat.data.copy_(cur.to(self.device))
 
+    def needs_reference(self) -> bool:
+        return self.tp_cfg.kl_beta != 0.0
+
     def reference_reset(self) -> None:
         """Make the current weights the new reference (every ``reference_reset_interval`` steps)."""
         self.reference_state = self.flat.data.to("cpu", copy=True)
+        self.reference_step = self.train_step
         if self.tp_cfg.reset_optimizer_with_reference:
-            self.optimizer.m.zero_()
-            self.optimizer.v.zero_()
+            self.optimizer.zero_moments()
 
     # ------------------------------------------------------------------ the step
     def step_training(self, rollouts: Sequence[Rollout], current_step: int, total_steps: int,

@@ -152,6 +152,9 @@ class LLMTrainer(Trainer):
         self.train_step = 0
         self.total_steps = 0
         self.weights_ready = False
+        self.reference_state: Optional[torch.Tensor] = None   # host copy of the frozen anchor policy (KL term, DPO)
+        self.reference_step = 0                               # step at which the anchor was last (re)set
+        self._ref_ship = None
         self.ema = None          # ShardEMA when train.ema_enable (created once the weights are in place)
 
     # ------------------------------------------------------------------
@@ -314,6 +317,16 @@ class LLMTrainer(Trainer):
         state = self.ckpt_manager.load_latest(self.device)
         if state is None:
             return False
+        ref = state["model"].get("reference")
+        if ref is not None:
+            self.reference_state = ref.to("cpu", self.flat.dtype, copy=True)
+            self.reference_step = int(state["model"].get("reference_step", 0))
+        elif self.needs_reference():
+            # a checkpoint written without the reference weights: the anchor is the model the run started from
+            # (cosmos_rl/policy/trainer/llm_trainer/grpo_trainer.py:2041-2051 reloads the HF weights the same way)
+            self.model_load_from_hf()
+            self.reference_state = self.flat.data.to("cpu", copy=True)
+            self.reference_step = 0
         self.flat.data.copy_(state["model"]["flat"].to(self.flat.dtype))
         self.optimizer.load_state_dict(state["optimizer"])
         self._init_ema()
@@ -343,6 +356,10 @@ class LLMTrainer(Trainer):
         model_state = {"flat": self.flat.data, "slots": [s.__dict__ for s in self.flat.slots]}
         if self.ema is not None:
             model_state["ema"] = self.ema.state_dict()
+        if self.reference_state is not None:
+            # the KL / DPO anchor is part of the run's state: a resume must not re-anchor to the resumed policy
+            model_state["reference"] = self.reference_state
+            model_state["reference_step"] = self.reference_step
         self.ckpt_manager.save(step, model_state=model_state,
                                optimizer_state=self.optimizer.state_dict(), scheduler_state={"step": step},
                                extra_info=extra, is_final=is_final)
@@ -392,8 +409,22 @@ class LLMTrainer(Trainer):
         ema = [("ema.shard", self.ema.shard)] if self.ema is not None else []
         if ema and self.ema.tail is not None:
             ema.append(("ema.tail", self.ema.tail))
-        return [("flat.data", self.flat.data), *self.optimizer.state_tensors(), *ema, ("meta", meta)]
+        ref = []
+        if self.needs_reference():
+            # every replica must score against the same anchor: the sender stages its host copy on the device (its
+            # current weights when no step has run yet), the receiver a buffer of the same size
+            src = self.reference_state if self.reference_state is not None else self.flat.data
+            self._ref_ship = src.to(self.device, copy=True) if self.weights_ready else torch.empty_like(self.flat.data)
+            ref = [("reference", self._ref_ship)]
+        return [("flat.data", self.flat.data), *self.optimizer.state_tensors(), *ema, *ref, ("meta", meta)]
+
+    def needs_reference(self) -> bool:
+        """Trainers that score against a frozen copy of the initial policy (KL term, DPO) return True."""
+        return False
 
     def after_state_received(self, meta: torch.Tensor) -> None:
         self.train_step, self.total_steps, self.optimizer.step_count = (int(x) for x in meta.tolist())
+        if getattr(self, "_ref_ship", None) is not None:
+            self.reference_state = self._ref_ship.to("cpu", copy=True)
+        self._ref_ship = None
         self.weights_ready = True

@@ -30,6 +30,21 @@ from ...utils.logging import logger
 from ..trainer.base import TrainerRegistry
 
 
+def agree_force_save(event: threading.Event, world_size: int) -> bool:
+    """MAX-reduce the "a checkpoint was requested by a signal" flag over the ranks of the replica and clear it where it
+    was set. Every rank must call this on every step (whether it runs is decided by configuration, never by the
+    signal itself): ranks see a forwarded signal at different moments, and a rank that reduced alone would pair its
+    flag with the first collective of the others' training step (cosmos_rl/policy/worker/rl_worker.py:598-608
+    gathers the flag on every step for the same reason)."""
+    flag = torch.tensor([1 if event.is_set() else 0])
+    if world_size > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    if int(flag) > 0:
+        event.clear()
+        return True
+    return False
+
+
 class RLPolicyWorker(CommMixin):
     role = Role.POLICY
 
@@ -68,6 +83,9 @@ class RLPolicyWorker(CommMixin):
         self.p2r_send_plan = None
         self.shard_infos_posted = False
         self.force_save = threading.Event()
+        # a forced checkpoint can only come from a handled signal or the exit hook; both are configuration, so every
+        # rank agrees on whether the per-step flag reduction exists
+        self.force_save_possible = bool(config.train.save_ckpt_at_exit or config.train.signal_to_handle)
         self.profiler = None
         if config.profiler.enable_profiler:
             from ...utils.profiler import CosmosProfiler
@@ -262,13 +280,8 @@ class RLPolicyWorker(CommMixin):
             return False
         rollouts = self.dispatch_rollouts(c.items_count)
         do_save = bool(c.do_save)
-        if self.config.train.save_ckpt_at_exit or self.force_save.is_set():
-            flag = torch.tensor([1 if self.force_save.is_set() else 0])
-            if self.world_size > 1:
-                dist.all_reduce(flag, op=dist.ReduceOp.MAX)
-            if int(flag) > 0:
-                do_save = True
-                self.force_save.clear()
+        if self.force_save_possible and agree_force_save(self.force_save, self.world_size):
+            do_save = True
         if self.profiler is not None and c.do_profile:
             self.profiler.start_dynamic(c)
         is_master = self.inter_replica.rank == 0

@@ -328,7 +328,8 @@ class RolloutEngine:
         if g is None:
             # warm up outside capture (lazy initialisations, autotuned library GEMMs), then restore state
             saved = (self.cur_len.clone(), self.last_tok.clone(), self.step_counter.clone(),
-                     self.out_tok.clone(), self.out_lp.clone())
+                     self.out_tok.clone(), self.out_lp.clone(),
+                     self.seen[:B].clone() if (self.rep_penalty != 1.0 and self.seen is not None) else None)
             s = torch.cuda.Stream()
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
@@ -343,6 +344,8 @@ class RolloutEngine:
             self.graph_launches[B] = native.LAUNCHES[0] - before
             self.cur_len.copy_(saved[0]); self.last_tok.copy_(saved[1]); self.step_counter.copy_(saved[2])
             self.out_tok.copy_(saved[3]); self.out_lp.copy_(saved[4])
+            if saved[5] is not None:
+                self.seen[:B].copy_(saved[5])     # the throw-away tokens of the warm-up must not count as "seen"
             self.graphs[B] = g
         g.replay()
         from ..ops import native

@@ -672,3 +672,25 @@ def _combo_worker(rank, world, store, out_dir, axis):
 @pytest.mark.parametrize("axis", ["tp", "cp", "pp"])
 def test_data_parallel_combined_with_model_parallel_axes(tmp_path, axis):
     _spawn(_combo_worker, 4, tmp_path, str(tmp_path), axis)
+
+
+def _force_save_worker(rank, world, store):
+    """Only rank 1 saw the forwarded signal: both ranks must agree to save on this step, and nobody on the next."""
+    import threading
+    from cosmos_rl_b200.policy.worker.rl_worker import agree_force_save
+    _init(rank, world, store)
+    ev = threading.Event()
+    if rank == 1:
+        ev.set()
+    assert agree_force_save(ev, world) is True
+    assert not ev.is_set()
+    # the following collective of the "training step" still pairs up on both ranks
+    t = torch.tensor([float(rank + 1)])
+    dist.all_reduce(t)
+    assert t.item() == 3.0
+    assert agree_force_save(ev, world) is False
+    dist.destroy_process_group()
+
+
+def test_force_save_flag_is_agreed_by_all_ranks_every_step(tmp_path):
+    _spawn(_force_save_worker, 2, tmp_path)

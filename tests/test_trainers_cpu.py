@@ -451,3 +451,94 @@ def test_force_use_hf_and_lora_init_modes(tmp_path):
         tr.model_load_from_hf()
         bs = [p for n, p in tr.model.named_parameters() if n.endswith("lora_B")]
         assert bs and all((p.abs().sum() == 0) == b_zero for p in bs)
+
+
+def test_reference_weights_survive_checkpoint_resume_and_optimizer_reset(tmp_path):
+    """The KL anchor is run state: a resume restores the weights the run started from (not the resumed policy), a
+    new replica receives it with the rest of the state, and a reference reset with 8-bit moments clears them."""
+    from cosmos_rl_b200.colocated import ColocatedGRPO
+
+    def cfg(resume, optm="AdamW"):
+        return Config.from_dict({
+            "mode": "colocated",
+            "policy": {"model_name_or_path": "tiny-qwen2", "model_max_length": 96, "model_gradient_checkpointing": False},
+            "rollout": {"n_generation": 4, "batch_size": 2, "max_response_length": 16, "seed": 3},
+            "train": {"seed": 0, "optm_lr": 1e-2, "optm_warmup_steps": 0, "output_dir": str(tmp_path), "resume": resume,
+                      "optm_name": optm,
+                      "train_policy": {"type": "grpo", "reward_function": ["even_token_fraction"], "mini_batch": 4,
+                                       "kl_beta": 0.05, "reset_optimizer_with_reference": True},
+                      "ckpt": {"enable_checkpoint": True, "save_mode": "sync"}}})
+
+    job = ColocatedGRPO(cfg(False), device=torch.device("cpu"), max_num_seqs=8)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 32000, (10,), generator=g) for _ in range(2)]
+    w_init = job.trainer.flat.data.clone()
+    job.step(prompts)
+    job.step(prompts)
+    tr = job.trainer
+    assert torch.equal(tr.reference_state, w_init) and not torch.equal(tr.flat.data, w_init)
+    tr.save_checkpoint(2, 10)
+    # a state hand-over to a new replica carries the anchor
+    names = dict(tr.state_tensors())
+    assert torch.equal(names["reference"].cpu(), w_init)
+
+    job2 = ColocatedGRPO(cfg(True), device=torch.device("cpu"), max_num_seqs=8)
+    tr2 = job2.trainer
+    assert tr2.train_step == 2 and torch.equal(tr2.flat.data, tr.flat.data)
+    assert torch.equal(tr2.reference_state, w_init)                  # anchored to the original model, not the resumed one
+    # reference log-probs of the resumed run equal those of the uninterrupted one
+    samples = tr._prepare(job.rollout(prompts))
+    b = tr._pack(samples[:4])
+    lp1 = tr._reference_logprobs([b])[0]
+    lp2 = tr2._reference_logprobs([tr2._pack(tr2._prepare(job.rollout(prompts))[:4])])[0]
+    assert lp1.shape == lp2.shape
+    b2 = tr2._pack(samples[:4])
+    assert torch.allclose(tr2._reference_logprobs([b2])[0], lp1, atol=1e-6)
+
+    # reference reset clears the moments in every representation
+    job8 = ColocatedGRPO(cfg(False, "AdamW8bit"), device=torch.device("cpu"), max_num_seqs=8)
+    job8.step(prompts)
+    opt = job8.trainer.optimizer
+    assert opt.m is None and opt.m8.q.abs().sum() > 0
+    job8.trainer.reference_reset()
+    assert opt.m8.q.abs().sum() == 0 and opt.v8.scale.abs().sum() == 0
+    assert torch.equal(job8.trainer.reference_state, job8.trainer.flat.data.cpu())
+
+
+def test_grpo_loss_masking_kl_and_divisor_follow_the_reference_rules():
+    """Off-policy sequence masking drops the surrogate of a masked sequence but keeps its KL penalty and its tokens in
+    the denominator; the unbiased KL estimate differentiates through the importance weight and clamps the product;
+    a non-positive ``unbiased_loss_max_tokens`` means "divide by the sequence length"."""
+    lp = torch.tensor([-1.0, -2.0, -0.5, -1.5], requires_grad=True)
+    old = torch.tensor([-1.0, -2.0, -3.0, -4.0])         # sequence 1 drifted: mean(old - lp) = -2.5 ... use rollout lp
+    roll = torch.tensor([-1.0, -2.0, 1.5, 0.5])          # behaviour - current = +2.0 on sequence 1
+    ref = torch.tensor([-1.2, -1.8, -0.7, -1.0])
+    A = torch.tensor([1.0, 1.0, -1.0, -1.0])
+    seq = torch.tensor([0, 0, 1, 1])
+    cfg = L.GrpoLossConfig(kl_beta=0.5, off_policy_masking_delta=1.0)
+    loss, m = L.grpo_loss(lp, old, A, seq, 2, cfg, ref_logprob=ref, rollout_logprob=roll)
+    r = ref - lp.detach()
+    kl = torch.exp(r) - r - 1.0
+    ratio = torch.exp((lp.detach() - old).clamp(-20, 20))
+    pg = -torch.minimum(ratio * A, ratio.clamp(0.8, 1.2) * A)
+    pg[2:] = 0.0                                          # sequence 1 is masked: surrogate gone ...
+    want = (pg + 0.5 * kl).sum() / 4                      # ... its KL and its two tokens stay
+    assert abs(loss.item() - want.item()) < 1e-5, (loss.item(), want.item())
+    assert abs(m["kl"].item() - kl.mean().item()) < 1e-6
+    # unbiased KL: d/dlp of w * k3 with w = exp(lp - old) differentiable
+    cfg_u = L.GrpoLossConfig(kl_beta=1.0, unbiased_kl_estimate=True, epsilon_low=1e9, epsilon_high=1e9)
+    lp2 = torch.tensor([-1.0, -2.0], requires_grad=True)
+    old2 = torch.tensor([-1.1, -1.9])
+    ref2 = torch.tensor([-1.3, -1.6])
+    loss2, _ = L.grpo_loss(lp2, old2, torch.zeros(2), torch.tensor([0, 0]), 1, cfg_u, ref_logprob=ref2)
+    loss2.backward()
+    w = torch.exp(lp2.detach() - old2)
+    r2 = ref2 - lp2.detach()
+    g = (w * (torch.exp(r2) - r2 - 1.0) + w * (-(torch.exp(r2) - 1.0))) / 2
+    assert torch.allclose(lp2.grad, g, atol=1e-6)
+    # Dr.GRPO divisor: 0 falls back to the sequence length
+    c0 = L.GrpoLossConfig(loss_type="seq-mean-token-mean", unbiased_loss_max_tokens=0)
+    c1 = L.GrpoLossConfig(loss_type="seq-mean-token-mean")
+    l0, _ = L.grpo_loss(lp.detach(), old, A, seq, 2, c0)
+    l1, _ = L.grpo_loss(lp.detach(), old, A, seq, 2, c1)
+    assert math.isfinite(l0.item()) and abs(l0.item() - l1.item()) < 1e-7
