@@ -99,34 +99,113 @@ class ClockSampler:
 
 # ---------------------------------------------------------------------------------------------------
 def run_reference(args):
-    """The reference arm: the unmodified reference from baseline/_ref through its own launcher API."""
-    ref = os.path.join(ROOT, "baseline", "_ref")
+    """The reference arm: the unmodified reference tree under baseline/_ref, driven by baseline/run_reference.py
+    (its vLLM rollout backend, then its GRPO trainer, on this benchmark's shapes; see that file for what is and is not
+    the reference's stock path). Under torchrun every rank runs its own generation engine, the trainer spans all
+    ranks with the reference's FSDP plan. Rank 0 prints ONE JSON line."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     out = {"impl": "reference"}
+
+    def finish(obj):
+        if rank == 0:
+            sys.stdout.write(json.dumps(obj) + "\n")
+            sys.stdout.flush()
+        return 0
+
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+                   "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29512"),
+                   os.path.abspath(__file__)] + sys.argv[1:]
+            return subprocess.call(cmd)
+        out["unavailable"] = f"WORLD_SIZE={world} does not match --gpus {args.gpus}"
+        return finish(out)
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    driver = os.path.join(ROOT, "baseline", "run_reference.py")
     if not os.path.isdir(os.path.join(ref, "cosmos_rl")):
-        out["unavailable"] = "baseline/_ref is absent (the offline pip install --no-deps of the reference source tree was not done on this box)"
-        print(json.dumps(out))
+        out["unavailable"] = ("baseline/_ref is absent (pip install --no-index --no-deps --target baseline/_ref of the "
+                              "reference source tree was not done on this box)")
+        return finish(out)
+    tag = f"{os.environ.get('MASTER_PORT', '0')}_{os.getppid() if world > 1 else os.getpid()}"
+    res_dir = os.path.join("/tmp", f"b200rl_ref_res_{tag}")
+    os.makedirs(res_dir, exist_ok=True)
+    log_dir = os.path.join(ROOT, "gpurun_out") if os.path.isdir(os.path.join(ROOT, "gpurun_out")) else res_dir
+    common = ["--steps", str(args.steps), "--warmup", str(args.warmup), "--prompts-per-gpu", str(args.prompts_per_gpu),
+              "--group", str(args.group), "--prompt-len", str(args.prompt_len), "--max-response", str(args.max_response)]
+    limit = float(os.environ.get("B200RL_REF_TIMEOUT_S", "1500"))
+
+    def run_half(half, env, result_path, log_name):
+        log = os.path.join(log_dir, log_name)
+        with open(log, "w") as lf:
+            try:
+                rc = subprocess.call([sys.executable, driver, "--half", half, "--result", result_path] + common,
+                                     env=env, stdout=lf, stderr=subprocess.STDOUT, timeout=limit)
+            except subprocess.TimeoutExpired:
+                return None, f"{half} half did not finish within {limit:.0f} s"
+        if rc != 0 or not os.path.exists(result_path):
+            tail = ""
+            try:
+                lines = [ln.strip() for ln in open(log, errors="replace").read().splitlines() if ln.strip()]
+                errs = [ln for ln in lines if "Error" in ln or "error" in ln]
+                tail = (errs[-1] if errs else lines[-1])[:300] if lines else ""
+            except Exception:
+                pass
+            return None, f"{half} half of the reference exited with code {rc}: {tail}"
+        return json.load(open(result_path)), None
+
+    # ---- generation half: one engine per GPU, each in its own single-rank world
+    env = dict(os.environ)
+    visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+    dev = visible.split(",")[local_rank] if visible else str(local_rank)
+    env.update({"RANK": "0", "WORLD_SIZE": "1", "LOCAL_RANK": "0", "LOCAL_WORLD_SIZE": "1", "GROUP_RANK": "0",
+                "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(29700 + local_rank), "CUDA_VISIBLE_DEVICES": dev})
+    for k in ("TORCHELASTIC_RUN_ID", "TORCHELASTIC_RESTART_COUNT", "TORCHELASTIC_MAX_RESTARTS", "ROLE_RANK",
+              "ROLE_WORLD_SIZE", "GROUP_WORLD_SIZE", "ROLE_NAME"):
+        env.pop(k, None)
+    r_res, r_err = run_half("rollout", env, os.path.join(res_dir, f"rollout_{rank}.json"), f"ref_rollout_rank{rank}.log")
+    with open(os.path.join(res_dir, f"rollout_{rank}.done"), "w") as f:
+        f.write(r_err or "ok")
+    # every rank finishes its engine (and frees the GPU) before the trainer, which spans all ranks, starts
+    deadline = time.time() + limit
+    while time.time() < deadline and not all(os.path.exists(os.path.join(res_dir, f"rollout_{r}.done"))
+                                             for r in range(world)):
+        time.sleep(1.0)
+    errs = [open(os.path.join(res_dir, f"rollout_{r}.done")).read() for r in range(world)
+            if os.path.exists(os.path.join(res_dir, f"rollout_{r}.done"))]
+    bad = [e for e in errs if e != "ok"]
+    # ---- training half: the launch environment's ranks
+    t_res, t_err = run_half("train", dict(os.environ), os.path.join(res_dir, "train.json"), f"ref_train_rank{rank}.log")
+    if rank != 0:
         return 0
-    sys.path.insert(0, ref)
-    reasons = []
-    try:
-        import cosmos_rl  # noqa: F401
-    except Exception as e:
-        reasons.append(f"import cosmos_rl fails: {type(e).__name__}: {e}")
-    for mod in ("redis", "torchao"):
-        try:
-            __import__(mod)
-        except Exception:
-            reasons.append(f"python module {mod!r} missing")
-    import shutil
-    if shutil.which("redis-server") is None:
-        reasons.append("redis-server binary missing (the controller hard-requires it)")
-    if reasons:
-        out["unavailable"] = ("reference installs with --no-deps but cannot run offline: " + "; ".join(reasons))[:400]
-        print(json.dumps(out))
-        return 0
-    out["unavailable"] = "reference imports, but its launcher path was not wired in this build"
-    print(json.dumps(out))
-    return 0
+    if bad or len(errs) < world or t_err or t_res is None:
+        out["unavailable"] = ("; ".join(bad[:1] + ([t_err] if t_err else [])) or "a rank did not report")[:500]
+        return finish(out)
+    rollout_s = max(json.load(open(os.path.join(res_dir, f"rollout_{r}.json")))["seconds_per_step"] for r in range(world))
+    train_s = t_res["seconds_per_step"]
+    n_seq = args.prompts_per_gpu * args.group * world
+    seq_len = args.prompt_len + args.max_response
+    step_s = rollout_s + train_s
+    value = n_seq * seq_len / step_s
+    out.update({
+        "metric": "GRPO step tokens/s (prompt+response tokens generated and trained per second)", "value": value,
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic prompts (uniform random token ids), random-init weights, even-token-fraction reward",
+        "config": {"model": "qwen2.5-7b-arch", "global_batch": n_seq, "seq_len": seq_len, "prompts": args.prompts_per_gpu * world,
+                   "group": args.group, "prompt_len": args.prompt_len, "max_response": args.max_response,
+                   "parallelism": f"colocated sequence rollout -> train on {world} GPU(s): vLLM tp1 per GPU, policy FSDP dp_shard{world}",
+                   "settings": "the reference's shipped qwen2-5-7b GRPO job file: compile, gradient checkpointing, mini_batch 8"},
+        "path": ("reference vLLMRollout.rollout_generation_single_turn + GRPOTrainer.step_training driven directly, one "
+                 "process per half; its controller / worker glue needs redis-server, which this machine lacks; no weight "
+                 "hand-over between the halves (upper bound of the reference's throughput)"),
+        "breakdown": {"rollout_s": rollout_s, "train_s": train_s},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": n_seq * seq_len * 9,
+                "d2h_bytes_per_step": n_seq * args.max_response * 8,
+                "api": "tokenisation, host-to-device copies and detokenisation happen inside both timed calls"},
+    })
+    return finish(out)
 
 
 # ---------------------------------------------------------------------------------------------------
