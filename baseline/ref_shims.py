@@ -6,10 +6,13 @@ call them (bf16 training of a dense decoder needs none of them). ``install()`` r
 serves empty placeholder modules for exactly those absent top-level packages; any attribute read from a placeholder
 yields an inert class, so ``from diffusers import DiffusionPipeline`` succeeds and nothing else changes. A package
 that IS installed is never shadowed. Calling into a placeholder raises, so a path that really needs the package
-fails loudly instead of computing something else.
+fails loudly instead of computing something else. Two names are real stand-ins because the bf16 dense path calls them:
+``strenum.StrEnum`` (= ``enum.StrEnum``) and ``accelerate.init_on_device`` (a context manager that creates
+parameters on the meta device, restated below).
 """
 from __future__ import annotations
 
+import contextlib
 import enum
 import importlib.abc
 import importlib.machinery
@@ -72,6 +75,39 @@ class _Callable(_Placeholder):
         raise RuntimeError(f"{self.__name__} is a placeholder for a package that is not installed on this machine")
 
 
+@contextlib.contextmanager
+def init_on_device(device, include_buffers: bool = False):
+    """Working stand-in for ``accelerate.init_on_device`` (the one function of that package the reference calls when
+    it builds a model, cosmos_rl/policy/model/base.py:706): inside the context every parameter a module registers
+    is moved to ``device`` (``"meta"`` = no storage), and buffers too when ``include_buffers``."""
+    import torch
+    from torch import nn
+    device = torch.device(device)
+    reg_param, reg_buffer = nn.Module.register_parameter, nn.Module.register_buffer
+
+    def register_parameter(module, name, param):
+        reg_param(module, name, param)
+        if param is not None:
+            cur = module._parameters[name]
+            extra = dict(cur.__dict__)
+            extra["requires_grad"] = param.requires_grad
+            module._parameters[name] = type(cur)(cur.to(device), **extra)
+
+    def register_buffer(module, name, buffer, persistent=True):
+        reg_buffer(module, name, buffer, persistent=persistent)
+        if buffer is not None:
+            module._buffers[name] = module._buffers[name].to(device)
+
+    nn.Module.register_parameter = register_parameter
+    if include_buffers:
+        nn.Module.register_buffer = register_buffer
+    try:
+        yield
+    finally:
+        nn.Module.register_parameter = reg_param
+        nn.Module.register_buffer = reg_buffer
+
+
 class _Finder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
     def __init__(self):
         self.served = set()
@@ -110,6 +146,9 @@ class _Finder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
         m.__path__ = []
         if spec.name == "strenum":
             m.StrEnum = enum.StrEnum
+        if spec.name == "accelerate":
+            m.init_on_device = init_on_device
+            m.init_empty_weights = lambda include_buffers=False: init_on_device("meta", include_buffers)
         return m
 
     def exec_module(self, module):

@@ -62,6 +62,18 @@ def make_model_dir(path: str, cfg: dict) -> str:
                                    pad_token=f"<t{cfg['bos_token_id']}>", bos_token=f"<t{cfg['bos_token_id']}>")
     fast.chat_template = "{% for m in messages %}{{ m['content'] }}{% endfor %}"
     fast.save_pretrained(path)
+    # The reference reads the vocabulary size from the SHAPE of lm_head.weight in the checkpoint's safetensors header
+    # (cosmos_rl/utils/util.py:640-697). A header that declares that one tensor, followed by a sparse (never
+    # written, never read) data section of the declared size, answers it; no weights are loaded from it.
+    import struct
+    nbytes = cfg["vocab_size"] * cfg["hidden_size"] * 2
+    header = json.dumps({"lm_head.weight": {"dtype": "BF16", "shape": [cfg["vocab_size"], cfg["hidden_size"]],
+                                            "data_offsets": [0, nbytes]}}).encode()
+    header += b" " * ((8 - len(header) % 8) % 8)
+    with open(os.path.join(path, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(header)))
+        f.write(header)
+        f.truncate(8 + len(header) + nbytes)
     open(marker, "w").close()
     return path
 
@@ -177,8 +189,12 @@ def run_train(a) -> dict:
             else:
                 t.zero_()
     trainer.model.train()
+    # one policy replica: the controller would send it a BuildMesh command that names only itself, after which the
+    # cross-replica gradient reduction is the identity (cosmos_rl/utils/distributed.py:637-647)
+    from cosmos_rl.dispatcher.command import BuildMeshCommand
     ha = HighAvailabilitylNccl(replica_name="bench-policy-0", global_rank=rank, api_client=None)
-    ha.is_single_peer.set()          # one policy replica: its cross-replica reduction is the identity
+    ha.push_cmd(BuildMeshCommand({"bench-policy-0": 0}))
+    ha.wait_comm_ready(timeout=60)
     n_seq = a.prompts_per_gpu * a.group
     V = QWEN25_7B["vocab_size"]
     times = []
@@ -211,6 +227,7 @@ def run_train(a) -> dict:
         if rank == 0:
             print(f"[reference train] step {it}: {float(dt):.2f} s {({k: v for k, v in rep.items() if 'loss' in k})}",
                   file=sys.stderr, flush=True)
+    ha.shutdown()
     return {"half": "train", "seconds_per_step": sum(times) / len(times), "steps": len(times), "world": world}
 
 
@@ -228,7 +245,12 @@ def main(argv=None) -> int:
     ap.add_argument("--model-dir", default="/tmp/b200rl_ref_model/qwen2.5-7b-arch")
     ap.add_argument("--output-dir", default="/tmp/b200rl_ref_out")
     ap.add_argument("--result", default=None, help="write the result JSON here as well")
+    ap.add_argument("--dump-stacks-after", type=float, default=0.0,
+                    help="seconds after which every thread's Python stack is written to stderr (diagnosis of a stall)")
     a = ap.parse_args(argv)
+    if a.dump_stacks_after > 0:
+        import faulthandler
+        faulthandler.dump_traceback_later(a.dump_stacks_after, repeat=False, file=sys.stderr)
     sys.path.insert(0, HERE)
     sys.path.insert(0, REF)
     import ref_shims
