@@ -36,6 +36,9 @@ def parse_args(argv=None):
     ap.add_argument("--node-ip-list", default=None, help="semicolon separated node addresses (multi-node)")
     ap.add_argument("--rdzv-port", type=int, default=29345)
     ap.add_argument("--cpu", action="store_true", help="run every replica on CPU (gloo); for plumbing tests")
+    ap.add_argument("--share-gpus", action="store_true",
+                    help="let replicas wrap around the node's GPUs when the job asks for more than there are (several "
+                         "replicas then share a GPU; for functional tests on small machines, not for performance)")
     ap.add_argument("--no-controller", action="store_true")
     ap.add_argument("script", nargs="?", default=None)
     ap.add_argument("script_args", nargs=argparse.REMAINDER)
@@ -73,9 +76,10 @@ def replica_counts(config: Config, args, n_gpus: int) -> Tuple[int, int, int]:
     return n_policy, n_rollout, n_ref
 
 
-def place_replicas(n_policy: int, n_rollout: int, n_ref: int, config: Config, n_gpus: int, colocated: bool
-                   ) -> List[Dict]:
-    """Assign GPU ids of this node to replicas, policies first. Colocated replicas share the policy's GPUs."""
+def place_replicas(n_policy: int, n_rollout: int, n_ref: int, config: Config, n_gpus: int, colocated: bool,
+                   share: bool = False) -> List[Dict]:
+    """Assign GPU ids of this node to replicas, policies first. Colocated replicas share the policy's GPUs. With
+    ``share`` the ids wrap around instead of running out (``--share-gpus``)."""
     out, next_gpu = [], 0
     sizes = {"policy": gpus_per_replica(config.policy.parallelism),
              "rollout": gpus_per_replica(config.rollout.parallelism),
@@ -89,7 +93,11 @@ def place_replicas(n_policy: int, n_rollout: int, n_ref: int, config: Config, n_
             else:
                 gpus = list(range(next_gpu, next_gpu + k))
                 next_gpu += k
-                if n_gpus and next_gpu > n_gpus:
+                if share and n_gpus:
+                    if k > n_gpus:
+                        raise ValueError(f"a {role} replica needs {k} GPUs, this node has {n_gpus}")
+                    gpus = [g % n_gpus for g in gpus]
+                elif n_gpus and next_gpu > n_gpus:
                     raise ValueError(f"job needs more than the {n_gpus} GPUs of this node "
                                      f"({role} replica {i} wants GPUs {gpus})")
             if role == "policy":
@@ -138,7 +146,7 @@ def main(argv=None) -> int:
         n_gpus = 0
     n_policy, n_rollout, n_ref = replica_counts(config, args, n_gpus)
     placement = place_replicas(n_policy, n_rollout, n_ref, config, n_gpus,
-                               config.mode in ("colocated", "colocated_separated"))
+                               config.mode in ("colocated", "colocated_separated"), share=args.share_gpus)
     log_dir = None
     if args.log_dir:
         log_dir = os.path.join(args.log_dir, time.strftime("logs_%Y%m%d-%H%M%S"))

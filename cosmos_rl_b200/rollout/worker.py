@@ -136,6 +136,8 @@ class DisaggregatedRolloutControlWorker(CommMixin):
         self._pending_version = c.weight_step if c.weight_step is not None else 0
         self.total_steps = c.total_steps
         self.stats["sync_ms"].append((time.perf_counter() - t0) * 1e3)
+        logger.info("[Rollout] weights of step %s received: transport=%s, %.1f ms, device %s", c.weight_step,
+                    "peer" if peer else "collective", self.stats["sync_ms"][-1], self.device)
         return False
 
     def _peer_pull(self, c, key: str) -> None:
@@ -195,6 +197,7 @@ class DisaggregatedRolloutControlWorker(CommMixin):
         else:
             self.current_weight_version = getattr(self, "_pending_version", 0)
         self.weights_ready = True
+        logger.info("[Rollout] weight version %d committed", self.current_weight_version)
         self.rollout.engine.weight_version = self.current_weight_version
         if c.total_steps is not None:
             self.total_steps = c.total_steps
