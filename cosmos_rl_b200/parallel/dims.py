@@ -143,6 +143,42 @@ class ParallelDims:
             if me in base:
                 self._groups["world"] = g
 
+    def build_ep_groups(self, base_ranks: Optional[List[int]] = None, backend: Optional[str] = None) -> None:
+        """Expert parallelism inside the dp_shard axis (``ep`` divides ``dp_shard``): consecutive blocks of ``ep`` ranks
+        of every dp_shard group exchange tokens (group ``"ep"``); ranks with the same position in different blocks
+        hold the same experts (group ``"ep_replica"``) and sum their expert gradients. With ``ep == dp_shard`` the
+        ``"ep"`` group is the dp_shard group and no replica group exists. Collective like ``build_groups``."""
+        if self.ep <= 1:
+            return
+        if self.dp_shard % self.ep:
+            raise ValueError(f"ep_size {self.ep} must divide dp_shard_size {self.dp_shard}")
+        if self.ep == self.dp_shard:
+            self._groups["ep"] = self._groups.get("dp_shard")
+            self._groups["ep_replica"] = None
+            return
+        base = base_ranks or list(range(self.world_size))
+        me = dist.get_rank()
+        done = set()
+        for r in range(self.world_size):
+            line = tuple(self.ranks_along("dp_shard", r))
+            if line in done:
+                continue
+            done.add(line)
+            blocks = [line[i:i + self.ep] for i in range(0, self.dp_shard, self.ep)]
+            for members in blocks:
+                g = dist.new_group([base[m] for m in members], backend=backend)
+                if me in [base[m] for m in members]:
+                    self._groups["ep"] = g
+            for j in range(self.ep):
+                members = [blk[j] for blk in blocks]
+                g = dist.new_group([base[m] for m in members], backend=backend)
+                if me in [base[m] for m in members]:
+                    self._groups["ep_replica"] = g
+
+    @property
+    def ep_coord(self) -> int:
+        return self.dp_shard_coord % self.ep
+
     def group(self, axis: str) -> Optional[dist.ProcessGroup]:
         return self._groups.get(axis)
 

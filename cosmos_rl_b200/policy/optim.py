@@ -89,7 +89,8 @@ class FlatAdamW:
                  master_dtype: torch.dtype = torch.float32, collective=None,
                  replicate_group: Optional[dist.ProcessGroup] = None,
                  tp_group: Optional[dist.ProcessGroup] = None, tp_replicated: Optional[torch.Tensor] = None,
-                 norm_groups=(), sum_groups=(), state_bits: int = 32):
+                 norm_groups=(), sum_groups=(), state_bits: int = 32,
+                 tail_replica_group: Optional[dist.ProcessGroup] = None):
         """``dp_group`` shards optimizer state (ZeRO-2 style); ``replicate_group`` is the outer data-parallel axis of
         HSDP / DDP (cosmos_rl/policy/model/gpt/parallelize.py:80-113, 426-442): ranks of it hold the same shard and
         average their reduced gradient shard before the update, so the all-reduce moves 1/dp_shard of the gradient."""
@@ -97,6 +98,10 @@ class FlatAdamW:
         # ones every tensor-parallel rank holds (``tp_replicated``: bool mask over the flat buffer) only once;
         # ``norm_groups`` are further groups whose ranks hold disjoint parameters (pipeline stages)
         # ``sum_groups``: ranks that hold partial gradients of the SAME samples (context-parallel chunks): summed
+        # ``tail_replica_group``: ranks of the dp group that hold the SAME rank-local tail (expert replicas when
+        # ep < dp_shard): their tail gradients are summed, and the tail counts once per distinct copy in the norm
+        self.tail_replica_group = tail_replica_group
+        self.n_tail_replicas = dist.get_world_size(tail_replica_group) if tail_replica_group is not None else 1
         self.sum_groups = tuple(g for g in sum_groups if g is not None)
         self.tp_group, self.norm_groups = tp_group, tuple(norm_groups)
         self.tp_replicated = tp_replicated
@@ -218,7 +223,12 @@ class FlatAdamW:
             gt = self.flat.grad[self.t0:self.t1]
             if self.trainable is not None:
                 gt.mul_(self.trainable[self.t0:self.t1].to(gt.dtype))
-            sumsq = sumsq + K.grad_sumsq([gt]) / float(self.world * self.world)
+            if self.tail_replica_group is not None:
+                # an expert's replicas each saw the tokens of their own block of ranks: the sum covers every rank
+                gt32 = gt.to(torch.float32)
+                dist.all_reduce(gt32, group=self.tail_replica_group)
+                gt.copy_(gt32)
+            sumsq = sumsq + K.grad_sumsq([gt]) / float(self.world * self.world * self.n_tail_replicas)
         rep = None
         if self.tp_group is not None and self.tp_replicated is not None:
             rep = K.grad_sumsq([(g.float() * self.tp_replicated[self.lo:self.hi].to(torch.float32))])

@@ -48,9 +48,13 @@ class LLMTrainer(Trainer):
         if ep > 1:
             # experts are spread over the dp_shard ranks (the layout of the reference's Qwen3-MoE plan,
             # cosmos_rl/policy/model/qwen3_moe/parallelize.py:120-190, with ep == dp_shard)
-            if ep != parallel_dims.dp_shard or parallel_dims.cp > 1:
-                raise NotImplementedError("expert parallelism needs ep_size == dp_shard_size and cp_size == 1")
-            build_kw = dict(ep_size=ep, ep_rank=parallel_dims.dp_shard_coord)
+            # with ep < dp_shard the dp_shard axis splits into blocks of ep ranks that exchange tokens; ranks at the
+            # same position of different blocks replicate the experts and sum their gradients
+            if parallel_dims.dp_shard % ep or parallel_dims.cp > 1:
+                raise NotImplementedError("expert parallelism needs ep_size to divide dp_shard_size, and cp_size == 1")
+            if parallel_dims.group("ep") is None and parallel_dims.dp_shard > 1:
+                parallel_dims.build_ep_groups()
+            build_kw = dict(ep_size=ep, ep_rank=parallel_dims.ep_coord)
         if parallel_dims.pp > 1:
             build_kw.update(pp_size=parallel_dims.pp, pp_rank=parallel_dims.pp_coord)
             if config.b200.pp_head_weight or config.b200.pp_embed_weight:
@@ -81,7 +85,7 @@ class LLMTrainer(Trainer):
         self.flat = FlatParams(model, self.param_dtype, self.device, shard_multiple=dp,
                                allocator=kw.get("allocator"), local_filter=is_expert)
         if ep > 1:
-            model.set_ep_group(parallel_dims.group("dp_shard"))
+            model.set_ep_group(parallel_dims.group("ep") or parallel_dims.group("dp_shard"))
         if self.lora_targets:
             from .. import lora
             lora.bind_lora(model)
@@ -106,15 +110,19 @@ class LLMTrainer(Trainer):
                                               and parallel_dims.pp == 1 and parallel_dims.cp == 1)
             model.tp.keep_gathered = bool(config.b200.sp_keep_gathered)
         if parallel_dims.cp > 1:
-            if not hasattr(model, "attach_context_parallel") or tp > 1 or parallel_dims.pp > 1:
-                raise NotImplementedError("cp_size > 1 needs a native model with tp_size == pp_size == 1")
+            # context parallelism composes with tp (the exchange moves this rank's heads between the cp ranks that
+            # share its tp coordinate) and with pp (every stage's attention layers exchange inside the stage)
+            if not hasattr(model, "attach_context_parallel"):
+                raise NotImplementedError("cp_size > 1 needs a native model")
             from ...parallel.context_parallel import ContextParallel
             model.attach_context_parallel(ContextParallel(parallel_dims.group("cp"), parallel_dims.cp,
                                                           parallel_dims.cp_coord, config.b200.cp_mode))
         self.pipeline = None
         if parallel_dims.pp > 1:
-            if not hasattr(getattr(model, "args", None), "pp_size") or tp > 1:
-                raise NotImplementedError("pp_size > 1 needs a native model and tp_size == 1")
+            # stages exchange the full [T, H] hidden states between ranks of equal tp / cp coordinates (tensor
+            # parallelism without sequence sharding keeps them replicated inside a stage)
+            if not hasattr(getattr(model, "args", None), "pp_size"):
+                raise NotImplementedError("pp_size > 1 needs a native model")
             from ...parallel.pipeline import PipelineStage
             self.pipeline = PipelineStage(model, parallel_dims.group("pp"), parallel_dims.pp_coord, parallel_dims.pp,
                                           model.args.dim, self.param_dtype, self.device,
@@ -144,6 +152,7 @@ class LLMTrainer(Trainer):
             norm_groups=[parallel_dims.group("pp")] if parallel_dims.pp > 1 else [],
             sum_groups=[parallel_dims.group("cp")] if parallel_dims.cp > 1 else [],
             dp_group=parallel_dims.group("dp_shard") if dp > 1 else None, collective=kw.get("collective"),
+            tail_replica_group=parallel_dims.group("ep_replica") if ep > 1 else None,
             replicate_group=parallel_dims.group("dp_replicate") if parallel_dims.dp_replicate > 1 else None)
         self.data_packer = data_packer or BaseDataPacker.get_default(mt)()
         self.tokenizer = kw.get("tokenizer")

@@ -626,7 +626,9 @@ def test_trainers_with_pipeline_parallelism(tmp_path):
 
 def _combo_worker(rank, world, store, out_dir, axis):
     """Four ranks: dp_shard 2 combined with tp 2, cp 2 or pp 2 through the SFT trainer. Each data-parallel rank trains
-    on its half of the batch; losses, gradient norm and weights must equal the single-process trainer on all of it."""
+    on its half of the batch; losses, gradient norm and weights must equal the single-process trainer on all of it.
+    ``axis`` of the form "tp+cp" combines two model-parallel axes instead (no data parallelism: every rank sees the
+    whole batch)."""
     from cosmos_rl_b200.config import Config
     from cosmos_rl_b200.models import hf_io
     from cosmos_rl_b200.parallel.dims import ParallelDims
@@ -641,7 +643,9 @@ def _combo_worker(rank, world, store, out_dir, axis):
                       "train_policy": {"type": "sft", "trainer_type": "sft", "mini_batch": 2},
                       "ckpt": {"enable_checkpoint": False}}})
     cpu = torch.device("cpu")
-    c = cfg({axis + "_size": 2, "dp_shard_size": 2})
+    two = axis.split("+")
+    n_dp = 2 if len(two) == 1 else 1
+    c = cfg(dict({a + "_size": 2 for a in two}, dp_shard_size=n_dp))
     dims = ParallelDims.from_config_parallelism(c.policy.parallelism, world, rank, cpu)
     dims.build_groups()
     tr = SFTTrainer(c, dims, device=cpu)
@@ -653,13 +657,14 @@ def _combo_worker(rank, world, store, out_dir, axis):
     tr.optimizer.refresh_master_from_params()
     g = torch.Generator().manual_seed(3)
     batch = [{"input_ids": torch.randint(0, 32000, (n,), generator=g).tolist()} for n in (12, 9, 15, 7, 10, 6, 8, 14)]
-    mine = batch[dims.dp_shard_coord::2]                                   # this data-parallel rank's samples
+    mine = batch[dims.dp_shard_coord::n_dp]                                # this data-parallel rank's samples
     for i in range(2):
         a = tr.step_training(mine, total_steps=10, train_step=i + 1)
         b = ref.step_training(batch, total_steps=10, train_step=i + 1)
         loss = torch.tensor(a["train/loss_avg"])
-        dist.all_reduce(loss, group=dims.group("dp_shard"))                # each dp rank reports its share of the sum
-        assert abs(loss.item() / 2 - b["train/loss_avg"]) < 1e-4, (axis, loss.item() / 2, b["train/loss_avg"])
+        if n_dp > 1:
+            dist.all_reduce(loss, group=dims.group("dp_shard"))            # each dp rank reports its share of the sum
+        assert abs(loss.item() / n_dp - b["train/loss_avg"]) < 1e-4, (axis, loss.item() / n_dp, b["train/loss_avg"])
         assert abs(a["train/grad_norm"] - b["train/grad_norm"]) < 2e-3 * b["train/grad_norm"], (axis, a["train/grad_norm"], b["train/grad_norm"])
     want = hf_io.hf_state_dict(ref.model, hf_cfg)
     probe = GPT(tr.model.args)
@@ -671,6 +676,13 @@ def _combo_worker(rank, world, store, out_dir, axis):
 
 @pytest.mark.parametrize("axis", ["tp", "cp", "pp"])
 def test_data_parallel_combined_with_model_parallel_axes(tmp_path, axis):
+    _spawn(_combo_worker, 4, tmp_path, str(tmp_path), axis)
+
+
+@pytest.mark.parametrize("axis", ["tp+cp", "tp+pp", "cp+pp"])
+def test_two_model_parallel_axes_combined(tmp_path, axis):
+    """tp x cp (context exchange inside a tensor-parallel group's heads), tp x pp and cp x pp on four ranks match the
+    single-process trainer (the reference composes its axes through one mesh: cosmos_rl/utils/parallelism.py:82-578)."""
     _spawn(_combo_worker, 4, tmp_path, str(tmp_path), axis)
 
 
@@ -694,3 +706,59 @@ def _force_save_worker(rank, world, store):
 
 def test_force_save_flag_is_agreed_by_all_ranks_every_step(tmp_path):
     _spawn(_force_save_worker, 2, tmp_path)
+
+
+def _ep_sub_worker(rank, world, store, out_dir):
+    """Four ranks, ``dp_shard_size = 4`` with ``ep_size = 2``: ranks {0, 1} and {2, 3} each hold all experts between
+    them, ranks {0, 2} and {1, 3} hold the same experts. Every rank trains on its quarter of the batch; loss, gradient
+    norm and weights (experts included) must equal the single-process trainer on the whole batch."""
+    from cosmos_rl_b200.config import Config
+    from cosmos_rl_b200.models import hf_io
+    from cosmos_rl_b200.models.base import ModelRegistry
+    from cosmos_rl_b200.parallel.dims import ParallelDims
+    from cosmos_rl_b200.policy.trainer.sft_trainer import SFTTrainer
+    _init(rank, world, store)
+
+    def cfg(par):
+        return Config.from_dict({
+            "policy": {"model_name_or_path": "tiny-qwen3-moe", "model_max_length": 64,
+                       "model_gradient_checkpointing": False,
+                       "parallelism": dict({"tp_size": 1, "dp_shard_size": 1, "ep_size": 1}, **par)},
+            "train": {"seed": 0, "optm_lr": 1e-3, "optm_warmup_steps": 0, "output_dir": out_dir, "optm_grad_norm_clip": 0.5,
+                      "train_policy": {"type": "sft", "trainer_type": "sft", "mini_batch": 2, "aux_loss_coeff": 0.0},
+                      "ckpt": {"enable_checkpoint": False}}})
+    cpu = torch.device("cpu")
+    c = cfg({"dp_shard_size": 4, "ep_size": 2})
+    dims = ParallelDims.from_config_parallelism(c.policy.parallelism, world, rank, cpu)
+    dims.build_groups()
+    tr = SFTTrainer(c, dims, device=cpu)
+    assert tr.model.args.ep_size == 2 and tr.model.args.ep_rank == rank % 2
+    assert dist.get_world_size(dims.group("ep")) == 2 and dist.get_world_size(dims.group("ep_replica")) == 2
+    ref = SFTTrainer(cfg({}), ParallelDims(world_size=1, device=cpu), device=cpu)
+    ref.model_load_from_hf()
+    hf_cfg = ref.model.args.to_hf_config()
+    state = hf_io.hf_state_dict(ref.model, hf_cfg)
+    hf_io.load_hf_state(tr.model, lambda k: state[k], state, hf_cfg, 1, 0)
+    tr.optimizer.refresh_master_from_params()
+    V = ref.model.args.vocab_size
+    g = torch.Generator().manual_seed(3)
+    batch = [{"input_ids": torch.randint(0, V, (n,), generator=g).tolist()} for n in (12, 9, 15, 7, 10, 6, 8, 14)]
+    mine = batch[rank::4]
+    for i in range(2):
+        a = tr.step_training(mine, total_steps=10, train_step=i + 1)
+        b = ref.step_training(batch, total_steps=10, train_step=i + 1)
+        loss = torch.tensor(a["train/loss_avg"])
+        dist.all_reduce(loss, group=dims.group("dp_shard"))
+        assert abs(loss.item() / 4 - b["train/loss_avg"]) < 2e-4, (loss.item() / 4, b["train/loss_avg"])
+        assert abs(a["train/grad_norm"] - b["train/grad_norm"]) < 5e-3 * b["train/grad_norm"], \
+            (a["train/grad_norm"], b["train/grad_norm"])
+    want = hf_io.hf_state_dict(ref.model, hf_cfg)
+    got = hf_io.hf_state_dict(tr.model, hf_cfg)
+    assert len(got) < len(want)                                     # this rank exports only the experts it owns
+    for k, v in got.items():
+        assert torch.allclose(v, want[k], atol=5e-4), (k, (v - want[k]).abs().max())
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_inside_a_larger_dp_shard_group(tmp_path):
+    _spawn(_ep_sub_worker, 4, tmp_path, str(tmp_path))
