@@ -161,9 +161,11 @@ def run_reference(args):
     dev = visible.split(",")[local_rank] if visible else str(local_rank)
     env.update({"RANK": "0", "WORLD_SIZE": "1", "LOCAL_RANK": "0", "LOCAL_WORLD_SIZE": "1", "GROUP_RANK": "0",
                 "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(29700 + local_rank), "CUDA_VISIBLE_DEVICES": dev})
-    for k in ("TORCHELASTIC_RUN_ID", "TORCHELASTIC_RESTART_COUNT", "TORCHELASTIC_MAX_RESTARTS", "ROLE_RANK",
-              "ROLE_WORLD_SIZE", "GROUP_WORLD_SIZE", "ROLE_NAME"):
-        env.pop(k, None)
+    # the engine's process is a world of its own: nothing of the launcher's rendezvous may leak into it (with
+    # TORCHELASTIC_USE_AGENT_STORE set, env:// would look for the launcher's store on the new port and wait forever)
+    for k in list(env):
+        if k.startswith("TORCHELASTIC_") or k in ("ROLE_RANK", "ROLE_WORLD_SIZE", "GROUP_WORLD_SIZE", "ROLE_NAME"):
+            env.pop(k, None)
     r_res, r_err = run_half("rollout", env, os.path.join(res_dir, f"rollout_{rank}.json"), f"ref_rollout_rank{rank}.log")
     with open(os.path.join(res_dir, f"rollout_{rank}.done"), "w") as f:
         f.write(r_err or "ok")

@@ -92,13 +92,19 @@ class CommMixin:
                 for mid, data in msgs:
                     self._last_cmd_id = mid
                     try:
-                        self._cmd_queue.put(cmd.Command.depack(data))
+                        c = cmd.Command.depack(data)
+                        self.on_command_received(c, data)
+                        self._cmd_queue.put(c)
                     except Exception as e:
                         logger.error("[%s] undecodable command: %s", self.role, e)
 
         t = threading.Thread(target=loop, name="fetch_command", daemon=True)
         t.start()
         self._threads.append(t)
+
+    def on_command_received(self, c: "cmd.Command", raw: bytes) -> None:
+        """Called on the command thread (rank 0) for every command, before it is queued for the main loop. Workers
+        override it for commands that must take effect while the main loop is busy (membership changes)."""
 
     def next_command(self, timeout: float = 0.0) -> Optional[cmd.Command]:
         """Rank 0 pops a command; every rank of the replica returns the same one."""

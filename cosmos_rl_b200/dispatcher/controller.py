@@ -210,19 +210,32 @@ class Controller:
                 return [], False
             n = min(n, room // n_gen)
             # never hand out more prompts than the remaining steps can consume
+            pps_now = max(1, gb // n_gen)
+
+            def still_needed() -> int:
+                # prompts the steps that have not started yet still need, beyond those already handed out and waiting
+                # (generated or being generated). Counted from the steps left, not from the start of the job, so a
+                # change of the batch size (a policy replica joined or was reaped) keeps the budget right; groups
+                # dropped by dynamic sampling leave the "waiting" count and are thereby replaced by fresh prompts
+                waiting_ = max(0, pm.samples_on_the_fly - pm.dispatched_in_step) // n_gen
+                return (pm.total_steps - pm.current_step) * pps_now - waiting_
+
             if pm.total_steps:
-                # dropped groups (dynamic sampling found no signal in them) are replaced by fresh prompts
-                budget = pm.total_steps * gb // n_gen - (self.prompts_handed_out - self.stat_invalid)
+                budget = still_needed()
                 if budget <= 0:
                     return [], True
                 n = min(n, budget)
             batch, is_end = self.data_fetcher.get_batched_prompt(n)
             pps = self.prompts_per_step()
             for _, payload in batch:
-                payload.weight_version = pm.start_step + max(0, self.prompts_handed_out - self.stat_invalid) // pps
+                # the step that will consume this prompt is current_step + 1 + (prompts handed out and not yet in
+                # training) // prompts_per_step; it needs the weights of the step before. Counting from the samples
+                # in flight keeps the tags right when the number of policy replicas (and so the batch) changes
+                waiting = max(0, pm.samples_on_the_fly - pm.dispatched_in_step) // n_gen
+                payload.weight_version = pm.current_step + waiting // pps
                 self.prompts_handed_out += 1
-            pm.samples_on_the_fly += len(batch) * n_gen
-            if pm.total_steps and self.prompts_handed_out - self.stat_invalid >= pm.total_steps * gb // n_gen:
+                pm.samples_on_the_fly += n_gen
+            if pm.total_steps and still_needed() <= 0:
                 # nothing more to hand out for now; a group dropped later reopens the budget, so the stream of a
                 # job with dynamic sampling only ends with the training itself
                 is_end = tp.variant != "dapo"

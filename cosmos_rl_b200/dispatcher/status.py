@@ -167,9 +167,19 @@ class PolicyStatusManager(_ManagerBase):
         tp = self.config.train.train_policy
         if tp.type != "grpo":
             return
-        self.total_steps = compute_total_steps(
+        total = compute_total_steps(
             n_samples=self.data_fetcher.n, n_generation=self.n_generation(), epochs=self.data_fetcher.epochs,
             global_batch=self.global_batch, max_num_steps=self.config.train.max_num_steps)
+        consumed = getattr(self, "samples_dispatched_total", 0)
+        if consumed and self.global_batch > 0:
+            # a membership change in the middle of the run: the steps already taken used a different batch, so the
+            # remaining samples decide how many steps of the new size are left
+            all_samples = self.data_fetcher.n * self.data_fetcher.epochs * max(self.n_generation(), 1)
+            total = self.current_step + max(0, all_samples - consumed) // self.global_batch
+            mx = self.config.train.max_num_steps
+            if mx is not None and mx > 0:
+                total = min(total, mx)
+        self.total_steps = total
 
     def training_finished(self) -> bool:
         return self.total_steps > 0 and self.current_step >= self.total_steps and self.all_reduced()
@@ -249,6 +259,13 @@ class PolicyStatusManager(_ManagerBase):
                 self.recompute_total_steps()
                 self.train_reports.pop(replica_name, None)
                 self._maybe_finish_step()
+                # the lost replica may have been the source of a weight hand-over that no rollout replica has
+                # adopted yet: the survivors hold the same weights, so stage it again from one of them
+                rm = self.rollout_manager
+                if rm is not None and self.last_staged_sync_step > rm.max_adopted_version() and rm.live():
+                    logger.info("[Controller] re-staging the weight sync of step %d from a surviving policy replica",
+                                self.last_staged_sync_step)
+                    self.trigger_weight_sync(self.last_staged_sync_step)
 
     # ------------------------------------------------------------------ rollouts in
     def filter_outdated(self, rollouts: List[Rollout]) -> List[Rollout]:
@@ -289,7 +306,11 @@ class PolicyStatusManager(_ManagerBase):
     def try_trigger_data_fetch_and_training(self, rollouts_ended: bool = False) -> bool:
         with self.lock:
             reps = self.mesh_replicas()
-            if not reps or len(self.live()) < self.n_init_replicas or not self.all_ready():
+            # the job starts when all of its initial replicas arrived; once it runs, a smaller membership (a replica
+            # was reaped) keeps training with the survivors
+            if not reps or not self.all_ready():
+                return False
+            if len(self.live()) < self.n_init_replicas and not getattr(self, "_started", False):
                 return False
             if self.total_steps and self.current_step >= self.total_steps:
                 return False
@@ -299,10 +320,12 @@ class PolicyStatusManager(_ManagerBase):
                     self._send_training_complete()
                 return False
             self.current_step += 1
+            self._started = True
             self.step_started_at = time.time()
             batch = [self.rollout_buffer.popleft() for _ in range(need)]
             self._record_rollout_stats(batch)
             self.dispatched_in_step = need
+            self.samples_dispatched_total = getattr(self, "samples_dispatched_total", 0) + need
             for i, r in enumerate(batch):
                 rep = reps[i % len(reps)]
                 self.broker.publish(rollout_stream(rep.name), r.model_dump_json().encode())

@@ -39,6 +39,9 @@ def parse_args(argv=None):
     ap.add_argument("--share-gpus", action="store_true",
                     help="let replicas wrap around the node's GPUs when the job asks for more than there are (several "
                          "replicas then share a GPU; for functional tests on small machines, not for performance)")
+    ap.add_argument("--tolerate-replica-failures", action="store_true",
+                    help="a replica that exits abnormally does not take the job down: the controller reaps it after "
+                         "its heartbeat stops and the remaining replicas carry on (elastic jobs)")
     ap.add_argument("--no-controller", action="store_true")
     ap.add_argument("script", nargs="?", default=None)
     ap.add_argument("script_args", nargs=argparse.REMAINDER)
@@ -216,7 +219,8 @@ def main(argv=None) -> int:
 
     rdzv = args.rdzv_port
     for rep in placement:
-        env = dict(env_base, COSMOS_ROLE=rep["role"].capitalize(), COSMOS_CONTROLLER_HOST=ctrl_hosts)
+        env = dict(env_base, COSMOS_ROLE=rep["role"].capitalize(), COSMOS_CONTROLLER_HOST=ctrl_hosts,
+                   COSMOS_REPLICA_TAG=f"{rep['role']}_{rep['index']}")
         if rep["gpus"] and n_gpus:
             env["CUDA_VISIBLE_DEVICES"] = ",".join(str(g) for g in rep["gpus"])
         elif args.cpu or not n_gpus:
@@ -248,6 +252,7 @@ def main(argv=None) -> int:
 
     # supervise: a failing replica or controller takes the job down; the controller's own SIGTERM is success
     rc = 0
+    lost = set()
     try:
         while True:
             alive = False
@@ -262,6 +267,11 @@ def main(argv=None) -> int:
                         rc = code or 1
                         raise KeyboardInterrupt
                 elif code != 0:
+                    if args.tolerate_replica_failures:
+                        if name not in lost:
+                            lost.add(name)
+                            logger.warning("%s exited with %s; the job continues without it", name, code)
+                        continue
                     logger.error("%s exited with %s", name, code)
                     rc = code
                     raise KeyboardInterrupt

@@ -131,6 +131,13 @@ def main(dataset=None, val_dataset=None, data_packer=None, val_data_packer=None,
          filter_reward_fns=None, val_reward_fns=None, custom_logger_fns=None, hook_fns=None, sampler=None,
          batch_sampler=None, args=None, **kw):
     role = os.environ.get("COSMOS_ROLE", "Controller").lower()
+    try:
+        # SIGUSR2 writes every thread's Python stack to stderr (the replica's log): where is a stuck job waiting?
+        import faulthandler
+        import signal
+        faulthandler.register(signal.SIGUSR2, all_threads=True, chain=False)
+    except Exception:
+        pass
     if dataset is None:
         # no dataset from the entry script: the rows of train_policy.dataset.name, read by the configured columns
         from ..tools.dataset.common import config_dataset

@@ -32,6 +32,7 @@ class InterReplicaComm:
         self.version = 0
         self.lock = threading.Lock()
         self.mesh_ready = threading.Event()
+        self._last_uid: Optional[str] = None
 
     # ------------------------------------------------------------------ membership
     @property
@@ -48,6 +49,9 @@ class InterReplicaComm:
     def rebuild(self, mapping: Dict[str, int], uid: str) -> None:
         """New membership. ``uid`` (the command's uuid) makes the rendezvous key unique per rebuild."""
         with self.lock:
+            if uid is not None and uid == self._last_uid:
+                return                       # the same command reached us twice (membership watcher and main loop)
+            self._last_uid = uid
             self.mesh_ready.clear()
             if self.comm is not None:
                 self.comm.abort()

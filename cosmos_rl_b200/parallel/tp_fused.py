@@ -112,6 +112,37 @@ class FusedTP:
         self._ctrl = self.buf.ptr
         dist.barrier(group=group)
 
+    @classmethod
+    def with_silent_peers(cls, size: int, device: torch.device, max_rows: int, max_cols: int,
+                          wait_s: float = 0.002) -> "FusedTP":
+        """Rank 0 of a ``size``-rank context whose other ranks are plain buffers on the SAME GPU that nothing ever
+        writes: a launch stages its tiles, waits ``wait_s`` for arrivals that never come, records the peer-flag
+        timeout in the status word, frees its tensor memory and returns. Used to exercise the bounded waits on one
+        GPU (no collective, no second process)."""
+        self = cls.__new__(cls)
+        self.group, self.size, self.rank, self.device = None, size, 0, device
+        self.max_tiles = ((max_rows + 127) // 128) * ((max_cols + 127) // 128)
+        self.slot_elems = ((max_rows + 127) // 128) * 128 * max_cols
+        self.flag_bytes = ((2 * self.max_tiles * 4 + 255) // 256) * 256
+        self.nbytes = _HEADER + self.flag_bytes + 2 * size * self.slot_elems * 2
+        self.wait_ns = int(wait_s * 1e9)
+        self.buf = PeerBuffer(self.nbytes, device)
+        self._silent = [PeerBuffer(self.nbytes, device) for _ in range(size - 1)]
+        self.maps = [None] * size
+        bases = [self.buf.ptr] + [b.ptr for b in self._silent]
+        arr = ctypes.c_void_p * 8
+        self._flags = arr(*[b + _HEADER for b in bases] + [None] * (8 - size))
+        self._stage = arr(*[b + _HEADER + self.flag_bytes for b in bases] + [None] * (8 - size))
+        self._ctrl = self.buf.ptr
+        torch.cuda.synchronize(device)
+        return self
+
+    def free_silent(self) -> None:
+        torch.cuda.synchronize(self.device)
+        for b in getattr(self, "_silent", []):
+            b.free()
+        self.buf.free()
+
     def fits(self, rows: int, cols: int, mode: int = 0) -> bool:
         r = rows if mode == 0 else rows // self.size
         return (r * cols <= self.slot_elems and cols % 8 == 0

@@ -138,6 +138,41 @@ class RLPolicyWorker(CommMixin):
         self.inter_replica.rebuild(c.replica_name_to_rank, c.uuid_value)
         return False
 
+    # A membership change must reach the inter-replica communicator even while the main loop sits inside a training
+    # step (a peer replica died: the step's gradient all-reduce fails and waits for the new mesh). Rank 0's command
+    # thread therefore also publishes every BuildMesh command under a key of the controller's KV store, and a
+    # watcher thread on every rank applies it (the reference hands the command to its HA_NCCL thread the same way,
+    # cosmos_rl/policy/worker/rl_worker.py:717-758, cosmos_rl/utils/distributed.py:600-620).
+    def on_command_received(self, c, raw: bytes) -> None:
+        if isinstance(c, cmd.BuildMeshCommand):
+            try:
+                self.broker.kv_set(f"mesh:{self.replica_name}", raw, ttl_s=24 * 3600)
+            except Exception as e:
+                logger.warning("[Policy] could not publish the mesh command: %s", e)
+
+    def start_mesh_watcher(self) -> None:
+        key = f"mesh:{self.replica_name}"
+
+        def loop():
+            seen = None
+            while not self.shutdown_signal.is_set():
+                try:
+                    raw = self.broker.kv_get(key)
+                except Exception:
+                    raw = None
+                if raw and raw != seen:
+                    seen = raw
+                    try:
+                        c = cmd.Command.depack(raw)
+                        self.inter_replica.rebuild(c.replica_name_to_rank, c.uuid_value)
+                    except Exception as e:
+                        logger.warning("[Policy] mesh rebuild from the watcher failed: %s", e)
+                time.sleep(0.3)
+
+        t = threading.Thread(target=loop, name="mesh_watcher", daemon=True)
+        t.start()
+        self._threads.append(t)
+
     def execute_policy_to_policy_broadcast(self, c: cmd.PolicyToPolicyBroadcastCommand) -> bool:
         src = self.inter_replica.mapping.get(c.src_replica_name, 0)
         tensors = self.trainer.state_tensors()
@@ -303,6 +338,7 @@ class RLPolicyWorker(CommMixin):
     def main_loop(self) -> None:
         self.start_command_thread()
         self.start_rollout_thread()
+        self.start_mesh_watcher()
         stop = False
         while not stop and not self.shutdown_signal.is_set():
             c = self.next_command(timeout=0.2)

@@ -124,10 +124,25 @@ class DisaggregatedRolloutControlWorker(CommMixin):
                 and not c.trainable_only:
             from ..utils.debug import WeightSyncCheck
             check = WeightSyncCheck(self.rollout.flat.data, slots=self.rollout.flat.slots)
-        if peer:
-            self._peer_pull(c, key)
-        else:
-            self._collective_recv(c)
+        try:
+            if peer:
+                self._peer_pull(c, key)
+            else:
+                self._collective_recv(c)
+        except (RuntimeError, TimeoutError) as e:
+            # the sending policy replica went away mid-transfer: drop the communicator that spans it and keep the
+            # current weights; the controller stages the hand-over again from a surviving replica
+            logger.warning("[Rollout] weight hand-over of step %s from %s failed (%s); keeping weight version %d",
+                           c.weight_step, c.src_replica_name, str(e).splitlines()[0][:200], self.current_weight_version)
+            pair = f"p2r-{c.src_replica_name}-{c.dst_replica_name}"
+            comm = self.p2r_comms.pop(pair, None)
+            if comm is not None:
+                try:
+                    comm.abort()
+                except Exception:
+                    pass
+            self.recv_plan = None
+            return False
         if check is not None:
             if self.device.type == "cuda":
                 torch.cuda.synchronize()

@@ -751,3 +751,38 @@ def test_linear_product_path_runs_own_gemm():
             assert native.LAUNCHES[0] > before
             assert torch.allclose(y2.float(), ref, rtol=2e-2, atol=0.2)
     native.read_status(w.device)
+
+
+def test_bounded_waits_run_out_report_status_and_release_tensor_memory():
+    """Failure detection on the device, without a fault: a wait on a flag that nothing sets runs into its (short)
+    limit, the kernel records ST_TIMEOUT_PEER_FLAG in the status word, frees what it holds and returns; the host
+    reads the code, and the next tensor-core launch on the same context works (its TMEM allocation would block
+    forever if the timed-out kernel had kept its columns)."""
+    from cosmos_rl_b200.parallel import peer
+    from cosmos_rl_b200.parallel.tp_fused import FusedTP
+    dev = torch.device("cuda", torch.cuda.current_device())
+    native.read_status(dev)
+    # 1. the plain flag-wait kernel
+    buf = peer.PeerBuffer(256, dev)
+    peer.flag_wait(buf.ptr, 1, dev, limit_s=0.002)
+    with pytest.raises(native.NativeError, match="peer flag"):
+        native.read_status(dev)
+    assert native.read_status(dev) == 0                      # reading the code re-arms the status word
+    buf.free()
+    # 2. the fused GEMM + all-reduce kernel (tcgen05 pipeline + side warps waiting for the other rank's arrivals)
+    torch.manual_seed(30)
+    M, N, K = 256, 512, 256
+    a, w = _bf16(M, K), _bf16(N, K, scale=0.05)
+    ctx = FusedTP.with_silent_peers(2, dev, M, N, wait_s=0.002)
+    out = ctx.gemm_all_reduce(a, w)
+    torch.cuda.synchronize()
+    with pytest.raises(native.NativeError, match="peer flag"):
+        native.read_status(dev)
+    ctx.free_silent()
+    del out
+    # 3. the context is intact and no tensor memory leaked: ordinary GEMMs (both kernels) still run and are right
+    ref = a.float() @ w.float().t()
+    for path in (1, 2):
+        c = F.gemm(a, w, path=path)
+        assert torch.allclose(c.float(), ref, rtol=2e-2, atol=0.2)
+    assert native.read_status(dev) == 0
