@@ -39,6 +39,11 @@ def parse_args():
     ap.add_argument("--max-response", type=int, default=1024)
     ap.add_argument("--mb-tokens", type=int, default=8192, help="token budget of one training micro-batch")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--config", type=int, default=2, choices=[2, 5],
+                    help="benchmark configuration: 2 = Qwen2.5-7B-arch GRPO step (the headline); 5 = weight-sync sweep "
+                         "on a separated layout (policy on the first half of the GPUs, rollout TP 1/2/4 on the "
+                         "second half; bf16 pull, fused fp8 pull, and the reference-style fp32 send/recv route). The "
+                         "MoE and long-context configurations are not wired into this script")
     ap.add_argument("--layout", default="auto", choices=["auto", "colocated", "disaggregated"],
                     help="auto: 8 GPUs use the named disaggregated layout (policy FSDP4 + rollout TP2 x 2); 1, 2 and 4 "
                          "GPUs run colocated data-parallel replicas (each GPU generates and trains its own prompts)")
@@ -229,6 +234,11 @@ def main():
             return subprocess.call(cmd)
         raise SystemExit(f"WORLD_SIZE={world} does not match --gpus {args.gpus}")
     torch.cuda.set_device(local_rank)
+    if args.config == 5:
+        if world < 2:
+            raise SystemExit("--config 5 needs at least 2 GPUs (one policy rank, one rollout rank)")
+        from cosmos_rl_b200.rollout.weight_sync_bench import main as sweep
+        return sweep(["--model", args.model, "--iters", str(max(args.steps, 3)), "--warmup", str(args.warmup)])
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))

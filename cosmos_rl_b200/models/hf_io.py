@@ -108,20 +108,56 @@ def load_hf_state(model, read, available, cfg: Dict[str, Any], tp: int = 1, r: i
         raise KeyError(f"parameters missing from checkpoint: {missing[:5]}{'...' if len(missing) > 5 else ''}")
 
 
-def load_hf_weights(model, path: str, parallel_dims=None) -> None:
-    """Fill ``model`` (already on its device, fused layout) from an HF safetensors folder."""
+_ST_DTYPES = {"BF16": torch.bfloat16, "F16": torch.float16, "F32": torch.float32, "F64": torch.float64,
+              "I64": torch.int64, "I32": torch.int32, "U8": torch.uint8, "BOOL": torch.bool}
+
+
+def load_hf_weights(model, path: str, parallel_dims=None, split_group=None) -> None:
+    """Fill ``model`` (already on its device, fused layout) from an HF safetensors folder.
+
+    ``split_group`` (default: the replica's dp_shard group when it has more than one rank): its ranks need the same
+    tensors (same tensor- and pipeline-parallel coordinates), so the checkpoint FILES are divided between them; the
+    owner of a file reads a tensor's bytes and broadcasts them, the others only read the file's header for shape and
+    dtype. An 8-rank replica then reads the checkpoint once instead of eight times
+    (cosmos_rl/utils/multi_rank_weight_loader.py:34-300 splits and broadcasts the same way)."""
     from safetensors import safe_open
     cfg = load_hf_config(path)
     tp = parallel_dims.tp if parallel_dims is not None else 1
     r = parallel_dims.tp_coord if parallel_dims is not None else 0
     index = _index(path)
     handles: Dict[str, Any] = {}
+    if split_group is None and parallel_dims is not None and os.environ.get("COSMOS_B200_SPLIT_LOAD", "1") != "0":
+        split_group = parallel_dims.group("dp_shard")
+    n_split = dist.get_world_size(split_group) if (split_group is not None and dist.is_initialized()) else 1
+    me = dist.get_rank(split_group) if n_split > 1 else 0
+    files = sorted(set(index.values()))
+    owner = {fn: i % n_split for i, fn in enumerate(files)}
+    dev = next(model.parameters()).device
+    # NCCL moves device tensors, gloo host tensors
+    on_dev = n_split > 1 and dev.type == "cuda" and dist.get_backend(split_group) != "gloo"
+    stats = {"read_bytes": 0, "recv_bytes": 0}
+    model._hf_load_stats = stats
+
+    def handle(fn):
+        if fn not in handles:
+            handles[fn] = safe_open(os.path.join(path, fn), framework="pt")
+        return handles[fn]
 
     def read(hf_name: str) -> torch.Tensor:
         fn = index[hf_name]
-        if fn not in handles:
-            handles[fn] = safe_open(os.path.join(path, fn), framework="pt")
-        return handles[fn].get_tensor(hf_name)
+        if n_split == 1:
+            return handle(fn).get_tensor(hf_name)
+        src = owner[fn]
+        if src == me:
+            t = handle(fn).get_tensor(hf_name)
+            stats["read_bytes"] += t.numel() * t.element_size()
+            t = t.to(dev) if on_dev else t.contiguous()
+        else:
+            sl = handle(fn).get_slice(hf_name)                    # header only: no tensor bytes are read here
+            t = torch.empty(sl.get_shape(), dtype=_ST_DTYPES[sl.get_dtype()], device=dev if on_dev else "cpu")
+            stats["recv_bytes"] += t.numel() * t.element_size()
+        dist.broadcast(t, dist.get_global_rank(split_group, src), group=split_group)
+        return t
 
     load_hf_state(model, read, index, cfg, tp, r)
 

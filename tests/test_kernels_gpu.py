@@ -786,3 +786,29 @@ def test_bounded_waits_run_out_report_status_and_release_tensor_memory():
         c = F.gemm(a, w, path=path)
         assert torch.allclose(c.float(), ref, rtol=2e-2, atol=0.2)
     assert native.read_status(dev) == 0
+
+
+def test_activation_offload_prefetches_and_keeps_gradients():
+    """Saved activations go to pinned host memory in forward; in backward the copies of the tensors needed next are
+    already enqueued when they are asked for (no host-side wait), and the gradients equal the resident run."""
+    from torch import nn
+    from cosmos_rl_b200.utils.activation_offloading import OffloadActivations
+    torch.manual_seed(31)
+    net = nn.Sequential(*[m for _ in range(6) for m in (nn.Linear(512, 512), nn.GELU())]).cuda()
+    x = torch.randn(2048, 512, device=DEV, requires_grad=True)
+    net(x).pow(2).sum().backward()
+    ref = [p.grad.clone() for p in net.parameters()]
+    gx = x.grad.clone()
+    net.zero_grad()
+    x.grad = None
+    ctx = OffloadActivations(min_bytes=1 << 16, params={p.untyped_storage().data_ptr() for p in net.parameters()})
+    with ctx:
+        y = net(x).pow(2).sum()
+    assert ctx.bytes_offloaded > 0 and len(ctx.stash) >= 6
+    y.backward()
+    torch.cuda.synchronize()
+    assert ctx.n_prefetched >= len(ref) // 2 - 2, ctx.n_prefetched          # most fetches were issued ahead of their use
+    assert not ctx.stash and not ctx.inflight
+    for a, p in zip(ref, net.parameters()):
+        assert torch.allclose(a, p.grad, rtol=1e-4, atol=1e-4)
+    assert torch.allclose(gx, x.grad, rtol=1e-4, atol=1e-4)

@@ -762,3 +762,37 @@ def _ep_sub_worker(rank, world, store, out_dir):
 
 def test_expert_parallel_inside_a_larger_dp_shard_group(tmp_path):
     _spawn(_ep_sub_worker, 4, tmp_path, str(tmp_path))
+
+
+def _split_load_worker(rank, world, store, ckpt):
+    """Two data-parallel ranks load one multi-file checkpoint: each reads the tensor bytes of its own files only and
+    receives the rest by broadcast; both end up with the full, identical model."""
+    from cosmos_rl_b200.models import hf_io
+    from cosmos_rl_b200.parallel.dims import ParallelDims
+    _init(rank, world, store)
+    dims = ParallelDims(dp_shard=2, world_size=2, global_rank=rank, device=torch.device("cpu"))
+    dims.build_groups()
+    m = GPT(_tiny())
+    hf_io.load_hf_weights(m, ckpt, dims)
+    st = m._hf_load_stats
+    assert st["read_bytes"] > 0 and st["recv_bytes"] > 0
+    total = torch.tensor([float(st["read_bytes"])])
+    dist.all_reduce(total)
+    n_bytes = sum(p.numel() * 4 for p in m.parameters())          # the checkpoint is fp32: every byte read once
+    assert abs(total.item() - n_bytes) < 1e-6 * n_bytes, (total.item(), n_bytes)
+    ref = GPT(_tiny())
+    ref.init_weights(5)
+    for (n, p), (_, q) in zip(m.named_parameters(), ref.named_parameters()):
+        assert torch.equal(p, q), n
+    dist.destroy_process_group()
+
+
+def test_checkpoint_files_are_split_between_data_parallel_ranks(tmp_path, monkeypatch):
+    from cosmos_rl_b200.models import hf_io
+    m = GPT(_tiny())
+    m.init_weights(5)
+    monkeypatch.setattr(hf_io, "MAX_SHARD_BYTES", 64 * 1024)       # several files
+    out = str(tmp_path / "ckpt")
+    hf_io.export_safetensors(m, m.args.to_hf_config(), out)
+    assert len([f for f in os.listdir(out) if f.endswith(".safetensors")]) >= 3
+    _spawn(_split_load_worker, 2, tmp_path, out)
