@@ -12,11 +12,12 @@ waited on forever (``CommTimeout``), which is what the controller's NCCL-error c
 from __future__ import annotations
 
 import base64
+import contextlib
 import json
 import threading
 import time
 from datetime import timedelta
-from typing import Callable, Dict, List, Optional, Sequence
+from typing import Callable, Dict, Iterable, List, Optional, Sequence, Union
 
 import torch
 import torch.distributed as dist
@@ -48,6 +49,115 @@ def _notify(name: str, phase: str, **info) -> None:
             pass
 
 
+# ---------------------------------------------------------------------------------------------------
+# watchdog contexts: a deadline over a *block* of operations, and over the device work they enqueue
+# ---------------------------------------------------------------------------------------------------
+class _WatchContext:
+    __slots__ = ("comms", "abort", "deadline")
+
+    def __init__(self, deadline: float):
+        self.comms: "set[DynComm]" = set()
+        self.abort = False
+        self.deadline = deadline
+
+
+_tls = threading.local()
+
+
+def _watch_stack() -> List[_WatchContext]:
+    st = getattr(_tls, "stack", None)
+    if st is None:
+        st = _tls.stack = []
+    return st
+
+
+def _stream_probe(stream) -> Callable[[], bool]:
+    """A callable that says whether everything enqueued on ``stream`` so far has finished. ``stream`` may be a
+    CUDA stream, ``None`` (the current stream when CUDA is up, else "always finished"), or already a callable
+    (host-side tests hand in a probe of their own)."""
+    if callable(stream) and not hasattr(stream, "record_event"):
+        return stream
+    if not torch.cuda.is_available():
+        return lambda: True
+    ev = torch.cuda.Event()
+    ev.record(stream if stream is not None else torch.cuda.current_stream())
+    return ev.query
+
+
+@contextlib.contextmanager
+def watchdog(timeout_s: Optional[float] = None, wait_stream: bool = False, stream=None):
+    """Deadline over a block of communicator calls (cosmos_rl/utils/pynccl.py:458-540 has the reference's form).
+
+    Every ``DynComm`` used inside the block joins the context. Without ``wait_stream`` a timer aborts those
+    communicators when the block is still running after ``timeout_s``, which makes a host call that is blocked
+    inside the library return with an error. With ``wait_stream`` the block's host calls are only enqueues; on
+    exit the context polls the stream (never a blocking synchronize) until the enqueued work has finished or the
+    deadline passes, and aborts the communicators in the second case. Either way ``CommTimeout`` is raised."""
+    limit = timeout_s if timeout_s is not None else constant.COSMOS_NCCL_TIMEOUT_MS / 1000.0
+    ctx = _WatchContext(time.monotonic() + limit)
+    stack = _watch_stack()
+    stack.append(ctx)
+    fired = threading.Event()
+
+    def fire():
+        fired.set()
+        ctx.abort = True
+        logger.error("watchdog: block exceeded %.1f s; aborting %s", limit, sorted(c.name for c in ctx.comms))
+        for c in list(ctx.comms):
+            c.abort()
+
+    timer = None
+    if not wait_stream:
+        timer = threading.Timer(limit, fire)
+        timer.daemon = True
+        timer.start()
+    failed = False
+    try:
+        yield ctx
+    except BaseException:
+        failed = True
+        ctx.abort = True
+        raise
+    finally:
+        if timer is not None:
+            timer.cancel()
+        if wait_stream and not failed:
+            done = _stream_probe(stream)
+            while not done():
+                if time.monotonic() >= ctx.deadline:
+                    fire()
+                    break
+                time.sleep(0.001)
+        stack.remove(ctx)
+        if ctx.abort:
+            for c in list(ctx.comms):
+                c.abort()
+        if fired.is_set() and not failed:
+            raise CommTimeout(f"watchdog: communicator block exceeded {limit:.1f} s and was aborted")
+
+
+def bounded_drain_or_abort(stream, timeout_s: float, context: str,
+                           comms: Optional[Iterable["DynComm"]] = None) -> bool:
+    """Teardown helper (cosmos_rl/utils/pynccl.py:629-673): wait at most ``timeout_s`` for the work in flight on
+    ``stream``. Per-operation deadlines only bound the enqueue of a collective, so a broadcast whose peer has left
+    keeps spinning on the device; a plain synchronize behind it would never return. Returns True when the stream
+    drained, False after aborting ``comms`` (all live communicators when omitted)."""
+    done = _stream_probe(stream)
+    t0 = time.monotonic()
+    while not done():
+        if time.monotonic() - t0 > timeout_s:
+            logger.warning("[abnormal teardown] %s: device work still in flight after %.1f s; a peer has most "
+                           "likely left in the middle of a collective. Aborting communicators.", context, timeout_s)
+            if comms is None:
+                abort_all()
+            else:
+                for c in list(comms):
+                    c.abort()
+            return False
+        time.sleep(0.005)
+    return True
+
+
 class DynComm:
     def __init__(self, name: str, store: dist.Store, rank: int, size: int, device: torch.device,
                  timeout_s: Optional[float] = None, owns_store: bool = False):
@@ -72,23 +182,75 @@ class DynComm:
         if self.aborted:
             raise CommTimeout(f"{self.name}: communicator was aborted")
         limit = timeout_s if timeout_s is not None else self.timeout_s
+        for ctx in _watch_stack():
+            ctx.comms.add(self)
+            limit = max(0.001, min(limit, ctx.deadline - time.monotonic()))
         _notify(self.name, "enter", op=what)
         ok = work.wait(timedelta(seconds=limit)) if work is not None else True
         if ok is False:
             _notify(self.name, "timeout", op=what)
             self.abort()
             raise CommTimeout(f"{self.name}: {what} did not finish within {limit:.0f} s")
+        err = self.async_error()
+        if err is not None:
+            _notify(self.name, "error", op=what, error=err)
+            self.abort()
+            raise CommTimeout(f"{self.name}: {what} left the communicator in error state {err}")
         _notify(self.name, "return", op=what)
+
+    def _issue(self, what: str, post: Callable[[], object], timeout_s: Optional[float]) -> None:
+        """Post one operation and wait for it. The library call that posts it can itself block (a first send
+        that has to connect to a peer which never arrives), and no deadline of the returned work object covers
+        that, so an abort is armed before the call and cancelled when it returns
+        (cosmos_rl/utils/pynccl.py:236-275)."""
+        if self.aborted:
+            raise CommTimeout(f"{self.name}: communicator was aborted")
+        limit = timeout_s if timeout_s is not None else self.timeout_s
+        lock, state = threading.Lock(), {"returned": False, "fired": False}
+
+        def abort_blocked_call():
+            with lock:
+                if state["returned"]:
+                    return
+                state["fired"] = True
+            _notify(self.name, "timeout", op=what, where="post")
+            self.abort()
+
+        timer = threading.Timer(limit, abort_blocked_call)
+        timer.daemon = True
+        timer.start()
+        try:
+            work = post()
+        finally:
+            with lock:
+                state["returned"] = True
+            timer.cancel()
+        if state["fired"]:
+            raise CommTimeout(f"{self.name}: posting {what} blocked for more than {limit:.0f} s")
+        self._run(what, work, timeout_s)
+
+    def async_error(self) -> Optional[str]:
+        """The communicator's asynchronous error state, ``None`` when healthy (the library reports remote
+        failures and aborted peers here, cosmos_rl/utils/pynccl.py:297-325). Gloo has no such state."""
+        get = getattr(self.pg, "get_error", None)
+        if get is None or self.aborted:
+            return None
+        try:
+            e = get()
+        except Exception as exc:                                    # a dead communicator cannot answer
+            return str(exc)
+        name = getattr(e, "name", str(e))
+        return None if name in ("SUCCESS", "0") else name
 
     def send(self, t: torch.Tensor, dst: int, tag: int = 0, timeout_s: Optional[float] = None) -> None:
         try:
-            self._run(f"send->{dst}", self.pg.send([t.contiguous()], dst, tag), timeout_s)
+            self._issue(f"send->{dst}", lambda: self.pg.send([t.contiguous()], dst, tag), timeout_s)
         except RuntimeError as e:
             self._fail(e)
 
     def recv(self, t: torch.Tensor, src: int, tag: int = 0, timeout_s: Optional[float] = None) -> None:
         try:
-            self._run(f"recv<-{src}", self.pg.recv([t], src, tag), timeout_s)
+            self._issue(f"recv<-{src}", lambda: self.pg.recv([t], src, tag), timeout_s)
         except RuntimeError as e:
             self._fail(e)
 
@@ -97,7 +259,7 @@ class DynComm:
         opts.rootRank = src
         opts.rootTensor = 0
         try:
-            self._run(f"broadcast<-{src}", self.pg.broadcast([t], opts), timeout_s)
+            self._issue(f"broadcast<-{src}", lambda: self.pg.broadcast([t], opts), timeout_s)
         except RuntimeError as e:
             self._fail(e)
 
@@ -105,7 +267,7 @@ class DynComm:
         opts = dist.AllreduceOptions()
         opts.reduceOp = op
         try:
-            self._run("all_reduce", self.pg.allreduce([t], opts), timeout_s)
+            self._issue("all_reduce", lambda: self.pg.allreduce([t], opts), timeout_s)
         except RuntimeError as e:
             self._fail(e)
 

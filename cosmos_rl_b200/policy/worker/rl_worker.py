@@ -244,9 +244,11 @@ class RLPolicyWorker(CommMixin):
         from ...utils.misc import str2dtype
         tdt = str2dtype(self.config.train.transfer_dtype) if self.device.type == "cuda" else None
         P = c.src_replica_size
-        for dst_rank, d in self.p2r_send_plan:
-            t = torch.as_strided(flat, (d[5], d[6]), (d[2], 1), flat.storage_offset() + d[1]).contiguous()
-            comm.send(t.to(tdt) if tdt is not None else t, P + dst_rank)
+        from ...parallel.dyncomm import watchdog
+        with watchdog(wait_stream=True):                 # the sends are enqueues; bound the device side too
+            for dst_rank, d in self.p2r_send_plan:
+                t = torch.as_strided(flat, (d[5], d[6]), (d[2], 1), flat.storage_offset() + d[1]).contiguous()
+                comm.send(t.to(tdt) if tdt is not None else t, P + dst_rank)
         return False
 
     def _peer_mode(self) -> bool:

@@ -192,10 +192,12 @@ class DisaggregatedRolloutControlWorker(CommMixin):
             self.recv_plan = self.api.get_shard_insts("rollout", self.global_rank)
         flat = self.rollout.flat.data
         tdt = str2dtype(self.config.train.transfer_dtype) if self.device.type == "cuda" else flat.dtype
-        for d in self.recv_plan:
-            buf = torch.empty(d[5], d[6], dtype=tdt, device=self.device)
-            comm.recv(buf, d[0])
-            torch.as_strided(flat, (d[5], d[6]), (d[4], 1), flat.storage_offset() + d[3]).copy_(buf)
+        from ..parallel.dyncomm import watchdog
+        with watchdog(wait_stream=True):                 # the receives are enqueues; bound the device side too
+            for d in self.recv_plan:
+                buf = torch.empty(d[5], d[6], dtype=tdt, device=self.device)
+                comm.recv(buf, d[0])
+                torch.as_strided(flat, (d[5], d[6]), (d[4], 1), flat.storage_offset() + d[3]).copy_(buf)
         if getattr(self.rollout, "fp8", None) is not None:
             self.rollout.fp8.quantize_local()      # no in-flight quantisation on this route: second pass
 
@@ -227,7 +229,9 @@ class DisaggregatedRolloutControlWorker(CommMixin):
             self.r2r_comm = create_comm(self.api, key + f"-{c.uuid_value}", rank, len(names), self.device,
                                         is_initiator=rank == 0)
         src = names.index(c.src_replica_name)
-        self.r2r_comm.broadcast(self.rollout.flat.data, src)
+        from ..parallel.dyncomm import watchdog
+        with watchdog(wait_stream=True):
+            self.r2r_comm.broadcast(self.rollout.flat.data, src)
 
     # ------------------------------------------------------------------ prompts
     def request_new_prompts(self, n: int, validation_step: Optional[int] = None) -> None:

@@ -40,7 +40,11 @@ def safe_destroy(timeout_s: float = 20.0, exit_code: int = 0) -> None:
         return
     gc.collect()
     if torch.cuda.is_available():
-        torch.cuda.synchronize()
+        from ..parallel.dyncomm import bounded_drain_or_abort
+        if not bounded_drain_or_abort(None, timeout_s, "process-group teardown"):
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(exit_code)
     t = threading.Thread(target=dist.destroy_process_group, daemon=True)
     t.start()
     t.join(timeout_s)

@@ -161,6 +161,52 @@ def test_rank_leaving_between_steps_times_out_and_mesh_is_rebuilt(tmp_path):
     mp.spawn(_failure_worker, args=(2, str(tmp_path / "fstore")), nprocs=2, join=True)
 
 
+def _watchdog_worker(rank, world, store_path):
+    """A block deadline shorter than the per-operation limit: the watchdog's timer aborts the communicator under a
+    receive whose sender never sends, and the block ends with CommTimeout. The stream form polls a probe and aborts
+    when the enqueued work does not finish; a drain that runs out aborts the named communicators and says so."""
+    import time
+    from datetime import timedelta
+    from cosmos_rl_b200.parallel import dyncomm
+    store = dist.FileStore(store_path, world)
+    comm = dyncomm.DynComm("p2r-a", store, rank, world, torch.device("cpu"), timeout_s=30.0)
+    x = torch.ones(2)
+    comm.all_reduce(x)
+    if rank == 1:
+        store.wait(["rank0_done"], timedelta(seconds=60))        # stays alive, sends nothing
+        return
+    t0 = time.time()
+    with pytest.raises(dyncomm.CommTimeout):
+        with dyncomm.watchdog(timeout_s=1.0) as ctx:
+            comm.recv(torch.empty(2), 1)
+    assert time.time() - t0 < 10.0 and comm.aborted and comm in ctx.comms
+    # stream form: healthy block leaves the communicator alone
+    solo = dyncomm.DynComm("solo-a", store, 0, 1, torch.device("cpu"), timeout_s=5.0)
+    with dyncomm.watchdog(timeout_s=1.0, wait_stream=True, stream=lambda: True):
+        solo.all_reduce(torch.ones(2))
+    assert not solo.aborted
+    # stream form: the device work never finishes
+    t0 = time.time()
+    with pytest.raises(dyncomm.CommTimeout):
+        with dyncomm.watchdog(timeout_s=0.5, wait_stream=True, stream=lambda: False):
+            solo.all_reduce(torch.ones(2))
+    assert 0.4 < time.time() - t0 < 5.0 and solo.aborted
+    # bounded drain
+    a = dyncomm.DynComm("solo-b", store, 0, 1, torch.device("cpu"), timeout_s=5.0)
+    b = dyncomm.DynComm("solo-c", store, 0, 1, torch.device("cpu"), timeout_s=5.0)
+    assert dyncomm.bounded_drain_or_abort(lambda: True, 0.2, "test") and not a.aborted
+    assert not dyncomm.bounded_drain_or_abort(lambda: False, 0.2, "test", comms=[a])
+    assert a.aborted and not b.aborted
+    assert not dyncomm.bounded_drain_or_abort(lambda: False, 0.2, "test")
+    assert b.aborted and dyncomm.live_comms() == []
+    assert a.async_error() is None
+    store.set("rank0_done", b"1")
+
+
+def test_watchdog_block_deadline_stream_deadline_and_bounded_drain(tmp_path):
+    mp.spawn(_watchdog_worker, args=(2, str(tmp_path / "wstore")), nprocs=2, join=True)
+
+
 def _tp_worker(rank, world, store, qk_norm, seq_parallel=False):
     """Tensor-parallel training step == unsharded model: log-probs and (gathered) gradients."""
     import copy
