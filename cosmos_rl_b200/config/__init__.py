@@ -443,6 +443,10 @@ class B200Config(_Section):
                                          # gradients (one all-gather less per projection in backward)
     sp_fused_kernels: bool = False       # sequence-parallel projections through the all-gather -> GEMM and
                                          # GEMM -> reduce-scatter kernels instead of library collectives + cuBLAS
+    shard_params: bool = False           # parameter-sharded data parallelism: weights and gradients are 1/dp_shard
+                                         # per rank too, gathered block by block around their use (same switch as
+                                         # train.fsdp_reshard_after_forward = "always"). Off by default: models whose
+                                         # bf16 weights fit stay resident and skip the gathers
     router_bias_update_rate: float = 1e-3  # DeepSeek-V3 load-balancing bias step per optimizer step (0 = frozen)
     recompute: str = "auto"              # with policy.model_gradient_checkpointing: "selective" (attention half +
                                          # SwiGLU only), "full" (whole block, least memory), "none", or "auto":

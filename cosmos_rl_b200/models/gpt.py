@@ -304,6 +304,7 @@ class GPT(BaseModel):
         else:
             self.lm_head = nn.Linear(a.dim, self.v_local, bias=False)
         self.gradient_checkpointing = False
+        self.param_sharder = None       # ShardedFlatParams under parameter-sharded data parallelism
         self.tp = None  # set by parallel.tp.TensorParallel when tp_size > 1
 
     # ------------------------------------------------------------------ registry hooks
@@ -355,6 +356,8 @@ class GPT(BaseModel):
 
         Under sequence parallelism the token axis is padded to the rank multiple with a dummy sequence, every block
         works on this rank's rows, and the final hidden states are gathered (and un-padded) before they are returned."""
+        if self.param_sharder is not None:
+            return self._forward_sharded(input_ids, position_ids, cu_seqlens, max_seqlen)
         sp = self.tp is not None and self.tp.sequence_parallel
         T = input_ids.shape[0]
         if sp:
@@ -386,6 +389,30 @@ class GPT(BaseModel):
             out = self.tp.gather_rows(out)[:T]
         return out
 
+    def _forward_sharded(self, input_ids, position_ids, cu_seqlens, max_seqlen) -> torch.Tensor:
+        """The same forward with parameter-sharded data parallelism: every unit (embedding, block, final norm + head)
+        runs inside ``param_sharder.run``, which gathers its weights and hooks its backward."""
+        sh, gc = self.param_sharder, self.gradient_checkpointing
+        h = sh.run(0, lambda: self.embed_tokens(input_ids)) if self.is_first_stage else input_ids
+        res = None
+        for i, layer in enumerate(self.layers):
+            def block(h, res, layer=layer):
+                if gc in ("selective", "swiglu") and torch.is_grad_enabled():
+                    return layer(h, res, position_ids, cu_seqlens, max_seqlen, None, recompute=gc)
+                if gc and torch.is_grad_enabled():
+                    return checkpoint(layer, h, res, position_ids, cu_seqlens, max_seqlen, None, use_reentrant=False)
+                return layer(h, res, position_ids, cu_seqlens, max_seqlen, None)
+            h, res = sh.run(1 + i, block, h, res)
+        return sh.run(len(self.layers) + 1,
+                      lambda h, res: F.rms_norm(h, self.norm, self.args.norm_eps, residual=res)[0], h, res)
+
+    def _head_unit(self):
+        """(unit that holds the output head, whether its gradient reduction waits for a later use of the unit)."""
+        sh = self.param_sharder
+        if self.lm_head is None:                      # tied: the head is the embedding; reduce before the blocks run
+            return sh.unit_of_param["embed_tokens.weight"], False
+        return sh.unit_of_param["lm_head.weight"], True
+
     def attach_context_parallel(self, cp) -> None:
         """Inputs of ``forward`` become this rank's chunk of every sequence (``ContextParallel.shard``), with global
         position ids and local ``cu_seqlens``; only the attention layers communicate."""
@@ -396,9 +423,16 @@ class GPT(BaseModel):
         """Per-token log-prob of ``labels`` and entropy from hidden states, through the fused lm_head kernel."""
         if self.tp is not None:
             return self.tp.vocab_parallel_logprob(hidden, self.lm_head_weight, labels, temperature)
+        if self.param_sharder is not None:
+            u, defer = self._head_unit()
+            return self.param_sharder.run(
+                u, lambda h: F.fused_logprob(h, self.lm_head_weight, labels, temperature), hidden, defer_reduce=defer)
         return F.fused_logprob(hidden, self.lm_head_weight, labels, temperature)
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        if self.param_sharder is not None:
+            u, defer = self._head_unit()
+            return self.param_sharder.run(u, lambda h: _linear(h, self.lm_head_weight), hidden, defer_reduce=defer)
         out = _linear(hidden, self.lm_head_weight)
         return self.tp.gather_vocab(out) if self.tp is not None else out
 

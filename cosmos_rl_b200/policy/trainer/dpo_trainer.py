@@ -58,9 +58,11 @@ class DPOTrainer(LLMTrainer):
             self.reference_state = self.flat.data.to("cpu", copy=True)
         cur = self.flat.data.to("cpu", copy=True)
         self.flat.data.copy_(self.reference_state.to(self.device))
+        self._weights_changed()
         with torch.no_grad():
             ref = [self._seq_logprobs(c) for c in chunks]
         self.flat.data.copy_(cur.to(self.device))
+        self._weights_changed()
         self.model.train()
         self.optimizer.zero_grad()
         losses, accs = [], []

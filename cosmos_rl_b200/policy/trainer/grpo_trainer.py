@@ -273,6 +273,7 @@ class GRPOTrainer(LLMTrainer):
     def _swap_flat(self, other: torch.Tensor) -> torch.Tensor:
         cur = self.flat.data.to("cpu", copy=True)
         self.flat.data.copy_(other.to(self.device))
+        self._weights_changed()
         return cur
 
     def _reference_logprobs(self, batches):
@@ -283,6 +284,7 @@ class GRPOTrainer(LLMTrainer):
             return self._compute_logprobs_nograd(batches)
         finally:
             self.flat.data.copy_(cur.to(self.device))
+            self._weights_changed()
 
     def needs_reference(self) -> bool:
         return self.tp_cfg.kl_beta != 0.0

@@ -82,8 +82,26 @@ class LLMTrainer(Trainer):
             self._apply_trainable_patterns()
         dp = parallel_dims.dp_shard
         is_expert = (lambda n: n.endswith("w_gate_up") or n.endswith("w_down")) if ep > 1 else None
-        self.flat = FlatParams(model, self.param_dtype, self.device, shard_multiple=dp,
-                               allocator=kw.get("allocator"), local_filter=is_expert)
+        # parameter-sharded data parallelism (``fsdp_reshard_after_forward = "always"`` or ``b200.shard_params``):
+        # weights, gradients and optimizer state are all 1/dp_shard per rank, gathered unit by unit around their use
+        self._allocator = kw.get("allocator")
+        self._sync_full = None
+        self.shard_params = bool(config.b200.shard_params or config.train.fsdp_reshard_after_forward == "always")
+        if self.shard_params:
+            if (tp > 1 or ep > 1 or parallel_dims.pp > 1 or parallel_dims.cp > 1 or self.lora_targets
+                    or config.train.fp8.enable_fp8 or not hasattr(model, "param_sharder")):
+                raise NotImplementedError("parameter sharding runs native dense models under dp_shard x dp_replicate "
+                                          "only (no tp / cp / pp / ep, no adapters, no fp8 weights)")
+            from ...parallel.sharded_params import ShardedFlatParams
+            rd = str2dtype(config.train.fsdp_reduce_dtype) if self.device.type == "cuda" else None
+            self.flat = ShardedFlatParams(model, self.param_dtype, self.device,
+                                          parallel_dims.group("dp_shard") if dp > 1 else None, reduce_dtype=rd)
+            model.param_sharder = self.flat
+            logger.info("[Policy] parameter sharding over %d ranks: %s", dp,
+                        {k: round(v, 2) for k, v in self.flat.memory_report().items()})
+        else:
+            self.flat = FlatParams(model, self.param_dtype, self.device, shard_multiple=dp,
+                                   allocator=kw.get("allocator"), local_filter=is_expert)
         if ep > 1:
             model.set_ep_group(parallel_dims.group("ep") or parallel_dims.group("dp_shard"))
         if self.lora_targets:
@@ -143,15 +161,17 @@ class LLMTrainer(Trainer):
             for slot in self.flat.slots:
                 if "norm" in slot.name:
                     tp_mask[slot.offset:slot.offset + slot.numel] = True
+        sharded_norm = [parallel_dims.group("dp_shard")] if (self.shard_params and dp > 1) else []
         self.optimizer = FlatAdamW(
-            self.flat, lr=lr, betas=tuple(config.train.optm_betas), eps=config.train.epsilon,
+            self.flat.optimizer_view() if self.shard_params else self.flat, lr=lr, betas=tuple(config.train.optm_betas), eps=config.train.epsilon,
             weight_decay=config.train.optm_weight_decay if config.train.optm_name.startswith("AdamW") else 0.0,
             state_bits=8 if config.train.optm_name.endswith("8bit") else 32,
             max_grad_norm=config.train.optm_grad_norm_clip,
             tp_group=parallel_dims.group("tp") if tp > 1 else None, tp_replicated=tp_mask,
-            norm_groups=[parallel_dims.group("pp")] if parallel_dims.pp > 1 else [],
+            norm_groups=([parallel_dims.group("pp")] if parallel_dims.pp > 1 else []) + sharded_norm,
             sum_groups=[parallel_dims.group("cp")] if parallel_dims.cp > 1 else [],
-            dp_group=parallel_dims.group("dp_shard") if dp > 1 else None, collective=kw.get("collective"),
+            dp_group=parallel_dims.group("dp_shard") if (dp > 1 and not self.shard_params) else None,
+            collective=kw.get("collective"),
             tail_replica_group=parallel_dims.group("ep_replica") if ep > 1 else None,
             replicate_group=parallel_dims.group("dp_replicate") if parallel_dims.dp_replicate > 1 else None)
         self.data_packer = data_packer or BaseDataPacker.get_default(mt)()
@@ -208,10 +228,18 @@ class LLMTrainer(Trainer):
             if pc.trainable_map and name in pc.trainable_map:
                 p.requires_grad_(bool(pc.trainable_map[name]))
 
+    def _weights_changed(self) -> None:
+        """Call after writing ``flat.data`` directly (weights swapped in or out): under parameter sharding the
+        gathered copies of the units have to be fetched again."""
+        if self.shard_params:
+            self.flat.invalidate()
+
     def optimizer_step(self) -> torch.Tensor:
         """One optimizer step plus what rides on it (the router bias of DeepSeek-style MoE blocks, moved from the
         expert load of the batch summed over the data-parallel ranks). Returns the gradient norm."""
         norm = self.optimizer.step(self.lr_scale(self.train_step))
+        if self.shard_params:
+            self.flat.invalidate()               # the gathered copies of the units are stale now
         if self.ema is not None:
             self.ema.step(self.optimizer.step_count - 1)
         rate = self.config.b200.router_bias_update_rate
@@ -240,6 +268,8 @@ class LLMTrainer(Trainer):
             with maybe_offload(self.config.train.activation_offload, self.model):
                 loss = loss_of(self.model(b["input_ids"], b["position_ids"], b["cu_seqlens"], b["max_seqlen"]), i, b)
             loss.backward()
+            if self.shard_params:
+                self.flat.finish_backward()
             losses.append(loss.detach())
         return losses
 
@@ -284,15 +314,19 @@ class LLMTrainer(Trainer):
     def model_load_from_hf(self) -> None:
         from ...models import hf_io
         path = self.config.policy.model_safetensor_path or self.config.policy.model_name_or_path
-        if path and os.path.isdir(path) and hf_io.has_safetensors(path):
-            hf_io.load_hf_weights(self.model, path, self.parallel_dims)
-        else:
-            seed = self.config.train.seed if self.config.train.seed is not None else 0
-            if self.device.type == "cuda":
-                self.model.init_weights_on_device(seed)
+        import contextlib
+        # sharded parameters: load into a transient full copy (device memory if it fits, else host) and keep the shard
+        whole = self.flat.materialized(fill=False, writeback=True) if self.shard_params else contextlib.nullcontext()
+        with whole as full:
+            if path and os.path.isdir(path) and hf_io.has_safetensors(path):
+                hf_io.load_hf_weights(self.model, path, self.parallel_dims)
             else:
-                self.model.init_weights(seed)
-            logger.info("[Policy] no checkpoint at %r: random-init weights from seed %d", path, seed)
+                seed = self.config.train.seed if self.config.train.seed is not None else 0
+                if self.device.type == "cuda" and (full is None or full.is_cuda):
+                    self.model.init_weights_on_device(seed)
+                else:
+                    self.model.init_weights(seed)
+                logger.info("[Policy] no checkpoint at %r: random-init weights from seed %d", path, seed)
         if self.lora_targets:
             from .. import lora
             lora.reset_lora_parameters(self.model, self.config.train.seed or 0,
@@ -316,6 +350,20 @@ class LLMTrainer(Trainer):
         if self.lora_targets:
             from .. import lora
             lora.merge_native(self.model)
+        if self.shard_params:
+            self.flat.gather_full(out=self.sync_buffer())
+
+    def sync_buffer(self) -> torch.Tensor:
+        """The buffer rollout replicas read the weights from (its layout is what ``flat.slots`` index). With resident
+        weights that is the flat buffer itself. Under parameter sharding it is a full copy that exists for weight
+        synchronisation only; it is allocated once (peer-visible where the flat buffer would be) so that its exported
+        handle stays valid, and refilled by ``before_weight_sync``."""
+        if not self.shard_params:
+            return self.flat.data
+        if self._sync_full is None:
+            alloc = self._allocator or (lambda n, dt, dev: torch.zeros(n, dtype=dt, device=dev))
+            self._sync_full = alloc(self.flat.total, self.flat.dtype, self.device)
+        return self._sync_full
 
     def after_weight_sync(self) -> None:
         if self.lora_targets:
@@ -337,6 +385,8 @@ class LLMTrainer(Trainer):
             self.reference_state = self.flat.data.to("cpu", copy=True)
             self.reference_step = 0
         self.flat.data.copy_(state["model"]["flat"].to(self.flat.dtype))
+        if self.shard_params:
+            self.flat.invalidate()
         self.optimizer.load_state_dict(state["optimizer"])
         self._init_ema()
         if self.ema is not None and state["model"].get("ema") is not None:
@@ -396,8 +446,10 @@ class LLMTrainer(Trainer):
                 with open(os.path.join(output_dir, "adapter_config.json"), "w") as f:
                     json.dump(lora.adapter_config(self.config.policy.lora, self.lora_targets), f, indent=1)
             return
-        hf_io.export_safetensors(self.model, self.hf_config, output_dir, self.parallel_dims,
-                                 source_dir=self.config.policy.model_name_or_path)
+        import contextlib
+        with (self.flat.materialized() if self.shard_params else contextlib.nullcontext()):
+            hf_io.export_safetensors(self.model, self.hf_config, output_dir, self.parallel_dims,
+                                     source_dir=self.config.policy.model_name_or_path)
         ck = self.config.train.ckpt
         if self.parallel_dims.global_rank == 0 and (ck.upload_hf or ck.upload_s3):
             from ...utils import upload

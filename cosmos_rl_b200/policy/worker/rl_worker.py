@@ -65,7 +65,8 @@ class RLPolicyWorker(CommMixin):
             trainer_kw["allocator"] = peer_allocator(self.device)
         trainer_kw.update(kw)
         self.trainer = TrainerRegistry.get_trainer_cls(tp.trainer_type)(config, parallel_dims, **trainer_kw)
-        if parallel_dims.dp_shard > 1 and self.device.type == "cuda" and config.b200.peer_weight_sync:
+        if (parallel_dims.dp_shard > 1 and self.device.type == "cuda" and config.b200.peer_weight_sync
+                and not getattr(self.trainer, "shard_params", False)):
             from ...parallel.fsdp import PeerCollective
             self.trainer.optimizer.collective = PeerCollective(self.trainer.flat, parallel_dims.group("dp_shard"))
         self.data_queue: "queue.Queue[Rollout]" = queue.Queue()
@@ -106,11 +107,15 @@ class RLPolicyWorker(CommMixin):
                 pass
 
     # ------------------------------------------------------------------ shard infos for weight sync
+    def _sync_buffer(self) -> torch.Tensor:
+        fn = getattr(self.trainer, "sync_buffer", None)
+        return fn() if fn is not None else self.trainer.flat.data
+
     def post_shard_infos(self) -> None:
         if self.shard_infos_posted:
             return
         info = shard_info(self.global_rank, model_parts(self.trainer.model, self.trainer.flat), self.trainer.flat.total)
-        buf = getattr(self.trainer.flat.data, "_peer_buffer", None)
+        buf = getattr(self._sync_buffer(), "_peer_buffer", None)
         if buf is not None:
             info["ipc_handle"] = buf.export()
             info["nbytes"] = buf.nbytes
@@ -240,7 +245,7 @@ class RLPolicyWorker(CommMixin):
             self.p2r_comms[pair] = comm
         if self.p2r_send_plan is None:
             self.p2r_send_plan = self.api.get_shard_insts("policy", self.global_rank)
-        flat = self.trainer.flat.data
+        flat = self._sync_buffer()
         from ...utils.misc import str2dtype
         tdt = str2dtype(self.config.train.transfer_dtype) if self.device.type == "cuda" else None
         P = c.src_replica_size
@@ -253,7 +258,7 @@ class RLPolicyWorker(CommMixin):
 
     def _peer_mode(self) -> bool:
         return bool(self.config.b200.peer_weight_sync and self.device.type == "cuda"
-                    and getattr(self.trainer.flat.data, "_peer_buffer", None) is not None)
+                    and getattr(self._sync_buffer(), "_peer_buffer", None) is not None)
 
     # ------------------------------------------------------------------ data path
     def start_rollout_thread(self) -> None:

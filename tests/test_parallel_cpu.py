@@ -842,3 +842,66 @@ def test_checkpoint_files_are_split_between_data_parallel_ranks(tmp_path, monkey
     hf_io.export_safetensors(m, m.args.to_hf_config(), out)
     assert len([f for f in os.listdir(out) if f.endswith(".safetensors")]) >= 3
     _spawn(_split_load_worker, 2, tmp_path, out)
+
+
+def _shard_params_worker(rank, world, store, out_dir, ckpt_mode):
+    """Parameter-sharded data parallelism on two ranks: every rank holds half of every unit (embedding, block, final
+    norm + head), units are gathered around their use and their gradients reduce-scattered after their backward.
+    Losses, gradient norm and weights after two optimizer steps equal the single-process trainer on the whole batch;
+    with full-block recomputation the same holds; gathers and reductions are counted."""
+    from cosmos_rl_b200.config import Config
+    from cosmos_rl_b200.parallel.dims import ParallelDims
+    from cosmos_rl_b200.policy.trainer.sft_trainer import SFTTrainer
+    _init(rank, world, store)
+
+    def cfg(par, **b200):
+        return Config.from_dict({
+            "policy": {"model_name_or_path": "tiny-qwen2", "model_max_length": 64,
+                       "model_gradient_checkpointing": ckpt_mode != "none",
+                       "parallelism": dict({"tp_size": 1, "cp_size": 1, "pp_size": 1, "dp_shard_size": 1}, **par)},
+            "b200": dict({"recompute": ckpt_mode}, **b200),
+            "train": {"seed": 0, "optm_lr": 1e-3, "optm_warmup_steps": 0, "output_dir": out_dir, "optm_grad_norm_clip": 0.5,
+                      "train_policy": {"type": "sft", "trainer_type": "sft", "mini_batch": 2},
+                      "ckpt": {"enable_checkpoint": False}}})
+    cpu = torch.device("cpu")
+    c = cfg({"dp_shard_size": 2}, shard_params=True)
+    dims = ParallelDims.from_config_parallelism(c.policy.parallelism, world, rank, cpu)
+    dims.build_groups()
+    tr = SFTTrainer(c, dims, device=cpu)
+    ref = SFTTrainer(cfg({}), ParallelDims(world_size=1, device=cpu), device=cpu)
+    tr.model_load_from_hf()                                # same seed: both start from the same weights
+    ref.model_load_from_hf()
+    sp = tr.flat
+    assert sp.sharded and sp.n_shard * 2 == sp.total and tr.optimizer.master.numel() == sp.n_shard
+    full0 = sp.gather_full()
+    for (n, q) in ref.model.named_parameters():
+        assert torch.equal(sp.view(n, full0), q), n
+    g = torch.Generator().manual_seed(3)
+    batch = [{"input_ids": torch.randint(0, 32000, (n,), generator=g).tolist()} for n in (12, 9, 15, 7, 10, 6, 8, 14)]
+    mine = batch[rank::2]
+    for i in range(2):
+        g0 = sp.n_gathers
+        a = tr.step_training(mine, total_steps=10, train_step=i + 1)
+        b = ref.step_training(batch, total_steps=10, train_step=i + 1)
+        loss = torch.tensor(a["train/loss_avg"])
+        dist.all_reduce(loss)
+        assert abs(loss.item() / 2 - b["train/loss_avg"]) < 1e-4, (loss.item() / 2, b["train/loss_avg"])
+        assert abs(a["train/grad_norm"] - b["train/grad_norm"]) < 2e-3 * b["train/grad_norm"]
+        assert sp.n_gathers - g0 >= 2 * len(sp.units)      # every unit fetched for forward and again for backward
+    assert sp.n_reduces >= 2 * len(sp.units)
+    full = sp.gather_full()
+    for (n, q) in ref.model.named_parameters():
+        assert torch.allclose(sp.view(n, full), q, atol=5e-4), (n, (sp.view(n, full) - q).abs().max())
+    # export reads the whole model through a transient full copy; the shards are untouched afterwards
+    before = sp.data.clone()
+    with sp.materialized() as whole:
+        assert torch.equal(whole, full)
+        assert tr.model.layers[0].self_attn.o_proj.weight.data_ptr() >= whole.data_ptr()
+    assert torch.equal(sp.data, before)
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("ckpt_mode", ["none", "full", "swiglu"])
+def test_parameter_sharded_training_matches_unsharded(tmp_path, ckpt_mode):
+    """The reference shards parameters per block with FSDP2 (cosmos_rl/policy/model/gpt/parallelize.py:366-423)."""
+    _spawn(_shard_params_worker, 2, tmp_path, str(tmp_path), ckpt_mode)
