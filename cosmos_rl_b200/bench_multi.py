@@ -101,7 +101,7 @@ def run_disaggregated(bench) -> Dict[str, Any]:
                 maps.append(m)
                 ptrs[e["rank"]] = m.ptr
         plan = build_plan(src_infos, my["info"])
-        sync = PeerWeightSync(flat.data, plan, ptrs)
+        sync = PeerWeightSync(flat.data, plan, ptrs, dst_rank=rank)
 
     def world_barrier():
         torch.cuda.synchronize()

@@ -182,3 +182,28 @@ def merge_descriptors(plan: List[List[int]]) -> List[List[int]]:
                 continue
         out.append(list(d))
     return out
+
+
+def interleave_sources(plan: List[List[int]], first: int = 0) -> List[List[int]]:
+    """Order descriptors so that a pull draws on every source at once: the lists of the sources are merged by the
+    fraction of each source's bytes already scheduled, starting with the ``first``-th source (callers pass the
+    destination's rank so that two destinations do not start on the same source). A plan sorted by source makes every
+    puller read one source at a time, and pullers that share a source then share its outgoing link."""
+    by_src: Dict[int, List[List[int]]] = {}
+    for d in plan:
+        by_src.setdefault(d[0], []).append(d)
+    srcs = sorted(by_src)
+    if len(srcs) <= 1:
+        return list(plan)
+    srcs = srcs[first % len(srcs):] + srcs[:first % len(srcs)]
+    total = {r: float(sum(d[5] * d[6] for d in by_src[r])) or 1.0 for r in srcs}
+    done = {r: 0.0 for r in srcs}
+    pos = {r: 0 for r in srcs}
+    out: List[List[int]] = []
+    while len(out) < len(plan):
+        r = min((r for r in srcs if pos[r] < len(by_src[r])), key=lambda r: (done[r] / total[r], srcs.index(r)))
+        d = by_src[r][pos[r]]
+        pos[r] += 1
+        done[r] += d[5] * d[6]
+        out.append(d)
+    return out

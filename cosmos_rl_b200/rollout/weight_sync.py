@@ -17,7 +17,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import native
-from ..parallel.reshard import merge_descriptors
+from ..parallel.reshard import interleave_sources, merge_descriptors
 
 TILE = 128
 
@@ -79,13 +79,14 @@ class Fp8WeightStore:
 
 class PeerWeightSync:
     def __init__(self, dst_flat: torch.Tensor, plan: List[List[int]], src_ptrs: Dict[int, int],
-                 fp8: Optional[Fp8WeightStore] = None):
+                 fp8: Optional[Fp8WeightStore] = None, dst_rank: int = 0):
         """``plan`` rows: [src_rank, src_off, src_ld, dst_off, dst_ld, rows, cols] (elements of bf16). With an
         ``fp8`` store, rectangles that land block-aligned inside a quantised matrix are written as e4m3 + scales by
         the same kernel pass (their bf16 copy is not refreshed); the rest stays bf16."""
         self.device = dst_flat.device
         self.dst = dst_flat
         plan = merge_descriptors(plan) if fp8 is None else [list(d) for d in plan]
+        plan = interleave_sources(plan, first=dst_rank)     # every source at once, pullers staggered
         self.n = len(plan)
         self.n_quant = 0
         self.bytes = sum(d[5] * d[6] for d in plan) * 2
@@ -145,39 +146,42 @@ class CollectiveWeightSync:
         return torch.as_strided(flat, (rows, cols), (ld, 1), storage_offset=flat.storage_offset() + off)
 
     def send(self, flat: torch.Tensor, send_plan: List[List[Any]]) -> None:
-        """``send_plan`` rows: [dst_rank, [src_rank, src_off, src_ld, dst_off, dst_ld, rows, cols]]."""
-        ops, keep = [], []
+        """``send_plan`` rows: [dst_rank, [src_rank, src_off, src_ld, dst_off, dst_ld, rows, cols]], the rectangles of
+        one destination in the order of that destination's plan.
+
+        Every group of point-to-point operations is matched by a group of the same composition on the other side:
+        a sender walks the destinations in rank order and sends each one's rectangles in chunks of ``batch``; a
+        receiver walks the sources in rank order and posts the receives of each in the same chunks. Groups of unequal
+        composition on the two sides (receives from several sources in one group against sends to one destination)
+        stalled on four GPUs."""
+        by_dst: Dict[int, List[Any]] = {}
         for dst_rank, d in send_plan:
-            t = self._view(flat, d[1], d[2], d[5], d[6]).contiguous()
-            if self.transfer_dtype is not None:
-                t = t.to(self.transfer_dtype)
-            keep.append(t)
-            ops.append(dist.P2POp(dist.isend, t, self.rmap[dst_rank], group=self.group))
-            if len(ops) >= self.batch:
+            by_dst.setdefault(dst_rank, []).append(d)
+        for dst_rank in sorted(by_dst):
+            rects = by_dst[dst_rank]
+            for i in range(0, len(rects), self.batch):
+                ops, keep = [], []
+                for d in rects[i:i + self.batch]:
+                    t = self._view(flat, d[1], d[2], d[5], d[6]).contiguous()
+                    if self.transfer_dtype is not None:
+                        t = t.to(self.transfer_dtype)
+                    keep.append(t)
+                    ops.append(dist.P2POp(dist.isend, t, self.rmap[dst_rank], group=self.group))
                 for w in dist.batch_isend_irecv(ops):
                     w.wait()
-                ops, keep = [], []
-        if ops:
-            for w in dist.batch_isend_irecv(ops):
-                w.wait()
 
     def recv(self, flat: torch.Tensor, recv_plan: List[List[int]]) -> None:
-        ops, pending = [], []
-
-        def flush():
-            nonlocal ops, pending
-            if ops:
+        by_src: Dict[int, List[List[int]]] = {}
+        for d in recv_plan:
+            by_src.setdefault(d[0], []).append(d)
+        dt = self.transfer_dtype or flat.dtype
+        for src in sorted(by_src):
+            rects = by_src[src]
+            for i in range(0, len(rects), self.batch):
+                chunk = rects[i:i + self.batch]
+                bufs = [torch.empty(d[5], d[6], dtype=dt, device=flat.device) for d in chunk]
+                ops = [dist.P2POp(dist.irecv, b, self.pmap[src], group=self.group) for b in bufs]
                 for w in dist.batch_isend_irecv(ops):
                     w.wait()
-                for buf, d in pending:
-                    self._view(flat, d[3], d[4], d[5], d[6]).copy_(buf)
-            ops, pending = [], []
-
-        for d in recv_plan:
-            dt = self.transfer_dtype or flat.dtype
-            buf = torch.empty(d[5], d[6], dtype=dt, device=flat.device)
-            pending.append((buf, d))
-            ops.append(dist.P2POp(dist.irecv, buf, self.pmap[d[0]], group=self.group))
-            if len(ops) >= self.batch:
-                flush()
-        flush()
+                for b, d in zip(bufs, chunk):
+                    self._view(flat, d[3], d[4], d[5], d[6]).copy_(b)

@@ -32,7 +32,8 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="qwen2.5-7b")
     ap.add_argument("--rollout-tp", type=int, nargs="+", default=[1, 2, 4])
-    ap.add_argument("--modes", nargs="+", default=["peer-bf16", "peer-fp8", "collective-fp32"])
+    ap.add_argument("--modes", nargs="+", default=["peer-bf16", "peer-fp8"],
+                    help="add collective-fp32 for the send / recv baseline")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     a = ap.parse_args(argv)
@@ -96,7 +97,7 @@ def main(argv=None) -> int:
             sync = fp8 = coll = None
             if not is_policy and mode.startswith("peer"):
                 fp8 = Fp8WeightStore(ro_flat) if mode == "peer-fp8" else None
-                sync = PeerWeightSync(ro_flat.data, plans[rank], ptrs, fp8=fp8)
+                sync = PeerWeightSync(ro_flat.data, plans[rank], ptrs, fp8=fp8, dst_rank=rank - P)
             if mode == "collective-fp32":
                 ident = {r: r for r in range(world)}
                 coll = CollectiveWeightSync(None, ident, ident, transfer_dtype=torch.float32)

@@ -171,7 +171,8 @@ class DisaggregatedRolloutControlWorker(CommMixin):
                 m = PeerMapping(info["ipc_handle"], info["nbytes"], self.device)
                 self._peer_maps.append(m)
                 ptrs[info["rank"]] = m.ptr
-            self.peer_sync = PeerWeightSync(self.rollout.flat.data, infos, ptrs, fp8=getattr(self.rollout, "fp8", None))
+            self.peer_sync = PeerWeightSync(self.rollout.flat.data, infos, ptrs, fp8=getattr(self.rollout, "fp8", None),
+                                          dst_rank=self.global_rank)
         self.peer_sync.pull()
         torch.cuda.synchronize()
         from ..ops import native

@@ -18,3 +18,14 @@ def test_two_gpu_peer_paths():
            "127.0.0.1", "--master-port", "29541", os.path.join(HERE, "mgpu_worker.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert r.returncode == 0 and "ALL OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_parameter_sharded_training():
+    """Units gathered by NCCL on a side stream while the previous unit computes; per-unit gradient reduce-scatter;
+    four optimizer steps equal the resident-weights trainer (cosmos_rl/policy/model/gpt/parallelize.py:366-423)."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29543", os.path.join(HERE, "mgpu_shard_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "SHARD OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

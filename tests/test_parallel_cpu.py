@@ -905,3 +905,50 @@ def _shard_params_worker(rank, world, store, out_dir, ckpt_mode):
 def test_parameter_sharded_training_matches_unsharded(tmp_path, ckpt_mode):
     """The reference shards parameters per block with FSDP2 (cosmos_rl/policy/model/gpt/parallelize.py:366-423)."""
     _spawn(_shard_params_worker, 2, tmp_path, str(tmp_path), ckpt_mode)
+
+
+def _collective_sync_worker(rank, world, store):
+    """Two policy ranks (data-parallel copies) and two rollout ranks (tensor parallel 2): the rectangles of the
+    resharding plan travel by grouped send / recv, every group matched by a group of the same composition on the other
+    side; the rollout ranks end up with exactly their tensor-parallel slices."""
+    import copy
+    from cosmos_rl_b200.models import hf_io
+    from cosmos_rl_b200.parallel.flat import FlatParams
+    from cosmos_rl_b200.parallel.reshard import build_plan, model_parts, shard_info
+    from cosmos_rl_b200.rollout.weight_sync import CollectiveWeightSync
+    _init(rank, world, store)
+    full = GPT(_tiny())
+    full.init_weights(4)
+    cfg = full.args.to_hf_config()
+    state = hf_io.hf_state_dict(full, cfg)
+    cpu = torch.device("cpu")
+    is_policy = rank < 2
+    a = copy.deepcopy(full.args)
+    if not is_policy:
+        a.tp_size, a.tp_rank = 2, rank - 2
+    m = GPT(a)
+    hf_io.load_hf_state(m, lambda k: state[k], state, cfg, a.tp_size, a.tp_rank)
+    flat = FlatParams(m, torch.float32, cpu, with_grad=False)
+    want = flat.data.clone()
+    if not is_policy:
+        flat.data.zero_()
+    infos = [None] * world
+    dist.all_gather_object(infos, {"policy": is_policy, "info": shard_info(rank, model_parts(m, flat), flat.total)})
+    pol = [e["info"] for e in infos if e["policy"]]
+    plans = {r: build_plan(pol, infos[r]["info"]) for r in (2, 3)}
+    assert {d[0] for pl in plans.values() for d in pl} == {0, 1}          # both copies serve rectangles
+    ident = {r: r for r in range(world)}
+    coll = CollectiveWeightSync(None, ident, ident, batch=7)              # several chunks per pair
+    if is_policy:
+        coll.send(flat.data, [[r, d] for r, pl in sorted(plans.items()) for d in pl if d[0] == rank])
+    else:
+        coll.recv(flat.data, plans[rank])
+        for name, p in m.named_parameters():
+            ref = torch.as_strided(want, p.shape, p.stride(), p.storage_offset())
+            assert torch.equal(p.data, ref), name
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_collective_weight_sync_between_two_policy_and_two_rollout_ranks(tmp_path):
+    _spawn(_collective_sync_worker, 4, tmp_path)

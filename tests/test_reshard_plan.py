@@ -116,3 +116,21 @@ def test_plan_gathers_expert_parallel_shards(family):
     E = base.n_experts
     late = next(p for p in model_parts(dst, dflat) if f"experts.{E - 1}." in p.key)
     assert any(d[0] == 1 and d[3] <= late.off < d[3] + d[4] * d[5] for d in plan)
+
+
+def test_interleave_sources_mixes_sources_and_staggers_destinations():
+    """A plan sorted by source becomes one that draws on all sources at every point; the destination's rank picks the
+    source it starts on; nothing is dropped or duplicated."""
+    from cosmos_rl_b200.parallel.reshard import interleave_sources
+    plan = [[0, i * 100, 10, i * 100, 10, 10, 10] for i in range(6)] + [[1, i * 100, 10, 600 + i * 100, 10, 10, 10] for i in range(3)] \
+        + [[1, 900, 10, 900, 10, 30, 10]]
+    out0, out1 = interleave_sources(plan, 0), interleave_sources(plan, 1)
+    assert sorted(map(tuple, out0)) == sorted(map(tuple, plan)) == sorted(map(tuple, out1))
+    assert out0[0][0] == 0 and out1[0][0] == 1
+    half = out0[:len(out0) // 2]
+    assert {d[0] for d in half} == {0, 1}                    # both sources appear in the first half
+    by = {0: 0, 1: 0}
+    for d in half:
+        by[d[0]] += d[5] * d[6]
+    assert abs(by[0] / 600 - by[1] / 600) < 0.5              # and about the same fraction of each has been scheduled
+    assert interleave_sources(plan[:6], 3) == plan[:6]       # a single source: order kept
