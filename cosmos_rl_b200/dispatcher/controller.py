@@ -22,6 +22,7 @@ from ..utils.logging import logger
 from ..utils.report import build_report_hooks
 from . import command as cmd
 from .data import ControllerDataFetcher, CosmosDataset
+from ..utils.payload_transport import PayloadTransportRegistry
 from .data.schema import RLPayload, Rollout, payload_to_rollouts
 from .protocol import RegisterRequest, Role
 from .replica import Atom
@@ -33,6 +34,11 @@ class Controller:
                  sampler=None, custom_logger_fns: Optional[List[Callable]] = None):
         self.config = config
         self.broker = broker or InProcessBroker()
+        from ..utils.payload_transport import PayloadTransportRegistry, get_payload_transfer_mode
+        if get_payload_transfer_mode(config) != "broker":
+            # the controller only ever releases parked payloads of rollouts it discards
+            PayloadTransportRegistry.get(get_payload_transfer_mode(config)).setup(config, self.broker, None,
+                                                                                 owner="controller")
         self.is_rl = config.train.train_policy.type == "grpo"
         ds = CosmosDataset.wrap(dataset, config)
         vds = CosmosDataset.wrap(val_dataset, config)
@@ -258,6 +264,8 @@ class Controller:
                 # DAPO-style dynamic sampling: the whole group is dropped
                 discarded += n_gen
                 self.stat_invalid += 1
+                if p.payload_refs:
+                    PayloadTransportRegistry.handle_discarded(p.payload_refs)
                 continue
             rs = payload_to_rollouts(p)
             discarded += max(0, n_gen - len(rs))
@@ -265,6 +273,8 @@ class Controller:
             self.rollout_status_manager.note_adopted_version(src_replica_name, p.weight_version)
             if p.completion_token_ids:
                 self.stat_completion_tokens += sum(len(c) for c in p.completion_token_ids)
+            elif p.payload_refs and p.extra_info:
+                self.stat_completion_tokens += sum(p.extra_info.get("completion_lengths", []))
         self.stat_samples += len(rollouts)
         if is_end:
             self.rollout_status_manager.mark_ended(src_replica_name)

@@ -35,6 +35,8 @@ class RLPayload(BaseModel):
     extra_info: Optional[Dict[str, Any]] = None
     report_metrics: Optional[List[Dict[str, Any]]] = None
     teacher_result_uuids: Optional[List[str]] = None
+    payload_refs: Optional[List[str]] = None        # per completion: reference to token ids + log-probs parked with a
+                                                    # payload transport (they then do not travel in this message)
 
     @staticmethod
     def collate_fn(batch: List["IdxAndRLPayload"]):
@@ -66,6 +68,7 @@ class Rollout(BaseModel):
     extra_info: Optional[Dict[str, Any]] = None
     weight_version: int = 0
     report_metrics: Optional[Dict[str, Any]] = None
+    payload_ref: str = ""
 
 
 def payload_to_rollouts(p: RLPayload) -> List[Rollout]:
@@ -87,5 +90,6 @@ def payload_to_rollouts(p: RLPayload) -> List[Rollout]:
             weight_version=p.weight_version,
             report_metrics=(p.report_metrics[i] if p.report_metrics else None),
             teacher_result_uuid=(p.teacher_result_uuids[i] if p.teacher_result_uuids else ""),
+            payload_ref=(p.payload_refs[i] if p.payload_refs else ""),
         ))
     return out

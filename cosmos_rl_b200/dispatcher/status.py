@@ -273,14 +273,24 @@ class PolicyStatusManager(_ManagerBase):
         allowed = tp.allowed_outdated_steps
         gb = max(self.global_batch, 1)
         kept = []
+        dropped_refs: List[str] = []
         pending = len(self.rollout_buffer)
         for i, r in enumerate(rollouts):
             consume_step = self.current_step + 1 + (pending + len(kept)) // gb
             if rollout_is_outdated(consume_step=consume_step, weight_version=r.weight_version,
                                    allowed_outdated_steps=allowed):
                 self.filtered_outdated += 1
+                if r.payload_ref:
+                    dropped_refs.append(r.payload_ref)
                 continue
             kept.append(r)
+        if dropped_refs:
+            # producers free the parked tensors of rollouts that will never be trained
+            from ..utils.payload_transport import PayloadTransportRegistry
+            try:
+                PayloadTransportRegistry.handle_discarded(dropped_refs)
+            except Exception as e:
+                logger.warning("[Controller] releasing %d discarded payloads failed: %s", len(dropped_refs), e)
         return kept
 
     def put_rollouts(self, rollouts: List[Rollout], n_discarded: int = 0) -> None:

@@ -165,7 +165,8 @@ class DynComm:
         self.timeout_s = timeout_s if timeout_s is not None else constant.COSMOS_NCCL_TIMEOUT_MS / 1000.0
         self.store = store
         self.aborted = False
-        td = timedelta(seconds=self.timeout_s)
+        # the constructor's timeout also bounds the rendezvous through the store; operations carry their own deadline
+        td = timedelta(seconds=max(self.timeout_s, 30.0))
         prefix = dist.PrefixStore(f"dyncomm/{name}", store)
         if device.type == "cuda":
             opts = dist.ProcessGroupNCCL.Options()

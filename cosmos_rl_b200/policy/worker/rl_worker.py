@@ -106,6 +106,18 @@ class RLPolicyWorker(CommMixin):
             except (ValueError, OSError):
                 pass
 
+    def _payload_prefetcher(self):
+        if not hasattr(self, "_payload_pf"):
+            from ...utils.payload_transport import (PayloadPrefetcher, PayloadTransportRegistry,
+                                                    get_payload_transfer_mode)
+            mode = get_payload_transfer_mode(self.config)
+            self._payload_pf = None
+            if mode != "broker":
+                tx = type(PayloadTransportRegistry.get(mode))()
+                tx.setup(self.config, self.broker, self.device, owner=f"{self.replica_name[:12]}-p{self.global_rank}")
+                self._payload_pf = PayloadPrefetcher(tx)
+        return self._payload_pf
+
     # ------------------------------------------------------------------ shard infos for weight sync
     def _sync_buffer(self) -> torch.Tensor:
         fn = getattr(self.trainer, "sync_buffer", None)
@@ -276,7 +288,10 @@ class RLPolicyWorker(CommMixin):
                     continue
                 for mid, data in msgs:
                     self._last_rollout_id = mid
-                    self.data_queue.put(Rollout.model_validate_json(data))
+                    r = Rollout.model_validate_json(data)
+                    if r.payload_ref and self._payload_prefetcher() is not None:
+                        self._payload_pf.prefetch([r.payload_ref])      # resolved in the background before the step
+                    self.data_queue.put(r)
 
         t = threading.Thread(target=loop, name="fetch_rollouts", daemon=True)
         t.start()
@@ -294,7 +309,15 @@ class RLPolicyWorker(CommMixin):
                     got.append(self.data_queue.get(timeout=1.0))
                 except queue.Empty:
                     continue
+            n_ref = sum(1 for r in got if r.payload_ref)
+            if n_ref:
+                logger.info("[Policy] fetching the per-token data of %d rollouts through the payload transport", n_ref)
             for r in got:
+                if r.payload_ref:
+                    from ...utils.payload_transport import restore_rollout
+                    if self._payload_prefetcher() is None or not restore_rollout(self._payload_pf, r):
+                        logger.warning("[Policy] payload %s could not be fetched: the rollout trains from its text",
+                                       r.payload_ref[:48])
                 if r.prompt is None:
                     self.data_fetcher.fill(r)
                 if self.config.distillation.enable and r.teacher_result_uuid and r.teacher_logprobs is None:

@@ -270,9 +270,27 @@ class DisaggregatedRolloutControlWorker(CommMixin):
         done = self.reward_dispatcher.dequeue(block=block and not self.reward_dispatcher.is_empty())
         if self.global_rank != 0:
             return
+        if done and self._payload_transport() is not None:
+            from ..utils.payload_transport import park_payload
+            for p in done:
+                park_payload(self._payload_tx, p, self.device if self.device.type == "cuda" else None)
         if done or is_end:
             self.api.post_rollout_completion(self.replica_name, done, is_end=is_end,
                                              metrics={"generated_tokens": self.stats["generated_tokens"]})
+
+    def _payload_transport(self):
+        """The transport per-token data of finished rollouts is parked with (``[custom] payload_transfer``); None for
+        the inline default."""
+        if not hasattr(self, "_payload_tx"):
+            from ..utils.payload_transport import PayloadTransportRegistry, get_payload_transfer_mode
+            mode = get_payload_transfer_mode(self.config)
+            self._payload_tx = None
+            if mode != "broker":
+                tx = type(PayloadTransportRegistry.get(mode))()          # an instance of this worker's own
+                tx.setup(self.config, self.broker, self.device, owner=f"{self.replica_name[:12]}-r{self.global_rank}")
+                self._payload_tx = tx
+                logger.info("[Rollout] per-token data of rollouts travels by the %r payload transport", mode)
+        return self._payload_tx
 
     # ------------------------------------------------------------------ generation
     def one_step_generation(self) -> None:

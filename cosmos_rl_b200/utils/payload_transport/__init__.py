@@ -8,7 +8,8 @@ single fetch on a miss, and the controller tells the producer to release resourc
 
 Shipped transports: ``broker`` (inline), ``kv`` (tensors parked in the controller key/value store; works on any
 machine), ``peer`` (tensors parked in a peer-visible device ring on the rollout GPU and pulled over NVLink by
-the policy rank with plain peer loads; same box only).
+the policy rank with plain peer loads; same box only), ``nccl`` (two-rank communicators between producer and
+consumer with a request / answer handshake over the broker, ``pair.py``).
 """
 from __future__ import annotations
 
@@ -217,7 +218,8 @@ class PayloadTransportRegistry:
     @classmethod
     def reset(cls) -> None:
         cls._by_name = {}
-        for c in (BrokerTransport, KVTransport, PeerTransport):
+        from .pair import PairTransport
+        for c in (BrokerTransport, KVTransport, PeerTransport, PairTransport):
             cls.register_class(c)
 
 
@@ -225,7 +227,10 @@ PayloadTransportRegistry.reset()
 
 
 def get_payload_transfer_mode(config) -> str:
-    mode = (getattr(config, "custom", None) or {}).get("payload_transfer", "broker")
+    custom = getattr(config, "custom", None) or {}
+    mode = custom.get("payload_transfer", "broker")
+    if mode in ("redis", "", None, "broker") and custom.get("nccl_payload_transfer"):
+        return "nccl"                               # the older boolean switch of the reference
     return "broker" if mode in ("redis", "", None) else mode
 
 
@@ -299,3 +304,51 @@ class PayloadPrefetcher:
         self.stop_flag.set()
         self.wake.set()
         self.thread.join(timeout=2)
+
+
+# ---------------------------------------------------------------------------------------------------
+# token ids + log-probs of a completion as one tensor (what the LLM workers park with a transport)
+# ---------------------------------------------------------------------------------------------------
+def pack_completion(token_ids: List[List[int]], logprobs: Optional[List[List[float]]], device=None) -> torch.Tensor:
+    """``[2, n, k]`` float32: plane 0 the ids (exact below 2**24), plane 1 the log-probs (zeros when absent)."""
+    ids = torch.tensor(token_ids, dtype=torch.float32)
+    lps = torch.tensor(logprobs, dtype=torch.float32) if logprobs else torch.zeros_like(ids)
+    out = torch.stack([ids, lps])
+    return out.to(device) if device is not None else out
+
+
+def unpack_completion(t: torch.Tensor, with_logprobs: bool = True):
+    t = t.detach().to("cpu")
+    ids = t[0].to(torch.int64).tolist()
+    return ids, (t[1].tolist() if with_logprobs else None)
+
+
+def park_payload(transport: PayloadTransport, payload, device=None) -> int:
+    """Producer side: move the per-token data of every completion of ``payload`` (an ``RLPayload``) out of the
+    message. Returns the number of completions parked."""
+    if transport.completion_prefix is None or not payload.completion_token_ids:
+        return 0
+    refs = []
+    for i, ids in enumerate(payload.completion_token_ids):
+        lps = payload.completion_logprobs[i] if payload.completion_logprobs else None
+        refs.append(transport.publish(pack_completion(ids, lps, device)))
+    payload.payload_refs = refs
+    payload.extra_info = dict(payload.extra_info or {}, payload_has_logprobs=bool(payload.completion_logprobs),
+                              completion_lengths=[len(x) for x in payload.completion_token_ids])
+    payload.completion_token_ids = None
+    payload.completion_logprobs = None
+    return len(refs)
+
+
+def restore_rollout(prefetcher: "PayloadPrefetcher", rollout) -> bool:
+    """Consumer side: put the per-token data back into ``rollout``. False when the payload could not be fetched (the
+    rollout then trains from its text, or is skipped by the caller)."""
+    if not rollout.payload_ref:
+        return True
+    t = prefetcher.resolve(rollout.payload_ref)
+    if t is None or isinstance(t, str):
+        return False
+    has_lp = bool((rollout.extra_info or {}).get("payload_has_logprobs", True))
+    rollout.completion_token_ids, rollout.completion_logprobs = unpack_completion(t, has_lp)
+    rollout.payload_ref = ""
+    return True

@@ -469,3 +469,89 @@ def test_grouped_reward_calculation_calls_each_function_once_per_prompt():
     p = calc.compute(RLPayload(prompt=[1], prompt_idx=0, completions=toks,
                                completion_token_ids=[[[t] for t in tl] for tl in toks]))
     assert calls == [3] and p.rewards == [1.0, 0.0, 1.0] and abs(sum(p.advantages)) < 1e-5
+
+
+def test_pair_payload_transport_registry_cache_and_transfers():
+    """Producer and consumer ends of the two-rank transport in one process (gloo communicators, in-process broker):
+    a parked tensor is fetched by reference and freed on the producer; a recycled buffer answers MISSING; a producer
+    that does not answer costs ``max_attempts`` receive budgets and is quarantined; the registry blocks then evicts the
+    oldest buffer; the communicator cache keeps at most ``max_live`` pairs and quarantines failed ones."""
+    import time
+    import torch
+    from cosmos_rl_b200.comm.broker import InProcessBroker
+    from cosmos_rl_b200.utils.payload_transport import PayloadTransportRegistry, get_payload_transfer_mode
+    from cosmos_rl_b200.utils.payload_transport.pair import (PairCommCache, PairTransport, SendBufferRegistry, parse_ref)
+    # registry: bounded, idempotent, protects buffers that are being sent
+    reg = SendBufferRegistry(capacity=2, block_s=0.05)
+    reg.register("a", torch.zeros(1))
+    reg.register("a", torch.ones(1))
+    reg.register("b", torch.zeros(1))
+    assert len(reg) == 2 and reg.acquire("a")[0].item() == 0.0
+    t0 = time.time()
+    reg.register("c", torch.zeros(1))                       # full: waits, then evicts the oldest idle buffer ("b")
+    assert time.time() - t0 >= 0.04 and "b" not in reg and "a" in reg and reg.evicted == 1
+    assert not reg.free("a")                                # in flight
+    reg.release("a")
+    assert reg.free("a") and not reg.free("a") and reg.acquire("a") is None
+    # communicator cache: LRU cap, quarantine, generations
+    class FakeComm:
+        def __init__(self, key, gen):
+            self.key, self.gen, self.aborted = key, gen, False
+        def abort(self):
+            self.aborted = True
+    now = [0.0]
+    cache = PairCommCache(lambda k, g: FakeComm(k, g), max_live=2, cooldown_s=10.0, clock=lambda: now[0])
+    c1, c2 = cache.get("p1"), cache.get("p2")
+    assert cache.get("p1") is c1
+    c3 = cache.get("p3")
+    assert c2.aborted and not c1.aborted and len(cache) == 2 and cache.evicted == 1
+    cache.fail("p1")
+    assert c1.aborted and cache.get("p1") is None           # quarantined
+    now[0] = 11.0
+    assert cache.get("p1").gen == 1                         # rebuilt under a new name after the cool-down
+    cache.set_generation("p3", 5)
+    assert c3.aborted and cache.get("p3").gen == 5
+    # end to end
+    broker = InProcessBroker()
+    prod, cons = PairTransport(), PairTransport()
+    prod.setup(broker=broker, device=torch.device("cpu"), owner="rollout-0", recv_timeout_s=3.0)
+    cons.setup(broker=broker, device=torch.device("cpu"), owner="policy-0", recv_timeout_s=3.0, max_attempts=2)
+    try:
+        x = torch.arange(24, dtype=torch.float32).view(2, 12)
+        ref = prod.publish(x)
+        assert cons.should_intercept(ref) and parse_ref(cons.cache_key(ref))[0] == "rollout-0"
+        got = cons.sync_fetch(ref)
+        assert torch.equal(got, x) and prod.stats["sent"] == 1 and cons.stats["received"] == 1
+        y = torch.randn(5)
+        assert torch.equal(cons.sync_fetch(prod.publish(y)), y)         # the pair's communicator is reused
+        assert prod.cache.built == 1 and cons.cache.built == 1
+        for _ in range(100):
+            if len(prod.registry) == 0:
+                break
+            time.sleep(0.02)
+        assert len(prod.registry) == 0                                  # the consumer's cleanup freed both buffers
+        assert cons.sync_fetch(ref) is None and cons.stats["missing"] == 1   # recycled buffer: episode dropped
+        # discarded rollouts: the controller's release reaches the producer
+        ref3 = prod.publish(torch.ones(3))
+        assert len(prod.registry) == 1
+        assert cons.release([cons.cache_key(ref3)]) == 1
+        for _ in range(100):
+            if len(prod.registry) == 0:
+                break
+            time.sleep(0.02)
+        assert len(prod.registry) == 0
+        # a producer that never answers
+        cons.recv_timeout_s = 0.2
+        t0 = time.time()
+        ghost = "nccl:rollout-9/1-deadbeef/float32/4"
+        assert cons.sync_fetch(ghost) is None
+        assert 0.35 < time.time() - t0 < 3.0 and cons.stats["cancelled"] == 2
+        t0 = time.time()
+        assert cons.sync_fetch(ghost) is None and time.time() - t0 < 0.1      # quarantined endpoint: skipped at once
+    finally:
+        prod.shutdown()
+        cons.shutdown()
+    assert PayloadTransportRegistry.get("nccl").completion_prefix == "nccl:"
+    class C:
+        custom = {"nccl_payload_transfer": True}
+    assert get_payload_transfer_mode(C) == "nccl"

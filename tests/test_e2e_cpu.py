@@ -142,3 +142,30 @@ def test_tiny_grpo_job_with_async_rollout_scheduler(tmp_path):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:] + detail
     assert "training finished at step 2" in logs["controller.log"], detail
     assert "async scheduler" in logs["rollout_0.log"], detail
+
+
+@pytest.mark.timeout(420)
+def test_tiny_grpo_job_with_pair_payload_transport(tmp_path):
+    """``[custom] payload_transfer = "nccl"``: token ids and log-probs of finished rollouts stay on the rollout worker
+    and reach the policy over a two-rank communicator (gloo here) after a request / answer handshake through the
+    controller's broker; the job trains to completion from the fetched data."""
+    from cosmos_rl_b200.config import dump_toml, load_toml
+    raw = load_toml(os.path.join(HERE, "configs", "tiny_grpo_cpu.toml"))
+    raw["custom"] = {"payload_transfer": "nccl"}
+    raw["train"]["output_dir"] = str(tmp_path / "out")
+    cfg = tmp_path / "job.toml"
+    cfg.write_text(dump_toml(raw))
+    log_dir = tmp_path / "logs"
+    env = dict(os.environ, COSMOS_LOG_LEVEL="INFO", COSMOS_HEARTBEAT_SEND_INTERVAL="2", PYTHONPATH=ROOT,
+               OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "cosmos_rl_b200.launcher.launch_all", "--config", str(cfg), "--policy", "1",
+           "--rollout", "1", "--cpu", "--log-dir", str(log_dir), os.path.join(HERE, "e2e_script.py")]
+    r = _run_job(cmd, env, 400)
+    latest = log_dir / "logs_latest"
+    logs = {f: open(latest / f).read() for f in sorted(os.listdir(latest))}
+    detail = "\n".join(f"==== {k}\n{v[-2500:]}" for k, v in logs.items())
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:] + detail
+    assert "training finished at step 2" in logs["controller.log"], detail
+    assert "'nccl' payload transport" in logs["rollout_0.log"], detail
+    assert "through the payload transport" in logs["policy_0.log"], detail
+    assert "could not be fetched" not in logs["policy_0.log"], detail
