@@ -394,6 +394,7 @@ class DisaggregatedRolloutControlWorker(CommMixin):
             logger.info("[Rollout] async scheduler: %d payloads in %d engine calls, %.1f s generating, %d errors",
                         st["tasks"], st["batches"], st["busy_s"], st["errors"])
             self.report_rollouts(block=True, is_end=True)
+            self._serve_parked_payloads()
             self.handle_shutdown()
             return
         while not self.shutdown_signal.is_set():
@@ -419,9 +420,26 @@ class DisaggregatedRolloutControlWorker(CommMixin):
             self.report_rollouts()
         # drain: finish rewards, report the end of this replica's stream
         self.report_rollouts(block=True, is_end=True)
+        self._serve_parked_payloads()
         self.handle_shutdown()
 
     work = main_loop
+
+    def _serve_parked_payloads(self) -> None:
+        """With a pull-based payload transport the per-token data of reported rollouts still sits on this worker:
+        keep answering fetches (and commands) until every parked buffer was fetched or released, the controller stops
+        the replica, or ``[custom] payload_drain_timeout`` seconds have passed."""
+        tx = getattr(self, "_payload_tx", None)
+        reg = getattr(tx, "registry", None)
+        if reg is None or self.stopped:
+            return
+        limit = float((self.config.custom or {}).get("payload_drain_timeout", 600.0))
+        t0 = time.time()
+        while len(reg) and time.time() - t0 < limit and not self.shutdown_signal.is_set():
+            if self.consume_commands(block=0.05) or self.stopped:
+                break
+        if len(reg):
+            logger.warning("[Rollout] leaving with %d parked payloads that nobody fetched", len(reg))
 
     def handle_shutdown(self) -> None:
         if getattr(self, "_shut", False):
@@ -436,4 +454,6 @@ class DisaggregatedRolloutControlWorker(CommMixin):
             self.r2r_comm.abort()
         for m in getattr(self, "_peer_maps", []):
             m.close()
+        if getattr(self, "_payload_tx", None) is not None:
+            self._payload_tx.shutdown()
         self.unregister_from_controller()

@@ -235,13 +235,18 @@ def get_payload_transfer_mode(config) -> str:
 
 
 class PayloadPrefetcher:
-    """Resolves references of upcoming rollouts on a background thread; ``resolve`` serves from the cache and
-    falls back to one blocking fetch."""
+    """Resolves references of upcoming rollouts on a background thread; ``resolve`` serves from the cache, waits for a
+    reference the thread is still working on (at most ``prefetch_timeout_s``; a second fetch of the same transfer
+    would find its buffer already handed out) and falls back to one blocking fetch for references it never saw."""
 
-    def __init__(self, transport: PayloadTransport, max_cached: int = 4096):
+    def __init__(self, transport: PayloadTransport, max_cached: int = 4096, prefetch_timeout_s: Optional[float] = None):
         self.t, self.max_cached = transport, max_cached
+        custom = (getattr(getattr(transport, "config", None), "custom", None) or {})
+        self.prefetch_timeout_s = float(prefetch_timeout_s if prefetch_timeout_s is not None
+                                        else custom.get("nccl_prefetch_timeout", 30.0))
         self.cache: Dict[str, Any] = {}
-        self.lock = threading.Lock()
+        self.inflight: set = set()
+        self.lock = threading.Condition()
         self.pending: List[List[str]] = []
         self.wake = threading.Event()
         self.stop_flag = threading.Event()
@@ -254,6 +259,7 @@ class PayloadPrefetcher:
         if refs:
             with self.lock:
                 self.pending.append(refs)
+                self.inflight.update(self.t.cache_key(r) for r in refs)
             self.wake.set()
         return len(refs)
 
@@ -266,26 +272,40 @@ class PayloadPrefetcher:
                     refs = self.pending.pop(0) if self.pending else None
                 if refs is None:
                     break
-                try:
-                    got = self.t.fetch_batch(refs)
-                except Exception as e:
-                    logger.warning("[payload] prefetch batch failed: %s", e)
-                    got = {}
-                with self.lock:
-                    self.cache.update(got)
-                    while len(self.cache) > self.max_cached:
-                        self.cache.pop(next(iter(self.cache)))
+                for r in refs:                      # one by one, so that a waiting ``resolve`` is served early
+                    try:
+                        got = self.t.fetch_batch([r])
+                    except Exception as e:
+                        logger.warning("[payload] prefetch of %s failed: %s", r, e)
+                        got = {}
+                    with self.lock:
+                        self.cache.update(got)
+                        self.inflight.discard(self.t.cache_key(r))
+                        while len(self.cache) > self.max_cached:
+                            self.cache.pop(next(iter(self.cache)))
+                        self.lock.notify_all()
 
     def resolve(self, completion: Any) -> Any:
         if not self.t.should_intercept(completion):
             return completion
         key = self.t.cache_key(completion)
+        seen = False
         with self.lock:
+            end = time.monotonic() + self.prefetch_timeout_s
+            while key in self.inflight and key not in self.cache:
+                seen = True
+                left = end - time.monotonic()
+                if left <= 0:
+                    break
+                self.lock.wait(left)
             v = self.cache.pop(key, None)
         if v is not None:
             self.hits += 1
             return v
         self.misses += 1
+        if seen:                                     # the prefetch thread tried and failed (or ran out of time)
+            self.failed += 1
+            return None
         v = self.t.sync_fetch(completion)
         if v is None:
             self.failed += 1
