@@ -138,6 +138,12 @@ class ParallelDims:
                 g = dist.new_group([base[m] for m in members], backend=backend)
                 if me in [base[m] for m in members]:
                     self._groups[axis] = g
+                if axis == "pp":
+                    # a second communicator over the same ranks: gradients between pipeline stages travel on it, so
+                    # that activations and gradients between two ranks never share one communicator's message order
+                    g2 = dist.new_group([base[m] for m in members], backend=backend)
+                    if me in [base[m] for m in members]:
+                        self._groups["pp_back"] = g2
         if self.world_size > 1:
             g = dist.new_group(base, backend=backend)
             if me in base:

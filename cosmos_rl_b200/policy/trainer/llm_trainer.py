@@ -144,7 +144,8 @@ class LLMTrainer(Trainer):
             from ...parallel.pipeline import PipelineStage
             self.pipeline = PipelineStage(model, parallel_dims.group("pp"), parallel_dims.pp_coord, parallel_dims.pp,
                                           model.args.dim, self.param_dtype, self.device,
-                                          schedule=config.policy.parallelism.pp_schedule)
+                                          schedule=config.policy.parallelism.pp_schedule,
+                                          back_group=parallel_dims.group("pp_back"))
         from ...utils.extension import parallelism_strategy
         custom_plan = parallelism_strategy(mt)
         if custom_plan is not None:

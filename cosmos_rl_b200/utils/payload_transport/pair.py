@@ -63,6 +63,7 @@ class SendBufferRegistry:
         self.capacity, self.block_s = capacity, block_s
         self._items: "OrderedDict[str, Tuple[torch.Tensor, Any]]" = OrderedDict()
         self._busy: set = set()
+        self._doomed: set = set()              # freed while a send was in flight: dropped when the send releases it
         self._cv = threading.Condition()
         self.evicted = self.freed = self.registered = 0
 
@@ -95,11 +96,15 @@ class SendBufferRegistry:
     def release(self, tid: str) -> None:
         with self._cv:
             self._busy.discard(tid)
+            if tid in self._doomed:
+                self._doomed.discard(tid)
+                self.freed += int(self._items.pop(tid, None) is not None)
             self._cv.notify_all()
 
     def free(self, tid: str) -> bool:
         with self._cv:
-            if tid in self._busy:                 # a send is in flight: it is freed by the sender afterwards
+            if tid in self._busy:                 # a send is in flight: ``release`` drops the buffer afterwards
+                self._doomed.add(tid)
                 return False
             gone = self._items.pop(tid, None) is not None
             self.freed += int(gone)

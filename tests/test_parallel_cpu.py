@@ -123,6 +123,98 @@ def test_pipeline_1f1b_matches_full_model(tmp_path):
     _spawn(_pp_worker, 2, tmp_path)
 
 
+def _pp_interleaved_worker(rank, world, store):
+    """Two ranks, two model chunks each (virtual stages 0..3 of a four-block model), five micro-batches (a short
+    last group): losses and gradients of the interleaved schedule equal the unsplit model; the forward-only pass
+    returns its results in micro-batch order."""
+    import copy
+    from cosmos_rl_b200.parallel.pipeline import MicroBatch, PipelineStage
+    _init(rank, world, store)
+    base = _tiny()
+    base.n_layers = 4
+    full = GPT(base)
+    full.init_weights(0)
+    sd = full.state_dict()
+    chunks = []
+    for c in range(2):
+        a = copy.deepcopy(full.args)
+        a.pp_size, a.pp_rank = 2 * world, c * world + rank
+        m = GPT(a)
+        with torch.no_grad():
+            for name, p in m.named_parameters():
+                src = name
+                if name.startswith("layers."):
+                    idx, rest = name[len("layers."):].split(".", 1)
+                    src = f"layers.{int(idx) + m.layer_offset}.{rest}"
+                p.copy_(sd[src])
+        chunks.append(m)
+    g = torch.Generator().manual_seed(3)
+    mbs, ref_loss = [], 0.0
+    for lens in ([5, 9], [12], [3, 3, 4], [7], [2, 6]):
+        T = sum(lens)
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)))
+        ids = torch.randint(0, 512, (T,), generator=g)
+        labels = torch.randint(0, 512, (T,), generator=g)
+        mbs.append(MicroBatch(ids, full.get_position_ids(cu, T), cu, max(lens), labels))
+
+    def loss_fn(model):
+        return lambda hidden, mb: -model.logprobs(hidden, mb.extra)[0].mean() / len(mbs)
+
+    per_mb = []
+    for mb in mbs:
+        l = loss_fn(full)(full(mb.input_ids, mb.position_ids, mb.cu_seqlens, mb.max_seqlen), mb)
+        l.backward()
+        per_mb.append(l.item())
+    ref = {n: p.grad for n, p in full.named_parameters()}
+    back = dist.new_group(list(range(world)))
+    runner = PipelineStage(chunks, dist.group.WORLD, rank, world, base.dim, torch.float32, torch.device("cpu"),
+                           schedule="Interleaved1F1B", back_group=back)
+    head = chunks[-1]
+    losses = runner.run(mbs, loss_fn(head))
+    if rank == world - 1:
+        assert abs(sum(x.item() for x in losses) - sum(per_mb)) < 1e-5
+    else:
+        assert losses == []
+    for m in chunks:
+        for name, p in m.named_parameters():
+            src = name
+            if name.startswith("layers."):
+                idx, rest = name[len("layers."):].split(".", 1)
+                src = f"layers.{int(idx) + m.layer_offset}.{rest}"
+            assert torch.allclose(p.grad, ref[src], atol=1e-5), (name, (p.grad - ref[src]).abs().max())
+    outs = runner.forward_only(mbs, lambda h, mb: loss_fn(head)(h, mb).item())
+    if rank == world - 1:
+        assert all(abs(a - b) < 1e-5 for a, b in zip(outs, per_mb)), (outs, per_mb)
+    dist.destroy_process_group()
+
+
+def test_pipeline_interleaved_1f1b_matches_full_model(tmp_path):
+    """Several stages per rank (cosmos_rl/utils/pipelining/pipelining_utils.py:170-260)."""
+    _spawn(_pp_interleaved_worker, 2, tmp_path)
+
+
+def test_interleaved_schedule_properties():
+    """Every (micro-batch, chunk) runs forward once and backward once, forward first; the schedule completes for
+    awkward micro-batch counts; the bubble shrinks with the number of chunks."""
+    from cosmos_rl_b200.parallel.pipeline import schedule_interleaved_1f1b, simulate_schedule
+    for P, V, M in ((2, 2, 5), (4, 3, 5), (4, 2, 8), (5, 4, 12), (3, 1, 7)):
+        for s in range(P):
+            steps = schedule_interleaved_1f1b(s, P, M, V)
+            seen = set()
+            for kind, i, c in steps:
+                if kind == "F":
+                    assert (i, c) not in seen
+                    seen.add((i, c))
+                else:
+                    assert (i, c) in seen
+            assert len(steps) == 2 * M * V and len(seen) == M * V
+        simulate_schedule(lambda r: schedule_interleaved_1f1b(r, P, M, V), P, M, V)       # raises on a deadlock
+    b1 = simulate_schedule(lambda r: schedule_interleaved_1f1b(r, 4, 8, 1), 4, 8, 1)["bubble"]
+    b2 = simulate_schedule(lambda r: schedule_interleaved_1f1b(r, 4, 8, 2), 4, 8, 2)["bubble"]
+    b4 = simulate_schedule(lambda r: schedule_interleaved_1f1b(r, 4, 8, 4), 4, 8, 4)["bubble"]
+    assert b1 > b2 > b4 and b1 > 0.25 and b4 < 0.1, (b1, b2, b4)
+
+
 def _failure_worker(rank, world, store_path):
     """Host-side failure injection: rank 1 leaves between two steps (no collective in flight); rank 0's next
     collective ends with CommTimeout within its limit, the communicator is aborted and a smaller one is built."""
