@@ -161,9 +161,18 @@ class Attention(nn.Module):
         """x [T, H] -> q [T, hq, d], k, v [T, hkv, d] with RoPE (and per-head q/k norm) applied."""
         return self.split_qkv(_linear(x, self.qkv_proj.weight, self.qkv_proj.bias), positions)
 
+    mrope_section = None    # rotary frequencies per position stream (time, height, width) of multimodal models
+
     def split_qkv(self, qkv: torch.Tensor, positions: torch.Tensor):
         T = qkv.shape[0]
         hq, hkv, d = self.hq, self.hkv, self.d
+        if positions.dim() == 2:
+            # multimodal rotary positions [3, T]: every frequency follows the stream of its section
+            from .qwen2_5_vl import apply_rotary, mrope_cos_sin
+            q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
+            cos, sin = mrope_cos_sin(positions, d, self.theta, self.mrope_section or [d // 2])
+            q, k = apply_rotary(q.reshape(T, hq, d), k.reshape(T, hkv, d), cos, sin)
+            return q.contiguous(), k.contiguous(), v.reshape(T, hkv, d)
         if self.qk_norm:
             q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
             qw, kw = self.q_norm, self.k_norm

@@ -181,6 +181,8 @@ def hf_state_dict(model, hf_config: Dict[str, Any]) -> Dict[str, torch.Tensor]:
 
 def _split_fused(name: str, t: torch.Tensor, mapper, cfg, hq: int, hkv: int, d: int) -> List[Tuple[str, torch.Tensor]]:
     hf_names = mapper.hf_names(name)
+    if hasattr(mapper, "export_tensor"):
+        t = mapper.export_tensor(name, t)            # layouts that differ from the checkpoint's (a flattened convolution)
     if len(hf_names) == 1:
         return [(hf_names[0], t)]
     if len(hf_names) == 3:   # q, k, v

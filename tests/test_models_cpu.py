@@ -347,3 +347,78 @@ def test_weighted_pipeline_layer_split():
     assert GPTArgs(n_layers=3, pp_size=3, pp_head_weight=50, **small).stage_bounds() == [0, 1, 2, 3]   # never empty
     stages = [GPT(GPTArgs(n_layers=7, pp_size=2, pp_rank=r, pp_head_weight=2, pp_embed_weight=1, **small)) for r in (0, 1)]
     assert [len(s.layers) for s in stages] == [4, 3] and stages[1].layer_offset == 4
+
+
+def _tiny_qwen25vl_config():
+    from transformers import Qwen2_5_VLConfig
+    return Qwen2_5_VLConfig(
+        text_config=dict(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                         intermediate_size=128, vocab_size=300, max_position_embeddings=512,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [2, 3, 3]}),
+        vision_config=dict(depth=3, hidden_size=32, num_heads=2, intermediate_size=48, out_hidden_size=64, patch_size=14,
+                           temporal_patch_size=2, spatial_merge_size=2, window_size=56, fullatt_block_indexes=[1],
+                           in_channels=3),
+        image_token_id=290, video_token_id=291, vision_start_token_id=292, vision_end_token_id=293)
+
+
+def test_native_qwen25vl_matches_transformers_and_round_trips_weights():
+    """The native Qwen2.5-VL (windowed vision tower, 2 x 2 merger, placeholder scatter, multimodal rotary positions on the
+    shared GPT decoder) reproduces the transformers implementation on a packed batch of two sequences with one image each
+    (different grids, so window and full-attention blocks differ); its weights export to checkpoint names and shapes and
+    load back; gradients reach the vision tower. Reference family: cosmos_rl/policy/model/qwen2_5_vl/__init__.py:566."""
+    from transformers import Qwen2_5_VLForConditionalGeneration
+    from cosmos_rl_b200.models.base import ModelRegistry
+    from cosmos_rl_b200.models.qwen2_5_vl import Qwen25VL, Qwen25VLArgs, mrope_positions
+    torch.manual_seed(0)
+    cfg = _tiny_qwen25vl_config()
+    hf = Qwen2_5_VLForConditionalGeneration(cfg).eval().float()
+    for p in hf.parameters():
+        torch.nn.init.normal_(p, 0, 0.05)
+    state = hf.state_dict()
+    assert ModelRegistry.get("qwen2_5_vl") is Qwen25VL
+    m = Qwen25VL(Qwen25VLArgs.from_hf_config(cfg.to_dict())).float()
+    hf_io.load_hf_state(m, lambda k: state[k], state, cfg.to_dict())
+    grids = torch.tensor([[1, 6, 4], [1, 4, 8]])
+    pix = torch.randn(int((grids[:, 0] * grids[:, 1] * grids[:, 2]).sum()), 3 * 2 * 14 * 14)
+    seq1 = [1, 2, 3, 4, 292] + [290] * 6 + [293, 7, 8, 9]
+    seq2 = [5, 292] + [290] * 8 + [293, 11, 12]
+    ids = torch.tensor(seq1 + seq2)
+    cu = torch.tensor([0, len(seq1), len(seq1) + len(seq2)], dtype=torch.int32)
+    m.mm_inputs = {"pixel_values": pix, "image_grid_thw": grids}
+    pos = m.get_position_ids(cu, ids.numel(), ids)
+    # 5 text tokens, a 3 x 2 merged grid starting at 5 (rows 5..7, columns 5..6), text resumes at 5 + max(3, 2)
+    assert pos[:, :len(seq1)].tolist() == [[0, 1, 2, 3, 4, 5, 5, 5, 5, 5, 5, 8, 9, 10, 11],
+                                           [0, 1, 2, 3, 4, 5, 5, 6, 6, 7, 7, 8, 9, 10, 11],
+                                           [0, 1, 2, 3, 4, 5, 6, 5, 6, 5, 6, 8, 9, 10, 11]]
+    assert pos[:, len(seq1)].tolist() == [0, 0, 0]                        # positions restart with every sequence
+    hid = m(ids, m.get_position_ids(cu, ids.numel()), cu, 15)             # 1-D positions in: the model derives the rest
+    mine = m.logits(hid)
+    ref, off = [], 0
+    with torch.no_grad():
+        for s, g in ((seq1, grids[0:1]), (seq2, grids[1:2])):
+            n = int(g[0, 0] * g[0, 1] * g[0, 2])
+            t = torch.tensor([s])
+            ref.append(hf(input_ids=t, pixel_values=pix[off:off + n], image_grid_thw=g,
+                          mm_token_type_ids=(t == 290).long()).logits[0])
+            off += n
+    ref = torch.cat(ref)
+    assert (mine - ref).abs().max().item() < 2e-4 * max(1.0, ref.abs().max().item()), (mine - ref).abs().max()
+    mine.square().mean().backward()
+    g_vis = m.visual.blocks[0].qkv.weight.grad
+    assert g_vis is not None and g_vis.abs().sum() > 0 and m.visual.patch_embed.weight.grad.abs().sum() > 0
+    # export: checkpoint names and shapes; load back into a fresh model
+    out = hf_io.hf_state_dict(m, cfg.to_dict())
+    assert set(out) == set(state), (sorted(set(state) - set(out))[:5], sorted(set(out) - set(state))[:5])
+    for k, v in out.items():
+        assert tuple(v.shape) == tuple(state[k].shape), k
+        assert torch.allclose(v, state[k]), k
+    m2 = Qwen25VL(Qwen25VLArgs.from_hf_config(cfg.to_dict())).float()
+    old = {("model." + k[len("model.language_model."):] if k.startswith("model.language_model.") else
+            (k[len("model."):] if k.startswith("model.visual.") else k)): v for k, v in out.items()}
+    hf_io.load_hf_state(m2, lambda k: old[k], old, cfg.to_dict())         # the older, flatter checkpoint naming
+    for (n, a), (_, b) in zip(m.named_parameters(), m2.named_parameters()):
+        assert torch.equal(a, b), n
+    # a video: 2 frames of a 2 x 2 merged grid, interval 2 tokens per second x 1 s
+    vpos = mrope_positions(torch.tensor([7, 291, 291, 291, 291, 291, 291, 291, 291, 9]), torch.tensor([0, 10]), 290, 291,
+                           None, torch.tensor([[2, 4, 4]]), 2, tokens_per_second=2.0, second_per_grid_ts=[1.0])
+    assert vpos[0].tolist() == [0, 1, 1, 1, 1, 3, 3, 3, 3, 4] and vpos[1].tolist() == [0, 1, 1, 2, 2, 1, 1, 2, 2, 4]

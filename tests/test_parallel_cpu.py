@@ -1044,3 +1044,70 @@ def _collective_sync_worker(rank, world, store):
 
 def test_collective_weight_sync_between_two_policy_and_two_rollout_ranks(tmp_path):
     _spawn(_collective_sync_worker, 4, tmp_path)
+
+
+def _vlm_tp_worker(rank, world, store, out_dir):
+    """Native Qwen2.5-VL through the SFT trainer with tensor parallelism 2: the decoder is sharded like any GPT, the
+    vision tower is replicated; samples carry pixels and placeholder tokens. Loss, gradient norm and the weights after
+    two steps equal the single-process trainer."""
+    from cosmos_rl_b200.config import Config
+    from cosmos_rl_b200.models import hf_io
+    from cosmos_rl_b200.models.qwen2_5_vl import Qwen25VL
+    from cosmos_rl_b200.parallel.dims import ParallelDims
+    from cosmos_rl_b200.policy.trainer.sft_trainer import SFTTrainer
+    _init(rank, world, store)
+
+    def cfg(par):
+        return Config.from_dict({
+            "policy": {"model_name_or_path": "tiny-qwen2.5-vl", "model_max_length": 128, "model_gradient_checkpointing": False,
+                       "parallelism": dict({"tp_size": 1, "cp_size": 1, "pp_size": 1, "dp_shard_size": 1}, **par)},
+            "train": {"seed": 0, "optm_lr": 1e-3, "optm_warmup_steps": 0, "output_dir": out_dir, "optm_grad_norm_clip": 0.5,
+                      "train_policy": {"type": "sft", "trainer_type": "sft", "mini_batch": 2},
+                      "ckpt": {"enable_checkpoint": False}}})
+    cpu = torch.device("cpu")
+    c = cfg({"tp_size": 2})
+    dims = ParallelDims.from_config_parallelism(c.policy.parallelism, world, rank, cpu)
+    dims.build_groups()
+    tr = SFTTrainer(c, dims, device=cpu)
+    ref = SFTTrainer(cfg({}), ParallelDims(world_size=1, device=cpu), device=cpu)
+    assert type(tr.model) is Qwen25VL and type(ref.model) is Qwen25VL
+    ref.model_load_from_hf()
+    hf_cfg = ref.model.args.to_hf_config()
+    state = hf_io.hf_state_dict(ref.model, hf_cfg)
+    hf_io.load_hf_state(tr.model, lambda k: state[k], state, hf_cfg, dims.tp, dims.tp_coord)
+    tr.optimizer.refresh_master_from_params()
+    g = torch.Generator().manual_seed(11)
+    IMG = ref.model.args.image_token_id
+
+    def sample(n_text, h, w):
+        ids = torch.randint(0, 30000, (n_text,), generator=g).tolist()
+        n_img = (h // 2) * (w // 2)
+        return {"input_ids": ids[:3] + [IMG] * n_img + ids[3:],
+                "pixel_values": torch.randn(h * w, 3 * 2 * 14 * 14, generator=g), "image_grid_thw": torch.tensor([[1, h, w]])}
+    batch = [sample(9, 4, 6), sample(12, 6, 4), sample(7, 8, 4), sample(10, 4, 4)]
+    w0 = ref.model.visual.blocks[0].qkv.weight.detach().clone()
+    for i in range(2):
+        a = tr.step_training(batch, total_steps=10, train_step=i + 1)
+        b = ref.step_training(batch, total_steps=10, train_step=i + 1)
+        assert abs(a["train/loss_avg"] - b["train/loss_avg"]) < 1e-4, (a["train/loss_avg"], b["train/loss_avg"])
+        assert abs(a["train/grad_norm"] - b["train/grad_norm"]) < 2e-3 * b["train/grad_norm"], (a["train/grad_norm"], b["train/grad_norm"])
+    want = hf_io.hf_state_dict(ref.model, hf_cfg)
+    probe = Qwen25VL(tr.model.args)
+    hf_io.load_hf_state(probe, lambda k: want[k], want, hf_cfg, dims.tp, dims.tp_coord)
+    for (n, p), (_, q) in zip(tr.model.named_parameters(), probe.named_parameters()):
+        assert torch.allclose(p, q, atol=5e-4), (n, (p - q).abs().max())
+    assert (ref.model.visual.blocks[0].qkv.weight - w0).abs().max() > 0           # the tower trained
+    # weight-sync plan: every tensor of the rollout side (tp 1) is covered by the two policy ranks
+    from cosmos_rl_b200.parallel.flat import FlatParams
+    from cosmos_rl_b200.parallel.reshard import build_plan, model_parts, shard_info
+    infos = [None] * world
+    dist.all_gather_object(infos, shard_info(rank, model_parts(tr.model, tr.flat), tr.flat.total))
+    plan = build_plan(infos, shard_info(0, model_parts(ref.model, ref.flat), ref.flat.total))
+    assert sum(d[5] * d[6] for d in plan) == sum(p.numel() for p in ref.model.parameters())
+    dist.destroy_process_group()
+
+
+def test_native_vlm_trains_with_tensor_parallelism(tmp_path):
+    """The reference's native VLM families carry parallel plans and a weight-sync map
+    (cosmos_rl/policy/model/qwen2_5_vl/__init__.py:566, weight_mapper.py)."""
+    _spawn(_vlm_tp_worker, 2, tmp_path, str(tmp_path))
