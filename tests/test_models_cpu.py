@@ -256,6 +256,7 @@ def test_vision_language_model_through_wrapper_packer_and_trainers(tmp_path):
         "custom": {"model_config": _tiny_vlm_config()},
         "rollout": {"n_generation": 2, "max_response_length": 4, "sampling_config": {"temperature": 1.0}},
         "train": {"seed": 0, "optm_lr": 2e-3, "optm_warmup_steps": 0, "output_dir": str(tmp_path),
+                  "force_use_hf": True,                  # the wrapper path (the family also has a native model)
                   "train_policy": {"type": "sft", "trainer_type": "sft", "mini_batch": 2},
                   "ckpt": {"enable_checkpoint": False}}})
     assert BaseDataPacker.get_default("qwen2_5_vl") is HFVLMDataPacker
