@@ -47,6 +47,19 @@ class SFTPolicyWorker(CommMixin):
         c = parallel_dims.coords
         self.dp_rank = c["dp_replicate"] * parallel_dims.dp_shard + c["dp_shard"]
         self.batch_per_rank = max(1, config.train.train_batch_per_replica // self.dp)
+        # several replicas: each one is a further data-parallel slice. The controller sends the membership as a
+        # BuildMesh command once the configured number of replicas has registered; the replicas then divide every
+        # global batch between them and average their gradients over the inter-replica communicator
+        self.stop_requested = False
+        if not standalone:
+            self.start_command_thread()
+            want = max(1, config.policy.parallelism.n_init_replicas)
+            if want > 1:
+                self._await_mesh(want)
+            self.dp, self.dp_rank = self.dp * self.inter_replica.world, self.inter_replica.rank * self.dp + self.dp_rank
+            if self.inter_replica.world > 1:
+                logger.info("[SFT] replica %d of %d: data-parallel slice %d of %d", self.inter_replica.rank,
+                            self.inter_replica.world, self.dp_rank, self.dp)
         n = len(self.dataset) if self.dataset is not None else 0
         per_step = self.batch_per_rank * self.dp
         self.steps_per_epoch = n // per_step if tp.dataloader_drop_last else -(-n // per_step)
@@ -68,6 +81,27 @@ class SFTPolicyWorker(CommMixin):
                 process_fn=self.trainer.data_packer.sft_process_sample)
             if self.start_step:
                 self.balancer.skip_steps(self.start_step)
+
+    def _consume_commands(self, block: float = 0.0) -> None:
+        """Membership changes and stop requests from the controller (every rank of the replica sees the same)."""
+        while True:
+            c = self.next_command(timeout=block)
+            block = 0.0
+            if c is None:
+                return
+            if isinstance(c, cmd.BuildMeshCommand):
+                self.inter_replica.rebuild(c.replica_name_to_rank, c.uuid_value)
+            elif isinstance(c, cmd.StopCommand):
+                self.stop_requested = True
+
+    def _await_mesh(self, n_replicas: int, timeout_s: float = 300.0) -> None:
+        import time
+        end = time.time() + timeout_s
+        while self.inter_replica.world < n_replicas and time.time() < end:
+            self._consume_commands(block=0.2)
+        if self.inter_replica.world < n_replicas:
+            logger.warning("[SFT] only %d of %d replicas joined within %.0f s: training with those",
+                           self.inter_replica.world, n_replicas, timeout_s)
 
     def _epoch_order(self, epoch: int) -> List[int]:
         tp = self.config.train.train_policy
@@ -110,6 +144,10 @@ class SFTPolicyWorker(CommMixin):
         if ck.save_freq_in_epoch > 0:           # takes priority over the step cadence (sft_worker.py:739-746)
             save_freq = max(1, ck.save_freq_in_epoch * max(1, self.steps_per_epoch))
         for step in range(self.start_step, self.total_steps):
+            if not self.standalone:
+                self._consume_commands()
+                if self.stop_requested:
+                    break
             do_save = ck.enable_checkpoint and ((step + 1) % save_freq == 0 or step + 1 == self.total_steps)
             report = self.trainer.step_training(self._batch(step), self.total_steps, step + 1, do_save=do_save)
             self.history.append({"step": step + 1, **report})

@@ -169,3 +169,41 @@ def test_tiny_grpo_job_with_pair_payload_transport(tmp_path):
     assert "'nccl' payload transport" in logs["rollout_0.log"], detail
     assert "through the payload transport" in logs["policy_0.log"], detail
     assert "could not be fetched" not in logs["policy_0.log"], detail
+
+
+@pytest.mark.timeout(300)
+def test_sft_job_with_two_policy_replicas(tmp_path):
+    """Multi-replica SFT through the launcher (cosmos_rl/policy/worker/multi_replica_sft_worker.py:44-565): the
+    controller sends the membership once both replicas have registered, each replica takes its slice of every global
+    batch (half the steps of a single replica), and the gradients are averaged over the inter-replica communicator, so
+    both report the same gradient norm on different losses."""
+    import re
+    from cosmos_rl_b200.config import dump_toml
+    raw = {"mode": "disaggregated",
+           "train": {"epoch": 1, "output_dir": str(tmp_path / "out"), "train_batch_per_replica": 4, "optm_lr": 1e-3,
+                     "optm_warmup_steps": 0, "seed": 0, "train_policy": {"type": "sft", "mini_batch": 2,
+                                                                         "dataloader_shuffle": False},
+                     "ckpt": {"enable_checkpoint": False}},
+           "policy": {"model_name_or_path": "tiny-qwen2", "model_max_length": 128, "model_gradient_checkpointing": False,
+                      "parallelism": {"tp_size": 1, "dp_shard_size": 1, "n_init_replicas": 2}},
+           "logging": {"logger": ["console"]}}
+    cfg = tmp_path / "job.toml"
+    cfg.write_text(dump_toml(raw))
+    log_dir = tmp_path / "logs"
+    env = dict(os.environ, COSMOS_LOG_LEVEL="INFO", COSMOS_HEARTBEAT_SEND_INTERVAL="2", PYTHONPATH=ROOT,
+               OMP_NUM_THREADS="2", E2E_N_PROMPTS="32")
+    cmd = [sys.executable, "-m", "cosmos_rl_b200.launcher.launch_all", "--config", str(cfg), "--policy", "2", "--cpu",
+           "--rdzv-port", "29761", "--log-dir", str(log_dir), os.path.join(HERE, "e2e_script.py")]
+    r = _run_job(cmd, env, 280)
+    latest = log_dir / "logs_latest"
+    logs = {f: open(latest / f).read() for f in sorted(os.listdir(latest))}
+    detail = "\n".join(f"==== {k}\n{v[-2500:]}" for k, v in logs.items())
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:] + detail
+    steps = {}
+    for name in ("policy_0.log", "policy_1.log"):
+        assert re.search(r"replica [01] of 2: data-parallel slice [01] of 2", logs[name]), detail
+        steps[name] = re.findall(r"\[SFT\] step (\d+)/(\d+) loss=([\d.]+) grad_norm=([\d.]+)", logs[name])
+        assert [s[0] for s in steps[name]] == ["1", "2", "3", "4"] and steps[name][0][1] == "4", detail
+    a, b = steps["policy_0.log"], steps["policy_1.log"]
+    assert [s[3] for s in a] == [s[3] for s in b], detail                 # one averaged gradient
+    assert [s[2] for s in a] != [s[2] for s in b], detail                 # from different halves of the batch

@@ -151,3 +151,16 @@ def test_config_driven_dataset_reads_columns_and_system_prompt(tmp_path):
     assert ds[1][0]["content"] == "own" and len(ds[1]) == 2                 # its own system turn is kept
     none = Config.from_dict({**base, "train": {"train_policy": {"type": "grpo"}}})
     assert CosmosDataset.wrap(lambda c: config_dataset(c), none) is None and CosmosDataset.wrap(None, none) is None
+
+
+def test_check_nccl_preflight_passes_and_reports_a_broken_piece(monkeypatch):
+    """The preflight runs its checks (device, transport registration, rendezvous store, a real loop-back transfer
+    through two transport ends) and exits 0; a piece that is broken shows up as FAIL and a non-zero exit code."""
+    from cosmos_rl_b200.tools.profiler import check_nccl
+    res = {n: (s, d) for n, s, d in check_nccl.run_checks()}
+    assert res["loop-back transfer"][0] == "ok" and "KiB" in res["loop-back transfer"][1]
+    assert res["transport registered"][0] == "ok" and res["rendezvous store"][0] == "ok"
+    assert check_nccl.main([]) == 0
+    from cosmos_rl_b200.utils.payload_transport import PayloadTransportRegistry
+    monkeypatch.setattr(PayloadTransportRegistry, "_by_name", {})
+    assert check_nccl.main([]) == 1
