@@ -443,6 +443,8 @@ class B200Config(_Section):
                                          # gradients (one all-gather less per projection in backward)
     sp_fused_kernels: bool = False       # sequence-parallel projections through the all-gather -> GEMM and
                                          # GEMM -> reduce-scatter kernels instead of library collectives + cuBLAS
+    pp_chunks: int = 1                   # model chunks per pipeline rank under pp_schedule = "Interleaved1F1B" (dense
+                                         # GPT family); 0 = derive from policy.parallelism.pp_layers_per_stage
     shard_params: bool = False           # parameter-sharded data parallelism: weights and gradients are 1/dp_shard
                                          # per rank too, gathered block by block around their use (same switch as
                                          # train.fsdp_reshard_after_forward = "always"). Off by default: models whose

@@ -45,6 +45,8 @@ class GPTArgs:
     tp_rank: int = 0
     pp_size: int = 1        # pipeline stages: a stage owns a contiguous range of blocks (+ embedding / head)
     pp_rank: int = 0
+    pp_chunks: int = 1      # model chunks per pipeline rank (interleaved schedule): chunk c of rank r is virtual stage
+                            # c * pp_size + r of pp_size * pp_chunks virtual stages
     pp_embed_weight: float = 0.0    # cost of the embedding (first stage) and of final norm + lm_head (last stage)
     pp_head_weight: float = 0.0     # in units of one block, for the layer split; -1 = from the shapes
 
@@ -57,12 +59,20 @@ class GPTArgs:
         bounds = self.stage_bounds()
         return bounds[self.pp_rank], bounds[self.pp_rank + 1]
 
-    def stage_bounds(self) -> List[int]:
+    def chunk_layers(self) -> List[Tuple[int, int]]:
+        """[lo, hi) block indices of every model chunk this rank holds (one chunk unless ``pp_chunks > 1``)."""
+        if self.pp_chunks <= 1:
+            return [self.stage_layers()]
+        bounds = self.stage_bounds(self.pp_size * self.pp_chunks)
+        return [(bounds[c * self.pp_size + self.pp_rank], bounds[c * self.pp_size + self.pp_rank + 1])
+                for c in range(self.pp_chunks)]
+
+    def stage_bounds(self, n_stages: Optional[int] = None) -> List[int]:
         """Block index where every stage starts (plus n_layers). Without weights: an even split. With
         ``pp_embed_weight`` / ``pp_head_weight`` the first / last stage are charged that many block-equivalents, so
         they get fewer blocks (the reference balances its DeepSeek stages by per-layer weights in the same spirit,
         cosmos_rl/utils/pipelining/pipelining_utils.py:36-110); every stage keeps at least one block."""
-        n, pp = self.n_layers, self.pp_size
+        n, pp = self.n_layers, (n_stages or self.pp_size)
         head = self.pp_head_weight
         if head < 0:        # lm_head GEMM against one block's GEMMs (attention projections + SwiGLU), per token
             per_block = self.dim * (self.n_heads + 2 * self.n_kv_heads) * self.head_dim \
@@ -274,13 +284,15 @@ class GPTWeightMapper(WeightMapper):
               "norm": "norm.weight"}
 
     layer_offset = 0    # first block index of this pipeline stage
+    layer_map = None    # block index in the whole model per local block (several chunks per rank); wins over the offset
 
     def hf_names(self, local: str) -> List[str]:
         """HF parameter names a local parameter is assembled from (in row order)."""
         name = local
-        if self.layer_offset and name.startswith("layers."):
+        if name.startswith("layers.") and (self.layer_offset or self.layer_map):
             idx, rest = name[len("layers."):].split(".", 1)
-            name = f"layers.{int(idx) + self.layer_offset}.{rest}"
+            g = self.layer_map[int(idx)] if self.layer_map else int(idx) + self.layer_offset
+            name = f"layers.{g}.{rest}"
         for k, v in self.RENAME.items():
             if name == k or name.endswith("." + k):
                 name = name[: len(name) - len(k)] + v
@@ -301,12 +313,17 @@ class GPT(BaseModel):
         a = args
         assert a.vocab_size % a.tp_size == 0 or a.tp_size == 1
         self.v_local = a.vocab_size // a.tp_size if a.tp_size > 1 else a.vocab_size
-        lo, hi = a.stage_layers()
-        self.layer_offset = lo
+        ranges = a.chunk_layers()
+        # local block i is block layer_map[i] of the whole model; with one chunk that is layer_offset + i
+        self.layer_map = [g for lo, hi in ranges for g in range(lo, hi)]
+        self.layer_offset = ranges[0][0] if len(ranges) == 1 else 0
+        self.chunk_bounds = [0]
+        for lo, hi in ranges:
+            self.chunk_bounds.append(self.chunk_bounds[-1] + hi - lo)
         self.is_first_stage, self.is_last_stage = a.pp_rank == 0, a.pp_rank == a.pp_size - 1
         assert a.pp_size == 1 or not a.tie_word_embeddings, "tied embeddings live on both ends of a pipeline"
         self.embed_tokens = nn.Embedding(self.v_local, a.dim) if self.is_first_stage else None
-        self.layers = nn.ModuleList([GPTBlock(a) for _ in range(hi - lo)])
+        self.layers = nn.ModuleList([GPTBlock(a) for _ in self.layer_map])
         self.norm = nn.Parameter(torch.ones(a.dim)) if self.is_last_stage else None
         if a.tie_word_embeddings or not self.is_last_stage:
             self.lm_head = None
@@ -367,10 +384,26 @@ class GPT(BaseModel):
         works on this rank's rows, and the final hidden states are gathered (and un-padded) before they are returned."""
         if self.param_sharder is not None:
             return self._forward_sharded(input_ids, position_ids, cu_seqlens, max_seqlen)
+        if len(self.chunk_bounds) > 2:
+            raise RuntimeError("a model built with pp_chunks > 1 runs chunk by chunk (forward_chunk) under the "
+                               "interleaved pipeline schedule")
+        return self._forward_layers(input_ids, position_ids, cu_seqlens, max_seqlen, self.layers, True, True)
+
+    def forward_chunk(self, chunk: int, x: torch.Tensor, position_ids: torch.Tensor, cu_seqlens: torch.Tensor,
+                      max_seqlen: int) -> torch.Tensor:
+        """One model chunk of this rank (interleaved pipeline schedule): chunk 0 of the first rank embeds ``x``
+        (token ids), the last chunk of the last rank applies the final norm; every other boundary carries the hidden
+        states."""
+        lo, hi = self.chunk_bounds[chunk], self.chunk_bounds[chunk + 1]
+        n_chunks = len(self.chunk_bounds) - 1
+        return self._forward_layers(x, position_ids, cu_seqlens, max_seqlen, self.layers[lo:hi],
+                                    self.is_first_stage and chunk == 0, self.is_last_stage and chunk == n_chunks - 1)
+
+    def _forward_layers(self, input_ids, position_ids, cu_seqlens, max_seqlen, layers, embeds: bool, finishes: bool):
         sp = self.tp is not None and self.tp.sequence_parallel
         T = input_ids.shape[0]
         if sp:
-            if not (self.is_first_stage and self.is_last_stage):
+            if not (embeds and finishes):
                 raise NotImplementedError("sequence parallelism is not combined with pipeline stages")
             mult = self.tp.row_multiple(input_ids.is_cuda)
             pad = (-T) % mult
@@ -380,9 +413,9 @@ class GPT(BaseModel):
                                                                      dtype=position_ids.dtype)])
                 cu_seqlens = torch.cat([cu_seqlens, cu_seqlens.new_tensor([T + pad])])
                 max_seqlen = max(int(max_seqlen), pad)
-        h = self.embed(input_ids) if self.is_first_stage else input_ids   # later stages receive hidden states
+        h = self.embed(input_ids) if embeds else input_ids                # later stages receive hidden states
         res = None
-        for layer in self.layers:
+        for layer in layers:
             if self.gradient_checkpointing in ("selective", "swiglu") and torch.is_grad_enabled():
                 h, res = layer(h, res, position_ids, cu_seqlens, max_seqlen, self.tp,
                                recompute=self.gradient_checkpointing)
@@ -390,7 +423,7 @@ class GPT(BaseModel):
                 h, res = checkpoint(layer, h, res, position_ids, cu_seqlens, max_seqlen, self.tp, use_reentrant=False)
             else:
                 h, res = layer(h, res, position_ids, cu_seqlens, max_seqlen, self.tp)
-        if not self.is_last_stage:
+        if not finishes:
             return h + res if res is not None else h                        # one tensor crosses the stage boundary
         norm_w = self.tp.shared_weight(self.norm) if self.tp is not None else self.norm
         out, _ = F.rms_norm(h, norm_w, self.args.norm_eps, residual=res)

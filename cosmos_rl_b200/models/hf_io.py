@@ -85,6 +85,7 @@ def load_hf_state(model, read, available, cfg: Dict[str, Any], tp: int = 1, r: i
     mapper = ModelRegistry.mapper(cfg.get("model_type"))(cfg)
     mapper.ep_rank = getattr(getattr(model, "args", None), "ep_rank", 0)
     mapper.layer_offset = getattr(model, "layer_offset", 0)
+    mapper.layer_map = getattr(model, "layer_map", None)
     missing = []
     with torch.no_grad():
         for name, p in model.named_parameters():
@@ -167,6 +168,7 @@ def hf_state_dict(model, hf_config: Dict[str, Any]) -> Dict[str, torch.Tensor]:
     from .base import ModelRegistry
     mapper = ModelRegistry.mapper(hf_config.get("model_type"))(hf_config)
     mapper.layer_offset = getattr(model, "layer_offset", 0)
+    mapper.layer_map = getattr(model, "layer_map", None)
     a = model.args
     out: Dict[str, torch.Tensor] = {}
     if hasattr(model, "export_items"):
@@ -199,6 +201,7 @@ def export_safetensors(model, hf_config: Dict[str, Any], output_dir: str, parall
     from .base import ModelRegistry
     mapper = ModelRegistry.mapper(hf_config.get("model_type"))(hf_config)
     mapper.layer_offset = getattr(model, "layer_offset", 0)
+    mapper.layer_map = getattr(model, "layer_map", None)
     tp = parallel_dims.tp if parallel_dims is not None else 1
     rank = parallel_dims.global_rank if parallel_dims is not None else 0
     writer = rank == 0

@@ -447,6 +447,7 @@ class Qwen25VL(GPT):
         from ..parallel.reshard import Part, gpt_parts
         mapper = Qwen25VLWeightMapper({"model_type": "qwen2_5_vl"})
         mapper.layer_offset = self.layer_offset
+        mapper.layer_map = self.layer_map
         dec = copy.copy(flat)
         dec.params = [(n, p) for n, p in flat.params if not n.startswith("visual.")]
         parts = gpt_parts(self, dec)

@@ -66,6 +66,7 @@ def gpt_parts(model, flat) -> List[Part]:
     from ..models.base import ModelRegistry
     mapper = ModelRegistry.mapper(a.model_type)({"model_type": a.model_type})
     mapper.layer_offset = getattr(model, "layer_offset", 0)
+    mapper.layer_map = getattr(model, "layer_map", None)
 
     def add(key, r0, r1, c0, c1, slot_off, row_in_local, col_in_local, ld, trainable):
         parts.append(Part(key, r0, r1, c0, c1, slot_off + row_in_local * ld + col_in_local, ld, trainable))

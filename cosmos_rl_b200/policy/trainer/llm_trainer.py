@@ -55,8 +55,24 @@ class LLMTrainer(Trainer):
             if parallel_dims.group("ep") is None and parallel_dims.dp_shard > 1:
                 parallel_dims.build_ep_groups()
             build_kw = dict(ep_size=ep, ep_rank=parallel_dims.ep_coord)
+        self.pp_chunks = 1
         if parallel_dims.pp > 1:
             build_kw.update(pp_size=parallel_dims.pp, pp_rank=parallel_dims.pp_coord)
+            par = config.policy.parallelism
+            if par.pp_schedule == "Interleaved1F1B":
+                # several model chunks per rank: asked for directly, or through the reference's layers-per-stage key
+                chunks = config.b200.pp_chunks
+                n_layers = (self.hf_config.get("num_hidden_layers") if isinstance(self.hf_config, dict)
+                            else getattr(self.hf_config, "num_hidden_layers", 0)) or 0
+                if chunks <= 0 or (chunks == 1 and par.pp_layers_per_stage > 0):
+                    chunks = max(1, -(-n_layers // max(1, par.pp_layers_per_stage)) // parallel_dims.pp) \
+                        if par.pp_layers_per_stage > 0 else 1
+                if chunks > 1:
+                    if n_layers < chunks * parallel_dims.pp:
+                        raise ValueError(f"{n_layers} blocks cannot fill {chunks} chunks on each of "
+                                         f"{parallel_dims.pp} pipeline ranks")
+                    self.pp_chunks = chunks
+                    build_kw.update(pp_chunks=chunks)
             if config.b200.pp_head_weight or config.b200.pp_embed_weight:
                 build_kw.update(pp_head_weight=config.b200.pp_head_weight, pp_embed_weight=config.b200.pp_embed_weight)
         with torch.device("meta"):
@@ -142,7 +158,12 @@ class LLMTrainer(Trainer):
             if not hasattr(getattr(model, "args", None), "pp_size"):
                 raise NotImplementedError("pp_size > 1 needs a native model")
             from ...parallel.pipeline import PipelineStage
-            self.pipeline = PipelineStage(model, parallel_dims.group("pp"), parallel_dims.pp_coord, parallel_dims.pp,
+            stage = model
+            if self.pp_chunks > 1:
+                if not hasattr(model, "forward_chunk"):
+                    raise NotImplementedError("several model chunks per pipeline rank need a model of the GPT family")
+                stage = [(lambda *a, c=c: model.forward_chunk(c, *a)) for c in range(self.pp_chunks)]
+            self.pipeline = PipelineStage(stage, parallel_dims.group("pp"), parallel_dims.pp_coord, parallel_dims.pp,
                                           model.args.dim, self.param_dtype, self.device,
                                           schedule=config.policy.parallelism.pp_schedule,
                                           back_group=parallel_dims.group("pp_back"))

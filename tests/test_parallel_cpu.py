@@ -1111,3 +1111,87 @@ def test_native_vlm_trains_with_tensor_parallelism(tmp_path):
     """The reference's native VLM families carry parallel plans and a weight-sync map
     (cosmos_rl/policy/model/qwen2_5_vl/__init__.py:566, weight_mapper.py)."""
     _spawn(_vlm_tp_worker, 2, tmp_path, str(tmp_path))
+
+
+def _pp_interleaved_trainer_worker(rank, world, store, out_dir):
+    """SFT and GRPO trainers with pp_size = 2 and two model chunks per rank (``pp_schedule = "Interleaved1F1B"``,
+    ``b200.pp_chunks = 2``): a four-block model, rank 0 holds blocks 0 and 2, rank 1 holds blocks 1 and 3. Loss,
+    gradient norm and weights equal the single-process trainers; checkpoint names follow the block map."""
+    import copy
+    from cosmos_rl_b200.config import Config
+    from cosmos_rl_b200.dispatcher.data.schema import Rollout
+    from cosmos_rl_b200.models import hf_io
+    from cosmos_rl_b200.parallel.dims import ParallelDims
+    from cosmos_rl_b200.policy.trainer.grpo_trainer import GRPOTrainer
+    from cosmos_rl_b200.policy.trainer.sft_trainer import SFTTrainer
+    _init(rank, world, store)
+    arch = copy.deepcopy(_tiny())
+    arch.n_layers = 4
+    model_cfg = arch.to_hf_config()
+
+    def cfg(pp, kind):
+        par = {"pp_size": pp, "dp_shard_size": 1, "tp_size": 1, "pp_micro_batch_size": 2,
+               "pp_schedule": "Interleaved1F1B" if pp > 1 else "1F1B"}
+        return Config.from_dict({
+            "policy": {"model_name_or_path": "four-block", "model_max_length": 64, "model_gradient_checkpointing": False,
+                       "parallelism": par},
+            "custom": {"model_config": model_cfg}, "b200": {"pp_chunks": 2 if pp > 1 else 1},
+            "train": {"seed": 0, "optm_lr": 1e-3, "optm_warmup_steps": 0, "output_dir": out_dir, "optm_grad_norm_clip": 0.5,
+                      "train_policy": {"type": kind, "trainer_type": kind, "mini_batch": 2},
+                      "ckpt": {"enable_checkpoint": False}}})
+    cpu = torch.device("cpu")
+    dims = ParallelDims.from_config_parallelism(cfg(2, "sft").policy.parallelism, world, rank, cpu)
+    dims.build_groups()
+    one = ParallelDims(world_size=1, device=cpu)
+
+    def same_weights(stage_tr, ref_tr):
+        hf_cfg = ref_tr.model.args.to_hf_config()
+        state = hf_io.hf_state_dict(ref_tr.model, hf_cfg)
+        hf_io.load_hf_state(stage_tr.model, lambda k: state[k], state, hf_cfg)
+        stage_tr.optimizer.refresh_master_from_params()
+        stage_tr.weights_ready = True
+
+    def check_weights(stage_tr, ref_tr):
+        ref_p = dict(ref_tr.model.named_parameters())
+        for n, p in stage_tr.model.named_parameters():
+            if n.startswith("layers."):
+                i, rest = n[len("layers."):].split(".", 1)
+                n = f"layers.{stage_tr.model.layer_map[int(i)]}.{rest}"
+            assert torch.allclose(p, ref_p[n], atol=5e-4), (n, (p - ref_p[n]).abs().max())
+
+    g = torch.Generator().manual_seed(3)
+    batch = [{"input_ids": torch.randint(0, 512, (n,), generator=g).tolist()} for n in (12, 9, 15, 7, 10, 6, 8, 11, 5, 13)]
+    tr, ref = SFTTrainer(cfg(2, "sft"), dims, device=cpu), SFTTrainer(cfg(1, "sft"), one, device=cpu)
+    ref.model_load_from_hf()
+    same_weights(tr, ref)
+    assert tr.model.layer_map == ([0, 2] if rank == 0 else [1, 3]) and tr.pipeline.n_chunks == 2
+    for i in range(2):
+        a = tr.step_training(batch, total_steps=10, train_step=i + 1)          # 5 micro-batches, 4 virtual stages
+        b = ref.step_training(batch, total_steps=10, train_step=i + 1)
+        assert abs(a["train/loss_avg"] - b["train/loss_avg"]) < 1e-4, (a["train/loss_avg"], b["train/loss_avg"])
+        assert abs(a["train/grad_norm"] - b["train/grad_norm"]) < 1e-3 * b["train/grad_norm"]
+    check_weights(tr, ref)
+    assert abs(tr.step_validation(batch)["val/loss"] - ref.step_validation(batch)["val/loss"]) < 1e-4
+    names = set(hf_io.hf_state_dict(tr.model, tr.model.args.to_hf_config()))
+    want = "model.layers.2.mlp.down_proj.weight" if rank == 0 else "model.layers.3.mlp.down_proj.weight"
+    assert want in names and ("model.layers.1.mlp.down_proj.weight" in names) == (rank == 1)
+    ros = []
+    for i in range(4):
+        n = [6, 11, 4, 9][i]
+        ros.append(Rollout(prompt=torch.randint(0, 512, (5 + i,), generator=g).tolist(),
+                           completion=torch.randint(0, 512, (n,), generator=g).tolist(),
+                           advantage=[0.5, -1.0, 1.5, -0.2][i], reward=float(i)))
+    gt, gref = GRPOTrainer(cfg(2, "grpo"), dims, device=cpu), GRPOTrainer(cfg(1, "grpo"), one, device=cpu)
+    gref.model_load_from_hf()
+    same_weights(gt, gref)
+    for t in (gt, gref):
+        t.tp_cfg.mu_iterations = 2
+    a, b = gt.step_training(ros, 1, 10), gref.step_training(ros, 1, 10)
+    assert abs(a["train/grad_norm"] - b["train/grad_norm"]) < 1e-3 * b["train/grad_norm"], (a["train/grad_norm"], b["train/grad_norm"])
+    assert abs(a["train/loss_avg"] - b["train/loss_avg"]) < 1e-5
+    check_weights(gt, gref)
+    dist.destroy_process_group()
+
+
+def test_trainers_with_interleaved_pipeline_chunks(tmp_path):
+    _spawn(_pp_interleaved_trainer_worker, 2, tmp_path, str(tmp_path))
