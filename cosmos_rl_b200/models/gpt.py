@@ -387,7 +387,8 @@ class GPT(BaseModel):
         if len(self.chunk_bounds) > 2:
             raise RuntimeError("a model built with pp_chunks > 1 runs chunk by chunk (forward_chunk) under the "
                                "interleaved pipeline schedule")
-        return self._forward_layers(input_ids, position_ids, cu_seqlens, max_seqlen, self.layers, True, True)
+        return self._forward_layers(input_ids, position_ids, cu_seqlens, max_seqlen, self.layers,
+                                    self.is_first_stage, self.is_last_stage)
 
     def forward_chunk(self, chunk: int, x: torch.Tensor, position_ids: torch.Tensor, cu_seqlens: torch.Tensor,
                       max_seqlen: int) -> torch.Tensor:
