@@ -434,7 +434,8 @@ class B200Config(_Section):
     dlogits_chunk: int = 16384
     pp_head_weight: float = 0.0          # pipeline layer split: cost of final norm + lm_head / of the embedding in
     pp_embed_weight: float = 0.0         # block-equivalents (the last / first stage get fewer blocks); -1 = from shapes
-    cp_mode: str = "kv-gather"           # context-parallel attention exchange: kv-gather | ring | ulysses
+    cp_mode: str = "kv-gather"           # context-parallel attention exchange: kv-gather | ring | ring-zigzag
+                                         # (ring on a layout that balances the causal work) | ulysses
     sequence_parallel: bool = False      # with tp_size > 1 (dense models, no pp / cp): residual stream and norms hold
                                          # T / tp rows (the reference's plan; halves activation memory at tp 2).
                                          # Off by default: one 7B block fwd+bwd at tp 2 takes 6.57 ms without it,

@@ -19,6 +19,10 @@ is the only layer that mixes positions. Two exchanges are provided:
   key length per GPU stays ``T / cp`` however long the sequences are. The backward pass runs the ring again: each
   step's dK/dV chunk is computed from the global log-sum-exp and handed on to its owner.
 
+* ``ring-zigzag``: the ring on a balanced layout. Every sequence is cut into ``2 cp`` chunks and rank ``r`` holds
+  chunks ``r`` and ``2 cp - 1 - r``; with contiguous chunks the last rank does ``cp`` times the causal work of the first
+  and everybody waits for it, here every hop is one attention call of the same size on every rank.
+
 All are autograd functions over ``torch.distributed`` collectives, so they run on NCCL and (for tests) on gloo.
 """
 from __future__ import annotations
@@ -32,11 +36,19 @@ from ..ops import functional as F
 from ..ops import reference
 
 
-def split_for_cp(x: torch.Tensor, cu_seqlens: torch.Tensor, cp: int, rank: int) -> torch.Tensor:
-    """Rows of the packed tensor ``x [T, ...]`` that belong to ``rank``: chunk ``rank`` of every sequence."""
+def split_for_cp(x: torch.Tensor, cu_seqlens: torch.Tensor, cp: int, rank: int, zigzag: bool = False) -> torch.Tensor:
+    """Rows of the packed tensor ``x [T, ...]`` that belong to ``rank``: chunk ``rank`` of every sequence. With
+    ``zigzag`` every sequence is cut into ``2 cp`` chunks and the rank holds chunks ``rank`` and ``2 cp - 1 - rank``
+    (in that order), which gives every rank the same share of a causal attention's work."""
     cs = cu_seqlens.tolist()
     parts = []
     for s, e in zip(cs[:-1], cs[1:]):
+        if zigzag:
+            n = (e - s) // (2 * cp)
+            assert n * 2 * cp == e - s, "sequence lengths must be multiples of twice the CP degree"
+            parts.append(x[s + rank * n:s + (rank + 1) * n])
+            parts.append(x[s + (2 * cp - 1 - rank) * n:s + (2 * cp - rank) * n])
+            continue
         n = (e - s) // cp
         assert n * cp == e - s, "sequence lengths must be multiples of the CP degree"
         parts.append(x[s + rank * n:s + (rank + 1) * n])
@@ -167,35 +179,39 @@ def kv_gather_attention(q, k, v, cu_local, max_local: int, group, scale: Optiona
 
 
 # ------------------------------------------------------------------------------------------------ ring
-def _fwd_with_lse(q, k, v, cu, max_len: int, scale: float, causal: bool):
-    """(out fp32-mergeable, lse [h, T] natural log) of one chunk pair; equal query and key segmentation."""
+def _fwd_with_lse(q, k, v, cu, max_len: int, scale: float, causal: bool, cu_k=None):
+    """(out fp32-mergeable, lse [h, T] natural log) of one chunk pair; ``cu_k`` when the keys are segmented
+    differently from the queries (half chunks of the zig-zag ring; non-causal only)."""
     if q.is_cuda:
         from ..ops import attention
         if attention.native_flash_supported(q, k, v):
-            i32 = cu if cu.dtype == torch.int32 else cu.to(torch.int32)
-            return attention.flash_fwd(q, k, v, i32, i32, max_len, scale, causal)
-    return reference.varlen_attention(q, k, v, cu, scale, causal, None, return_lse=True)
+            i32 = lambda t: t if t.dtype == torch.int32 else t.to(torch.int32)
+            return attention.flash_fwd(q, k, v, i32(cu), i32(cu if cu_k is None else cu_k), max_len, scale, causal)
+    return reference.varlen_attention(q, k, v, cu, scale, causal, cu_k, return_lse=True)
 
 
-def _bwd_from_lse(dout, q, k, v, out, lse, cu, max_len: int, scale: float, causal: bool):
+def _bwd_from_lse(dout, q, k, v, out, lse, cu, max_len: int, scale: float, causal: bool, cu_k=None, max_k=None):
     """Gradients of one chunk pair given the GLOBAL output and log-sum-exp of the queries (the probabilities of this
-    chunk are exp(s - lse), the softmax correction term is rowsum(dout * out) over the whole row)."""
+    chunk are exp(s - lse), the softmax correction term is rowsum(dout * out) over the whole row). ``cu_k`` /
+    ``max_k`` when the keys are segmented differently from the queries (non-causal only)."""
     if q.is_cuda:
         from ..ops import attention
         if attention.native_flash_supported(q, k, v):
-            i32 = cu if cu.dtype == torch.int32 else cu.to(torch.int32)
-            return attention.flash_bwd(dout, q, k, v, out, lse, i32, max_len, scale, causal=causal)
+            i32 = lambda t: t if t.dtype == torch.int32 else t.to(torch.int32)
+            return attention.flash_bwd(dout, q, k, v, out, lse, i32(cu), max_len, scale,
+                                       cu_k=None if cu_k is None else i32(cu_k), max_k=max_k, causal=causal)
     hq, hkv = q.shape[1], k.shape[1]
     g = hq // hkv
     dq, dk, dv = torch.zeros_like(q, dtype=torch.float32), torch.zeros_like(k, dtype=torch.float32), \
         torch.zeros_like(v, dtype=torch.float32)
     cs = cu.tolist()
-    for s, e in zip(cs[:-1], cs[1:]):
-        if e <= s:
+    ks = cs if cu_k is None else cu_k.tolist()
+    for s, e, ks0, ke0 in zip(cs[:-1], cs[1:], ks[:-1], ks[1:]):
+        if e <= s or ke0 <= ks0:
             continue
         qi = q[s:e].float().transpose(0, 1)                               # [hq, L, d]
-        ki = k[s:e].float().transpose(0, 1).repeat_interleave(g, dim=0)
-        vi = v[s:e].float().transpose(0, 1).repeat_interleave(g, dim=0)
+        ki = k[ks0:ke0].float().transpose(0, 1).repeat_interleave(g, dim=0)
+        vi = v[ks0:ke0].float().transpose(0, 1).repeat_interleave(g, dim=0)
         do, o = dout[s:e].float().transpose(0, 1), out[s:e].float().transpose(0, 1)
         sc = (qi @ ki.transpose(-1, -2)) * scale
         if causal:
@@ -205,8 +221,8 @@ def _bwd_from_lse(dout, q, k, v, out, lse, cu, max_len: int, scale: float, causa
         delta = (do * o).sum(-1, keepdim=True)
         ds = p * (do @ vi.transpose(-1, -2) - delta)
         dq[s:e] = ((ds @ ki) * scale).transpose(0, 1)
-        dk[s:e] = ((ds.transpose(-1, -2) @ qi) * scale).view(hkv, g, e - s, -1).sum(1).transpose(0, 1)
-        dv[s:e] = (p.transpose(-1, -2) @ do).view(hkv, g, e - s, -1).sum(1).transpose(0, 1)
+        dk[ks0:ke0] = ((ds.transpose(-1, -2) @ qi) * scale).view(hkv, g, ke0 - ks0, -1).sum(1).transpose(0, 1)
+        dv[ks0:ke0] = (p.transpose(-1, -2) @ do).view(hkv, g, ke0 - ks0, -1).sum(1).transpose(0, 1)
     return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
 
 
@@ -285,16 +301,136 @@ def ring_attention(q, k, v, cu_local, max_local: int, group, scale: Optional[flo
     return _RingAttention.apply(q, k, v, cu_local, max_local, group, scale)
 
 
+# ------------------------------------------------------------------------------------------------ zig-zag ring
+def _half_rows(cu_local: torch.Tensor, device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Row indices of the first and of the second half of every local sequence."""
+    cs = cu_local.tolist()
+    lo, hi = [], []
+    for s, e in zip(cs[:-1], cs[1:]):
+        m = (s + e) // 2
+        lo.append(torch.arange(s, m))
+        hi.append(torch.arange(m, e))
+    cat = lambda xs: (torch.cat(xs) if xs else torch.zeros(0, dtype=torch.int64)).to(device)
+    return cat(lo), cat(hi)
+
+
+def _merge(out, lse, o_j, lse_j, rows=None):
+    """Fold a partial result (for all rows, or for ``rows`` only) into the running output and log-sum-exp."""
+    o_j = o_j.float()
+    if out is None:
+        return o_j, lse_j
+    if rows is None:
+        new = torch.logaddexp(lse, lse_j)
+        out = out * torch.exp(lse - new).t()[..., None] + o_j * torch.exp(lse_j - new).t()[..., None]
+        return out, new
+    cur_o, cur_l = out[rows], lse[:, rows]
+    new = torch.logaddexp(cur_l, lse_j)
+    out = out.index_copy(0, rows, cur_o * torch.exp(cur_l - new).t()[..., None] + o_j * torch.exp(lse_j - new).t()[..., None])
+    lse = lse.index_copy(1, rows, new)
+    return out, lse
+
+
+class _ZigzagRingAttention(torch.autograd.Function):
+    """Ring attention on the zig-zag layout (rank r holds chunks r and 2 cp - 1 - r of every sequence). Per hop the
+    chunk pair needs exactly one call of half the size of a full chunk pair on every rank: the rank's own chunks ->
+    causal over the local order; chunks of an earlier rank -> all local queries against the first half of the keys;
+    chunks of a later rank -> the second half of the local queries against all keys. No rank waits for another."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_local, max_local, group, scale):
+        cp, rank = dist.get_world_size(group), dist.get_rank(group)
+        scale = scale if scale is not None else q.shape[-1] ** -0.5
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        lo, hi = _half_rows(cu_local, q.device)
+        cu_half = (cu_local // 2).to(cu_local.dtype)
+        kv = torch.stack([k, v])
+        out = lse = None
+        for step in range(cp):
+            src = (rank - step) % cp
+            if step < cp - 1:
+                nxt_kv, reqs = _ring_exchange(kv, group, cp, rank)
+            if src == rank:
+                o_j, l_j = _fwd_with_lse(q, kv[0], kv[1], cu_local, max_local, scale, True)
+                out, lse = _merge(out, lse, o_j, l_j)
+            elif src < rank:
+                o_j, l_j = _fwd_with_lse(q, kv[0][lo].contiguous(), kv[1][lo].contiguous(), cu_local, max_local, scale,
+                                         False, cu_k=cu_half)
+                out, lse = _merge(out, lse, o_j, l_j)
+            else:
+                o_j, l_j = _fwd_with_lse(q[hi].contiguous(), kv[0], kv[1], cu_half, max_local // 2, scale, False,
+                                         cu_k=cu_local)
+                out, lse = _merge(out, lse, o_j, l_j, rows=hi)
+            if step < cp - 1:
+                for r_ in reqs:
+                    r_.wait()
+                kv = nxt_kv
+        out = out.to(q.dtype)
+        ctx.save_for_backward(q, k, v, out, lse, cu_local)
+        ctx.group, ctx.max_local, ctx.scale = group, max_local, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse, cu_local = ctx.saved_tensors
+        group = ctx.group
+        cp, rank = dist.get_world_size(group), dist.get_rank(group)
+        ml, scale = ctx.max_local, ctx.scale
+        dout = dout.contiguous()
+        lo, hi = _half_rows(cu_local, q.device)
+        cu_half = (cu_local // 2).to(cu_local.dtype)
+        dq = torch.zeros_like(q, dtype=torch.float32)
+        kv = torch.stack([k, v])
+        dkv = torch.zeros_like(kv, dtype=torch.float32)
+        for step in range(cp):
+            src = (rank - step) % cp
+            if step < cp - 1:
+                nxt_kv, reqs = _ring_exchange(kv, group, cp, rank)
+            if src == rank:
+                dq_j, dk_j, dv_j = _bwd_from_lse(dout, q, kv[0], kv[1], out, lse, cu_local, ml, scale, True)
+                dq += dq_j.float()
+                dkv[0] += dk_j.float()
+                dkv[1] += dv_j.float()
+            elif src < rank:
+                dq_j, dk_j, dv_j = _bwd_from_lse(dout, q, kv[0][lo].contiguous(), kv[1][lo].contiguous(), out, lse,
+                                                 cu_local, ml, scale, False, cu_k=cu_half, max_k=ml // 2)
+                dq += dq_j.float()
+                dkv[0].index_add_(0, lo, dk_j.float())
+                dkv[1].index_add_(0, lo, dv_j.float())
+            else:
+                dq_j, dk_j, dv_j = _bwd_from_lse(dout[hi].contiguous(), q[hi].contiguous(), kv[0], kv[1],
+                                                 out[hi].contiguous(), lse[:, hi].contiguous(), cu_half, ml // 2, scale,
+                                                 False, cu_k=cu_local, max_k=ml)
+                dq.index_add_(0, hi, dq_j.float())
+                dkv[0] += dk_j.float()
+                dkv[1] += dv_j.float()
+            nxt_dkv, greqs = _ring_exchange(dkv, group, cp, rank)
+            if step < cp - 1:
+                for r_ in reqs:
+                    r_.wait()
+                kv = nxt_kv
+            for r_ in greqs:
+                r_.wait()
+            dkv = nxt_dkv
+        return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None, None, None, None
+
+
+def zigzag_ring_attention(q, k, v, cu_local, max_local: int, group, scale: Optional[float] = None):
+    return _ZigzagRingAttention.apply(q, k, v, cu_local, max_local, group, scale)
+
+
 class ContextParallel:
     """Attached to a model as ``model.cp``; the attention layer calls ``attention`` instead of the local kernel."""
 
     def __init__(self, group, size: int, rank: int, mode: str = "kv-gather"):
-        assert mode in ("kv-gather", "ulysses", "ring")
+        assert mode in ("kv-gather", "ulysses", "ring", "ring-zigzag")
         self.group, self.size, self.rank, self.mode = group, size, rank, mode
+        self.zigzag = mode == "ring-zigzag"
+        self.seq_multiple = size * (2 if self.zigzag else 1)       # sequences are padded to multiples of this
 
     def attention(self, q, k, v, cu_local, max_local: int, scale: Optional[float] = None):
-        fn = {"ulysses": ulysses_attention, "ring": ring_attention}.get(self.mode, kv_gather_attention)
+        fn = {"ulysses": ulysses_attention, "ring": ring_attention,
+              "ring-zigzag": zigzag_ring_attention}.get(self.mode, kv_gather_attention)
         return fn(q, k, v, cu_local, max_local, self.group, scale)
 
     def shard(self, x, cu_seqlens):
-        return split_for_cp(x, cu_seqlens, self.size, self.rank)
+        return split_for_cp(x, cu_seqlens, self.size, self.rank, self.zigzag)

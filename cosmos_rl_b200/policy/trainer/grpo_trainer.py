@@ -120,7 +120,7 @@ class GRPOTrainer(LLMTrainer):
         return [list(range(i, min(i + mb, len(samples)))) for i in range(0, len(samples), mb)]
 
     def _pack(self, samples: List[_Sample]) -> Dict[str, Any]:
-        pad_mult = self.parallel_dims.cp * self.parallel_dims.tp
+        pad_mult = self.pack_multiple()
         b = pack_sequences([s.ids for s in samples], [s.mask for s in samples], device=self.device,
                            pad_multiple=1 if pad_mult == 1 else pad_mult)
         rlp_full = None
@@ -170,18 +170,22 @@ class GRPOTrainer(LLMTrainer):
         if rlp_full is not None:
             if self.parallel_dims.cp > 1:
                 from ...parallel.context_parallel import split_for_cp
-                rlp_full = split_for_cp(rlp_full, cu_full, self.parallel_dims.cp, self.parallel_dims.cp_coord)
+                rlp_full = split_for_cp(rlp_full, cu_full, self.parallel_dims.cp, self.parallel_dims.cp_coord,
+                                        zigzag=self.config.b200.cp_mode == "ring-zigzag")
             b["rollout_lp"] = rlp_full[sel]
         if tlp_full is not None:
             if self.parallel_dims.cp > 1:
                 from ...parallel.context_parallel import split_for_cp
-                tlp_full = split_for_cp(tlp_full, cu_full, self.parallel_dims.cp, self.parallel_dims.cp_coord)
+                tlp_full = split_for_cp(tlp_full, cu_full, self.parallel_dims.cp, self.parallel_dims.cp_coord,
+                                        zigzag=self.config.b200.cp_mode == "ring-zigzag")
             b["teacher_lp"] = tlp_full[sel]
         if tk_ids is not None:
             if self.parallel_dims.cp > 1:
                 from ...parallel.context_parallel import split_for_cp
-                tk_ids = split_for_cp(tk_ids, cu_full, self.parallel_dims.cp, self.parallel_dims.cp_coord)
-                tk_lp = split_for_cp(tk_lp, cu_full, self.parallel_dims.cp, self.parallel_dims.cp_coord)
+                tk_ids = split_for_cp(tk_ids, cu_full, self.parallel_dims.cp, self.parallel_dims.cp_coord,
+                                        zigzag=self.config.b200.cp_mode == "ring-zigzag")
+                tk_lp = split_for_cp(tk_lp, cu_full, self.parallel_dims.cp, self.parallel_dims.cp_coord,
+                                        zigzag=self.config.b200.cp_mode == "ring-zigzag")
             b["teacher_topk_ids"], b["teacher_topk_lp"] = tk_ids[sel], tk_lp[sel]
         return b
 

@@ -325,7 +325,14 @@ class LLMTrainer(Trainer):
         if dims.cp == 1:
             return b
         from ...utils.sequence_packing import shard_packed
-        return shard_packed(b, dims.cp, dims.cp_coord)
+        return shard_packed(b, dims.cp, dims.cp_coord, zigzag=self.config.b200.cp_mode == "ring-zigzag")
+
+    def pack_multiple(self) -> int:
+        """Sequences of a packed batch are padded to multiples of this (context-parallel chunks, twice as many for the
+        zig-zag layout, times the tensor-parallel row split)."""
+        dims = self.parallel_dims
+        cp = dims.cp * (2 if (dims.cp > 1 and self.config.b200.cp_mode == "ring-zigzag") else 1)
+        return max(1, cp * dims.tp)
 
     def lr_scale(self, step: int) -> float:
         t = self.config.train

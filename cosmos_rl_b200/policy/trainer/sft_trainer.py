@@ -22,7 +22,7 @@ class SFTTrainer(LLMTrainer):
         masks = [[1 if (i + 1 < len(s["label_ids"]) and s["label_ids"][i + 1] != -100) else 0
                   for i in range(len(s["input_ids"]))] for s in samples]
         b = pack_sequences(seqs, masks, device=self.device,
-                           pad_multiple=max(1, self.parallel_dims.cp * self.parallel_dims.tp))
+                           pad_multiple=self.pack_multiple())
         b = self.cp_shard(b)
         sel = (b["label_ids"] >= 0).nonzero(as_tuple=True)[0]
         b["sel"], b["labels_sel"] = sel, b["label_ids"][sel]

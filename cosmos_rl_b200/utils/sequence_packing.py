@@ -39,13 +39,14 @@ def pack_sequences(seqs: Sequence[Sequence[int]], masks: Sequence[Sequence[int]]
             "seq_ids": t(seq_ids, torch.long)}
 
 
-def shard_packed(b: Dict[str, Any], cp: int, rank: int) -> Dict[str, Any]:
-    """This context-parallel rank's part of a packed batch (sequences padded to multiples of ``cp``): chunk ``rank`` of
-    every sequence for the token-wise tensors, local ``cu_seqlens`` / ``max_seqlen``; position ids stay global."""
+def shard_packed(b: Dict[str, Any], cp: int, rank: int, zigzag: bool = False) -> Dict[str, Any]:
+    """This context-parallel rank's part of a packed batch (sequences padded to multiples of ``cp``, or of ``2 cp`` for
+    the zig-zag layout): chunk ``rank`` of every sequence (zig-zag: chunks ``rank`` and ``2 cp - 1 - rank``) for the
+    token-wise tensors, local ``cu_seqlens`` / ``max_seqlen``; position ids stay global."""
     from ..parallel.context_parallel import local_cu_seqlens, split_for_cp
     out = dict(b)
     for k in ("input_ids", "position_ids", "label_ids", "seq_ids"):
-        out[k] = split_for_cp(b[k], b["cu_seqlens"], cp, rank)
+        out[k] = split_for_cp(b[k], b["cu_seqlens"], cp, rank, zigzag)
     out["cu_seqlens"] = local_cu_seqlens(b["cu_seqlens"], cp)
     out["max_seqlen"] = b["max_seqlen"] // cp
     out["cu_seqlens_full"] = b["cu_seqlens"]

@@ -31,6 +31,8 @@ def _cp_worker(rank, world, store, mode):
     m.init_weights(0)
     lens = [8, 20, 4]
     cu = torch.tensor([0, 8, 28, 32])
+    if mode == "ring-zigzag-long":                         # four ranks: lengths have to be multiples of 2 * 4
+        mode, lens, cu = "ring-zigzag", [8, 16, 8], torch.tensor([0, 8, 24, 32])
     g = torch.Generator().manual_seed(1)
     ids = torch.randint(0, 512, (32,), generator=g)
     labels = torch.randint(0, 512, (32,), generator=g)
@@ -54,9 +56,19 @@ def _cp_worker(rank, world, store, mode):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["kv-gather", "ulysses", "ring"])
+@pytest.mark.parametrize("mode", ["kv-gather", "ulysses", "ring", "ring-zigzag"])
 def test_context_parallel_matches_full_model(tmp_path, mode):
     _spawn(_cp_worker, 2, tmp_path, mode)
+
+
+def test_zigzag_ring_on_four_ranks_and_its_layout(tmp_path):
+    """Four ranks, eight chunks per sequence: every rank holds chunks r and 7 - r, and the model matches the unsplit
+    one. (Sequence lengths of the worker are multiples of 8.)"""
+    from cosmos_rl_b200.parallel.context_parallel import split_for_cp
+    x, cu = torch.arange(24), torch.tensor([0, 16, 24])
+    assert split_for_cp(x, cu, 2, 0, zigzag=True).tolist() == [0, 1, 2, 3, 12, 13, 14, 15, 16, 17, 22, 23]
+    assert split_for_cp(x, cu, 2, 1, zigzag=True).tolist() == [4, 5, 6, 7, 8, 9, 10, 11, 18, 19, 20, 21]
+    _spawn(_cp_worker, 4, tmp_path, "ring-zigzag-long")
 
 
 def test_ring_attention_on_four_ranks(tmp_path):
@@ -681,7 +693,7 @@ def _cp_trainer_worker(rank, world, store, out_dir, mode):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["kv-gather", "ring"])
+@pytest.mark.parametrize("mode", ["kv-gather", "ring", "ring-zigzag"])
 def test_trainers_with_context_parallelism(tmp_path, mode):
     _spawn(_cp_trainer_worker, 2, tmp_path, str(tmp_path), mode)
 
