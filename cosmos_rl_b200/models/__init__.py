@@ -5,6 +5,7 @@ from . import qwen3_moe  # noqa: F401
 from . import deepseek_v3  # noqa: F401
 from . import dit  # noqa: F401
 from . import qwen2_5_vl  # noqa: F401
+from . import internvl  # noqa: F401
 from . import hf_model  # noqa: F401  (fallback for every other transformers causal LM)
 
 
@@ -17,6 +18,7 @@ def named_architectures():
         out.update(deepseek_v3.ARCHS)
         out.update(dit.ARCHS)
         out.update(qwen2_5_vl.ARCHS)
+        out.update(internvl.ARCHS)
     except ImportError:
         pass
     return out

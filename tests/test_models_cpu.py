@@ -423,3 +423,65 @@ def test_native_qwen25vl_matches_transformers_and_round_trips_weights():
     vpos = mrope_positions(torch.tensor([7, 291, 291, 291, 291, 291, 291, 291, 291, 9]), torch.tensor([0, 10]), 290, 291,
                            None, torch.tensor([[2, 4, 4]]), 2, tokens_per_second=2.0, second_per_grid_ts=[1.0])
     assert vpos[0].tolist() == [0, 1, 1, 1, 1, 3, 3, 3, 3, 4] and vpos[1].tolist() == [0, 1, 1, 2, 2, 1, 1, 2, 2, 4]
+
+
+@pytest.mark.parametrize("norm_type,qk_norm", [("layer_norm", False), ("rms_norm", True)])
+def test_native_internvl_matches_transformers(norm_type, qk_norm):
+    """Native InternVL (tile tower with class token and learned positions, layer-scaled blocks, pixel-shuffle projector,
+    placeholder scatter on the shared GPT decoder) against transformers on a packed batch of two sequences with two tiles
+    and one tile; checkpoint names and shapes round-trip; the weight-sync parts of a tensor-parallel pair of policy
+    ranks cover an unsharded rollout model. Reference family: cosmos_rl/policy/model/internvl/__init__.py:247."""
+    from transformers import InternVLConfig, InternVLForConditionalGeneration
+    from cosmos_rl_b200.models.base import ModelRegistry
+    from cosmos_rl_b200.models.internvl import InternVL, InternVLArgs
+    torch.manual_seed(0)
+    cfg = InternVLConfig(
+        text_config=dict(model_type="qwen2", hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, intermediate_size=128, vocab_size=300, max_position_embeddings=512,
+                         rope_theta=10000.0),
+        vision_config=dict(hidden_size=32, num_hidden_layers=2, num_attention_heads=2, intermediate_size=48,
+                           image_size=[56, 56], patch_size=[14, 14], norm_type=norm_type, use_qk_norm=qk_norm,
+                           attention_bias=True),
+        image_token_id=290, downsample_ratio=0.5)
+    hf = InternVLForConditionalGeneration(cfg).eval().float()
+    for p in hf.parameters():
+        torch.nn.init.normal_(p, 0, 0.05)
+    state = hf.state_dict()
+    assert ModelRegistry.get("internvl") is InternVL
+    m = InternVL(InternVLArgs.from_hf_config(cfg.to_dict())).float()
+    hf_io.load_hf_state(m, lambda k: state[k], state, cfg.to_dict())
+    pix = torch.randn(3, 3, 56, 56)                       # three tiles of 4 x 4 patches -> 4 tokens each
+    seq1 = [1, 2, 3] + [290] * 8 + [7, 8, 9]
+    seq2 = [5] + [290] * 4 + [11, 12]
+    ids = torch.tensor(seq1 + seq2)
+    cu = torch.tensor([0, len(seq1), len(seq1) + len(seq2)], dtype=torch.int32)
+    m.mm_inputs = {"pixel_values": pix}
+    mine = m.logits(m(ids, m.get_position_ids(cu, ids.numel()), cu, len(seq1)))
+    with torch.no_grad():
+        ref = torch.cat([hf(input_ids=torch.tensor([seq1]), pixel_values=pix[:2]).logits[0],
+                         hf(input_ids=torch.tensor([seq2]), pixel_values=pix[2:]).logits[0]])
+    assert (mine - ref).abs().max().item() < 1e-4, (mine - ref).abs().max()
+    mine.square().mean().backward()
+    assert m.visual.blocks[0].q_proj.weight.grad.abs().sum() > 0 and m.visual.patch_embed.weight.grad.abs().sum() > 0
+    out = hf_io.hf_state_dict(m, cfg.to_dict())
+    assert set(out) == set(state)
+    for k, v in out.items():
+        assert tuple(v.shape) == tuple(state[k].shape) and torch.allclose(v, state[k]), k
+    # weight sync: two tensor-parallel policy ranks -> one unsharded rollout model
+    flat_dst = FlatParams(m, torch.float32, torch.device("cpu"), with_grad=False)
+    infos = []
+    for r in range(2):
+        a = InternVLArgs.from_hf_config(cfg.to_dict(), tp_size=2, tp_rank=r)
+        mr = InternVL(a).float()
+        hf_io.load_hf_state(mr, lambda k: state[k], state, cfg.to_dict(), 2, r)
+        fr = FlatParams(mr, torch.float32, torch.device("cpu"), with_grad=False)
+        infos.append((shard_info(r, model_parts(mr, fr), fr.total), fr))
+    want = flat_dst.data.clone()
+    flat_dst.data.zero_()
+    plan = build_plan([i for i, _ in infos], shard_info(0, model_parts(m, flat_dst), flat_dst.total))
+    for src, so, sld, do, dld, rows, cols in plan:
+        torch.as_strided(flat_dst.data, (rows, cols), (dld, 1), do).copy_(
+            torch.as_strided(infos[src][1].data, (rows, cols), (sld, 1), so))
+    for name, p in m.named_parameters():
+        ref_p = torch.as_strided(want, p.shape, p.stride(), p.storage_offset())
+        assert torch.equal(p.data, ref_p), name
