@@ -315,18 +315,19 @@ def _half_rows(cu_local: torch.Tensor, device) -> Tuple[torch.Tensor, torch.Tens
 
 
 def _merge(out, lse, o_j, lse_j, rows=None):
-    """Fold a partial result (for all rows, or for ``rows`` only) into the running output and log-sum-exp."""
-    o_j = o_j.float()
+    """Fold a partial result (for all rows, or for ``rows`` only) into the running output and log-sum-exp, in place
+    (called inside autograd functions, where nothing is recorded)."""
     if out is None:
-        return o_j, lse_j
+        return o_j.float(), lse_j
     if rows is None:
         new = torch.logaddexp(lse, lse_j)
-        out = out * torch.exp(lse - new).t()[..., None] + o_j * torch.exp(lse_j - new).t()[..., None]
+        out.mul_(torch.exp(lse - new).t()[..., None]).add_(o_j.float() * torch.exp(lse_j - new).t()[..., None])
         return out, new
-    cur_o, cur_l = out[rows], lse[:, rows]
+    cur_l = lse[:, rows]
     new = torch.logaddexp(cur_l, lse_j)
-    out = out.index_copy(0, rows, cur_o * torch.exp(cur_l - new).t()[..., None] + o_j * torch.exp(lse_j - new).t()[..., None])
-    lse = lse.index_copy(1, rows, new)
+    upd = out[rows] * torch.exp(cur_l - new).t()[..., None] + o_j.float() * torch.exp(lse_j - new).t()[..., None]
+    out.index_copy_(0, rows, upd)
+    lse.index_copy_(1, rows, new)
     return out, lse
 
 

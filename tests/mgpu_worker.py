@@ -474,10 +474,10 @@ def main():
         e_ = (l_.grad.float() - ref_g).abs().max().item()
         assert e_ <= 0.04 * ref_g.abs().max().item() + 2e-2, ("zigzag", name, e_)
 
-    Lb = 16384                                             # one long sequence for the timing
+    Lb = 65536                                             # one long sequence for the timing
     cub = torch.tensor([0, Lb], dtype=torch.int32, device=dev)
     lcub = local_cu_seqlens(cub, world)
-    big = [torch.randn(Lb, h_, 128, generator=g).to(dev, torch.bfloat16) for h_ in (8, 2, 2)]
+    big = [torch.randn(Lb, h_, 128, generator=g).to(dev, torch.bfloat16) for h_ in (16, 4, 4)]
 
     def timed_cp(cpo, zigzag):
         loc_ = [split_for_cp(t, cub, world, rank, zigzag=zigzag).contiguous() for t in big]
@@ -500,7 +500,7 @@ def main():
     if rank == 0:
         print(f"zig-zag ring attention over {world} GPUs: output (max err {e_z:.4f}) and dq/dk/dv match single-GPU "
               f"attention; forward + backward {t_zz:.3f} ms against {t_ring:.3f} ms for the contiguous ring "
-              f"(max over ranks, one sequence of {Lb} tokens, 8 query / 2 key heads)", flush=True)
+              f"(max over ranks, one sequence of {Lb} tokens, 16 query / 4 key heads)", flush=True)
 
     if mp is not None:
         mp.close()
