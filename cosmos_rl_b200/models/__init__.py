@@ -6,6 +6,7 @@ from . import deepseek_v3  # noqa: F401
 from . import dit  # noqa: F401
 from . import qwen2_5_vl  # noqa: F401
 from . import internvl  # noqa: F401
+from . import qwen3_vl_moe  # noqa: F401
 from . import hf_model  # noqa: F401  (fallback for every other transformers causal LM)
 
 
@@ -19,6 +20,7 @@ def named_architectures():
         out.update(dit.ARCHS)
         out.update(qwen2_5_vl.ARCHS)
         out.update(internvl.ARCHS)
+        out.update(qwen3_vl_moe.ARCHS)
     except ImportError:
         pass
     return out

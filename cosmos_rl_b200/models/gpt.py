@@ -180,7 +180,11 @@ class Attention(nn.Module):
             # multimodal rotary positions [3, T]: every frequency follows the stream of its section
             from .qwen2_5_vl import apply_rotary, mrope_cos_sin
             q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
-            cos, sin = mrope_cos_sin(positions, d, self.theta, self.mrope_section or [d // 2])
+            if self.qk_norm:
+                q = F.rms_norm(q.reshape(T * hq, d), self.q_norm, self.eps)[0]
+                k = F.rms_norm(k.reshape(T * hkv, d), self.k_norm, self.eps)[0]
+            cos, sin = mrope_cos_sin(positions, d, self.theta, self.mrope_section or [d // 2],
+                                     getattr(self, "mrope_interleaved", False))
             q, k = apply_rotary(q.reshape(T, hq, d), k.reshape(T, hkv, d), cos, sin)
             return q.contiguous(), k.contiguous(), v.reshape(T, hkv, d)
         if self.qk_norm:

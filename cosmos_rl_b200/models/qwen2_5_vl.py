@@ -141,13 +141,21 @@ def apply_rotary(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch
     return (qf * c + _rotate_half(qf) * s).to(q.dtype), (kf * c + _rotate_half(kf) * s).to(k.dtype)
 
 
-def mrope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float, sections: List[int]):
+def mrope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float, sections: List[int],
+                  interleaved: bool = False):
     """``positions [3, T]`` -> ``cos, sin [T, head_dim]``: rotary frequency ``j`` follows the stream its section belongs
-    to (the sections count frequencies: they sum to ``head_dim / 2``)."""
+    to (the sections count frequencies: they sum to ``head_dim / 2``). Chunked layout: the first ``sections[0]``
+    frequencies follow time, the next height, the rest width. ``interleaved`` (Qwen3-VL): frequencies 1, 4, 7, ... up
+    to ``3 sections[1]`` follow height, 2, 5, 8, ... up to ``3 sections[2]`` width, everything else time."""
     half = head_dim // 2
     inv = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float32, device=positions.device) / half))
-    owner = torch.repeat_interleave(torch.arange(len(sections), device=positions.device) % 3,
-                                    torch.tensor(sections, device=positions.device))
+    if interleaved:
+        owner = torch.zeros(half, dtype=torch.int64, device=positions.device)
+        owner[1:3 * sections[1]:3] = 1
+        owner[2:3 * sections[2]:3] = 2
+    else:
+        owner = torch.repeat_interleave(torch.arange(len(sections), device=positions.device) % 3,
+                                        torch.tensor(sections, device=positions.device))
     pos = positions.to(torch.float32)[owner, :]                  # [half, T]: the stream of every frequency
     freqs = (pos * inv[:, None]).transpose(0, 1)                 # [T, half]
     emb = torch.cat((freqs, freqs), dim=-1)

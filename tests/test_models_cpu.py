@@ -485,3 +485,75 @@ def test_native_internvl_matches_transformers(norm_type, qk_norm):
     for name, p in m.named_parameters():
         ref_p = torch.as_strided(want, p.shape, p.stride(), p.storage_offset())
         assert torch.equal(p.data, ref_p), name
+
+
+def test_native_qwen3_vl_moe_matches_transformers():
+    """Native Qwen3-VL-MoE (vision tower with bilinearly resampled learned positions and deep-stack taps added behind the
+    first decoder blocks, interleaved multimodal rotary positions, Qwen3-MoE decoder with stacked experts) against
+    transformers on a packed batch with two images; checkpoint names and shapes round-trip; the weight-sync plan from
+    two expert-parallel policy ranks covers an unsharded rollout model.
+    Reference family: cosmos_rl/policy/model/qwen3_vl_moe/__init__.py:356."""
+    from transformers import Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration
+    from cosmos_rl_b200.models.base import ModelRegistry
+    from cosmos_rl_b200.models.qwen3_vl_moe import Qwen3VLMoE, Qwen3VLMoEArgs
+    torch.manual_seed(0)
+    cfg = Qwen3VLMoeConfig(
+        text_config=dict(hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                         intermediate_size=128, moe_intermediate_size=32, num_experts=4, num_experts_per_tok=2,
+                         vocab_size=300, max_position_embeddings=512, decoder_sparse_step=1, mlp_only_layers=[],
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [4, 2, 2],
+                                          "mrope_interleaved": True}),
+        vision_config=dict(depth=3, hidden_size=32, num_heads=2, intermediate_size=48, out_hidden_size=64, patch_size=16,
+                           temporal_patch_size=2, spatial_merge_size=2, num_position_embeddings=36,
+                           deepstack_visual_indexes=[0, 2], in_channels=3),
+        image_token_id=290, video_token_id=291, vision_start_token_id=292, vision_end_token_id=293)
+    hf = Qwen3VLMoeForConditionalGeneration(cfg).eval().float()
+    for p in hf.parameters():
+        torch.nn.init.normal_(p, 0, 0.05)
+    state = hf.state_dict()
+    assert ModelRegistry.get("qwen3_vl_moe") is Qwen3VLMoE
+    m = Qwen3VLMoE(Qwen3VLMoEArgs.from_hf_config(cfg.to_dict())).float()
+    hf_io.load_hf_state(m, lambda k: state[k], state, cfg.to_dict())
+    grids = torch.tensor([[1, 6, 4], [1, 4, 8]])
+    pix = torch.randn(int((grids[:, 0] * grids[:, 1] * grids[:, 2]).sum()), 3 * 2 * 16 * 16)
+    seq1 = [1, 2, 3, 4, 292] + [290] * 6 + [293, 7, 8, 9]
+    seq2 = [5, 292] + [290] * 8 + [293, 11, 12]
+    ids = torch.tensor(seq1 + seq2)
+    cu = torch.tensor([0, len(seq1), len(seq1) + len(seq2)], dtype=torch.int32)
+    m.mm_inputs = {"pixel_values": pix, "image_grid_thw": grids}
+    mine = m.logits(m(ids, m.get_position_ids(cu, ids.numel()), cu, 15))
+    assert all(l.ds_rows is None for l in m.layers)                    # the taps do not outlive the call
+    ref, off = [], 0
+    with torch.no_grad():
+        for s, g in ((seq1, grids[0:1]), (seq2, grids[1:2])):
+            n = int(g[0, 0] * g[0, 1] * g[0, 2])
+            t = torch.tensor([s])
+            ref.append(hf(input_ids=t, pixel_values=pix[off:off + n], image_grid_thw=g,
+                          mm_token_type_ids=(t == 290).long()).logits[0])
+            off += n
+    ref = torch.cat(ref)
+    assert (mine - ref).abs().max().item() < 1e-4, (mine - ref).abs().max()
+    mine.square().mean().backward()
+    assert m.visual.deepstack[0].fc1.weight.grad.abs().sum() > 0 and m.visual.pos_embed.weight.grad.abs().sum() > 0
+    assert m.layers[0].mlp.w_gate_up.grad.abs().sum() > 0
+    out = hf_io.hf_state_dict(m, cfg.to_dict())
+    assert set(out) == set(state)
+    for k, v in out.items():
+        assert tuple(v.shape) == tuple(state[k].shape) and torch.allclose(v, state[k]), k
+    # weight sync: two expert-parallel policy ranks -> one rollout model that holds every expert
+    flat_dst = FlatParams(m, torch.float32, torch.device("cpu"), with_grad=False)
+    infos = []
+    for r in range(2):
+        mr = Qwen3VLMoE(Qwen3VLMoEArgs.from_hf_config(cfg.to_dict(), ep_size=2, ep_rank=r)).float()
+        hf_io.load_hf_state(mr, lambda k: state[k], state, cfg.to_dict())
+        assert mr.layers[0].mlp.w_down.shape[0] == 2
+        fr = FlatParams(mr, torch.float32, torch.device("cpu"), with_grad=False)
+        infos.append((shard_info(r, model_parts(mr, fr), fr.total), fr))
+    want = flat_dst.data.clone()
+    flat_dst.data.zero_()
+    plan = build_plan([i for i, _ in infos], shard_info(0, model_parts(m, flat_dst), flat_dst.total))
+    for src, so, sld, do, dld, rows, cols in plan:
+        torch.as_strided(flat_dst.data, (rows, cols), (dld, 1), do).copy_(
+            torch.as_strided(infos[src][1].data, (rows, cols), (sld, 1), so))
+    for name, p in m.named_parameters():
+        assert torch.equal(p.data, torch.as_strided(want, p.shape, p.stride(), p.storage_offset())), name
