@@ -585,6 +585,72 @@ def test_dit_bf16_on_gpu_matches_fp32_reference():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("family", ["qwen2_5_vl", "internvl", "qwen3_vl_moe"])
+def test_native_vision_language_models_bf16_on_gpu_match_fp32_reference(family):
+    """The native vision-language families on the GPU in bf16 (decoder with head_dim 128 on the tcgen05 attention and
+    GEMM kernels, vision towers with the head sizes of the public checkpoints) against the same weights in fp32 on the
+    CPU: logits of a packed batch with two images, and the gradient that reaches the vision tower."""
+    import copy
+    torch.manual_seed(0)
+    if family == "qwen2_5_vl":
+        from cosmos_rl_b200.models.qwen2_5_vl import Qwen25VL, Qwen25VLArgs, VisionArgs
+        a = Qwen25VLArgs(vocab_size=2048, dim=512, n_layers=2, n_heads=4, n_kv_heads=2, ffn_dim=1024, rope_theta=1e6,
+                         qkv_bias=True, model_type="qwen2_5_vl", mrope_section=[16, 24, 24], image_token_id=2000)
+        a.vision = VisionArgs(depth=3, hidden_size=160, num_heads=2, intermediate_size=216, out_hidden_size=512,
+                              window_size=56, fullatt_block_indexes=[1])
+        ref = Qwen25VL(a)
+        grids = torch.tensor([[1, 6, 4], [1, 4, 8]])
+        mm = {"pixel_values": torch.randn(56, 3 * 2 * 14 * 14), "image_grid_thw": grids}
+        n_img, probe = (6, 8), lambda m: m.visual.blocks[0].qkv.weight
+    elif family == "internvl":
+        from cosmos_rl_b200.models.internvl import InternViTArgs, InternVL, InternVLArgs
+        a = InternVLArgs(vocab_size=2048, dim=512, n_layers=2, n_heads=4, n_kv_heads=2, ffn_dim=1024, rope_theta=1e6,
+                         qkv_bias=True, model_type="internvl", image_token_id=2000)
+        a.vision = InternViTArgs(hidden_size=128, num_hidden_layers=2, num_attention_heads=2, intermediate_size=256,
+                                 image_size=56, patch_size=14)
+        ref = InternVL(a)
+        mm = {"pixel_values": torch.randn(3, 3, 56, 56)}
+        n_img, probe = (8, 4), lambda m: m.visual.blocks[0].q_proj.weight
+    else:
+        from cosmos_rl_b200.models.qwen3_vl_moe import Qwen3VisionArgs, Qwen3VLMoE, Qwen3VLMoEArgs
+        a = Qwen3VLMoEArgs(vocab_size=2048, dim=512, n_layers=3, n_heads=4, n_kv_heads=2, head_dim=128, ffn_dim=512,
+                           rope_theta=5e6, qkv_bias=False, qk_norm=True, model_type="qwen3_vl_moe", n_experts=8, top_k=2,
+                           moe_ffn_dim=256, mrope_section=[24, 20, 20], image_token_id=2000)
+        a.vision = Qwen3VisionArgs(depth=3, hidden_size=144, num_heads=2, intermediate_size=256, out_hidden_size=512,
+                                   num_position_embeddings=64, deepstack_visual_indexes=[0, 2])
+        ref = Qwen3VLMoE(a)
+        grids = torch.tensor([[1, 6, 4], [1, 4, 8]])
+        mm = {"pixel_values": torch.randn(56, 3 * 2 * 16 * 16), "image_grid_thw": grids}
+        n_img, probe = (6, 8), lambda m: m.visual.blocks[0].qkv.weight
+    ref = ref.float()
+    with torch.no_grad():
+        for n, p in ref.named_parameters():
+            p.normal_(0, 0.05) if p.dim() > 1 else p.fill_(1.0 if "norm" in n and not n.endswith("_b") else 0.0)
+    g = torch.Generator().manual_seed(1)
+    seq1 = torch.randint(0, 1900, (40,), generator=g).tolist()
+    seq2 = torch.randint(0, 1900, (25,), generator=g).tolist()
+    seq1[5:5] = [2000] * n_img[0]
+    seq2[3:3] = [2000] * n_img[1]
+    ids = torch.tensor(seq1 + seq2)
+    cu = torch.tensor([0, len(seq1), len(seq1) + len(seq2)], dtype=torch.int32)
+    ref.mm_inputs = mm
+    want = ref.logits(ref(ids, ref.get_position_ids(cu, ids.numel()), cu, len(seq1)))
+    want.square().mean().backward()
+    gpu = copy.deepcopy(ref).to("cuda", torch.bfloat16)
+    gpu.zero_grad()
+    gpu.mm_inputs = {k: v.cuda() if k == "pixel_values" else v for k, v in mm.items()}
+    cu_g = cu.cuda()
+    got = gpu.logits(gpu(ids.cuda(), gpu.get_position_ids(cu_g, ids.numel()), cu_g, len(seq1)))
+    got.square().mean().backward()
+    torch.cuda.synchronize()
+    assert native.read_status(torch.device("cuda")) == 0
+    err = (got.float().cpu() - want).abs().max()
+    assert err < 0.06 * want.abs().max() + 0.03, (family, err, want.abs().max())
+    g_ref, g_gpu = probe(ref).grad, probe(gpu).grad.float().cpu()
+    assert torch.nn.functional.cosine_similarity(g_ref.flatten(), g_gpu.flatten(), dim=0) > 0.97, family
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("rows,cols,swizzle", [(128, 128, False), (300, 2880, True), (1, 32, True), (257, 96, False)])
 def test_mxfp4_quant_matches_reference_bit_for_bit(rows, cols, swizzle):
     torch.manual_seed(9)
