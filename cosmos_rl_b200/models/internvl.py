@@ -247,6 +247,7 @@ class InternVLWeightMapper(GPTWeightMapper):
 @ModelRegistry.register(InternVLWeightMapper)
 class InternVL(GPT):
     is_vlm = True
+    paged_engine = False     # rollouts re-run the packed forward (no vision prefill in the paged engine)
 
     def __init__(self, args: InternVLArgs):
         saved, args.model_type = args.model_type, args.text_model_type       # the decoder is built as its own family

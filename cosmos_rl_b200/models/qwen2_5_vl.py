@@ -392,6 +392,7 @@ class Qwen25VLWeightMapper(GPTWeightMapper):
 @ModelRegistry.register(Qwen25VLWeightMapper)
 class Qwen25VL(GPT):
     is_vlm = True
+    paged_engine = False     # rollouts re-run the packed forward (no vision prefill in the paged engine)
 
     def __init__(self, args: Qwen25VLArgs):
         super().__init__(args)

@@ -280,6 +280,7 @@ class Qwen3VLMoEWeightMapper(Qwen3MoEWeightMapper):
 @ModelRegistry.register(Qwen3VLMoEWeightMapper)
 class Qwen3VLMoE(Qwen3MoE):
     is_vlm = True
+    paged_engine = False     # rollouts re-run the packed forward (no vision prefill in the paged engine)
 
     def __init__(self, args: Qwen3VLMoEArgs):
         super().__init__(args)

@@ -72,10 +72,11 @@ class HFRollout(RolloutBase):
 
 @RolloutRegistry.register("recompute")
 class RecomputeRollout(HFRollout):
-    """Generation for native families the paged engine has no attention path for (DeepSeek-V3's latent attention):
-    every step re-runs the packed forward over all live sequences and samples with the engine's sampling kernel. No KV
-    cache, so a step costs O(length); it keeps such families usable end to end (rollouts, weight sync, validation)
-    at small scale. The reference serves them through vLLM (cosmos_rl/rollout/vllm_rollout/vllm_rollout.py:262-326)."""
+    """Generation for native families the paged engine has no path for (DeepSeek-V3's latent attention; the native
+    vision-language models, whose prompts carry pixels and multimodal positions): every step re-runs the packed forward
+    over all live sequences and samples with the engine's sampling kernel. No KV cache, so a step costs O(length); it
+    keeps such families usable end to end (rollouts, weight sync, validation) at small scale. Pixel inputs of the live
+    sequences are handed to the model before every step. The reference serves them through vLLM (cosmos_rl/rollout/vllm_rollout/vllm_rollout.py:262-326)."""
 
     @torch.no_grad()
     def rollout_generation(self, payloads, data_packer, data_fetcher=None, is_validation: bool = False, **kw
@@ -83,7 +84,9 @@ class RecomputeRollout(HFRollout):
         from ..ops import functional as F
         sp = SamplingParams.from_config(self.config, validation=is_validation)
         model, dev = self.model, self.device
-        prompts = [list(data_packer.get_rollout_input(p.prompt)) for p in payloads]
+        items = [data_packer.get_rollout_input(p.prompt) for p in payloads]
+        prompts = [list(it["input_ids"]) if isinstance(it, dict) else list(it) for it in items]
+        mms = [it.get("mm") if isinstance(it, dict) else None for it in items for _ in range(sp.n)]
         seqs = [list(pr) for pr in prompts for _ in range(sp.n)]
         plen = [len(s) for s in seqs]
         logps: List[List[float]] = [[] for _ in seqs]
@@ -96,6 +99,10 @@ class RecomputeRollout(HFRollout):
             lens = [len(seqs[i]) for i in live]
             ids = torch.tensor([t for i in live for t in seqs[i]], dtype=torch.long, device=dev)
             cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0).tolist()), dtype=torch.int32, device=dev)
+            if getattr(model, "is_vlm", False):
+                from ..data.packer import merge_mm
+                model.mm_inputs = {k: v.to(dev) if k.startswith("pixel") else v
+                                   for k, v in merge_mm([mms[i] for i in live]).items()}
             h = model(ids, model.get_position_ids(cu, int(ids.numel())), cu, max(lens))
             last = h[(cu[1:] - 1).long()]
             logits = torch.nn.functional.linear(last, w).float().contiguous()
