@@ -625,7 +625,10 @@ def test_native_vision_language_models_bf16_on_gpu_match_fp32_reference(family):
     ref = ref.float()
     with torch.no_grad():
         for n, p in ref.named_parameters():
-            p.normal_(0, 0.05) if p.dim() > 1 else p.fill_(1.0 if "norm" in n and not n.endswith("_b") else 0.0)
+            if p.dim() > 1:
+                p.normal_(0, 0.05)
+            else:                               # norm weights 1, layer scales 0.1, biases 0
+                p.fill_(1.0 if "norm" in n and not n.endswith("_b") else (0.1 if "scale" in n else 0.0))
     g = torch.Generator().manual_seed(1)
     seq1 = torch.randint(0, 1900, (40,), generator=g).tolist()
     seq2 = torch.randint(0, 1900, (25,), generator=g).tolist()
