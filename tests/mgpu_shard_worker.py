@@ -29,7 +29,7 @@ def main():
                        "parallelism": {"tp_size": 1, "cp_size": 1, "pp_size": 1, "dp_shard_size": world}},
             "b200": dict({"recompute": "swiglu"}, **b200),
             "train": {"seed": 0, "optm_lr": 1e-4, "optm_warmup_steps": 0, "output_dir": out_dir,
-                      "optm_grad_norm_clip": 1.0, "fsdp_reduce_dtype": "float32",
+                      "optm_grad_norm_clip": 1.0, "fsdp_reduce_dtype": os.environ.get("SHARD_REDUCE_DTYPE", "float32"),
                       "train_policy": {"type": "sft", "trainer_type": "sft", "mini_batch": 4},
                       "ckpt": {"enable_checkpoint": False}}})
     g = torch.Generator().manual_seed(5 + rank)
