@@ -67,6 +67,19 @@ class SFTPolicyWorker(CommMixin):
         if config.train.max_num_steps:
             self.total_steps = min(self.total_steps, config.train.max_num_steps)
         self.history: List[dict] = []
+        self.sample_cache = None
+        if tp.enable_dataset_cache and self.dataset is not None:
+            # processed samples (tokenised conversations, image-processor outputs) are kept on disk per sample index;
+            # the folder name carries the data set, the model and the length limit, which decide the processed form
+            import hashlib
+            import os
+            from ...utils.cache import DiskCache
+            key = hashlib.sha1(repr((getattr(tp.dataset, "name", ""), getattr(tp.dataset, "subset", ""),
+                                     config.policy.model_name_or_path, config.policy.model_max_length,
+                                     getattr(tp, "conversation_column_name", ""))).encode()).hexdigest()[:16]
+            root = os.environ.get("COSMOS_CACHE", os.path.join(os.path.expanduser("~"), ".cache", "cosmos"))
+            self.sample_cache = DiskCache(os.path.join(root, "datasets_cache", f"{getattr(tp.dataset, 'name', 'dataset') or 'dataset'}-{key}"))
+            logger.info("[SFT] processed samples are cached under %s", self.sample_cache.path)
         self.balancer = None
         if tp.enable_dp_load_balancing and self.dataset is not None:
             # token-budgeted batches from a per-rank pool instead of a fixed sample count per rank; the cost of a
@@ -118,7 +131,19 @@ class SFTPolicyWorker(CommMixin):
         order = self._epoch_order(epoch)
         per_step = self.batch_per_rank * self.dp
         idxs = order[k * per_step:(k + 1) * per_step][self.dp_rank::self.dp]
-        return [self.dataset[i] for i in idxs]
+        return [self._sample(i) for i in idxs]
+
+    def _sample(self, i: int) -> Any:
+        """Sample ``i``, processed once and read back from the disk cache afterwards when the cache is on."""
+        if self.sample_cache is None:
+            return self.dataset[i]
+        got = self.sample_cache.get(i)
+        if got is None:
+            got = self.trainer.data_packer.sft_process_sample(self.dataset[i])
+            self.sample_cache.set(i, got)
+        flat = dict(got)
+        flat.update(flat.pop("mm", None) or {})        # processed vision inputs go back where the packer looks for them
+        return flat
 
     def validate(self, step: int) -> Optional[float]:
         if self.val_dataset is None:

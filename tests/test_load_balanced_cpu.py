@@ -1,4 +1,5 @@
 """Token-balanced SFT batching: batcher rules and the standalone SFT worker on top of it."""
+import os
 import random
 
 import pytest
@@ -103,3 +104,38 @@ def test_standalone_sft_worker_fixed_batches(tmp_path):
     assert w.balancer is None and w.steps_per_epoch == 4 and w.total_steps == 4
     w.main_loop()
     assert [h["step"] for h in w.history] == [1, 2, 3, 4]
+
+
+def test_dataset_cache_serves_processed_samples_from_disk(tmp_path, monkeypatch):
+    """``enable_dataset_cache``: the first epoch processes every sample and writes it, the second epoch reads them back
+    (no call of the data packer's processing), and training sees the same samples either way. Plus the cache's own
+    contract: background writes through a temporary name, misses, clearing."""
+    from cosmos_rl_b200.policy.worker.sft_worker import SFTPolicyWorker
+    from cosmos_rl_b200.utils.cache import DiskCache
+    c = DiskCache(str(tmp_path / "c"), files_per_dir=2)
+    assert c.get(5) is None and c.set(5, {"a": torch.arange(3)}) and c.set(0, "x")
+    c.flush()
+    assert torch.equal(c.get(5)["a"], torch.arange(3)) and c.get(0) == "x" and c.hits == 2 and c.misses == 1
+    assert sorted(os.listdir(tmp_path / "c")) == ["0", "2"]              # sub-folders of two files
+    c.clear()
+    assert not os.path.exists(tmp_path / "c") and not c.set(1, "y")
+    monkeypatch.setenv("COSMOS_CACHE", str(tmp_path / "cache"))
+    cfg = _sft_config(tmp_path, enable_dataset_cache=True)
+    cfg.train.epoch, cfg.train.max_num_steps = 2, 8
+    cfg.train.ckpt.enable_checkpoint = False
+    ds = _dataset(16, hi=40)
+    w = SFTPolicyWorker(cfg, ParallelDims(world_size=1, device=torch.device("cpu")), dataset=ds, standalone=True,
+                        device=torch.device("cpu"))
+    calls = []
+    orig = w.trainer.data_packer.sft_process_sample
+    w.trainer.data_packer.sft_process_sample = lambda s: (calls.append(1), orig(s))[1]
+    n_steps = w.total_steps
+    for step in range(n_steps // 2):
+        w._batch(step)
+    w.sample_cache.flush()
+    first = len(calls)
+    assert first == 16 and w.sample_cache.hits == 0
+    for step in range(n_steps // 2, n_steps):
+        w._batch(step)
+    assert len(calls) == first and w.sample_cache.hits == 16          # the second epoch never processed a sample
+    assert w._sample(3)["input_ids"] == orig(ds[3])["input_ids"]
