@@ -47,7 +47,7 @@ class LatentStore:
 
 
 def diffusion_options(config) -> Dict[str, Any]:
-    d = dict(sample_steps=10, sampler="ode", noise_level=0.7, shift=1.0, guidance=1.0, latent_shape=[4, 8, 8],
+    d = dict(sample_steps=10, sampler="ode", solver="euler", noise_level=0.7, shift=1.0, guidance=1.0, latent_shape=[4, 8, 8],
              nft_beta=1.0, train_timesteps=4, old_decay="ramp", timestep_scheme="logit_normal")
     d.update(config.custom.get("diffusion", {}))
     return d
@@ -105,6 +105,10 @@ class DiffusionRollout(RolloutGenerationMixin, RolloutBase):
             if o["sampler"] == "sde" and not is_validation:
                 return D.sde_sample(model, noise[rows], text[rows], mask[rows], o["sample_steps"], o["shift"],
                                     o["noise_level"])
+            if o.get("solver", "euler") != "euler":       # higher-order / multistep ODE solvers (policy/diffusion_solvers.py)
+                from ..policy.diffusion_solvers import sample
+                return {"x0": sample(model, noise[rows], text[rows], mask[rows], o["sample_steps"], o["shift"],
+                                     solver=o["solver"])}
             return {"x0": D.euler_sample(model, noise[rows], text[rows], mask[rows], o["sample_steps"], o["shift"])}
 
         # rollout.n_generation_mini_batch: the sampler sees that many latents at a time (activation memory of a large

@@ -212,3 +212,46 @@ def test_ode_solvers_converge_at_their_order_on_a_gaussian_flow():
     assert abs(float(sm.log().mean()) + 1.2) < 0.1 and sm.min() >= 0.002 and sm.max() <= 80.0
     ks = karras_sigmas(10)
     assert ks.shape == (11,) and abs(float(ks[0]) - 80.0) < 1e-3 and ks[-1] == 0 and bool((ks[:-1].diff() < 0).all())
+
+
+def test_causal_video_vae_shapes_causality_and_training():
+    """The tokenizer in front of the DiT: 1 + 4 k frames -> 1 + k latent frames at 1/8 resolution and back; a single
+    frame is a valid clip; latents of a prefix equal the prefix of the latents (nothing flows from the future, neither
+    in the encoder nor in the decoder); a few optimisation steps reduce the reconstruction loss; latent statistics
+    normalise what the DiT sees."""
+    from cosmos_rl_b200.models.video_vae import VideoVAE, VideoVAEArgs
+    torch.manual_seed(0)
+    vae = VideoVAE(VideoVAEArgs(base_dim=8, dim_mult=(1, 2, 2, 2), num_res_blocks=1, z_dim=4))
+    assert vae.args.spatial_factor == 8 and vae.args.temporal_factor == 4 and vae.latent_frames(9) == 3
+    x = torch.rand(2, 3, 9, 32, 32) * 2 - 1
+    mean, logvar = vae.encode(x)
+    assert mean.shape == (2, 4, 3, 4, 4) == logvar.shape
+    assert vae.decode(vae.tokenize(x)).shape == x.shape
+    assert vae.encode(x[:, :, :1])[0].shape == (2, 4, 1, 4, 4) and vae.decode(mean[:, :, :1], False).shape == (2, 3, 1, 32, 32)
+    with pytest.raises(ValueError):
+        vae.encode(x[:, :, :8])
+    with torch.no_grad():
+        # encoder: frames 5.. do not reach latent frames 0 and 1 (which cover pixel frames 0..4)
+        y = x.clone()
+        y[:, :, 5:] = torch.rand(2, 3, 4, 32, 32)
+        m2 = vae.encode(y)[0]
+        assert torch.allclose(m2[:, :, :2], mean[:, :, :2], atol=1e-5) and not torch.allclose(m2[:, :, 2], mean[:, :, 2], atol=1e-3)
+        assert torch.allclose(vae.encode(x[:, :, :5])[0], mean[:, :, :2], atol=1e-5)       # prefix of a clip
+        # decoder: the last latent frame does not reach pixel frames 0..4
+        z2 = mean.clone()
+        z2[:, :, 2] += 1.0
+        a, b = vae.decode(mean, False), vae.decode(z2, False)
+        assert torch.allclose(a[:, :, :5], b[:, :, :5], atol=1e-5) and not torch.allclose(a[:, :, 5:], b[:, :, 5:], atol=1e-3)
+    opt = torch.optim.Adam(vae.parameters(), lr=2e-3)
+    clip = torch.sin(torch.linspace(0, 6, 32))[None, None, None, None, :].expand(1, 3, 5, 32, 32).contiguous()
+    first = None
+    for _ in range(30):
+        out = vae.loss(clip)
+        opt.zero_grad()
+        out["loss"].backward()
+        opt.step()
+        first = first if first is not None else float(out["rec"])
+    assert float(out["rec"]) < 0.7 * first, (first, float(out["rec"]))
+    vae.fit_latent_stats([clip, x[:1, :, :5]])
+    z = vae.tokenize(torch.cat([clip, x[:1, :, :5]]))
+    assert z.transpose(0, 1).reshape(4, -1).mean(1).abs().max() < 0.2
