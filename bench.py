@@ -44,8 +44,9 @@ def parse_args():
                          "on a separated layout (policy on the first half of the GPUs, rollout TP 1/2/4 on the "
                          "second half; bf16 pull, fused fp8 pull, and the reference-style fp32 send/recv route). The "
                          "MoE and long-context configurations are not wired into this script")
-    ap.add_argument("--layout", default="auto", choices=["auto", "colocated", "disaggregated"],
-                    help="auto: 8 GPUs use the named disaggregated layout (policy FSDP4 + rollout TP2 x 2); 1, 2 and 4 "
+    ap.add_argument("--layout", default="auto", choices=["auto", "colocated", "disaggregated", "launcher"],
+                    help="launcher: start the same job through launcher.launch_all (controller, broker and workers as "
+                         "a user's job runs) and read tokens/s from the controller's step reports; auto: 8 GPUs use the named disaggregated layout (policy FSDP4 + rollout TP2 x 2); 1, 2 and 4 "
                          "GPUs run colocated data-parallel replicas (each GPU generates and trains its own prompts)")
     return ap.parse_args()
 
@@ -220,6 +221,12 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.layout == "launcher":
+        # the job starts its own processes: under a multi-rank launch only rank 0 acts, and it holds no GPU itself
+        if int(os.environ.get("RANK", "0")) == 0:
+            from cosmos_rl_b200.bench_launcher import run
+            print(json.dumps(run(args)))
+        return 0
     import torch
     import torch.distributed as dist
     rank = int(os.environ.get("RANK", "0"))

@@ -207,3 +207,22 @@ def test_sft_job_with_two_policy_replicas(tmp_path):
     a, b = steps["policy_0.log"], steps["policy_1.log"]
     assert [s[3] for s in a] == [s[3] for s in b], detail                 # one averaged gradient
     assert [s[2] for s in a] != [s[2] for s in b], detail                 # from different halves of the batch
+
+
+@pytest.mark.timeout(300)
+def test_launcher_layout_benchmark_reads_the_controllers_step_reports():
+    """``bench.py --layout launcher``: the job runs through ``launcher.launch_all`` and the figure comes from the
+    stamps of the controller's step reports (here the colocated worker on CPU with a tiny model)."""
+    import argparse
+    from cosmos_rl_b200 import bench_launcher as BL
+    rows = [{"step": s, "time": 100.0 + 2.0 * s} for s in range(1, 5)]
+    t = BL.throughput(rows, warmup=1, steps=3, tokens_per_step=1000)
+    assert abs(t["value"] - 500.0) < 1e-9 and abs(t["ms_per_step"] - 2000.0) < 1e-6
+    with pytest.raises(ValueError):
+        BL.throughput(rows, warmup=2, steps=3, tokens_per_step=1000)
+    assert BL.job_layout(1)[0] == "colocated" and BL.job_layout(8) == ("disaggregated", 4, 2, 2)
+    a = argparse.Namespace(gpus=1, steps=2, warmup=1, model="tiny-qwen2", prompts_per_gpu=2, group=2, prompt_len=16,
+                           max_response=8, mb_tokens=256, rdzv_port=29781)
+    out = BL.run(a, cpu=True, timeout_s=240)
+    assert out["breakdown"]["steps_reported"] == 3 and out["value"] > 0
+    assert out["breakdown"]["tokens_trained_per_step"] == 2 * 2 * 24 and out["config"]["layout"] == "launcher"
