@@ -35,6 +35,9 @@ def parse_args(argv=None):
     ap.add_argument("--worker-idx", type=int, default=0, help="index of this node")
     ap.add_argument("--node-ip-list", default=None, help="semicolon separated node addresses (multi-node)")
     ap.add_argument("--rdzv-port", type=int, default=29345)
+    ap.add_argument("--gpus-per-node", type=int, default=None,
+                    help="GPUs of every node of the job (default: what this node shows); with --cpu it is the number "
+                         "of ranks one node hosts")
     ap.add_argument("--cpu", action="store_true", help="run every replica on CPU (gloo); for plumbing tests")
     ap.add_argument("--share-gpus", action="store_true",
                     help="let replicas wrap around the node's GPUs when the job asks for more than there are (several "
@@ -109,6 +112,56 @@ def place_replicas(n_policy: int, n_rollout: int, n_ref: int, config: Config, n_
     return out
 
 
+def plan_nodes(n_policy: int, n_rollout: int, n_ref: int, config: Config, gpus_per_node: int) -> List[List[Dict]]:
+    """Place every replica of the job on the nodes of the job; every node's launcher computes the same plan and starts
+    its own row (cosmos_rl/launcher/utility.py:584-760 does the same walk).
+
+    Roles are placed in the order policy, rollout, reference. A replica that fits a node takes the next free GPUs of
+    the current node, or starts the next node when they do not suffice. A replica larger than a node spans
+    ``gpus / gpus_per_node`` whole nodes (it must divide), starting on a fresh node; each of those nodes runs one
+    ``torchrun`` of the replica with ``nnodes`` / ``node_rank`` and the first node of the span as the rendezvous host.
+    In ``colocated_separated`` mode the rollout replicas restart at node 0, GPU 0 (they share the policies' GPUs).
+    Entries: ``role, index, ordinal`` (replica number over the whole job, fixes the rendezvous port), ``gpus, nproc,
+    nnodes, node_rank, rdzv_node``."""
+    G = gpus_per_node
+    if G <= 0:
+        raise ValueError("gpus_per_node must be positive")
+    sizes = {"policy": gpus_per_replica(config.policy.parallelism),
+             "rollout": gpus_per_replica(config.rollout.parallelism),
+             "reference": gpus_per_replica(config.distillation.parallelism)}
+    nodes: List[List[Dict]] = [[]]
+    node, gpu, ordinal = 0, 0, 0
+
+    def row(i: int) -> List[Dict]:
+        while len(nodes) <= i:
+            nodes.append([])
+        return nodes[i]
+
+    for role, n in (("policy", n_policy), ("rollout", n_rollout), ("reference", n_ref)):
+        if role == "rollout" and config.mode == "colocated_separated":
+            node, gpu = 0, 0
+        k = sizes[role]
+        for i in range(n):
+            ordinal += 1
+            if k > G:
+                if k % G:
+                    raise ValueError(f"a {role} replica of {k} GPUs does not divide into nodes of {G}")
+                if gpu > 0:
+                    node, gpu = node + 1, 0
+                span = k // G
+                for j in range(span):
+                    row(node + j).append({"role": role, "index": i, "ordinal": ordinal, "gpus": list(range(G)),
+                                          "nproc": G, "nnodes": span, "node_rank": j, "rdzv_node": node})
+                node += span
+                continue
+            if gpu + k > G:
+                node, gpu = node + 1, 0
+            row(node).append({"role": role, "index": i, "ordinal": ordinal, "gpus": list(range(gpu, gpu + k)),
+                              "nproc": k, "nnodes": 1, "node_rank": 0, "rdzv_node": node})
+            gpu += k
+    return nodes
+
+
 def reserve_port(port: Optional[int]) -> Tuple[socket.socket, int]:
     """Bind the controller's listening socket here and hand the descriptor to the controller process, so the
     port cannot be taken by someone else between choosing it and serving on it."""
@@ -147,9 +200,21 @@ def main(argv=None) -> int:
         n_gpus = 0 if args.cpu else torch.cuda.device_count()
     except Exception:
         n_gpus = 0
-    n_policy, n_rollout, n_ref = replica_counts(config, args, n_gpus)
-    placement = place_replicas(n_policy, n_rollout, n_ref, config, n_gpus,
-                               config.mode in ("colocated", "colocated_separated"), share=args.share_gpus)
+    per_node = args.gpus_per_node or n_gpus
+    n_policy, n_rollout, n_ref = replica_counts(config, args, per_node * max(1, args.num_workers))
+    ips = args.node_ip_list.split(";") if args.node_ip_list else []
+    if args.num_workers > 1:
+        # a job of several nodes: --policy / --rollout count the replicas of the WHOLE job, every node's launcher
+        # derives the same plan and starts its own row of it
+        plan = plan_nodes(n_policy, n_rollout, n_ref, config, per_node)
+        if len(plan) > args.num_workers:
+            raise ValueError(f"the job needs {len(plan)} nodes of {per_node} GPUs, --num-workers is {args.num_workers}")
+        if any(e["nnodes"] > 1 for row in plan for e in row) and len(ips) < len(plan):
+            raise ValueError("a replica spans several nodes: --node-ip-list must name every node of the job")
+        placement = plan[args.worker_idx] if args.worker_idx < len(plan) else []
+    else:
+        placement = place_replicas(n_policy, n_rollout, n_ref, config, n_gpus,
+                                   config.mode in ("colocated", "colocated_separated"), share=args.share_gpus)
     log_dir = None
     if args.log_dir:
         log_dir = os.path.join(args.log_dir, time.strftime("logs_%Y%m%d-%H%M%S"))
@@ -203,6 +268,12 @@ def main(argv=None) -> int:
     controller = None
     if args.url:
         host = args.url
+    elif args.worker_idx > 0:
+        # a further node of the job: the controller lives on node 0 at the agreed port
+        if not (ips and args.port):
+            raise ValueError("a node with --worker-idx > 0 needs --url, or --node-ip-list together with --port")
+        host = f"{ips[0]}:{args.port}"
+        wait_for_url(f"http://{host}", timeout_s=600.0)
     else:
         sock, port = reserve_port(args.port)
         host = f"127.0.0.1:{port}"
@@ -214,13 +285,14 @@ def main(argv=None) -> int:
             controller = spawn("controller", cmd, env, pass_fds=(sock.fileno(),))
             wait_for_url(f"http://{host}")
         sock.close()
-    ips = args.node_ip_list.split(";") if args.node_ip_list else []
     ctrl_hosts = host if not ips else ";".join(f"{ip}:{host.split(':')[1]}" for ip in ips[:1])
 
     rdzv = args.rdzv_port
     for rep in placement:
         env = dict(env_base, COSMOS_ROLE=rep["role"].capitalize(), COSMOS_CONTROLLER_HOST=ctrl_hosts,
                    COSMOS_REPLICA_TAG=f"{rep['role']}_{rep['index']}")
+        if args.num_workers > 1:
+            env["COSMOS_NODE_INDEX"] = str(args.worker_idx)
         if rep["gpus"] and n_gpus:
             env["CUDA_VISIBLE_DEVICES"] = ",".join(str(g) for g in rep["gpus"])
         elif args.cpu or not n_gpus:
@@ -231,9 +303,16 @@ def main(argv=None) -> int:
                   "reference": "cosmos_rl_b200.reference.reference_entry"}[rep["role"]]
         target = script if script else ["-m", module]
         rdzv += 1
-        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={max(1, rep['nproc'])}",
-               "--master-addr", "127.0.0.1", "--master-port", str(rdzv)] + \
-              (target if script else ["--module", module])
+        nnodes, master, port_ = rep.get("nnodes", 1), "127.0.0.1", rdzv
+        if "ordinal" in rep:
+            port_ = args.rdzv_port + rep["ordinal"]          # the same port on every node of the replica's span
+        if nnodes > 1 and rep["rdzv_node"] != args.worker_idx:
+            master = ips[rep["rdzv_node"]]
+        cmd = [sys.executable, "-m", "torch.distributed.run", f"--nnodes={nnodes}",
+               f"--nproc-per-node={max(1, rep['nproc'])}", "--master-addr", master, "--master-port", str(port_)]
+        if nnodes > 1:
+            cmd += [f"--node-rank={rep['node_rank']}"]
+        cmd += target if script else ["--module", module]
         spawn(f"{rep['role']}_{rep['index']}", cmd, env)
 
     policy_procs = [p for n, p in procs if n.startswith("policy")]

@@ -65,8 +65,12 @@ class RLPolicyWorker(CommMixin):
             trainer_kw["allocator"] = peer_allocator(self.device)
         trainer_kw.update(kw)
         self.trainer = TrainerRegistry.get_trainer_cls(tp.trainer_type)(config, parallel_dims, **trainer_kw)
+        from ...utils.dist_util import group_on_one_host
         if (parallel_dims.dp_shard > 1 and self.device.type == "cuda" and config.b200.peer_weight_sync
-                and not getattr(self.trainer, "shard_params", False)):
+                and not getattr(self.trainer, "shard_params", False)
+                and group_on_one_host(parallel_dims.group("dp_shard"))):
+            # peer loads / stores need every rank of the group on this machine; a group that spans machines keeps
+            # the NCCL reduce-scatter / all-gather of the optimizer
             from ...parallel.fsdp import PeerCollective
             self.trainer.optimizer.collective = PeerCollective(self.trainer.flat, parallel_dims.group("dp_shard"))
         self.data_queue: "queue.Queue[Rollout]" = queue.Queue()
@@ -131,7 +135,8 @@ class RLPolicyWorker(CommMixin):
         if buf is not None:
             info["ipc_handle"] = buf.export()
             info["nbytes"] = buf.nbytes
-            info["host"] = __import__("socket").gethostname()
+            from ...utils.dist_util import host_id
+            info["host"] = host_id()
         infos = [None] * self.world_size
         if self.world_size > 1:
             dist.all_gather_object(infos, info)
@@ -229,7 +234,7 @@ class RLPolicyWorker(CommMixin):
         if self.device.type == "cuda":
             torch.cuda.synchronize()
         key = f"p2r:{c.uuid_value}"
-        if self._peer_mode():
+        if self._peer_mode() and self._pair_transport(c) == "peer":
             if self.world_size > 1:
                 dist.barrier()
             if self.global_rank == 0:
@@ -267,6 +272,30 @@ class RLPolicyWorker(CommMixin):
                 t = torch.as_strided(flat, (d[5], d[6]), (d[2], 1), flat.storage_offset() + d[1]).contiguous()
                 comm.send(t.to(tdt) if tdt is not None else t, P + dst_rank)
         return False
+
+    def _pair_transport(self, c) -> str:
+        """"peer" or "collective" for this (policy replica, rollout replica) pair. The rollout replica knows where the
+        policy's buffers live (the posted shard infos carry the machine's identity) and announces its choice under
+        ``p2r-mode:<src>:<dst>``; rank 0 reads it once per pair and tells the other ranks."""
+        pair = f"p2r-mode:{c.src_replica_name}:{c.dst_replica_name}"
+        cache = self.__dict__.setdefault("_pair_modes", {})
+        if pair not in cache:
+            box = [None]
+            if self.global_rank == 0:
+                deadline = time.time() + 600
+                while box[0] is None and time.time() < deadline:
+                    v = self.broker.kv_get(pair)
+                    if v:
+                        box[0] = v.decode() if isinstance(v, (bytes, bytearray)) else str(v)
+                    else:
+                        time.sleep(0.01)
+                if box[0] is None:
+                    raise TimeoutError(f"rollout replica {c.dst_replica_name} never announced its weight transport")
+            if self.world_size > 1:
+                dist.broadcast_object_list(box, src=0)
+            cache[pair] = box[0]
+            logger.info("[Policy] weights for %s travel by the %s transport", c.dst_replica_name, box[0])
+        return cache[pair]
 
     def _peer_mode(self) -> bool:
         return bool(self.config.b200.peer_weight_sync and self.device.type == "cuda"

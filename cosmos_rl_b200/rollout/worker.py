@@ -118,7 +118,7 @@ class DisaggregatedRolloutControlWorker(CommMixin):
             return False
         t0 = time.perf_counter()
         key = f"p2r:{c.uuid_value}"
-        peer = bool(self.config.b200.peer_weight_sync and self.device.type == "cuda")
+        peer = self._pair_transport(c) == "peer"
         check = None
         if getattr(c, "do_weight_sync_check", False) and getattr(self.rollout, "flat", None) is not None \
                 and not c.trainable_only:
@@ -154,6 +154,37 @@ class DisaggregatedRolloutControlWorker(CommMixin):
         logger.info("[Rollout] weights of step %s received: transport=%s, %.1f ms, device %s", c.weight_step,
                     "peer" if peer else "collective", self.stats["sync_ms"][-1], self.device)
         return False
+
+    def _pair_transport(self, c) -> str:
+        """Choose how the weights of this (policy replica, rollout replica) pair travel: "peer" (this replica reads the
+        policy's buffers through CUDA IPC mappings) needs every policy rank's buffer exported and on this machine,
+        for every rank of this replica; otherwise "collective" (send / recv over the pair's communicator, which also
+        crosses machines). Decided once per pair and announced to the policy under ``p2r-mode:<src>:<dst>``."""
+        pair = f"p2r-mode:{c.src_replica_name}:{c.dst_replica_name}"
+        cache = self.__dict__.setdefault("_pair_modes", {})
+        if pair in cache:
+            return cache[pair]
+        from ..utils.dist_util import host_id
+        pol, deadline = self._policy_infos(), time.time() + 600
+        while pol is None:                              # the policy posts them when it takes up the same command
+            if time.time() > deadline:
+                raise TimeoutError("the policy replica never posted its shard infos")
+            time.sleep(0.02)
+            pol = self._policy_infos()
+        exported = all("ipc_handle" in i for i in pol["ranks"])
+        if not exported:
+            cache[pair] = "collective"                  # the policy serves no buffers: it does not wait for a choice
+            return cache[pair]
+        mine = bool(self.config.b200.peer_weight_sync and self.device.type == "cuda"
+                    and all(i.get("host") == host_id() for i in pol["ranks"]))
+        if self.world_size > 1:
+            votes = [None] * self.world_size
+            dist.all_gather_object(votes, mine)
+            mine = all(votes)
+        cache[pair] = "peer" if mine else "collective"
+        if self.global_rank == 0:
+            self.broker.kv_set(pair, cache[pair].encode(), ttl_s=7 * 24 * 3600)
+        return cache[pair]
 
     def _peer_pull(self, c, key: str) -> None:
         from ..parallel.peer import PeerMapping

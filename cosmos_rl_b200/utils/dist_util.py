@@ -53,3 +53,29 @@ def safe_destroy(timeout_s: float = 20.0, exit_code: int = 0) -> None:
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(exit_code)
+
+
+def host_id() -> str:
+    """Identity of the machine this process runs on: host name plus the kernel's boot id (two processes that agree on
+    it can exchange CUDA IPC handles; two that do not must talk through a network transport). ``COSMOS_HOST_ID``
+    overrides it (tests that stand in several machines on one)."""
+    forced = os.environ.get("COSMOS_HOST_ID")
+    if forced:
+        return forced
+    import socket
+    boot = ""
+    try:
+        with open("/proc/sys/kernel/random/boot_id") as f:
+            boot = f.read().strip()
+    except OSError:
+        pass
+    return f"{socket.gethostname()}:{boot}"
+
+
+def group_on_one_host(group=None) -> bool:
+    """True when every rank of ``group`` (default: the world) runs on the same machine."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return True
+    ids = [None] * dist.get_world_size(group)
+    dist.all_gather_object(ids, host_id(), group=group)
+    return len(set(ids)) == 1

@@ -560,3 +560,37 @@ def test_pair_payload_transport_registry_cache_and_transfers():
     class C:
         custom = {"nccl_payload_transfer": True}
     assert get_payload_transfer_mode(C) == "nccl"
+
+
+def test_launcher_plan_over_nodes_and_machine_identity(monkeypatch):
+    """The job-wide plan every node's launcher derives: policies first, packing within a node, a replica larger than
+    a node spans whole nodes from a fresh one (node rank and rendezvous node recorded), colocated_separated rollouts
+    restart at node 0; and the machine identity that decides between peer memory and a network transport."""
+    from cosmos_rl_b200.config import Config
+    from cosmos_rl_b200.launcher import launch_all as L
+    from cosmos_rl_b200.utils.dist_util import group_on_one_host, host_id
+    base = {"policy": {"model_name_or_path": "tiny-qwen2", "parallelism": {"tp_size": 2, "dp_shard_size": 8}},
+            "rollout": {"parallelism": {"tp_size": 4}}, "train": {"train_policy": {"type": "grpo"}}}
+    plan = L.plan_nodes(2, 3, 0, Config.from_dict(base), 8)
+    assert len(plan) == 6
+    assert [(e["index"], e["nnodes"], e["node_rank"], e["rdzv_node"]) for r in plan[:4] for e in r] == \
+        [(0, 2, 0, 0), (0, 2, 1, 0), (1, 2, 0, 2), (1, 2, 1, 2)]
+    assert [(e["role"], e["index"], e["gpus"]) for e in plan[4]] == [("rollout", 0, [0, 1, 2, 3]), ("rollout", 1, [4, 5, 6, 7])]
+    assert [(e["role"], e["index"], e["gpus"]) for e in plan[5]] == [("rollout", 2, [0, 1, 2, 3])]
+    assert sorted({e["ordinal"] for r in plan for e in r}) == [1, 2, 3, 4, 5]     # one rendezvous port per replica
+    base["policy"]["parallelism"] = {"tp_size": 1, "dp_shard_size": 3}
+    small = L.plan_nodes(1, 2, 0, Config.from_dict(base), 8)
+    assert [(e["role"], e["gpus"]) for e in small[0]] == [("policy", [0, 1, 2]), ("rollout", [3, 4, 5, 6])]
+    assert [(e["role"], e["gpus"]) for e in small[1]] == [("rollout", [0, 1, 2, 3])]        # 4 GPUs no longer fit node 0
+    base["policy"]["parallelism"] = {"tp_size": 1, "dp_shard_size": 12}
+    with pytest.raises(ValueError):
+        L.plan_nodes(1, 0, 0, Config.from_dict(base), 8)                        # 12 GPUs do not divide into nodes of 8
+    sep = dict(base, mode="colocated_separated")
+    sep["policy"] = {"model_name_or_path": "tiny-qwen2", "parallelism": {"tp_size": 4, "dp_shard_size": 1}}
+    p = L.plan_nodes(2, 2, 0, Config.from_dict(sep), 8)
+    assert [(e["role"], e["gpus"]) for e in p[0]] == [("policy", [0, 1, 2, 3]), ("policy", [4, 5, 6, 7]),
+                                                       ("rollout", [0, 1, 2, 3]), ("rollout", [4, 5, 6, 7])]
+    monkeypatch.setenv("COSMOS_HOST_ID", "machine-a")
+    assert host_id() == "machine-a" and group_on_one_host()
+    monkeypatch.delenv("COSMOS_HOST_ID")
+    assert ":" in host_id()

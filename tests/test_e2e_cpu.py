@@ -226,3 +226,59 @@ def test_launcher_layout_benchmark_reads_the_controllers_step_reports():
     out = BL.run(a, cpu=True, timeout_s=240)
     assert out["breakdown"]["steps_reported"] == 3 and out["value"] > 0
     assert out["breakdown"]["tokens_trained_per_step"] == 2 * 2 * 24 and out["config"]["layout"] == "launcher"
+
+
+@pytest.mark.timeout(420)
+def test_job_over_three_nodes_with_a_policy_replica_that_spans_two(tmp_path):
+    """Three launchers stand in three nodes of two ranks each (``--num-workers 3 --gpus-per-node 2``): every one
+    derives the same plan from the job-wide replica counts. The policy replica (dp_shard 4) spans nodes 0 and 1 (two
+    ``torchrun`` groups that meet at node 0's rendezvous port), the rollout replica lands on node 2; nodes 1 and 2
+    find the controller of node 0 through ``--node-ip-list`` and ``--port``. Each node claims its own machine
+    identity, so the weights take the communicator route."""
+    import socket
+    import time as _time
+    from cosmos_rl_b200.config import dump_toml, load_toml
+    from cosmos_rl_b200.launcher import launch_all as L
+    from cosmos_rl_b200.config import Config
+    raw = load_toml(os.path.join(HERE, "configs", "tiny_grpo_cpu.toml"))
+    raw["policy"]["parallelism"]["dp_shard_size"] = 4
+    raw["train"]["output_dir"] = str(tmp_path / "out")
+    cfg = tmp_path / "job.toml"
+    cfg.write_text(dump_toml(raw))
+    plan = L.plan_nodes(1, 1, 0, Config.from_dict(raw), 2)
+    assert [[(e["role"], e["nnodes"], e["node_rank"], e["rdzv_node"]) for e in row] for row in plan] == \
+        [[("policy", 2, 0, 0)], [("policy", 2, 1, 0)], [("rollout", 1, 0, 2)]]
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    procs = []
+    import signal
+    try:
+        for idx in range(3):
+            env = dict(os.environ, COSMOS_LOG_LEVEL="INFO", COSMOS_HEARTBEAT_SEND_INTERVAL="2", PYTHONPATH=ROOT,
+                       OMP_NUM_THREADS="1", COSMOS_HOST_ID=f"node{idx}")
+            cmd = [sys.executable, "-m", "cosmos_rl_b200.launcher.launch_all", "--config", str(cfg), "--policy", "1",
+                   "--rollout", "1", "--cpu", "--num-workers", "3", "--worker-idx", str(idx), "--gpus-per-node", "2",
+                   "--node-ip-list", "127.0.0.1;127.0.0.1;127.0.0.1", "--port", str(port), "--rdzv-port", "29801",
+                   "--log-dir", str(tmp_path / f"logs{idx}"), os.path.join(HERE, "e2e_script.py")]
+            procs.append(subprocess.Popen(cmd, env=env, cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                                          text=True, start_new_session=True))
+        deadline = _time.time() + 380
+        while _time.time() < deadline and any(p.poll() is None for p in procs):
+            _time.sleep(0.5)
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                os.killpg(p.pid, signal.SIGKILL)          # the groups this test started, by their exact ids
+    outs = [p.communicate()[0] for p in procs]
+    logs = {}
+    for idx in range(3):
+        d = tmp_path / f"logs{idx}" / "logs_latest"
+        for f in (sorted(os.listdir(d)) if d.exists() else []):
+            logs[f"node{idx}/{f}"] = open(d / f).read()
+    detail = "\n".join(f"==== {k}\n{v[-2500:]}" for k, v in logs.items()) + "\n".join(o[-1500:] for o in outs)
+    assert [p.returncode for p in procs] == [0, 0, 0], detail
+    assert sorted(logs) == ["node0/controller.log", "node0/policy_0.log", "node1/policy_0.log", "node2/rollout_0.log"]
+    assert "training finished at step 2" in logs["node0/controller.log"], detail
+    assert "transport=collective" in logs["node2/rollout_0.log"], detail

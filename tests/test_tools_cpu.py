@@ -71,14 +71,16 @@ def test_slurm_plan_script_and_node_commands(tmp_path, capsys):
     out = capsys.readouterr().out
     assert rc == 0 and "#SBATCH --nodes=6" in out and "--signal=B:USR1@300" in out and "scontrol requeue" in out
     assert node_launch.expand_nodelist("n[01-03,07],gpu5") == ["n01", "n02", "n03", "n07", "gpu5"]
-    a = [node_launch.node_assignment(i, 4, 2, 2, 6) for i in range(6)]
-    assert [x["policy"] for x in a] == [1, 0, 1, 0, 0, 0] and [x["rollout"] for x in a] == [0, 0, 0, 0, 3, 3]
     ns = type("A", (), dict(policy_nodes=4, rollout_nodes=2, n_policy_replicas=2, n_rollout_replicas=6,
                             config=str(cfg), log_dir=None, script=None))
-    env = {"SLURM_JOB_NODELIST": "n[01-06]", "SLURM_NODEID": "4"}
+    env = {"SLURM_JOB_NODELIST": "n[01-06]", "SLURM_NODEID": "4", "SLURM_GPUS_ON_NODE": "8"}
     cmd = node_launch.build_command(ns, env)
-    assert "--no-controller" in cmd and cmd[cmd.index("--url") + 1] == "n01:8000" and cmd[cmd.index("--rollout") + 1] == "3"
-    assert node_launch.build_command(ns, {"SLURM_JOB_NODELIST": "n[01-06]", "SLURM_NODEID": "1"}) is None
+    # every node passes the job-wide counts; the launcher's plan picks this node's row
+    assert "--no-controller" in cmd and cmd[cmd.index("--url") + 1] == "n01:8000"
+    assert cmd[cmd.index("--policy") + 1] == "2" and cmd[cmd.index("--rollout") + 1] == "6"
+    assert cmd[cmd.index("--worker-idx") + 1] == "4" and cmd[cmd.index("--gpus-per-node") + 1] == "8"
+    cmd0 = node_launch.build_command(ns, {"SLURM_JOB_NODELIST": "n[01-06]", "SLURM_NODEID": "0"})
+    assert "--no-controller" not in cmd0 and cmd0[cmd0.index("--node-ip-list") + 1].split(";")[5] == "n06"
 
 
 def test_mxfp4_reference_quantiser():
