@@ -27,6 +27,7 @@ import torch
 import torch.nn as nn
 
 from ..policy import diffusion as D
+from .base import BaseModel, ModelRegistry, WeightMapper
 from .dit import DiT, DiTArgs
 
 
@@ -41,9 +42,47 @@ class FlowVLAArgs:
     expert_head_dim: int = 128
     expert_ffn: int = 2048
     freeze_backbone: bool = False
+    backbone: Optional[Dict[str, Any]] = None     # the backbone's own config (HF form); None when it is passed in
+    model_type: str = "flow_vla"
+
+    @classmethod
+    def from_hf_config(cls, c, **over) -> "FlowVLAArgs":
+        d = {k: v for k, v in dict(c).items() if k in cls.__dataclass_fields__}
+        d.update(over)
+        return cls(**d)
+
+    def to_hf_config(self) -> Dict[str, Any]:
+        d = {k: getattr(self, k) for k in self.__dataclass_fields__}
+        d["architectures"] = ["FlowVLA"]
+        return d
 
 
-class FlowVLA(nn.Module):
+class FlowVLAWeightMapper(WeightMapper):
+    """Checkpoints of this family are stored under the framework's own parameter names (``backbone.*``, ``expert.*``,
+    ``state_in.*``)."""
+
+    def hf_names(self, local: str) -> List[str]:
+        return [local]
+
+
+@ModelRegistry.register(FlowVLAWeightMapper)
+class FlowVLA(BaseModel):
+    paged_engine = False                  # acting integrates a flow: no token-by-token decoding
+
+    @staticmethod
+    def supported_model_types():
+        return ["flow_vla"]
+
+    @classmethod
+    def from_hf_config(cls, hf_config, **kw):
+        args = FlowVLAArgs.from_hf_config(hf_config)
+        if not args.backbone:
+            raise ValueError("a flow_vla config needs the backbone's config under 'backbone'")
+        bkw = {k: v for k, v in kw.items() if k in ("tp_size", "tp_rank") and v not in (None, 1, 0)}
+        if bkw.get("tp_size", 1) > 1:
+            raise NotImplementedError("the flow-matching action policy trains with data parallelism only")
+        return cls(ModelRegistry.build_model(args.backbone), args)
+
     def __init__(self, backbone: nn.Module, args: FlowVLAArgs):
         super().__init__()
         self.args, self.backbone = args, backbone
@@ -64,7 +103,9 @@ class FlowVLA(nn.Module):
             g = torch.Generator().manual_seed(seed + 2)
             with torch.no_grad():
                 for p in self.state_in.parameters():
-                    p.copy_(torch.randn(p.shape, generator=g) * 0.02) if p.dim() > 1 else p.zero_()
+                    p.copy_((torch.randn(p.shape, generator=g) * 0.02).to(p.dtype)) if p.dim() > 1 else p.zero_()
+
+    init_weights_on_device = init_weights
 
     # ------------------------------------------------------------------ context
     def context(self, prompts: Sequence[Sequence[int]], state: Optional[torch.Tensor] = None, mm: Optional[Dict] = None
@@ -159,3 +200,15 @@ def normalize_actions(a: torch.Tensor, low: torch.Tensor, high: torch.Tensor) ->
 
 def denormalize_actions(a: torch.Tensor, low: torch.Tensor, high: torch.Tensor) -> torch.Tensor:
     return (a.clamp(-1.0, 1.0) + 1.0) * 0.5 * (high - low) + low
+
+
+def _tiny_backbone() -> Dict[str, Any]:
+    from .gpt import ARCHS as GPT_ARCHS
+    return GPT_ARCHS["tiny-qwen2"].to_hf_config()
+
+
+ARCHS = {
+    # pendulum-sized: 1 action dimension, chunks of 4 actions, the 3 observation values as proprioceptive state
+    "tiny-flow-vla": FlowVLAArgs(action_dim=1, horizon=4, state_dim=3, expert_dim=64, expert_layers=2, expert_heads=2,
+                                 expert_head_dim=32, expert_ffn=128, backbone=_tiny_backbone()),
+}
