@@ -189,7 +189,7 @@ class DecoderOnlyLLMDataPacker(BaseDataPacker):
 
 BaseDataPacker.register(["llama", "qwen2", "qwen3", "qwen3_moe", "hfmodel"], DecoderOnlyLLMDataPacker)
 
-MM_KEYS = ("pixel_values", "image_grid_thw", "pixel_values_videos", "video_grid_thw")
+MM_KEYS = ("pixel_values", "image_grid_thw", "pixel_values_videos", "video_grid_thw", "proprio")
 
 
 def merge_mm(items: List[Optional[Dict[str, Any]]]) -> Dict[str, torch.Tensor]:
@@ -259,3 +259,52 @@ class HFVLMDataPacker(DecoderOnlyLLMDataPacker):
 
 BaseDataPacker.register(["qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "internvl", "llava", "gemma3"],
                         HFVLMDataPacker)
+
+
+class OpenVLADataPacker(HFVLMDataPacker):
+    """Robot-manipulation records for the OpenVLA family (the role of
+    cosmos_rl/policy/model/vla/processing_utils.py and the prismatic processors). A record is
+    ``{"instruction_ids": [...], "image": [3 * featurizers, S, S], "actions": [[...] * action_dim] * chunk,
+    "proprio": [...] (optional), "unnorm_key": name (optional)}``; already processed samples (``input_ids`` with the
+    placeholders in place) pass through. The prompt is ``bos + placeholders for the patches (+ state) + instruction``;
+    for supervised training the actions follow as tokens of the last ``n_action_bins`` vocabulary ids and only they
+    carry labels."""
+
+    def setup(self, config, tokenizer=None, processor=None, *a, **kw):
+        super().setup(config, tokenizer, processor)
+        from ..models import hf_io
+        from ..models.openvla import ActionBins, OpenVLAArgs
+        args = OpenVLAArgs.from_hf_config(hf_io.load_hf_config(config.policy.model_name_or_path,
+                                                               config.custom.get("model_config")))
+        self.vla_args = args
+        g = args.towers[0].image_size // args.towers[0].patch_size
+        self.n_patches = g * g
+        self.bins = ActionBins(args.vocab_size - args.pad_to_multiple_of, args.n_action_bins, args.norm_stats)
+
+    def _process(self, sample) -> Dict[str, Any]:
+        if isinstance(sample, dict) and "prompt" in sample and "input_ids" not in sample and "instruction_ids" not in sample:
+            sample = sample["prompt"]
+        if isinstance(sample, dict) and "instruction_ids" in sample:
+            from ..models.openvla import build_prompt
+            a = self.vla_args
+            has_state = bool(a.proprio_dim) and sample.get("proprio") is not None
+            ids = build_prompt(sample["instruction_ids"], self.n_patches, a.image_token_id, extra=int(has_state))
+            mm = {"pixel_values": torch.as_tensor(sample["image"], dtype=torch.float32)[None]}
+            if has_state:
+                mm["proprio"] = torch.as_tensor(sample["proprio"], dtype=torch.float32)[None]
+            return {"input_ids": ids, "mm": mm}
+        return super()._process(sample)
+
+    def action_tokens(self, sample) -> List[int]:
+        acts = torch.as_tensor(sample["actions"], dtype=torch.float32)
+        return self.bins.encode(acts, sample.get("unnorm_key")).reshape(-1).tolist()
+
+    def sft_process_sample(self, sample):
+        if isinstance(sample, dict) and "instruction_ids" in sample:
+            pr = self._process(sample)
+            act = self.action_tokens(sample)
+            return {"input_ids": pr["input_ids"] + act, "label_ids": [-100] * len(pr["input_ids"]) + act, "mm": pr["mm"]}
+        return super().sft_process_sample(sample)
+
+
+BaseDataPacker.register(["openvla"], OpenVLADataPacker)

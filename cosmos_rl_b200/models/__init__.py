@@ -8,6 +8,7 @@ from . import qwen2_5_vl  # noqa: F401
 from . import internvl  # noqa: F401
 from . import qwen3_vl_moe  # noqa: F401
 from . import vla_flow  # noqa: F401
+from . import openvla  # noqa: F401
 from . import hf_model  # noqa: F401  (fallback for every other transformers causal LM)
 
 
@@ -23,6 +24,7 @@ def named_architectures():
         out.update(internvl.ARCHS)
         out.update(qwen3_vl_moe.ARCHS)
         out.update(vla_flow.ARCHS)
+        out.update(openvla.ARCHS)
     except ImportError:
         pass
     return out

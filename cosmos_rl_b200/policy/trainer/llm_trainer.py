@@ -181,7 +181,7 @@ class LLMTrainer(Trainer):
             # parameters every tensor-parallel rank holds in full (norm weights): counted once in the gradient norm
             tp_mask = torch.zeros(self.flat.total, dtype=torch.bool, device=self.device)
             for slot in self.flat.slots:
-                if "norm" in slot.name or slot.name.startswith("visual."):      # the vision tower is replicated too
+                if "norm" in slot.name or slot.name.startswith(("visual.", "projector.", "proprio_projector.", "action_head.")):   # towers and heads beside the decoder are replicated too
                     tp_mask[slot.offset:slot.offset + slot.numel] = True
         sharded_norm = [parallel_dims.group("dp_shard")] if (self.shard_params and dp > 1) else []
         self.optimizer = FlatAdamW(
