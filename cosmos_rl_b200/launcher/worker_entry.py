@@ -56,7 +56,8 @@ def _tokenizer(config):
 
 def policy_entry(dataset=None, val_dataset=None, data_packer=None, val_data_packer=None, hook_fns=None, **kw):
     config, dims, device, api = _worker_setup("POLICY")
-    from ..policy.trainer import dpo_trainer, grpo_trainer, sft_trainer  # noqa: F401 (registry)
+    from ..policy.trainer import (diffusion_trainer, dpo_trainer, grpo_trainer, sft_trainer,  # noqa: F401 (registry)
+                                  vla_flow_trainer, vla_trainer)
     tp = config.train.train_policy
     if tp.type == "sft":
         from ..policy.worker.sft_worker import SFTPolicyWorker

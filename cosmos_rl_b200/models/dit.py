@@ -161,6 +161,11 @@ class DiT(BaseModel):
 
     init_weights_on_device = init_weights
 
+    def shard_parts(self, flat):
+        """Weight-sync parts: every tensor whole (the family runs data parallel only)."""
+        from ..parallel.reshard import whole_parts
+        return whole_parts(flat)
+
     # ------------------------------------------------------------------ patches
     def patchify(self, z: torch.Tensor) -> Tuple[torch.Tensor, Tuple[int, int, int]]:
         """[B, C, T, H, W] -> [B, n, C*pt*ph*pw] and the token grid."""

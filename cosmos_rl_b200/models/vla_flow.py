@@ -107,6 +107,11 @@ class FlowVLA(BaseModel):
 
     init_weights_on_device = init_weights
 
+    def shard_parts(self, flat):
+        """Weight-sync parts: every tensor whole (the family runs data parallel only)."""
+        from ..parallel.reshard import whole_parts
+        return whole_parts(flat)
+
     # ------------------------------------------------------------------ context
     def context(self, prompts: Sequence[Sequence[int]], state: Optional[torch.Tensor] = None, mm: Optional[Dict] = None
                 ) -> Tuple[torch.Tensor, torch.Tensor]:

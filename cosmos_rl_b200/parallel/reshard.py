@@ -105,6 +105,17 @@ def gpt_parts(model, flat) -> List[Part]:
     return parts
 
 
+def whole_parts(flat, prefix: str = "") -> List[Part]:
+    """Every parameter as one whole part under its own name: models that run data parallel only (diffusion
+    transformers, action experts) have the same layout on the policy and the rollout side."""
+    parts: List[Part] = []
+    for name, p in flat.params:
+        slot = flat.by_name[name]
+        rows, cols = (1, p.numel()) if p.dim() <= 1 else (p.shape[0], p.numel() // p.shape[0])
+        parts.append(Part(prefix + name, 0, rows, 0, cols, slot.offset, cols, bool(p.requires_grad)))
+    return parts
+
+
 def model_parts(model, flat) -> List[Part]:
     if hasattr(model, "shard_parts"):
         return model.shard_parts(flat)

@@ -21,6 +21,7 @@ class _DiffusionBase(LLMTrainer):
     def __init__(self, config, parallel_dims, device=None, **kw):
         super().__init__(config, parallel_dims, device=device, **kw)
         self.opts = diffusion_options(config)
+        LatentStore.configure(config)
         self.model.gradient_checkpointing = bool(config.policy.model_gradient_checkpointing)
 
     def _replica(self) -> torch.nn.Module:

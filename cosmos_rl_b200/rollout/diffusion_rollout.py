@@ -20,12 +20,30 @@ from .generation_mixin import RolloutGenerationMixin
 
 
 class LatentStore:
-    """Process-local store of generated latents and sampler traces, keyed by the id carried in the completion."""
+    """Store of generated latents and sampler traces, keyed by the id carried in the completion. Process-local by
+    default (colocated jobs); with a replay-buffer folder (``configure``: ``[custom] replay_buffer_dir``) every item is a
+    file on a file system the rollout and policy workers share, so the two can be separate processes or nodes."""
     _items: Dict[str, Dict[str, torch.Tensor]] = {}
     _lock = threading.Lock()
+    _fs = None                                   # utils.replay_buffer.ReplayBuffer when configured
+
+    @classmethod
+    def configure(cls, config=None, buffer_dir: Optional[str] = None) -> None:
+        from ..utils.replay_buffer import ReplayBuffer, buffer_dir_of
+        d = buffer_dir or buffer_dir_of(config)
+        if d and (cls._fs is None or cls._fs.dir != d):
+            cls._fs = ReplayBuffer(d)
+        elif not d:
+            cls._fs = None
+
+    @staticmethod
+    def _key(c: Any) -> str:
+        return c["latent_id"] if isinstance(c, dict) else c
 
     @classmethod
     def put(cls, item: Dict[str, torch.Tensor]) -> str:
+        if cls._fs is not None:
+            return cls._fs.save(item)
         key = uuid.uuid4().hex
         with cls._lock:
             cls._items[key] = item
@@ -33,13 +51,23 @@ class LatentStore:
 
     @classmethod
     def get(cls, completion: Any) -> Dict[str, torch.Tensor]:
-        return cls._items[completion["latent_id"] if isinstance(completion, dict) else completion]
+        key = cls._key(completion)
+        with cls._lock:
+            if key in cls._items:
+                return cls._items[key]
+        if cls._fs is not None:
+            return cls._fs.load(key, wait_s=30.0)
+        raise KeyError(f"latent {key} is not in this process; separate rollout and policy processes need "
+                       f"[custom] replay_buffer_dir on a file system they share")
 
     @classmethod
     def release(cls, completions) -> None:
+        keys = [cls._key(c) for c in completions]
         with cls._lock:
-            for c in completions:
-                cls._items.pop(c["latent_id"] if isinstance(c, dict) else c, None)
+            for k in keys:
+                cls._items.pop(k, None)
+        if cls._fs is not None:
+            cls._fs.delete(keys)
 
     @classmethod
     def __len__(cls) -> int:
@@ -58,6 +86,7 @@ class DiffusionRollout(RolloutGenerationMixin, RolloutBase):
     def __init__(self, config, parallel_dims, device, tokenizer=None, **kw):
         super().__init__(config, parallel_dims, device)
         self.opts = diffusion_options(config)
+        LatentStore.configure(config)
         self.model = None
         self.behaviour = None      # set by the NFT trainer: samples come from the trailing "old" weights
 

@@ -38,6 +38,7 @@ class FlowVLARollout(RolloutBase):
     def __init__(self, config, parallel_dims, device, tokenizer=None, **kw):
         super().__init__(config, parallel_dims, device)
         self.opts = flow_vla_options(config)
+        LatentStore.configure(config)
         self.model = None
 
     def init_engine(self, load_format: str = "dummy", shared_model=None, seed: Optional[int] = None, **kw) -> None:

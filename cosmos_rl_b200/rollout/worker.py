@@ -29,7 +29,7 @@ from ..reward.dispatcher import RewardDispatcher, make_reward_calculator
 from ..utils import constant
 from ..utils.logging import logger
 from .base import RolloutRegistry
-from . import b200_rollout, hf_rollout  # noqa: F401  (register the built-in backends)
+from . import b200_rollout, diffusion_rollout, hf_rollout, vla_flow_rollout, vla_rollout  # noqa: F401  (register the built-in backends)
 
 
 class DisaggregatedRolloutControlWorker(CommMixin):
@@ -47,7 +47,7 @@ class DisaggregatedRolloutControlWorker(CommMixin):
         self.data_fetcher = WorkerDataFetcher(config, ds, vds)
         self.tokenizer = tokenizer
         backend = config.rollout.backend
-        if backend != "hf":
+        if backend == "b200":
             # families without a native model are served by the generic transformers wrapper and its backend
             from ..models import hf_io
             from ..models.base import ModelRegistry
@@ -247,7 +247,9 @@ class DisaggregatedRolloutControlWorker(CommMixin):
             self.current_weight_version = getattr(self, "_pending_version", 0)
         self.weights_ready = True
         logger.info("[Rollout] weight version %d committed", self.current_weight_version)
-        self.rollout.engine.weight_version = self.current_weight_version
+        engine = getattr(self.rollout, "engine", None)      # backends without a token engine (diffusion, action flows)
+        if engine is not None:
+            engine.weight_version = self.current_weight_version
         if c.total_steps is not None:
             self.total_steps = c.total_steps
         return bool(c.replica_should_stop())

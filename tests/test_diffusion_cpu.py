@@ -255,3 +255,60 @@ def test_causal_video_vae_shapes_causality_and_training():
     vae.fit_latent_stats([clip, x[:1, :, :5]])
     z = vae.tokenize(torch.cat([clip, x[:1, :, :5]]))
     assert z.transpose(0, 1).reshape(4, -1).mean(1).abs().max() < 0.2
+
+
+@pytest.mark.timeout(300)
+def test_flow_grpo_job_with_separate_rollout_and_policy_processes(tmp_path):
+    """FlowGRPO as a disaggregated job through the launcher: the rollout process samples latents with the SDE sampler and
+    writes latent + trace to the trajectory store on a shared folder (``[custom] replay_buffer_dir``), only the id
+    travels through the controller, the policy process loads the traces, trains, releases them, and the new weights of
+    the diffusion transformer reach the rollout process over the pair's communicator. Plus the store's own contract."""
+    import os
+    import subprocess
+    import sys
+    from cosmos_rl_b200.config import dump_toml
+    from cosmos_rl_b200.utils.replay_buffer import ReplayBuffer
+    rb = ReplayBuffer(str(tmp_path / "rb"))
+    k = rb.save({"x": torch.arange(4)})
+    assert k in rb and torch.equal(rb.load(k)["x"], torch.arange(4)) and len(rb) == 1
+    with pytest.raises(KeyError):
+        rb.load("0" * 32)
+    with pytest.raises(ValueError):
+        rb.load("../etc")
+    assert rb.cleanup(max_age_s=3600) == 0 and rb.delete([k, "missing"]) == 1 and len(rb) == 0
+    here = os.path.dirname(os.path.abspath(__file__))
+    root = os.path.dirname(here)
+    raw = {"mode": "disaggregated",
+           "custom": {"replay_buffer_dir": str(tmp_path / "replay"),
+                      "diffusion": {"latent_shape": [4, 8, 8], "sample_steps": 4, "sampler": "sde", "noise_level": 0.7}},
+           "policy": {"model_name_or_path": "tiny-dit", "model_gradient_checkpointing": False,
+                      "parallelism": {"tp_size": 1, "dp_shard_size": 1}},
+           "rollout": {"backend": "diffusion", "batch_size": 4, "n_generation": 4, "seed": 0,
+                       "parallelism": {"tp_size": 1}},
+           "train": {"seed": 0, "epoch": 1, "optm_lr": 2e-3, "optm_warmup_steps": 0, "optm_weight_decay": 0.0,
+                     "output_dir": str(tmp_path / "out"), "train_batch_per_replica": 16,
+                     "train_policy": {"type": "grpo", "trainer_type": "flow_grpo", "mini_batch": 8,
+                                      "dataloader_shuffle": False, "allowed_outdated_steps": 1},
+                     "ckpt": {"enable_checkpoint": False}},
+           "logging": {"logger": ["console"]}}
+    cfg = tmp_path / "job.toml"
+    cfg.write_text(dump_toml(raw))
+    env = dict(os.environ, COSMOS_LOG_LEVEL="INFO", PYTHONPATH=root, OMP_NUM_THREADS="2", N_PROMPTS="16")
+    cmd = [sys.executable, "-m", "cosmos_rl_b200.launcher.launch_all", "--config", str(cfg), "--policy", "1",
+           "--rollout", "1", "--cpu", "--rdzv-port", "29851", "--log-dir", str(tmp_path / "logs"),
+           os.path.join(here, "diffusion_job_script.py")]
+    p = subprocess.Popen(cmd, env=env, cwd=root, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                         start_new_session=True)
+    try:
+        out, _ = p.communicate(timeout=260)
+    except subprocess.TimeoutExpired:
+        import signal
+        os.killpg(p.pid, signal.SIGKILL)                  # the group this test started, by its exact id
+        out, _ = p.communicate()
+    latest = tmp_path / "logs" / "logs_latest"
+    logs = {f: open(latest / f).read() for f in sorted(os.listdir(latest))} if latest.exists() else {}
+    detail = "\n".join(f"==== {k}\n{v[-2500:]}" for k, v in logs.items())
+    assert p.returncode == 0, out[-2000:] + detail
+    assert "training finished at step 4" in logs["controller.log"], detail
+    assert "weight version" in logs["rollout_0.log"] and "transport=collective" in logs["rollout_0.log"], detail
+    assert os.listdir(tmp_path / "replay") == []                          # every trace was fetched and released
