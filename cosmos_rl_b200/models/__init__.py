@@ -4,6 +4,7 @@ from . import gpt  # noqa: F401
 from . import qwen3_moe  # noqa: F401
 from . import deepseek_v3  # noqa: F401
 from . import dit  # noqa: F401
+from . import mmdit  # noqa: F401
 from . import qwen2_5_vl  # noqa: F401
 from . import internvl  # noqa: F401
 from . import qwen3_vl_moe  # noqa: F401
@@ -20,6 +21,7 @@ def named_architectures():
         out.update(qwen3_moe.ARCHS)
         out.update(deepseek_v3.ARCHS)
         out.update(dit.ARCHS)
+        out.update(mmdit.ARCHS)
         out.update(qwen2_5_vl.ARCHS)
         out.update(internvl.ARCHS)
         out.update(qwen3_vl_moe.ARCHS)

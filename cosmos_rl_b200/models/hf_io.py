@@ -176,7 +176,8 @@ def hf_state_dict(model, hf_config: Dict[str, Any]) -> Dict[str, torch.Tensor]:
     for name, p in model.named_parameters():
         if ".lora_" in name:
             continue
-        for hf_name, piece in _split_fused(name, p.detach(), mapper, hf_config, a.n_heads, a.n_kv_heads, a.head_dim):
+        for hf_name, piece in _split_fused(name, p.detach(), mapper, hf_config, getattr(a, "n_heads", 0),
+                                           getattr(a, "n_kv_heads", 0), getattr(a, "head_dim", 0)):
             out[hf_name] = piece
     return out
 
@@ -208,9 +209,9 @@ def export_safetensors(model, hf_config: Dict[str, Any], output_dir: str, parall
     if writer:
         os.makedirs(output_dir, exist_ok=True)
     a = getattr(model, "args", None)
-    hq = (a.n_heads // tp) if a else 0
-    hkv = max(1, a.n_kv_heads // tp) if a else 0
-    d = a.head_dim if a else 0
+    hq = getattr(a, "n_heads", 0) // tp          # only families with fused q / k / v projections need these
+    hkv = max(1, getattr(a, "n_kv_heads", 0) // tp)
+    d = getattr(a, "head_dim", 0)
     shard: Dict[str, torch.Tensor] = {}
     shard_bytes = 0
     files: List[Dict[str, torch.Tensor]] = []

@@ -20,6 +20,8 @@ def _embed(meta: Dict[str, Any], text_dim: int, length: int = 8) -> List[List[fl
     """Text conditioning of a sample: precomputed ``text_embeds`` when present, else a deterministic hash embedding of
     the caption (lets jobs run without a text encoder; replace with real encoder outputs for actual training)."""
     if "text_embeds" in meta:
+        if "pooled_embeds" in meta:                 # SD3-style networks read the pooled vector from row 0
+            return with_pooled(meta["text_embeds"], meta["pooled_embeds"])
         return meta["text_embeds"]
     words = str(meta.get("caption", meta.get("prompt", ""))).lower().split()[:length] or ["<empty>"]
     out = []
@@ -27,6 +29,15 @@ def _embed(meta: Dict[str, Any], text_dim: int, length: int = 8) -> List[List[fl
         g = torch.Generator().manual_seed(int.from_bytes(w.encode()[:8].ljust(8, b"\0"), "little") % (2 ** 31))
         out.append(torch.randn(text_dim, generator=g).tolist())
     return out
+
+
+def with_pooled(text_embeds: List[List[float]], pooled: List[float]) -> List[List[float]]:
+    """Put the pooled text embedding in front of the token embeddings as row 0, zero-padded to their width: the layout
+    two-stream networks with a pooled conditioning input expect (``models/mmdit.py``)."""
+    width = len(text_embeds[0])
+    if len(pooled) > width:
+        raise ValueError(f"pooled embedding of {len(pooled)} values does not fit the text width {width}")
+    return [list(pooled) + [0.0] * (width - len(pooled))] + [list(r) for r in text_embeds]
 
 
 class LatentFolderDataset:
