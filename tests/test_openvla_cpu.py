@@ -236,3 +236,49 @@ def test_openvla_sft_through_the_trainer_and_data_packer(tmp_path):
         act = m.decode_actions(pred[None], "demo")[0]
         hits += int((act - torch.tensor(demo[i])).abs().max() < 0.05)
     assert hits >= 3, hits
+
+
+def test_robot_episodes_to_records_and_sft_worker(tmp_path):
+    """Demonstration episodes in a tar shard -> per-step records (published prompt wording, letter-boxed camera frame
+    normalised once per featurizer, action chunk, state) -> data packer -> the standalone SFT worker on the native
+    model; the action statistics give the q01 / q99 the bins un-normalise with."""
+    from cosmos_rl_b200.config import Config
+    from cosmos_rl_b200.parallel.dims import ParallelDims
+    from cosmos_rl_b200.policy.worker.sft_worker import SFTPolicyWorker
+    from cosmos_rl_b200.tools.dataset import robot_records as R
+    from cosmos_rl_b200.tools.dataset.tar_shards import write_shard
+    g = torch.Generator().manual_seed(0)
+    episodes = []
+    for e in range(3):
+        T = 6
+        acts = torch.rand(T, 3, generator=g) * 2 - 1
+        acts[:, 2] = (acts[:, 2] > 0).float()                               # gripper open / closed
+        episodes.append({"instruction": f"Pick up the block number {e}", "actions": acts,
+                         "images": torch.randint(0, 256, (T, 40, 72, 3), generator=g, dtype=torch.uint8)})
+    write_shard(str(tmp_path / "demo-000.tar"), [{"__key__": f"{i:04d}", "episode.pt": R.episode_bytes(ep)}
+                                                 for i, ep in enumerate(episodes)])
+    loaded = R.load_episodes(str(tmp_path / "demo-{000..000}.tar"))
+    assert len(loaded) == 3 and torch.equal(loaded[1]["actions"], episodes[1]["actions"])
+    stats = R.action_statistics(loaded)
+    assert stats["action"]["mask"] == [True, True, False] and stats["num_transitions"] == 18
+    assert all(lo < hi for lo, hi in zip(stats["action"]["q01"], stats["action"]["q99"]))
+    px = R.featurizer_pixels(loaded[0]["images"][0], 56, 2)
+    assert px.shape == (6, 56, 56)
+    band = px[3:, :12]                                                       # letter-box rows above the 72 x 40 frame
+    assert torch.allclose(band, torch.full_like(band, -1.0))                # black after the 0.5 / 0.5 normalisation
+    cfg = Config.from_dict({
+        "policy": {"model_name_or_path": "tiny-openvla", "model_max_length": 64, "model_gradient_checkpointing": False},
+        "train": {"seed": 0, "optm_lr": 1e-3, "optm_warmup_steps": 0, "output_dir": str(tmp_path / "out"), "epoch": 1,
+                  "train_batch_per_replica": 6, "max_num_steps": 3,
+                  "train_policy": {"type": "sft", "trainer_type": "sft", "mini_batch": 3},
+                  "ckpt": {"enable_checkpoint": False}}})
+    ds = R.RobotStepDataset(episodes=loaded, unnorm_key="demo")
+    ds.setup(cfg, None)
+    assert len(ds) == 18 and ds.image_size == 56 and ds.n_feat == 2
+    rec = ds[7]
+    assert rec["instruction_ids"][0] == 1 and rec["image"].shape == (6, 56, 56) and len(rec["actions"]) == 1
+    cpu = torch.device("cpu")
+    w = SFTPolicyWorker(cfg, ParallelDims(world_size=1, device=cpu), dataset=ds, standalone=True, device=cpu)
+    assert type(w.trainer.data_packer).__name__ == "OpenVLADataPacker" and type(w.trainer.model).__name__ == "OpenVLA"
+    w.main_loop()
+    assert [h["step"] for h in w.history] == [1, 2, 3] and all(h["train/loss_avg"] > 0 for h in w.history)
