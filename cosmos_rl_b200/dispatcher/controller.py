@@ -65,6 +65,8 @@ class Controller:
         self._stop_monitor = threading.Event()
         self.finalized = threading.Event()
         self.self_terminate = False
+        self.failed: Optional[str] = None       # why the job was ended without finishing (exit status 3)
+        self._starved_since: Optional[float] = None
         self.rollouts_have_checked_out = False
 
     # ------------------------------------------------------------------ meta
@@ -131,6 +133,9 @@ class Controller:
         if no_replicas and self.policy_status_manager.had_replicas:
             self.finalized.set()
             if self.self_terminate:
+                if self.failed:
+                    logger.error("[Controller] job ended without finishing: %s", self.failed)
+                    os._exit(3)                 # not the coordinated SIGTERM exit: the launcher reports a failure
                 os.kill(os.getpid(), signal.SIGTERM)
 
     def monitor_once(self, now: Optional[float] = None) -> List[str]:
@@ -142,7 +147,39 @@ class Controller:
                 self.unregister(name)
                 reaped.append(name)
         self._settle_nccl_errors(now)
+        self._check_rollout_starvation(now)
         return reaped
+
+    def _check_rollout_starvation(self, now: Optional[float] = None) -> bool:
+        """An RL job that has lost EVERY rollout replica cannot make another step once the buffered rollouts are used
+        up: the policies would wait for data forever (on several nodes nobody else notices a node that went away).
+        After ``COSMOS_NO_ROLLOUT_GRACE_S`` in that state with no new rollout replica registering, the job is ended in
+        order: the policies get ``TrainingComplete`` (final checkpoint when checkpoints are on) and the controller
+        leaves with a failure status. Returns True when it just did that."""
+        pm, rm = self.policy_status_manager, self.rollout_status_manager
+        if self.config.train.train_policy.type == "sft" or self.failed:
+            return False
+        from .replica import ReplicaStatus
+        reps = pm.mesh_replicas()
+        stuck = (rm.had_replicas and not rm.replicas and bool(reps) and not pm.complete_sent
+                 and not (pm.total_steps and pm.current_step >= pm.total_steps)
+                 and not any(r.status == ReplicaStatus.RUNNING for r in reps)
+                 and len(pm.rollout_buffer) < pm.batch_per_replica * len(reps))
+        if not stuck:
+            self._starved_since = None
+            return False
+        now = time.time() if now is None else now
+        if self._starved_since is None:
+            self._starved_since = now
+            return False
+        if now - self._starved_since < constant.COSMOS_NO_ROLLOUT_GRACE_S:
+            return False
+        self.failed = (f"no rollout replica for {now - self._starved_since:.0f} s at step {pm.current_step} of "
+                       f"{pm.total_steps}")
+        logger.error("[Controller] %s: ending the job", self.failed)
+        with pm.lock:
+            pm._send_training_complete()
+        return True
 
     def start_monitor(self, interval: Optional[float] = None) -> None:
         interval = interval if interval is not None else constant.COSMOS_ROLLOUT_SCAN_INTERVAL

@@ -469,6 +469,7 @@ class RolloutStatusManager(_ManagerBase):
     def __init__(self, config, broker):
         super().__init__(config, broker)
         self.policy_manager: Optional[PolicyStatusManager] = None
+        self.had_replicas = False
         self.ended: set = set()
         self.stop_broadcast_sent = False
         self.adopted_versions: Dict[str, int] = {}
@@ -489,6 +490,7 @@ class RolloutStatusManager(_ManagerBase):
             rep.add_atom(atom)
             rep.heartbeat()
             if rep.all_atoms_arrived:
+                self.had_replicas = True
                 self._post_register(rep)
             return rep
 

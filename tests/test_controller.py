@@ -323,3 +323,35 @@ def test_dropped_groups_are_replaced_by_fresh_prompts():
     c.put_rollouts("r0", [bad], is_end=False)
     again, _ = c.get_batched_prompt(4)
     assert len(again) == 1 and again[0][1].weight_version == batch[3][1].weight_version
+
+
+def test_job_that_lost_every_rollout_replica_is_ended_in_order(monkeypatch):
+    """The only rollout replica stops sending heartbeats and is reaped: the policy would wait for data forever. After the
+    grace period the controller sends ``TrainingComplete`` to the policy and records why; a rollout replica that
+    registers in time resets the clock instead."""
+    monkeypatch.setattr(constant, "COSMOS_NO_ROLLOUT_GRACE_S", 30.0)
+    c = Controller(_config(), dataset=SyntheticTokenDataset(64, 8, 100))
+    _reg(c, "p0", "POLICY")
+    _reg(c, "r0", "ROLLOUT")
+    now = time.time()
+    c.policy_status_manager.replicas["p0"].last_heartbeat = now + 1000
+    c.rollout_status_manager.replicas["r0"].last_heartbeat = now - constant.COSMOS_HEARTBEAT_TIMEOUT - 1
+    assert c.monitor_once(now) == ["r0"] and c.failed is None           # reaped; the clock starts
+    assert c._starved_since == now
+    c.monitor_once(now + 10)
+    assert c.failed is None
+    _reg(c, "r1", "ROLLOUT")                                              # a replacement arrives in time
+    c.rollout_status_manager.replicas["r1"].last_heartbeat = now + 1000
+    c.monitor_once(now + 20)
+    assert c._starved_since is None and c.failed is None
+    c.rollout_status_manager.replicas["r1"].last_heartbeat = now - constant.COSMOS_HEARTBEAT_TIMEOUT - 1
+    assert c.monitor_once(now + 40) == ["r1"]
+    c.monitor_once(now + 60)
+    assert c.failed is None                                               # 20 s into the new period
+    n0 = len(_commands(c, "p0"))
+    c.monitor_once(now + 75)
+    assert c.failed and "no rollout replica" in c.failed
+    last = _commands(c, "p0")[n0:]
+    assert [x.command_type for x in last] == [cmd.CommandType.TRAINING_COMPLETE]
+    c.monitor_once(now + 200)                                             # nothing is sent twice
+    assert len(_commands(c, "p0")) == n0 + 1
