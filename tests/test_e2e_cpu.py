@@ -126,7 +126,7 @@ def test_tiny_grpo_job_with_async_rollout_scheduler(tmp_path):
     from cosmos_rl_b200.config import dump_toml, load_toml
     raw = load_toml(os.path.join(HERE, "configs", "tiny_grpo_cpu.toml"))
     raw["rollout"]["mode"] = "async"
-    raw["rollout"]["async_config"] = {"max_concurrent_requests": 2}
+    raw["rollout"]["async_config"] = {"max_concurrent_requests": 8}
     raw["train"]["output_dir"] = str(tmp_path / "out")
     cfg = tmp_path / "job.toml"
     cfg.write_text(dump_toml(raw))
