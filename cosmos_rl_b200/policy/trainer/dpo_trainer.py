@@ -1,6 +1,8 @@
 """Direct preference optimisation on (prompt, chosen, rejected) triples: sequence log-probs of both
 completions under the policy and under the frozen reference (the initial weights, kept on the host),
-``-logsigmoid(beta * margin)`` (cosmos_rl/policy/trainer/llm_trainer/dpo_trainer.py:34-475)."""
+``-logsigmoid(beta * margin)`` (cosmos_rl/policy/trainer/llm_trainer/dpo_trainer.py:34-475). Prompts of a
+vision-language model carry their pixel inputs (multimodal preference data such as MMPR): the data packer returns them
+with the tokens and both completions of a pair are scored against the same images."""
 from __future__ import annotations
 
 import time
@@ -32,17 +34,23 @@ class DPOTrainer(LLMTrainer):
         out = {}
         for key in ("chosen", "rejected"):
             pi = pk.get_policy_input(sample["prompt"], sample[key])
-            out[key] = (pi.input_ids, pi.logprob_masks)
+            out[key] = (pi.input_ids, pi.logprob_masks, getattr(pi, "mm", None))    # mm: the prompt's pixel inputs
         return out
 
     def _seq_logprobs(self, pairs: List[Dict[str, Any]]) -> torch.Tensor:
         """[2 * n] sequence log-probs ordered chosen_0, rejected_0, chosen_1, ..."""
-        seqs, masks = [], []
+        seqs, masks, mms = [], [], []
         for e in pairs:
             for key in ("chosen", "rejected"):
                 seqs.append(e[key][0])
                 masks.append(e[key][1])
+                mms.append(e[key][2])
         b = pack_sequences(seqs, masks, device=self.device)
+        if getattr(self.model, "is_vlm", False):
+            # vision-language preference pairs: both completions of a pair carry the prompt's images, so the pixel
+            # inputs are stacked once per packed sequence, in packing order
+            from ...data.packer import merge_mm
+            self.model.mm_inputs = merge_mm(mms)
         sel = (b["label_ids"] >= 0).nonzero(as_tuple=True)[0]
         hidden = self.model(b["input_ids"], b["position_ids"], b["cu_seqlens"], b["max_seqlen"])
         lp, _ = self.model.logprobs(hidden[sel], b["label_ids"][sel], 1.0)
