@@ -137,7 +137,8 @@ def run_reference(args):
     tag = f"{os.environ.get('MASTER_PORT', '0')}_{os.getppid() if world > 1 else os.getpid()}"
     res_dir = os.path.join("/tmp", f"b200rl_ref_res_{tag}")
     os.makedirs(res_dir, exist_ok=True)
-    log_dir = os.path.join(ROOT, "gpurun_out") if os.path.isdir(os.path.join(ROOT, "gpurun_out")) else res_dir
+    log_dir = os.environ.get("B200RL_REF_LOG_DIR") or res_dir        # where the two halves write their logs
+    os.makedirs(log_dir, exist_ok=True)
     common = ["--steps", str(args.steps), "--warmup", str(args.warmup), "--prompts-per-gpu", str(args.prompts_per_gpu),
               "--group", str(args.group), "--prompt-len", str(args.prompt_len), "--max-response", str(args.max_response)]
     limit = float(os.environ.get("B200RL_REF_TIMEOUT_S", "1500"))
