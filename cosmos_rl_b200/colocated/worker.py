@@ -26,7 +26,8 @@ from ..parallel.dims import ParallelDims
 from ..policy.trainer import diffusion_trainer, grpo_trainer, vla_flow_trainer, vla_trainer  # noqa: F401
 from ..policy.trainer.base import TrainerRegistry
 from ..reward.dispatcher import make_reward_calculator
-from ..rollout import b200_rollout, diffusion_rollout, hf_rollout, vla_flow_rollout, vla_rollout  # noqa: F401  (register the built-in backends)
+from ..rollout import (b200_rollout, diffusion_rollout, hf_rollout, openvla_rollout, vla_flow_rollout,  # noqa: F401
+                       vla_rollout)                       # (registers the built-in backends)
 from ..rollout.base import RolloutRegistry
 from ..utils.logging import logger
 

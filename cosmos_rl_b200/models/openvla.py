@@ -484,6 +484,29 @@ class OpenVLA(GPT):
     def decode_actions(self, tokens: torch.Tensor, unnorm_key: Optional[str] = None) -> torch.Tensor:
         return self.bins.decode(tokens.cpu(), unnorm_key)
 
+    # ------------------------------------------------------------------ the policy over action tokens
+    @property
+    def action_token_range(self) -> Tuple[int, int]:
+        """``[lo, hi)``: the ids of the action bins (the last ``n_action_bins`` of the un-padded vocabulary)."""
+        hi = self.args.vocab_size - self.args.pad_to_multiple_of
+        return hi - self.args.n_action_bins, hi
+
+    def action_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        """Logits over the action bins only (``[N, n_action_bins]``, column j = token ``lo + j``): RL samples and scores
+        actions under this restricted distribution, so no probability mass sits on text tokens."""
+        lo, hi = self.action_token_range
+        return _linear(hidden, self.lm_head_weight[lo:hi]).float()
+
+    def logprobs(self, hidden: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0):
+        """With ``action_only_logprobs`` set (the action-token RL trainer does): log-probability and entropy under the
+        softmax over the action bins; otherwise the decoder's full-vocabulary path."""
+        if not getattr(self, "action_only_logprobs", False):
+            return super().logprobs(hidden, labels, temperature)
+        lo, hi = self.action_token_range
+        lsm = torch.log_softmax(self.action_logits(hidden) / float(temperature), dim=-1)
+        idx = (labels.long() - lo).clamp(0, hi - lo - 1)
+        return lsm.gather(1, idx[:, None])[:, 0], -(lsm.exp() * lsm).sum(-1)
+
     def shard_parts(self, flat):
         """The decoder's parts plus every other tensor whole (featurizers, projectors and the action head are
         replicated over tensor-parallel ranks)."""

@@ -29,7 +29,8 @@ from ..reward.dispatcher import RewardDispatcher, make_reward_calculator
 from ..utils import constant
 from ..utils.logging import logger
 from .base import RolloutRegistry
-from . import b200_rollout, diffusion_rollout, hf_rollout, vla_flow_rollout, vla_rollout  # noqa: F401  (register the built-in backends)
+from . import (b200_rollout, diffusion_rollout, hf_rollout, openvla_rollout, vla_flow_rollout,  # noqa: F401
+               vla_rollout)                               # (registers the built-in backends)
 
 
 class DisaggregatedRolloutControlWorker(CommMixin):
