@@ -39,8 +39,10 @@ def parse_args():
     ap.add_argument("--max-response", type=int, default=1024)
     ap.add_argument("--mb-tokens", type=int, default=8192, help="token budget of one training micro-batch")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--config", type=int, default=2, choices=[2, 5],
-                    help="benchmark configuration: 2 = Qwen2.5-7B-arch GRPO step (the headline); 5 = weight-sync sweep "
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 5],
+                    help="benchmark configuration: 1 = the tiny Qwen2-arch plumbing job on CPU / gloo (controller + 1 "
+                         "policy rank + 1 rollout rank through the launcher; fp32, no GPU); 2 = Qwen2.5-7B-arch GRPO "
+                         "step (the headline); 5 = weight-sync sweep "
                          "on a separated layout (policy on the first half of the GPUs, rollout TP 1/2/4 on the "
                          "second half; bf16 pull, fused fp8 pull, and the reference-style fp32 send/recv route). The "
                          "MoE and long-context configurations are not wired into this script")
@@ -222,6 +224,17 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.config == 1:
+        # 8 prompts of 64 tokens, group 4, 64 response tokens, tiny Qwen2 architecture, two ranks on CPU
+        if int(os.environ.get("RANK", "0")) == 0:
+            from cosmos_rl_b200.bench_launcher import run
+            a = argparse.Namespace(**vars(args))
+            a.gpus, a.model, a.prompts_per_gpu, a.group, a.prompt_len, a.max_response = 2, "tiny-qwen2", 4, 4, 64, 64
+            a.mb_tokens = 2048
+            out = run(a, cpu=True)
+            out["n_gpus"], out["config"]["parallelism"] = 0, "CPU / gloo: controller + 1 policy rank + 1 rollout rank"
+            print(json.dumps(out))
+        return 0
     if args.layout == "launcher":
         # the job starts its own processes: under a multi-rank launch only rank 0 acts, and it holds no GPU itself
         if int(os.environ.get("RANK", "0")) == 0:
