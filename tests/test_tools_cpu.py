@@ -215,3 +215,20 @@ def test_tar_shard_dataset_streams_splits_shuffles_and_augments(tmp_path):
     assert len(list(TarShardDataset(pat, augmentors=[SampleFrames("pt", n=9)]))) == 0        # clips too short: dropped
     loader = torch.utils.data.DataLoader(TarShardDataset(pat, seed=2), batch_size=None, num_workers=2)
     assert sorted(ids(loader)) == sorted(a + b)                          # workers split the shards, nothing twice
+
+
+def test_deepmath_distillation_dataset_renders_the_open_thinking_prompt():
+    from cosmos_rl_b200.tools.dataset import deepmath_distill as D
+    rows = [{"question": "What is 6 * 7?", "final_answer": "42"},
+            {"problem": "Simplify 2/4.", "solution": "We get \\boxed{\\frac{1}{2}}."}]
+    ds = D.deepmath_dataset(rows)
+    assert len(ds) == 2
+    assert ds[0] == "<|im_start|>user\nWhat is 6 * 7?<|im_end|>\n<|im_start|>assistant\n<think>\n"
+    assert ds.get_reference_answer(0) == "42" and ds.get_reference_answer(1) == "\\frac{1}{2}"
+    assert D.deepmath_accuracy("so the answer is \\boxed{42}", "42") == 1.0
+    assert D.deepmath_accuracy("<think>hm</think> \\boxed{0.5}", "\\frac{1}{2}") == 1.0
+    assert D.deepmath_accuracy("no box here", "42") == 0.0 and D.deepmath_accuracy("\\boxed{41}", "42") == 0.0
+    multi = D.render_chatml([{"role": "user", "content": "a"},
+                             {"role": "assistant", "content": "<think>long</think>\n\nshort"},
+                             {"role": "user", "content": "b"}, {"role": "assistant", "content": ""}], open_thinking=False)
+    assert "long" not in multi and multi.endswith("<|im_start|>assistant\n") and "short<|im_end|>" in multi
