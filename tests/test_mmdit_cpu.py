@@ -122,5 +122,5 @@ def test_mmdit_trains_through_the_flow_matching_trainer(tmp_path):
     batch = [{"latents": (base + 0.05 * torch.randn(4, 8, 8, generator=g)).tolist(),
               "text_embeds": torch.randn(4, 64, generator=g).tolist()} for _ in range(8)]
     torch.manual_seed(0)
-    losses = [tr.step_training(batch, total_steps=40, train_step=i + 1)["train/loss_avg"] for i in range(40)]
-    assert sum(losses[-5:]) / 5 < 0.8 * sum(losses[:5]) / 5, (losses[:5], losses[-5:])
+    losses = [tr.step_training(batch, total_steps=100, train_step=i + 1)["train/loss_avg"] for i in range(100)]
+    assert sum(losses[-10:]) < 0.6 * sum(losses[:10]), (losses[:10], losses[-10:])      # measured: 0.27
