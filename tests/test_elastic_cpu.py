@@ -104,7 +104,7 @@ def test_rollout_replica_joins_a_running_job(tmp_path):
     port = s.getsockname()[1]
     s.close()
     env = dict(os.environ, COSMOS_LOG_LEVEL="INFO", COSMOS_HEARTBEAT_SEND_INTERVAL="1", COSMOS_ROLLOUT_SCAN_INTERVAL="1",
-               COSMOS_NCCL_TIMEOUT_MS="30000", PYTHONPATH=ROOT, OMP_NUM_THREADS="2", E2E_N_PROMPTS="48")   # 6 steps of 32
+               COSMOS_NCCL_TIMEOUT_MS="30000", PYTHONPATH=ROOT, OMP_NUM_THREADS="2", E2E_N_PROMPTS="96")   # 12 steps of 32: long enough for the newcomer to come up on a fast machine
     base = [sys.executable, "-m", "cosmos_rl_b200.launcher.launch_all", "--config", str(cfg), "--cpu"]
     first = subprocess.Popen(base + ["--policy", "1", "--rollout", "1", "--port", str(port), "--rdzv-port", "29821",
                                      "--log-dir", str(tmp_path / "logs_a"), os.path.join(HERE, "e2e_script.py")],
