@@ -27,6 +27,8 @@ _MOVED = {
     "policy.model.gpt": "models.gpt",
     "utils.ulysses": "parallel.context_parallel",
     "utils.trace": "utils.trace",
+    "dispatcher.algo.base": "dispatcher.algo.grpo",
+    "utils.distributed": "utils.dist_util",
 }
 
 

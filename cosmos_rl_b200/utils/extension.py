@@ -11,14 +11,23 @@ _LOCAL_CONFIGS: Dict[str, Callable[[str], Dict[str, Any]]] = {}
 _PARALLELISM: Dict[str, Callable] = {}
 
 
-def register_tokenizer_loader(prefix: str, loader: Callable[[str], Any]) -> None:
-    """``loader(model_name_or_path)`` is used for model names starting with ``prefix`` (return None for no tokenizer)."""
+def register_tokenizer_loader(prefix, loader: Callable[[str], Any]) -> None:
+    """``loader(model_name_or_path)`` is used for model names starting with ``prefix``, or, when ``prefix`` is a
+    callable, for names it returns true for (the reference's ``predicate`` form). Return None for no tokenizer."""
     _TOKENIZER_LOADERS[prefix] = loader
+
+
+def clear_tokenizer_loaders() -> None:
+    _TOKENIZER_LOADERS.clear()
 
 
 def load_tokenizer(name_or_path: str):
     for prefix, fn in _TOKENIZER_LOADERS.items():
-        if name_or_path.startswith(prefix):
+        try:
+            hit = bool(prefix(name_or_path)) if callable(prefix) else (name_or_path or "").startswith(prefix)
+        except Exception:  # noqa: BLE001  (a predicate that cannot judge this name does not match it)
+            hit = False
+        if hit:
             return fn(name_or_path), True
     return None, False
 

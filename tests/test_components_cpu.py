@@ -594,3 +594,62 @@ def test_launcher_plan_over_nodes_and_machine_identity(monkeypatch):
     assert host_id() == "machine-a" and group_on_one_host()
     monkeypatch.delenv("COSMOS_HOST_ID")
     assert ":" in host_id()
+
+
+def test_reference_import_paths_for_user_scripts(tmp_path):
+    """Entry scripts written for the reference import helpers from ``cosmos_rl.utils.util`` and register algorithms
+    through ``cosmos_rl.dispatcher.algo.base``: those paths resolve to this package, with the reference's calling
+    conventions (predicate-form tokenizer loaders, both ``setup`` signatures, bare and parametrised ``retry``)."""
+    import warnings
+    from cosmos_rl.dispatcher.algo.base import RuleBasedAlgo, register_rule_based_algo   # noqa: F401
+    from cosmos_rl.utils import util
+    from cosmos_rl.utils.util import call_setup, clear_tokenizer_loaders, register_tokenizer_loader, setup_tokenizer
+    from cosmos_rl_b200.config import Config
+    register_tokenizer_loader(lambda p: p.endswith(".toml"), lambda p: "no-op tokenizer")
+    try:
+        setup_tokenizer.cache_clear()
+        assert setup_tokenizer("job.toml") == "no-op tokenizer" and setup_tokenizer("tiny-qwen2") is None
+    finally:
+        clear_tokenizer_loaders()
+        setup_tokenizer.cache_clear()
+
+    class New:
+        def setup(self, config):
+            self.config = config
+
+    class Old:
+        def setup(self, config, tokenizer):
+            self.config, self.tokenizer = config, tokenizer
+
+    c = Config.from_dict({"policy": {"model_name_or_path": "tiny-qwen2"}})
+    a, b = New(), Old()
+    call_setup(a, c)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        call_setup(b, c)
+    call_setup(object(), c)                                      # nothing to set up
+    assert a.config is c and b.config is c and b.tokenizer is None
+    x, idx = torch.randn(4, 10), torch.tensor([1, 5, 0, 9])
+    want = torch.log_softmax(x, -1).gather(-1, idx[:, None])[:, 0]
+    assert torch.allclose(util.selective_log_softmax(x, idx), want, atol=1e-6)
+    assert torch.allclose(util.entropy_from_logits_with_chunking(x, 3), util.entropy_from_logits(x))
+    calls = {"n": 0}
+
+    @util.retry(max_retry=3, max_delay=0.01)
+    def flaky():
+        calls["n"] += 1
+        if calls["n"] < 3:
+            raise RuntimeError("not yet")
+        return calls["n"]
+
+    assert flaky() == 3 and util.retry(lambda: 7)() == 7
+    assert util.b64_to_list(util.list_to_b64([1, -2, 300])) == [1, -2, 300]
+    assert float(util.masked_mean(torch.tensor([1.0, 2.0, 3.0]), torch.tensor([1, 0, 1]))) == 2.0
+    assert util.str2torch_dtype("bfloat16") is torch.bfloat16 and util.basename_from_modelpath("/a/b/Qwen/") == "Qwen"
+    util.write_json_file({"a": [1, 2]}, str(tmp_path / "x.json"))
+    assert util.read_json_file(str(tmp_path / "x.json")) == {"a": [1, 2]}
+    assert util.sanitize({"t": torch.tensor(2.5), "l": (torch.ones(2), "s")}) == {"t": 2.5, "l": [[1.0, 1.0], "s"]}
+    tr, va = util.split_train_n_val_dataset(list(range(10)), 0.2)
+    assert tr == list(range(8)) and va == [8, 9]
+    rep = util.aggregate_report_data([{"train/loss_avg": 1.0, "train/loss_max": 2.0}, {"train/loss_avg": 3.0, "train/loss_max": 5.0}])
+    assert rep == {"train/loss_avg": 2.0, "train/loss_max": 5.0}
