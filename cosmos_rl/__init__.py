@@ -29,6 +29,20 @@ _MOVED = {
     "utils.trace": "utils.trace",
     "dispatcher.algo.base": "dispatcher.algo.grpo",
     "utils.distributed": "utils.dist_util",
+    "utils.tools_use.hermes_tool_parser": "utils.tools_use",
+    "utils.tools_use.schema": "utils.tools_use",
+    "utils.tools_use.base_tool": "utils.tools_use",
+    "utils.tools_use.base_tool_parser": "utils.tools_use",
+    "utils.tools_use.tool_agent": "utils.tools_use",
+    "rollout.schema": "rollout.base",
+    "policy.trainer.llm_trainer": "policy.trainer",
+    "policy.trainer.llm_trainer.grpo_trainer": "policy.trainer.grpo_trainer",
+    "policy.trainer.llm_trainer.sft_trainer": "policy.trainer.sft_trainer",
+    "policy.trainer.llm_trainer.dpo_trainer": "policy.trainer.dpo_trainer",
+    "policy.trainer.llm_trainer.llm_trainer": "policy.trainer.llm_trainer",
+    "dispatcher.data.packer.tensor_data_packer": "data.packer",
+    "dispatcher.data.packer.trajectory_packer": "data.packer",
+    "dispatcher.data.packer.hf_vlm_data_packer": "data.packer",
 }
 
 

@@ -11,7 +11,8 @@ import re
 from typing import Any, Callable, Dict, List, Optional, Tuple
 
 Conversation = List[Dict[str, Any]]
-_CALL = re.compile(r"<tool_call>\s*(\{.*?\})\s*</tool_call>", re.DOTALL)
+# the body never crosses a closing tag, so a malformed block cannot swallow the well-formed one after it
+_CALL = re.compile(r"<tool_call>\s*((?:(?!</tool_call>).)*?)\s*</tool_call>", re.DOTALL)
 
 
 class ToolRegistry:

@@ -308,3 +308,65 @@ class OpenVLADataPacker(HFVLMDataPacker):
 
 
 BaseDataPacker.register(["openvla"], OpenVLADataPacker)
+
+
+DataPacker = BaseDataPacker       # the name language-model packers of user scripts derive from
+
+
+class TensorDataPacker(BaseDataPacker):
+    """Packer for rollouts that are tensor trajectories instead of text (control tasks, simulators; the reference's
+    cosmos_rl/dispatcher/data/packer/tensor_data_packer.py:69). Everything passes through: the data set's sample is the
+    rollout engine's input, the engine's trajectory dict is the trainer's per-episode payload, and a batch is the list
+    of those dicts (episodes have different lengths; the trainer knows how to pad or pack for its algorithm). No
+    tokenizer is needed. Subclasses override single hooks, e.g. ``get_rollout_input`` to parse initial conditions, or
+    ``get_rollout_output`` / ``get_policy_input`` to swap tensors for references to a transport."""
+
+    def get_rollout_input(self, item: Any, **kw) -> Any:
+        return item
+
+    def get_rollout_output(self, items: List[Any], completed_conversations=None, logprobs=None, token_ids=None, **kw):
+        return items
+
+    def get_policy_input(self, sample: Any, rollout_output: Any, n_ignore_prefix_tokens: int = 0, **kw) -> Any:
+        return rollout_output
+
+    def policy_compute_max_len(self, processed: List[Any]) -> int:
+        return max((int(p.get("episode_length", 0)) if isinstance(p, dict) else 0 for p in processed), default=0)
+
+    def policy_collate_fn(self, processed: List[Any], computed_max_len: int = 0) -> List[Any]:
+        return list(processed)
+
+    def batch_size(self, batch) -> int:
+        return len(batch)
+
+    def slice_batch(self, batch, start: int, end: int):
+        return batch[start:end]
+
+
+class TrajectoryPacker:
+    """Contract of packers whose rollouts hold several trainable transitions under one envelope (one prompt index, one
+    group-relative advantage): ``num_transitions`` and ``iter_transitions`` are the packer's to write; chunks and
+    batches of rollouts have defaults. The methods describe STRUCTURE only: they never scale advantages or weights
+    (loss aggregation is the trainer's), and ``num_transitions(r) == len(list(iter_transitions(r)))``
+    (cosmos_rl/dispatcher/data/packer/trajectory_packer.py:37; ``policy/trainer/trajectory_mixin.py`` consumes it)."""
+
+    def num_transitions(self, rollout) -> int:
+        raise NotImplementedError
+
+    def iter_transitions(self, rollout):
+        raise NotImplementedError
+
+    def iter_chunks(self, rollout, chunk_size: int):
+        """Consecutive runs of at most ``chunk_size`` transitions, in order."""
+        chunk: List[Any] = []
+        for t in self.iter_transitions(rollout):
+            chunk.append(t)
+            if len(chunk) == chunk_size:
+                yield chunk
+                chunk = []
+        if chunk:
+            yield chunk
+
+    def iter_rollouts(self, rollouts):
+        """Batches of rollouts in the order the trainer should walk them (default: one batch with all)."""
+        yield list(rollouts)

@@ -27,6 +27,14 @@ class WeightMapper:
         return name
 
 
+class IdentityWeightMapper(WeightMapper):
+    """For families whose checkpoints are stored under the framework's own parameter names (custom policies of
+    non-language workloads): every tensor maps to itself."""
+
+    def hf_names(self, local: str) -> List[str]:
+        return [local]
+
+
 class ModelRegistry:
     _models: Dict[str, Type["BaseModel"]] = {}
     _mappers: Dict[str, Type[WeightMapper]] = {}

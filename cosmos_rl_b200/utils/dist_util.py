@@ -79,3 +79,11 @@ def group_on_one_host(group=None) -> bool:
     ids = [None] * dist.get_world_size(group)
     dist.all_gather_object(ids, host_id(), group=group)
     return len(set(ids)) == 1
+
+
+def __getattr__(name: str):
+    # the reference's name for the fault-tolerant communicator between policy replicas
+    if name == "HighAvailabilitylNccl":
+        from ..parallel.inter_replica import InterReplicaComm
+        return InterReplicaComm
+    raise AttributeError(name)

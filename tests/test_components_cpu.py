@@ -653,3 +653,86 @@ def test_reference_import_paths_for_user_scripts(tmp_path):
     assert tr == list(range(8)) and va == [8, 9]
     rep = util.aggregate_report_data([{"train/loss_avg": 1.0, "train/loss_max": 2.0}, {"train/loss_avg": 3.0, "train/loss_max": 5.0}])
     assert rep == {"train/loss_avg": 2.0, "train/loss_max": 5.0}
+
+
+def test_object_style_tools_and_tensor_packers():
+    """The extension API in the reference's object form: tools as classes with a derived schema, the Hermes parser, the
+    agent that runs parsed calls (failures become responses the model can read) and mounts the tools into the
+    multi-turn rollout's registry; the pass-through tensor packer and the trajectory packer contract."""
+    from cosmos_rl.dispatcher.data.packer.tensor_data_packer import TensorDataPacker
+    from cosmos_rl.dispatcher.data.packer.trajectory_packer import TrajectoryPacker
+    from cosmos_rl.policy.model.base import IdentityWeightMapper
+    from cosmos_rl.utils.tools_use import BaseTool, OpenAIFunctionToolSchema, ToolAgent, ToolResponse
+    from cosmos_rl.utils.tools_use.hermes_tool_parser import HermesToolParser
+    from cosmos_rl_b200.data.multi_turn import ToolRegistry, extend_conversation
+
+    class Add(BaseTool):
+        def function(self, a: int, b: int = 1) -> ToolResponse:
+            """Add two integers.
+
+            a: the first term
+            b: the second term
+            """
+            return ToolResponse(text=str(a + b))
+
+    class Check(BaseTool):
+        def __init__(self, name):
+            super().__init__(name)
+            self.truth = None
+
+        from contextlib import contextmanager
+
+        @contextmanager
+        def tool_context(self, ground_truth=None):
+            self.truth = ground_truth
+            try:
+                yield self
+            finally:
+                self.truth = None
+
+        def function(self, guess: str) -> ToolResponse:
+            return ToolResponse(text="right" if guess == self.truth else "wrong")
+
+    add = Add("add")
+    sch = add.tool_schema
+    assert isinstance(sch, OpenAIFunctionToolSchema) and sch.function.name == "add"
+    assert sch.function.description == "Add two integers." and sch.function.parameters.required == ["a"]
+    assert sch.function.parameters.properties["b"].type == "integer"
+    assert sch.function.parameters.properties["a"].description == "the first term"
+    agent = ToolAgent(HermesToolParser(), [add, Check("check")])
+    text = ('let me see <tool_call>{"name": "add", "arguments": {"a": 2, "b": 5}}</tool_call> and '
+            '<tool_call>{"name": "check", "arguments": {"guess": "7"}}</tool_call><tool_call>{broken</tool_call>'
+            '<tool_call>{"name": "nope", "arguments": {}}</tool_call><tool_call>{"name": "add", "arguments": {"x": 1}}</tool_call>')
+    content, calls = agent.tool_parser.extract_tool_calls(text)
+    assert [c.name for c in calls] == ["add", "check", "nope", "add"] and "<tool_call>" not in content
+    out = agent.call_tools(text, ground_truth="7")
+    assert [r.text for r in out[:2]] == ["7", "right"] and "unknown tool" in out[2].text and "error" in out[3].text
+    assert agent.call_tools("no calls here") is None and HermesToolParser().extract_tool_calls("plain")[0] == "plain"
+    assert [s["function"]["name"] for s in agent.tool_schemas()] == ["add", "check"]
+    ToolRegistry.clear()
+    try:
+        agent.mount()
+        conv, done = extend_conversation([{"role": "user", "content": "2+5?"}],
+                                         '<tool_call>{"name": "add", "arguments": {"a": 2, "b": 5}}</tool_call>', True)
+        assert not done and conv[-1] == {"role": "tool", "name": "add", "content": "7"}
+        assert {s["function"]["name"] for s in ToolRegistry.schemas()} == {"add", "check"}
+    finally:
+        ToolRegistry.clear()
+    # packers
+    pk = TensorDataPacker()
+    pk.setup(None)
+    traj = {"observations": torch.zeros(5, 3), "episode_length": 5}
+    assert pk.get_rollout_input({"seed": 3}) == {"seed": 3} and pk.get_policy_input(None, traj) is traj
+    batch = pk.policy_collate_fn([traj, dict(traj, episode_length=2)], 0)
+    assert pk.policy_compute_max_len(batch) == 5 and pk.batch_size(batch) == 2 and pk.slice_batch(batch, 1, 2) == batch[1:]
+
+    class Steps(TrajectoryPacker):
+        def num_transitions(self, r):
+            return len(r)
+
+        def iter_transitions(self, r):
+            return iter(r)
+
+    s = Steps()
+    assert [len(c) for c in s.iter_chunks(list(range(7)), 3)] == [3, 3, 1] and list(s.iter_rollouts([1, 2])) == [[1, 2]]
+    assert IdentityWeightMapper({}).hf_names("expert.blocks.0.w") == ["expert.blocks.0.w"]
