@@ -35,6 +35,7 @@ _MOVED = {
     "utils.tools_use.base_tool_parser": "utils.tools_use",
     "utils.tools_use.tool_agent": "utils.tools_use",
     "rollout.schema": "rollout.base",
+    "utils.model_config": "utils.extension",
     "policy.trainer.llm_trainer": "policy.trainer",
     "policy.trainer.llm_trainer.grpo_trainer": "policy.trainer.grpo_trainer",
     "policy.trainer.llm_trainer.sft_trainer": "policy.trainer.sft_trainer",

@@ -117,3 +117,27 @@ def math_equal(prediction: str, reference: str, rel_tol: float = 1e-4, allow_per
     if len(a) > 64 or len(b) > 64:
         return False
     return _symbolic_equal(a, b)
+
+
+# ---- names of the reference's grader that data set scripts import (cosmos_rl/tools/eval_utils/grader.py:448-540)
+def math_answer_cleaning(answer: str) -> str:
+    return normalize_answer(str(answer))
+
+
+def is_equal_after_calculation(extracted_answer: str, gold: str) -> bool:
+    """Equal as numbers once fractions and arithmetic are evaluated."""
+    a, b = _to_number(normalize_answer(str(extracted_answer))), _to_number(normalize_answer(str(gold)))
+    if a is None or b is None:
+        return _symbolic_equal(str(extracted_answer), str(gold))
+    return abs(a - b) <= 1e-6 * max(1.0, abs(b))
+
+
+def round_number(answer: str) -> str:
+    """Numbers below 0.01 in magnitude are kept to two significant figures (so 0.00123456 compares as 0.0012)."""
+    try:
+        v = float(answer)
+    except (TypeError, ValueError):
+        return answer
+    if v != 0 and abs(v) < 0.01:
+        return f"{v:.2g}"
+    return answer

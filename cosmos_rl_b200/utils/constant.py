@@ -18,6 +18,8 @@ COSMOS_ROLLOUT_PROMPT_QUEUE_MAX_SIZE = env_int("COSMOS_ROLLOUT_PROMPT_QUEUE_MAX_
 COSMOS_WEIGHT_GATE_SLEEP = env_float("COSMOS_WEIGHT_GATE_SLEEP", 0.05)
 COSMOS_WEIGHT_SYNC_CHECK = env_int("COSMOS_WEIGHT_SYNC_CHECK", 0)   # verify the first policy-to-rollout transfer
 COSMOS_DEFAULT_MODEL_TYPE = "hfmodel"
+import os as _os  # noqa: E402
+CACHE_DIR = _os.environ.get("COSMOS_CACHE", _os.path.join(_os.path.expanduser("~"), ".cache", "cosmos"))
 
 RedisStreamConstant = type("RedisStreamConstant", (), {
     "CMD_FETCH_SIZE": 5, "ROLLOUT_FETCH_SIZE": 8, "STREAM_MAXLEN": 10000, "CMD_READING_TIMEOUT_MS": 500,

@@ -736,3 +736,30 @@ def test_object_style_tools_and_tensor_packers():
     s = Steps()
     assert [len(c) for c in s.iter_chunks(list(range(7)), 3)] == [3, 3, 1] and list(s.iter_rollouts([1, 2])) == [[1, 2]]
     assert IdentityWeightMapper({}).hf_names("expert.blocks.0.w") == ["expert.blocks.0.w"]
+
+
+def test_small_compatibility_modules(tmp_path):
+    import os
+    import signal
+    from cosmos_rl.utils.dist_signal_handler import DistributedSignalHandler
+    from cosmos_rl.utils.model_config import register_local_model_config   # noqa: F401
+    from cosmos_rl.utils.modelscope import modelscope_load_dataset
+    from cosmos_rl.utils.no_op_tokenizer import NoOpTokenizer
+    from cosmos_rl_b200.tools.eval_utils import grader
+    from cosmos_rl_b200.utils import constant
+    tok = NoOpTokenizer()
+    assert tok.encode({"episode_length": torch.tensor(7)}) == [0] * 7 and tok.encode("x") == [0]
+    assert tok({"episode_length": 3})["input_ids"].shape == (1, 3) and tok.decode([1, 2]) == "" and tok.pad_token_id == 2
+    assert tok.batch_decode([[1], [2]]) == ["", ""]
+    before = signal.getsignal(signal.SIGUSR1)
+    with DistributedSignalHandler(["SIGUSR1"]) as h:
+        assert h.signals_received() == [False]
+        os.kill(os.getpid(), signal.SIGUSR1)
+        assert h.signals_received() == [True]
+    assert signal.getsignal(signal.SIGUSR1) == before and h.released
+    with pytest.raises(RuntimeError):
+        modelscope_load_dataset("org/some-hub-dataset")
+    assert grader.is_equal_after_calculation("\\frac{1}{2}", "0.5") and not grader.is_equal_after_calculation("3", "4")
+    assert grader.round_number("0.00123456") == "0.0012" and grader.round_number("12.5") == "12.5"
+    assert grader.math_answer_cleaning(" \\text{42} ") == grader.normalize_answer(" \\text{42} ")
+    assert isinstance(constant.CACHE_DIR, str) and constant.CACHE_DIR
