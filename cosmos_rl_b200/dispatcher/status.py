@@ -470,6 +470,7 @@ class RolloutStatusManager(_ManagerBase):
         super().__init__(config, broker)
         self.policy_manager: Optional[PolicyStatusManager] = None
         self.had_replicas = False
+        self.left_after_end = 0
         self.ended: set = set()
         self.stop_broadcast_sent = False
         self.adopted_versions: Dict[str, int] = {}
@@ -581,6 +582,8 @@ class RolloutStatusManager(_ManagerBase):
     def unregister(self, name: str) -> None:
         with self.lock:
             rep = self.replicas.pop(name, None)
+            if name in self.ended:
+                self.left_after_end += 1        # it had reported the end of its prompt stream: a regular exit
             self.ended.discard(name)
             if rep is not None and rep.in_mesh:
                 survivors = [r for r in self.live() if r.in_mesh]
@@ -593,8 +596,13 @@ class RolloutStatusManager(_ManagerBase):
             self.ended.add(name)
 
     def all_ended(self) -> bool:
+        """Every rollout replica has reported the end of its prompt stream. Replicas that reported it and then left
+        count too: with nobody left to generate, a policy whose buffer runs short of a step (rollouts dropped as
+        outdated, say) must be told that training is over instead of waiting for data that will never come."""
         live = self.live()
-        return bool(live) and all(r.name in self.ended for r in live)
+        if live:
+            return all(r.name in self.ended for r in live)
+        return self.left_after_end > 0
 
     def note_adopted_version(self, name: str, version: int) -> None:
         self.adopted_versions[name] = max(version, self.adopted_versions.get(name, -1))

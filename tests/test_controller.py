@@ -355,3 +355,28 @@ def test_job_that_lost_every_rollout_replica_is_ended_in_order(monkeypatch):
     assert [x.command_type for x in last] == [cmd.CommandType.TRAINING_COMPLETE]
     c.monitor_once(now + 200)                                             # nothing is sent twice
     assert len(_commands(c, "p0")) == n0 + 1
+
+
+def test_training_completes_when_the_rollout_side_left_and_the_buffer_runs_short():
+    """The rollout replica reports the end of its prompt stream and leaves while a step is still training; some of its
+    rollouts never made it into the buffer (dropped as outdated, say), so the planned number of steps cannot be reached.
+    When the running step is acknowledged the policy must be told that training is over, not left waiting for data."""
+    c = Controller(_config(), dataset=SyntheticTokenDataset(8, 8, 100))       # 8 prompts * 4 / 8 = 4 planned steps
+    _reg(c, "p0", "POLICY")
+    _reg(c, "r0", "ROLLOUT")
+    pm = c.policy_status_manager
+    assert pm.total_steps == 4
+    batch, _ = c.get_batched_prompt(2)
+    c.put_rollouts("r0", [_payload(i, 0) for i, _ in batch], is_end=False)        # step 1 is dispatched
+    assert pm.current_step == 1
+    more, _ = c.get_batched_prompt(1)
+    c.put_rollouts("r0", [_payload(i, 0) for i, _ in more], is_end=True)          # half a step, then the stream ends
+    assert len(pm.rollout_buffer) == 4 and not pm.complete_sent                   # step 1 is still running
+    c.unregister("r0")                                                            # regular exit after the end report
+    assert c.rollout_status_manager.all_ended()
+    n0 = len(_commands(c, "p0"))
+    c.train_ack("p0", 1, 4, False, {"train/loss_avg": 0.5})
+    new = _commands(c, "p0")[n0:]
+    assert [x.command_type for x in new] == [cmd.CommandType.TRAINING_COMPLETE] and pm.complete_sent
+    assert not c._check_rollout_starvation(time.time() + 10_000)                  # an orderly end, not a starved job
+    assert c.failed is None

@@ -288,7 +288,7 @@ def test_flow_grpo_job_with_separate_rollout_and_policy_processes(tmp_path):
            "train": {"seed": 0, "epoch": 1, "optm_lr": 2e-3, "optm_warmup_steps": 0, "optm_weight_decay": 0.0,
                      "output_dir": str(tmp_path / "out"), "train_batch_per_replica": 16,
                      "train_policy": {"type": "grpo", "trainer_type": "flow_grpo", "mini_batch": 8,
-                                      "dataloader_shuffle": False, "allowed_outdated_steps": 1},
+                                      "dataloader_shuffle": False},   # default staleness bound (4): nothing is dropped in 4 steps
                      "ckpt": {"enable_checkpoint": False}},
            "logging": {"logger": ["console"]}}
     cfg = tmp_path / "job.toml"
