@@ -39,6 +39,21 @@ def _worker_setup(role: str):
     return config, dims, device, api
 
 
+def _leave(ok: bool) -> None:
+    """End a worker PROCESS that finished its work and shut down in order (checkpoints finalised, communicators
+    aborted, process group destroyed) without running interpreter teardown: communication libraries keep helper
+    threads whose destruction order at exit is not defined, and a process that did all its work must not end in an
+    abort raised there. Only in processes the launcher started (``COSMOS_ROLE`` set); ``COSMOS_HARD_EXIT=0`` keeps the
+    ordinary exit."""
+    if not ok or not os.environ.get("COSMOS_ROLE") or os.environ.get("COSMOS_HARD_EXIT", "1") == "0":
+        return
+    import logging
+    logging.shutdown()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
 def _tokenizer(config):
     path = config.policy.model_name_or_path
     from ..utils.extension import load_tokenizer
@@ -69,14 +84,17 @@ def policy_entry(dataset=None, val_dataset=None, data_packer=None, val_data_pack
         worker = RLPolicyWorker(config, dims, dataset=dataset, val_dataset=val_dataset, data_packer=data_packer,
                                 val_data_packer=val_data_packer, hook_fns=hook_fns, api=api, device=device,
                                 tokenizer=_tokenizer(config))
+    ok = False
     try:
         worker.execute()
+        ok = True
     finally:
         worker.handle_shutdown()
         from ..parallel.dyncomm import abort_all
         from ..utils.dist_util import safe_destroy
         abort_all()
         safe_destroy()
+    _leave(ok)
 
 
 def rollout_entry(dataset=None, val_dataset=None, data_packer=None, val_data_packer=None, reward_fns=None,
@@ -87,14 +105,17 @@ def rollout_entry(dataset=None, val_dataset=None, data_packer=None, val_data_pac
         config, dims, dataset=dataset, val_dataset=val_dataset, data_packer=data_packer,
         val_data_packer=val_data_packer, reward_fns=reward_fns, filter_reward_fns=filter_reward_fns,
         val_reward_fns=val_reward_fns, api=api, device=device, tokenizer=_tokenizer(config))
+    ok = False
     try:
         worker.work()
+        ok = True
     finally:
         worker.handle_shutdown()
         from ..parallel.dyncomm import abort_all
         from ..utils.dist_util import safe_destroy
         abort_all()
         safe_destroy()
+    _leave(ok)
 
 
 def reference_entry(**kw):
