@@ -232,3 +232,30 @@ def test_deepmath_distillation_dataset_renders_the_open_thinking_prompt():
                              {"role": "assistant", "content": "<think>long</think>\n\nshort"},
                              {"role": "user", "content": "b"}, {"role": "assistant", "content": ""}], open_thinking=False)
     assert "long" not in multi and multi.endswith("<|im_start|>assistant\n") and "short<|im_end|>" in multi
+
+
+def test_vision_language_preference_dataset(tmp_path):
+    import json
+    from cosmos_rl_b200.tools.dataset.vlm_dpo import VLMPreferenceDataset, to_pair
+    rows = [{"image": "a.jpg", "question": "What is shown?", "chosen": "A cat.", "rejected": "A dog."},
+            {"image": ["b.jpg", "c.jpg"], "question": "Same?", "chosen": "yes", "rejected": "yes"},          # no preference
+            {"image": "d.jpg", "question": "Count.", "chosen": [{"role": "assistant", "content": "three"}],
+             "rejected": [{"role": "assistant", "content": "four"}]},
+            {"image": "e.jpg", "question": "Colour?", "chosen": "red", "rejected": ""}]
+    ds = VLMPreferenceDataset(rows, root=str(tmp_path))
+    assert len(ds) == 2 and ds.n_skipped == 2
+    first = ds[0]
+    assert first["chosen"] == "A cat." and first["rejected"] == "A dog."
+    content = first["prompt"][0]["content"]
+    assert content[0] == {"type": "image", "image": str(tmp_path / "a.jpg")} and content[1]["text"] == "What is shown?"
+    assert ds[1]["chosen"] == "three" and ds[1]["rejected"] == "four" and all(m["role"] != "assistant" for m in ds[1]["prompt"])
+    assert to_pair(rows[1], "") is None and len(VLMPreferenceDataset(rows, max_pairs=1)) == 1
+    # rows from a file named by the job config
+    f = tmp_path / "pairs.jsonl"
+    f.write_text("\n".join(json.dumps(r) for r in rows))
+    from cosmos_rl_b200.config import Config
+    cfg = Config.from_dict({"policy": {"model_name_or_path": "tiny-qwen2"},
+                            "train": {"train_policy": {"type": "sft", "trainer_type": "dpo", "dataset": {"name": str(f)}}}})
+    lazy = VLMPreferenceDataset()
+    lazy.setup(cfg)
+    assert len(lazy) == 2 and lazy.root == str(tmp_path)
