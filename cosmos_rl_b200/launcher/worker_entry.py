@@ -122,10 +122,13 @@ def reference_entry(**kw):
     config, dims, device, api = _worker_setup("REFERENCE")
     from ..reference.teacher_worker import TeacherWorker
     worker = TeacherWorker(config, dims, api=api, device=device)
+    ok = False
     try:
         worker.execute()
+        ok = True
     finally:
         worker.handle_shutdown()
+    _leave(ok)
 
 
 def colocated_entry(dataset=None, val_dataset=None, data_packer=None, reward_fns=None, custom_logger_fns=None, **kw):
